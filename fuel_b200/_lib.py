@@ -1,0 +1,66 @@
+"""ctypes binding of libfuelq.so (the C ABI declared in include/fuelq.h).
+
+There is no fallback: if the shared library is missing or a symbol is absent the
+import fails, and every call that returns a non-zero status raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfuelq.so")
+
+OK, MISALIGNED, INVALID_PROBLEM, NOT_SUPPORTED, WORKSPACE, LAUNCH_FAILURE = range(6)
+OPT_PDL, OPT_DECODE_MAX_M, OPT_DECODE_GRID = 1, 2, 3
+
+_i32, _i64, _vp, _sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
+
+# name -> (restype, argtypes); must list every symbol include/fuelq.h declares
+PROTOTYPES = {
+    "fuelq_status_string": (ctypes.c_char_p, [_i32]),
+    "fuelq_block_elems": (_i32, [_i32]),
+    "fuelq_block_bytes": (_i32, [_i32]),
+    "fuelq_set_option": (_i32, [_i32, _i64]),
+    "fuelq_get_option": (_i64, [_i32]),
+    "fuelq_device_error": (_i32, [ctypes.POINTER(_i32), _i32]),
+    "fuelq_quantize_act": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp]),
+    "fuelq_act_packed_bytes": (_sz, [_i32, _i64, _i64]),
+    "fuelq_quantize_act_packed": (_i32, [_i32, _i64, _i64, _vp, _vp, _sz, _vp]),
+    "fuelq_qmatmul_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
+    "fuelq_qmatmul_can_implement": (_i32, [_i32, _i64, _i64, _i64]),
+    "fuelq_qmatmul": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "fuelq_qmatmul_packed": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "fuelq_dequantize": (_i32, [_i32, _i64, _vp, _vp, _i32, _vp]),
+}
+
+
+class FuelqError(RuntimeError):
+    def __init__(self, op: str, status: int, reason: str):
+        super().__init__(f"{op}: status {status} ({reason})")
+        self.status = status
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback for this library.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError if the build is stale
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def status_string(status: int) -> str:
+    return lib.fuelq_status_string(status).decode()
+
+
+def check(status: int, op: str) -> None:
+    if status != OK:
+        raise FuelqError(op, status, status_string(status))

@@ -1,0 +1,139 @@
+// Block -> float dequantization (f32 / f16 / bf16 out), the exact arithmetic of the
+// reference's to_float: Q4_K d1 = d*sc, y = d1*q - m1 with two roundings
+// (fuel-quantized/src/k_quants.rs:1595-1622); Q6_K (d*sc)*q left to right (:2158-2189);
+// Q8_0 q*d (:611-627); Q4_0 (nibble-8)*d (:177-197). Replaces the reference's
+// per-format dequantize FFI calls (fuel-cuda-backend/src/quantized.rs:58-124).
+// __fmul_rn / __fsub_rn keep the compiler from contracting into an fma.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "fq_common.cuh"
+
+namespace fq {
+
+template <typename T> __device__ __forceinline__ T cvt_out(float v);
+template <> __device__ __forceinline__ float cvt_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half cvt_out<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
+__device__ __forceinline__ uint32_t ldg_u32_2b(const uint8_t* p) { return ldg_u16(p) | (ldg_u16(p + 2) << 16); }
+
+// one thread per 16-byte nibble chunk: 16 low-nibble + 16 high-nibble elements
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q4k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 3;
+  const int cc = (int)(u & 7), g = cc >> 1, h = cc & 1;
+  const uint8_t* b = w + blk * Q4KL::kBytes;
+  const uint4 hdr = *reinterpret_cast<const uint4*>(b);
+  const uint4 qv = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 16 * cc);
+  const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
+  uint32_t scw, mnw;
+  if (g < 2) {
+    scw = hdr.y & 0x3f3f3f3fu;
+    mnw = hdr.z & 0x3f3f3f3fu;
+  } else {
+    scw = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+    mnw = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
+  }
+  const int sh = (g & 1) * 16;
+  const float d1 = __fmul_rn(d, (float)((scw >> sh) & 0xff)), m1 = __fmul_rn(dmin, (float)((mnw >> sh) & 0xff));
+  const float d2 = __fmul_rn(d, (float)((scw >> (sh + 8)) & 0xff)), m2 = __fmul_rn(dmin, (float)((mnw >> (sh + 8)) & 0xff));
+  T* out = y + blk * 256 + 64 * g + 16 * h;
+  const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const uint32_t byte = (qw[j] >> (8 * t)) & 0xff;
+      out[4 * j + t] = cvt_out<T>(__fsub_rn(__fmul_rn(d1, (float)(byte & 0xF)), m1));
+      out[32 + 4 * j + t] = cvt_out<T>(__fsub_rn(__fmul_rn(d2, (float)(byte >> 4)), m2));
+    }
+  }
+}
+
+// one thread per four consecutive l of one 128-half: 16 elements
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 4;
+  const int uu = (int)(u & 15), half = uu >> 3, l0 = (uu & 7) * 4;
+  const uint8_t* b = w + blk * Q6KL::kBytes;
+  const uint32_t ql_a = ldg_u32_2b(b + Q6KL::kOffQl + 64 * half + l0);
+  const uint32_t ql_b = ldg_u32_2b(b + Q6KL::kOffQl + 64 * half + 32 + l0);
+  const uint32_t qh = ldg_u32_2b(b + Q6KL::kOffQh + 32 * half + l0);
+  const float d = h2f_bits(ldg_u16(b + Q6KL::kOffD));
+  const int8_t* scp = reinterpret_cast<const int8_t*>(b + Q6KL::kOffScales + 8 * half + (l0 >> 4));
+  const float s[4] = {__fmul_rn(d, (float)scp[0]), __fmul_rn(d, (float)scp[2]), __fmul_rn(d, (float)scp[4]),
+                      __fmul_rn(d, (float)scp[6])};
+  T* out = y + blk * 256 + 128 * half + l0;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int a = (ql_a >> (8 * t)) & 0xff, c = (ql_b >> (8 * t)) & 0xff, hh = (qh >> (8 * t)) & 0xff;
+    const int q1 = ((a & 0xF) | ((hh & 3) << 4)) - 32;
+    const int q2 = ((c & 0xF) | (((hh >> 2) & 3) << 4)) - 32;
+    const int q3 = ((a >> 4) | (((hh >> 4) & 3) << 4)) - 32;
+    const int q4 = ((c >> 4) | (((hh >> 6) & 3) << 4)) - 32;
+    out[t] = cvt_out<T>(__fmul_rn(s[0], (float)q1));
+    out[t + 32] = cvt_out<T>(__fmul_rn(s[1], (float)q2));
+    out[t + 64] = cvt_out<T>(__fmul_rn(s[2], (float)q3));
+    out[t + 96] = cvt_out<T>(__fmul_rn(s[3], (float)q4));
+  }
+}
+
+// one thread per 8 elements of a 32-block (4 threads per block)
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q8_0_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 2;
+  const int part = (int)(u & 3);
+  const uint8_t* b = w + blk * Q8_0L::kBytes;
+  const float d = h2f_bits(ldg_u16(b));
+  T* out = y + blk * 32 + 8 * part;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t v = ldg_u16(b + Q8_0L::kOffQs + 8 * part + 2 * j);
+    out[2 * j] = cvt_out<T>(__fmul_rn((float)(int8_t)(v & 0xff), d));
+    out[2 * j + 1] = cvt_out<T>(__fmul_rn((float)(int8_t)(v >> 8), d));
+  }
+}
+
+// one thread per 4 bytes of nibbles: elements 4p..4p+3 and 16+4p..
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q4_0_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 2;
+  const int part = (int)(u & 3);
+  const uint8_t* b = w + blk * Q4_0L::kBytes;
+  const float d = h2f_bits(ldg_u16(b));
+  const uint32_t v = ldg_u32_2b(b + Q4_0L::kOffQs + 4 * part);
+  T* out = y + blk * 32 + 4 * part;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int byte = (v >> (8 * t)) & 0xff;
+    out[t] = cvt_out<T>(__fmul_rn((float)((byte & 0xF) - 8), d));
+    out[16 + t] = cvt_out<T>(__fmul_rn((float)((byte >> 4) - 8), d));
+  }
+}
+
+// Q8_K blocks back to f32 (x.d * q, k_quants.rs:2269-2280); one thread per 4 elements
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q8k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 6;
+  const int part = (int)(u & 63);
+  const uint8_t* b = w + blk * Q8KL::kBytes;
+  const float d = *reinterpret_cast<const float*>(b);
+  const uint32_t v = *reinterpret_cast<const uint32_t*>(b + Q8KL::kOffQs + 4 * part);
+  T* out = y + blk * 256 + 4 * part;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) out[t] = cvt_out<T>(__fmul_rn(d, (float)(int8_t)((v >> (8 * t)) & 0xff)));
+}
+
+}  // namespace fq

@@ -1,0 +1,166 @@
+// Shared definitions for the sm_100a quantized-matmul kernels: GGUF block layouts,
+// status codes, the internal activation layout, and thin PTX wrappers
+// (mbarrier, 1-D bulk TMA copies, programmatic dependent launch).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fq {
+
+// ---- status codes: the reference's FFI convention for kernel providers
+// (fuel-cuda-backend/src/baracuda/status.rs:5-12) plus one for a bounded wait that expired.
+enum Status : int32_t {
+  kOk = 0,
+  kMisaligned = 1,
+  kInvalidProblem = 2,
+  kNotSupported = 3,
+  kWorkspace = 4,
+  kLaunchFailure = 5,
+};
+
+// ---- GGUF type ids (fuel-ir/src/quantized.rs:35-75)
+enum GgmlType : int32_t { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ8_0 = 8, kQ4K = 12, kQ6K = 14, kQ8K = 15, kBF16 = 30 };
+
+constexpr int QK_K = 256;
+constexpr int QK_S = 32;
+
+// Byte layouts (fuel-quantized/src/k_quants.rs:56-169). Offsets only; the kernels
+// address blocks by byte because Q6_K / Q8_0 / Q4_0 rows are only 2-byte aligned.
+struct Q4_0L { static constexpr int kBytes = 18, kElems = 32, kOffD = 0, kOffQs = 2; };
+struct Q8_0L { static constexpr int kBytes = 34, kElems = 32, kOffD = 0, kOffQs = 2; };
+struct Q4KL { static constexpr int kBytes = 144, kElems = 256, kOffD = 0, kOffDmin = 2, kOffScales = 4, kOffQs = 16; };
+struct Q6KL { static constexpr int kBytes = 210, kElems = 256, kOffQl = 0, kOffQh = 128, kOffScales = 192, kOffD = 208; };
+struct Q8KL { static constexpr int kBytes = 292, kElems = 256, kOffD = 0, kOffQs = 4, kOffBsums = 260; };
+
+__host__ __device__ inline int block_elems(int t) {
+  switch (t) {
+    case kQ4_0: case kQ8_0: return 32;
+    case kQ4K: case kQ6K: case kQ8K: return 256;
+    default: return 0;
+  }
+}
+__host__ __device__ inline int block_bytes(int t) {
+  switch (t) {
+    case kQ4_0: return 18;
+    case kQ8_0: return 34;
+    case kQ4K: return 144;
+    case kQ6K: return 210;
+    case kQ8K: return 292;
+    default: return 0;
+  }
+}
+// The reference quantizes activations to the weight format's dot-product partner
+// (GgmlType::VecDotType, k_quants.rs:174,608,1372,1930): Q8_K for k-quants, Q8_0 otherwise.
+__host__ __device__ inline int act_type_for(int t) { return (t == kQ4K || t == kQ6K) ? kQ8K : kQ8_0; }
+
+// ---- internal activation layout ("packed"): the same numbers as the reference's
+// Q8_K / Q8_0 blocks, split into planes so every plane is 16-byte aligned:
+//   qs    int8  [m][k]
+//   d     f32   [m][k / act_block]      (for Q8_0: the f16-rounded scale widened to f32)
+//   bsums int16 [m][k / 16]             (Q8_K only)
+struct ActPlanes {
+  const int8_t* qs;
+  const float* d;
+  const int16_t* bsums;
+};
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+__host__ __device__ inline size_t act_packed_bytes(int weight_type, int64_t m, int64_t k) {
+  const int at = act_type_for(weight_type);
+  const int be = block_elems(at);
+  size_t b = align_up((size_t)m * k, 256) + align_up((size_t)m * (k / be) * 4, 256);
+  if (at == kQ8K) b += align_up((size_t)m * (k / 16) * 2, 256);
+  return b;
+}
+__host__ __device__ inline ActPlanes act_planes(void* base, int weight_type, int64_t m, int64_t k) {
+  const int at = act_type_for(weight_type);
+  const int be = block_elems(at);
+  uint8_t* p = (uint8_t*)base;
+  ActPlanes a;
+  a.qs = (const int8_t*)p;
+  p += align_up((size_t)m * k, 256);
+  a.d = (const float*)p;
+  p += align_up((size_t)m * (k / be) * 4, 256);
+  a.bsums = (at == kQ8K) ? (const int16_t*)p : nullptr;
+  return a;
+}
+
+// ---- device-side error word. A kernel whose bounded wait expires records where it
+// gave up here and returns; the host reads it with fuelq_device_error().
+enum DevErr : int { kErrNone = 0, kErrFullWait = 1, kErrEmptyWait = 2, kErrDrainWait = 3, kErrMmaWait = 4, kErrTmemWait = 5 };
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a
+// hardware-defined time slice) and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization
+// attribute may start before its predecessor finishes; it must not touch data the
+// predecessor writes until pdl_wait() returns. Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
+
+// unaligned-by-2 32-bit read from shared memory: two aligned words and a funnel shift
+__device__ __forceinline__ uint32_t lds_u32_2b(const uint8_t* p) {
+  const uint32_t a = smem_u32(p);
+  const uint32_t base = a & ~3u;
+  uint32_t lo, hi;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(lo) : "r"(base));
+  asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(hi) : "r"(base));
+  return __funnelshift_r(lo, hi, (a & 2u) * 8u);
+}
+__device__ __forceinline__ uint32_t lds_u16(const uint8_t* p) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(smem_u32(p)));
+  return v;
+}
+__device__ __forceinline__ float h2f_bits(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+// defined once: the library is a single translation unit
+__device__ int g_fq_dev_error = 0;
+__device__ __forceinline__ void record_dev_error(int code) { atomicCAS(&g_fq_dev_error, 0, code); }
+
+#endif  // __CUDACC__
+
+}  // namespace fq

@@ -1,0 +1,384 @@
+// libfuelq.so — C ABI over the sm_100a kernels (see include/fuelq.h for the contract).
+// Single translation unit: the kernels live in the .cuh files included below.
+#include "../../include/fuelq.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "decode.cuh"
+#include "dequantize.cuh"
+#include "fq_common.cuh"
+#include "quantize_act.cuh"
+
+namespace fq {
+
+namespace {
+
+struct Options {
+  int64_t pdl = 0;
+  int64_t decode_max_m = kDecodeMaxM;
+  int64_t decode_grid = 0;
+};
+Options g_opt;
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int max_smem_optin = 0;
+};
+DeviceInfo g_dev[64];
+
+bool device_info(DeviceInfo** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  DeviceInfo& d = g_dev[dev];
+  if (d.sm_count == 0) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
+    if (cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+      return false;
+  }
+  *out = &d;
+  return true;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+bool supported_weight(int t) { return t == kQ4_0 || t == kQ8_0 || t == kQ4K || t == kQ6K; }
+
+// launch with or without the programmatic-dependent-launch attribute
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ------------------------------------------------------------------ activation quantization
+int32_t quantize_act_impl(int weight_type, int64_t m, int64_t k, const float* x, void* ref_out, void* packed,
+                          cudaStream_t stream) {
+  if (!supported_weight(weight_type)) return kNotSupported;
+  const int at = act_type_for(weight_type);
+  const int be = block_elems(at);
+  if (m < 0 || k <= 0 || k % be) return kInvalidProblem;
+  if (m == 0) return kOk;
+  if (!x || (!ref_out && !packed)) return kInvalidProblem;
+  if (!aligned(x, 16)) return kMisaligned;
+  const int64_t total = m * k;
+  const int warps_per_cta = 8;
+  if (at == kQ8K) {
+    const int64_t nb = total / QK_K;
+    const dim3 grid((unsigned)((nb + warps_per_cta - 1) / warps_per_cta)), block(32 * warps_per_cta);
+    cudaError_t e;
+    if (ref_out) {
+      if (!aligned(ref_out, 4)) return kMisaligned;
+      e = launch(quantize_q8k_kernel<true>, grid, block, 0, stream, x, nb, (uint8_t*)ref_out, (int8_t*)nullptr,
+                 (float*)nullptr, (int16_t*)nullptr);
+    } else {
+      ActPlanes a = act_planes(packed, weight_type, m, k);
+      e = launch(quantize_q8k_kernel<false>, grid, block, 0, stream, x, nb, (uint8_t*)nullptr, (int8_t*)a.qs,
+                 (float*)a.d, (int16_t*)a.bsums);
+    }
+    return e == cudaSuccess ? kOk : kLaunchFailure;
+  }
+  const int64_t nb32 = total / QK_S;
+  const int64_t ng = (total + QK_K - 1) / QK_K;
+  const dim3 grid((unsigned)((ng + warps_per_cta - 1) / warps_per_cta)), block(32 * warps_per_cta);
+  cudaError_t e;
+  if (ref_out) {
+    if (!aligned(ref_out, 2)) return kMisaligned;
+    e = launch(quantize_q8_0_kernel<true>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)ref_out, (int8_t*)nullptr,
+               (float*)nullptr);
+  } else {
+    ActPlanes a = act_planes(packed, weight_type, m, k);
+    e = launch(quantize_q8_0_kernel<false>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)nullptr, (int8_t*)a.qs,
+               (float*)a.d);
+  }
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// ------------------------------------------------------------------ decode mat-vec
+struct DecodePlan {
+  int rows_per_stage, nseg, num_stages, stage_stride, grid;
+  size_t smem;
+};
+
+// Stage sizing: whole rows per stage; eight or more work items per stage so every consumer
+// warp has one. Short rows: a multiple of 8 rows. Long rows: fewer rows, each cut into
+// k-segments (4 rows x 2, 2 x 4, 1 x 8).
+int32_t plan_decode(int type, int64_t n, int64_t k, const DeviceInfo& di, DecodePlan* pl) {
+  const int row_bytes = (int)(k / block_elems(type) * block_bytes(type));
+  const size_t header = align_up(sizeof(DecodeSmemHeader), 128);
+  const size_t per_cta_budget = ((size_t)di.max_smem_optin + 1024) / 2 - 1024 - 512;  // two CTAs per SM
+  const size_t ring_budget = per_cta_budget - header;
+  const int stage_target = 24 * 1024;
+  int fit = (stage_target - 32) / row_bytes;
+  int R, nseg;
+  if (fit >= 8) {
+    R = fit & ~7;
+    if (R > 32) R = 32;
+    nseg = 1;
+  } else if (fit >= 4) {
+    R = 4, nseg = 2;
+  } else if (fit >= 2) {
+    R = 2, nseg = 4;
+  } else {
+    R = 1, nseg = 8;
+  }
+  const int stride = (int)align_up((size_t)R * row_bytes + 32, 128);
+  int stages = (int)(ring_budget / stride);
+  if (stages < 2) {  // very long rows: one CTA per SM
+    const size_t big = (size_t)di.max_smem_optin - header;
+    stages = (int)(big / stride);
+    if (stages < 2) return kNotSupported;
+  }
+  if (stages > kDecodeMaxStages) stages = kDecodeMaxStages;
+  int grid = g_opt.decode_grid > 0 ? (int)g_opt.decode_grid : 2 * di.sm_count;
+  if (grid > n) grid = (int)n;
+  pl->rows_per_stage = R;
+  pl->nseg = nseg;
+  pl->num_stages = stages;
+  pl->stage_stride = stride;
+  pl->grid = grid;
+  pl->smem = header + (size_t)stages * stride;
+  return kOk;
+}
+
+template <class Fmt>
+cudaError_t launch_decode_fmt(const DecodeParams& p, const DecodePlan& pl, cudaStream_t stream) {
+  void (*kern)(const DecodeParams) = nullptr;
+  if (p.m == 1)
+    kern = decode_matvec_kernel<Fmt, 1>;
+  else if (p.m == 2)
+    kern = decode_matvec_kernel<Fmt, 2>;
+  else if (p.m <= 4)
+    kern = decode_matvec_kernel<Fmt, 4>;
+  else
+    kern = decode_matvec_kernel<Fmt, 8>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  if (e != cudaSuccess) return e;
+  return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p);
+}
+
+int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
+                    cudaStream_t stream) {
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  DecodePlan pl;
+  const int32_t st = plan_decode(type, n, k, *di, &pl);
+  if (st != kOk) return st;
+  DecodeParams p;
+  p.w = (const uint8_t*)w;
+  p.act = act_planes(packed_act, type, m, k);
+  p.y = y;
+  p.n = n;
+  p.k = (int)k;
+  p.m = (int)m;
+  p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
+  p.total_bytes = n * (int64_t)p.row_bytes;
+  p.rows_per_stage = pl.rows_per_stage;
+  p.nseg = pl.nseg;
+  p.num_stages = pl.num_stages;
+  p.stage_stride = pl.stage_stride;
+  cudaError_t e;
+  switch (type) {
+    case kQ4K:
+      p.units_per_row = (int)(k / 256) * Q4KDecode::kUnitsPerBlock;
+      e = launch_decode_fmt<Q4KDecode>(p, pl, stream);
+      break;
+    case kQ6K:
+      p.units_per_row = (int)(k / 256) * Q6KDecode::kUnitsPerBlock;
+      e = launch_decode_fmt<Q6KDecode>(p, pl, stream);
+      break;
+    case kQ8_0:
+      p.units_per_row = (int)(k / 32);
+      e = launch_decode_fmt<Q8_0Decode>(p, pl, stream);
+      break;
+    case kQ4_0:
+      p.units_per_row = (int)(k / 32);
+      e = launch_decode_fmt<Q4_0Decode>(p, pl, stream);
+      break;
+    default:
+      return kNotSupported;
+  }
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t check_problem(int type, int64_t m, int64_t n, int64_t k) {
+  if (!supported_weight(type)) return kNotSupported;
+  if (m < 0 || n < 0 || k <= 0) return kInvalidProblem;
+  if (k % block_elems(type)) return kInvalidProblem;  // every reference entry rejects this (byte_kernels.rs:4768-4773)
+  if (k > (1 << 24) || n > ((int64_t)1 << 31)) return kNotSupported;
+  return kOk;
+}
+
+}  // namespace
+}  // namespace fq
+
+using namespace fq;
+
+extern "C" {
+
+const char* fuelq_status_string(int32_t status) {
+  switch (status) {
+    case kOk: return "success";
+    case kMisaligned: return "misaligned operand (16-byte alignment required)";
+    case kInvalidProblem: return "invalid problem (non-positive size, k not a multiple of the block size, or null operand)";
+    case kNotSupported: return "not supported (type or shape outside what the kernels implement)";
+    case kWorkspace: return "workspace too small or null when required";
+    case kLaunchFailure: return "internal kernel error (CUDA launch failure)";
+    default: return "unknown status code";
+  }
+}
+
+int32_t fuelq_block_elems(int32_t t) { return block_elems(t); }
+int32_t fuelq_block_bytes(int32_t t) { return block_bytes(t); }
+
+int32_t fuelq_set_option(int32_t key, int64_t value) {
+  switch (key) {
+    case FUELQ_OPT_PDL: g_opt.pdl = value ? 1 : 0; return kOk;
+    case FUELQ_OPT_DECODE_MAX_M:
+      if (value < 0 || value > kDecodeMaxM) return kInvalidProblem;
+      g_opt.decode_max_m = value;
+      return kOk;
+    case FUELQ_OPT_DECODE_GRID:
+      if (value < 0 || value > 65535) return kInvalidProblem;
+      g_opt.decode_grid = value;
+      return kOk;
+    default: return kInvalidProblem;
+  }
+}
+
+int64_t fuelq_get_option(int32_t key) {
+  switch (key) {
+    case FUELQ_OPT_PDL: return g_opt.pdl;
+    case FUELQ_OPT_DECODE_MAX_M: return g_opt.decode_max_m;
+    case FUELQ_OPT_DECODE_GRID: return g_opt.decode_grid;
+    default: return -1;
+  }
+}
+
+int32_t fuelq_device_error(int32_t* host_code_out, int32_t clear) {
+  int code = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return kLaunchFailure;
+  if (cudaMemcpyFromSymbol(&code, g_fq_dev_error, sizeof(int)) != cudaSuccess) return kLaunchFailure;
+  if (clear && code) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_fq_dev_error, &zero, sizeof(int)) != cudaSuccess) return kLaunchFailure;
+  }
+  if (host_code_out) *host_code_out = code;
+  return kOk;
+}
+
+int32_t fuelq_quantize_act(int32_t weight_type, int64_t m_total, int64_t k, const float* x, void* q8_blocks,
+                           void* stream) {
+  if (m_total > 0 && !q8_blocks) return kInvalidProblem;
+  return quantize_act_impl(weight_type, m_total, k, x, q8_blocks, nullptr, (cudaStream_t)stream);
+}
+
+size_t fuelq_act_packed_bytes(int32_t weight_type, int64_t m_total, int64_t k) {
+  if (!supported_weight(weight_type) || m_total < 0 || k <= 0) return 0;
+  return act_packed_bytes(weight_type, m_total, k);
+}
+
+int32_t fuelq_quantize_act_packed(int32_t weight_type, int64_t m_total, int64_t k, const float* x, void* packed,
+                                  size_t packed_bytes, void* stream) {
+  if (!supported_weight(weight_type)) return kNotSupported;
+  if (m_total > 0 && (!packed || packed_bytes < act_packed_bytes(weight_type, m_total, k))) return kWorkspace;
+  if (packed && !aligned(packed, 16)) return kMisaligned;
+  return quantize_act_impl(weight_type, m_total, k, x, nullptr, packed, (cudaStream_t)stream);
+}
+
+size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
+  if (check_problem(ggml_type, m_total, n, k) != kOk) return 0;
+  return act_packed_bytes(ggml_type, m_total, k);
+}
+
+int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
+  const int32_t st = check_problem(ggml_type, m_total, n, k);
+  if (st != kOk) return st;
+  if (m_total > g_opt.decode_max_m) return kNotSupported;
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  DecodePlan pl;
+  return n == 0 ? kOk : plan_decode(ggml_type, n, k, *di, &pl);
+}
+
+int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
+                             const void* packed_act, float* y, void* stream) {
+  const int32_t st = check_problem(ggml_type, m_total, n, k);
+  if (st != kOk) return st;
+  if (m_total == 0 || n == 0) return kOk;
+  if (!w || !packed_act || !y) return kInvalidProblem;
+  if (!aligned(w, 16) || !aligned(packed_act, 16) || !aligned(y, 4)) return kMisaligned;
+  if (m_total > kDecodeMaxM) return kNotSupported;
+  return decode_impl(ggml_type, m_total, n, k, w, const_cast<void*>(packed_act), y, (cudaStream_t)stream);
+}
+
+int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
+                      float* y, void* workspace, size_t workspace_bytes, void* stream) {
+  int32_t st = check_problem(ggml_type, m_total, n, k);
+  if (st != kOk) return st;
+  if (m_total == 0 || n == 0) return kOk;
+  if (!w || !x || !y) return kInvalidProblem;
+  if (!aligned(w, 16) || !aligned(x, 16) || !aligned(y, 4)) return kMisaligned;
+  if (m_total > g_opt.decode_max_m) return kNotSupported;
+  const size_t need = act_packed_bytes(ggml_type, m_total, k);
+  if (!workspace || workspace_bytes < need) return kWorkspace;
+  if (!aligned(workspace, 16)) return kMisaligned;
+  st = quantize_act_impl(ggml_type, m_total, k, x, nullptr, workspace, (cudaStream_t)stream);
+  if (st != kOk) return st;
+  return decode_impl(ggml_type, m_total, n, k, w, workspace, y, (cudaStream_t)stream);
+}
+
+int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, void* y, int32_t out_type,
+                         void* stream_v) {
+  const int be = block_elems(ggml_type);
+  if (be == 0) return kNotSupported;
+  if (numel < 0 || numel % be) return kInvalidProblem;
+  if (out_type != kF32 && out_type != kF16 && out_type != kBF16) return kNotSupported;
+  if (numel == 0) return kOk;
+  if (!blocks || !y) return kInvalidProblem;
+  const size_t in_align = ggml_type == kQ4K ? 16 : (ggml_type == kQ8K ? 4 : 2);
+  if (!aligned(blocks, in_align) || !aligned(y, out_type == kF32 ? 4 : 2)) return kMisaligned;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  const int64_t nb = numel / be;
+  const uint8_t* w = (const uint8_t*)blocks;
+  int64_t units;
+  switch (ggml_type) {
+    case kQ4K: units = nb * 8; break;
+    case kQ6K: units = nb * 16; break;
+    case kQ8_0: units = nb * 4; break;
+    case kQ4_0: units = nb * 4; break;
+    case kQ8K: units = nb * 64; break;
+    default: return kNotSupported;
+  }
+  const dim3 block(256), grid((unsigned)((units + 255) / 256));
+#define FQ_DEQ(KERNEL)                                                                        \
+  do {                                                                                        \
+    if (out_type == kF32)                                                                     \
+      KERNEL<float><<<grid, block, 0, stream>>>(w, units, (float*)y);                         \
+    else if (out_type == kF16)                                                                \
+      KERNEL<__half><<<grid, block, 0, stream>>>(w, units, (__half*)y);                       \
+    else                                                                                      \
+      KERNEL<__nv_bfloat16><<<grid, block, 0, stream>>>(w, units, (__nv_bfloat16*)y);         \
+  } while (0)
+  switch (ggml_type) {
+    case kQ4K: FQ_DEQ(dequant_q4k_kernel); break;
+    case kQ6K: FQ_DEQ(dequant_q6k_kernel); break;
+    case kQ8_0: FQ_DEQ(dequant_q8_0_kernel); break;
+    case kQ4_0: FQ_DEQ(dequant_q4_0_kernel); break;
+    case kQ8K: FQ_DEQ(dequant_q8k_kernel); break;
+  }
+#undef FQ_DEQ
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+}  // extern "C"

@@ -1,0 +1,108 @@
+/* fuelq — B200 (sm_100a) kernels for fuel's GGUF k-quant matrix multiply.
+ *
+ * C ABI of libfuelq.so: the symbols a fuel backend binds in place of the
+ * quantized entries it gets today from its CUDA kernel provider. Conventions are
+ * the ones fuel's FFI wrappers already assume (fuel-cuda-backend/src/quantized.rs:58-65,
+ * 138-144; fuel-cuda-backend/src/baracuda/status.rs:5-12):
+ *   - every entry returns an int32 status: 0 ok, 1 misaligned operand, 2 invalid
+ *     problem, 3 not supported, 4 workspace too small or null, 5 launch failure;
+ *   - all pointers are device pointers on the current device unless the name says
+ *     host; weights are GGUF block bytes, row-major [n][k / block] ("one row per
+ *     output feature"), activations and outputs contiguous row-major f32;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call
+ *     returns without synchronizing; nothing is allocated; outputs and workspace
+ *     are caller-owned.
+ */
+#ifndef FUELQ_H_
+#define FUELQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FUELQ_OK 0
+#define FUELQ_MISALIGNED 1
+#define FUELQ_INVALID_PROBLEM 2
+#define FUELQ_NOT_SUPPORTED 3
+#define FUELQ_WORKSPACE 4
+#define FUELQ_LAUNCH_FAILURE 5
+
+/* GGUF type ids (fuel-ir/src/quantized.rs:35-75, GgmlDType::to_u32). */
+#define FUELQ_TYPE_F32 0
+#define FUELQ_TYPE_F16 1
+#define FUELQ_TYPE_Q4_0 2
+#define FUELQ_TYPE_Q8_0 8
+#define FUELQ_TYPE_Q4K 12
+#define FUELQ_TYPE_Q6K 14
+#define FUELQ_TYPE_Q8K 15
+#define FUELQ_TYPE_BF16 30
+
+/* Text for a status code (fuel-cuda-backend/src/baracuda/status.rs:37-48, status_reason). */
+const char* fuelq_status_string(int32_t status);
+
+/* Elements / bytes per block (fuel-ir/src/quantized.rs:77-103, GgmlDType::block_size / type_size).
+ * 0 for a type this library does not handle. */
+int32_t fuelq_block_elems(int32_t ggml_type);
+int32_t fuelq_block_bytes(int32_t ggml_type);
+
+/* Options. key: */
+#define FUELQ_OPT_PDL 1          /* 1: launch kernels with programmatic dependent launch so a kernel's weight
+                                    prefetch overlaps its predecessor's tail (default 0) */
+#define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the decode mat-vec (default 16) */
+#define FUELQ_OPT_DECODE_GRID 3  /* CTAs for the decode kernel; 0 = two per SM (default) */
+int32_t fuelq_set_option(int32_t key, int64_t value);
+int64_t fuelq_get_option(int32_t key);
+
+/* Reads (and, if `clear`, resets) the device-side error word set by a kernel whose
+ * bounded wait expired. Synchronizes the device. 0 = no error recorded. */
+int32_t fuelq_device_error(int32_t* host_code_out, int32_t clear);
+
+/* Activation quantization to the weight format's dot-product partner: Q8_K blocks for
+ * Q4K/Q6K weights, Q8_0 blocks otherwise — the first half of the reference's
+ * matmul (fuel-quantized/src/k_quants.rs:2303-2313, BlockQ8K::from_float :2230-2267,
+ * BlockQ8_0::from_float :629-658). Output bytes are identical to the reference's.
+ * x: f32 [m_total, k]; q8_blocks: m_total * k / block * block_bytes bytes, 4-byte aligned. */
+int32_t fuelq_quantize_act(int32_t weight_type, int64_t m_total, int64_t k, const float* x, void* q8_blocks,
+                           void* stream);
+
+/* Same numbers in the plane-split layout the mat-vec kernels read (int8 plane, f32 scale
+ * plane, int16 block-sum plane). Lets several projections of one input (Q/K/V, gate/up)
+ * share one quantization — the reference re-quantizes per call (k_quants.rs:2303-2313). */
+size_t fuelq_act_packed_bytes(int32_t weight_type, int64_t m_total, int64_t k);
+int32_t fuelq_quantize_act_packed(int32_t weight_type, int64_t m_total, int64_t k, const float* x, void* packed,
+                                  size_t packed_bytes, void* stream);
+
+/* Workspace needed by fuelq_qmatmul for this problem (the FFI contract the reference
+ * follows passes (workspace, workspace_bytes) on every call, quantized.rs:193-195). */
+size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
+
+/* 0 if fuelq_qmatmul handles (type, m_total, n, k), else the status it would return. */
+int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
+
+/* y[m_total, n] = x[m_total, k] * W[n, k]^T with W in GGUF blocks — QMatMul::forward /
+ * DynQuantizedStorage::fwd (fuel-backend-contract/src/quantized.rs:72-80), i.e.
+ * fuel_quantized::matmul (k_quants.rs:2284-2331) and the CUDA entry it replaces,
+ * baracuda_kernels_mmvq_<fmt>_batched_run (fuel-cuda-backend/src/quantized.rs:138-231).
+ * Quantizes x, then runs the decode mat-vec (m_total <= DECODE_MAX_M) or the
+ * tensor-core path. w must be 16-byte aligned, x and y 16-byte aligned. */
+int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
+                      float* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The mat-vec alone, on activations already quantized by fuelq_quantize_act_packed. */
+int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
+                             const void* packed_act, float* y, void* stream);
+
+/* Blocks -> floats: DynQuantizedStorage::dequantize / dequantize_f16
+ * (fuel-backend-contract/src/quantized.rs:56-62), GgmlType::to_float; replaces
+ * baracuda_kernels_dequantize_<fmt>_run (fuel-cuda-backend/src/quantized.rs:58-105).
+ * out_type: FUELQ_TYPE_F32, _F16 or _BF16. numel a multiple of the block size. */
+int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, void* y, int32_t out_type,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUELQ_H_ */

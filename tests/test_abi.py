@@ -1,0 +1,86 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the header
+declares, and rejects bad arguments with the reference's status codes before any
+device work (fuel-cuda-backend/src/baracuda/status.rs:5-12). No compute is launched."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    names = set()
+    for fn in os.listdir(os.path.join(ROOT, "include")):
+        if fn.endswith(".h"):
+            text = open(os.path.join(ROOT, "include", fn)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names |= set(re.findall(r"\b(fuelq_\w+)\s*\(", text))
+    return sorted(names)
+
+
+@pytest.fixture(scope="module")
+def L():
+    from fuel_b200 import _lib
+    return _lib
+
+
+def test_library_exports_every_declared_symbol(L):
+    declared = _declared_symbols()
+    assert len(declared) >= 10
+    for name in declared:
+        assert hasattr(L.lib, name), f"libfuelq.so lacks {name}"
+    assert set(declared) == set(L.PROTOTYPES), set(declared) ^ set(L.PROTOTYPES)
+
+
+def test_status_strings_and_block_tables(L):
+    assert L.status_string(0) == "success"
+    for code in range(1, 6):
+        assert L.status_string(code) and "unknown" not in L.status_string(code)
+    assert "unknown" in L.status_string(99)
+    # fuel-ir/src/quantized.rs:77-103
+    from fuel_b200 import GgmlDType as T
+    for t in (T.Q4_0, T.Q8_0, T.Q4K, T.Q6K, T.Q8K):
+        assert L.lib.fuelq_block_elems(int(t)) == t.block_size()
+        assert L.lib.fuelq_block_bytes(int(t)) == t.type_size()
+    assert L.lib.fuelq_block_elems(13) == 0  # Q5K: not handled
+    assert T.from_u32(12) is T.Q4K and T.Q6K.to_u32() == 14
+    with pytest.raises(ValueError):
+        T.from_u32(99)
+
+
+def test_argument_validation_needs_no_device(L):
+    f = L.lib
+    Q4K, Q8_0 = 12, 8
+    # k not a multiple of the block size: every reference entry rejects it (byte_kernels.rs:4768-4773)
+    assert f.fuelq_qmatmul(Q4K, 1, 8, 255, 16, 16, 16, 16, 1 << 20, None) == L.INVALID_PROBLEM
+    assert f.fuelq_qmatmul(Q8_0, 1, 8, 33, 16, 16, 16, 16, 1 << 20, None) == L.INVALID_PROBLEM
+    assert f.fuelq_qmatmul(Q4K, -1, 8, 256, 16, 16, 16, 16, 1 << 20, None) == L.INVALID_PROBLEM
+    assert f.fuelq_qmatmul(13, 1, 8, 256, 16, 16, 16, 16, 1 << 20, None) == L.NOT_SUPPORTED
+    # empty problems succeed without touching anything (byte_kernels.rs:4805-4807)
+    assert f.fuelq_qmatmul(Q4K, 0, 8, 256, None, None, None, None, 0, None) == L.OK
+    assert f.fuelq_qmatmul(Q4K, 1, 0, 256, None, None, None, None, 0, None) == L.OK
+    # null / misaligned operands, missing workspace
+    assert f.fuelq_qmatmul(Q4K, 1, 8, 256, None, 16, 16, 16, 1 << 20, None) == L.INVALID_PROBLEM
+    assert f.fuelq_qmatmul(Q4K, 1, 8, 256, 8, 16, 16, 16, 1 << 20, None) == L.MISALIGNED
+    assert f.fuelq_qmatmul(Q4K, 1, 8, 256, 16, 16, 16, None, 0, None) == L.WORKSPACE
+    assert f.fuelq_qmatmul(Q4K, 1, 8, 256, 16, 16, 16, 16, 8, None) == L.WORKSPACE
+    assert f.fuelq_quantize_act(Q4K, 1, 100, 16, 16, None) == L.INVALID_PROBLEM
+    assert f.fuelq_quantize_act(Q4K, 1, 256, 4, 16, None) == L.MISALIGNED
+    assert f.fuelq_dequantize(Q4K, 100, 16, 16, 0, None) == L.INVALID_PROBLEM
+    assert f.fuelq_dequantize(Q4K, 256, 16, 16, 12, None) == L.NOT_SUPPORTED
+    assert f.fuelq_dequantize(Q4K, 256, 8, 16, 0, None) == L.MISALIGNED
+    assert f.fuelq_dequantize(Q4K, 0, None, None, 0, None) == L.OK
+    # workspace sizing is pure arithmetic
+    assert f.fuelq_qmatmul_workspace_bytes(Q4K, 1, 4096, 4096) == f.fuelq_act_packed_bytes(Q4K, 1, 4096) >= 4096 + 64 + 512
+    assert f.fuelq_qmatmul_workspace_bytes(Q4K, 1, 4096, 100) == 0
+
+
+def test_options_round_trip(L):
+    f = L.lib
+    assert f.fuelq_get_option(L.OPT_PDL) == 0
+    assert f.fuelq_set_option(L.OPT_PDL, 1) == L.OK and f.fuelq_get_option(L.OPT_PDL) == 1
+    assert f.fuelq_set_option(L.OPT_PDL, 0) == L.OK
+    assert f.fuelq_set_option(L.OPT_DECODE_MAX_M, 999) == L.INVALID_PROBLEM
+    assert f.fuelq_set_option(77, 1) == L.INVALID_PROBLEM
