@@ -333,6 +333,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_matvec_kernel(const 
     if (nseg > 1) {
       // all consumer warps meet here (bounded), then sum the k-segments in fixed order
       if (lane == 0) mbar_arrive(&hd->part_ready[buf]);
+      __syncwarp();  // reconverge first: lanes spinning below must not starve lane 0's arrive
       if (!mbar_wait_bounded(&hd->part_ready[buf], (it >> 1) & 1)) {
         record_dev_error(kErrFullWait);
         return;
