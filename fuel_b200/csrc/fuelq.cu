@@ -10,6 +10,7 @@
 #include "dequantize.cuh"
 #include "fq_common.cuh"
 #include "quantize_act.cuh"
+#include "quantize_weights.cuh"
 
 namespace fq {
 
@@ -336,6 +337,26 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   st = quantize_act_impl(ggml_type, m_total, k, x, nullptr, workspace, (cudaStream_t)stream);
   if (st != kOk) return st;
   return decode_impl(ggml_type, m_total, n, k, w, workspace, y, (cudaStream_t)stream);
+}
+
+int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x, void* blocks, void* stream_v) {
+  if (!supported_weight(ggml_type)) return kNotSupported;
+  const int be = block_elems(ggml_type);
+  if (numel < 0 || numel % be) return kInvalidProblem;
+  if (numel == 0) return kOk;
+  if (!x || !blocks) return kInvalidProblem;
+  if (!aligned(x, 16) || !aligned(blocks, ggml_type == kQ4K ? 4 : 2)) return kMisaligned;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  const int64_t nb = numel / be;
+  uint8_t* out = (uint8_t*)blocks;
+  switch (ggml_type) {
+    case kQ8_0: quantize_w_q8_0_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ4_0: quantize_w_q4_0_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ4K: quantize_w_q4k_kernel<<<(unsigned)((nb * 8 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ6K: quantize_w_q6k_kernel<<<(unsigned)((nb * 16 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    default: return kNotSupported;
+  }
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailure;
 }
 
 int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, void* y, int32_t out_type,

@@ -90,6 +90,18 @@ def qmatmul_packed(dtype: GgmlDType, w_blocks: torch.Tensor, n: int, k: int, m: 
     return out
 
 
+def quantize_weights(dtype: GgmlDType, w: torch.Tensor) -> torch.Tensor:
+    """f32 weights (any shape, row length a multiple of the block) -> GGUF block bytes, on the device."""
+    _need_cuda(w, "w")
+    if w.dtype != torch.float32:
+        raise ValueError("only f32 can be quantized")  # fuel-cuda-backend/src/quantized.rs:414-418
+    out = torch.empty(storage_bytes(dtype, w.numel()), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        _lib.check(_L.fuelq_quantize_weights(int(dtype), w.numel(), w.data_ptr(), out.data_ptr(), _stream()),
+                   "fuelq_quantize_weights")
+    return out
+
+
 def dequantize(dtype: GgmlDType, blocks: torch.Tensor, elem_count: int,
                out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     _need_cuda(blocks, "blocks")

@@ -95,6 +95,14 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
 int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
                              const void* packed_act, float* y, void* stream);
 
+/* f32 -> GGUF blocks on the device, byte-identical to the reference's host quantizers
+ * (GgmlType::from_float: Q8_0 k_quants.rs:629-658, Q4_0 :199-235, Q4_K :1470-1528 with
+ * make_qkx1_quants utils.rs:229-286, Q6_K :2005-2075 with make_qx_quants utils.rs:62-191).
+ * This is DynQuantizedStorage::quantize (fuel-backend-contract/src/quantized.rs:34-35); the
+ * reference's CUDA backend does it on the CPU and uploads (fuel-cuda-backend/src/quantized.rs:389-412).
+ * x: f32 [numel] device, 16-byte aligned; numel a multiple of the block size. */
+int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x, void* blocks, void* stream);
+
 /* Blocks -> floats: DynQuantizedStorage::dequantize / dequantize_f16
  * (fuel-backend-contract/src/quantized.rs:56-62), GgmlType::to_float; replaces
  * baracuda_kernels_dequantize_<fmt>_run (fuel-cuda-backend/src/quantized.rs:58-105).

@@ -234,3 +234,39 @@ def test_error_statuses_on_device(ops):
         ops.qmatmul(T.Q4K, w, 2, torch.zeros(1, 256, device="cuda"))
     with pytest.raises(ValueError):
         ops.qmatmul(T.Q4K, w, 1, torch.zeros(1, 256))
+
+
+# ----------------------------------------------------------------- weight quantizers on the device
+def _weight_edge_cases(k):
+    w = _weights(24, k, seed=3)
+    w[1] = 0.0                                    # all-zero blocks
+    w[2] = np.float32(0.25)                       # constant: max == min
+    w[3, :32] = 0.0                               # one zero sub-block inside a live block
+    w[4] = np.abs(w[4])                           # all positive: min clamps to 0
+    w[5] = -np.abs(w[5])
+    w[6] *= np.float32(1e4)
+    w[7] *= np.float32(1e-6)
+    w[8, ::2] = w[8, 1::2]                        # repeated values (ties)
+    w[9] = np.round(w[9] * 64) / 64               # coarse grid: many exact .5 cases
+    w[10, :16] = 0.0                              # zero 16-sub-block (Q6_K scale 0)
+    w[11] = np.linspace(-1, 1, k, dtype=np.float32)
+    return w
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_quantize_weights_bytes_identical(ops, oracle, name):
+    for k in (256, 1024, 4096):
+        w = _weight_edge_cases(k)
+        got = ops.quantize_weights(_T(name), _dev(w)).cpu().numpy()
+        want = oracle.quantize(_ot(oracle, name), w)
+        diff = np.nonzero(got != want)[0]
+        assert diff.size == 0, f"{name} k={k}: {diff.size} bytes differ, first at block {diff[0] // _T(name).type_size()}"
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_quantize_weights_large_random(ops, oracle, name):
+    w = _weights(1024, 4096, seed=21)
+    got = ops.quantize_weights(_T(name), _dev(w)).cpu().numpy()
+    assert np.array_equal(got, oracle.quantize(_ot(oracle, name), w))
+    g = np.load(GOLDEN)
+    assert np.array_equal(ops.quantize_weights(_T(name), _dev(g["w"])).cpu().numpy(), g[f"{name}_blocks"])
