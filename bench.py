@@ -1,0 +1,366 @@
+"""Benchmark of the quantized mat-vec hot path.
+
+Workload (BASELINE config 2, the Q4_K decode case): y[1, 11008] = x[1, 4096] . W^T with W a
+Q4_K matrix [11008 x 4096] (25 362 432 bytes of blocks). One step = one pass over LAYERS
+distinct weight matrices (each with its own activation row), i.e. LAYERS quantized
+mat-vec calls; cycling over 32 x 25.4 MB = 811 MB of weights keeps every read in HBM, not L2.
+Weights are N(0, 0.02) from a seeded generator, quantized by the library's device quantizer
+(byte-identical to the reference's); activations N(0, 1).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Metric: achieved HBM GB/s = algorithmic bytes (W blocks + 4*M*k + 4*M*n per mat-vec) / time.
+N > 1 (torchrun): every rank runs the same pass over its own matrices — the path has no
+exchange step, so scaling is weak and there is no collective.
+--impl reference: the reference's CPU path (its arithmetic restated under oracle/, AVX2 order,
+all host threads) on the same step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_OUT, K_IN, M_ROWS = 11008, 4096, 1
+LAYERS = 32
+W_BYTES = N_OUT * (K_IN // 256) * 144
+ALGO_BYTES = W_BYTES + 4 * M_ROWS * K_IN + 4 * M_ROWS * N_OUT  # 25 422 848
+WORKLOAD = f"q4k_qmatmul_m{M_ROWS}_k{K_IN}_n{N_OUT}_x{LAYERS}_distinct_matrices"
+
+
+def _peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self, t0: float, t1: float):
+        rows = [s for t, s in self.samples if t0 <= t <= t1] or [s for _, s in self.samples[-5:]]
+        mhz, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            p = [c.strip() for c in r.split(",")]
+            try:
+                mhz.append(float(p[0]))
+                mx = max(mx, float(p[1]))
+            except Exception:
+                continue
+            for name, val in zip(names, p[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def _dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def make_weights(torch, ops, T, device, rank):
+    ws = []
+    g = torch.Generator(device=device)
+    for i in range(LAYERS):
+        g.manual_seed(1000 * rank + i)
+        w = torch.randn(N_OUT, K_IN, generator=g, device=device, dtype=torch.float32) * 0.02
+        ws.append(ops.quantize_weights(T.Q4K, w))
+        del w
+    return ws
+
+
+def cpu_pass(O, w_host, x_host, threads):
+    for wb, x in zip(w_host, x_host):
+        O.matmul(O.Q4K, x, wb, N_OUT, O.AVX2, threads)
+
+
+def run_reference(args):
+    """The reference's CPU path on the same step (all host threads)."""
+    rank, local_rank, world = _dist_env()
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+    threads = O.max_threads()
+    rng = np.random.Generator(np.random.PCG64(0))
+    # one quantized matrix per layer would cost ~1 s of host quantization each; the CPU timing
+    # does not depend on the weight values, so LAYERS views of 4 distinct matrices are used,
+    # still 4 x 25 MB > any host cache
+    base = [O.quantize(O.Q4K, rng.standard_normal((N_OUT, K_IN), dtype=np.float32) * np.float32(0.02))
+            for _ in range(4)]
+    w_host = [base[i % 4] for i in range(LAYERS)]
+    x_host = [rng.standard_normal((M_ROWS, K_IN), dtype=np.float32) for _ in range(LAYERS)]
+    for _ in range(max(args.warmup, 1)):
+        cpu_pass(O, w_host, x_host, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(O, w_host, x_host, threads)
+    dt = time.perf_counter() - t0
+    gbs = ALGO_BYTES * LAYERS * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "q4k_qmatmul_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": M_ROWS, "k": K_IN, "n": N_OUT, "format": "Q4_K", "layers": LAYERS},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{args.steps} full steps of {LAYERS} mat-vecs (4 distinct matrices cycled)"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    global LAYERS, WORKLOAD
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="fuelq", choices=["fuelq", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step (profiling runs use fewer)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    LAYERS = args.layers
+    WORKLOAD = f"q4k_qmatmul_m{M_ROWS}_k{K_IN}_n{N_OUT}_x{LAYERS}_distinct_matrices"
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import ctypes
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from fuel_b200 import GgmlDType as T, _lib, ops
+
+    rank, local_rank, world = _dist_env()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    L = _lib.lib
+    _lib.check(L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0), "set_option")
+
+    ws = make_weights(torch, ops, T, device, rank)
+    g = torch.Generator(device=device)
+    g.manual_seed(7 + rank)
+    xs = [torch.randn(M_ROWS, K_IN, generator=g, device=device) for _ in range(LAYERS)]
+    ys = [torch.empty(M_ROWS, N_OUT, device=device) for _ in range(LAYERS)]
+    ws_bytes = L.fuelq_qmatmul_workspace_bytes(int(T.Q4K), M_ROWS, N_OUT, K_IN)
+    scratch = [torch.empty(ws_bytes, dtype=torch.uint8, device=device) for _ in range(LAYERS)]
+
+    stream = torch.cuda.Stream(device)
+    sptr = stream.cuda_stream
+
+    def one_pass():
+        for w, x, y, s in zip(ws, xs, ys, scratch):
+            st = L.fuelq_qmatmul(int(T.Q4K), M_ROWS, N_OUT, K_IN, w.data_ptr(), x.data_ptr(), y.data_ptr(),
+                                 s.data_ptr(), ws_bytes, sptr)
+            if st:
+                _lib.check(st, "fuelq_qmatmul")
+
+    def matvec_only_pass():
+        for w, y, s in zip(ws, ys, scratch):
+            st = L.fuelq_qmatmul_packed(int(T.Q4K), M_ROWS, N_OUT, K_IN, w.data_ptr(), s.data_ptr(), y.data_ptr(), sptr)
+            if st:
+                _lib.check(st, "fuelq_qmatmul_packed")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.cuda.stream(stream):
+        one_pass()  # eager once: sets kernel attributes outside capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        graph_mv = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph_mv, stream=stream):
+            matvec_only_pass()
+
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        for _ in range(args.warmup):
+            graph.replay()
+        stream.synchronize()
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_wall0 = time.time()
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        barrier()
+        t_wall1 = time.time()
+        ms_total = max_over_ranks(e0.elapsed_time(e1))
+        if t_wall1 - t_wall0 < 0.4:  # region shorter than the sampler period: hold the same load a little longer
+            t_end = time.time() + 0.6
+            while time.time() < t_end:
+                for _ in range(50):
+                    graph.replay()
+                stream.synchronize()
+            t_wall1 = time.time()
+        clocks = sampler.summary(t_wall0, t_wall1)
+
+        # dominant kernel alone (activations already quantized): average launch duration
+        for _ in range(3):
+            graph_mv.replay()
+        stream.synchronize()
+        reps = max(args.steps, 50)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(stream)
+        for _ in range(reps):
+            graph_mv.replay()
+        k1.record(stream)
+        stream.synchronize()
+        kern_us = k0.elapsed_time(k1) * 1e3 / (reps * LAYERS)
+
+        # end to end through the host-buffer entry point: pinned x in, y out, every mat-vec
+        hws_bytes = L.fuelq_qmatmul_host_workspace_bytes(int(T.Q4K), M_ROWS, N_OUT, K_IN)
+        hws = [torch.empty(hws_bytes, dtype=torch.uint8, device=device) for _ in range(LAYERS)]
+        xh = [x.cpu().pin_memory() for x in xs]
+        yh = [torch.empty(M_ROWS, N_OUT).pin_memory() for _ in range(LAYERS)]
+
+        def host_pass():
+            for w, x, y, s in zip(ws, xh, yh, hws):
+                st = L.fuelq_qmatmul_host(int(T.Q4K), M_ROWS, N_OUT, K_IN, w.data_ptr(), x.data_ptr(), y.data_ptr(),
+                                          s.data_ptr(), hws_bytes, sptr)
+                if st:
+                    _lib.check(st, "fuelq_qmatmul_host")
+            stream.synchronize()  # the step's results are read on the host
+
+        for _ in range(args.warmup):
+            host_pass()
+        barrier()
+        h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0.record(stream)
+        e2e_steps = args.steps
+        for _ in range(e2e_steps):
+            host_pass()
+        h1.record(stream)
+        stream.synchronize()
+        e2e_ms = max_over_ranks(h0.elapsed_time(h1))
+        sampler.stop()
+
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0, "a kernel recorded an expired bounded wait"
+    # the graph path and the host path must agree bit for bit on the last layer
+    assert torch.equal(ys[-1].cpu(), yh[-1]), "graph and host-buffer results differ"
+
+    ms_per_step = ms_total / args.steps
+    value = world * LAYERS * ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
+    e2e_value = world * LAYERS * ALGO_BYTES / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    peak, peak_kind = _peaks()
+    achieved = ALGO_BYTES / (kern_us * 1e-6) / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu_baseline = None
+    if not args.no_cpu_baseline and world == 1:
+        from oracle import oracle as O
+        threads = O.max_threads()
+        w_host = [ws[i].cpu().numpy() for i in range(4)]
+        x_host = [xs[i].cpu().numpy() for i in range(4)]
+        # parity spot check beside the timing: GPU output vs the CPU path on layer 0
+        r = O.matmul(O.Q4K, x_host[0], w_host[0], N_OUT, O.SCALAR, threads)
+        err = float(np.abs(ys[0].cpu().numpy() - r).max() / np.abs(r).max())
+        assert err <= 2e-6, f"GPU result off the CPU path by {err}"
+        cpu_pass(O, w_host, x_host, threads)
+        n_mv, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < 10.0:
+            cpu_pass(O, w_host, x_host, threads)
+            n_mv += 4
+        dt = time.perf_counter() - t0
+        cpu_baseline = {"value": ALGO_BYTES * n_mv / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                        "sample": f"{n_mv} mat-vecs over 4 of the {LAYERS} matrices in {dt:.1f} s (AVX2 order, OpenMP)",
+                        "parity_max_rel_err_vs_gpu": err}
+
+    traffic = None
+    try:  # per-launch DRAM bytes from the committed ncu summary, if present
+        with open(os.path.join(ROOT, "profiles", "decode_q4k_m1_traffic.json")) as f:
+            traffic = json.load(f).get("dram_bytes_per_launch")
+    except Exception:
+        pass
+
+    line = {
+        "metric": "q4k_qmatmul_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": M_ROWS, "k": K_IN, "n": N_OUT, "format": "Q4_K", "layers": LAYERS,
+                   "l2": f"inputs larger than L2: {LAYERS * W_BYTES / 1e6:.0f} MB of distinct weights per step", "cuda_graph": True,
+                   "pdl": bool(args.pdl), "parallelism": f"independent matrices per rank x{world}"},
+        "pct_of_8tbs": value / world / 8000.0 * 100.0,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_matvec_kernel<Q4KDecode,1>",
+                     "avg_launch_us": kern_us, "algorithmic_bytes_per_launch": ALGO_BYTES},
+        "cpu_baseline": cpu_baseline,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * M_ROWS * K_IN * 4,
+                "d2h_bytes_per_step": LAYERS * M_ROWS * N_OUT * 4, "ms_per_step": e2e_ms / e2e_steps,
+                "api": "fuelq_qmatmul_host (pinned host x in, host y out, per mat-vec)"},
+        "gpu_launches": args.steps * LAYERS * 2,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

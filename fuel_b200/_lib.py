@@ -30,6 +30,8 @@ PROTOTYPES = {
     "fuelq_qmatmul_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul_can_implement": (_i32, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "fuelq_qmatmul_host_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
+    "fuelq_qmatmul_host": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "fuelq_qmatmul_packed": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "fuelq_quantize_weights": (_i32, [_i32, _i64, _vp, _vp, _vp]),
     "fuelq_dequantize": (_i32, [_i32, _i64, _vp, _vp, _i32, _vp]),

@@ -163,8 +163,19 @@ cudaError_t launch_decode_fmt(const DecodeParams& p, const DecodePlan& pl, cudaS
     kern = decode_matvec_kernel<Fmt, 4>;
   else
     kern = decode_matvec_kernel<Fmt, 8>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
-  if (e != cudaSuccess) return e;
+  // raise the dynamic shared-memory limit once per (kernel, device) to the most any plan uses
+  static bool attr_set[4][64] = {};
+  const int slot = p.m == 1 ? 0 : p.m == 2 ? 1 : p.m <= 4 ? 2 : 3;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[slot][dev]) {
+    DeviceInfo* di;
+    if (!device_info(&di)) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+    if (e != cudaSuccess) return e;
+    attr_set[slot][dev] = true;
+  }
   return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p);
 }
 
@@ -337,6 +348,37 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   st = quantize_act_impl(ggml_type, m_total, k, x, nullptr, workspace, (cudaStream_t)stream);
   if (st != kOk) return st;
   return decode_impl(ggml_type, m_total, n, k, w, workspace, y, (cudaStream_t)stream);
+}
+
+size_t fuelq_qmatmul_host_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
+  if (check_problem(ggml_type, m_total, n, k) != kOk) return 0;
+  return align_up((size_t)m_total * k * 4, 256) + align_up((size_t)m_total * n * 4, 256) +
+         fuelq_qmatmul_workspace_bytes(ggml_type, m_total, n, k);
+}
+
+int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
+                           const float* x_host, float* y_host, void* workspace, size_t workspace_bytes,
+                           void* stream_v) {
+  const int32_t st = check_problem(ggml_type, m_total, n, k);
+  if (st != kOk) return st;
+  if (m_total == 0 || n == 0) return kOk;
+  if (!w || !x_host || !y_host) return kInvalidProblem;
+  if (!workspace || workspace_bytes < fuelq_qmatmul_host_workspace_bytes(ggml_type, m_total, n, k)) return kWorkspace;
+  if (!aligned(workspace, 256)) return kMisaligned;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  uint8_t* p = (uint8_t*)workspace;
+  float* x_dev = (float*)p;
+  p += align_up((size_t)m_total * k * 4, 256);
+  float* y_dev = (float*)p;
+  p += align_up((size_t)m_total * n * 4, 256);
+  if (cudaMemcpyAsync(x_dev, x_host, (size_t)m_total * k * 4, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+    return kLaunchFailure;
+  const int32_t s2 = fuelq_qmatmul(ggml_type, m_total, n, k, w, x_dev, y_dev, p,
+                                   workspace_bytes - (size_t)(p - (uint8_t*)workspace), stream_v);
+  if (s2 != kOk) return s2;
+  if (cudaMemcpyAsync(y_host, y_dev, (size_t)m_total * n * 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess)
+    return kLaunchFailure;
+  return kOk;
 }
 
 int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x, void* blocks, void* stream_v) {

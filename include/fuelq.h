@@ -91,6 +91,18 @@ int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t 
 int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
                       float* y, void* workspace, size_t workspace_bytes, void* stream);
 
+/* fuelq_qmatmul for callers holding HOST activations: copies x_host to the device, runs the
+ * product and copies y back, all enqueued on `stream` (pinned host memory keeps it
+ * asynchronous); the caller synchronizes the stream before reading y_host. This is the
+ * shape of the reference's eager CUDA forward, which stages small host arrays and reads
+ * results back around every call (fuel-cuda-backend/src/quantized.rs:170-231), without
+ * its per-call allocations and device synchronize. workspace: device, 256-byte aligned,
+ * fuelq_qmatmul_host_workspace_bytes() bytes. */
+size_t fuelq_qmatmul_host_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
+int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
+                           const float* x_host, float* y_host, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
 /* The mat-vec alone, on activations already quantized by fuelq_quantize_act_packed. */
 int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
                              const void* packed_act, float* y, void* stream);
