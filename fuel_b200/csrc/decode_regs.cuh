@@ -1,0 +1,274 @@
+// Decode mat-vec, register-resident activations (M = 1 or 2).
+//
+// Same job and same streaming structure as decode.cuh (a producer warp feeds a ring of
+// shared-memory stages with 1-D bulk TMA copies of whole weight rows; bounded waits), but the
+// inner loop is rebuilt around the instruction budget of an HBM-bound kernel: at ~23 bytes per
+// clock per SM there are fewer than 90 issue slots for every 512 bytes of weights, so
+//   * each lane owns fixed positions along k for the whole kernel and keeps the matching
+//     8-bit activations, block sums and scales in registers (loaded once, after the
+//     predecessor kernel is known to have finished) — no activation loads in the loop;
+//   * a lane's unit is 32 bytes of nibbles (Q4_K: one 64-element group, two sub-blocks), so
+//     the 6-bit scale decode is paid once per 32 bytes;
+//   * high nibbles are not shifted down: dp4a(unsigned bytes & 0xf0, act) gives 16x the
+//     dot product, which is shifted once;
+//   * every byte offset is a lane constant; per row only the row base changes.
+// A row is handled by `ks` warps (k-slices) so that a lane never owns more than NU units;
+// the slices of a row are summed in a fixed order from shared memory.
+#pragma once
+#include "decode.cuh"
+#include "fq_common.cuh"
+
+namespace fq {
+
+struct DecodeRegsParams {
+  const uint8_t* w;
+  ActPlanes act;
+  float* y;
+  int64_t n;
+  int64_t total_bytes;
+  int k;
+  int m;
+  int row_bytes;
+  int units_per_row;
+  int rows_per_stage;
+  int ks;  // warps per row: 1, 2, 4 or 8
+  int num_stages;
+  int stage_stride;
+  int debug_flags;                // bit 0: consumers skip the arithmetic (streaming-rate experiments)
+  unsigned long long* trace;      // optional: 4 global-timer stamps per CTA
+};
+
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// ---- Q4_K: unit = 32 bytes of nibbles = group g of a super-block (elements 64g..64g+63)
+struct Q4KRegs {
+  static constexpr int kUnitsPerBlock = 4;
+  struct Unit {
+    uint32_t off_hdr, off_qs;  // byte offsets from the row base
+    uint32_t sh;               // 16 * (g & 1)
+    bool upper;                // g >= 2: scales 4..7 use the split 4+2 bit packing
+  };
+  struct Act {
+    int q[16];  // 64 activations: [0..8) words pair with low nibbles, [8..16) with high nibbles
+    int bs_lo, bs_hi;
+    float yd;
+  };
+  __device__ __forceinline__ static void make_unit(int u, bool valid, Unit& un) {
+    const int blk = valid ? (u >> 2) : 0, g = valid ? (u & 3) : 0;
+    un.off_hdr = blk * Q4KL::kBytes;
+    un.off_qs = blk * Q4KL::kBytes + Q4KL::kOffQs + 32 * g;
+    un.sh = 16 * (g & 1);
+    un.upper = g >= 2;
+  }
+  __device__ __forceinline__ static void load_act(int u, bool valid, const ActPlanes& a, int k, int m, Act& ac) {
+    if (!valid) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) ac.q[i] = 0;
+      ac.bs_lo = ac.bs_hi = 0;
+      ac.yd = 0.f;
+      return;
+    }
+    const int blk = u >> 2, g = u & 3;
+    const int4* q8 = reinterpret_cast<const int4*>(a.qs + (size_t)m * k + blk * 256 + 64 * g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int4 v = q8[i];
+      ac.q[4 * i] = v.x, ac.q[4 * i + 1] = v.y, ac.q[4 * i + 2] = v.z, ac.q[4 * i + 3] = v.w;
+    }
+    const int2 bs = *reinterpret_cast<const int2*>(a.bsums + (size_t)m * (k >> 4) + blk * 16 + 4 * g);
+    ac.bs_lo = (int)(short)(bs.x & 0xffff) + (bs.x >> 16);
+    ac.bs_hi = (int)(short)(bs.y & 0xffff) + (bs.y >> 16);
+    ac.yd = a.d[(size_t)m * (k >> 8) + blk];
+  }
+  template <int M>
+  __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
+    const uint4 hdr = lds128(rowbase + un.off_hdr);
+    const uint4 qa = lds128(rowbase + un.off_qs);
+    const uint4 qb = lds128(rowbase + un.off_qs + 16);
+    const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
+    // scales / mins of sub-blocks 2g, 2g+1 as two bytes each (get_scale_min_k4, fuel-quantized/src/utils.rs:50-60)
+    const uint32_t lo_sc = (hdr.y >> un.sh) & 0x3f3fu, lo_mn = (hdr.z >> un.sh) & 0x3f3fu;
+    const uint32_t hi_sc = ((hdr.w >> un.sh) & 0x0f0fu) | (((hdr.y >> (un.sh + 6)) & 0x0303u) << 4);
+    const uint32_t hi_mn = ((hdr.w >> (un.sh + 4)) & 0x0f0fu) | (((hdr.z >> (un.sh + 6)) & 0x0303u) << 4);
+    const uint32_t sc2 = un.upper ? hi_sc : lo_sc, mn2 = un.upper ? hi_mn : lo_mn;
+    const int sc_lo = sc2 & 0xff, sc_hi = sc2 >> 8, mn_lo = mn2 & 0xff, mn_hi = mn2 >> 8;
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int i = 0; i < M; ++i) {
+      int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;  // four independent chains
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        dl0 = dp4a_ss((int)(w[j] & 0x0f0f0f0fu), ac[i].q[j], dl0);
+        dl1 = dp4a_ss((int)(w[j + 1] & 0x0f0f0f0fu), ac[i].q[j + 1], dl1);
+        dh0 = dp4a_us(w[j] & 0xf0f0f0f0u, ac[i].q[8 + j], dh0);  // 16 x the high-nibble dot product
+        dh1 = dp4a_us(w[j + 1] & 0xf0f0f0f0u, ac[i].q[9 + j], dh1);
+      }
+      const int dl = dl0 + dl1, dh = dh0 + dh1;
+      const int si = sc_lo * dl + sc_hi * (dh >> 4);
+      const int mi = mn_lo * ac[i].bs_lo + mn_hi * ac[i].bs_hi;
+      acc[i] += (d * ac[i].yd) * (float)si - (dmin * ac[i].yd) * (float)mi;
+    }
+  }
+};
+
+struct DecodeRegsSmemHeader {
+  uint64_t full[kDecodeMaxStages];
+  uint64_t empty[kDecodeMaxStages];
+  uint64_t part_ready[2];
+  float partial[2][32][8][2];  // [buffer][row in stage][k-slice][m]
+};
+
+template <class Fmt, int M, int NU>
+__global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const DecodeRegsParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  DecodeRegsSmemHeader* hd = reinterpret_cast<DecodeRegsSmemHeader*>(smem_raw);
+  uint8_t* stages = smem_raw + align_up(sizeof(DecodeRegsSmemHeader), 128);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.num_stages, R = p.rows_per_stage;
+  const int64_t r_begin = p.n * (int64_t)blockIdx.x / gridDim.x;
+  const int64_t r_end = p.n * (int64_t)(blockIdx.x + 1) / gridDim.x;
+  const int n_iter = (int)((r_end - r_begin + R - 1) / R);
+  if (p.trace && threadIdx.x == 0) p.trace[4 * blockIdx.x] = gtimer();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&hd->full[s], 1);
+      mbar_init(&hd->empty[s], kDecodeConsumerWarps);
+    }
+    mbar_init(&hd->part_ready[0], kDecodeConsumerWarps);
+    mbar_init(&hd->part_ready[1], kDecodeConsumerWarps);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  if (warp == kDecodeConsumerWarps) {
+    // ---------------- producer (weights do not depend on the previous kernel: no pdl_wait before loading)
+    if (lane == 0) {
+      const int64_t tma_limit = p.total_bytes & ~(int64_t)15;
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < n_iter; ++it) {
+        const int s = it % S;
+        if (it >= S && !mbar_wait_bounded(&hd->empty[s], ((it / S) - 1) & 1)) {
+          record_dev_error(kErrEmptyWait);
+          ok = false;
+          break;
+        }
+        const int64_t row0 = r_begin + (int64_t)it * R;
+        const int64_t row1 = (row0 + R < r_end) ? row0 + R : r_end;
+        const int64_t b0 = row0 * p.row_bytes, b1 = row1 * p.row_bytes;
+        const int64_t a0 = b0 & ~(int64_t)15;
+        int64_t a1 = (b1 + 15) & ~(int64_t)15;
+        if (a1 > tma_limit) a1 = tma_limit;
+        uint8_t* dst = stages + (size_t)s * p.stage_stride;
+        if (b1 > a1) {
+          const int64_t from = a1 > a0 ? a1 : a0;
+          for (int64_t j = from; j < b1; ++j) dst[j - a0] = p.w[j];
+        }
+        if (a1 > a0) {
+          mbar_arrive_expect_tx(&hd->full[s], (uint32_t)(a1 - a0));
+          bulk_g2s(dst, p.w + a0, (uint32_t)(a1 - a0), &hd->full[s]);
+        } else {
+          mbar_arrive(&hd->full[s]);
+        }
+        issued = it + 1;
+      }
+      if (!ok) {
+        for (int it = (issued > S ? issued - S : 0); it < issued; ++it)
+          if (!mbar_wait_bounded(&hd->full[it % S], (it / S) & 1)) record_dev_error(kErrDrainWait);
+      }
+    }
+    pdl_wait();
+    return;
+  }
+
+  // ---------------- consumers
+  const int ks = p.ks;
+  const int slice = warp % ks, rgroup = warp / ks, n_rgroups = kDecodeConsumerWarps / ks;
+  const int u_begin = (int)((int64_t)p.units_per_row * slice / ks);
+  const int u_end = (int)((int64_t)p.units_per_row * (slice + 1) / ks);
+
+  typename Fmt::Unit un[NU];
+  typename Fmt::Act ac[NU][M];
+  pdl_wait();  // activation planes are written by the preceding kernel
+#pragma unroll
+  for (int j = 0; j < NU; ++j) {
+    const int u = u_begin + lane + 32 * j;
+    const bool valid = u < u_end;
+    Fmt::make_unit(u, valid, un[j]);
+#pragma unroll
+    for (int i = 0; i < M; ++i) Fmt::load_act(u, valid, p.act, p.k, i, ac[j][i]);
+  }
+
+  const uint32_t stages_u32 = smem_u32(stages);
+  if (p.trace && threadIdx.x == 0) p.trace[4 * blockIdx.x + 1] = gtimer();
+  for (int it = 0; it < n_iter; ++it) {
+    const int s = it % S;
+    if (!mbar_wait_bounded(&hd->full[s], (it / S) & 1)) {
+      record_dev_error(kErrFullWait);
+      return;
+    }
+    if (p.trace && threadIdx.x == 0 && (it == 0 || it == n_iter - 1)) p.trace[4 * blockIdx.x + (it == 0 ? 2 : 3)] = gtimer();
+    const int64_t row0 = r_begin + (int64_t)it * R;
+    const int rows_here = (int)((row0 + R < r_end ? row0 + R : r_end) - row0);
+    const uint32_t sbase = stages_u32 + (uint32_t)s * p.stage_stride + (uint32_t)((row0 * p.row_bytes) & 15);
+    const int buf = it & 1;
+    for (int r = rgroup; r < rows_here && !(p.debug_flags & 1); r += n_rgroups) {
+      const uint32_t rowbase = sbase + (uint32_t)r * p.row_bytes;
+      float acc[M];
+#pragma unroll
+      for (int i = 0; i < M; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NU; ++j) Fmt::template compute<M>(rowbase, un[j], ac[j], acc);
+#pragma unroll
+      for (int i = 0; i < M; ++i) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < M; ++i) {
+          if (ks == 1)
+            p.y[(size_t)i * p.n + row0 + r] = acc[i];
+          else
+            hd->partial[buf][r][slice][i] = acc[i];
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&hd->empty[s]);
+    if (ks > 1) {
+      if (lane == 0) mbar_arrive(&hd->part_ready[buf]);
+      __syncwarp();  // reconverge first: lanes spinning below must not starve lane 0's arrive
+      if (!mbar_wait_bounded(&hd->part_ready[buf], (it >> 1) & 1)) {
+        record_dev_error(kErrFullWait);
+        return;
+      }
+      for (int t = threadIdx.x; t < rows_here * M; t += 32 * kDecodeConsumerWarps) {
+        const int r = t / M, i = t - r * M;
+        float sum = hd->partial[buf][r][0][i];
+        for (int sg = 1; sg < ks; ++sg) sum += hd->partial[buf][r][sg][i];
+        p.y[(size_t)i * p.n + row0 + r] = sum;
+      }
+    }
+  }
+}
+
+}  // namespace fq

@@ -107,18 +107,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+  // the last operand is a suspend-time hint in ns: the thread may sleep in hardware up to that
+  // long waiting for the phase instead of spinning through issue slots
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a
-// hardware-defined time slice) and reports failure instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+// Bounded wait: gives up after `limit` polls (each poll may suspend up to the hint above, so
+// the default bound is about two seconds) and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 100000u) {
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
@@ -133,11 +135,39 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
                : "memory");
 }
 
+// Bulk prefetch of a global range into L2 (no shared-memory destination, no completion to wait on).
+// Address 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
+
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization
 // attribute may start before its predecessor finishes; it must not touch data the
 // predecessor writes until pdl_wait() returns. Both are no-ops in a plain launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Streams a weight buffer from HBM into L2 ahead of the kernel that will read it. Launched
+// with programmatic dependent launch it runs beside the PREVIOUS mat-vec, so the HBM transfer
+// of the next matrix overlaps the current one's arithmetic and the dependency bubble between
+// kernels. It ends with pdl_wait() so that kernels ordered after it still wait, transitively,
+// for everything before it.
+__global__ void __launch_bounds__(32) prefetch_l2_kernel(const uint8_t* __restrict__ w, long long bytes) {
+  pdl_launch_dependents();
+  const long long chunk = 4096;
+  const long long n_chunks = (bytes & ~15ll) / chunk;
+  const long long per = (n_chunks + gridDim.x - 1) / gridDim.x;
+  const long long c0 = per * blockIdx.x;
+  long long c1 = c0 + per;
+  if (c1 > n_chunks) c1 = n_chunks;
+  for (long long c = c0 + threadIdx.x; c < c1; c += 32) bulk_prefetch_l2(w + c * chunk, (uint32_t)chunk);
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+    const long long done = n_chunks * chunk, rest = (bytes & ~15ll) - done;
+    if (rest > 0) bulk_prefetch_l2(w + done, (uint32_t)rest);
+  }
+  pdl_wait();
+}
+
 
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
 

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include "decode.cuh"
+#include "decode_regs.cuh"
 #include "dequantize.cuh"
 #include "fq_common.cuh"
 #include "quantize_act.cuh"
@@ -20,6 +21,11 @@ struct Options {
   int64_t pdl = 0;
   int64_t decode_max_m = kDecodeMaxM;
   int64_t decode_grid = 0;
+  int64_t debug_flags = 0;
+  int64_t trace_ptr = 0;
+  int64_t dbg_stage_kb = 0, dbg_max_stages = 0, dbg_smem_kb = 0;
+  int64_t l2_prefetch = 0;
+  int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
 };
 Options g_opt;
 
@@ -179,8 +185,98 @@ cudaError_t launch_decode_fmt(const DecodeParams& p, const DecodePlan& pl, cudaS
   return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p);
 }
 
+// ---- register-resident variant (decode_regs.cuh): M <= 2, rows that fit NU <= 2 units per lane
+struct RegsPlan {
+  int rows_per_stage, ks, nu, num_stages, stage_stride, grid;
+  size_t smem;
+};
+
+int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl) {
+  int ks = 1;
+  while (ks <= 8 && (units_per_row + ks - 1) / ks > 64) ks *= 2;
+  if (ks > 8) return kNotSupported;
+  const int per_slice = (units_per_row + ks - 1) / ks;
+  pl->ks = ks;
+  pl->nu = per_slice > 32 ? 2 : 1;
+  const int n_rgroups = kDecodeConsumerWarps / ks;
+  const size_t header = align_up(sizeof(DecodeRegsSmemHeader), 128);
+  const size_t per_cta_budget = ((size_t)di.max_smem_optin + 1024) / 2 - 1024 - 512;
+  const size_t ring_budget = (g_opt.dbg_smem_kb ? (size_t)g_opt.dbg_smem_kb * 1024 : per_cta_budget) - header;
+  const int stage_target = g_opt.dbg_stage_kb ? (int)g_opt.dbg_stage_kb * 1024 : 24 * 1024;
+  int fit = (stage_target - 32) / row_bytes;
+  if (fit > 32) fit = 32;
+  int R = fit >= n_rgroups ? fit / n_rgroups * n_rgroups : (fit >= 1 ? fit : 1);
+  const int stride = (int)align_up((size_t)R * row_bytes + 32, 128);
+  int stages = (int)(ring_budget / stride);
+  if (stages < 2) return kNotSupported;
+  if (stages > kDecodeMaxStages) stages = kDecodeMaxStages;
+  if (g_opt.dbg_max_stages && stages > g_opt.dbg_max_stages) stages = (int)g_opt.dbg_max_stages;
+  int grid = g_opt.decode_grid > 0 ? (int)g_opt.decode_grid : 2 * di.sm_count;
+  if (grid > n) grid = (int)n;
+  pl->rows_per_stage = R;
+  pl->num_stages = stages;
+  pl->stage_stride = stride;
+  pl->grid = grid;
+  pl->smem = header + (size_t)stages * stride;
+  return kOk;
+}
+
+template <class Fmt, int M, int NU>
+cudaError_t launch_decode_regs(const DecodeRegsParams& p, const RegsPlan& pl, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  auto kern = decode_regs_kernel<Fmt, M, NU>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    DeviceInfo* di;
+    if (!device_info(&di)) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p);
+}
+
+// returns kNotSupported when this variant does not cover the problem (the caller falls back)
+int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
+                         cudaStream_t stream) {
+  if (m > 2 || type != kQ4K) return kNotSupported;
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  DecodeRegsParams p;
+  p.units_per_row = (int)(k / 256) * Q4KRegs::kUnitsPerBlock;
+  p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
+  RegsPlan pl;
+  const int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl);
+  if (st != kOk) return st;
+  p.w = (const uint8_t*)w;
+  p.act = act_planes(packed_act, type, m, k);
+  p.y = y;
+  p.n = n;
+  p.k = (int)k;
+  p.m = (int)m;
+  p.total_bytes = n * (int64_t)p.row_bytes;
+  p.rows_per_stage = pl.rows_per_stage;
+  p.ks = pl.ks;
+  p.num_stages = pl.num_stages;
+  p.stage_stride = pl.stage_stride;
+  p.debug_flags = (int)g_opt.debug_flags;
+  p.trace = (unsigned long long*)(uintptr_t)g_opt.trace_ptr;
+  cudaError_t e;
+  if (m == 1)
+    e = pl.nu == 1 ? launch_decode_regs<Q4KRegs, 1, 1>(p, pl, stream) : launch_decode_regs<Q4KRegs, 1, 2>(p, pl, stream);
+  else
+    e = pl.nu == 1 ? launch_decode_regs<Q4KRegs, 2, 1>(p, pl, stream) : launch_decode_regs<Q4KRegs, 2, 2>(p, pl, stream);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
 int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
                     cudaStream_t stream) {
+  if (g_opt.decode_kernel != 1) {
+    const int32_t st = decode_regs_impl(type, m, n, k, w, packed_act, y, stream);
+    if (st != kNotSupported || g_opt.decode_kernel == 2) return st;
+  }
   DeviceInfo* di;
   if (!device_info(&di)) return kLaunchFailure;
   DecodePlan pl;
@@ -220,6 +316,18 @@ int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, vo
     default:
       return kNotSupported;
   }
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// Weight stream-in ahead of use (see prefetch_l2_kernel). One small CTA per SM.
+int32_t prefetch_impl(const void* w, int64_t bytes, cudaStream_t stream) {
+  if (bytes <= 0) return kOk;
+  if (!w) return kInvalidProblem;
+  if (!aligned(w, 16)) return kMisaligned;
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  const cudaError_t e = launch(prefetch_l2_kernel, dim3(di->sm_count), dim3(32), 0, stream, (const uint8_t*)w,
+                               (long long)bytes);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
@@ -264,6 +372,16 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
       if (value < 0 || value > 65535) return kInvalidProblem;
       g_opt.decode_grid = value;
       return kOk;
+    case FUELQ_OPT_DECODE_KERNEL:
+      if (value < 0 || value > 2) return kInvalidProblem;
+      g_opt.decode_kernel = value;
+      return kOk;
+    case 100: g_opt.debug_flags = value; return kOk;  // development switches, not part of the contract
+    case 101: g_opt.trace_ptr = value; return kOk;
+    case 102: g_opt.dbg_stage_kb = value; return kOk;
+    case 103: g_opt.dbg_max_stages = value; return kOk;
+    case 104: g_opt.dbg_smem_kb = value; return kOk;
+    case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     default: return kInvalidProblem;
   }
 }
@@ -273,6 +391,8 @@ int64_t fuelq_get_option(int32_t key) {
     case FUELQ_OPT_PDL: return g_opt.pdl;
     case FUELQ_OPT_DECODE_MAX_M: return g_opt.decode_max_m;
     case FUELQ_OPT_DECODE_GRID: return g_opt.decode_grid;
+    case FUELQ_OPT_DECODE_KERNEL: return g_opt.decode_kernel;
+    case FUELQ_OPT_L2_PREFETCH: return g_opt.l2_prefetch;
     default: return -1;
   }
 }
@@ -331,6 +451,10 @@ int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int6
   if (!w || !packed_act || !y) return kInvalidProblem;
   if (!aligned(w, 16) || !aligned(packed_act, 16) || !aligned(y, 4)) return kMisaligned;
   if (m_total > kDecodeMaxM) return kNotSupported;
+  if (g_opt.l2_prefetch) {
+    const int32_t sp = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
+    if (sp != kOk) return sp;
+  }
   return decode_impl(ggml_type, m_total, n, k, w, const_cast<void*>(packed_act), y, (cudaStream_t)stream);
 }
 
@@ -345,6 +469,10 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   const size_t need = act_packed_bytes(ggml_type, m_total, k);
   if (!workspace || workspace_bytes < need) return kWorkspace;
   if (!aligned(workspace, 16)) return kMisaligned;
+  if (g_opt.l2_prefetch) {
+    st = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
+    if (st != kOk) return st;
+  }
   st = quantize_act_impl(ggml_type, m_total, k, x, nullptr, workspace, (cudaStream_t)stream);
   if (st != kOk) return st;
   return decode_impl(ggml_type, m_total, n, k, w, workspace, y, (cudaStream_t)stream);
@@ -379,6 +507,11 @@ int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_
   if (cudaMemcpyAsync(y_host, y_dev, (size_t)m_total * n * 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess)
     return kLaunchFailure;
   return kOk;
+}
+
+int32_t fuelq_prefetch_weights(const void* w, int64_t bytes, void* stream) {
+  if (bytes < 0) return kInvalidProblem;
+  return prefetch_impl(w, bytes, (cudaStream_t)stream);
 }
 
 int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x, void* blocks, void* stream_v) {

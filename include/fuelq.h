@@ -53,6 +53,11 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
                                     prefetch overlaps its predecessor's tail (default 0) */
 #define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the decode mat-vec (default 16) */
 #define FUELQ_OPT_DECODE_GRID 3  /* CTAs for the decode kernel; 0 = two per SM (default) */
+#define FUELQ_OPT_DECODE_KERNEL 4 /* 0 = pick per problem (default); 1 = generic decode kernel (activations read
+                                    through L1, any M <= 16); 2 = register-resident kernel only (M <= 2) */
+#define FUELQ_OPT_L2_PREFETCH 5   /* 1: every mat-vec call first enqueues a small kernel that streams its weight
+                                    matrix from HBM into L2; with FUELQ_OPT_PDL it runs beside the preceding
+                                    kernels, so the transfer overlaps their work (default 0) */
 int32_t fuelq_set_option(int32_t key, int64_t value);
 int64_t fuelq_get_option(int32_t key);
 
@@ -102,6 +107,11 @@ size_t fuelq_qmatmul_host_workspace_bytes(int32_t ggml_type, int64_t m_total, in
 int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
                            const float* x_host, float* y_host, void* workspace, size_t workspace_bytes,
                            void* stream);
+
+/* Streams `bytes` of a weight buffer from HBM into L2 ahead of the call that will read it (no
+ * reference counterpart: the reference has no notion of cache residency; the nearest thing is its
+ * transfer-cost model, fuel-hardware/src/transfer_cost.rs). Purely a hint: results never depend on it. */
+int32_t fuelq_prefetch_weights(const void* w, int64_t bytes, void* stream);
 
 /* The mat-vec alone, on activations already quantized by fuelq_quantize_act_packed. */
 int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
