@@ -36,6 +36,17 @@ PROTOTYPES = {
     "fuelq_qmatmul_packed": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "fuelq_quantize_weights": (_i32, [_i32, _i64, _vp, _vp, _vp]),
     "fuelq_dequantize": (_i32, [_i32, _i64, _vp, _vp, _i32, _vp]),
+    # include/fuelq_host.h
+    "fuelq_last_error": (ctypes.c_char_p, []),
+    "fuelq_qtensor_load": (_i32, [_i32, _vp, _i32, _i64, _i64, _vp, _sz, ctypes.POINTER(_vp)]),
+    "fuelq_qtensor_quantize": (_i32, [_i32, _vp, _i32, _i64, _i64, _vp, _i32, ctypes.POINTER(_vp)]),
+    "fuelq_qtensor_free": (_i32, [_vp]),
+    "fuelq_qtensor_info": (_i32, [_vp, ctypes.POINTER(_i32), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
+                                  ctypes.POINTER(_sz), ctypes.POINTER(_vp)]),
+    "fuelq_qtensor_data": (_i32, [_vp, _vp, _sz]),
+    "fuelq_qtensor_dequantize": (_i32, [_vp, _vp, _i32]),
+    "fuelq_qmatmul_forward": (_i32, [_vp, _vp, _i64, _vp]),
+    "fuelq_qmatmul_forward_host": (_i32, [_vp, _vp, _i64, _vp]),
 }
 
 

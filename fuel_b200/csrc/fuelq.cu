@@ -239,7 +239,7 @@ cudaError_t launch_decode_regs(const DecodeRegsParams& p, const RegsPlan& pl, cu
 }
 
 // returns kNotSupported when this variant does not cover the problem (the caller falls back)
-int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
+int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const ActPlanes& planes, float* y,
                          cudaStream_t stream) {
   if (m > 2 || type != kQ4K) return kNotSupported;
   DeviceInfo* di;
@@ -251,7 +251,7 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   const int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl);
   if (st != kOk) return st;
   p.w = (const uint8_t*)w;
-  p.act = act_planes(packed_act, type, m, k);
+  p.act = planes;
   p.y = y;
   p.n = n;
   p.k = (int)k;
@@ -271,10 +271,10 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
-int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
+int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const ActPlanes& planes, float* y,
                     cudaStream_t stream) {
   if (g_opt.decode_kernel != 1) {
-    const int32_t st = decode_regs_impl(type, m, n, k, w, packed_act, y, stream);
+    const int32_t st = decode_regs_impl(type, m, n, k, w, planes, y, stream);
     if (st != kNotSupported || g_opt.decode_kernel == 2) return st;
   }
   DeviceInfo* di;
@@ -284,7 +284,7 @@ int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, vo
   if (st != kOk) return st;
   DecodeParams p;
   p.w = (const uint8_t*)w;
-  p.act = act_planes(packed_act, type, m, k);
+  p.act = planes;
   p.y = y;
   p.n = n;
   p.k = (int)k;
@@ -329,6 +329,24 @@ int32_t prefetch_impl(const void* w, int64_t bytes, cudaStream_t stream) {
   const cudaError_t e = launch(prefetch_l2_kernel, dim3(di->sm_count), dim3(32), 0, stream, (const uint8_t*)w,
                                (long long)bytes);
   return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// Any m_total through the decode kernels: activation rows are taken kDecodeMaxM at a time, each
+// chunk streaming the weights once. Exactly the integer arithmetic of the small-M path.
+int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
+                       cudaStream_t stream) {
+  const ActPlanes all = act_planes(packed_act, type, m_total, k);
+  const int abe = block_elems(act_type_for(type));
+  for (int64_t m0 = 0; m0 < m_total; m0 += kDecodeMaxM) {
+    const int64_t mc = m_total - m0 < kDecodeMaxM ? m_total - m0 : kDecodeMaxM;
+    ActPlanes a;
+    a.qs = all.qs + m0 * k;
+    a.d = all.d + m0 * (k / abe);
+    a.bsums = all.bsums ? all.bsums + m0 * (k / 16) : nullptr;
+    const int32_t st = decode_impl(type, mc, n, k, w, a, y + m0 * n, stream);
+    if (st != kOk) return st;
+  }
+  return kOk;
 }
 
 int32_t check_problem(int type, int64_t m, int64_t n, int64_t k) {
@@ -436,7 +454,6 @@ size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t
 int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
   const int32_t st = check_problem(ggml_type, m_total, n, k);
   if (st != kOk) return st;
-  if (m_total > g_opt.decode_max_m) return kNotSupported;
   DeviceInfo* di;
   if (!device_info(&di)) return kLaunchFailure;
   DecodePlan pl;
@@ -450,12 +467,11 @@ int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int6
   if (m_total == 0 || n == 0) return kOk;
   if (!w || !packed_act || !y) return kInvalidProblem;
   if (!aligned(w, 16) || !aligned(packed_act, 16) || !aligned(y, 4)) return kMisaligned;
-  if (m_total > kDecodeMaxM) return kNotSupported;
   if (g_opt.l2_prefetch) {
     const int32_t sp = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
     if (sp != kOk) return sp;
   }
-  return decode_impl(ggml_type, m_total, n, k, w, const_cast<void*>(packed_act), y, (cudaStream_t)stream);
+  return decode_chunked(ggml_type, m_total, n, k, w, const_cast<void*>(packed_act), y, (cudaStream_t)stream);
 }
 
 int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
@@ -465,7 +481,6 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   if (m_total == 0 || n == 0) return kOk;
   if (!w || !x || !y) return kInvalidProblem;
   if (!aligned(w, 16) || !aligned(x, 16) || !aligned(y, 4)) return kMisaligned;
-  if (m_total > g_opt.decode_max_m) return kNotSupported;
   const size_t need = act_packed_bytes(ggml_type, m_total, k);
   if (!workspace || workspace_bytes < need) return kWorkspace;
   if (!aligned(workspace, 16)) return kMisaligned;
@@ -475,7 +490,7 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   }
   st = quantize_act_impl(ggml_type, m_total, k, x, nullptr, workspace, (cudaStream_t)stream);
   if (st != kOk) return st;
-  return decode_impl(ggml_type, m_total, n, k, w, workspace, y, (cudaStream_t)stream);
+  return decode_chunked(ggml_type, m_total, n, k, w, workspace, y, (cudaStream_t)stream);
 }
 
 size_t fuelq_qmatmul_host_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
