@@ -7,8 +7,9 @@
 //   * each lane owns fixed positions along k for the whole kernel and keeps the matching
 //     8-bit activations, block sums and scales in registers (loaded once, after the
 //     predecessor kernel is known to have finished) — no activation loads in the loop;
-//   * a lane's unit is 32 bytes of nibbles (Q4_K: one 64-element group, two sub-blocks), so
-//     the 6-bit scale decode is paid once per 32 bytes;
+//   * a lane's unit is 64 bytes of nibbles (Q4_K: half a super-block, four sub-blocks), so one
+//     header load and one 4-wide 6-bit scale decode are paid per 64 bytes; the mins term is
+//     two dp2a instructions on packed int16 block sums;
 //   * high nibbles are not shifted down: dp4a(unsigned bytes & 0xf0, act) gives 16x the
 //     dot product, which is shifted once;
 //   * every byte offset is a lane constant; per row only the row base changes.
@@ -34,6 +35,7 @@ struct DecodeRegsParams {
   int ks;  // warps per row: 1, 2, 4 or 8
   int num_stages;
   int stage_stride;
+  int depth;                      // copies a CTA keeps in flight (< num_stages)
   int debug_flags;                // bit 0: consumers skip the arithmetic (streaming-rate experiments)
   unsigned long long* trace;      // optional: 4 global-timer stamps per CTA
 };
@@ -55,72 +57,81 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
   return d;
 }
 
-// ---- Q4_K: unit = 32 bytes of nibbles = group g of a super-block (elements 64g..64g+63)
+// ---- Q4_K: unit = 64 bytes of nibbles = half a super-block (groups 2h, 2h+1: sub-blocks 4h..4h+3,
+// elements 128h..128h+127). One header load and one 4-wide scale decode per 64 bytes.
 struct Q4KRegs {
-  static constexpr int kUnitsPerBlock = 4;
+  static constexpr int kUnitsPerBlock = 2;
   struct Unit {
     uint32_t off_hdr, off_qs;  // byte offsets from the row base
-    uint32_t sh;               // 16 * (g & 1)
-    bool upper;                // g >= 2: scales 4..7 use the split 4+2 bit packing
+    bool upper;                // h == 1: scales 4..7 use the split 4+2 bit packing
   };
   struct Act {
-    int q[16];  // 64 activations: [0..8) words pair with low nibbles, [8..16) with high nibbles
-    int bs_lo, bs_hi;
+    int q[32];       // 128 activations, in element order
+    int bs01, bs23;  // sums of the four 32-element sub-blocks as packed int16 pairs
     float yd;
   };
   __device__ __forceinline__ static void make_unit(int u, bool valid, Unit& un) {
-    const int blk = valid ? (u >> 2) : 0, g = valid ? (u & 3) : 0;
+    const int blk = valid ? (u >> 1) : 0, h = valid ? (u & 1) : 0;
     un.off_hdr = blk * Q4KL::kBytes;
-    un.off_qs = blk * Q4KL::kBytes + Q4KL::kOffQs + 32 * g;
-    un.sh = 16 * (g & 1);
-    un.upper = g >= 2;
+    un.off_qs = blk * Q4KL::kBytes + Q4KL::kOffQs + 64 * h;
+    un.upper = h != 0;
   }
   __device__ __forceinline__ static void load_act(int u, bool valid, const ActPlanes& a, int k, int m, Act& ac) {
     if (!valid) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) ac.q[i] = 0;
-      ac.bs_lo = ac.bs_hi = 0;
+      for (int i = 0; i < 32; ++i) ac.q[i] = 0;
+      ac.bs01 = ac.bs23 = 0;
       ac.yd = 0.f;
       return;
     }
-    const int blk = u >> 2, g = u & 3;
-    const int4* q8 = reinterpret_cast<const int4*>(a.qs + (size_t)m * k + blk * 256 + 64 * g);
+    const int blk = u >> 1, h = u & 1;
+    const int4* q8 = reinterpret_cast<const int4*>(a.qs + (size_t)m * k + blk * 256 + 128 * h);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
       const int4 v = q8[i];
       ac.q[4 * i] = v.x, ac.q[4 * i + 1] = v.y, ac.q[4 * i + 2] = v.z, ac.q[4 * i + 3] = v.w;
     }
-    const int2 bs = *reinterpret_cast<const int2*>(a.bsums + (size_t)m * (k >> 4) + blk * 16 + 4 * g);
-    ac.bs_lo = (int)(short)(bs.x & 0xffff) + (bs.x >> 16);
-    ac.bs_hi = (int)(short)(bs.y & 0xffff) + (bs.y >> 16);
+    // eight 16-element sums -> four 32-element sums (each |s| <= 4096, fits int16)
+    const int4 bs = *reinterpret_cast<const int4*>(a.bsums + (size_t)m * (k >> 4) + blk * 16 + 8 * h);
+    const int s0 = (int)(short)(bs.x & 0xffff) + (bs.x >> 16), s1 = (int)(short)(bs.y & 0xffff) + (bs.y >> 16);
+    const int s2 = (int)(short)(bs.z & 0xffff) + (bs.z >> 16), s3 = (int)(short)(bs.w & 0xffff) + (bs.w >> 16);
+    ac.bs01 = (s0 & 0xffff) | (s1 << 16);
+    ac.bs23 = (s2 & 0xffff) | (s3 << 16);
     ac.yd = a.d[(size_t)m * (k >> 8) + blk];
   }
   template <int M>
   __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
     const uint4 hdr = lds128(rowbase + un.off_hdr);
-    const uint4 qa = lds128(rowbase + un.off_qs);
-    const uint4 qb = lds128(rowbase + un.off_qs + 16);
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = lds128(rowbase + un.off_qs + 16 * i);
+      w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+    }
     const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
-    // scales / mins of sub-blocks 2g, 2g+1 as two bytes each (get_scale_min_k4, fuel-quantized/src/utils.rs:50-60)
-    const uint32_t lo_sc = (hdr.y >> un.sh) & 0x3f3fu, lo_mn = (hdr.z >> un.sh) & 0x3f3fu;
-    const uint32_t hi_sc = ((hdr.w >> un.sh) & 0x0f0fu) | (((hdr.y >> (un.sh + 6)) & 0x0303u) << 4);
-    const uint32_t hi_mn = ((hdr.w >> (un.sh + 4)) & 0x0f0fu) | (((hdr.z >> (un.sh + 6)) & 0x0303u) << 4);
-    const uint32_t sc2 = un.upper ? hi_sc : lo_sc, mn2 = un.upper ? hi_mn : lo_mn;
-    const int sc_lo = sc2 & 0xff, sc_hi = sc2 >> 8, mn_lo = mn2 & 0xff, mn_hi = mn2 >> 8;
-    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    // four 6-bit scales and mins at once, one per byte (get_scale_min_k4, fuel-quantized/src/utils.rs:50-60)
+    const uint32_t sc_lo4 = hdr.y & 0x3f3f3f3fu, mn_lo4 = hdr.z & 0x3f3f3f3fu;
+    const uint32_t sc_hi4 = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+    const uint32_t mn_hi4 = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
+    const uint32_t sc4 = un.upper ? sc_hi4 : sc_lo4, mn4 = un.upper ? mn_hi4 : mn_lo4;
+    const int sc0 = sc4 & 0xff, sc1 = (sc4 >> 8) & 0xff, sc2 = (sc4 >> 16) & 0xff, sc3 = sc4 >> 24;
 #pragma unroll
     for (int i = 0; i < M; ++i) {
-      int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;  // four independent chains
+      int d0a = 0, d0b = 0, d1a = 0, d1b = 0, d2a = 0, d2b = 0, d3a = 0, d3b = 0;  // independent chains
 #pragma unroll
       for (int j = 0; j < 8; j += 2) {
-        dl0 = dp4a_ss((int)(w[j] & 0x0f0f0f0fu), ac[i].q[j], dl0);
-        dl1 = dp4a_ss((int)(w[j + 1] & 0x0f0f0f0fu), ac[i].q[j + 1], dl1);
-        dh0 = dp4a_us(w[j] & 0xf0f0f0f0u, ac[i].q[8 + j], dh0);  // 16 x the high-nibble dot product
-        dh1 = dp4a_us(w[j + 1] & 0xf0f0f0f0u, ac[i].q[9 + j], dh1);
+        d0a = dp4a_ss((int)(w[j] & 0x0f0f0f0fu), ac[i].q[j], d0a);
+        d0b = dp4a_ss((int)(w[j + 1] & 0x0f0f0f0fu), ac[i].q[j + 1], d0b);
+        d1a = dp4a_us(w[j] & 0xf0f0f0f0u, ac[i].q[8 + j], d1a);  // 16 x the high-nibble dot product
+        d1b = dp4a_us(w[j + 1] & 0xf0f0f0f0u, ac[i].q[9 + j], d1b);
+        d2a = dp4a_ss((int)(w[8 + j] & 0x0f0f0f0fu), ac[i].q[16 + j], d2a);
+        d2b = dp4a_ss((int)(w[9 + j] & 0x0f0f0f0fu), ac[i].q[17 + j], d2b);
+        d3a = dp4a_us(w[8 + j] & 0xf0f0f0f0u, ac[i].q[24 + j], d3a);
+        d3b = dp4a_us(w[9 + j] & 0xf0f0f0f0u, ac[i].q[25 + j], d3b);
       }
-      const int dl = dl0 + dl1, dh = dh0 + dh1;
-      const int si = sc_lo * dl + sc_hi * (dh >> 4);
-      const int mi = mn_lo * ac[i].bs_lo + mn_hi * ac[i].bs_hi;
+      // the two high-nibble dots are multiples of 16, and stay so after the integer scale
+      const int si = sc0 * (d0a + d0b) + sc2 * (d2a + d2b) + ((sc1 * (d1a + d1b) + sc3 * (d3a + d3b)) >> 4);
+      const int mi = __dp2a_hi(ac[i].bs23, (int)mn4, __dp2a_lo(ac[i].bs01, (int)mn4, 0));
       acc[i] += (d * ac[i].yd) * (float)si - (dmin * ac[i].yd) * (float)mi;
     }
   }
@@ -170,6 +181,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
           record_dev_error(kErrEmptyWait);
           ok = false;
           break;
+        }
+        // Keep at most `depth` copies of this CTA in flight: with every CTA's whole share queued
+        // at once the memory system interleaves them all and no stage completes until nearly all
+        // have, which serializes streaming and arithmetic in a kernel this short. A bounded depth
+        // makes stages complete in order, so consumers start after the first one.
+        if (it >= p.depth) {
+          const int j = it - p.depth;
+          if (!mbar_wait_bounded(&hd->full[j % S], (j / S) & 1)) {
+            record_dev_error(kErrFullWait);
+            ok = false;
+            break;
+          }
         }
         const int64_t row0 = r_begin + (int64_t)it * R;
         const int64_t row1 = (row0 + R < r_end) ? row0 + R : r_end;

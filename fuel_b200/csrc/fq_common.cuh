@@ -121,8 +121,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after `limit` polls (each poll may suspend up to the hint above, so
 // the default bound is about two seconds) and reports failure instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 100000u) {
-  for (uint32_t i = 0; i < limit; ++i)
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (i >= 2) __nanosleep(i < 64 ? 40 : 400);  // back off: waiting warps should not eat issue slots
+  }
   return false;
 }
 

@@ -25,6 +25,7 @@ struct Options {
   int64_t trace_ptr = 0;
   int64_t dbg_stage_kb = 0, dbg_max_stages = 0, dbg_smem_kb = 0;
   int64_t l2_prefetch = 0;
+  int64_t dbg_depth = 0;
   int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
 };
 Options g_opt;
@@ -193,8 +194,8 @@ struct RegsPlan {
 
 int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl) {
   int ks = 1;
-  while (ks <= 8 && (units_per_row + ks - 1) / ks > 64) ks *= 2;
-  if (ks > 8) return kNotSupported;
+  while (ks < 8 && (units_per_row + ks - 1) / ks > 32) ks *= 2;  // one unit per lane if eight slices allow it
+  if ((units_per_row + ks - 1) / ks > 64) return kNotSupported;
   const int per_slice = (units_per_row + ks - 1) / ks;
   pl->ks = ks;
   pl->nu = per_slice > 32 ? 2 : 1;
@@ -261,6 +262,8 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.ks = pl.ks;
   p.num_stages = pl.num_stages;
   p.stage_stride = pl.stage_stride;
+  p.depth = g_opt.dbg_depth ? (int)g_opt.dbg_depth : 3;
+  if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
   p.debug_flags = (int)g_opt.debug_flags;
   p.trace = (unsigned long long*)(uintptr_t)g_opt.trace_ptr;
   cudaError_t e;
@@ -399,6 +402,7 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 102: g_opt.dbg_stage_kb = value; return kOk;
     case 103: g_opt.dbg_max_stages = value; return kOk;
     case 104: g_opt.dbg_smem_kb = value; return kOk;
+    case 105: g_opt.dbg_depth = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     default: return kInvalidProblem;
   }
