@@ -36,8 +36,11 @@ struct DecodeRegsParams {
   int num_stages;
   int stage_stride;
   int depth;                      // copies a CTA keeps in flight (< num_stages)
+  int pre_stages;                 // stages issued before the consumers hold their activations (0 = all)
+  int rows_q, rows_rem;           // n / grid, n % grid: CTA c owns rows_q (+1 if c < rows_rem) rows
+  int u_begin[9];                 // unit range of k-slice s: [u_begin[s], u_begin[s+1])
   int debug_flags;                // bit 0: consumers skip the arithmetic (streaming-rate experiments)
-  unsigned long long* trace;      // optional: 4 global-timer stamps per CTA
+  unsigned long long* trace;      // optional: 24 global-timer stamps per CTA
 };
 
 __device__ __forceinline__ unsigned long long gtimer() {
@@ -99,6 +102,7 @@ struct Q4KRegs {
     ac.bs23 = (s2 & 0xffff) | (s3 << 16);
     ac.yd = a.d[(size_t)m * (k >> 8) + blk];
   }
+  __device__ __forceinline__ static int probe(const Act& ac) { return ac.q[0] ^ ac.q[31] ^ ac.bs23 ^ __float_as_int(ac.yd); }
   template <int M>
   __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
     const uint4 hdr = lds128(rowbase + un.off_hdr);
@@ -141,6 +145,7 @@ struct DecodeRegsSmemHeader {
   uint64_t full[kDecodeMaxStages];
   uint64_t empty[kDecodeMaxStages];
   uint64_t part_ready[2];
+  uint64_t acts_ready;
   float partial[2][32][8][2];  // [buffer][row in stage][k-slice][m]
 };
 
@@ -152,10 +157,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.num_stages, R = p.rows_per_stage;
-  const int64_t r_begin = p.n * (int64_t)blockIdx.x / gridDim.x;
-  const int64_t r_end = p.n * (int64_t)(blockIdx.x + 1) / gridDim.x;
-  const int n_iter = (int)((r_end - r_begin + R - 1) / R);
-  if (p.trace && threadIdx.x == 0) p.trace[4 * blockIdx.x] = gtimer();
+  // this CTA's contiguous rows; all index arithmetic is 32-bit with host-computed quotients, since a
+  // CTA lives for only a few dozen rows and 64-bit divisions would dominate its prologue
+  const int cta = blockIdx.x;
+  const int r_begin = cta * p.rows_q + (cta < p.rows_rem ? cta : p.rows_rem);
+  const int r_count = p.rows_q + (cta < p.rows_rem ? 1 : 0);
+  const int n_iter = (int)(((unsigned)r_count + (unsigned)R - 1u) / (unsigned)R);
+  if (p.trace && threadIdx.x == 0) p.trace[24 * blockIdx.x] = gtimer();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -164,6 +172,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
     }
     mbar_init(&hd->part_ready[0], kDecodeConsumerWarps);
     mbar_init(&hd->part_ready[1], kDecodeConsumerWarps);
+    mbar_init(&hd->acts_ready, kDecodeConsumerWarps);
     mbar_init_fence();
   }
   __syncthreads();
@@ -175,33 +184,39 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
       const int64_t tma_limit = p.total_bytes & ~(int64_t)15;
       int issued = 0;
       bool ok = true;
+      int s = 0, js = 0;          // ring slot of stage `it`, and of stage `it - depth`
+      uint32_t ph = 0, jph = 0;   // their phase parities
       for (int it = 0; it < n_iter; ++it) {
-        const int s = it % S;
-        if (it >= S && !mbar_wait_bounded(&hd->empty[s], ((it / S) - 1) & 1)) {
+        if (it >= S && !mbar_wait_bounded(&hd->empty[s], ph ^ 1u)) {
           record_dev_error(kErrEmptyWait);
           ok = false;
           break;
         }
-        // Keep at most `depth` copies of this CTA in flight: with every CTA's whole share queued
-        // at once the memory system interleaves them all and no stage completes until nearly all
-        // have, which serializes streaming and arithmetic in a kernel this short. A bounded depth
-        // makes stages complete in order, so consumers start after the first one.
+        // Activation loads queue behind whatever bulk traffic this SM has outstanding; hold the
+        // rest of the stream back until the consumers have theirs.
+        if (p.pre_stages && it == p.pre_stages && !mbar_wait_bounded(&hd->acts_ready, 0)) {
+          record_dev_error(kErrFullWait);
+          ok = false;
+          break;
+        }
+        // Keep at most `depth` copies of this CTA in flight, so stages complete in order and the
+        // consumers can start on the first while the rest stream in.
         if (it >= p.depth) {
-          const int j = it - p.depth;
-          if (!mbar_wait_bounded(&hd->full[j % S], (j / S) & 1)) {
+          if (!mbar_wait_bounded(&hd->full[js], jph)) {
             record_dev_error(kErrFullWait);
             ok = false;
             break;
           }
+          if (++js == S) js = 0, jph ^= 1u;
         }
-        const int64_t row0 = r_begin + (int64_t)it * R;
-        const int64_t row1 = (row0 + R < r_end) ? row0 + R : r_end;
-        const int64_t b0 = row0 * p.row_bytes, b1 = row1 * p.row_bytes;
+        const int row0 = r_begin + it * R;
+        const int rows_here = (r_count - it * R < R) ? r_count - it * R : R;
+        const int64_t b0 = (int64_t)row0 * p.row_bytes, b1 = b0 + (int64_t)rows_here * p.row_bytes;
         const int64_t a0 = b0 & ~(int64_t)15;
         int64_t a1 = (b1 + 15) & ~(int64_t)15;
         if (a1 > tma_limit) a1 = tma_limit;
         uint8_t* dst = stages + (size_t)s * p.stage_stride;
-        if (b1 > a1) {
+        if (b1 > a1) {  // matrix ends off a 16-byte boundary: last few bytes by hand
           const int64_t from = a1 > a0 ? a1 : a0;
           for (int64_t j = from; j < b1; ++j) dst[j - a0] = p.w[j];
         }
@@ -212,8 +227,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
           mbar_arrive(&hd->full[s]);
         }
         issued = it + 1;
+        if (++s == S) s = 0, ph ^= 1u;
       }
-      if (!ok) {
+      if (!ok) {  // consumers stopped releasing stages: let our own copies land before leaving
         for (int it = (issued > S ? issued - S : 0); it < issued; ++it)
           if (!mbar_wait_bounded(&hd->full[it % S], (it / S) & 1)) record_dev_error(kErrDrainWait);
       }
@@ -224,9 +240,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
 
   // ---------------- consumers
   const int ks = p.ks;
-  const int slice = warp % ks, rgroup = warp / ks, n_rgroups = kDecodeConsumerWarps / ks;
-  const int u_begin = (int)((int64_t)p.units_per_row * slice / ks);
-  const int u_end = (int)((int64_t)p.units_per_row * (slice + 1) / ks);
+  const int slice = warp & (ks - 1), rgroup = warp / ks, n_rgroups = kDecodeConsumerWarps / ks;  // ks is a power of two
+  const int u_begin = p.u_begin[slice], u_end = p.u_begin[slice + 1];
 
   typename Fmt::Unit un[NU];
   typename Fmt::Act ac[NU][M];
@@ -240,18 +255,32 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
     for (int i = 0; i < M; ++i) Fmt::load_act(u, valid, p.act, p.k, i, ac[j][i]);
   }
 
+  {
+    // wait for the loads to land (a use of the last-loaded registers), then tell the producer
+    int probe = 0;
+#pragma unroll
+    for (int j = 0; j < NU; ++j)
+#pragma unroll
+      for (int i = 0; i < M; ++i) probe ^= Fmt::probe(ac[j][i]);
+    asm volatile("" ::"r"(probe));
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&hd->acts_ready);
+  }
   const uint32_t stages_u32 = smem_u32(stages);
-  if (p.trace && threadIdx.x == 0) p.trace[4 * blockIdx.x + 1] = gtimer();
+  if (p.trace && threadIdx.x == 0) p.trace[24 * blockIdx.x + 1] = gtimer();
+  int s = 0;
+  uint32_t ph = 0;
   for (int it = 0; it < n_iter; ++it) {
-    const int s = it % S;
-    if (!mbar_wait_bounded(&hd->full[s], (it / S) & 1)) {
+    if (!mbar_wait_bounded(&hd->full[s], ph)) {
       record_dev_error(kErrFullWait);
       return;
     }
-    if (p.trace && threadIdx.x == 0 && (it == 0 || it == n_iter - 1)) p.trace[4 * blockIdx.x + (it == 0 ? 2 : 3)] = gtimer();
-    const int64_t row0 = r_begin + (int64_t)it * R;
-    const int rows_here = (int)((row0 + R < r_end ? row0 + R : r_end) - row0);
-    const uint32_t sbase = stages_u32 + (uint32_t)s * p.stage_stride + (uint32_t)((row0 * p.row_bytes) & 15);
+    if (p.trace && threadIdx.x == 0 && (it == 0 || it == n_iter - 1)) p.trace[24 * blockIdx.x + (it == 0 ? 2 : 3)] = gtimer();
+    if (p.trace && threadIdx.x == 0 && it < 10) p.trace[24 * blockIdx.x + 4 + 2 * it] = gtimer();
+    const int row0 = r_begin + it * R;
+    const int rows_here = (r_count - it * R < R) ? r_count - it * R : R;
+    const uint32_t skew = (uint32_t)(((int64_t)row0 * p.row_bytes) & 15);
+    const uint32_t sbase = stages_u32 + (uint32_t)s * p.stage_stride + skew;
     const int buf = it & 1;
     for (int r = rgroup; r < rows_here && !(p.debug_flags & 1); r += n_rgroups) {
       const uint32_t rowbase = sbase + (uint32_t)r * p.row_bytes;
@@ -276,8 +305,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
       }
     }
     __syncwarp();
+    if (p.trace && threadIdx.x == 0 && it < 10) p.trace[24 * blockIdx.x + 5 + 2 * it] = gtimer();
     if (lane == 0) mbar_arrive(&hd->empty[s]);
     if (ks > 1) {
+      // all consumer warps meet here (bounded), then the k-slices of each row are summed in fixed order
       if (lane == 0) mbar_arrive(&hd->part_ready[buf]);
       __syncwarp();  // reconverge first: lanes spinning below must not starve lane 0's arrive
       if (!mbar_wait_bounded(&hd->part_ready[buf], (it >> 1) & 1)) {
@@ -291,6 +322,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
         p.y[(size_t)i * p.n + row0 + r] = sum;
       }
     }
+    if (++s == S) s = 0, ph ^= 1u;
   }
 }
 

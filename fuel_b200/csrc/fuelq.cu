@@ -26,6 +26,7 @@ struct Options {
   int64_t dbg_stage_kb = 0, dbg_max_stages = 0, dbg_smem_kb = 0;
   int64_t l2_prefetch = 0;
   int64_t dbg_depth = 0;
+  int64_t dbg_pre = -1;
   int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
 };
 Options g_opt;
@@ -262,8 +263,12 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.ks = pl.ks;
   p.num_stages = pl.num_stages;
   p.stage_stride = pl.stage_stride;
+  p.rows_q = (int)(n / pl.grid);
+  p.rows_rem = (int)(n % pl.grid);
+  for (int sl = 0; sl <= 8; ++sl) p.u_begin[sl] = sl <= pl.ks ? (int)((int64_t)p.units_per_row * sl / pl.ks) : p.units_per_row;
   p.depth = g_opt.dbg_depth ? (int)g_opt.dbg_depth : 3;
   if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
+  p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
   p.debug_flags = (int)g_opt.debug_flags;
   p.trace = (unsigned long long*)(uintptr_t)g_opt.trace_ptr;
   cudaError_t e;
@@ -403,6 +408,7 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 103: g_opt.dbg_max_stages = value; return kOk;
     case 104: g_opt.dbg_smem_kb = value; return kOk;
     case 105: g_opt.dbg_depth = value; return kOk;
+    case 106: g_opt.dbg_pre = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     default: return kInvalidProblem;
   }
