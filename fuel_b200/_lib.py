@@ -32,6 +32,8 @@ PROTOTYPES = {
     "fuelq_qmatmul": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "fuelq_qmatmul_host_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul_host": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "fuelq_static_scratch_bytes": (_sz, []),
+    "fuelq_qmatmul_static_scratch": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "fuelq_prefetch_weights": (_i32, [_vp, _i64, _vp]),
     "fuelq_qmatmul_packed": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "fuelq_quantize_weights": (_i32, [_i32, _i64, _vp, _vp, _vp]),

@@ -534,6 +534,39 @@ int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_
   return kOk;
 }
 
+// ---- mat-vec for callers that cannot allocate -------------------------------------------------
+// Some hosts of this library may not call cudaMalloc at all: code running inside a captured or
+// latency-critical region whose memory was fixed at start-up, plug-in sandboxes that are handed
+// device pointers but no allocator, or a process whose memory pool is owned by another runtime.
+// For them the activation scratch lives in the library image itself: a fixed device array that
+// every GPU loading the library carries until the process exits.
+constexpr size_t kStaticScratchBytes = 1u << 20;  // 1 MiB: e.g. m_total * k up to ~900k elements
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+size_t fuelq_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int32_t fuelq_qmatmul_static_scratch(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
+                                     const float* x, float* y, void* stream) {
+  const int32_t st = check_problem(ggml_type, m_total, n, k);
+  if (st != kOk) return st;
+  if (m_total == 0 || n == 0) return kOk;
+  // sizes beyond the built-in scratch are refused, never truncated
+  if (act_packed_bytes(ggml_type, m_total, k) > kStaticScratchBytes) return kWorkspace;
+  // In host code the array's name is only a handle; the device address has to be asked for, once
+  // per device, with that device current.
+  static void* scratch_addr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kLaunchFailure;
+  if (!scratch_addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return kLaunchFailure;
+    scratch_addr[dev] = p;
+  }
+  // every plane of the scratch is written by the activation-quantization kernel before the
+  // mat-vec reads it, so nothing in it needs clearing between calls
+  return fuelq_qmatmul(ggml_type, m_total, n, k, w, x, y, scratch_addr[dev], kStaticScratchBytes, stream);
+}
+
 int32_t fuelq_prefetch_weights(const void* w, int64_t bytes, void* stream) {
   if (bytes < 0) return kInvalidProblem;
   return prefetch_impl(w, bytes, (cudaStream_t)stream);

@@ -108,6 +108,23 @@ int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_
                            const float* x_host, float* y_host, void* workspace, size_t workspace_bytes,
                            void* stream);
 
+/* fuelq_qmatmul without a workspace argument, for callers that are not able to allocate device
+ * memory (no counterpart in the reference, whose CUDA forward allocates on every call,
+ * fuel-cuda-backend/src/quantized.rs:193-198): a plug-in that receives device pointers but owns no
+ * allocator, or code whose memory was fixed before it started. The activation scratch is a 1 MiB
+ * array built into the library and resident on every GPU that loads it until the process ends.
+ *  - problems whose activation blocks need more than fuelq_static_scratch_bytes() are refused with
+ *    status 4 (roughly m_total * k > 900 000 elements); nothing is truncated;
+ *  - the first call on each device also does the set-up (it looks up the array's device address);
+ *    that first call should come before any stream capture begins;
+ *  - all calls share the one array: two calls whose kernels may run at the same time on the GPU
+ *    (different streams, or different host threads) would overwrite each other's activations. Keep
+ *    them on one stream. Nothing in the array has to be cleared between calls.
+ * Results are bit-identical to fuelq_qmatmul. Calls no allocation routine of any kind. */
+size_t fuelq_static_scratch_bytes(void);
+int32_t fuelq_qmatmul_static_scratch(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
+                                     const float* x, float* y, void* stream);
+
 /* Streams `bytes` of a weight buffer from HBM into L2 ahead of the call that will read it (no
  * reference counterpart: the reference has no notion of cache residency; the nearest thing is its
  * transfer-cost model, fuel-hardware/src/transfer_cost.rs). Purely a hint: results never depend on it. */
