@@ -348,7 +348,7 @@ def main():
                    "pdl": bool(args.pdl), "parallelism": f"independent matrices per rank x{world}"},
         "pct_of_8tbs": value / world / 8000.0 * 100.0,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_matvec_kernel<Q4KDecode,1>",
+                     "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_regs_kernel<Q4KRegs,1,1>",
                      "avg_launch_us": kern_us, "algorithmic_bytes_per_launch": ALGO_BYTES},
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * M_ROWS * K_IN * 4,

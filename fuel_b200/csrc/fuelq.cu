@@ -204,7 +204,7 @@ int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const Devi
   const size_t header = align_up(sizeof(DecodeRegsSmemHeader), 128);
   const size_t per_cta_budget = ((size_t)di.max_smem_optin + 1024) / 2 - 1024 - 512;
   const size_t ring_budget = (g_opt.dbg_smem_kb ? (size_t)g_opt.dbg_smem_kb * 1024 : per_cta_budget) - header;
-  const int stage_target = g_opt.dbg_stage_kb ? (int)g_opt.dbg_stage_kb * 1024 : 24 * 1024;
+  const int stage_target = g_opt.dbg_stage_kb ? (int)g_opt.dbg_stage_kb * 1024 : 40 * 1024;  // two rows per consumer warp per stage at k = 4096
   int fit = (stage_target - 32) / row_bytes;
   if (fit > 32) fit = 32;
   int R = fit >= n_rgroups ? fit / n_rgroups * n_rgroups : (fit >= 1 ? fit : 1);
