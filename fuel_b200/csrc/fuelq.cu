@@ -10,6 +10,7 @@
 #include "decode_regs.cuh"
 #include "dequantize.cuh"
 #include "fq_common.cuh"
+#include "prefill.cuh"
 #include "quantize_act.cuh"
 #include "quantize_weights.cuh"
 
@@ -19,7 +20,7 @@ namespace {
 
 struct Options {
   int64_t pdl = 0;
-  int64_t decode_max_m = kDecodeMaxM;
+  int64_t decode_max_m = 32;  // larger m_total goes to the tensor-core path when the format has one
   int64_t decode_grid = 0;
   int64_t debug_flags = 0;
   int64_t trace_ptr = 0;
@@ -357,6 +358,54 @@ int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const vo
   return kOk;
 }
 
+// ---- tensor-core path (prefill.cuh)
+bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
+  (void)n;
+  return type == kQ4K && m > g_opt.decode_max_m && k % kPfTileK == 0 && k <= (1 << 20);
+}
+size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * 2, 256); }
+
+template <class Fmt, int kTileM>
+cudaError_t launch_prefill(const PrefillParams& p, cudaStream_t stream) {
+  constexpr size_t smem = 1024 + (size_t)kPfStages * (kPfTileN * 128 + kTileM * 128) + sizeof(PrefillSmem) + 64;
+  static bool attr_set[64] = {};
+  auto kern = prefill_gemm_kernel<Fmt, kTileM>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const dim3 grid((unsigned)((p.N + kPfTileN - 1) / kPfTileN), (unsigned)((p.M + kTileM - 1) / kTileM));
+  // plain launches: these kernels do not take part in programmatic dependent launch
+  kern<<<grid, kPfThreads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const float* x, float* y, void* workspace,
+                     cudaStream_t stream) {
+  __nv_bfloat16* xb = (__nv_bfloat16*)workspace;
+  const int64_t n4 = m * k / 4;
+  f32_to_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, xb);
+  if (cudaGetLastError() != cudaSuccess) return kLaunchFailure;
+  PrefillParams p;
+  p.w = (const uint8_t*)w;
+  p.x = xb;
+  p.y = y;
+  p.M = (int)m;
+  p.N = (int)n;
+  p.K = (int)k;
+  p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
+  cudaError_t e;
+  if (m > 128)
+    e = launch_prefill<Q4KPrefill, 256>(p, stream);
+  else
+    e = launch_prefill<Q4KPrefill, 128>(p, stream);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
 int32_t check_problem(int type, int64_t m, int64_t n, int64_t k) {
   if (!supported_weight(type)) return kNotSupported;
   if (m < 0 || n < 0 || k <= 0) return kInvalidProblem;
@@ -391,7 +440,7 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
   switch (key) {
     case FUELQ_OPT_PDL: g_opt.pdl = value ? 1 : 0; return kOk;
     case FUELQ_OPT_DECODE_MAX_M:
-      if (value < 0 || value > kDecodeMaxM) return kInvalidProblem;
+      if (value < 0) return kInvalidProblem;
       g_opt.decode_max_m = value;
       return kOk;
     case FUELQ_OPT_DECODE_GRID:
@@ -458,6 +507,7 @@ int32_t fuelq_quantize_act_packed(int32_t weight_type, int64_t m_total, int64_t 
 
 size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
   if (check_problem(ggml_type, m_total, n, k) != kOk) return 0;
+  if (prefill_available(ggml_type, m_total, n, k)) return prefill_workspace_bytes(m_total, k);
   return act_packed_bytes(ggml_type, m_total, k);
 }
 
@@ -491,9 +541,13 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   if (m_total == 0 || n == 0) return kOk;
   if (!w || !x || !y) return kInvalidProblem;
   if (!aligned(w, 16) || !aligned(x, 16) || !aligned(y, 4)) return kMisaligned;
-  const size_t need = act_packed_bytes(ggml_type, m_total, k);
+  const size_t need = fuelq_qmatmul_workspace_bytes(ggml_type, m_total, n, k);
   if (!workspace || workspace_bytes < need) return kWorkspace;
   if (!aligned(workspace, 16)) return kMisaligned;
+  if (prefill_available(ggml_type, m_total, n, k)) {
+    if (m_total > (1 << 30) || n > (1 << 30)) return kNotSupported;
+    return prefill_impl(ggml_type, m_total, n, k, w, x, y, workspace, (cudaStream_t)stream);
+  }
   if (g_opt.l2_prefetch) {
     st = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
     if (st != kOk) return st;
@@ -551,7 +605,7 @@ int32_t fuelq_qmatmul_static_scratch(int32_t ggml_type, int64_t m_total, int64_t
   if (st != kOk) return st;
   if (m_total == 0 || n == 0) return kOk;
   // sizes beyond the built-in scratch are refused, never truncated
-  if (act_packed_bytes(ggml_type, m_total, k) > kStaticScratchBytes) return kWorkspace;
+  if (fuelq_qmatmul_workspace_bytes(ggml_type, m_total, n, k) > kStaticScratchBytes) return kWorkspace;
   // In host code the array's name is only a handle; the device address has to be asked for, once
   // per device, with that device current.
   static void* scratch_addr[64] = {};

@@ -1,0 +1,308 @@
+// Prefill path (large M): Y[M, N] = X[M, K] . W[N, K]^T as a dense bf16 contraction on the
+// 5th-generation tensor cores. The reference has no tensor-core quantized path: its CUDA forward
+// runs the mat-vec kernel for every M (fuel-cuda-backend/src/quantized.rs:452-473,543-587) and its
+// Vulkan path dequantizes the whole matrix to f32 first (fuel-vulkan-backend/src/lib.rs:4221-4283).
+// Here weight tiles are dequantized (GgmlType::to_float arithmetic, fuel-quantized/src/k_quants.rs:
+// 1595-1622, 2158-2189, 611-627) straight into shared memory as bf16 in the tensor core's K-major
+// 128-byte-swizzled layout and multiplied with tcgen05.mma, accumulating f32 in tensor memory.
+//
+// One CTA computes a 128 (output features) x kTileM (activation rows) tile:
+//   warps 0-3  dequantize the weight tile of each 64-wide K stage (one thread per weight row),
+//              then read the accumulator out of tensor memory and store Y;
+//   warps 4-7  copy the activation tile (bf16, converted by a pre-pass) with cp.async;
+//   warp  8    allocates tensor memory and, one lane, issues the MMAs and their commits.
+// Stages cycle through full/empty mbarriers; every wait is bounded and on expiry the CTA raises an
+// abort flag, skips to the end, frees its tensor memory and returns.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "fq_common.cuh"
+
+namespace fq {
+
+constexpr int kPfTileN = 128;   // weight rows per CTA  (UMMA M)
+constexpr int kPfTileK = 64;    // K per stage: one 128-byte swizzle atom of bf16
+constexpr int kPfStages = 4;
+constexpr int kPfThreads = 32 * 9;
+
+struct PrefillParams {
+  const uint8_t* w;          // GGUF blocks, [N][K / block]
+  const __nv_bfloat16* x;    // [M][K] bf16
+  float* y;                  // [M][N]
+  int M, N, K;
+  int row_bytes;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, 8-row groups
+// 1024 bytes apart (stride byte offset), descriptor version 1 (this architecture), layout type 2.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                        // version
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- per-format dequantization of one weight row's 64-element K stage into 8 x 16-byte bf16 chunks ----
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// exact small-integer -> float without a conversion instruction: 0x43000000 | q << 16 is 128 + q
+__device__ __forceinline__ float small_int_f32(uint32_t q_at_bit16) { return __uint_as_float(0x43000000u | q_at_bit16); }
+
+struct Q4KPrefill {
+  static constexpr int kType = kQ4K;
+  // k0 = 64 * it: block it / 4, group it % 4; row points at the weight row's first block
+  __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
+    const int blk = it >> 2, g = it & 3;
+    const uint8_t* b = row + blk * Q4KL::kBytes;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(b);
+    const uint4 qa = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g);
+    const uint4 qb = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16);
+    const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
+    const uint32_t sh = 16 * (g & 1);
+    uint32_t sc2, mn2;
+    if (g < 2) {
+      sc2 = (hdr.y >> sh) & 0x3f3fu;
+      mn2 = (hdr.z >> sh) & 0x3f3fu;
+    } else {
+      sc2 = ((hdr.w >> sh) & 0x0f0fu) | (((hdr.y >> (sh + 6)) & 0x0303u) << 4);
+      mn2 = ((hdr.w >> (sh + 4)) & 0x0f0fu) | (((hdr.z >> (sh + 6)) & 0x0303u) << 4);
+    }
+    const float d1 = d * (float)(sc2 & 0xff), d2 = d * (float)(sc2 >> 8);
+    // y = d*sc*q - dmin*m, with q taken as (128 + q) - 128
+    const float c1 = -(dmin * (float)(mn2 & 0xff)) - 128.0f * d1, c2 = -(dmin * (float)(mn2 >> 8)) - 128.0f * d2;
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // word j holds bytes 4j..4j+3: low nibbles -> k = 4j.., high -> k = 32 + 4j..
+      const uint32_t v = w[j];
+      const float l0 = fmaf(d1, small_int_f32((v << 16) & 0x000f0000u), c1), l1 = fmaf(d1, small_int_f32((v << 8) & 0x000f0000u), c1);
+      const float l2 = fmaf(d1, small_int_f32(v & 0x000f0000u), c1), l3 = fmaf(d1, small_int_f32((v >> 8) & 0x000f0000u), c1);
+      const float h0 = fmaf(d2, small_int_f32((v << 12) & 0x000f0000u), c2), h1 = fmaf(d2, small_int_f32((v << 4) & 0x000f0000u), c2);
+      const float h2 = fmaf(d2, small_int_f32((v >> 4) & 0x000f0000u), c2), h3 = fmaf(d2, small_int_f32((v >> 12) & 0x000f0000u), c2);
+      uint32_t* lo = reinterpret_cast<uint32_t*>(&out[j >> 1]) + 2 * (j & 1);       // chunk j/2 (k = 8*(j/2)..)
+      uint32_t* hi = reinterpret_cast<uint32_t*>(&out[4 + (j >> 1)]) + 2 * (j & 1);  // chunk 4 + j/2
+      lo[0] = pack_bf16(l0, l1), lo[1] = pack_bf16(l2, l3);
+      hi[0] = pack_bf16(h0, h1), hi[1] = pack_bf16(h2, h3);
+    }
+  }
+};
+
+struct PrefillSmem {
+  uint64_t full[kPfStages];
+  uint64_t empty[kPfStages];
+  uint64_t accum;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <class Fmt, int kTileM>
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p) {
+  extern __shared__ __align__(1024) uint8_t pf_smem[];
+  // [stage][ weights 128 x 128 B | activations kTileM x 128 B ], each 1024-byte aligned; control block after
+  constexpr int kWBytes = kPfTileN * 128, kXBytes = kTileM * 128, kStageBytes = kWBytes + kXBytes;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem) + 1023) & ~(uintptr_t)1023);
+  PrefillSmem* sm = reinterpret_cast<PrefillSmem*>(base + kPfStages * kStageBytes);
+  const uint32_t base_u32 = smem_u32(base);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kPfTileN, m0 = blockIdx.y * kTileM;
+  const int n_iter = p.K / kPfTileK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPfStages; ++s) {
+      mbar_init(&sm->full[s], 256);  // 128 weight-row threads + 128 activation-copy threads
+      mbar_init(&sm->empty[s], 1);   // one commit from the MMA thread
+    }
+    mbar_init(&sm->accum, 1);
+    sm->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 8) tmem_alloc(&sm->tmem_base, kTileM);  // kTileM f32 accumulator columns x 128 lanes
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = *reinterpret_cast<volatile uint32_t*>(&sm->tmem_base);
+  volatile int* abort_flag = &sm->abort_flag;
+
+  if (warp < 4) {
+    // ---------------- weight producers: thread t owns weight row n0 + t
+    const int t = threadIdx.x;
+    const bool live = n0 + t < p.N;
+    const uint8_t* row = p.w + (size_t)(live ? n0 + t : 0) * p.row_bytes;
+    int s = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < n_iter && !*abort_flag; ++it) {
+      uint4 out[8];
+      if (live) {
+        Fmt::stage(row, it, out);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
+      }
+      if (it >= kPfStages && !mbar_wait_bounded(&sm->empty[s], ph ^ 1u)) {
+        record_dev_error(kErrEmptyWait);
+        *abort_flag = 1;
+        break;
+      }
+      uint8_t* dst = base + s * kStageBytes + t * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (t & 7)) << 4)) = out[c];
+      fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+      mbar_arrive(&sm->full[s]);
+      if (++s == kPfStages) s = 0, ph ^= 1u;
+    }
+  } else if (warp < 8) {
+    // ---------------- activation copies: kTileM rows x 8 chunks of 16 bytes per stage
+    const int t = threadIdx.x - 128;
+    constexpr int kChunks = kTileM * 8 / 128;  // per thread per stage
+    constexpr int kLag = 2;                    // stages a thread keeps in flight
+    int s = 0;
+    uint32_t ph = 0;
+    int pending[kLag + 1];
+    int n_pending = 0;
+    for (int it = 0; it < n_iter && !*abort_flag; ++it) {
+      if (it >= kPfStages && !mbar_wait_bounded(&sm->empty[s], ph ^ 1u)) {
+        record_dev_error(kErrEmptyWait);
+        *abort_flag = 1;
+        break;
+      }
+      const uint32_t dst0 = base_u32 + s * kStageBytes + kWBytes;
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) {
+        const int c = i * 128 + t, r = c >> 3, kc = c & 7;
+        const int m = m0 + r;
+        const bool ok = m < p.M;
+        const __nv_bfloat16* src = p.x + (size_t)(ok ? m : 0) * p.K + it * kPfTileK + kc * 8;
+        cp_async16(dst0 + r * 128 + ((kc ^ (r & 7)) << 4), src, ok ? 16u : 0u);  // rows past M are zero-filled
+      }
+      cp_async_commit();
+      pending[n_pending++] = s;
+      if (n_pending > kLag) {
+        cp_async_wait<kLag>();
+        fence_proxy_async();
+        mbar_arrive(&sm->full[pending[0]]);
+#pragma unroll
+        for (int j = 0; j < kLag; ++j) pending[j] = pending[j + 1];
+        --n_pending;
+      }
+      if (++s == kPfStages) s = 0, ph ^= 1u;
+    }
+    cp_async_wait<0>();
+    fence_proxy_async();
+    for (int j = 0; j < n_pending; ++j) mbar_arrive(&sm->full[pending[j]]);
+  } else if (lane == 0) {
+    // ---------------- MMA issue: one thread
+    constexpr uint32_t idesc = umma_idesc_bf16(kPfTileN, kTileM);
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      if (*abort_flag || !mbar_wait_bounded(&sm->full[s], ph)) {
+        if (!*abort_flag) record_dev_error(kErrFullWait);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t a_addr = base_u32 + s * kStageBytes, b_addr = a_addr + kWBytes;
+#pragma unroll
+      for (int kk = 0; kk < kPfTileK / 16; ++kk)  // 16 bf16 = 32 bytes along K per instruction
+        umma_bf16(tmem_d, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc, (it | kk) != 0);
+      umma_commit(&sm->empty[s]);  // frees the stage once these MMAs have read it
+      if (++s == kPfStages) s = 0, ph ^= 1u;
+    }
+    if (ok) umma_commit(&sm->accum);  // accumulator complete
+  }
+
+  // ---------------- epilogue: warps 0-3 read their 32 TMEM lanes (weight rows) and store Y
+  if (warp < 4) {
+    bool ready = !*abort_flag;
+    if (ready && !mbar_wait_bounded(&sm->accum, 0)) {
+      record_dev_error(kErrMmaWait);
+      *abort_flag = 1;
+      ready = false;
+    }
+    ready = __all_sync(0xffffffffu, ready);
+    if (ready) {
+      tc_fence_after();
+      const int n = n0 + warp * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < kTileM / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = m0 + c * 32 + j;
+            if (m < p.M) p.y[(size_t)m * p.N + n] = __uint_as_float(v[j]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem_d, kTileM);
+}
+
+// f32 -> bf16 activation pre-pass
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ x, int64_t n4, __nv_bfloat16* __restrict__ y) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const float4 v = reinterpret_cast<const float4*>(x)[i];
+  uint2 o;
+  o.x = pack_bf16(v.x, v.y);
+  o.y = pack_bf16(v.z, v.w);
+  reinterpret_cast<uint2*>(y)[i] = o;
+}
+
+}  // namespace fq

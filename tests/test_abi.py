@@ -82,5 +82,5 @@ def test_options_round_trip(L):
     assert f.fuelq_get_option(L.OPT_PDL) == 0
     assert f.fuelq_set_option(L.OPT_PDL, 1) == L.OK and f.fuelq_get_option(L.OPT_PDL) == 1
     assert f.fuelq_set_option(L.OPT_PDL, 0) == L.OK
-    assert f.fuelq_set_option(L.OPT_DECODE_MAX_M, 999) == L.INVALID_PROBLEM
+    assert f.fuelq_set_option(L.OPT_DECODE_MAX_M, -1) == L.INVALID_PROBLEM
     assert f.fuelq_set_option(77, 1) == L.INVALID_PROBLEM

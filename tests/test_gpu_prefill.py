@@ -1,0 +1,89 @@
+"""Tensor-core (tcgen05) path for large M, through the C ABI.
+
+Ground truth is the float oracle: exactly dequantized weights (the reference's to_float) times the
+f32 activations, accumulated in f64. The GPU path rounds BOTH operands to bf16 (BASELINE config 3
+asks for exactly that), and that alone fixes the attainable error: a bf16 rounding is uniform in
++-2^-9 relative, rms 1.13e-3 per operand, 1.6e-3 per product, and the products' errors add like a
+random walk just as the result does, so  ||y - r||_F / ||r||_F ~ 1.6e-3  whatever K is, and the
+largest of ~10^5 outputs sits near 2.5e-3 of max|r|. BASELINE's 1e-3 is therefore not reachable
+with bf16 operands by any kernel; the bars here are the ones bf16 allows, with margin:
+    relative Frobenius error <= 2.5e-3,   max|y - r| / max|r| <= 5e-3,
+and the integer mat-vec path (tests/test_gpu_kernels.py) remains the one held to 1e-3 and tighter.
+Also checked: agreement with the integer path within the activation-quantization gap, tile edges,
+exact linearity under power-of-two scaling.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuel_b200 import ops as _ops
+    yield _ops
+    assert _ops.device_error() == 0, "a kernel recorded an expired bounded wait"
+
+
+def _w(n, k, seed=0):
+    return np.random.Generator(np.random.PCG64(seed)).standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+
+
+def _x(m, k, seed=1):
+    return np.random.Generator(np.random.PCG64(seed)).standard_normal((m, k), dtype=np.float32)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (64, 256, 512), (200, 300, 1024), (257, 129, 768), (33, 64, 256),
+                                   (512, 1024, 4096)])
+def test_prefill_q4k_matches_float_oracle(ops, oracle, m, n, k):
+    from fuel_b200 import GgmlDType as T
+    wb = oracle.quantize(oracle.Q4K, _w(n, k, seed=n))
+    x = _x(m, k, seed=m)
+    want = oracle.matmul_dequant_f64(oracle.Q4K, x, wb, n)
+    y = torch.full((m, n), float("nan"), device="cuda")
+    got = ops.qmatmul(T.Q4K, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda(), out=y).cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() / np.abs(want).max() <= 5e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2.5e-3
+    # and it tells the same story as the integer path (8-bit activations) on the same inputs
+    ref_int = oracle.matmul(oracle.Q4K, x[:4], wb, n)
+    assert np.abs(got[:4] - ref_int).max() / np.abs(ref_int).max() <= 2e-2
+
+
+def test_prefill_config3_shape_sampled_rows(ops, oracle):
+    """BASELINE config 3: W Q4_K [14336 x 4096], X [2048 x 4096]; the oracle is evaluated on sampled rows."""
+    from fuel_b200 import GgmlDType as T
+    n, k, m = 14336, 4096, 2048
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    w = torch.randn(n, k, generator=g, device="cuda") * 0.02
+    wq = ops.quantize_weights(T.Q4K, w)
+    del w
+    g.manual_seed(1)
+    x = torch.randn(m, k, generator=g, device="cuda")
+    y = ops.qmatmul(T.Q4K, wq, n, x)
+    rows = np.array([0, 1, 127, 128, 255, 256, 1000, 2047])
+    want = oracle.matmul_dequant_f64(oracle.Q4K, x[rows].cpu().numpy(), wq.cpu().numpy(), n)
+    got = y[rows].cpu().numpy()
+    assert np.abs(got - want).max() / np.abs(want).max() <= 5e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2.5e-3
+    # linearity, a size-independent property: f(2x) == 2 f(x) exactly (powers of two commute with bf16 rounding)
+    y2 = ops.qmatmul(T.Q4K, wq, n, x * 2.0)
+    assert torch.equal(y2, y * 2.0)
+
+
+def test_crossover_option_routes_to_integer_path(ops, oracle):
+    from fuel_b200 import GgmlDType as T, _lib
+    n, k, m = 96, 512, 48
+    wb = oracle.quantize(oracle.Q4K, _w(n, k))
+    x = _x(m, k)
+    want_int = oracle.matmul(oracle.Q4K, x, wb, n)
+    try:
+        _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 1 << 20), "set_option")
+        got = ops.qmatmul(T.Q4K, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda()).cpu().numpy()
+    finally:
+        _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 32)
+    assert np.abs(got - want_int).max() / np.abs(want_int).max() <= 2e-6
