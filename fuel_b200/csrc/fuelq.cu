@@ -361,7 +361,7 @@ int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const vo
 // ---- tensor-core path (prefill.cuh)
 bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   (void)n;
-  return type == kQ4K && m > g_opt.decode_max_m && k % kPfTileK == 0 && k <= (1 << 20);
+  return (type == kQ4K || type == kQ6K || type == kQ8_0) && m > g_opt.decode_max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }
 size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * 2, 256); }
 
@@ -399,10 +399,13 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   p.K = (int)k;
   p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
   cudaError_t e;
-  if (m > 128)
-    e = launch_prefill<Q4KPrefill, 256>(p, stream);
-  else
-    e = launch_prefill<Q4KPrefill, 128>(p, stream);
+  const bool wide = m > 128;
+  switch (type) {
+    case kQ4K: e = wide ? launch_prefill<Q4KPrefill, 256>(p, stream) : launch_prefill<Q4KPrefill, 128>(p, stream); break;
+    case kQ6K: e = wide ? launch_prefill<Q6KPrefill, 256>(p, stream) : launch_prefill<Q6KPrefill, 128>(p, stream); break;
+    case kQ8_0: e = wide ? launch_prefill<Q8_0Prefill, 256>(p, stream) : launch_prefill<Q8_0Prefill, 128>(p, stream); break;
+    default: return kNotSupported;
+  }
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 

@@ -16,6 +16,7 @@
 #pragma once
 #include <cuda_bf16.h>
 
+#include "dequantize.cuh"
 #include "fq_common.cuh"
 
 namespace fq {
@@ -132,6 +133,54 @@ struct Q4KPrefill {
       uint32_t* hi = reinterpret_cast<uint32_t*>(&out[4 + (j >> 1)]) + 2 * (j & 1);  // chunk 4 + j/2
       lo[0] = pack_bf16(l0, l1), lo[1] = pack_bf16(l2, l3);
       hi[0] = pack_bf16(h0, h1), hi[1] = pack_bf16(h2, h3);
+    }
+  }
+};
+
+// Q8_0: a 64-wide stage is two 34-byte blocks (2-byte aligned): y = q * d
+struct Q8_0Prefill {
+  static constexpr int kType = kQ8_0;
+  __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint8_t* b = row + (size_t)(2 * it + h) * Q8_0L::kBytes;
+      const float d = h2f_bits(ldg_u16(b));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // 4 values per j -> two packed words
+        const uint32_t v0 = ldg_u16(b + Q8_0L::kOffQs + 4 * j), v1 = ldg_u16(b + Q8_0L::kOffQs + 4 * j + 2);
+        const float f0 = (float)(int8_t)(v0 & 0xff) * d, f1 = (float)(int8_t)(v0 >> 8) * d;
+        const float f2 = (float)(int8_t)(v1 & 0xff) * d, f3 = (float)(int8_t)(v1 >> 8) * d;
+        uint32_t* o = reinterpret_cast<uint32_t*>(&out[4 * h + (j >> 1)]) + 2 * (j & 1);
+        o[0] = pack_bf16(f0, f1), o[1] = pack_bf16(f2, f3);
+      }
+    }
+  }
+};
+
+// Q6_K: a 64-wide stage is a quarter super-block: half = elements 128*half.., sub selects low (l, l+32)
+// or high (l+64, l+96) nibbles of the same 64 ql bytes; y = d * sc * (q - 32)
+struct Q6KPrefill {
+  static constexpr int kType = kQ6K;
+  __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
+    const int blk = it >> 2, half = (it >> 1) & 1, sub = it & 1;
+    const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
+    const float d = h2f_bits(ldg_u16(b + Q6KL::kOffD));
+    const uint8_t* ql = b + Q6KL::kOffQl + 64 * half;
+    const uint8_t* qh = b + Q6KL::kOffQh + 32 * half;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(b + Q6KL::kOffScales + 8 * half + 4 * sub);
+    // scales for elements [0,16) [16,32) of the first 32 and of the second 32
+    const float s00 = d * (float)sc[0], s01 = d * (float)sc[1], s10 = d * (float)sc[2], s11 = d * (float)sc[3];
+    const int nsh = 4 * sub, hsh = 4 * sub;  // nibble shift in ql, bit-pair shift in qh (pairs 2*sub, 2*sub+1)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {  // two l values per j
+      const uint32_t a = ldg_u16(ql + 2 * j), c = ldg_u16(ql + 32 + 2 * j), h = ldg_u16(qh + 2 * j);
+      const int a0 = a & 0xff, a1 = a >> 8, c0 = c & 0xff, c1 = c >> 8, h0 = h & 0xff, h1 = h >> 8;
+      const int qa0 = (((a0 >> nsh) & 0xF) | (((h0 >> hsh) & 3) << 4)) - 32, qa1 = (((a1 >> nsh) & 0xF) | (((h1 >> hsh) & 3) << 4)) - 32;
+      const int qc0 = (((c0 >> nsh) & 0xF) | (((h0 >> (hsh + 2)) & 3) << 4)) - 32, qc1 = (((c1 >> nsh) & 0xF) | (((h1 >> (hsh + 2)) & 3) << 4)) - 32;
+      const float sa = j < 8 ? s00 : s01, sb = j < 8 ? s10 : s11;
+      // first 32 elements of the stage: l = 2j, 2j+1 ; second 32: the same l from the other ql half
+      reinterpret_cast<uint32_t*>(&out[j >> 2])[j & 3] = pack_bf16(sa * (float)qa0, sa * (float)qa1);
+      reinterpret_cast<uint32_t*>(&out[4 + (j >> 2)])[j & 3] = pack_bf16(sb * (float)qc0, sb * (float)qc1);
     }
   }
 };

@@ -53,6 +53,19 @@ def test_prefill_q4k_matches_float_oracle(ops, oracle, m, n, k):
     assert np.abs(got[:4] - ref_int).max() / np.abs(ref_int).max() <= 2e-2
 
 
+@pytest.mark.parametrize("name", ["q6k", "q8_0"])
+@pytest.mark.parametrize("m,n,k", [(64, 128, 256), (200, 300, 1024), (130, 129, 4096), (256, 4096, 11008)])
+def test_prefill_other_formats_match_float_oracle(ops, oracle, name, m, n, k):
+    from fuel_b200 import GgmlDType as T
+    t, ot = {"q6k": (T.Q6K, oracle.Q6K), "q8_0": (T.Q8_0, oracle.Q8_0)}[name]
+    wb = oracle.quantize(ot, _w(n, k, seed=n))
+    x = _x(m, k, seed=m)
+    want = oracle.matmul_dequant_f64(ot, x, wb, n)
+    got = ops.qmatmul(t, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.abs(got - want).max() / np.abs(want).max() <= 5e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2.5e-3
+
+
 def test_prefill_config3_shape_sampled_rows(ops, oracle):
     """BASELINE config 3: W Q4_K [14336 x 4096], X [2048 x 4096]; the oracle is evaluated on sampled rows."""
     from fuel_b200 import GgmlDType as T
