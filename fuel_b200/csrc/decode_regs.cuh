@@ -141,6 +141,162 @@ struct Q4KRegs {
   }
 };
 
+// ---- helpers for formats whose blocks are only 2-byte aligned in the stage --------------------
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+// NW consecutive 32-bit words starting at a 2-byte-aligned shared address: NW + 1 aligned loads
+// and one funnel shift each (a no-op shift when the address happens to be 4-byte aligned)
+template <int NW>
+__device__ __forceinline__ void lds_words_2b(uint32_t addr, uint32_t (&w)[NW]) {
+  const uint32_t base = addr & ~3u, sh = (addr & 2u) * 8u;
+  uint32_t prev = lds32(base);
+#pragma unroll
+  for (int i = 0; i < NW; ++i) {
+    const uint32_t nxt = lds32(base + 4 * (i + 1));
+    w[i] = __funnelshift_r(prev, nxt, sh);
+    prev = nxt;
+  }
+}
+
+// ---- Q6_K: unit = half a super-block (128 elements: 64 B ql, 32 B qh, 8 scales). The 6-bit values are
+// used unsigned (0..63) in dp4a; the "-32" of every element is folded into one correction per half,
+// 32 * sum_g scale_g * (sum of the 16 activations of group g), from the activation block sums.
+struct Q6KRegs {
+  static constexpr int kUnitsPerBlock = 2;
+  struct Unit {
+    uint32_t off_blk;  // byte offset of the super-block from the row base
+    uint32_t half;
+  };
+  struct Act {
+    int q[32];
+    int bs[4];  // eight 16-element sums as packed int16 pairs
+    float yd;
+  };
+  __device__ __forceinline__ static void make_unit(int u, bool valid, Unit& un) {
+    un.off_blk = (valid ? (u >> 1) : 0) * Q6KL::kBytes;
+    un.half = valid ? (u & 1) : 0;
+  }
+  __device__ __forceinline__ static void load_act(int u, bool valid, const ActPlanes& a, int k, int m, Act& ac) {
+    if (!valid) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) ac.q[i] = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ac.bs[i] = 0;
+      ac.yd = 0.f;
+      return;
+    }
+    const int blk = u >> 1, h = u & 1;
+    const int4* q8 = reinterpret_cast<const int4*>(a.qs + (size_t)m * k + blk * 256 + 128 * h);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int4 v = q8[i];
+      ac.q[4 * i] = v.x, ac.q[4 * i + 1] = v.y, ac.q[4 * i + 2] = v.z, ac.q[4 * i + 3] = v.w;
+    }
+    const int4 bs = *reinterpret_cast<const int4*>(a.bsums + (size_t)m * (k >> 4) + blk * 16 + 8 * h);
+    ac.bs[0] = bs.x, ac.bs[1] = bs.y, ac.bs[2] = bs.z, ac.bs[3] = bs.w;
+    ac.yd = a.d[(size_t)m * (k >> 8) + blk];
+  }
+  __device__ __forceinline__ static int probe(const Act& ac) { return ac.q[0] ^ ac.q[31] ^ ac.bs[3] ^ __float_as_int(ac.yd); }
+  template <int M>
+  __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
+    const uint32_t b = rowbase + un.off_blk;
+    uint32_t ql[16], qh[8], sc[2];
+    lds_words_2b<16>(b + Q6KL::kOffQl + 64 * un.half, ql);
+    lds_words_2b<8>(b + Q6KL::kOffQh + 32 * un.half, qh);
+    lds_words_2b<2>(b + Q6KL::kOffScales + 8 * un.half, sc);
+    uint16_t dh;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dh) : "r"(b + Q6KL::kOffD));
+    const float d = h2f_bits(dh);
+    // unsigned 6-bit values, four per word; word j covers l = 4j..4j+3
+    uint32_t qv[32];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t h = qh[j];
+      qv[j] = (ql[j] & 0x0f0f0f0fu) | ((h << 4) & 0x30303030u);             // elements l
+      qv[8 + j] = (ql[8 + j] & 0x0f0f0f0fu) | ((h << 2) & 0x30303030u);     // l + 32
+      qv[16 + j] = ((ql[j] >> 4) & 0x0f0f0f0fu) | (h & 0x30303030u);        // l + 64
+      qv[24 + j] = ((ql[8 + j] >> 4) & 0x0f0f0f0fu) | ((h >> 2) & 0x30303030u);  // l + 96
+    }
+    int s8[8];  // signed scales of the eight 16-element groups
+#pragma unroll
+    for (int g = 0; g < 8; ++g) s8[g] = (int)(int8_t)((sc[g >> 2] >> (8 * (g & 3))) & 0xff);
+#pragma unroll
+    for (int i = 0; i < M; ++i) {
+      int si = 0;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        int dg = dp4a_us(qv[4 * g], ac[i].q[4 * g], 0);
+        dg = dp4a_us(qv[4 * g + 1], ac[i].q[4 * g + 1], dg);
+        dg = dp4a_us(qv[4 * g + 2], ac[i].q[4 * g + 2], dg);
+        dg = dp4a_us(qv[4 * g + 3], ac[i].q[4 * g + 3], dg);
+        si += s8[g] * dg;
+      }
+      // correction: sum_g scale_g * bsum_g, two groups per dp2a
+      int corr = __dp2a_lo(ac[i].bs[0], (int)sc[0], 0);
+      corr = __dp2a_hi(ac[i].bs[1], (int)sc[0], corr);
+      corr = __dp2a_lo(ac[i].bs[2], (int)sc[1], corr);
+      corr = __dp2a_hi(ac[i].bs[3], (int)sc[1], corr);
+      acc[i] += (d * ac[i].yd) * (float)(si - 32 * corr);
+    }
+  }
+};
+
+// ---- Q8_0: unit = four 34-byte blocks (128 elements)
+struct Q8_0Regs {
+  static constexpr int kUnitsPerBlock = 0;  // units are counted per 128 elements, see the launcher
+  struct Unit {
+    uint32_t off;  // byte offset of the first of the four blocks
+  };
+  struct Act {
+    int q[32];
+    float yd[4];
+  };
+  __device__ __forceinline__ static void make_unit(int u, bool valid, Unit& un) { un.off = (valid ? u : 0) * 4 * Q8_0L::kBytes; }
+  __device__ __forceinline__ static void load_act(int u, bool valid, const ActPlanes& a, int k, int m, Act& ac) {
+    if (!valid) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) ac.q[i] = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ac.yd[i] = 0.f;
+      return;
+    }
+    const int4* q8 = reinterpret_cast<const int4*>(a.qs + (size_t)m * k + u * 128);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int4 v = q8[i];
+      ac.q[4 * i] = v.x, ac.q[4 * i + 1] = v.y, ac.q[4 * i + 2] = v.z, ac.q[4 * i + 3] = v.w;
+    }
+    const float4 dv = *reinterpret_cast<const float4*>(a.d + (size_t)m * (k >> 5) + u * 4);
+    ac.yd[0] = dv.x, ac.yd[1] = dv.y, ac.yd[2] = dv.z, ac.yd[3] = dv.w;
+  }
+  __device__ __forceinline__ static int probe(const Act& ac) { return ac.q[0] ^ ac.q[31] ^ __float_as_int(ac.yd[3]); }
+  template <int M>
+  __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+      const uint32_t b = rowbase + un.off + blk * Q8_0L::kBytes;
+      uint16_t dh;
+      asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dh) : "r"(b));
+      const float d = h2f_bits(dh);
+      uint32_t w[8];
+      lds_words_2b<8>(b + Q8_0L::kOffQs, w);
+#pragma unroll
+      for (int i = 0; i < M; ++i) {
+        int s0 = 0, s1 = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          s0 = dp4a_ss((int)w[j], ac[i].q[8 * blk + j], s0);
+          s1 = dp4a_ss((int)w[j + 1], ac[i].q[8 * blk + j + 1], s1);
+        }
+        acc[i] += (d * ac[i].yd[blk]) * (float)(s0 + s1);
+      }
+    }
+  }
+};
+
 struct DecodeRegsSmemHeader {
   uint64_t full[kDecodeMaxStages];
   uint64_t empty[kDecodeMaxStages];

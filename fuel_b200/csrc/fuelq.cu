@@ -20,7 +20,7 @@ namespace {
 
 struct Options {
   int64_t pdl = 0;
-  int64_t decode_max_m = 32;  // larger m_total goes to the tensor-core path when the format has one
+  int64_t decode_max_m = 16;  // larger m_total goes to the tensor-core path when the format has one
   int64_t decode_grid = 0;
   int64_t debug_flags = 0;
   int64_t trace_ptr = 0;
@@ -244,11 +244,12 @@ cudaError_t launch_decode_regs(const DecodeRegsParams& p, const RegsPlan& pl, cu
 // returns kNotSupported when this variant does not cover the problem (the caller falls back)
 int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const ActPlanes& planes, float* y,
                          cudaStream_t stream) {
-  if (m > 2 || type != kQ4K) return kNotSupported;
+  if (m > 2 || (type != kQ4K && type != kQ6K && type != kQ8_0)) return kNotSupported;
+  if (type == kQ8_0 && k % 128) return kNotSupported;  // its lane unit is four blocks
   DeviceInfo* di;
   if (!device_info(&di)) return kLaunchFailure;
   DecodeRegsParams p;
-  p.units_per_row = (int)(k / 256) * Q4KRegs::kUnitsPerBlock;
+  p.units_per_row = (int)(k / 128);  // every format's lane unit covers 128 elements
   p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
   RegsPlan pl;
   const int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl);
@@ -273,10 +274,19 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.debug_flags = (int)g_opt.debug_flags;
   p.trace = (unsigned long long*)(uintptr_t)g_opt.trace_ptr;
   cudaError_t e;
-  if (m == 1)
-    e = pl.nu == 1 ? launch_decode_regs<Q4KRegs, 1, 1>(p, pl, stream) : launch_decode_regs<Q4KRegs, 1, 2>(p, pl, stream);
-  else
-    e = pl.nu == 1 ? launch_decode_regs<Q4KRegs, 2, 1>(p, pl, stream) : launch_decode_regs<Q4KRegs, 2, 2>(p, pl, stream);
+#define FQ_REGS_DISPATCH(FMT)                                                                                          \
+  do {                                                                                                                 \
+    if (m == 1)                                                                                                        \
+      e = pl.nu == 1 ? launch_decode_regs<FMT, 1, 1>(p, pl, stream) : launch_decode_regs<FMT, 1, 2>(p, pl, stream);    \
+    else                                                                                                               \
+      e = pl.nu == 1 ? launch_decode_regs<FMT, 2, 1>(p, pl, stream) : launch_decode_regs<FMT, 2, 2>(p, pl, stream);    \
+  } while (0)
+  switch (type) {
+    case kQ4K: FQ_REGS_DISPATCH(Q4KRegs); break;
+    case kQ6K: FQ_REGS_DISPATCH(Q6KRegs); break;
+    default: FQ_REGS_DISPATCH(Q8_0Regs); break;
+  }
+#undef FQ_REGS_DISPATCH
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
@@ -346,8 +356,13 @@ int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const vo
                        cudaStream_t stream) {
   const ActPlanes all = act_planes(packed_act, type, m_total, k);
   const int abe = block_elems(act_type_for(type));
-  for (int64_t m0 = 0; m0 < m_total; m0 += kDecodeMaxM) {
-    const int64_t mc = m_total - m0 < kDecodeMaxM ? m_total - m0 : kDecodeMaxM;
+  // Two rows at a time through the register-resident kernel beats sixteen at a time through the generic
+  // one when the matrix fits in L2 (every pass after the first streams from there).
+  const bool regs_ok = g_opt.decode_kernel != 1 && (type == kQ4K || type == kQ6K || (type == kQ8_0 && k % 128 == 0)) &&
+                       (k / 128 + 7) / 8 <= 64 && m_total > 2;
+  const int64_t step = regs_ok ? 2 : kDecodeMaxM;
+  for (int64_t m0 = 0; m0 < m_total; m0 += step) {
+    const int64_t mc = m_total - m0 < step ? m_total - m0 : step;
     ActPlanes a;
     a.qs = all.qs + m0 * k;
     a.d = all.d + m0 * (k / abe);
@@ -399,7 +414,10 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   p.K = (int)k;
   p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
   cudaError_t e;
-  const bool wide = m > 128;
+  // the wide tile halves the weight dequantization per flop, but only pays once it still fills the SMs
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  const bool wide = m > 128 && ((n + kPfTileN - 1) / kPfTileN) * ((m + 255) / 256) >= di->sm_count;
   switch (type) {
     case kQ4K: e = wide ? launch_prefill<Q4KPrefill, 256>(p, stream) : launch_prefill<Q4KPrefill, 128>(p, stream); break;
     case kQ6K: e = wide ? launch_prefill<Q6KPrefill, 256>(p, stream) : launch_prefill<Q6KPrefill, 128>(p, stream); break;

@@ -51,7 +51,7 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
 /* Options. key: */
 #define FUELQ_OPT_PDL 1          /* 1: launch kernels with programmatic dependent launch so a kernel's weight
                                     prefetch overlaps its predecessor's tail (default 0) */
-#define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the integer mat-vec kernels (default 32); above it the
+#define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the integer mat-vec kernels (default 16); above it the
                                     tensor-core path runs for formats that have one */
 #define FUELQ_OPT_DECODE_GRID 3  /* CTAs for the decode kernel; 0 = two per SM (default) */
 #define FUELQ_OPT_DECODE_KERNEL 4 /* 0 = pick per problem (default); 1 = generic decode kernel (activations read

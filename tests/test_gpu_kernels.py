@@ -182,7 +182,8 @@ def test_decode_batch_shapes_and_row_independence(ops, oracle):
         y1g = ops.qmatmul(T.Q4K, wb, n, x[1, 2:3].contiguous())
     finally:
         _lib.lib.fuelq_set_option(_lib.OPT_DECODE_KERNEL, 0)
-    assert torch.equal(yg, y)
+    assert_matmul_close(yg.cpu().numpy(), y.cpu().numpy())
+    assert torch.equal(y1g, yg[1, 2:3])  # the generic kernel gives a row the same bits in any batch
     assert_matmul_close(y1g.cpu().numpy(), y1.cpu().numpy())
 
 

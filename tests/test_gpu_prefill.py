@@ -98,5 +98,5 @@ def test_crossover_option_routes_to_integer_path(ops, oracle):
         _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 1 << 20), "set_option")
         got = ops.qmatmul(T.Q4K, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda()).cpu().numpy()
     finally:
-        _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 32)
+        _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 16)
     assert np.abs(got - want_int).max() / np.abs(want_int).max() <= 2e-6
