@@ -38,6 +38,12 @@ PROTOTYPES = {
     "fuelq_qmatmul_packed": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "fuelq_quantize_weights": (_i32, [_i32, _i64, _vp, _vp, _vp]),
     "fuelq_dequantize": (_i32, [_i32, _i64, _vp, _vp, _i32, _vp]),
+    "fuelq_embed_rows": (_i32, [_i32, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "fuelq_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _vp]),
+    "fuelq_rope_store": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "fuelq_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
+    "fuelq_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "fuelq_argmax_last": (_i32, [_vp, _i64, _vp, _vp]),
     # include/fuelq_host.h
     "fuelq_last_error": (ctypes.c_char_p, []),
     "fuelq_qtensor_load": (_i32, [_i32, _vp, _i32, _i64, _i64, _vp, _sz, ctypes.POINTER(_vp)]),

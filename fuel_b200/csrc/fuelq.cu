@@ -10,6 +10,7 @@
 #include "decode_regs.cuh"
 #include "dequantize.cuh"
 #include "fq_common.cuh"
+#include "llama_glue.cuh"
 #include "prefill.cuh"
 #include "quantize_act.cuh"
 #include "quantize_weights.cuh"
@@ -665,6 +666,77 @@ int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x,
     default: return kNotSupported;
   }
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// ---- f32 glue of a LLaMA-style decode step (llama_glue.cuh) -----------------------------------------
+int32_t fuelq_embed_rows(int32_t ggml_type, const void* table, int64_t k, const int32_t* ids, int64_t n_ids, float* out,
+                         void* stream) {
+  if (ggml_type != kQ4K) return kNotSupported;
+  if (k <= 0 || k % 256 || n_ids < 0) return kInvalidProblem;
+  if (n_ids == 0) return kOk;
+  if (!table || !ids || !out) return kInvalidProblem;
+  if (!aligned(table, 16) || !aligned(out, 4)) return kMisaligned;
+  const cudaError_t e = launch(embed_q4k_kernel, dim3((unsigned)n_ids), dim3(256), 0, (cudaStream_t)stream,
+                               (const uint8_t*)table, (int)(k / 256 * 144), (int)k, (const int*)ids, out);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_add_rmsnorm(float* x, const float* delta, const float* gain, float* out, int64_t rows, int64_t dim, float eps,
+                          void* stream) {
+  if (rows < 0 || dim <= 0 || dim > (1 << 30)) return kInvalidProblem;
+  if (rows == 0) return kOk;
+  if (!x || !gain || !out) return kInvalidProblem;
+  const cudaError_t e = launch(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream, x, delta, gain,
+                               out, (int)dim, eps);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_rope_store(float* q, const float* k, const float* v, float* kcache, float* vcache, const float* cos_table,
+                         const float* sin_table, const int32_t* pos, int32_t n_heads, int32_t n_kv, int32_t head_dim,
+                         int32_t max_seq, void* stream) {
+  if (n_heads <= 0 || n_kv <= 0 || head_dim <= 0 || head_dim % 2 || max_seq <= 0) return kInvalidProblem;
+  if (!q || !k || !v || !kcache || !vcache || !cos_table || !sin_table || !pos) return kInvalidProblem;
+  const cudaError_t e = launch(rope_store_kernel, dim3((unsigned)(n_heads + n_kv)), dim3(128), 0, (cudaStream_t)stream, q, k, v,
+                               kcache, vcache, cos_table, sin_table, (const int*)pos, (int)n_heads, (int)n_kv, (int)head_dim,
+                               (int)max_seq);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_attn_decode(const float* q, const float* kcache, const float* vcache, float* out, const int32_t* pos,
+                          int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* stream) {
+  if (head_dim != 128) return kNotSupported;
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
+  if (!q || !kcache || !vcache || !out || !pos) return kInvalidProblem;
+  if (!aligned(q, 16) || !aligned(kcache, 16)) return kMisaligned;
+  const size_t smem = ((size_t)max_seq + 8 + 256) * sizeof(float);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return kLaunchFailure;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (8192 + 8 + 256) * 4) != cudaSuccess)
+      return kLaunchFailure;
+    attr_set[dev] = true;
+  }
+  const cudaError_t e = launch(attn_decode_kernel, dim3((unsigned)n_heads), dim3(256), smem, (cudaStream_t)stream, q, kcache,
+                               vcache, out, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_swiglu(const float* gate, const float* up, float* out, int64_t n, void* stream) {
+  if (n < 0) return kInvalidProblem;
+  if (n == 0) return kOk;
+  if (!gate || !up || !out) return kInvalidProblem;
+  const cudaError_t e = launch(swiglu_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, gate, up,
+                               out, (int64_t)n);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_argmax_last(const float* x, int64_t n, int32_t* out_index, void* stream) {
+  if (n <= 0 || n > (1 << 30)) return kInvalidProblem;
+  if (!x || !out_index) return kInvalidProblem;
+  const cudaError_t e = launch(argmax_last_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, x, (int)n, (int*)out_index);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
 int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, void* y, int32_t out_type,

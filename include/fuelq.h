@@ -150,6 +150,33 @@ int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x,
 int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, void* y, int32_t out_type,
                          void* stream);
 
+/* ---- callers of the hot path: f32 glue of a LLaMA-style decode step, batch 1 -------------------------
+ * What the reference's model code runs between its quantized linears (fuel-core/src/lazy.rs:7363-7447).
+ * All device pointers; `pos` points at the current position on the device so a step can be replayed
+ * from a CUDA graph. */
+
+/* token ids -> dequantized rows of a Q4_K embedding table [vocab][k] (the reference keeps embeddings
+ * in f32, fuel-core/src/lazy.rs:8626-8636; BASELINE config 4 quantizes them). */
+int32_t fuelq_embed_rows(int32_t ggml_type, const void* table, int64_t k, const int32_t* ids, int64_t n_ids, float* out,
+                         void* stream);
+/* x += delta (delta may be null), then out = x / sqrt(mean(x^2) + eps) * gain, per row
+ * (rms_norm_last_dim_f32, fuel-cpu-backend/src/byte_kernels.rs:2339-2367 + the affine gain of lazy.rs:10330-10347). */
+int32_t fuelq_add_rmsnorm(float* x, const float* delta, const float* gain, float* out, int64_t rows, int64_t dim, float eps,
+                          void* stream);
+/* rotate-half RoPE of q [n_heads][hd] (in place) and k [n_kv][hd] at position *pos, then store the rotated k
+ * and v into caches [n_kv][max_seq][hd] (rope_f32, byte_kernels.rs:1885-1960; cache layout lazy.rs:8578-8700). */
+int32_t fuelq_rope_store(float* q, const float* k, const float* v, float* kcache, float* vcache, const float* cos_table,
+                         const float* sin_table, const int32_t* pos, int32_t n_heads, int32_t n_kv, int32_t head_dim,
+                         int32_t max_seq, void* stream);
+/* out[h] = softmax(q[h] . K[kv(h)][0..*pos]^T * scale) . V, max-subtracted softmax (byte_kernels.rs:2259-2305). head_dim 128. */
+int32_t fuelq_attn_decode(const float* q, const float* kcache, const float* vcache, float* out, const int32_t* pos,
+                          int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* stream);
+/* out = silu(gate) * up */
+int32_t fuelq_swiglu(const float* gate, const float* up, float* out, int64_t n, void* stream);
+/* index of the LAST maximum of x[0..n) (LogitsProcessor argmax: max_by + total_cmp,
+ * fuel-transformers/src/generation/mod.rs:84-93). */
+int32_t fuelq_argmax_last(const float* x, int64_t n, int32_t* out_index, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
