@@ -41,7 +41,11 @@ PROTOTYPES = {
     "fuelq_embed_rows": (_i32, [_i32, _vp, _i64, _vp, _i64, _vp, _vp]),
     "fuelq_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _vp]),
     "fuelq_rope_store": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
-    "fuelq_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
+    "fuelq_attn_decode_workspace_bytes": (_sz, [_i32]),
+    "fuelq_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _vp]),
+    "fuelq_add_rmsnorm_q8k": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, _vp, _sz, _vp]),
+    "fuelq_swiglu_q8k": (_i32, [_vp, _vp, _i64, _vp, _sz, _vp]),
+    "fuelq_attn_decode_q8k": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _vp, _sz, _vp]),
     "fuelq_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "fuelq_argmax_last": (_i32, [_vp, _i64, _vp, _vp]),
     # include/fuelq_host.h

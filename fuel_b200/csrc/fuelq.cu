@@ -683,11 +683,13 @@ int32_t fuelq_embed_rows(int32_t ggml_type, const void* table, int64_t k, const 
 
 int32_t fuelq_add_rmsnorm(float* x, const float* delta, const float* gain, float* out, int64_t rows, int64_t dim, float eps,
                           void* stream) {
-  if (rows < 0 || dim <= 0 || dim > (1 << 30)) return kInvalidProblem;
+  if (rows < 0 || dim <= 0 || dim % 256 || dim > 8192) return kInvalidProblem;
   if (rows == 0) return kOk;
   if (!x || !gain || !out) return kInvalidProblem;
-  const cudaError_t e = launch(add_rmsnorm_kernel, dim3((unsigned)rows), dim3(256), 0, (cudaStream_t)stream, x, delta, gain,
-                               out, (int)dim, eps);
+  if (!aligned(x, 16) || !aligned(gain, 16) || (delta && !aligned(delta, 16)) || !aligned(out, 16)) return kMisaligned;
+  const cudaError_t e = launch(add_rmsnorm_kernel<false>, dim3((unsigned)rows), dim3((unsigned)(dim / 256 * 32)), 0,
+                               (cudaStream_t)stream, x, delta, gain, out, (int)dim, eps, (int8_t*)nullptr, (float*)nullptr,
+                               (int16_t*)nullptr);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
@@ -702,24 +704,67 @@ int32_t fuelq_rope_store(float* q, const float* k, const float* v, float* kcache
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
+size_t fuelq_attn_decode_workspace_bytes(int32_t n_heads) {
+  return n_heads > 0 ? (size_t)n_heads * kAttnSplits * kAttnPartStride * sizeof(float) : 0;
+}
+
 int32_t fuelq_attn_decode(const float* q, const float* kcache, const float* vcache, float* out, const int32_t* pos,
-                          int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* stream) {
+                          int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
+                          size_t workspace_bytes, void* stream) {
   if (head_dim != 128) return kNotSupported;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
   if (!q || !kcache || !vcache || !out || !pos) return kInvalidProblem;
-  if (!aligned(q, 16) || !aligned(kcache, 16)) return kMisaligned;
-  const size_t smem = ((size_t)max_seq + 8 + 256) * sizeof(float);
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return kLaunchFailure;
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (8192 + 8 + 256) * 4) != cudaSuccess)
-      return kLaunchFailure;
-    attr_set[dev] = true;
-  }
-  const cudaError_t e = launch(attn_decode_kernel, dim3((unsigned)n_heads), dim3(256), smem, (cudaStream_t)stream, q, kcache,
-                               vcache, out, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+  if (!workspace || workspace_bytes < fuelq_attn_decode_workspace_bytes(n_heads)) return kWorkspace;
+  if (!aligned(q, 16) || !aligned(kcache, 16) || !aligned(vcache, 16) || !aligned(workspace, 16)) return kMisaligned;
+  cudaError_t e = launch(attn_partial_kernel, dim3((unsigned)n_heads, kAttnSplits), dim3(256), 0, (cudaStream_t)stream, q,
+                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+  if (e != cudaSuccess) return kLaunchFailure;
+  e = launch(attn_combine_kernel, dim3((unsigned)n_heads), dim3(128), 0, (cudaStream_t)stream, (const float*)workspace, out);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// ---- fused producers for the single-GPU step: the same values as the plain call followed by
+// fuelq_quantize_act_packed (weight type Q4K/Q6K, m = 1), written straight into the packed planes
+int32_t fuelq_add_rmsnorm_q8k(float* x, const float* delta, const float* gain, int64_t dim, float eps, void* packed,
+                              size_t packed_bytes, void* stream) {
+  if (dim <= 0 || dim % 256 || dim > 8192) return kInvalidProblem;
+  if (!x || !gain) return kInvalidProblem;
+  if (!packed || packed_bytes < act_packed_bytes(kQ4K, 1, dim)) return kWorkspace;
+  if (!aligned(x, 16) || !aligned(gain, 16) || (delta && !aligned(delta, 16)) || !aligned(packed, 16)) return kMisaligned;
+  const ActPlanes a = act_planes(packed, kQ4K, 1, dim);
+  const cudaError_t e = launch(add_rmsnorm_kernel<true>, dim3(1), dim3((unsigned)(dim / 256 * 32)), 0, (cudaStream_t)stream, x,
+                               delta, gain, (float*)nullptr, (int)dim, eps, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_swiglu_q8k(const float* gate, const float* up, int64_t n, void* packed, size_t packed_bytes, void* stream) {
+  if (n <= 0 || n % 256) return kInvalidProblem;
+  if (!gate || !up) return kInvalidProblem;
+  if (!packed || packed_bytes < act_packed_bytes(kQ4K, 1, n)) return kWorkspace;
+  if (!aligned(gate, 16) || !aligned(up, 16) || !aligned(packed, 16)) return kMisaligned;
+  const ActPlanes a = act_planes(packed, kQ4K, 1, n);
+  const int64_t nb = n / 256;
+  const cudaError_t e = launch(swiglu_q8k_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, gate, up,
+                               nb, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* vcache, const int32_t* pos, int32_t n_heads,
+                              int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
+                              size_t workspace_bytes, void* packed, size_t packed_bytes, void* stream) {
+  if (head_dim != 128) return kNotSupported;
+  if (n_heads <= 0 || n_heads % 2 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
+  if (!q || !kcache || !vcache || !pos) return kInvalidProblem;
+  if (!workspace || workspace_bytes < fuelq_attn_decode_workspace_bytes(n_heads)) return kWorkspace;
+  if (!packed || packed_bytes < act_packed_bytes(kQ4K, 1, (int64_t)n_heads * 128)) return kWorkspace;
+  if (!aligned(q, 16) || !aligned(kcache, 16) || !aligned(vcache, 16) || !aligned(workspace, 16) || !aligned(packed, 16))
+    return kMisaligned;
+  cudaError_t e = launch(attn_partial_kernel, dim3((unsigned)n_heads, kAttnSplits), dim3(256), 0, (cudaStream_t)stream, q,
+                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+  if (e != cudaSuccess) return kLaunchFailure;
+  const ActPlanes a = act_planes(packed, kQ4K, 1, (int64_t)n_heads * 128);
+  e = launch(attn_combine_q8k_kernel, dim3((unsigned)(n_heads / 2)), dim3(32), 0, (cudaStream_t)stream,
+             (const float*)workspace, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 

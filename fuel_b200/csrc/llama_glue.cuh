@@ -10,6 +10,7 @@
 // reduction orders so a value never depends on how many GPUs share the model.
 #pragma once
 #include "fq_common.cuh"
+#include "quantize_act.cuh"
 
 namespace fq {
 
@@ -23,30 +24,6 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
   float t = 0.f;
   for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];  // fixed order
   return t;
-}
-
-// rows of `dim`: optional residual add (x += delta, written back), then RMSNorm with gain into out
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
-                                                          const float* __restrict__ gain, float* __restrict__ out, int dim,
-                                                          float eps) {
-  __shared__ float red[8];
-  pdl_launch_dependents();
-  pdl_wait();
-  float* xr = x + (size_t)blockIdx.x * dim;
-  const float* dr = delta ? delta + (size_t)blockIdx.x * dim : nullptr;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-    float v = xr[i];
-    if (dr) {
-      v += dr[i];
-      xr[i] = v;
-    }
-    ss += v * v;
-  }
-  const float tot = block_sum_256(ss, red);
-  const float rinv = 1.0f / sqrtf(tot * (1.0f / (float)dim) + eps);
-  float* o = out + (size_t)blockIdx.x * dim;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = xr[i] * rinv * gain[i];
 }
 
 // token ids -> dequantized Q4_K rows of the embedding table (one CTA per id, 16 threads per super-block)
@@ -122,34 +99,47 @@ __global__ void __launch_bounds__(128) rope_store_kernel(float* __restrict__ q, 
   }
 }
 
-// one query per head against positions 0..*pos of the cache (GQA: head h reads kv head h / (n_heads / n_kv))
-// hd must be 128; dynamic shared memory: (max_seq + 8 + 2 * 128) floats
-__global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc,
-                                                          const float* __restrict__ vc, float* __restrict__ out,
-                                                          const int* __restrict__ pos_p, int n_heads, int n_kv,
-                                                          int max_seq, float scale) {
-  extern __shared__ float sm_attn[];
-  float* scores = sm_attn;           // [max_seq]
-  float* red = sm_attn + max_seq;    // [8]
-  float* part = red + 8;             // [2][128]
+// one query per head against positions 0..*pos of the cache (GQA: head h reads kv head h / (n_heads / n_kv)),
+// head_dim 128. The context is cut into kAttnSplits equal chunks, one CTA each (grid = heads x splits):
+// a CTA computes its chunk's scores, their maximum, the exponentials' sum and the unnormalized
+// weighted sum of V rows; attn_combine_kernel merges the chunks in a fixed order. The split count
+// is a constant, so a value never depends on the launch configuration or on how many GPUs there are.
+constexpr int kAttnSplits = 8;
+constexpr int kAttnPartStride = 132;  // 128 outputs + max + sum (+ pad)
+
+__global__ void __launch_bounds__(256) attn_partial_kernel(const float* __restrict__ q, const float* __restrict__ kc,
+                                                           const float* __restrict__ vc, float* __restrict__ part,
+                                                           const int* __restrict__ pos_p, int n_heads, int n_kv,
+                                                           int max_seq, float scale) {
+  __shared__ float scores[1024];
+  __shared__ float red[8];
+  __shared__ float4 vacc[8][32];
   pdl_launch_dependents();
   pdl_wait();
   constexpr int hd = 128;
-  const int head = blockIdx.x, kvh = head / (n_heads / n_kv);
+  const int head = blockIdx.x, split = blockIdx.y, kvh = head / (n_heads / n_kv);
   const int n_ctx = *pos_p + 1;
+  const int chunk = (n_ctx + kAttnSplits - 1) / kAttnSplits;  // <= 1024 for max_seq <= 8192
+  const int t0 = split * chunk, t1 = min(t0 + chunk, n_ctx);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* out = part + ((size_t)head * kAttnSplits + split) * kAttnPartStride;
+  if (t0 >= t1) {  // empty chunk: neutral element
+    if (threadIdx.x < hd) out[threadIdx.x] = 0.f;
+    if (threadIdx.x == 0) out[128] = -INFINITY, out[129] = 0.f;
+    return;
+  }
   const float4 qv = reinterpret_cast<const float4*>(q + (size_t)head * hd)[lane];
   const float* kbase = kc + (size_t)kvh * max_seq * hd;
-  for (int t = warp; t < n_ctx; t += 8) {
+  for (int t = t0 + warp; t < t1; t += 8) {
     const float4 kv = reinterpret_cast<const float4*>(kbase + (size_t)t * hd)[lane];
     float s = qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) scores[t] = s * scale;
+    if (lane == 0) scores[t - t0] = s * scale;
   }
   __syncthreads();
   float mx = -INFINITY;
-  for (int t = threadIdx.x; t < n_ctx; t += blockDim.x) mx = fmaxf(mx, scores[t]);
+  for (int t = threadIdx.x; t < t1 - t0; t += blockDim.x) mx = fmaxf(mx, scores[t]);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   if (lane == 0) red[warp] = mx;
@@ -157,22 +147,146 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
   mx = red[0];
   for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
   float sum = 0.f;
-  for (int t = threadIdx.x; t < n_ctx; t += blockDim.x) {
+  for (int t = threadIdx.x; t < t1 - t0; t += blockDim.x) {
     const float e = expf(scores[t] - mx);
     scores[t] = e;
     sum += e;
   }
-  const float tot = block_sum_256(sum, red);  // also orders the score writes before the reads below
-  const float inv = 1.0f / tot;
-  // out[d] = sum_t p_t * v[t][d]: two halves of the context per column, combined in fixed order
-  const int d = threadIdx.x & 127, hsel = threadIdx.x >> 7;
-  const int t_mid = (n_ctx + 1) >> 1;
+  const float tot = block_sum_256(sum, red);  // its barriers also order the score updates
   const float* vbase = vc + (size_t)kvh * max_seq * hd;
-  float acc = 0.f;
-  for (int t = hsel ? t_mid : 0; t < (hsel ? n_ctx : t_mid); ++t) acc += scores[t] * vbase[(size_t)t * hd + d];
-  part[hsel * 128 + d] = acc;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int t = t0 + warp; t < t1; t += 8) {  // a warp per V row, a lane per four columns
+    const float pw = scores[t - t0];
+    const float4 vv = reinterpret_cast<const float4*>(vbase + (size_t)t * hd)[lane];
+    a.x += pw * vv.x, a.y += pw * vv.y, a.z += pw * vv.z, a.w += pw * vv.w;
+  }
+  vacc[warp][lane] = a;
   __syncthreads();
-  if (hsel == 0) out[(size_t)head * hd + d] = (part[d] + part[128 + d]) * inv;
+  if (threadIdx.x < 32) {
+    float4 r = vacc[0][lane];
+    for (int w = 1; w < 8; ++w) {  // fixed order
+      const float4 o = vacc[w][lane];
+      r.x += o.x, r.y += o.y, r.z += o.z, r.w += o.w;
+    }
+    reinterpret_cast<float4*>(out)[lane] = r;
+    if (lane == 0) out[128] = mx, out[129] = tot;
+  }
+}
+
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int head = blockIdx.x, d = threadIdx.x;
+  const float* p = part + (size_t)head * kAttnSplits * kAttnPartStride;
+  float M = -INFINITY;
+  for (int s = 0; s < kAttnSplits; ++s) M = fmaxf(M, p[s * kAttnPartStride + 128]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < kAttnSplits; ++s) {
+    const float w = expf(p[s * kAttnPartStride + 128] - M);  // exp(-inf) = 0 for empty chunks
+    num += w * p[s * kAttnPartStride + d];
+    den += w * p[s * kAttnPartStride + 129];
+  }
+  out[(size_t)head * 128 + d] = num / den;
+}
+
+// ---- fused producers: the same results as the plain kernels above followed by the activation
+// quantizer, without the f32 round trip and the extra launch (single-GPU step only: with tensor
+// parallelism the full vector exists only after an all-gather).
+
+// Rows of `dim` (a multiple of 256, at most 8192; one CTA per row, one warp per 256 elements): optional
+// residual add (x += delta, written back), then RMSNorm with gain. kQuant = false stores the f32 row to
+// `out`; kQuant = true (one row) quantizes it into the activation planes. Both forms share every
+// arithmetic step and its order, so they produce the same values.
+template <bool kQuant>
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                           const float* __restrict__ gain, float* __restrict__ out, int dim,
+                                                           float eps, int8_t* __restrict__ out_qs, float* __restrict__ out_d,
+                                                           int16_t* __restrict__ out_bsums) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t base = (size_t)blockIdx.x * dim + warp * 256;
+  float e[8];
+  float ss = 0.f;
+  {
+    float4* xr = reinterpret_cast<float4*>(x + base);
+    float4 v0 = xr[lane], v1 = xr[32 + lane];
+    if (delta) {
+      const float4* dr = reinterpret_cast<const float4*>(delta + base);
+      const float4 d0 = dr[lane], d1 = dr[32 + lane];
+      v0.x += d0.x, v0.y += d0.y, v0.z += d0.z, v0.w += d0.w;
+      v1.x += d1.x, v1.y += d1.y, v1.z += d1.z, v1.w += d1.w;
+      xr[lane] = v0, xr[32 + lane] = v1;
+    }
+    e[0] = v0.x, e[1] = v0.y, e[2] = v0.z, e[3] = v0.w, e[4] = v1.x, e[5] = v1.y, e[6] = v1.z, e[7] = v1.w;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += e[i] * e[i];
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];  // fixed order
+  const float rinv = 1.0f / sqrtf(tot * (1.0f / (float)dim) + eps);
+  const float4 g0 = reinterpret_cast<const float4*>(gain + warp * 256)[lane];
+  const float4 g1 = reinterpret_cast<const float4*>(gain + warp * 256)[32 + lane];
+  const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) e[i] = e[i] * rinv * gg[i];
+  if constexpr (kQuant) {
+    q8k_block_from_regs(e, lane, warp, out_qs, out_d, out_bsums);
+  } else {
+    float4* o = reinterpret_cast<float4*>(out + base);
+    o[lane] = make_float4(e[0], e[1], e[2], e[3]);
+    o[32 + lane] = make_float4(e[4], e[5], e[6], e[7]);
+  }
+}
+
+// silu(gate) * up, quantized; one warp per 256 elements
+__global__ void __launch_bounds__(256) swiglu_q8k_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                                         int64_t n_blocks, int8_t* __restrict__ out_qs,
+                                                         float* __restrict__ out_d, int16_t* __restrict__ out_bsums) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (blk >= n_blocks) return;
+  const float4* gp = reinterpret_cast<const float4*>(gate + blk * 256);
+  const float4* up4 = reinterpret_cast<const float4*>(up + blk * 256);
+  const float4 a0 = gp[lane], a1 = gp[32 + lane], b0 = up4[lane], b1 = up4[32 + lane];
+  const float g[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+  const float u[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  float e[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) e[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
+  q8k_block_from_regs(e, lane, blk, out_qs, out_d, out_bsums);
+}
+
+// merge of the attention chunks for two heads (256 outputs) per warp, quantized
+__global__ void __launch_bounds__(32) attn_combine_q8k_kernel(const float* __restrict__ part, int8_t* __restrict__ out_qs,
+                                                              float* __restrict__ out_d, int16_t* __restrict__ out_bsums) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x, blk = blockIdx.x;
+  float e[8];
+#pragma unroll
+  for (int hsel = 0; hsel < 2; ++hsel) {  // elements 4*lane.. belong to head 2*blk, 128 + 4*lane.. to head 2*blk + 1
+    const float* p = part + (size_t)(2 * blk + hsel) * kAttnSplits * kAttnPartStride;
+    float M = -INFINITY;
+    for (int s = 0; s < kAttnSplits; ++s) M = fmaxf(M, p[s * kAttnPartStride + 128]);
+    float num[4] = {0, 0, 0, 0}, den = 0.f;
+    for (int s = 0; s < kAttnSplits; ++s) {
+      const float w = expf(p[s * kAttnPartStride + 128] - M);
+      const float4 v = reinterpret_cast<const float4*>(p + s * kAttnPartStride)[lane];
+      num[0] += w * v.x, num[1] += w * v.y, num[2] += w * v.z, num[3] += w * v.w;
+      den += w * p[s * kAttnPartStride + 129];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[4 * hsel + i] = num[i] / den;
+  }
+  q8k_block_from_regs(e, lane, blk, out_qs, out_d, out_bsums);
 }
 
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,

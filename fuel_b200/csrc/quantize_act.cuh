@@ -19,6 +19,68 @@
 
 namespace fq {
 
+// One warp quantizes one 256-element block held as e[0..3] = elements 4*lane.., e[4..7] = elements
+// 128 + 4*lane..; writes the plane-split layout. Shared by the stand-alone kernel and by the fused
+// producers (norm / SwiGLU / attention merge) so all of them emit identical bytes.
+__device__ __forceinline__ void q8k_block_from_regs(const float (&e)[8], int lane, int64_t blk, int8_t* __restrict__ out_qs,
+                                                    float* __restrict__ out_d, int16_t* __restrict__ out_bsums) {
+  float amax = 0.f, smax = 0.f;
+  int idx = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float a = fabsf(e[i]);
+    if (amax < a) {
+      amax = a;
+      smax = e[i];
+      idx = (i < 4 ? 4 * lane + i : 128 + 4 * lane + (i - 4));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float oa = __shfl_xor_sync(0xffffffffu, amax, off);
+    const float os = __shfl_xor_sync(0xffffffffu, smax, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+    if (oa > amax || (oa == amax && oi < idx)) {
+      amax = oa;
+      smax = os;
+      idx = oi;
+    }
+  }
+  int q[8];
+  float d;
+  if (amax == 0.f) {
+    d = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = 0;
+  } else {
+    const float iscale = -128.0f / smax;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float r = fminf(roundf(iscale * e[i]), 127.0f);
+      q[i] = max(__float2int_rz(r), -128);
+    }
+    d = 1.0f / iscale;
+  }
+  int s0 = q[0] + q[1] + q[2] + q[3];
+  int s1 = q[4] + q[5] + q[6] + q[7];
+  s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+  s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+  s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+  s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+  const uint32_t p0 = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) |
+                      ((uint32_t)(q[3] & 0xff) << 24);
+  const uint32_t p1 = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) |
+                      ((uint32_t)(q[7] & 0xff) << 24);
+  uint32_t* qs = reinterpret_cast<uint32_t*>(out_qs + blk * QK_K);
+  qs[lane] = p0;
+  qs[32 + lane] = p1;
+  if (lane == 0) out_d[blk] = d;
+  if ((lane & 3) == 0) {
+    out_bsums[blk * 16 + (lane >> 2)] = (int16_t)s0;
+    out_bsums[blk * 16 + 8 + (lane >> 2)] = (int16_t)s1;
+  }
+}
+
 template <bool kRefLayout>
 __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* __restrict__ x, int64_t n_blocks,
                                                            uint8_t* __restrict__ out_ref, int8_t* __restrict__ out_qs,

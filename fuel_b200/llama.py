@@ -161,7 +161,9 @@ class QLlama:
             self.attn, self.o, self.s, self.d, self.logits = self.attn_l, self.o_l, self.s_l, self.d_l, self.logits_l
         nb = max(_L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.dim), _L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.ffn_dim))
         self.packed = torch.zeros(nb, dtype=torch.uint8, device=device)
+        self.attn_ws = torch.zeros(max(_L.fuelq_attn_decode_workspace_bytes(self.hl), 16), dtype=torch.uint8, device=device)
         self.graph = None
+        self.fused = True  # single-GPU step uses the fused producers
         self.weight_bytes = (sum(l[k].blocks.numel() for l in self.layers for k in ("qk", "v", "o", "gu", "down"))
                              + self.head.blocks.numel())
 
@@ -175,6 +177,46 @@ class QLlama:
                                             stream), "fuelq_quantize_act_packed")
 
     def step(self) -> None:
+        if self.world == 1 and self.fused:
+            return self._step_fused()
+        return self._step_plain()
+
+    def _step_fused(self) -> None:
+        """Single-GPU step: norm / attention merge / SwiGLU write the quantized activations directly."""
+        c = self.cfg
+        st = torch.cuda.current_stream().cuda_stream
+        scale = 1.0 / math.sqrt(c.head_dim)
+        pk, pkn = self.packed.data_ptr(), self.packed.numel()
+        _check(_L.fuelq_embed_rows(int(T.Q4K), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
+               "fuelq_embed_rows")
+        delta = None
+        qd = self.hl * c.head_dim
+        for l in self.layers:
+            _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), delta, l["attn_norm"].data_ptr(), c.dim, c.norm_eps, pk, pkn, st),
+                   "add_rmsnorm_q8k")
+            l["qk"].matvec_packed(self.packed, self.qk, st)
+            l["v"].matvec_packed(self.packed, self.v, st)
+            _check(_L.fuelq_rope_store(self.qk.data_ptr(), self.qk.data_ptr() + 4 * qd, self.v.data_ptr(), l["kc"].data_ptr(),
+                                       l["vc"].data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
+                                       self.hl, self.kvl, c.head_dim, c.max_seq, st), "rope_store")
+            _check(_L.fuelq_attn_decode_q8k(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.pos.data_ptr(),
+                                            self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
+                                            self.attn_ws.numel(), pk, pkn, st), "attn_decode_q8k")
+            l["o"].matvec_packed(self.packed, self.o_l, st)
+            _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), self.o_l.data_ptr(), l["ffn_norm"].data_ptr(), c.dim, c.norm_eps,
+                                            pk, pkn, st), "add_rmsnorm_q8k")
+            l["gu"].matvec_packed(self.packed, self.gu, st)
+            _check(_L.fuelq_swiglu_q8k(self.gu.data_ptr(), self.gu.data_ptr() + 4 * c.ffn_dim, c.ffn_dim, pk, pkn, st), "swiglu_q8k")
+            l["down"].matvec_packed(self.packed, self.d_l, st)
+            delta = self.d_l.data_ptr()
+        _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), delta, self.out_norm.data_ptr(), c.dim, c.norm_eps, pk, pkn, st),
+               "add_rmsnorm_q8k")
+        self.head.matvec_packed(self.packed, self.logits_l, st)
+        _check(_L.fuelq_argmax_last(self.logits.data_ptr(), c.vocab, self.next_token.data_ptr(), st), "argmax_last")
+        self.pos.add_(1)
+        self.token.copy_(self.next_token)
+
+    def _step_plain(self) -> None:
         c = self.cfg
         st = torch.cuda.current_stream().cuda_stream
         scale = 1.0 / math.sqrt(c.head_dim)
@@ -192,7 +234,8 @@ class QLlama:
                                        l["vc"].data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
                                        self.hl, self.kvl, c.head_dim, c.max_seq, st), "rope_store")
             _check(_L.fuelq_attn_decode(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.attn_l.data_ptr(),
-                                        self.pos.data_ptr(), self.hl, self.kvl, c.head_dim, c.max_seq, scale, st), "attn_decode")
+                                        self.pos.data_ptr(), self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
+                                        self.attn_ws.numel(), st), "attn_decode")
             self._gather(self.attn, self.attn_l)
             self._quant(self.attn, c.dim, st)
             l["o"].matvec_packed(self.packed, self.o_l, st)

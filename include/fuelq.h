@@ -160,7 +160,8 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
 int32_t fuelq_embed_rows(int32_t ggml_type, const void* table, int64_t k, const int32_t* ids, int64_t n_ids, float* out,
                          void* stream);
 /* x += delta (delta may be null), then out = x / sqrt(mean(x^2) + eps) * gain, per row
- * (rms_norm_last_dim_f32, fuel-cpu-backend/src/byte_kernels.rs:2339-2367 + the affine gain of lazy.rs:10330-10347). */
+ * (rms_norm_last_dim_f32, fuel-cpu-backend/src/byte_kernels.rs:2339-2367 + the affine gain of lazy.rs:10330-10347).
+ * dim a multiple of 256, at most 8192; pointers 16-byte aligned. */
 int32_t fuelq_add_rmsnorm(float* x, const float* delta, const float* gain, float* out, int64_t rows, int64_t dim, float eps,
                           void* stream);
 /* rotate-half RoPE of q [n_heads][hd] (in place) and k [n_kv][hd] at position *pos, then store the rotated k
@@ -169,8 +170,19 @@ int32_t fuelq_rope_store(float* q, const float* k, const float* v, float* kcache
                          const float* sin_table, const int32_t* pos, int32_t n_heads, int32_t n_kv, int32_t head_dim,
                          int32_t max_seq, void* stream);
 /* out[h] = softmax(q[h] . K[kv(h)][0..*pos]^T * scale) . V, max-subtracted softmax (byte_kernels.rs:2259-2305). head_dim 128. */
+size_t fuelq_attn_decode_workspace_bytes(int32_t n_heads);
 int32_t fuelq_attn_decode(const float* q, const float* kcache, const float* vcache, float* out, const int32_t* pos,
-                          int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* stream);
+                          int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
+                          size_t workspace_bytes, void* stream);
+/* Fused forms for a single-GPU step: the plain call followed by fuelq_quantize_act_packed (k-quant weights,
+ * m = 1), written straight into the packed planes with the same bytes, one launch instead of two.
+ * dim / n multiples of 256. */
+int32_t fuelq_add_rmsnorm_q8k(float* x, const float* delta, const float* gain, int64_t dim, float eps, void* packed,
+                              size_t packed_bytes, void* stream);
+int32_t fuelq_swiglu_q8k(const float* gate, const float* up, int64_t n, void* packed, size_t packed_bytes, void* stream);
+int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* vcache, const int32_t* pos, int32_t n_heads,
+                              int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
+                              size_t workspace_bytes, void* packed, size_t packed_bytes, void* stream);
 /* out = silu(gate) * up */
 int32_t fuelq_swiglu(const float* gate, const float* up, float* out, int64_t n, void* stream);
 /* index of the LAST maximum of x[0..n) (LogitsProcessor argmax: max_by + total_cmp,

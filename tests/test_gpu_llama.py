@@ -67,3 +67,20 @@ def test_greedy_tokens_match_cpu_reference_path(oracle):
     finally:
         _lib.lib.fuelq_set_option(_lib.OPT_PDL, 0)
     assert ops.device_error() == 0
+
+
+def test_fused_step_is_bit_identical_to_plain_step():
+    """The single-GPU step fuses norm / attention merge / SwiGLU with the activation quantizer; tensor-parallel
+    steps cannot. Both must give the same bits, or greedy tokens could depend on the GPU count."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuel_b200.llama import QLlama
+    model = QLlama(_tiny(), torch.device("cuda", 0))
+    prompt = np.random.Generator(np.random.PCG64(4)).integers(0, 512, 20).tolist()
+    outs = []
+    for fused in (True, False):
+        model.fused = fused
+        toks = model.generate(prompt, 16)
+        outs.append((toks, model.logits.clone(), model.x.clone()))
+    assert outs[0][0] == outs[1][0]
+    assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][2], outs[1][2])
