@@ -16,6 +16,16 @@ OPT_PDL, OPT_DECODE_MAX_M, OPT_DECODE_GRID, OPT_DECODE_KERNEL, OPT_L2_PREFETCH =
 
 _i32, _i64, _vp, _sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
 
+PEER_MAX_WORLD, PEER_MAX_SEQ = 8, 1024
+
+
+class Peers(ctypes.Structure):
+    """struct fuelq_peers of include/fuelq.h."""
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("epoch", ctypes.c_void_p)]
+
+
+_pp = ctypes.POINTER(Peers)
+
 # name -> (restype, argtypes); must list every symbol include/fuelq.h declares
 PROTOTYPES = {
     "fuelq_status_string": (ctypes.c_char_p, [_i32]),
@@ -46,6 +56,18 @@ PROTOTYPES = {
     "fuelq_add_rmsnorm_q8k": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, _vp, _sz, _vp]),
     "fuelq_swiglu_q8k": (_i32, [_vp, _vp, _i64, _vp, _sz, _vp]),
     "fuelq_attn_decode_q8k": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _vp, _sz, _vp]),
+    "fuelq_peer_act_bytes": (_sz, [_i64]),
+    "fuelq_peer_vec_bytes": (_sz, [_i64]),
+    "fuelq_ipc_alloc": (_i32, [_sz, ctypes.POINTER(_vp), _vp]),
+    "fuelq_ipc_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
+    "fuelq_ipc_close": (_i32, [_vp]),
+    "fuelq_ipc_free": (_i32, [_vp]),
+    "fuelq_qmatmul_packed_peer": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp, _i64, _pp, _i32, _i32, _vp]),
+    "fuelq_add_rmsnorm_q8k_peer": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, _vp, _sz, _pp, _i32, _vp]),
+    "fuelq_swiglu_q8k_peer": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _pp, _i32, _vp]),
+    "fuelq_attn_decode_q8k_peer": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _i32, _i64,
+                                          _vp, _pp, _i32, _vp]),
+    "fuelq_argmax_last_peer": (_i32, [_vp, _i64, _vp, _pp, _i32, _vp, _vp]),
     "fuelq_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "fuelq_argmax_last": (_i32, [_vp, _i64, _vp, _vp]),
     # include/fuelq_host.h

@@ -18,6 +18,7 @@
 #pragma once
 #include "decode.cuh"
 #include "fq_common.cuh"
+#include "peer.cuh"
 
 namespace fq {
 
@@ -41,6 +42,17 @@ struct DecodeRegsParams {
   int u_begin[9];                 // unit range of k-slice s: [u_begin[s], u_begin[s+1])
   int debug_flags;                // bit 0: consumers skip the arithmetic (streaming-rate experiments)
   unsigned long long* trace;      // optional: 24 global-timer stamps per CTA
+};
+
+// Extra arguments of the tensor-parallel form (kPeer): the output rows go, as stamped pairs of exchange
+// point ctx.push_seq, to dst[q] on every rank q (already offset to this rank's slice); with
+// ctx.wait_seq >= 0 the activations are the stamped planes `act_ll` that exchange point filled, which
+// the CTA first copies (polling) into plain planes at byte act_smem_off of its shared memory.
+struct DecodeRegsPeer {
+  PeerCtx ctx;
+  uint2* dst[kPeerMaxWorld];
+  StampedPlanes act_ll;
+  int act_smem_off;
 };
 
 __device__ __forceinline__ unsigned long long gtimer() {
@@ -94,14 +106,18 @@ struct Q4KRegs {
       const int4 v = q8[i];
       ac.q[4 * i] = v.x, ac.q[4 * i + 1] = v.y, ac.q[4 * i + 2] = v.z, ac.q[4 * i + 3] = v.w;
     }
-    // eight 16-element sums -> four 32-element sums (each |s| <= 4096, fits int16)
     const int4 bs = *reinterpret_cast<const int4*>(a.bsums + (size_t)m * (k >> 4) + blk * 16 + 8 * h);
-    const int s0 = (int)(short)(bs.x & 0xffff) + (bs.x >> 16), s1 = (int)(short)(bs.y & 0xffff) + (bs.y >> 16);
-    const int s2 = (int)(short)(bs.z & 0xffff) + (bs.z >> 16), s3 = (int)(short)(bs.w & 0xffff) + (bs.w >> 16);
-    ac.bs01 = (s0 & 0xffff) | (s1 << 16);
-    ac.bs23 = (s2 & 0xffff) | (s3 << 16);
+    set_sums(bs.x, bs.y, bs.z, bs.w, ac);
     ac.yd = a.d[(size_t)m * (k >> 8) + blk];
   }
+  // eight 16-element sums -> four 32-element sums (each |s| <= 4096, fits int16)
+  __device__ __forceinline__ static void set_sums(int x, int y, int z, int w, Act& ac) {
+    const int s0 = (int)(short)(x & 0xffff) + (x >> 16), s1 = (int)(short)(y & 0xffff) + (y >> 16);
+    const int s2 = (int)(short)(z & 0xffff) + (z >> 16), s3 = (int)(short)(w & 0xffff) + (w >> 16);
+    ac.bs01 = (s0 & 0xffff) | (s1 << 16);
+    ac.bs23 = (s2 & 0xffff) | (s3 << 16);
+  }
+  static constexpr bool kHasRaw = true;  // Q8_K activations: a stamped form exists
   __device__ __forceinline__ static int probe(const Act& ac) { return ac.q[0] ^ ac.q[31] ^ ac.bs23 ^ __float_as_int(ac.yd); }
   template <int M>
   __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
@@ -199,6 +215,7 @@ struct Q6KRegs {
     ac.bs[0] = bs.x, ac.bs[1] = bs.y, ac.bs[2] = bs.z, ac.bs[3] = bs.w;
     ac.yd = a.d[(size_t)m * (k >> 8) + blk];
   }
+  static constexpr bool kHasRaw = true;
   __device__ __forceinline__ static int probe(const Act& ac) { return ac.q[0] ^ ac.q[31] ^ ac.bs[3] ^ __float_as_int(ac.yd); }
   template <int M>
   __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
@@ -272,6 +289,7 @@ struct Q8_0Regs {
     const float4 dv = *reinterpret_cast<const float4*>(a.d + (size_t)m * (k >> 5) + u * 4);
     ac.yd[0] = dv.x, ac.yd[1] = dv.y, ac.yd[2] = dv.z, ac.yd[3] = dv.w;
   }
+  static constexpr bool kHasRaw = false;  // its activations are Q8_0 blocks; no stamped form
   __device__ __forceinline__ static int probe(const Act& ac) { return ac.q[0] ^ ac.q[31] ^ __float_as_int(ac.yd[3]); }
   template <int M>
   __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
@@ -305,8 +323,9 @@ struct DecodeRegsSmemHeader {
   float partial[2][32][8][2];  // [buffer][row in stage][k-slice][m]
 };
 
-template <class Fmt, int M, int NU>
-__global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const DecodeRegsParams p) {
+template <class Fmt, int M, int NU, bool kPeer>
+__device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, const DecodeRegsPeer* g) {
+  static_assert(!kPeer || M == 1, "the tensor-parallel form is a single-row mat-vec");
   extern __shared__ __align__(128) uint8_t smem_raw[];
   DecodeRegsSmemHeader* hd = reinterpret_cast<DecodeRegsSmemHeader*>(smem_raw);
   uint8_t* stages = smem_raw + align_up(sizeof(DecodeRegsSmemHeader), 128);
@@ -401,14 +420,30 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
 
   typename Fmt::Unit un[NU];
   typename Fmt::Act ac[NU][M];
+  uint32_t push_stamp = 0;
   pdl_wait();  // activation planes are written by the preceding kernel
+  ActPlanes planes = p.act;
+  if constexpr (kPeer) {
+    push_stamp = peer_stamp(g->ctx, g->ctx.push_seq);
+    if (Fmt::kHasRaw && g->ctx.wait_seq >= 0) {
+      // ... or arrive from the peers' kernels as stamped planes: the consumer warps copy them once per CTA
+      // into shared memory (each thread polling its own pairs), then load from there
+      planes = act_planes(smem_raw + g->act_smem_off, kQ4K, 1, p.k);
+      const uint32_t want = peer_stamp(g->ctx, g->ctx.wait_seq);
+      const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
+      peer_copy_words(g->act_ll.qs, (uint32_t*)planes.qs, p.k >> 2, want, t, nt);
+      peer_copy_words(g->act_ll.bs, (uint32_t*)planes.bsums, p.k >> 5, want, t, nt);
+      peer_copy_words1(g->act_ll.d, (uint32_t*)planes.d, p.k >> 8, want, t, nt);
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
+    }
+  }
 #pragma unroll
   for (int j = 0; j < NU; ++j) {
     const int u = u_begin + lane + 32 * j;
     const bool valid = u < u_end;
     Fmt::make_unit(u, valid, un[j]);
 #pragma unroll
-    for (int i = 0; i < M; ++i) Fmt::load_act(u, valid, p.act, p.k, i, ac[j][i]);
+    for (int i = 0; i < M; ++i) Fmt::load_act(u, valid, planes, p.k, i, ac[j][i]);
   }
 
   {
@@ -453,9 +488,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
       if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < M; ++i) {
-          if (ks == 1)
-            p.y[(size_t)i * p.n + row0 + r] = acc[i];
-          else
+          if (ks == 1) {
+            if constexpr (kPeer) {
+              for (int q = 0; q < g->ctx.world; ++q) st_pair(g->dst[q] + row0 + r, __float_as_uint(acc[i]), push_stamp);
+            } else {
+              p.y[(size_t)i * p.n + row0 + r] = acc[i];
+            }
+          } else
             hd->partial[buf][r][slice][i] = acc[i];
         }
       }
@@ -475,11 +514,27 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const De
         const int r = t / M, i = t - r * M;
         float sum = hd->partial[buf][r][0][i];
         for (int sg = 1; sg < ks; ++sg) sum += hd->partial[buf][r][sg][i];
-        p.y[(size_t)i * p.n + row0 + r] = sum;
+        if constexpr (kPeer) {
+          for (int q = 0; q < g->ctx.world; ++q) st_pair(g->dst[q] + row0 + r, __float_as_uint(sum), push_stamp);
+        } else {
+          p.y[(size_t)i * p.n + row0 + r] = sum;
+        }
       }
     }
     if (++s == S) s = 0, ph ^= 1u;
   }
+}
+
+template <class Fmt, int M, int NU>
+__global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const DecodeRegsParams p) {
+  decode_regs_body<Fmt, M, NU, false>(p, nullptr);
+}
+
+// Tensor-parallel form: same arithmetic and order, output scattered to every rank.
+template <class Fmt, int NU>
+__global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_peer_kernel(const DecodeRegsParams p,
+                                                                             const DecodeRegsPeer g) {
+  decode_regs_body<Fmt, 1, NU, true>(p, &g);
 }
 
 }  // namespace fq

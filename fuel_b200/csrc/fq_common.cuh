@@ -87,7 +87,7 @@ __host__ __device__ inline ActPlanes act_planes(void* base, int weight_type, int
 
 // ---- device-side error word. A kernel whose bounded wait expires records where it
 // gave up here and returns; the host reads it with fuelq_device_error().
-enum DevErr : int { kErrNone = 0, kErrFullWait = 1, kErrEmptyWait = 2, kErrDrainWait = 3, kErrMmaWait = 4, kErrTmemWait = 5 };
+enum DevErr : int { kErrNone = 0, kErrFullWait = 1, kErrEmptyWait = 2, kErrDrainWait = 3, kErrMmaWait = 4, kErrTmemWait = 5, kErrPeerWait = 6 };
 
 #ifdef __CUDACC__
 

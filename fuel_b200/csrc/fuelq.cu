@@ -195,7 +195,8 @@ struct RegsPlan {
   size_t smem;
 };
 
-int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl) {
+// `reserve`: bytes of shared memory kept free after the stage ring (the tensor-parallel form stages its activations there)
+int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl, size_t reserve = 0) {
   int ks = 1;
   while (ks < 8 && (units_per_row + ks - 1) / ks > 32) ks *= 2;  // one unit per lane if eight slices allow it
   if ((units_per_row + ks - 1) / ks > 64) return kNotSupported;
@@ -205,7 +206,8 @@ int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const Devi
   const int n_rgroups = kDecodeConsumerWarps / ks;
   const size_t header = align_up(sizeof(DecodeRegsSmemHeader), 128);
   const size_t per_cta_budget = ((size_t)di.max_smem_optin + 1024) / 2 - 1024 - 512;
-  const size_t ring_budget = (g_opt.dbg_smem_kb ? (size_t)g_opt.dbg_smem_kb * 1024 : per_cta_budget) - header;
+  if (reserve + header + 4096 > per_cta_budget) return kNotSupported;
+  const size_t ring_budget = (g_opt.dbg_smem_kb ? (size_t)g_opt.dbg_smem_kb * 1024 : per_cta_budget) - header - reserve;
   const int stage_target = g_opt.dbg_stage_kb ? (int)g_opt.dbg_stage_kb * 1024 : 40 * 1024;  // two rows per consumer warp per stage at k = 4096
   int fit = (stage_target - 32) / row_bytes;
   if (fit > 32) fit = 32;
@@ -221,7 +223,7 @@ int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const Devi
   pl->num_stages = stages;
   pl->stage_stride = stride;
   pl->grid = grid;
-  pl->smem = header + (size_t)stages * stride;
+  pl->smem = header + (size_t)stages * stride + reserve;
   return kOk;
 }
 
@@ -242,9 +244,28 @@ cudaError_t launch_decode_regs(const DecodeRegsParams& p, const RegsPlan& pl, cu
   return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p);
 }
 
+template <class Fmt, int NU>
+cudaError_t launch_decode_regs_peer(const DecodeRegsParams& p, const DecodeRegsPeer& g, const RegsPlan& pl,
+                                    cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  auto kern = decode_regs_peer_kernel<Fmt, NU>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    DeviceInfo* di;
+    if (!device_info(&di)) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p, g);
+}
+
 // returns kNotSupported when this variant does not cover the problem (the caller falls back)
 int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const ActPlanes& planes, float* y,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const DecodeRegsPeer* peer = nullptr) {
+  if (peer && m != 1) return kNotSupported;
   if (m > 2 || (type != kQ4K && type != kQ6K && type != kQ8_0)) return kNotSupported;
   if (type == kQ8_0 && k % 128) return kNotSupported;  // its lane unit is four blocks
   DeviceInfo* di;
@@ -253,8 +274,15 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.units_per_row = (int)(k / 128);  // every format's lane unit covers 128 elements
   p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
   RegsPlan pl;
-  const int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl);
+  const size_t reserve = (peer && peer->ctx.wait_seq >= 0) ? align_up(act_packed_bytes(kQ4K, 1, k), 128) : 0;
+  const int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, reserve);
   if (st != kOk) return st;
+  DecodeRegsPeer peer_args;
+  if (peer) {
+    peer_args = *peer;
+    peer_args.act_smem_off = (int)(pl.smem - reserve);
+    peer = &peer_args;
+  }
   p.w = (const uint8_t*)w;
   p.act = planes;
   p.y = y;
@@ -275,6 +303,17 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.debug_flags = (int)g_opt.debug_flags;
   p.trace = (unsigned long long*)(uintptr_t)g_opt.trace_ptr;
   cudaError_t e;
+  if (peer) {
+#define FQ_REGS_PEER(FMT) \
+  e = pl.nu == 1 ? launch_decode_regs_peer<FMT, 1>(p, *peer, pl, stream) : launch_decode_regs_peer<FMT, 2>(p, *peer, pl, stream)
+    switch (type) {
+      case kQ4K: FQ_REGS_PEER(Q4KRegs); break;
+      case kQ6K: FQ_REGS_PEER(Q6KRegs); break;
+      default: FQ_REGS_PEER(Q8_0Regs); break;
+    }
+#undef FQ_REGS_PEER
+    return e == cudaSuccess ? kOk : kLaunchFailure;
+  }
 #define FQ_REGS_DISPATCH(FMT)                                                                                          \
   do {                                                                                                                 \
     if (m == 1)                                                                                                        \
@@ -781,6 +820,175 @@ int32_t fuelq_argmax_last(const float* x, int64_t n, int32_t* out_index, void* s
   if (n <= 0 || n > (1 << 30)) return kInvalidProblem;
   if (!x || !out_index) return kInvalidProblem;
   const cudaError_t e = launch(argmax_last_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, x, (int)n, (int*)out_index);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// ---- tensor-parallel decode over peer-mapped memory (peer.cuh)
+namespace {
+int32_t make_peer_ctx(const fuelq_peers* peers, int32_t wait_seq, int32_t push_seq, PeerCtx* c) {
+  if (!peers || peers->world < 1 || peers->world > kPeerMaxWorld || peers->rank < 0 || peers->rank >= peers->world)
+    return kInvalidProblem;
+  if (wait_seq >= kPeerMaxSeq || push_seq >= kPeerMaxSeq) return kInvalidProblem;
+  if (!peers->epoch) return kInvalidProblem;
+  c->world = peers->world;
+  c->rank = peers->rank;
+  c->wait_seq = wait_seq < 0 ? -1 : wait_seq;
+  c->push_seq = push_seq < 0 ? -1 : push_seq;
+  c->epoch = peers->epoch;
+  return kOk;
+}
+int32_t make_peer_planes(void* const* act_dst, int64_t k_total, int world, PeerStampedPlanes* out) {
+  if (!act_dst) return kInvalidProblem;
+  for (int q = 0; q < kPeerMaxWorld; ++q) {
+    out->r[q] = StampedPlanes{nullptr, nullptr, nullptr};
+    if (q >= world) continue;
+    if (!act_dst[q]) return kInvalidProblem;
+    if (!aligned(act_dst[q], 16)) return kMisaligned;
+    out->r[q] = stamped_planes(act_dst[q], k_total);
+  }
+  return kOk;
+}
+}  // namespace
+
+size_t fuelq_peer_act_bytes(int64_t k) { return (k > 0 && k % 256 == 0) ? stamped_planes_bytes(k) : 0; }
+size_t fuelq_peer_vec_bytes(int64_t n) { return n > 0 ? (size_t)n * 8 : 0; }
+
+int32_t fuelq_ipc_alloc(size_t bytes, void** dev_ptr, void* handle64) {
+  if (!dev_ptr || !handle64 || bytes == 0) return kInvalidProblem;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return kLaunchFailure;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+      cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle64, p) != cudaSuccess) {
+    cudaFree(p);
+    cudaGetLastError();
+    return kLaunchFailure;
+  }
+  *dev_ptr = p;
+  return kOk;
+}
+int32_t fuelq_ipc_open(const void* handle64, void** dev_ptr) {
+  if (!handle64 || !dev_ptr) return kInvalidProblem;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  if (cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return kLaunchFailure;
+  }
+  return kOk;
+}
+int32_t fuelq_ipc_close(void* dev_ptr) {
+  if (!dev_ptr) return kOk;
+  return cudaIpcCloseMemHandle(dev_ptr) == cudaSuccess ? kOk : kLaunchFailure;
+}
+int32_t fuelq_ipc_free(void* dev_ptr) {
+  if (!dev_ptr) return kOk;
+  return cudaFree(dev_ptr) == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_qmatmul_packed_peer(int32_t ggml_type, int64_t k, int64_t n_local, const void* w, const void* act,
+                                  void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t wait_seq,
+                                  int32_t push_seq, void* stream) {
+  const int32_t st = check_problem(ggml_type, 1, n_local, k);
+  if (st != kOk) return st;
+  if (n_local == 0 || dst_offset < 0) return kInvalidProblem;  // every rank contributes to an exchange point
+  if (!w || !act || !dst) return kInvalidProblem;
+  if (!aligned(w, 16) || !aligned(act, 16)) return kMisaligned;
+  DecodeRegsPeer g;
+  const int32_t sc = make_peer_ctx(peers, wait_seq, push_seq, &g.ctx);
+  if (sc != kOk) return sc;
+  if (g.ctx.push_seq < 0) return kInvalidProblem;
+  for (int q = 0; q < kPeerMaxWorld; ++q) {
+    g.dst[q] = nullptr;
+    if (q >= g.ctx.world) continue;
+    if (!dst[q]) return kInvalidProblem;
+    if (!aligned(dst[q], 16)) return kMisaligned;
+    g.dst[q] = (uint2*)dst[q] + dst_offset;
+  }
+  ActPlanes planes = {};
+  g.act_ll = StampedPlanes{nullptr, nullptr, nullptr};
+  g.act_smem_off = 0;
+  if (g.ctx.wait_seq >= 0) {
+    if (ggml_type != kQ4K && ggml_type != kQ6K) return kNotSupported;  // stamped planes are Q8_K activations
+    g.act_ll = stamped_planes(const_cast<void*>(act), k);
+  } else {
+    planes = act_planes(const_cast<void*>(act), ggml_type, 1, k);
+  }
+  return decode_regs_impl(ggml_type, 1, n_local, k, w, planes, nullptr, (cudaStream_t)stream, &g);
+}
+
+int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, const float* gain, int64_t dim, float eps, void* packed,
+                                   size_t packed_bytes, const fuelq_peers* peers, int32_t wait_seq, void* stream) {
+  if (dim <= 0 || dim % 256 || dim > 8192) return kInvalidProblem;
+  if (!x || !gain) return kInvalidProblem;
+  if (!packed || packed_bytes < act_packed_bytes(kQ4K, 1, dim)) return kWorkspace;
+  if (!aligned(x, 16) || !aligned(gain, 16) || (delta && !aligned(delta, 16)) || !aligned(packed, 16)) return kMisaligned;
+  PeerCtx c;
+  const int32_t sc = make_peer_ctx(peers, wait_seq, -1, &c);
+  if (sc != kOk) return sc;
+  if ((delta != nullptr) != (c.wait_seq >= 0)) return kInvalidProblem;
+  const ActPlanes a = act_planes(packed, kQ4K, 1, dim);
+  const cudaError_t e = launch(add_rmsnorm_q8k_peer_kernel, dim3(1), dim3((unsigned)(dim / 256 * 32)), 0, (cudaStream_t)stream,
+                               x, (const uint2*)delta, gain, (int)dim, eps, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums, c);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_swiglu_q8k_peer(const float* gate, const float* up, int64_t n_local, int64_t col0, int64_t k_total,
+                              void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream) {
+  if (n_local <= 0 || n_local % 256 || col0 < 0 || col0 % 256 || k_total % 256 || col0 + n_local > k_total ||
+      k_total > (1 << 30))
+    return kInvalidProblem;
+  if (!gate || !up) return kInvalidProblem;
+  if (!aligned(gate, 16) || !aligned(up, 16)) return kMisaligned;
+  PeerCtx c;
+  int32_t sc = make_peer_ctx(peers, -1, push_seq, &c);
+  if (sc != kOk) return sc;
+  if (c.push_seq < 0) return kInvalidProblem;
+  PeerStampedPlanes pp;
+  sc = make_peer_planes(act_dst, k_total, c.world, &pp);
+  if (sc != kOk) return sc;
+  const int nb = (int)(n_local / 256);
+  const cudaError_t e = launch(swiglu_q8k_peer_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, gate,
+                               up, nb, (int)(col0 / 256), pp, c);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_attn_decode_q8k_peer(const float* q, const float* kcache, const float* vcache, const int32_t* pos,
+                                   int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale,
+                                   void* workspace, size_t workspace_bytes, int32_t head0, int64_t k_total,
+                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream) {
+  if (head_dim != 128) return kNotSupported;
+  if (n_heads <= 0 || n_heads % 2 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
+  if (head0 < 0 || head0 % 2 || k_total % 256 || (int64_t)(head0 + n_heads) * 128 > k_total) return kInvalidProblem;
+  if (!q || !kcache || !vcache || !pos) return kInvalidProblem;
+  if (!workspace || workspace_bytes < fuelq_attn_decode_workspace_bytes(n_heads)) return kWorkspace;
+  if (!aligned(q, 16) || !aligned(kcache, 16) || !aligned(vcache, 16) || !aligned(workspace, 16)) return kMisaligned;
+  PeerCtx c;
+  int32_t sc = make_peer_ctx(peers, -1, push_seq, &c);
+  if (sc != kOk) return sc;
+  if (c.push_seq < 0) return kInvalidProblem;
+  PeerStampedPlanes pp;
+  sc = make_peer_planes(act_dst, k_total, c.world, &pp);
+  if (sc != kOk) return sc;
+  cudaError_t e = launch(attn_partial_kernel, dim3((unsigned)n_heads, kAttnSplits), dim3(256), 0, (cudaStream_t)stream, q,
+                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+  if (e != cudaSuccess) return kLaunchFailure;
+  e = launch(attn_combine_q8k_peer_kernel, dim3((unsigned)(n_heads / 2)), dim3(32), 0, (cudaStream_t)stream,
+             (const float*)workspace, (int)(head0 / 2), pp, c);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_argmax_last_peer(const void* x, int64_t n, int32_t* out_index, const fuelq_peers* peers, int32_t wait_seq,
+                               uint32_t* epoch, void* stream) {
+  if (n <= 0 || n % 2 || n > (1 << 30)) return kInvalidProblem;
+  if (!x || !out_index || !epoch) return kInvalidProblem;
+  if (!aligned(x, 16)) return kMisaligned;
+  PeerCtx c;
+  const int32_t sc = make_peer_ctx(peers, wait_seq, -1, &c);
+  if (sc != kOk) return sc;
+  if (epoch != c.epoch || c.wait_seq < 0) return kInvalidProblem;
+  const cudaError_t e = launch(argmax_last_peer_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, (const float*)x, (int)n,
+                               (int*)out_index, c, epoch);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 

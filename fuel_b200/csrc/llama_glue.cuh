@@ -10,9 +10,14 @@
 // reduction orders so a value never depends on how many GPUs share the model.
 #pragma once
 #include "fq_common.cuh"
+#include "peer.cuh"
 #include "quantize_act.cuh"
 
 namespace fq {
+
+// No pointer parameter in this file is __restrict__: under programmatic dependent launch these kernels start
+// while their predecessor is still writing their inputs, and a read-only-for-the-kernel's-lifetime promise
+// would let the compiler move such loads above the dependency wait.
 
 __device__ __forceinline__ float block_sum_256(float v, float* red) {
 #pragma unroll
@@ -27,8 +32,8 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
 }
 
 // token ids -> dequantized Q4_K rows of the embedding table (one CTA per id, 16 threads per super-block)
-__global__ void __launch_bounds__(256) embed_q4k_kernel(const uint8_t* __restrict__ table, int row_bytes, int k,
-                                                        const int* __restrict__ ids, float* __restrict__ out) {
+__global__ void __launch_bounds__(256) embed_q4k_kernel(const uint8_t* table, int row_bytes, int k,
+                                                        const int* ids, float* out) {
   pdl_launch_dependents();
   pdl_wait();
   const uint8_t* row = table + (size_t)ids[blockIdx.x] * row_bytes;
@@ -65,10 +70,10 @@ __global__ void __launch_bounds__(256) embed_q4k_kernel(const uint8_t* __restric
 
 // rotate q (n_heads) and k (n_kv) at position *pos, then append k and v to the caches
 // caches: [n_kv][max_seq][hd]; cos/sin: [max_seq][hd] (both halves hold the same angles)
-__global__ void __launch_bounds__(128) rope_store_kernel(float* __restrict__ q, const float* __restrict__ k,
-                                                         const float* __restrict__ v, float* __restrict__ kc,
-                                                         float* __restrict__ vc, const float* __restrict__ cosT,
-                                                         const float* __restrict__ sinT, const int* __restrict__ pos_p,
+__global__ void __launch_bounds__(128) rope_store_kernel(float* q, const float* k,
+                                                         const float* v, float* kc,
+                                                         float* vc, const float* cosT,
+                                                         const float* sinT, const int* pos_p,
                                                          int n_heads, int n_kv, int hd, int max_seq) {
   pdl_launch_dependents();
   pdl_wait();
@@ -107,9 +112,9 @@ __global__ void __launch_bounds__(128) rope_store_kernel(float* __restrict__ q, 
 constexpr int kAttnSplits = 8;
 constexpr int kAttnPartStride = 132;  // 128 outputs + max + sum (+ pad)
 
-__global__ void __launch_bounds__(256) attn_partial_kernel(const float* __restrict__ q, const float* __restrict__ kc,
-                                                           const float* __restrict__ vc, float* __restrict__ part,
-                                                           const int* __restrict__ pos_p, int n_heads, int n_kv,
+__global__ void __launch_bounds__(256) attn_partial_kernel(const float* q, const float* kc,
+                                                           const float* vc, float* part,
+                                                           const int* pos_p, int n_heads, int n_kv,
                                                            int max_seq, float scale) {
   __shared__ float scores[1024];
   __shared__ float red[8];
@@ -173,7 +178,7 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float* __restri
   }
 }
 
-__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out) {
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* part, float* out) {
   pdl_launch_dependents();
   pdl_wait();
   const int head = blockIdx.x, d = threadIdx.x;
@@ -197,11 +202,11 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
 // residual add (x += delta, written back), then RMSNorm with gain. kQuant = false stores the f32 row to
 // `out`; kQuant = true (one row) quantizes it into the activation planes. Both forms share every
 // arithmetic step and its order, so they produce the same values.
-template <bool kQuant>
-__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
-                                                           const float* __restrict__ gain, float* __restrict__ out, int dim,
-                                                           float eps, int8_t* __restrict__ out_qs, float* __restrict__ out_d,
-                                                           int16_t* __restrict__ out_bsums) {
+template <bool kQuant, bool kPeer>
+__device__ __forceinline__ void add_rmsnorm_body(float* x, const void* delta_v,
+                                                 const float* gain, float* out, int dim, float eps,
+                                                 int8_t* out_qs, float* out_d,
+                                                 int16_t* out_bsums, const PeerCtx* pc) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -212,9 +217,20 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
   {
     float4* xr = reinterpret_cast<float4*>(x + base);
     float4 v0 = xr[lane], v1 = xr[32 + lane];
-    if (delta) {
-      const float4* dr = reinterpret_cast<const float4*>(delta + base);
-      const float4 d0 = dr[lane], d1 = dr[32 + lane];
+    if (delta_v) {
+      float4 d0, d1;
+      if constexpr (kPeer) {
+        // delta arrives from the peers' kernels as stamped pairs (one row)
+        const uint2* dl = reinterpret_cast<const uint2*>(delta_v) + warp * 256;
+        const uint32_t want = peer_stamp(*pc, pc->wait_seq);
+        uint32_t a[4], b[4];
+        peer_load_words2<4, 4>(dl + 4 * lane, dl + 128 + 4 * lane, want, a, b);
+        d0 = make_float4(__uint_as_float(a[0]), __uint_as_float(a[1]), __uint_as_float(a[2]), __uint_as_float(a[3]));
+        d1 = make_float4(__uint_as_float(b[0]), __uint_as_float(b[1]), __uint_as_float(b[2]), __uint_as_float(b[3]));
+      } else {
+        const float4* dr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(delta_v) + base);
+        d0 = dr[lane], d1 = dr[32 + lane];
+      }
       v0.x += d0.x, v0.y += d0.y, v0.z += d0.z, v0.w += d0.w;
       v1.x += d1.x, v1.y += d1.y, v1.z += d1.z, v1.w += d1.w;
       xr[lane] = v0, xr[32 + lane] = v1;
@@ -244,10 +260,50 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
   }
 }
 
+template <bool kQuant>
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* x, const float* delta,
+                                                           const float* gain, float* out, int dim,
+                                                           float eps, int8_t* out_qs, float* out_d,
+                                                           int16_t* out_bsums) {
+  add_rmsnorm_body<kQuant, false>(x, delta, gain, out, dim, eps, out_qs, out_d, out_bsums, nullptr);
+}
+
+// quantizing form whose residual delta (stamped pairs) arrives through exchange point pc.wait_seq
+__global__ void __launch_bounds__(1024) add_rmsnorm_q8k_peer_kernel(float* x, const uint2* delta,
+                                                                    const float* gain, int dim, float eps,
+                                                                    int8_t* out_qs, float* out_d,
+                                                                    int16_t* out_bsums, const PeerCtx pc) {
+  add_rmsnorm_body<true, true>(x, delta, gain, nullptr, dim, eps, out_qs, out_d, out_bsums, &pc);
+}
+
+// Stamped activation planes of every rank, for producers that quantize their slice and store it everywhere.
+struct PeerStampedPlanes {
+  StampedPlanes r[kPeerMaxWorld];
+};
+
+// One warp stores its quantized 256-block `blk` as stamped pairs into every rank's planes.
+__device__ __forceinline__ void q8k_block_store_stamped(const Q8KLaneBlock& b, int lane, int blk, const PeerStampedPlanes& out,
+                                                        int world, uint32_t stamp) {
+  // 16-sums as int16 pairs: word j < 4 holds sums 2j, 2j+1 (lanes 8j, 8j+4, first half), word 4+j the second half
+  const uint32_t lo0 = (uint32_t)b.s0 & 0xffffu, lo1 = (uint32_t)b.s1 & 0xffffu;
+  const uint32_t hi0 = (uint32_t)__shfl_down_sync(0xffffffffu, b.s0, 4) & 0xffffu;
+  const uint32_t hi1 = (uint32_t)__shfl_down_sync(0xffffffffu, b.s1, 4) & 0xffffu;
+  for (int q = 0; q < world; ++q) {
+    const StampedPlanes& sp = out.r[q];
+    st_pair(sp.qs + (size_t)blk * 64 + lane, b.p0, stamp);
+    st_pair(sp.qs + (size_t)blk * 64 + 32 + lane, b.p1, stamp);
+    if ((lane & 7) == 0) {
+      st_pair(sp.bs + (size_t)blk * 8 + (lane >> 3), lo0 | (hi0 << 16), stamp);
+      st_pair(sp.bs + (size_t)blk * 8 + 4 + (lane >> 3), lo1 | (hi1 << 16), stamp);
+    }
+    if (lane == 0) st_pair(sp.d + blk, __float_as_uint(b.d), stamp);
+  }
+}
+
 // silu(gate) * up, quantized; one warp per 256 elements
-__global__ void __launch_bounds__(256) swiglu_q8k_kernel(const float* __restrict__ gate, const float* __restrict__ up,
-                                                         int64_t n_blocks, int8_t* __restrict__ out_qs,
-                                                         float* __restrict__ out_d, int16_t* __restrict__ out_bsums) {
+__global__ void __launch_bounds__(256) swiglu_q8k_kernel(const float* gate, const float* up,
+                                                         int64_t n_blocks, int8_t* out_qs,
+                                                         float* out_d, int16_t* out_bsums) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -265,8 +321,8 @@ __global__ void __launch_bounds__(256) swiglu_q8k_kernel(const float* __restrict
 }
 
 // merge of the attention chunks for two heads (256 outputs) per warp, quantized
-__global__ void __launch_bounds__(32) attn_combine_q8k_kernel(const float* __restrict__ part, int8_t* __restrict__ out_qs,
-                                                              float* __restrict__ out_d, int16_t* __restrict__ out_bsums) {
+__global__ void __launch_bounds__(32) attn_combine_q8k_kernel(const float* part, int8_t* out_qs,
+                                                              float* out_d, int16_t* out_bsums) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x, blk = blockIdx.x;
@@ -289,8 +345,55 @@ __global__ void __launch_bounds__(32) attn_combine_q8k_kernel(const float* __res
   q8k_block_from_regs(e, lane, blk, out_qs, out_d, out_bsums);
 }
 
-__global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
-                                                     float* __restrict__ out, int64_t n) {
+// Tensor-parallel forms of the two kernels above: this rank's blocks [blk0, blk0 + n_blocks) of the full
+// vector are quantized once and stored, as stamped pairs of exchange point pc.push_seq, into every rank's planes.
+__global__ void __launch_bounds__(256) swiglu_q8k_peer_kernel(const float* gate, const float* up,
+                                                              int n_blocks, int blk0, const PeerStampedPlanes out,
+                                                              const PeerCtx pc) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t stamp = peer_stamp(pc, pc.push_seq);
+  const int lane = threadIdx.x & 31;
+  const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (blk >= n_blocks) return;
+  const float4* gp = reinterpret_cast<const float4*>(gate + (size_t)blk * 256);
+  const float4* up4 = reinterpret_cast<const float4*>(up + (size_t)blk * 256);
+  const float4 a0 = gp[lane], a1 = gp[32 + lane], b0 = up4[lane], b1 = up4[32 + lane];
+  const float g[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+  const float u[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  float e[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) e[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
+  q8k_block_store_stamped(q8k_block_quantize(e, lane), lane, blk0 + blk, out, pc.world, stamp);
+}
+
+__global__ void __launch_bounds__(32) attn_combine_q8k_peer_kernel(const float* part, int blk0,
+                                                                   const PeerStampedPlanes out, const PeerCtx pc) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t stamp = peer_stamp(pc, pc.push_seq);
+  const int lane = threadIdx.x, blk = blockIdx.x;
+  float e[8];
+#pragma unroll
+  for (int hsel = 0; hsel < 2; ++hsel) {
+    const float* p = part + (size_t)(2 * blk + hsel) * kAttnSplits * kAttnPartStride;
+    float M = -INFINITY;
+    for (int s = 0; s < kAttnSplits; ++s) M = fmaxf(M, p[s * kAttnPartStride + 128]);
+    float num[4] = {0, 0, 0, 0}, den = 0.f;
+    for (int s = 0; s < kAttnSplits; ++s) {
+      const float w = expf(p[s * kAttnPartStride + 128] - M);
+      const float4 v = reinterpret_cast<const float4*>(p + s * kAttnPartStride)[lane];
+      num[0] += w * v.x, num[1] += w * v.y, num[2] += w * v.z, num[3] += w * v.w;
+      den += w * p[s * kAttnPartStride + 129];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[4 * hsel + i] = num[i] / den;
+  }
+  q8k_block_store_stamped(q8k_block_quantize(e, lane), lane, blk0 + blk, out, pc.world, stamp);
+}
+
+__global__ void __launch_bounds__(256) swiglu_kernel(const float* gate, const float* up,
+                                                     float* out, int64_t n) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -301,16 +404,33 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
 }
 
 // index of the LAST maximum (ties and NaN-free data); one CTA
-__global__ void __launch_bounds__(1024) argmax_last_kernel(const float* __restrict__ x, int n, int* __restrict__ out) {
+template <bool kPeer>
+__device__ __forceinline__ void argmax_last_body(const float* x, int n, int* out, const PeerCtx* pc,
+                                                 uint32_t* epoch) {
   __shared__ float sv[32];
   __shared__ int si[32];
   pdl_launch_dependents();
   pdl_wait();
   float bv = -INFINITY;
   int bi = -1;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = x[i];
-    if (v > bv || (v == bv && i > bi)) bv = v, bi = i;
+  if constexpr (kPeer) {
+    // x is a buffer of n stamped pairs (n even) filled through exchange point pc->wait_seq
+    const uint2* xl = reinterpret_cast<const uint2*>(x);
+    const uint32_t want = peer_stamp(*pc, pc->wait_seq);
+    for (int i = 2 * threadIdx.x; i < n; i += 2 * blockDim.x) {
+      uint32_t w[2];
+      peer_load_words<2>(xl + i, want, w);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float v = __uint_as_float(w[j]);
+        if (v > bv || (v == bv && i + j > bi)) bv = v, bi = i + j;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = x[i];
+      if (v > bv || (v == bv && i > bi)) bv = v, bi = i;
+    }
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
@@ -325,7 +445,18 @@ __global__ void __launch_bounds__(1024) argmax_last_kernel(const float* __restri
     for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
       if (sv[w] > bv || (sv[w] == bv && si[w] > bi)) bv = sv[w], bi = si[w];
     *out = bi;
+    if constexpr (kPeer) *epoch = *epoch + 1u;  // last kernel of a step: the next step's stamps differ
   }
+}
+
+__global__ void __launch_bounds__(1024) argmax_last_kernel(const float* x, int n, int* out) {
+  argmax_last_body<false>(x, n, out, nullptr, nullptr);
+}
+
+// logits arrive as stamped pairs through exchange point pc.wait_seq; also advances this rank's step counter
+__global__ void __launch_bounds__(1024) argmax_last_peer_kernel(const float* x, int n, int* out,
+                                                                const PeerCtx pc, uint32_t* epoch) {
+  argmax_last_body<true>(x, n, out, &pc, epoch);
 }
 
 }  // namespace fq

@@ -22,8 +22,13 @@ namespace fq {
 // One warp quantizes one 256-element block held as e[0..3] = elements 4*lane.., e[4..7] = elements
 // 128 + 4*lane..; writes the plane-split layout. Shared by the stand-alone kernel and by the fused
 // producers (norm / SwiGLU / attention merge) so all of them emit identical bytes.
-__device__ __forceinline__ void q8k_block_from_regs(const float (&e)[8], int lane, int64_t blk, int8_t* __restrict__ out_qs,
-                                                    float* __restrict__ out_d, int16_t* __restrict__ out_bsums) {
+struct Q8KLaneBlock {
+  uint32_t p0, p1;  // this lane's eight quants, packed
+  float d;
+  int s0, s1;       // sums of the 16-element groups this lane belongs to (valid in every lane of the group)
+};
+
+__device__ __forceinline__ Q8KLaneBlock q8k_block_quantize(const float (&e)[8], int lane) {
   float amax = 0.f, smax = 0.f;
   int idx = 0;
 #pragma unroll
@@ -71,20 +76,32 @@ __device__ __forceinline__ void q8k_block_from_regs(const float (&e)[8], int lan
                       ((uint32_t)(q[3] & 0xff) << 24);
   const uint32_t p1 = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) |
                       ((uint32_t)(q[7] & 0xff) << 24);
+  Q8KLaneBlock b;
+  b.p0 = p0, b.p1 = p1, b.d = d, b.s0 = s0, b.s1 = s1;
+  return b;
+}
+
+__device__ __forceinline__ void q8k_block_store(const Q8KLaneBlock& b, int lane, int64_t blk, int8_t* out_qs,
+                                                float* out_d, int16_t* out_bsums) {
   uint32_t* qs = reinterpret_cast<uint32_t*>(out_qs + blk * QK_K);
-  qs[lane] = p0;
-  qs[32 + lane] = p1;
-  if (lane == 0) out_d[blk] = d;
+  qs[lane] = b.p0;
+  qs[32 + lane] = b.p1;
+  if (lane == 0) out_d[blk] = b.d;
   if ((lane & 3) == 0) {
-    out_bsums[blk * 16 + (lane >> 2)] = (int16_t)s0;
-    out_bsums[blk * 16 + 8 + (lane >> 2)] = (int16_t)s1;
+    out_bsums[blk * 16 + (lane >> 2)] = (int16_t)b.s0;
+    out_bsums[blk * 16 + 8 + (lane >> 2)] = (int16_t)b.s1;
   }
 }
 
+__device__ __forceinline__ void q8k_block_from_regs(const float (&e)[8], int lane, int64_t blk, int8_t* out_qs,
+                                                    float* out_d, int16_t* out_bsums) {
+  q8k_block_store(q8k_block_quantize(e, lane), lane, blk, out_qs, out_d, out_bsums);
+}
+
 template <bool kRefLayout>
-__global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* __restrict__ x, int64_t n_blocks,
-                                                           uint8_t* __restrict__ out_ref, int8_t* __restrict__ out_qs,
-                                                           float* __restrict__ out_d, int16_t* __restrict__ out_bsums) {
+__global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* x, int64_t n_blocks,
+                                                           uint8_t* out_ref, int8_t* out_qs,
+                                                           float* out_d, int16_t* out_bsums) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -171,9 +188,9 @@ __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* __restri
 
 // One warp per 256 elements = eight Q8_0 blocks; a block is 8 neighbouring lanes of one half.
 template <bool kRefLayout>
-__global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* __restrict__ x, int64_t n_groups /* of 256 */,
-                                                            int64_t n_blocks32, uint8_t* __restrict__ out_ref,
-                                                            int8_t* __restrict__ out_qs, float* __restrict__ out_d) {
+__global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* x, int64_t n_groups /* of 256 */,
+                                                            int64_t n_blocks32, uint8_t* out_ref,
+                                                            int8_t* out_qs, float* out_d) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;

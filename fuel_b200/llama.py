@@ -9,10 +9,18 @@ rows, no block is cut) and the pieces are put back with an all-gather; heads are
 way, so attention is local. Nothing is ever summed across ranks, which makes every value — and so
 every greedy token — bit-identical for 1, 2, 4 or 8 GPUs by construction. The price is four small
 all-gathers per layer instead of the usual two all-reduces.
+
+Two ways to do those gathers: comm="nccl" calls the library all-gather between the kernels (the
+baseline), comm="peer" does the exchange inside the kernels themselves: the mat-vec, the attention
+merge and the SwiGLU kernel store their slice straight into every GPU's buffer over NVLink and stamp
+a flag, and the next kernel polls its own flags before it reads (include/fuelq.h, fuelq_*_peer).
+The peer form also keeps the fused activation quantizers, so a layer is the same eleven launches as
+on one GPU.
 """
 from __future__ import annotations
 
 import dataclasses
+import gc
 import math
 
 import numpy as np
@@ -71,6 +79,83 @@ def init_weight(n: int, k: int, seed: int, device) -> torch.Tensor:
     return torch.randn(n, k, generator=g, device=device, dtype=torch.float32) * 0.02
 
 
+def shard_range(total: int, world: int, rank: int, unit: int = 1):
+    """Rows [lo, hi) of `total` owned by `rank`: whole `unit`s, the first total/unit % world ranks get one more."""
+    assert total % unit == 0
+    blocks = total // unit
+    q, rem = divmod(blocks, world)
+    lo = rank * q + min(rank, rem)
+    return lo * unit, (lo + q + (1 if rank < rem else 0)) * unit
+
+
+class _RawCuda:
+    """A device range owned elsewhere, for torch.as_tensor."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class PeerRegion:
+    """One zeroed device allocation per rank that the other ranks of the node map: the exchange flags and the
+    destination buffers. `base[q]` is rank q's region as addressed from this process."""
+
+    def __init__(self, sizes: dict, device: torch.device, rank: int, world: int):
+        import ctypes
+        self.rank, self.world = rank, world
+        self.off, total = {}, 0
+        for name, nbytes in sizes.items():
+            self.off[name] = total
+            total += _align(nbytes)
+        self.nbytes = total
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        _check(_L.fuelq_ipc_alloc(total, ctypes.byref(own), handle), "fuelq_ipc_alloc")
+        self.own = own.value
+        self.base = [None] * world
+        self.base[rank] = self.own
+        self.opened = []
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, handle.raw)
+            for q in range(world):
+                if q == rank:
+                    continue
+                ptr = ctypes.c_void_p()
+                _check(_L.fuelq_ipc_open(handles[q], ctypes.byref(ptr)), "fuelq_ipc_open")
+                self.base[q] = ptr.value
+                self.opened.append(ptr.value)
+            dist.barrier()
+        self.bytes_view = torch.as_tensor(_RawCuda(self.own, total), device=device)
+
+    def ptrs(self, name: str, extra: int = 0):
+        """ctypes array of `name`'s address on every rank (+ extra bytes)."""
+        import ctypes
+        arr = (ctypes.c_void_p * _lib.PEER_MAX_WORLD)()
+        for q in range(self.world):
+            arr[q] = self.base[q] + self.off[name] + extra
+        return arr
+
+    def view(self, name: str, nbytes: int, dtype) -> torch.Tensor:
+        return self.bytes_view[self.off[name]: self.off[name] + nbytes].view(dtype)
+
+    def close(self) -> None:
+        """After every rank has finished its last step (callers synchronize and barrier first)."""
+        if self.own is None:
+            return
+        self.bytes_view = None
+        for ptr in self.opened:
+            _L.fuelq_ipc_close(ptr)
+        self.opened = []
+        if self.world > 1:
+            dist.barrier()
+        _L.fuelq_ipc_free(self.own)
+        self.own = None
+
+
 def _check(st: int, op: str) -> None:
     if st:
         _lib.check(st, op)
@@ -94,11 +179,20 @@ class _Linear:
 
 class QLlama:
     def __init__(self, cfg: LlamaConfig, device: torch.device, rank: int = 0, world: int = 1, seed: int = 0,
-                 mix=q4km_mix):
-        assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0 and cfg.ffn_dim % world == 0
+                 mix=q4km_mix, comm: str = "nccl"):
+        assert comm in ("nccl", "peer")
+        assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0
         assert cfg.dim % world == 0 and cfg.vocab % world == 0 and cfg.head_dim == 128
-        self.cfg, self.device, self.rank, self.world = cfg, device, rank, world
+        self.cfg, self.device, self.rank, self.world, self.comm = cfg, device, rank, world, comm
         c, g, r = cfg, world, rank
+        # FFN rows: equal parts for the library all-gather; whole 256-blocks (so a rank can quantize its own
+        # part of the SwiGLU output) for the in-kernel exchange
+        self.f_lo, self.f_hi = shard_range(c.ffn_dim, g, r, 256 if comm == "peer" else 1)
+        if comm == "nccl":
+            assert c.ffn_dim % g == 0
+        else:
+            assert (c.n_heads // g) % 2 == 0 and world <= _lib.PEER_MAX_WORLD and 4 * c.n_layers + 1 <= _lib.PEER_MAX_SEQ
+        fl = self.f_hi - self.f_lo
         self.hl, self.kvl = c.n_heads // g, c.n_kv_heads // g
         qd, kvd = self.hl * c.head_dim, self.kvl * c.head_dim
         f32 = dict(dtype=torch.float32, device=device)
@@ -114,8 +208,8 @@ class QLlama:
             wk = rows(init_weight(c.n_kv_heads * c.head_dim, c.dim, s0 + 2, device), r * kvd, (r + 1) * kvd)
             wv = rows(init_weight(c.n_kv_heads * c.head_dim, c.dim, s0 + 3, device), r * kvd, (r + 1) * kvd)
             wo = rows(init_weight(c.dim, c.dim, s0 + 4, device), r * c.dim // g, (r + 1) * c.dim // g)
-            wg = rows(init_weight(c.ffn_dim, c.dim, s0 + 5, device), r * c.ffn_dim // g, (r + 1) * c.ffn_dim // g)
-            wu = rows(init_weight(c.ffn_dim, c.dim, s0 + 6, device), r * c.ffn_dim // g, (r + 1) * c.ffn_dim // g)
+            wg = rows(init_weight(c.ffn_dim, c.dim, s0 + 5, device), self.f_lo, self.f_hi)
+            wu = rows(init_weight(c.ffn_dim, c.dim, s0 + 6, device), self.f_lo, self.f_hi)
             wd = rows(init_weight(c.dim, c.ffn_dim, s0 + 7, device), r * c.dim // g, (r + 1) * c.dim // g)
             tq, tv, to, tg, td = (mix("attn_q", li), mix("attn_v", li), mix("attn_output", li), mix("ffn_gate", li),
                                   mix("ffn_down", li))
@@ -123,7 +217,7 @@ class QLlama:
                 qk=_Linear(tq, _quantize(tq, torch.cat([wq, wk])), qd + kvd, c.dim),
                 v=_Linear(tv, _quantize(tv, wv), kvd, c.dim),
                 o=_Linear(to, _quantize(to, wo), c.dim // g, c.dim),
-                gu=_Linear(tg, _quantize(tg, torch.cat([wg, wu])), 2 * c.ffn_dim // g, c.dim),
+                gu=_Linear(tg, _quantize(tg, torch.cat([wg, wu])), 2 * fl, c.dim),
                 down=_Linear(td, _quantize(td, wd), c.dim // g, c.ffn_dim),
                 attn_norm=torch.ones(c.dim, **f32), ffn_norm=torch.ones(c.dim, **f32),
                 kc=torch.zeros(self.kvl, c.max_seq, c.head_dim, **f32),
@@ -147,8 +241,8 @@ class QLlama:
         self.v = torch.zeros(kvd, **f32)
         self.attn_l = torch.zeros(qd, **f32)
         self.o_l = torch.zeros(c.dim // g, **f32)
-        self.gu = torch.zeros(2 * c.ffn_dim // g, **f32)
-        self.s_l = torch.zeros(c.ffn_dim // g, **f32)
+        self.gu = torch.zeros(2 * fl, **f32)
+        self.s_l = torch.zeros(fl, **f32)
         self.d_l = torch.zeros(c.dim // g, **f32)
         self.logits_l = torch.zeros(c.vocab // g, **f32)
         if g > 1:
@@ -162,6 +256,9 @@ class QLlama:
         nb = max(_L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.dim), _L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.ffn_dim))
         self.packed = torch.zeros(nb, dtype=torch.uint8, device=device)
         self.attn_ws = torch.zeros(max(_L.fuelq_attn_decode_workspace_bytes(self.hl), 16), dtype=torch.uint8, device=device)
+        self.peer = None
+        if comm == "peer":
+            self._init_peer()
         self.graph = None
         self.fused = True  # single-GPU step uses the fused producers
         self.weight_bytes = (sum(l[k].blocks.numel() for l in self.layers for k in ("qk", "v", "o", "gu", "down"))
@@ -177,9 +274,87 @@ class QLlama:
                                             stream), "fuelq_quantize_act_packed")
 
     def step(self) -> None:
+        if self.comm == "peer":
+            return self._step_peer()
         if self.world == 1 and self.fused:
             return self._step_fused()
         return self._step_plain()
+
+    # ---- in-kernel exchange over peer-mapped memory
+    def _init_peer(self) -> None:
+        import ctypes
+        c, g, r = self.cfg, self.world, self.rank
+        self.peer = PeerRegion({"pattn": _L.fuelq_peer_act_bytes(c.dim), "ps": _L.fuelq_peer_act_bytes(c.ffn_dim),
+                                "o": _L.fuelq_peer_vec_bytes(c.dim), "d": _L.fuelq_peer_vec_bytes(c.dim),
+                                "logits": _L.fuelq_peer_vec_bytes(c.vocab)}, self.device, r, g)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.peers = _lib.Peers()
+        self.peers.world, self.peers.rank, self.peers.epoch = g, r, self.epoch.data_ptr()
+        self.peers_ref = ctypes.byref(self.peers)
+        self.dst_pattn, self.dst_ps = self.peer.ptrs("pattn"), self.peer.ptrs("ps")
+        self.dst_o, self.dst_d, self.dst_logits = self.peer.ptrs("o"), self.peer.ptrs("d"), self.peer.ptrs("logits")
+        own = self.peer.own
+        self.own_pattn, self.own_ps = own + self.peer.off["pattn"], own + self.peer.off["ps"]
+        self.own_o, self.own_d = own + self.peer.off["o"], own + self.peer.off["d"]
+        self.own_logits = own + self.peer.off["logits"]
+        self.logits_pairs = self.peer.view("logits", 8 * c.vocab, torch.float32)  # {value, stamp} pairs
+
+    @property
+    def logits(self) -> torch.Tensor:
+        if self.peer is not None:
+            return self.logits_pairs[0::2]
+        return self._logits
+
+    @logits.setter
+    def logits(self, t: torch.Tensor) -> None:
+        self._logits = t
+
+    def _step_peer(self) -> None:
+        c, r = self.cfg, self.rank
+        st = torch.cuda.current_stream().cuda_stream
+        scale = 1.0 / math.sqrt(c.head_dim)
+        pk, pkn = self.packed.data_ptr(), self.packed.numel()
+        pr = self.peers_ref
+        dl, vl, fl = c.dim // self.world, c.vocab // self.world, self.f_hi - self.f_lo
+        qd = self.hl * c.head_dim
+        _check(_L.fuelq_embed_rows(int(T.Q4K), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
+               "fuelq_embed_rows")
+        delta, wait = None, -1
+        for li, l in enumerate(self.layers):
+            sq = 4 * li  # exchange points of this layer: attention, o, SwiGLU, down
+            _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), delta, l["attn_norm"].data_ptr(), c.dim, c.norm_eps, pk, pkn,
+                                                 pr, wait, st), "add_rmsnorm_q8k_peer")
+            l["qk"].matvec_packed(self.packed, self.qk, st)
+            l["v"].matvec_packed(self.packed, self.v, st)
+            _check(_L.fuelq_rope_store(self.qk.data_ptr(), self.qk.data_ptr() + 4 * qd, self.v.data_ptr(), l["kc"].data_ptr(),
+                                       l["vc"].data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
+                                       self.hl, self.kvl, c.head_dim, c.max_seq, st), "rope_store")
+            _check(_L.fuelq_attn_decode_q8k_peer(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.pos.data_ptr(),
+                                                 self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
+                                                 self.attn_ws.numel(), r * self.hl, c.dim, self.dst_pattn, pr, sq, st),
+                   "attn_decode_q8k_peer")
+            o = l["o"]
+            _check(_L.fuelq_qmatmul_packed_peer(int(o.dtype), c.dim, dl, o.blocks.data_ptr(), self.own_pattn, self.dst_o, r * dl,
+                                                pr, sq, sq + 1, st), "qmatmul_packed_peer")
+            _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), self.own_o, l["ffn_norm"].data_ptr(), c.dim, c.norm_eps, pk,
+                                                 pkn, pr, sq + 1, st), "add_rmsnorm_q8k_peer")
+            l["gu"].matvec_packed(self.packed, self.gu, st)
+            _check(_L.fuelq_swiglu_q8k_peer(self.gu.data_ptr(), self.gu.data_ptr() + 4 * fl, fl, self.f_lo, c.ffn_dim,
+                                            self.dst_ps, pr, sq + 2, st), "swiglu_q8k_peer")
+            dn = l["down"]
+            _check(_L.fuelq_qmatmul_packed_peer(int(dn.dtype), c.ffn_dim, dl, dn.blocks.data_ptr(), self.own_ps, self.dst_d,
+                                                r * dl, pr, sq + 2, sq + 3, st), "qmatmul_packed_peer")
+            delta, wait = self.own_d, sq + 3
+        last = 4 * len(self.layers)
+        _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), delta, self.out_norm.data_ptr(), c.dim, c.norm_eps, pk, pkn, pr,
+                                             wait, st), "add_rmsnorm_q8k_peer")
+        h = self.head
+        _check(_L.fuelq_qmatmul_packed_peer(int(h.dtype), c.dim, vl, h.blocks.data_ptr(), pk, self.dst_logits, r * vl, pr, -1,
+                                            last, st), "qmatmul_packed_peer")
+        _check(_L.fuelq_argmax_last_peer(self.own_logits, c.vocab, self.next_token.data_ptr(), pr, last, self.epoch.data_ptr(),
+                                         st), "argmax_last_peer")
+        self.pos.add_(1)
+        self.token.copy_(self.next_token)
 
     def _step_fused(self) -> None:
         """Single-GPU step: norm / attention merge / SwiGLU write the quantized activations directly."""
@@ -244,7 +419,7 @@ class QLlama:
                                         c.dim, c.norm_eps, st), "add_rmsnorm")
             self._quant(self.h, c.dim, st)
             l["gu"].matvec_packed(self.packed, self.gu, st)
-            fl = c.ffn_dim // self.world
+            fl = self.f_hi - self.f_lo
             _check(_L.fuelq_swiglu(self.gu.data_ptr(), self.gu.data_ptr() + 4 * fl, self.s_l.data_ptr(), fl, st), "swiglu")
             self._gather(self.s, self.s_l)
             self._quant(self.s, c.ffn_dim, st)
@@ -271,6 +446,19 @@ class QLlama:
         torch.cuda.synchronize()
         self.token.copy_(saved[0])
         self.pos.copy_(saved[1])
+
+    def release(self) -> None:
+        """Drop the captured graph. Must run before the process group is destroyed: tearing down NCCL while a
+        graph that holds its kernels is alive stalls."""
+        self.graph = None
+        gc.collect()
+        torch.cuda.synchronize()
+        if self.peer is not None:
+            keep = self.logits.clone()
+            self.logits_pairs = None
+            self.peer.close()
+            self.peer = None
+            self.logits = keep
 
     def run_step(self) -> None:
         if self.graph is not None:

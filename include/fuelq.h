@@ -183,6 +183,58 @@ int32_t fuelq_swiglu_q8k(const float* gate, const float* up, int64_t n, void* pa
 int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* vcache, const int32_t* pos, int32_t n_heads,
                               int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
                               size_t workspace_bytes, void* packed, size_t packed_bytes, void* stream);
+/* ---- Tensor-parallel decode step over peer-mapped memory.
+ * The reference has no multi-GPU form of this path (its QMatMul runs on one device,
+ * fuel-core/src/quantized/mod.rs:854-868); these entry points are how the 7B decode of the benchmark is
+ * split over the GPUs of one node. Every linear layer is split along its OUTPUT rows, so no sum crosses a
+ * GPU and the result has the same bits for any GPU count. The slices are exchanged inside the producing and
+ * consuming kernels: every 32-bit word that crosses GPUs is stored as an 8-byte pair {word, stamp} with one
+ * store, straight into a destination buffer on every rank over NVLink; the consumer re-reads the pairs it
+ * needs from its own buffer until all carry the expected stamp (with a deadline of a few seconds, after which
+ * it records device error 6 and carries on). No fences, flags, collectives or multicast. A step has a fixed
+ * list of exchange points numbered seq = 0 .. FUELQ_PEER_MAX_SEQ-1, each used once per step; the stamp is
+ * epoch * FUELQ_PEER_MAX_SEQ + seq + 1, `epoch` counting steps on the device (advanced by
+ * fuelq_argmax_last_peer), so a captured CUDA graph replays without changes. Destination buffers must start
+ * zeroed, come from fuelq_ipc_alloc and are mapped into the other processes with fuelq_ipc_open. A buffer
+ * may serve several exchange points of a step only if every rank must have consumed the earlier contents
+ * before any rank can produce the later ones. All ranks issue the same sequence of calls. */
+#define FUELQ_PEER_MAX_WORLD 8
+#define FUELQ_PEER_MAX_SEQ 1024
+typedef struct fuelq_peers {
+  int32_t world, rank;
+  const uint32_t* epoch; /* device word on this rank, starts at 0 */
+} fuelq_peers;
+/* bytes of a destination buffer for the stamped Q8_K activation planes of a k-wide vector / for n f32 words */
+size_t fuelq_peer_act_bytes(int64_t k);
+size_t fuelq_peer_vec_bytes(int64_t n);
+/* zeroed device memory that other processes of this node can map: handle64 receives 64 opaque bytes */
+int32_t fuelq_ipc_alloc(size_t bytes, void** dev_ptr, void* handle64);
+int32_t fuelq_ipc_open(const void* handle64, void** dev_ptr);
+int32_t fuelq_ipc_close(void* dev_ptr);
+int32_t fuelq_ipc_free(void* dev_ptr);
+/* y_local = W_local · act (m = 1, integer path), stored as stamped pairs of push_seq at word dst_offset of the
+ * vector buffer dst[q] of every rank q. wait_seq < 0: `act` is this rank's packed planes
+ * (fuelq_quantize_act_packed layout; Q4_K / Q6_K / Q8_0). wait_seq >= 0: `act` is this rank's stamped-planes
+ * buffer filled through that exchange point (Q4_K / Q6_K). */
+int32_t fuelq_qmatmul_packed_peer(int32_t ggml_type, int64_t k, int64_t n_local, const void* w, const void* act,
+                                  void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t wait_seq,
+                                  int32_t push_seq, void* stream);
+/* fuelq_add_rmsnorm_q8k whose delta is a vector buffer filled through wait_seq (null and -1: no delta) */
+int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, const float* gain, int64_t dim, float eps, void* packed,
+                                   size_t packed_bytes, const fuelq_peers* peers, int32_t wait_seq, void* stream);
+/* fuelq_swiglu_q8k over this rank's columns [col0, col0 + n_local) of a k_total-wide vector (multiples of 256),
+ * quantized blocks stored as stamped pairs of push_seq into every rank's stamped-planes buffer act_dst[q] */
+int32_t fuelq_swiglu_q8k_peer(const float* gate, const float* up, int64_t n_local, int64_t col0, int64_t k_total,
+                              void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream);
+/* fuelq_attn_decode_q8k over this rank's heads [head0, head0 + n_heads), stored into every rank's planes */
+int32_t fuelq_attn_decode_q8k_peer(const float* q, const float* kcache, const float* vcache, const int32_t* pos,
+                                   int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale,
+                                   void* workspace, size_t workspace_bytes, int32_t head0, int64_t k_total,
+                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream);
+/* fuelq_argmax_last over a vector buffer of n (even) words filled through wait_seq; then *epoch += 1
+ * (epoch must be peers->epoch) */
+int32_t fuelq_argmax_last_peer(const void* x, int64_t n, int32_t* out_index, const fuelq_peers* peers, int32_t wait_seq,
+                               uint32_t* epoch, void* stream);
 /* out = silu(gate) * up */
 int32_t fuelq_swiglu(const float* gate, const float* up, float* out, int64_t n, void* stream);
 /* index of the LAST maximum of x[0..n) (LogitsProcessor argmax: max_by + total_cmp,

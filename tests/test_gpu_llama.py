@@ -84,3 +84,28 @@ def test_fused_step_is_bit_identical_to_plain_step():
         outs.append((toks, model.logits.clone(), model.x.clone()))
     assert outs[0][0] == outs[1][0]
     assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][2], outs[1][2])
+
+
+def test_in_kernel_exchange_single_rank_matches_fused_step():
+    """comm="peer" with one rank runs the exchange protocol against itself (stamped pairs, step counter,
+    stores into its own destination buffers); values must equal the plain single-GPU step, eagerly and
+    as a replayed graph."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuel_b200 import ops
+    from fuel_b200.llama import QLlama
+    dev = torch.device("cuda", 0)
+    prompt = np.random.Generator(np.random.PCG64(4)).integers(0, 512, 20).tolist()
+    ref = QLlama(_tiny(), dev)
+    want = ref.generate(prompt, 16)
+    model = QLlama(_tiny(), dev, comm="peer")
+    try:
+        got = model.generate(prompt, 16)
+        assert got == want
+        assert torch.equal(model.logits, ref.logits) and torch.equal(model.x, ref.x)
+        assert int(model.epoch.item()) == len(prompt) + 15
+        model.capture()
+        assert model.generate(prompt, 16) == want
+        assert ops.device_error() == 0
+    finally:
+        model.release()
