@@ -19,6 +19,7 @@
 #include "decode.cuh"
 #include "fq_common.cuh"
 #include "peer.cuh"
+#include "quantize_act.cuh"
 
 namespace fq {
 
@@ -42,6 +43,8 @@ struct DecodeRegsParams {
   int u_begin[9];                 // unit range of k-slice s: [u_begin[s], u_begin[s+1])
   int debug_flags;                // bit 0: consumers skip the arithmetic (streaming-rate experiments)
   unsigned long long* trace;      // optional: 24 global-timer stamps per CTA
+  const float* x_f32;             // not null: f32 activations [m][k]; every CTA quantizes them itself (Q8_K) into
+  int act_smem_off;               //   plain planes at this byte offset of its shared memory, instead of reading `act`
 };
 
 // Extra arguments of the tensor-parallel form (kPeer): the output rows go, as stamped pairs of exchange
@@ -423,6 +426,24 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
   uint32_t push_stamp = 0;
   pdl_wait();  // activation planes are written by the preceding kernel
   ActPlanes planes = p.act;
+  if (Fmt::kHasRaw && p.x_f32) {
+    // fused activation quantization: the consumer warps take the 256-element blocks of the M rows in turn
+    // (the same routine as the stand-alone kernel, so the same bytes), while the producer streams weights
+    planes = act_planes(smem_raw + p.act_smem_off, kQ4K, M, p.k);
+    const int nblk = M * (p.k >> 8);
+    for (int b = warp; b < nblk; b += 2 * kDecodeConsumerWarps) {  // two blocks per round: both loads in flight at once
+      const int b2 = b + kDecodeConsumerWarps;
+      const bool two = b2 < nblk;
+      const float4* s0 = reinterpret_cast<const float4*>(p.x_f32 + (size_t)b * 256);
+      const float4* s1 = reinterpret_cast<const float4*>(p.x_f32 + (size_t)(two ? b2 : b) * 256);
+      const float4 a0 = s0[lane], a1 = s0[32 + lane], c0 = s1[lane], c1 = s1[32 + lane];
+      const float e0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float e1[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      q8k_block_from_regs(e0, lane, b, (int8_t*)planes.qs, (float*)planes.d, (int16_t*)planes.bsums);
+      if (two) q8k_block_from_regs(e1, lane, b2, (int8_t*)planes.qs, (float*)planes.d, (int16_t*)planes.bsums);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
+  }
   if constexpr (kPeer) {
     push_stamp = peer_stamp(g->ctx, g->ctx.push_seq);
     if (Fmt::kHasRaw && g->ctx.wait_seq >= 0) {

@@ -30,6 +30,7 @@ struct Options {
   int64_t dbg_depth = 0;
   int64_t dbg_pre = -1;
   int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
+  int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
 };
 Options g_opt;
 
@@ -264,8 +265,9 @@ cudaError_t launch_decode_regs_peer(const DecodeRegsParams& p, const DecodeRegsP
 
 // returns kNotSupported when this variant does not cover the problem (the caller falls back)
 int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const ActPlanes& planes, float* y,
-                         cudaStream_t stream, const DecodeRegsPeer* peer = nullptr) {
+                         cudaStream_t stream, const DecodeRegsPeer* peer = nullptr, const float* x_f32 = nullptr) {
   if (peer && m != 1) return kNotSupported;
+  if (x_f32 && (peer || (type != kQ4K && type != kQ6K))) return kNotSupported;
   if (m > 2 || (type != kQ4K && type != kQ6K && type != kQ8_0)) return kNotSupported;
   if (type == kQ8_0 && k % 128) return kNotSupported;  // its lane unit is four blocks
   DeviceInfo* di;
@@ -274,17 +276,29 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.units_per_row = (int)(k / 128);  // every format's lane unit covers 128 elements
   p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
   RegsPlan pl;
-  const size_t reserve = (peer && peer->ctx.wait_seq >= 0) ? align_up(act_packed_bytes(kQ4K, 1, k), 128) : 0;
-  const int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, reserve);
+  // Activations staged in shared memory (quantized in the kernel, or copied from stamped planes) are dead
+  // once the consumers hold them in registers, so they borrow the LAST stage buffer of the ring: the
+  // producer fills that stage only after the consumers report their activations loaded.
+  const size_t staged = ((peer && peer->ctx.wait_seq >= 0) || x_f32) ? align_up(act_packed_bytes(kQ4K, m, k), 128) : 0;
+  int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, 0);
   if (st != kOk) return st;
+  size_t reserve = 0;
+  if (staged > (size_t)pl.stage_stride || pl.num_stages < 3) {  // does not fit a stage: keep it beside the ring
+    reserve = staged;
+    st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, reserve);
+    if (st != kOk) return st;
+  }
+  const int staged_off = reserve ? (int)(pl.smem - reserve) : (int)(pl.smem - pl.stage_stride);
   DecodeRegsPeer peer_args;
   if (peer) {
     peer_args = *peer;
-    peer_args.act_smem_off = (int)(pl.smem - reserve);
+    peer_args.act_smem_off = staged_off;
     peer = &peer_args;
   }
   p.w = (const uint8_t*)w;
   p.act = planes;
+  p.x_f32 = x_f32;
+  p.act_smem_off = staged_off;
   p.y = y;
   p.n = n;
   p.k = (int)k;
@@ -300,6 +314,7 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.depth = g_opt.dbg_depth ? (int)g_opt.dbg_depth : 3;
   if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
   p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
+  if (staged && !reserve) p.pre_stages = pl.num_stages - 1;
   p.debug_flags = (int)g_opt.debug_flags;
   p.trace = (unsigned long long*)(uintptr_t)g_opt.trace_ptr;
   cudaError_t e;
@@ -520,6 +535,7 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 105: g_opt.dbg_depth = value; return kOk;
     case 106: g_opt.dbg_pre = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
+    case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     default: return kInvalidProblem;
   }
 }
@@ -531,6 +547,7 @@ int64_t fuelq_get_option(int32_t key) {
     case FUELQ_OPT_DECODE_GRID: return g_opt.decode_grid;
     case FUELQ_OPT_DECODE_KERNEL: return g_opt.decode_kernel;
     case FUELQ_OPT_L2_PREFETCH: return g_opt.l2_prefetch;
+    case FUELQ_OPT_FUSED_QUANT: return g_opt.fused_quant;
     default: return -1;
   }
 }
@@ -612,6 +629,12 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   if (g_opt.l2_prefetch) {
     st = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
     if (st != kOk) return st;
+  }
+  if (m_total <= 2 && g_opt.fused_quant && g_opt.decode_kernel != 1) {
+    // one kernel: every thread block quantizes the activation rows itself while its weights stream in
+    const ActPlanes none = {};
+    st = decode_regs_impl(ggml_type, m_total, n, k, w, none, y, (cudaStream_t)stream, nullptr, x);
+    if (st != kNotSupported) return st;
   }
   st = quantize_act_impl(ggml_type, m_total, k, x, nullptr, workspace, (cudaStream_t)stream);
   if (st != kOk) return st;

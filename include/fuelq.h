@@ -59,6 +59,11 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
 #define FUELQ_OPT_L2_PREFETCH 5   /* 1: every mat-vec call first enqueues a small kernel that streams its weight
                                     matrix from HBM into L2; with FUELQ_OPT_PDL it runs beside the preceding
                                     kernels, so the transfer overlaps their work (default 0) */
+#define FUELQ_OPT_FUSED_QUANT 6   /* 1: fuelq_qmatmul with m_total <= 2 and Q4_K / Q6_K weights runs as ONE kernel
+                                    whose thread blocks quantize the activation rows themselves (same bytes as
+                                    fuelq_quantize_act). 0 (default): quantize kernel, then mat-vec kernel, which
+                                    measured faster in a chain of launches (the small kernel overlaps the
+                                    previous mat-vec's tail; in-kernel quantization sits on the critical path) */
 int32_t fuelq_set_option(int32_t key, int64_t value);
 int64_t fuelq_get_option(int32_t key);
 

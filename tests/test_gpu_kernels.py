@@ -235,6 +235,23 @@ def test_pdl_launch_gives_same_bits(ops, oracle):
         assert torch.equal(y, y0)
 
 
+@pytest.mark.parametrize("name", ["q4k", "q6k"])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (2, 1000, 11008), (1, 33, 256)])
+def test_fused_quantization_gives_same_bits(ops, oracle, name, m, n, k):
+    """m <= 2, option on: the mat-vec kernel quantizes the activation rows itself; same bits as the two-kernel path."""
+    from fuel_b200 import _lib
+    wb = _dev(oracle.quantize(_ot(oracle, name), _weights(n, k)))
+    x = _dev(_acts(m, k))
+    y_two = ops.qmatmul(_T(name), wb, n, x)
+    try:
+        _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_FUSED_QUANT, 1), "set_option")
+        y_fused = ops.qmatmul(_T(name), wb, n, x)
+    finally:
+        _lib.lib.fuelq_set_option(_lib.OPT_FUSED_QUANT, 0)
+    assert torch.equal(y_fused, y_two)
+    assert_matmul_close(y_fused.cpu().numpy(), oracle.matmul(_ot(oracle, name), x.cpu().numpy(), wb.cpu().numpy(), n))
+
+
 def test_error_statuses_on_device(ops):
     from fuel_b200 import GgmlDType as T, _lib
     x = torch.zeros(1, 100, device="cuda")
