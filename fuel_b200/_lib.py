@@ -56,6 +56,12 @@ PROTOTYPES = {
     "fuelq_add_rmsnorm_q8k": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, _vp, _sz, _vp]),
     "fuelq_swiglu_q8k": (_i32, [_vp, _vp, _i64, _vp, _sz, _vp]),
     "fuelq_attn_decode_q8k": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _vp, _sz, _vp]),
+    "fuelq_moe_route": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "fuelq_moe_bucket": (_i32, [_vp, _i64, _i32, _vp, _vp, _vp]),
+    "fuelq_moe_quantize_rows": (_i32, [_vp, _i64, _vp, _i32, _i64, _vp, _sz, _vp]),
+    "fuelq_moe_swiglu_quantize": (_i32, [_vp, _i64, _i64, _vp, _sz, _vp]),
+    "fuelq_moe_qmatmul": (_i32, [_i32, _i32, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp]),
+    "fuelq_moe_combine": (_i32, [_vp, _vp, _vp, _i64, _i32, _i64, _vp, _vp]),
     "fuelq_peer_act_bytes": (_sz, [_i64]),
     "fuelq_peer_vec_bytes": (_sz, [_i64]),
     "fuelq_ipc_alloc": (_i32, [_sz, ctypes.POINTER(_vp), _vp]),

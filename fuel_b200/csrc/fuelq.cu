@@ -11,6 +11,7 @@
 #include "dequantize.cuh"
 #include "fq_common.cuh"
 #include "llama_glue.cuh"
+#include "moe.cuh"
 #include "prefill.cuh"
 #include "quantize_act.cuh"
 #include "quantize_weights.cuh"
@@ -843,6 +844,144 @@ int32_t fuelq_argmax_last(const float* x, int64_t n, int32_t* out_index, void* s
   if (n <= 0 || n > (1 << 30)) return kInvalidProblem;
   if (!x || !out_index) return kInvalidProblem;
   const cudaError_t e = launch(argmax_last_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, x, (int)n, (int*)out_index);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// ---- mixture-of-experts block (moe.cuh)
+int32_t fuelq_moe_route(const float* logits, int64_t n_tokens, int32_t n_experts, int32_t top_k, int32_t* topk_ids,
+                        float* topk_weights, void* stream) {
+  if (n_tokens < 0 || n_experts <= 0 || n_experts > 1024 || top_k <= 0 || top_k > kMoeMaxTopK || top_k > n_experts)
+    return kInvalidProblem;
+  if (n_tokens == 0) return kOk;
+  if (n_tokens > (1 << 24)) return kNotSupported;
+  if (!logits || !topk_ids || !topk_weights) return kInvalidProblem;
+  const cudaError_t e = launch(moe_route_kernel, dim3((unsigned)((n_tokens + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
+                               logits, (int)n_tokens, (int)n_experts, (int)top_k, (int*)topk_ids, topk_weights);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_moe_bucket(const int32_t* topk_ids, int64_t n_pairs, int32_t n_experts, int32_t* sorted_ids,
+                         int32_t* expert_offsets, void* stream) {
+  if (n_pairs < 0 || n_pairs > (1 << 24) || n_experts <= 0 || n_experts > 8192) return kInvalidProblem;
+  if (!expert_offsets || (n_pairs > 0 && (!topk_ids || !sorted_ids))) return kInvalidProblem;
+  const cudaError_t e = launch(moe_bucket_kernel, dim3(1), dim3(1024), (size_t)(n_experts + 1) * sizeof(int),
+                               (cudaStream_t)stream, (const int*)topk_ids, (int)n_pairs, (int)n_experts, (int*)sorted_ids,
+                               (int*)expert_offsets);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_moe_quantize_rows(const float* x, int64_t k, const int32_t* row_ids, int32_t divisor, int64_t n_rows,
+                                void* packed, size_t packed_bytes, void* stream) {
+  if (k <= 0 || k % 256 || k > (1 << 24) || divisor <= 0 || n_rows < 0) return kInvalidProblem;
+  if (n_rows == 0) return kOk;
+  if (!x || !row_ids || !packed) return kInvalidProblem;
+  if (packed_bytes < act_packed_bytes(kQ4K, n_rows, k)) return kWorkspace;
+  if (!aligned(x, 16) || !aligned(packed, 16)) return kMisaligned;
+  const ActPlanes a = act_planes(packed, kQ4K, n_rows, k);
+  const int64_t nb = n_rows * (k / 256);
+  const cudaError_t e = launch(moe_gather_quantize_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, x,
+                               (int)k, (const int*)row_ids, (int)divisor, nb, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_moe_swiglu_quantize(const float* gate_up, int64_t f, int64_t n_rows, void* packed, size_t packed_bytes,
+                                  void* stream) {
+  if (f <= 0 || f % 256 || f > (1 << 24) || n_rows < 0) return kInvalidProblem;
+  if (n_rows == 0) return kOk;
+  if (!gate_up || !packed) return kInvalidProblem;
+  if (packed_bytes < act_packed_bytes(kQ4K, n_rows, f)) return kWorkspace;
+  if (!aligned(gate_up, 16) || !aligned(packed, 16)) return kMisaligned;
+  const ActPlanes a = act_planes(packed, kQ4K, n_rows, f);
+  const int64_t nb = n_rows * (f / 256);
+  const cudaError_t e = launch(moe_swiglu_quantize_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
+                               gate_up, (int)f, nb, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+extern "C++" {
+namespace {
+template <class Fmt>
+cudaError_t launch_moe(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  auto kern = moe_decode_kernel<Fmt>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    DeviceInfo* di;
+    if (!device_info(&di)) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  return launch(kern, grid, dim3(kDecodeThreads), smem, stream, p);
+}
+}  // namespace
+}  // extern "C++"
+
+int32_t fuelq_moe_qmatmul(int32_t ggml_type, int32_t n_experts, int64_t n, int64_t k, const void* w, const void* packed_act,
+                          int64_t n_rows, const int32_t* expert_offsets, const int32_t* out_rows, float* y, void* stream) {
+  if (ggml_type != kQ4K && ggml_type != kQ6K) return kNotSupported;
+  if (n_experts <= 0 || n_experts > 65535 || n <= 0 || n > (1 << 24) || k <= 0 || k % 256 || k > (1 << 24) || n_rows < 0)
+    return kInvalidProblem;
+  if (n_rows == 0) return kOk;
+  if (!w || !packed_act || !expert_offsets || !y) return kInvalidProblem;
+  if (!aligned(w, 16) || !aligned(packed_act, 16)) return kMisaligned;
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  MoeParams p;
+  p.row_bytes = (int)(k / 256 * block_bytes(ggml_type));
+  if (p.row_bytes % 16) return kNotSupported;  // rows are bulk-copied whole: Q6_K needs k a multiple of 2048
+  p.w = (const uint8_t*)w;
+  p.act = act_planes(const_cast<void*>(packed_act), ggml_type, n_rows, k);
+  p.offsets = (const int*)expert_offsets;
+  p.out_rows = (const int*)out_rows;
+  p.y = y;
+  p.n = (int)n;
+  p.k = (int)k;
+  p.expert_bytes = n * (int64_t)p.row_bytes;
+  p.units_per_row = (int)(k / 256) * (ggml_type == kQ4K ? Q4KDecode::kUnitsPerBlock : Q6KDecode::kUnitsPerBlock);
+  const size_t header = align_up(sizeof(MoeSmemHeader), 128);
+  // shared memory per thread block (two per SM): activation rows of one pass, then the ring of weight stages
+  int act_rows = (int)((40 * 1024) / (k + k / 8 + k / 64 + 64)) / kMoeMT * kMoeMT;
+  if (act_rows > 32) act_rows = 32;
+  if (act_rows < kMoeMT) return kNotSupported;
+  const size_t act_bytes = align_up(act_packed_bytes(kQ4K, act_rows, k), 128);
+  const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
+  if (header + act_bytes + 8192 > per_cta) return kNotSupported;
+  const size_t budget = per_cta - header - act_bytes;
+  int R = (24 * 1024) / p.row_bytes;
+  if (R > 64) R = 64;
+  if (R >= kDecodeConsumerWarps) R = R / kDecodeConsumerWarps * kDecodeConsumerWarps;
+  if (R < 1) return kNotSupported;
+  p.rows_per_stage = R;
+  p.stage_stride = (int)align_up((size_t)R * p.row_bytes, 128);
+  int stages = (int)(budget / p.stage_stride);
+  if (stages < 2) return kNotSupported;
+  if (stages > kDecodeMaxStages) stages = kDecodeMaxStages;
+  p.num_stages = stages;
+  p.act_rows = act_rows;
+  p.act_smem_off = (int)(header + (size_t)stages * p.stage_stride);
+  // enough thread blocks per expert to fill the GPU a few times over, never more than one per stage of rows
+  int per_expert = (4 * di->sm_count + n_experts - 1) / n_experts;
+  const int max_per = (int)((n + R - 1) / R);
+  if (per_expert > max_per) per_expert = max_per;
+  if (per_expert < 1) per_expert = 1;
+  const size_t smem = header + (size_t)stages * p.stage_stride + act_bytes;
+  const dim3 grid((unsigned)per_expert, (unsigned)n_experts);
+  const cudaError_t e = ggml_type == kQ4K ? launch_moe<Q4KDecode>(p, grid, smem, (cudaStream_t)stream)
+                                          : launch_moe<Q6KDecode>(p, grid, smem, (cudaStream_t)stream);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_moe_combine(const float* y_pairs, const int32_t* topk_ids, const float* topk_weights, int64_t n_tokens,
+                          int32_t top_k, int64_t n, float* out, void* stream) {
+  if (n_tokens < 0 || n_tokens > (1 << 24) || top_k <= 0 || top_k > kMoeMaxTopK || n <= 0 || n > (1 << 24))
+    return kInvalidProblem;
+  if (n_tokens == 0) return kOk;
+  if (!y_pairs || !topk_ids || !topk_weights || !out) return kInvalidProblem;
+  const cudaError_t e = launch(moe_combine_kernel, dim3((unsigned)n_tokens), dim3(256), 0, (cudaStream_t)stream, y_pairs,
+                               (const int*)topk_ids, topk_weights, (int)top_k, (int)n, out);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 

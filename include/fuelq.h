@@ -188,6 +188,36 @@ int32_t fuelq_swiglu_q8k(const float* gate, const float* up, int64_t n, void* pa
 int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* vcache, const int32_t* pos, int32_t n_heads,
                               int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
                               size_t workspace_bytes, void* packed, size_t packed_bytes, void* stream);
+/* ---- Mixture-of-experts block with quantized experts (the grouped / indexed quantized mat-vec).
+ * Replaces the slot the reference leaves empty (indexed_moe_forward, fuel-backend-contract/src/quantized.rs:29-103;
+ * the CUDA implementation was retired and its grouped kernel is only named: fuel-cuda-backend/src/quantized.rs:292-304)
+ * and follows the reference's sparse MoE forward for everything around it (fuel-core/src/lazy_nn/moe.rs:92-127,
+ * 296-348): K rounds of first-maximum argmax with the picked logit lowered by 1e30, softmax over the picked logits,
+ * experts visited in ascending id, rows inside an expert in ascending token order, a token's result accumulated as
+ * ((0 + w_a*y_a) + w_b*y_b) + ... over its experts in ascending id. A "pair" is token * top_k + slot.
+ * All calls are stream-ordered, allocate nothing and read the routing on the device (no host round trip). */
+/* logits [n_tokens][n_experts] -> topk_ids, topk_weights [n_tokens][top_k]; n_experts <= 1024, top_k <= 16 */
+int32_t fuelq_moe_route(const float* logits, int64_t n_tokens, int32_t n_experts, int32_t top_k, int32_t* topk_ids,
+                        float* topk_weights, void* stream);
+/* pairs sorted by expert (ascending pair id inside an expert) -> sorted_ids [n_pairs], expert_offsets [n_experts + 1] */
+int32_t fuelq_moe_bucket(const int32_t* topk_ids, int64_t n_pairs, int32_t n_experts, int32_t* sorted_ids,
+                         int32_t* expert_offsets, void* stream);
+/* sorted row i <- Q8_K( x[row_ids[i] / divisor] ), packed as fuelq_quantize_act_packed lays out n_rows rows;
+ * divisor = top_k gathers a token's row for each of its pairs, divisor = 1 gathers per pair */
+int32_t fuelq_moe_quantize_rows(const float* x, int64_t k, const int32_t* row_ids, int32_t divisor, int64_t n_rows,
+                                void* packed, size_t packed_bytes, void* stream);
+/* rows [gate | up] of width 2f -> Q8_K( silu(gate) * up ), same packed layout (f a multiple of 256) */
+int32_t fuelq_moe_swiglu_quantize(const float* gate_up, int64_t f, int64_t n_rows, void* packed, size_t packed_bytes,
+                                  void* stream);
+/* y[out_rows[i] or i][0..n) = W[e] . act row i for every sorted row i of every expert e (rows
+ * expert_offsets[e] .. expert_offsets[e+1]); w is [n_experts][n][k] GGUF blocks, Q4_K or Q6_K, each row a multiple of
+ * 16 bytes. An expert's matrix is streamed once, and not at all when it has no rows. */
+int32_t fuelq_moe_qmatmul(int32_t ggml_type, int32_t n_experts, int64_t n, int64_t k, const void* w, const void* packed_act,
+                          int64_t n_rows, const int32_t* expert_offsets, const int32_t* out_rows, float* y, void* stream);
+/* out[t] = sum over the token's pairs, in ascending expert id, of topk_weights[pair] * y_pairs[pair] */
+int32_t fuelq_moe_combine(const float* y_pairs, const int32_t* topk_ids, const float* topk_weights, int64_t n_tokens,
+                          int32_t top_k, int64_t n, float* out, void* stream);
+
 /* ---- Tensor-parallel decode step over peer-mapped memory.
  * The reference has no multi-GPU form of this path (its QMatMul runs on one device,
  * fuel-core/src/quantized/mod.rs:854-868); these entry points are how the 7B decode of the benchmark is
