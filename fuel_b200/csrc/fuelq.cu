@@ -12,6 +12,7 @@
 #include "fq_common.cuh"
 #include "llama_glue.cuh"
 #include "moe.cuh"
+#include "moe_mma.cuh"
 #include "prefill.cuh"
 #include "quantize_act.cuh"
 #include "quantize_weights.cuh"
@@ -31,6 +32,7 @@ struct Options {
   int64_t dbg_depth = 0;
   int64_t dbg_pre = -1;
   int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
+  int64_t moe_kernel = 0;     // development switch: 1 = grouped mat-vec on the dp4a kernel even where the tensor-core form fits
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
 };
 Options g_opt;
@@ -535,6 +537,7 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 104: g_opt.dbg_smem_kb = value; return kOk;
     case 105: g_opt.dbg_depth = value; return kOk;
     case 106: g_opt.dbg_pre = value; return kOk;
+    case 107: g_opt.moe_kernel = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     default: return kInvalidProblem;
@@ -900,6 +903,62 @@ int32_t fuelq_moe_swiglu_quantize(const float* gate_up, int64_t f, int64_t n_row
 
 extern "C++" {
 namespace {
+// Tensor-core form (Q4_K): kNotSupported when the shared-memory plan does not fit, so the caller can fall back.
+int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const ActPlanes& act, const int* offsets,
+                     int fixed_rows, const int* out_rows, float* y, cudaStream_t stream) {
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  MmaParams p;
+  p.row_bytes = (int)(k / 256 * Q4KL::kBytes);
+  const size_t header = align_up(sizeof(MmaSmemHeader), 128);
+  const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
+  const size_t act_bytes = mma_act_bytes((int)k), part_bytes = kDecodeConsumerWarps * 128 * sizeof(float);
+  if (header + act_bytes + part_bytes >= per_cta) return kNotSupported;
+  const size_t ring = per_cta - header - act_bytes - part_bytes;
+  int R = 0;
+  size_t stride = 0;
+  for (int cand = 32; cand >= 8; cand >>= 1) {
+    stride = align_up((size_t)cand * (p.row_bytes + 16), 128);
+    if (2 * stride <= ring) {
+      R = cand;
+      break;
+    }
+  }
+  if (!R) return kNotSupported;
+  int stages = (int)(ring / stride);
+  if (stages > 4) stages = 4;
+  p.w = (const uint8_t*)w;
+  p.act = act;
+  p.offsets = offsets;
+  p.fixed_rows = fixed_rows;
+  p.out_rows = out_rows;
+  p.y = y;
+  p.n = (int)n;
+  p.k = (int)k;
+  p.group_bytes = n * (int64_t)p.row_bytes;
+  p.rows_per_stage = R;
+  p.num_stages = stages;
+  p.stage_stride = (int)stride;
+  p.act_off = (int)(header + (size_t)stages * stride);
+  p.part_off = (int)(p.act_off + act_bytes);
+  int per_group = (4 * di->sm_count + n_groups - 1) / n_groups;
+  const int max_per = (int)((n + R - 1) / R);
+  if (per_group > max_per) per_group = max_per;
+  if (per_group < 1) per_group = 1;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return kLaunchFailure;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(mma_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin) != cudaSuccess)
+      return kLaunchFailure;
+    attr_set[dev] = true;
+  }
+  const size_t smem = header + (size_t)stages * stride + act_bytes + part_bytes;
+  const cudaError_t e = launch(mma_q4k_kernel, dim3((unsigned)per_group, (unsigned)n_groups), dim3(kDecodeThreads), smem, stream, p);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
 template <class Fmt>
 cudaError_t launch_moe(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
   static bool attr_set[64] = {};
@@ -927,6 +986,11 @@ int32_t fuelq_moe_qmatmul(int32_t ggml_type, int32_t n_experts, int64_t n, int64
   if (n_rows == 0) return kOk;
   if (!w || !packed_act || !expert_offsets || !y) return kInvalidProblem;
   if (!aligned(w, 16) || !aligned(packed_act, 16)) return kMisaligned;
+  if (ggml_type == kQ4K && g_opt.moe_kernel != 1) {
+    const int32_t sm = moe_mma_impl(n_experts, n, k, w, act_planes(const_cast<void*>(packed_act), ggml_type, n_rows, k),
+                                    (const int*)expert_offsets, 0, (const int*)out_rows, y, (cudaStream_t)stream);
+    if (sm != kNotSupported) return sm;
+  }
   DeviceInfo* di;
   if (!device_info(&di)) return kLaunchFailure;
   MoeParams p;

@@ -83,3 +83,37 @@ def test_moe_grouped_matvec_equals_plain_matvec_per_expert():
             assert (y[r0:r0 + m] - ref).abs().max().item() <= 2e-6 * ref.abs().max().item()
         r0 += m
     assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize("E,n,k,rows", [(6, 384, 1024, [0, 5, 1, 16, 0, 9]), (3, 1536, 2048, [33, 0, 2]), (2, 100, 768, [7, 20]),
+                                        (1, 37, 4096, [13])])
+def test_tensor_core_grouped_kernel_matches_dp4a_grouped_kernel(E, n, k, rows):
+    """Q4_K groups run on the integer tensor-core kernel; the dp4a kernel (development switch 107) computes the same
+    integer dots, so the two agree up to f32 summation order."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    L = _lib.lib
+    g = np.random.Generator(np.random.PCG64(5))
+    w = ops.quantize_weights(T.Q4K, torch.from_numpy(g.standard_normal((E * n, k), dtype=np.float32) * np.float32(0.02)).cuda())
+    R = sum(rows)
+    x = torch.from_numpy(g.standard_normal((R, k), dtype=np.float32)).cuda()
+    off = torch.tensor(np.concatenate([[0], np.cumsum(rows)]), dtype=torch.int32, device="cuda")
+    perm = torch.from_numpy(g.permutation(R).astype(np.int32)).cuda()
+    ident = torch.arange(R, dtype=torch.int32, device="cuda")
+    packed = torch.zeros(L.fuelq_act_packed_bytes(int(T.Q4K), R, k), dtype=torch.uint8, device="cuda")
+    _lib.check(L.fuelq_moe_quantize_rows(x.data_ptr(), k, ident.data_ptr(), 1, R, packed.data_ptr(), packed.numel(), None), "q")
+    ys = []
+    for sw in (0, 1):
+        y = torch.full((R, n), float("nan"), device="cuda")
+        try:
+            L.fuelq_set_option(107, sw)
+            _lib.check(L.fuelq_moe_qmatmul(int(T.Q4K), E, n, k, w.data_ptr(), packed.data_ptr(), R, off.data_ptr(),
+                                           perm.data_ptr(), y.data_ptr(), None), "moe")
+        finally:
+            L.fuelq_set_option(107, 0)
+        torch.cuda.synchronize()
+        ys.append(y)
+    assert not torch.isnan(ys[0]).any() and not torch.isnan(ys[1]).any()
+    assert (ys[0] - ys[1]).abs().max().item() <= 2e-6 * ys[1].abs().max().item()
+    assert ops.device_error() == 0
