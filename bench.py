@@ -151,6 +151,87 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _time_graph(torch, stream, fn, reps):
+    """Average microseconds per call of fn(), replayed as a CUDA graph on `stream` (events on that stream)."""
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def run_side_workload(args):
+    """BASELINE configs 2 (batch sweep), 3 (prefill GEMM) and 5 (MoE block) on one GPU: seeded synthetic tensors of the
+    stated shapes, distinct weight copies cycling through more than L2, CUDA-graph replay, one JSON line per case."""
+    import torch
+
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    from fuel_b200.moe import QMoeBlock
+    L = _lib.lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0)
+    st = torch.cuda.Stream(dev)
+    peak, peak_kind = _peaks()
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+
+    def matmul_case(t, name, n, k, m, copies, reps):
+        ws = [ops.quantize_weights(t, torch.randn(n, k, generator=gen, device=dev) * 0.02) for _ in range(copies)]
+        x = torch.randn(m, k, generator=gen, device=dev)
+        y = torch.empty(m, n, device=dev)
+        wsb = L.fuelq_qmatmul_workspace_bytes(int(t), m, n, k)
+        scratch = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+
+        def p():
+            for w in ws:
+                _lib.check(L.fuelq_qmatmul(int(t), m, n, k, w.data_ptr(), x.data_ptr(), y.data_ptr(), scratch.data_ptr(), wsb,
+                                           st.cuda_stream), "fuelq_qmatmul")
+        us = _time_graph(torch, st, p, reps) / copies
+        algo = ws[0].numel() + 4 * m * k + 4 * m * n
+        return {"workload": f"{name}_k{k}_n{n}_m{m}", "us": us, "GB/s": algo / us / 1e3, "TFLOP/s": 2 * m * n * k / us / 1e6,
+                "hbm_frac": algo / us / 1e3 / peak, "peak_kind": f"of {peak_kind}", "weight_copies": copies}
+
+    if args.workload == "sweep":
+        for t, name in ((T.Q4K, "Q4_K"), (T.Q6K, "Q6_K"), (T.Q8_0, "Q8_0")):
+            for n, k in ((11008, 4096), (4096, 11008)):
+                for m in (1, 2, 4, 8, 16, 32, 64, 128):
+                    print(json.dumps(matmul_case(t, name, n, k, m, 12, 20)), flush=True)
+    elif args.workload == "prefill":
+        print(json.dumps(matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10)), flush=True)
+    else:
+        E, H, F, K, N, copies = 128, 2048, 768, 8, 256, 4
+        blocks = []
+        for _ in range(copies):
+            bgu = ops.quantize_weights(T.Q4K, torch.randn(E * 2 * F, H, generator=gen, device=dev) * 0.02)
+            bd = ops.quantize_weights(T.Q4K, torch.randn(E * H, F, generator=gen, device=dev) * 0.02)
+            blocks.append(QMoeBlock(E, H, F, K, bgu, bd, max_tokens=N))
+        x = torch.randn(N, H, generator=gen, device=dev)
+        logits = torch.randn(N, E, generator=gen, device=dev)
+        outs = [torch.empty(N, H, device=dev) for _ in range(copies)]
+
+        def p():
+            for b, o in zip(blocks, outs):
+                b.forward(x, logits, o)
+        us = _time_graph(torch, st, p, 20) / copies
+        wbytes = E * 3 * F * H // 256 * 144
+        print(json.dumps({"workload": f"moe_block_e{E}_h{H}_f{F}_top{K}_tokens{N}_q4k", "us": us, "GB/s": wbytes / us / 1e3,
+                          "tokens_per_s": N / us * 1e6, "hbm_frac": wbytes / us / 1e3 / peak, "peak_kind": f"of {peak_kind}",
+                          "weight_bytes": wbytes, "weight_copies": copies, "launches_per_block": 9}), flush=True)
+    assert ops.device_error() == 0, "a kernel recorded an expired bounded wait"
+
+
 def run_decode_7b(torch, dist, device, rank, world):
     """LLaMA-2-7B-architecture greedy decode, batch 1 (Q4_K_M-style mix, random-init weights, f32 KV cache):
     a 512-token seeded prompt fed one token at a time, then 128 new tokens timed with CUDA events on a replayed
@@ -215,12 +296,17 @@ def main():
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step (profiling runs use fewer)")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-architecture decode that is reported beside the metric")
+    ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe"],
+                    help="decode: the headline line (default). sweep / prefill / moe: BASELINE configs 2 / 3 / 5 on one GPU, "
+                         "one JSON line per case")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     LAYERS = args.layers
     WORKLOAD = f"q4k_qmatmul_m{M_ROWS}_k{K_IN}_n{N_OUT}_x{LAYERS}_distinct_matrices"
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload != "decode":
+        return run_side_workload(args)
 
     import ctypes
 

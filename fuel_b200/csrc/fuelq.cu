@@ -408,11 +408,72 @@ int32_t prefetch_impl(const void* w, int64_t bytes, cudaStream_t stream) {
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
+// Tensor-core form (Q4_K): kNotSupported when the shared-memory plan does not fit, so the caller can fall back.
+int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const ActPlanes& act, const int* offsets,
+                     int fixed_rows, const int* out_rows, float* y, cudaStream_t stream) {
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  MmaParams p;
+  p.row_bytes = (int)(k / 256 * Q4KL::kBytes);
+  const size_t header = align_up(sizeof(MmaSmemHeader), 128);
+  const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
+  const size_t act_bytes = mma_act_bytes((int)k), part_bytes = kDecodeConsumerWarps * 128 * sizeof(float);
+  if (header + act_bytes + part_bytes >= per_cta) return kNotSupported;
+  const size_t ring = per_cta - header - act_bytes - part_bytes;
+  int R = 0;
+  size_t stride = 0;
+  for (int cand = 32; cand >= 8; cand >>= 1) {
+    stride = align_up((size_t)cand * (p.row_bytes + 16), 128);
+    if (2 * stride <= ring) {
+      R = cand;
+      break;
+    }
+  }
+  if (!R) return kNotSupported;
+  int stages = (int)(ring / stride);
+  if (stages > 4) stages = 4;
+  p.w = (const uint8_t*)w;
+  p.act = act;
+  p.offsets = offsets;
+  p.fixed_rows = fixed_rows;
+  p.out_rows = out_rows;
+  p.y = y;
+  p.n = (int)n;
+  p.k = (int)k;
+  p.group_bytes = n * (int64_t)p.row_bytes;
+  p.rows_per_stage = R;
+  p.num_stages = stages;
+  p.stage_stride = (int)stride;
+  p.act_off = (int)(header + (size_t)stages * stride);
+  p.part_off = (int)(p.act_off + act_bytes);
+  int per_group = (4 * di->sm_count + n_groups - 1) / n_groups;
+  const int max_per = (int)((n + R - 1) / R);
+  if (per_group > max_per) per_group = max_per;
+  if (per_group < 1) per_group = 1;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return kLaunchFailure;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(mma_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin) != cudaSuccess)
+      return kLaunchFailure;
+    attr_set[dev] = true;
+  }
+  const size_t smem = header + (size_t)stages * stride + act_bytes + part_bytes;
+  const cudaError_t e = launch(mma_q4k_kernel, dim3((unsigned)per_group, (unsigned)n_groups), dim3(kDecodeThreads), smem, stream, p);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
 // Any m_total through the decode kernels: activation rows are taken kDecodeMaxM at a time, each
 // chunk streaming the weights once. Exactly the integer arithmetic of the small-M path.
 int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
                        cudaStream_t stream) {
   const ActPlanes all = act_planes(packed_act, type, m_total, k);
+  if (type == kQ4K && m_total > 2 && g_opt.decode_kernel == 0 && g_opt.moe_kernel != 1 && n <= (1 << 24)) {
+    // a few rows of Q4_K: one pass over the weights on the integer tensor cores (16 rows per pass)
+    const int32_t st = moe_mma_impl(1, n, k, w, all, nullptr, (int)m_total, nullptr, y, stream);
+    if (st != kNotSupported) return st;
+  }
   const int abe = block_elems(act_type_for(type));
   // Two rows at a time through the register-resident kernel beats sixteen at a time through the generic
   // one when the matrix fits in L2 (every pass after the first streams from there).
@@ -432,9 +493,21 @@ int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const vo
 }
 
 // ---- tensor-core path (prefill.cuh)
+// whether the integer tensor-core kernel (moe_mma.cuh) has a shared-memory plan for this k
+bool mma_plan_fits(int64_t k) {
+  DeviceInfo* di;
+  if (k % 256 || k > (1 << 20) || !device_info(&di)) return false;
+  const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
+  const size_t fixed = align_up(sizeof(MmaSmemHeader), 128) + mma_act_bytes((int)k) + kDecodeConsumerWarps * 128 * sizeof(float);
+  return fixed + 2 * align_up((size_t)8 * (k / 256 * Q4KL::kBytes + 16), 128) <= per_cta;
+}
+
 bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   (void)n;
-  return (type == kQ4K || type == kQ6K || type == kQ8_0) && m > g_opt.decode_max_m && k % kPfTileK == 0 && k <= (1 << 20);
+  int64_t max_m = g_opt.decode_max_m;
+  // Q4_K rows go through the integer tensor-core kernel 16 at a time; two such passes still beat the bf16 GEMM
+  if (type == kQ4K && max_m == 16 && g_opt.decode_kernel == 0 && g_opt.moe_kernel != 1 && mma_plan_fits(k)) max_m = 32;
+  return (type == kQ4K || type == kQ6K || type == kQ8_0) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }
 size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * 2, 256); }
 
@@ -903,62 +976,6 @@ int32_t fuelq_moe_swiglu_quantize(const float* gate_up, int64_t f, int64_t n_row
 
 extern "C++" {
 namespace {
-// Tensor-core form (Q4_K): kNotSupported when the shared-memory plan does not fit, so the caller can fall back.
-int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const ActPlanes& act, const int* offsets,
-                     int fixed_rows, const int* out_rows, float* y, cudaStream_t stream) {
-  DeviceInfo* di;
-  if (!device_info(&di)) return kLaunchFailure;
-  MmaParams p;
-  p.row_bytes = (int)(k / 256 * Q4KL::kBytes);
-  const size_t header = align_up(sizeof(MmaSmemHeader), 128);
-  const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
-  const size_t act_bytes = mma_act_bytes((int)k), part_bytes = kDecodeConsumerWarps * 128 * sizeof(float);
-  if (header + act_bytes + part_bytes >= per_cta) return kNotSupported;
-  const size_t ring = per_cta - header - act_bytes - part_bytes;
-  int R = 0;
-  size_t stride = 0;
-  for (int cand = 32; cand >= 8; cand >>= 1) {
-    stride = align_up((size_t)cand * (p.row_bytes + 16), 128);
-    if (2 * stride <= ring) {
-      R = cand;
-      break;
-    }
-  }
-  if (!R) return kNotSupported;
-  int stages = (int)(ring / stride);
-  if (stages > 4) stages = 4;
-  p.w = (const uint8_t*)w;
-  p.act = act;
-  p.offsets = offsets;
-  p.fixed_rows = fixed_rows;
-  p.out_rows = out_rows;
-  p.y = y;
-  p.n = (int)n;
-  p.k = (int)k;
-  p.group_bytes = n * (int64_t)p.row_bytes;
-  p.rows_per_stage = R;
-  p.num_stages = stages;
-  p.stage_stride = (int)stride;
-  p.act_off = (int)(header + (size_t)stages * stride);
-  p.part_off = (int)(p.act_off + act_bytes);
-  int per_group = (4 * di->sm_count + n_groups - 1) / n_groups;
-  const int max_per = (int)((n + R - 1) / R);
-  if (per_group > max_per) per_group = max_per;
-  if (per_group < 1) per_group = 1;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return kLaunchFailure;
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(mma_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin) != cudaSuccess)
-      return kLaunchFailure;
-    attr_set[dev] = true;
-  }
-  const size_t smem = header + (size_t)stages * stride + act_bytes + part_bytes;
-  const cudaError_t e = launch(mma_q4k_kernel, dim3((unsigned)per_group, (unsigned)n_groups), dim3(kDecodeThreads), smem, stream, p);
-  return e == cudaSuccess ? kOk : kLaunchFailure;
-}
-
 template <class Fmt>
 cudaError_t launch_moe(const MoeParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
   static bool attr_set[64] = {};

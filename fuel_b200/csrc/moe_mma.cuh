@@ -18,6 +18,7 @@
 // consecutive ranges of the 256-blocks along k; their partial sums meet in shared memory and are added in
 // a fixed order. Every wait is bounded.
 #pragma once
+#include "decode_regs.cuh"
 #include "fq_common.cuh"
 #include "moe.cuh"
 
@@ -44,6 +45,14 @@ struct MmaSmemHeader {
   uint64_t empty[kDecodeMaxStages];
 };
 
+// four 8x8 (16-byte-row) matrices: exactly the A fragment of m16n8k32 for 8-bit operands when the lanes
+// address rows 0-7 / 8-15 at byte columns 0-15 / 16-31 of a 16 x 32-byte tile
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
 __device__ __forceinline__ void mma_s8_16832(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -53,7 +62,7 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], const uint32_t (&a)[4]
 
 __host__ __device__ inline size_t mma_act_bytes(int k) {
   // quants (padded rows), 32-element sums (int16), block scales (f32)
-  return align_up((size_t)kMmaActRows * (k + 16), 128) + align_up((size_t)kMmaActRows * (k / 32) * 2, 128) +
+  return align_up((size_t)kMmaActRows * (k + 16), 128) + align_up((size_t)kMmaActRows * ((k / 32) * 2 + 16), 128) +
          align_up((size_t)kMmaActRows * (k / 256) * 4, 128);
 }
 
@@ -120,7 +129,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
   // ---------------- consumers
   uint8_t* act_qs = smem_raw + p.act_off;
   int16_t* act_bs = reinterpret_cast<int16_t*>(act_qs + align_up((size_t)kMmaActRows * astride, 128));
-  float* act_d = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(act_bs) + align_up((size_t)kMmaActRows * (p.k >> 5) * 2, 128));
+  const int bstride = (p.k >> 5) * 2 + 16;  // bytes per row of 32-sums (padded: rows fall in different banks)
+  float* act_d = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(act_bs) + align_up((size_t)kMmaActRows * bstride, 128));
   float* part = reinterpret_cast<float*>(smem_raw + p.part_off);  // [tile][k-part][128]
   const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
   const int nblk = p.k >> 8;
@@ -152,7 +162,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
           const int16_t* bs = p.act.bsums + (size_t)(a0 + r) * (p.k >> 4) + 2 * c;
           v = (int)bs[0] + (int)bs[1];
         }
-        act_bs[i] = (int16_t)v;
+        *reinterpret_cast<int16_t*>(reinterpret_cast<uint8_t*>(act_bs) + (size_t)r * bstride + 2 * c) = (int16_t)v;
       }
       for (int i = t; i < kMmaActRows * nblk; i += nt) {
         const int r = i / nblk, c = i - r * nblk;
@@ -169,54 +179,53 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
       }
       const int row0 = r_begin + it * R;
       const int rows_here = ((row0 + R < r_end) ? row0 + R : r_end) - row0;
-      const uint8_t* sbase = stages + (size_t)s * p.stage_stride + (size_t)(tile * 8) * wstride;
       float facc[4] = {0.f, 0.f, 0.f, 0.f};  // (row gid, col 2tig) (gid, 2tig+1) (gid+8, 2tig) (gid+8, 2tig+1)
       if (tile * 8 < rows_here) {
-        const uint8_t* wrow_b = sbase + (size_t)gid * wstride;          // B fragments: weight row gid
-        const uint8_t* wrow_c0 = sbase + (size_t)(2 * tig) * wstride;   // accumulator columns: weight rows 2tig, 2tig+1
-        const uint8_t* wrow_c1 = wrow_c0 + wstride;
-        const uint8_t* aq_lo = act_qs + (size_t)gid * astride + 4 * tig;
-        const uint8_t* aq_hi = aq_lo + (size_t)8 * astride;
+        // 32-bit shared addresses, so every load below is one ld.shared with an immediate offset
+        const uint32_t tile_s = smem_u32(stages) + (uint32_t)s * p.stage_stride + (uint32_t)(tile * 8) * wstride;
+        const uint32_t wb_s = tile_s + (uint32_t)gid * wstride + Q4KL::kOffQs + 4 * tig;  // B fragments: weight row gid
+        const uint32_t wc_s = tile_s + (uint32_t)(2 * tig) * wstride;                      // accumulator columns: rows 2tig, 2tig+1
+        // A fragments by ldmatrix: lane l addresses row (l & 7) + 8 * ((l >> 3) & 1), byte column 16 * (l >> 4)
+        const uint32_t aq_s = smem_u32(act_qs) + (uint32_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * astride + 16 * (lane >> 4);
+        const uint32_t bs_s = smem_u32(act_bs) + (uint32_t)gid * bstride;
+        const uint32_t d_s = smem_u32(act_d) + (uint32_t)gid * nblk * 4;
         for (int b = b_begin; b < b_end; ++b) {
-          const uint4 h0 = *reinterpret_cast<const uint4*>(wrow_c0 + b * Q4KL::kBytes);
-          const uint4 h1 = *reinterpret_cast<const uint4*>(wrow_c1 + b * Q4KL::kBytes);
+          const uint4 h0 = lds128(wc_s + b * Q4KL::kBytes);
+          const uint4 h1 = lds128(wc_s + wstride + b * Q4KL::kBytes);
           // eight 6-bit scales / mins per row as bytes of two words (get_scale_min_k4, fuel-quantized/src/utils.rs:50-60)
           const uint32_t sc0[2] = {h0.y & 0x3f3f3f3fu, (h0.w & 0x0f0f0f0fu) | (((h0.y >> 6) & 0x03030303u) << 4)};
           const uint32_t mn0[2] = {h0.z & 0x3f3f3f3fu, ((h0.w >> 4) & 0x0f0f0f0fu) | (((h0.z >> 6) & 0x03030303u) << 4)};
           const uint32_t sc1[2] = {h1.y & 0x3f3f3f3fu, (h1.w & 0x0f0f0f0fu) | (((h1.y >> 6) & 0x03030303u) << 4)};
           const uint32_t mn1[2] = {h1.z & 0x3f3f3f3fu, ((h1.w >> 4) & 0x0f0f0f0fu) | (((h1.z >> 6) & 0x03030303u) << 4)};
-          const uint4 bl = *reinterpret_cast<const uint4*>(act_bs + (size_t)gid * (p.k >> 5) + b * 8);        // 8 sums, row gid
-          const uint4 bh = *reinterpret_cast<const uint4*>(act_bs + (size_t)(gid + 8) * (p.k >> 5) + b * 8);  // row gid + 8
-          const uint32_t blw[4] = {bl.x, bl.y, bl.z, bl.w}, bhw[4] = {bh.x, bh.y, bh.z, bh.w};
-          int S4[4] = {0, 0, 0, 0}, T4[4] = {0, 0, 0, 0};
-          const uint8_t* qs = wrow_b + b * Q4KL::kBytes + Q4KL::kOffQs + 4 * tig;
+          const uint4 bl = lds128(bs_s + b * 16);                 // eight 32-sums of activation row gid
+          const uint4 bh = lds128(bs_s + 8 * bstride + b * 16);   // ... of row gid + 8
+          int S4[4] = {0, 0, 0, 0};
 #pragma unroll
           for (int gq = 0; gq < 4; ++gq) {  // 64 elements: low nibbles = sub-block 2gq, high nibbles = 2gq + 1
-            const uint32_t q0 = *reinterpret_cast<const uint32_t*>(qs + 32 * gq);
-            const uint32_t q1 = *reinterpret_cast<const uint32_t*>(qs + 32 * gq + 16);
+            const uint32_t q0 = lds32(wb_s + b * Q4KL::kBytes + 32 * gq);
+            const uint32_t q1 = lds32(wb_s + b * Q4KL::kBytes + 32 * gq + 16);
 #pragma unroll
             for (int sb = 0; sb < 2; ++sb) {
               const int j = 2 * gq + sb;
               const uint32_t b0 = (q0 >> (4 * sb)) & 0x0f0f0f0fu, b1 = (q1 >> (4 * sb)) & 0x0f0f0f0fu;
               uint32_t a[4];
-              a[0] = *reinterpret_cast<const uint32_t*>(aq_lo + b * 256 + 32 * j);
-              a[1] = *reinterpret_cast<const uint32_t*>(aq_hi + b * 256 + 32 * j);
-              a[2] = *reinterpret_cast<const uint32_t*>(aq_lo + b * 256 + 32 * j + 16);
-              a[3] = *reinterpret_cast<const uint32_t*>(aq_hi + b * 256 + 32 * j + 16);
+              ldmatrix_x4(a, aq_s + b * 256 + 32 * j);
               int c[4] = {0, 0, 0, 0};
               mma_s8_16832(c, a, b0, b1);
               const int sh = 8 * (j & 3);
               const int s0 = (int)((sc0[j >> 2] >> sh) & 0xff), s1 = (int)((sc1[j >> 2] >> sh) & 0xff);
-              const int m0 = (int)((mn0[j >> 2] >> sh) & 0xff), m1 = (int)((mn1[j >> 2] >> sh) & 0xff);
               S4[0] += c[0] * s0, S4[1] += c[1] * s1, S4[2] += c[2] * s0, S4[3] += c[3] * s1;
-              const int bsl = (int)(short)((blw[j >> 1] >> (16 * (j & 1))) & 0xffff);
-              const int bsh = (int)(short)((bhw[j >> 1] >> (16 * (j & 1))) & 0xffff);
-              T4[0] += m0 * bsl, T4[1] += m1 * bsl, T4[2] += m0 * bsh, T4[3] += m1 * bsh;
             }
           }
+          // sum_j min_j * bsum_j: two sub-blocks per dp2a (16-bit sums x 8-bit mins)
+          int T4[4];
+          T4[0] = __dp2a_hi((int)bl.w, (int)mn0[1], __dp2a_lo((int)bl.z, (int)mn0[1], __dp2a_hi((int)bl.y, (int)mn0[0], __dp2a_lo((int)bl.x, (int)mn0[0], 0))));
+          T4[1] = __dp2a_hi((int)bl.w, (int)mn1[1], __dp2a_lo((int)bl.z, (int)mn1[1], __dp2a_hi((int)bl.y, (int)mn1[0], __dp2a_lo((int)bl.x, (int)mn1[0], 0))));
+          T4[2] = __dp2a_hi((int)bh.w, (int)mn0[1], __dp2a_lo((int)bh.z, (int)mn0[1], __dp2a_hi((int)bh.y, (int)mn0[0], __dp2a_lo((int)bh.x, (int)mn0[0], 0))));
+          T4[3] = __dp2a_hi((int)bh.w, (int)mn1[1], __dp2a_lo((int)bh.z, (int)mn1[1], __dp2a_hi((int)bh.y, (int)mn1[0], __dp2a_lo((int)bh.x, (int)mn1[0], 0))));
           const float d0 = h2f_bits(h0.x & 0xffffu), dm0 = h2f_bits(h0.x >> 16);
           const float d1 = h2f_bits(h1.x & 0xffffu), dm1 = h2f_bits(h1.x >> 16);
-          const float yl = act_d[gid * nblk + b], yh = act_d[(gid + 8) * nblk + b];
+          const float yl = __uint_as_float(lds32(d_s + 4 * b)), yh = __uint_as_float(lds32(d_s + 8 * nblk * 4 + 4 * b));
           facc[0] += (d0 * yl) * (float)S4[0] - (dm0 * yl) * (float)T4[0];
           facc[1] += (d1 * yl) * (float)S4[1] - (dm1 * yl) * (float)T4[1];
           facc[2] += (d0 * yh) * (float)S4[2] - (dm0 * yh) * (float)T4[2];
