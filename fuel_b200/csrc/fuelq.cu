@@ -940,9 +940,11 @@ int32_t fuelq_moe_bucket(const int32_t* topk_ids, int64_t n_pairs, int32_t n_exp
                          int32_t* expert_offsets, void* stream) {
   if (n_pairs < 0 || n_pairs > (1 << 24) || n_experts <= 0 || n_experts > 8192) return kInvalidProblem;
   if (!expert_offsets || (n_pairs > 0 && (!topk_ids || !sorted_ids))) return kInvalidProblem;
-  const cudaError_t e = launch(moe_bucket_kernel, dim3(1), dim3(1024), (size_t)(n_experts + 1) * sizeof(int),
+  const int in_smem = (size_t)(n_experts + 1 + n_pairs) * sizeof(int) <= 48 * 1024 ? 1 : 0;  // default dynamic limit
+  const size_t bsm = (size_t)(n_experts + 1 + (in_smem ? n_pairs : 0)) * sizeof(int);
+  const cudaError_t e = launch(moe_bucket_kernel, dim3(1), dim3(1024), bsm,
                                (cudaStream_t)stream, (const int*)topk_ids, (int)n_pairs, (int)n_experts, (int*)sorted_ids,
-                               (int*)expert_offsets);
+                               (int*)expert_offsets, in_smem);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 

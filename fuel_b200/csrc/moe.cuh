@@ -77,20 +77,38 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* logits, int
 }
 
 // ---- bucketing: pairs (token * top_k + slot) sorted by expert, ascending pair id inside an expert.
-// One CTA; a warp per expert scans the pair list with ballots, so the order never depends on timing.
+// One CTA; the pair list is read into shared memory once (when it fits), then every warp scans it with
+// ballots for up to kBucketPerWarp experts at a time, so the order never depends on timing.
+constexpr int kBucketPerWarp = 4;
+
 __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int* topk_ids, int n_pairs, int n_experts, int* sorted_ids,
-                                                          int* offsets) {
-  extern __shared__ int counts[];  // n_experts + 1
+                                                          int* offsets, int in_smem) {
+  extern __shared__ int bsm[];  // counts [n_experts + 1], then the pair list if it fits
+  int* counts = bsm;
+  int* ids_s = bsm + n_experts + 1;
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int e = warp; e < n_experts; e += nwarps) {
-    int c = 0;
+  if (in_smem)
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) ids_s[p] = topk_ids[p];
+  __syncthreads();
+  const int* ids = in_smem ? ids_s : topk_ids;
+  // pass 1: counts
+  for (int e0 = warp * kBucketPerWarp; e0 < n_experts; e0 += nwarps * kBucketPerWarp) {
+    int c[kBucketPerWarp];
+#pragma unroll
+    for (int i = 0; i < kBucketPerWarp; ++i) c[i] = 0;
     for (int p0 = 0; p0 < n_pairs; p0 += 32) {
       const int p = p0 + lane;
-      c += __popc(__ballot_sync(0xffffffffu, p < n_pairs && topk_ids[p] == e));
+      const int id = p < n_pairs ? ids[p] : -1;
+#pragma unroll
+      for (int i = 0; i < kBucketPerWarp; ++i) c[i] += __popc(__ballot_sync(0xffffffffu, id == e0 + i));
     }
-    if (lane == 0) counts[e] = c;
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < kBucketPerWarp; ++i)
+        if (e0 + i < n_experts) counts[e0 + i] = c[i];
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -105,14 +123,21 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int* topk_ids, i
     offsets[n_experts] = run;
   }
   __syncthreads();
-  for (int e = warp; e < n_experts; e += nwarps) {
-    int pos = counts[e];
+  // pass 2: positions
+  for (int e0 = warp * kBucketPerWarp; e0 < n_experts; e0 += nwarps * kBucketPerWarp) {
+    int pos[kBucketPerWarp];
+#pragma unroll
+    for (int i = 0; i < kBucketPerWarp; ++i) pos[i] = (e0 + i < n_experts) ? counts[e0 + i] : 0;
     for (int p0 = 0; p0 < n_pairs; p0 += 32) {
       const int p = p0 + lane;
-      const bool hit = p < n_pairs && topk_ids[p] == e;
-      const unsigned b = __ballot_sync(0xffffffffu, hit);
-      if (hit) sorted_ids[pos + __popc(b & ((1u << lane) - 1u))] = p;
-      pos += __popc(b);
+      const int id = p < n_pairs ? ids[p] : -1;
+#pragma unroll
+      for (int i = 0; i < kBucketPerWarp; ++i) {
+        const bool hit = id == e0 + i;
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (hit) sorted_ids[pos[i] + __popc(bal & ((1u << lane) - 1u))] = p;
+        pos[i] += __popc(bal);
+      }
     }
   }
 }

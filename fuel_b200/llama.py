@@ -486,3 +486,33 @@ class QLlama:
             self.run_step()
             out.append(self.next_token.clone())
         return torch.cat(out).cpu().tolist()
+
+
+def _main() -> None:
+    """python -m fuel_b200.llama [--comm nccl|peer] [--steps N] [--pdl 0|1]: builds the 7B-architecture model on GPU 0,
+    runs N eager decode steps and brackets the last one with cudaProfilerStart/Stop, so that a profiler started with
+    --profile-from-start off lists exactly the kernels of one token."""
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--comm", default="nccl", choices=["nccl", "peer"])
+    ap.add_argument("--steps", type=int, default=41)
+    ap.add_argument("--pdl", type=int, default=0)
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    _L.fuelq_set_option(_lib.OPT_PDL, args.pdl)
+    model = QLlama(LlamaConfig.llama2_7b(), torch.device("cuda", 0), comm=args.comm)
+    try:
+        for _ in range(args.steps - 1):
+            model.step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        model.step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print("next token", int(model.next_token.item()), "pos", int(model.pos.item()))
+    finally:
+        model.release()
+
+
+if __name__ == "__main__":
+    _main()

@@ -36,3 +36,16 @@ def test_two_gpus_decode_the_same_tokens(comm):
     assert got["err"] == 0
     assert got["eager"] == want and got["graph_pdl"] == want
     assert got["logits_sum"] == logits_sum      # every logit has the same bits, so does their f64 sum
+
+
+def test_two_gpus_expert_parallel_block_equals_single_gpu_block():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29534", os.path.join(ROOT, "tests", "_ep_worker.py")]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=400)
+    lines = [l for l in r.stdout.splitlines() if l.startswith("EPRESULT ")]
+    assert r.returncode == 0 and lines, (r.stdout[-2000:], r.stderr[-2000:])
+    got = json.loads(lines[-1][len("EPRESULT "):])
+    assert got["err"] == 0 and got["equal"], got
