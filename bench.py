@@ -179,6 +179,10 @@ def run_side_workload(args):
     from fuel_b200 import GgmlDType as T, _lib, ops
     from fuel_b200.moe import QMoeBlock
     L = _lib.lib
+    rank, local_rank, world = _dist_env()
+    if world > 1:
+        assert args.workload == "moe", "only the MoE block has a multi-GPU (expert-parallel) form here"
+        return run_moe_expert_parallel(args, rank, local_rank, world)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0)
@@ -230,6 +234,56 @@ def run_side_workload(args):
                           "tokens_per_s": N / us * 1e6, "hbm_frac": wbytes / us / 1e3 / peak, "peak_kind": f"of {peak_kind}",
                           "weight_bytes": wbytes, "weight_copies": copies, "launches_per_block": 9}), flush=True)
     assert ops.device_error() == 0, "a kernel recorded an expired bounded wait"
+
+
+def run_moe_expert_parallel(args, rank, local_rank, world):
+    """BASELINE config 5 expert-parallel: 128 experts split over the ranks, 256 tokens split over the ranks, two NCCL
+    all-to-alls per block. Eager calls (the exchange sizes are read on the host), CUDA events, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    from fuel_b200.moe import QMoeExpertParallel
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    _lib.lib.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0)
+    E, H, F, K, N, copies = 128, 2048, 768, 8, 256, 4
+    El, nl = E // world, N // world
+    gen = torch.Generator(device=dev)
+    blocks = []
+    for c in range(copies):
+        gen.manual_seed(1000 * c + rank)
+        bgu = ops.quantize_weights(T.Q4K, torch.randn(El * 2 * F, H, generator=gen, device=dev) * 0.02)
+        bd = ops.quantize_weights(T.Q4K, torch.randn(El * H, F, generator=gen, device=dev) * 0.02)
+        blocks.append(QMoeExpertParallel(E, H, F, K, bgu, bd, rank, world, max_local_tokens=nl, max_recv_rows=N * K))
+    gen.manual_seed(77 + rank)
+    x = torch.randn(nl, H, generator=gen, device=dev)
+    logits = torch.randn(nl, E, generator=gen, device=dev)
+    for b in blocks:
+        b.forward(x, logits)
+    torch.cuda.synchronize()
+    dist.barrier()
+    reps = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        for b in blocks:
+            b.forward(x, logits)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t.item()) * 1e3 / (reps * copies)
+    assert ops.device_error() == 0
+    if rank == 0:
+        wbytes = E * 3 * F * H // 256 * 144
+        print(json.dumps({"workload": f"moe_block_e{E}_h{H}_f{F}_top{K}_tokens{N}_q4k_expert_parallel", "n_gpus": world, "us": us,
+                          "tokens_per_s": N / us * 1e6, "GB/s": wbytes / us / 1e3, "weight_bytes_per_gpu": wbytes // world,
+                          "exchange": "two NCCL all-to-alls per block + one host read of the routing counts",
+                          "cuda_graph": False}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def run_decode_7b(torch, dist, device, rank, world):

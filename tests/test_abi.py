@@ -84,3 +84,31 @@ def test_options_round_trip(L):
     assert f.fuelq_set_option(L.OPT_PDL, 0) == L.OK
     assert f.fuelq_set_option(L.OPT_DECODE_MAX_M, -1) == L.INVALID_PROBLEM
     assert f.fuelq_set_option(77, 1) == L.INVALID_PROBLEM
+
+
+def test_argument_validation_of_moe_and_peer_entries_needs_no_gpu():
+    """Bad arguments are refused with a status code before anything is launched (status 2 invalid problem, 3 not
+    supported, 4 workspace), so these calls are safe on a machine without a GPU."""
+    import ctypes
+
+    from fuel_b200 import _lib
+    L = _lib.lib
+    INV, NOSUP = _lib.INVALID_PROBLEM, _lib.NOT_SUPPORTED
+    assert L.fuelq_moe_route(None, 4, 8, 2, None, None, None) == INV            # null pointers
+    assert L.fuelq_moe_route(None, 0, 8, 2, None, None, None) == 0              # no tokens: nothing to do
+    assert L.fuelq_moe_route(None, 4, 2000, 2, None, None, None) == INV         # more experts than the router handles
+    assert L.fuelq_moe_route(None, 4, 8, 9, None, None, None) == INV            # top_k > n_experts
+    assert L.fuelq_moe_bucket(None, 16, 0, None, None, None) == INV
+    assert L.fuelq_moe_quantize_rows(None, 100, None, 1, 4, None, 0, None) == INV   # k not a multiple of 256
+    assert L.fuelq_moe_quantize_rows(None, 256, None, 0, 4, None, 0, None) == INV   # divisor
+    assert L.fuelq_moe_swiglu_quantize(None, 300, 4, None, 0, None) == INV
+    assert L.fuelq_moe_qmatmul(8, 4, 64, 256, None, None, 4, None, None, None, None) == NOSUP   # Q8_0 experts
+    assert L.fuelq_moe_qmatmul(12, 4, 64, 256, None, None, 0, None, None, None, None) == 0      # no rows
+    assert L.fuelq_moe_qmatmul(12, 4, 64, 256, None, None, 4, None, None, None, None) == INV
+    assert L.fuelq_moe_combine(None, None, None, 4, 99, 64, None, None) == INV
+    peers = _lib.Peers()
+    peers.world, peers.rank, peers.epoch = 9, 0, 16
+    assert L.fuelq_add_rmsnorm_q8k_peer(16, None, 16, 256, 1e-5, 16, 1 << 20, ctypes.byref(peers), -1, None) == INV  # world > 8
+    peers.world, peers.rank = 2, 2
+    assert L.fuelq_argmax_last_peer(16, 8, 16, ctypes.byref(peers), 0, 16, None) == INV                              # rank >= world
+    assert L.fuelq_peer_act_bytes(100) == 0 and L.fuelq_peer_act_bytes(256) > 0 and L.fuelq_peer_vec_bytes(10) == 80
