@@ -452,9 +452,9 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       planes = act_planes(smem_raw + g->act_smem_off, kQ4K, 1, p.k);
       const uint32_t want = peer_stamp(g->ctx, g->ctx.wait_seq);
       const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
-      peer_copy_words(g->act_ll.qs, (uint32_t*)planes.qs, p.k >> 2, want, t, nt);
-      peer_copy_words(g->act_ll.bs, (uint32_t*)planes.bsums, p.k >> 5, want, t, nt);
-      peer_copy_words1(g->act_ll.d, (uint32_t*)planes.d, p.k >> 8, want, t, nt);
+      peer_copy_words(g->act_ll.qs, (uint32_t*)planes.qs, p.k >> 2, want, t, nt, g->ctx.wait_ns);
+      peer_copy_words(g->act_ll.bs, (uint32_t*)planes.bsums, p.k >> 5, want, t, nt, g->ctx.wait_ns);
+      peer_copy_words1(g->act_ll.d, (uint32_t*)planes.d, p.k >> 8, want, t, nt, g->ctx.wait_ns);
       asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
     }
   }

@@ -33,6 +33,7 @@ struct Options {
   int64_t dbg_pre = -1;
   int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
   int64_t moe_kernel = 0;     // development switch: 1 = grouped mat-vec on the dp4a kernel even where the tensor-core form fits
+  int64_t peer_wait_ms = 4000; // deadline of the exchange polls in the tensor-parallel kernels
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
 };
 Options g_opt;
@@ -613,6 +614,10 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 107: g_opt.moe_kernel = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
+    case FUELQ_OPT_PEER_WAIT_MS:
+      if (value < 1 || value > 60000) return kInvalidProblem;
+      g_opt.peer_wait_ms = value;
+      return kOk;
     default: return kInvalidProblem;
   }
 }
@@ -625,6 +630,7 @@ int64_t fuelq_get_option(int32_t key) {
     case FUELQ_OPT_DECODE_KERNEL: return g_opt.decode_kernel;
     case FUELQ_OPT_L2_PREFETCH: return g_opt.l2_prefetch;
     case FUELQ_OPT_FUSED_QUANT: return g_opt.fused_quant;
+    case FUELQ_OPT_PEER_WAIT_MS: return g_opt.peer_wait_ms;
     default: return -1;
   }
 }
@@ -1080,6 +1086,7 @@ int32_t make_peer_ctx(const fuelq_peers* peers, int32_t wait_seq, int32_t push_s
   c->wait_seq = wait_seq < 0 ? -1 : wait_seq;
   c->push_seq = push_seq < 0 ? -1 : push_seq;
   c->epoch = peers->epoch;
+  c->wait_ns = (unsigned long long)g_opt.peer_wait_ms * 1000000ull;
   return kOk;
 }
 int32_t make_peer_planes(void* const* act_dst, int64_t k_total, int world, PeerStampedPlanes* out) {

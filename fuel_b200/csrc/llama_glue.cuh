@@ -224,7 +224,7 @@ __device__ __forceinline__ void add_rmsnorm_body(float* x, const void* delta_v,
         const uint2* dl = reinterpret_cast<const uint2*>(delta_v) + warp * 256;
         const uint32_t want = peer_stamp(*pc, pc->wait_seq);
         uint32_t a[4], b[4];
-        peer_load_words2<4, 4>(dl + 4 * lane, dl + 128 + 4 * lane, want, a, b);
+        peer_load_words2<4, 4>(dl + 4 * lane, dl + 128 + 4 * lane, want, a, b, pc->wait_ns);
         d0 = make_float4(__uint_as_float(a[0]), __uint_as_float(a[1]), __uint_as_float(a[2]), __uint_as_float(a[3]));
         d1 = make_float4(__uint_as_float(b[0]), __uint_as_float(b[1]), __uint_as_float(b[2]), __uint_as_float(b[3]));
       } else {
@@ -419,7 +419,7 @@ __device__ __forceinline__ void argmax_last_body(const float* x, int n, int* out
     const uint32_t want = peer_stamp(*pc, pc->wait_seq);
     for (int i = 2 * threadIdx.x; i < n; i += 2 * blockDim.x) {
       uint32_t w[2];
-      peer_load_words<2>(xl + i, want, w);
+      peer_load_words<2>(xl + i, want, w, pc->wait_ns);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const float v = __uint_as_float(w[j]);

@@ -25,13 +25,13 @@ namespace fq {
 
 constexpr int kPeerMaxWorld = 8;
 constexpr int kPeerMaxSeq = 1024;
-constexpr unsigned long long kPeerWaitNs = 4000000000ull;  // four seconds
 
 struct PeerCtx {
   int world, rank;
   int wait_seq;            // exchange point whose data this kernel consumes, or -1
   int push_seq;            // exchange point this kernel produces, or -1
   const uint32_t* epoch;   // local step counter
+  unsigned long long wait_ns;  // deadline of every poll loop (FUELQ_OPT_PEER_WAIT_MS)
 };
 
 __device__ __forceinline__ uint32_t peer_stamp(const PeerCtx& c, int seq) {
@@ -61,15 +61,16 @@ __device__ __forceinline__ unsigned long long peer_now_ns() {
 
 // Bounded retry bookkeeping for one thread's poll loop.
 struct PeerPoll {
-  unsigned long long t0 = 0;
+  unsigned long long t0 = 0, limit_ns;
   uint32_t i = 0;
+  __device__ __forceinline__ explicit PeerPoll(unsigned long long limit) : limit_ns(limit) {}
   // call after a failed attempt; false = give up (error recorded or already present)
   __device__ __forceinline__ bool again() {
     if (i == 0) t0 = peer_now_ns();
     ++i;
     if (*reinterpret_cast<volatile int*>(&g_fq_dev_error) != 0) return false;
     if (i > 16) __nanosleep(i < 256 ? 64 : 512);
-    if ((i & 63u) == 0u && peer_now_ns() - t0 > kPeerWaitNs) {
+    if ((i & 63u) == 0u && peer_now_ns() - t0 > limit_ns) {
       record_dev_error(kErrPeerWait);
       return false;
     }
@@ -84,9 +85,9 @@ struct PeerPoll {
 // stamps match.
 template <int NA, int NB>
 __device__ __forceinline__ void peer_load_words2(const uint2* srca, const uint2* srcb, uint32_t want, uint32_t (&outa)[NA],
-                                                 uint32_t (&outb)[NB == 0 ? 2 : NB]) {
+                                                 uint32_t (&outb)[NB == 0 ? 2 : NB], unsigned long long limit_ns) {
   static_assert(NA % 2 == 0 && NB % 2 == 0, "pairs are read two at a time");
-  PeerPoll poll;
+  PeerPoll poll(limit_ns);
   for (;;) {
     uint4 va[NA / 2], vb[NB == 0 ? 1 : NB / 2];
 #pragma unroll
@@ -108,18 +109,18 @@ __device__ __forceinline__ void peer_load_words2(const uint2* srca, const uint2*
   }
 }
 template <int NW>
-__device__ __forceinline__ void peer_load_words(const uint2* src, uint32_t want, uint32_t (&out)[NW]) {
+__device__ __forceinline__ void peer_load_words(const uint2* src, uint32_t want, uint32_t (&out)[NW], unsigned long long limit_ns) {
   uint32_t none[2];
-  peer_load_words2<NW, 0>(src, src, want, out, none);
+  peer_load_words2<NW, 0>(src, src, want, out, none, limit_ns);
 }
 
 // n_words words (even count, 16-byte aligned source, 8-byte aligned destination) from a stamped buffer into
 // plain words at dst (shared or global), by `nthreads` cooperating threads of which this is thread t. Each
 // thread polls its own pairs; the caller synchronizes the threads afterwards.
 __device__ __forceinline__ void peer_copy_words(const uint2* src, uint32_t* dst, int n_words, uint32_t want, int t,
-                                                int nthreads) {
+                                                int nthreads, unsigned long long limit_ns) {
   for (int i = t; i < n_words / 2; i += nthreads) {
-    PeerPoll poll;
+    PeerPoll poll(limit_ns);
     for (;;) {
       const uint4 v = ld_pair2(src + 2 * i);
       if ((((v.y ^ want) | (v.w ^ want)) == 0u) || !poll.again()) {
@@ -131,9 +132,9 @@ __device__ __forceinline__ void peer_copy_words(const uint2* src, uint32_t* dst,
 }
 // same for any count, one pair at a time
 __device__ __forceinline__ void peer_copy_words1(const uint2* src, uint32_t* dst, int n_words, uint32_t want, int t,
-                                                 int nthreads) {
+                                                 int nthreads, unsigned long long limit_ns) {
   for (int i = t; i < n_words; i += nthreads) {
-    PeerPoll poll;
+    PeerPoll poll(limit_ns);
     for (;;) {
       const uint2 v = ld_pair(src + i);
       if (v.y == want || !poll.again()) {

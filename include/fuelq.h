@@ -66,6 +66,9 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
                                     fuelq_quantize_act). 0 (default): quantize kernel, then mat-vec kernel, which
                                     measured faster in a chain of launches (the small kernel overlaps the
                                     previous mat-vec's tail; in-kernel quantization sits on the critical path) */
+#define FUELQ_OPT_PEER_WAIT_MS 7  /* deadline, in milliseconds, of the exchange polls in the fuelq_*_peer kernels (default
+                                    4000, 1..60000): a kernel whose peer never delivers records device error 6 after
+                                    this long and carries on, so the context stays usable */
 int32_t fuelq_set_option(int32_t key, int64_t value);
 int64_t fuelq_get_option(int32_t key);
 

@@ -109,3 +109,46 @@ def test_in_kernel_exchange_single_rank_matches_fused_step():
         assert ops.device_error() == 0
     finally:
         model.release()
+
+
+def test_exchange_wait_expires_with_an_error_code_and_the_context_stays_usable():
+    """Failure detection without a fault: a consumer polls an exchange point that nothing ever stamps. After the
+    deadline (FUELQ_OPT_PEER_WAIT_MS, shortened here) the kernel records device error 6 and finishes; the next call on
+    the same context works and gives the right answer."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import ctypes
+    import time
+
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    from oracle import oracle as O
+    L = _lib.lib
+    dim = 512
+    x = torch.ones(dim, device="cuda")
+    gain = torch.ones(dim, device="cuda")
+    never_stamped = torch.zeros(2 * dim, dtype=torch.int32, device="cuda")   # a vector buffer nobody writes
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    packed = torch.zeros(L.fuelq_act_packed_bytes(int(T.Q4K), 1, dim), dtype=torch.uint8, device="cuda")
+    peers = _lib.Peers()
+    peers.world, peers.rank, peers.epoch = 1, 0, epoch.data_ptr()
+    assert ops.device_error() == 0
+    try:
+        _lib.check(L.fuelq_set_option(_lib.OPT_PEER_WAIT_MS, 200), "set_option")
+        t0 = time.time()
+        _lib.check(L.fuelq_add_rmsnorm_q8k_peer(x.data_ptr(), never_stamped.data_ptr(), gain.data_ptr(), dim, 1e-5,
+                                                packed.data_ptr(), packed.numel(), ctypes.byref(peers), 3, None), "peer")
+        torch.cuda.synchronize()
+        dt = time.time() - t0
+    finally:
+        L.fuelq_set_option(_lib.OPT_PEER_WAIT_MS, 4000)
+    assert 0.15 <= dt <= 3.0, dt
+    assert ops.device_error() == 6          # kErrPeerWait; reading it clears it
+    assert ops.device_error() == 0
+    # the context is intact: an ordinary mat-vec right after gives the reference's numbers
+    g = np.random.Generator(np.random.PCG64(0))
+    w = g.standard_normal((64, 256), dtype=np.float32) * np.float32(0.02)
+    xa = g.standard_normal((1, 256), dtype=np.float32)
+    wb = O.quantize(O.Q4K, w)
+    y = ops.qmatmul(T.Q4K, torch.from_numpy(wb).cuda(), 64, torch.from_numpy(xa).cuda()).cpu().numpy()
+    r = O.matmul(O.Q4K, xa, wb, 64)
+    assert np.abs(y - r).max() <= 2e-6 * np.abs(r).max()
