@@ -101,13 +101,27 @@ __device__ __forceinline__ float small_int_f32(uint32_t q_at_bit16) { return __u
 
 struct Q4KPrefill {
   static constexpr int kType = kQ4K;
+  static constexpr bool kSplitLoad = true;
+  // the bytes of one 64-wide stage of a row: block header and 32 bytes of nibbles
+  struct Raw {
+    uint4 hdr, qa, qb;
+  };
   // k0 = 64 * it: block it / 4, group it % 4; row points at the weight row's first block
-  __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
+  __device__ __forceinline__ static void load(const uint8_t* row, int it, Raw& r) {
     const int blk = it >> 2, g = it & 3;
     const uint8_t* b = row + blk * Q4KL::kBytes;
-    const uint4 hdr = *reinterpret_cast<const uint4*>(b);
-    const uint4 qa = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g);
-    const uint4 qb = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16);
+    r.hdr = *reinterpret_cast<const uint4*>(b);
+    r.qa = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g);
+    r.qb = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16);
+  }
+  __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
+    Raw r;
+    load(row, it, r);
+    convert(r, it, out);
+  }
+  __device__ __forceinline__ static void convert(const Raw& r, int it, uint4 (&out)[8]) {
+    const int g = it & 3;
+    const uint4 hdr = r.hdr, qa = r.qa, qb = r.qb;
     const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
     const uint32_t sh = 16 * (g & 1);
     uint32_t sc2, mn2;
@@ -140,6 +154,10 @@ struct Q4KPrefill {
 // Q8_0: a 64-wide stage is two 34-byte blocks (2-byte aligned): y = q * d
 struct Q8_0Prefill {
   static constexpr int kType = kQ8_0;
+  static constexpr bool kSplitLoad = false;
+  struct Raw {};
+  __device__ __forceinline__ static void load(const uint8_t*, int, Raw&) {}
+  __device__ __forceinline__ static void convert(const Raw&, int, uint4 (&)[8]) {}
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -161,6 +179,10 @@ struct Q8_0Prefill {
 // or high (l+64, l+96) nibbles of the same 64 ql bytes; y = d * sc * (q - 32)
 struct Q6KPrefill {
   static constexpr int kType = kQ6K;
+  static constexpr bool kSplitLoad = false;
+  struct Raw {};
+  __device__ __forceinline__ static void load(const uint8_t*, int, Raw&) {}
+  __device__ __forceinline__ static void convert(const Raw&, int, uint4 (&)[8]) {}
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
     const int blk = it >> 2, half = (it >> 1) & 1, sub = it & 1;
     const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
@@ -229,10 +251,25 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
     const uint8_t* row = p.w + (size_t)(live ? n0 + t : 0) * p.row_bytes;
     int s = 0;
     uint32_t ph = 0;
+    // the bytes of the next three stages, requested that far ahead: a stage takes less time than one trip to L2
+    typename Fmt::Raw r0, r1, r2;
+    if (Fmt::kSplitLoad && live) {
+      if (n_iter > 0) Fmt::load(row, 0, r0);
+      if (n_iter > 1) Fmt::load(row, 1, r1);
+      if (n_iter > 2) Fmt::load(row, 2, r2);
+    }
     for (int it = 0; it < n_iter && !*abort_flag; ++it) {
       uint4 out[8];
       if (live) {
-        Fmt::stage(row, it, out);
+        if constexpr (Fmt::kSplitLoad) {
+          const typename Fmt::Raw cur = r0;
+          r0 = r1;
+          r1 = r2;
+          if (it + 3 < n_iter) Fmt::load(row, it + 3, r2);
+          Fmt::convert(cur, it, out);
+        } else {
+          Fmt::stage(row, it, out);
+        }
       } else {
 #pragma unroll
         for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
