@@ -512,8 +512,31 @@ bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
 }
 size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * 2, 256); }
 
+// tensor map of the bf16 activation matrix [M][K]: boxes of 64 columns x tile_m rows, 128-byte swizzle, zero fill
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, CUtensorMap* map) {
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn)
+      return false;
+    encode = (EncodeTiledFn)fn;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kPfTileK, (cuuint32_t)tile_m};
+  const cuuint32_t estr[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xb), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <class Fmt, int kTileM>
-cudaError_t launch_prefill(const PrefillParams& p, cudaStream_t stream) {
+cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t stream) {
   constexpr size_t smem = 1024 + (size_t)kPfStages * (kPfTileN * 128 + kTileM * 128) + sizeof(PrefillSmem) + 64;
   static bool attr_set[64] = {};
   auto kern = prefill_gemm_kernel<Fmt, kTileM>;
@@ -525,9 +548,10 @@ cudaError_t launch_prefill(const PrefillParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
+  CUtensorMap xmap;
+  if (!make_x_map(xb, p.M, p.K, kTileM, &xmap)) return cudaErrorUnknown;
   const dim3 grid((unsigned)((p.N + kPfTileN - 1) / kPfTileN), (unsigned)((p.M + kTileM - 1) / kTileM));
-  // plain launches: these kernels do not take part in programmatic dependent launch
-  kern<<<grid, kPfThreads, smem, stream>>>(p);
+  kern<<<grid, kPfThreads, smem, stream>>>(p, xmap);
   return cudaGetLastError();
 }
 
@@ -539,7 +563,6 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   if (cudaGetLastError() != cudaSuccess) return kLaunchFailure;
   PrefillParams p;
   p.w = (const uint8_t*)w;
-  p.x = xb;
   p.y = y;
   p.M = (int)m;
   p.N = (int)n;
@@ -551,9 +574,9 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   if (!device_info(&di)) return kLaunchFailure;
   const bool wide = m > 128 && ((n + kPfTileN - 1) / kPfTileN) * ((m + 255) / 256) >= di->sm_count;
   switch (type) {
-    case kQ4K: e = wide ? launch_prefill<Q4KPrefill, 256>(p, stream) : launch_prefill<Q4KPrefill, 128>(p, stream); break;
-    case kQ6K: e = wide ? launch_prefill<Q6KPrefill, 256>(p, stream) : launch_prefill<Q6KPrefill, 128>(p, stream); break;
-    case kQ8_0: e = wide ? launch_prefill<Q8_0Prefill, 256>(p, stream) : launch_prefill<Q8_0Prefill, 128>(p, stream); break;
+    case kQ4K: e = wide ? launch_prefill<Q4KPrefill, 256>(p, xb, stream) : launch_prefill<Q4KPrefill, 128>(p, xb, stream); break;
+    case kQ6K: e = wide ? launch_prefill<Q6KPrefill, 256>(p, xb, stream) : launch_prefill<Q6KPrefill, 128>(p, xb, stream); break;
+    case kQ8_0: e = wide ? launch_prefill<Q8_0Prefill, 256>(p, xb, stream) : launch_prefill<Q8_0Prefill, 128>(p, xb, stream); break;
     default: return kNotSupported;
   }
   return e == cudaSuccess ? kOk : kLaunchFailure;

@@ -7,13 +7,21 @@
 // 128-byte-swizzled layout and multiplied with tcgen05.mma, accumulating f32 in tensor memory.
 //
 // One CTA computes a 128 (output features) x kTileM (activation rows) tile:
-//   warps 0-3  dequantize the weight tile of each 64-wide K stage (one thread per weight row),
-//              then read the accumulator out of tensor memory and store Y;
-//   warps 4-7  copy the activation tile (bf16, converted by a pre-pass) with cp.async;
+//   warps 0-7  dequantize the weight tile of each 64-wide K stage (two threads per weight row, one per
+//              32-element half, for Q4_K; one thread per row for the other formats); thread 0 also
+//              issues the stage's activation tile as ONE tensor-map (TMA) copy of the bf16 matrix
+//              (converted by a pre-pass) with the same 128-byte swizzle; warps 0-3 then read the
+//              accumulator out of tensor memory and store Y;
 //   warp  8    allocates tensor memory and, one lane, issues the MMAs and their commits.
+// Measured: sixteen dequantizing warps (a quarter row each) are slower than eight; per stage the kernel moves
+// 48 KB into shared memory and the MMAs read 48 KB back, which at 128 B/clk is already the stage time of a
+// single-SM MMA - the next step is the two-SM form (cta_group::2), which halves the activation reads.
 // Stages cycle through full/empty mbarriers; every wait is bounded and on expiry the CTA raises an
 // abort flag, skips to the end, frees its tensor memory and returns.
 #pragma once
+#include <cuda.h>
+
+#include <type_traits>
 #include <cuda_bf16.h>
 
 #include "dequantize.cuh"
@@ -24,11 +32,11 @@ namespace fq {
 constexpr int kPfTileN = 128;   // weight rows per CTA  (UMMA M)
 constexpr int kPfTileK = 64;    // K per stage: one 128-byte swizzle atom of bf16
 constexpr int kPfStages = 4;
-constexpr int kPfThreads = 32 * 9;
+constexpr int kPfDequantWarps = 8;   // 8: two threads per weight row (halves); 16: four (quarters) - measured slower
+constexpr int kPfThreads = 32 * (kPfDequantWarps + 1);
 
 struct PrefillParams {
   const uint8_t* w;          // GGUF blocks, [N][K / block]
-  const __nv_bfloat16* x;    // [M][K] bf16
   float* y;                  // [M][N]
   int M, N, K;
   int row_bytes;
@@ -74,6 +82,14 @@ __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// 2-D tiled tensor-map copy global -> shared, completion in bytes on an mbarrier. x (innermost, in elements) times the
+// element size must be a multiple of 16 bytes; rows outside the tensor arrive as zeros.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_dst),
+               "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+               : "memory");
+}
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, 8-row groups
 // 1024 bytes apart (stride byte offset), descriptor version 1 (this architecture), layout type 2.
@@ -106,6 +122,44 @@ struct Q4KPrefill {
   struct Raw {
     uint4 hdr, qa, qb;
   };
+  // ... and of one 16-element quarter of it (part = 2 * half + quarter: half 0 = low nibbles = elements 0..31,
+  // quarter = which 16 bytes of the 32): header and 16 bytes of nibbles
+  struct RawQ {
+    uint4 hdr, q;
+  };
+  __device__ __forceinline__ static void load_part(const uint8_t* row, int it, int part, RawQ& r) {
+    const int blk = it >> 2, g = it & 3;
+    const uint8_t* b = row + blk * Q4KL::kBytes;
+    r.hdr = *reinterpret_cast<const uint4*>(b);
+    r.q = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16 * (part & 1));
+  }
+  // -> two 16-byte chunks: elements 32 * half + 16 * quarter + (0..15) of the stage
+  __device__ __forceinline__ static void convert_part(const RawQ& r, int it, int part, uint4 (&out)[2]) {
+    const int g = it & 3, half = part >> 1;
+    const uint4 hdr = r.hdr;
+    const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
+    const uint32_t sh = 16 * (g & 1) + 8 * half;
+    uint32_t sc, mn;
+    if (g < 2) {
+      sc = (hdr.y >> sh) & 0x3fu;
+      mn = (hdr.z >> sh) & 0x3fu;
+    } else {
+      sc = ((hdr.w >> sh) & 0x0fu) | (((hdr.y >> (sh + 6)) & 0x03u) << 4);
+      mn = ((hdr.w >> (sh + 4)) & 0x0fu) | (((hdr.z >> (sh + 6)) & 0x03u) << 4);
+    }
+    const float d1 = d * (float)sc;
+    const float c1 = -(dmin * (float)mn) - 128.0f * d1;  // y = d*sc*q - dmin*m, with q taken as (128 + q) - 128
+    const uint32_t w[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+    const uint32_t nsh = 4 * half;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {  // word j holds bytes 4j..4j+3 -> elements 4j..4j+3 of this quarter
+      const uint32_t v = w[j] >> nsh;
+      const float l0 = fmaf(d1, small_int_f32((v << 16) & 0x000f0000u), c1), l1 = fmaf(d1, small_int_f32((v << 8) & 0x000f0000u), c1);
+      const float l2 = fmaf(d1, small_int_f32(v & 0x000f0000u), c1), l3 = fmaf(d1, small_int_f32((v >> 8) & 0x000f0000u), c1);
+      uint32_t* o = reinterpret_cast<uint32_t*>(&out[j >> 1]) + 2 * (j & 1);
+      o[0] = pack_bf16(l0, l1), o[1] = pack_bf16(l2, l3);
+    }
+  }
   // k0 = 64 * it: block it / 4, group it % 4; row points at the weight row's first block
   __device__ __forceinline__ static void load(const uint8_t* row, int it, Raw& r) {
     const int blk = it >> 2, g = it & 3;
@@ -113,6 +167,18 @@ struct Q4KPrefill {
     r.hdr = *reinterpret_cast<const uint4*>(b);
     r.qa = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g);
     r.qb = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16);
+  }
+  // one 32-element half of the stage (half 0: low nibbles, elements 0..31; half 1: high nibbles) -> 4 chunks
+  __device__ __forceinline__ static void convert_half(const Raw& r, int it, int half, uint4 (&out)[4]) {
+    RawQ q;
+    q.hdr = r.hdr;
+    uint4 o2[2];
+    q.q = r.qa;
+    convert_part(q, it, 2 * half, o2);
+    out[0] = o2[0], out[1] = o2[1];
+    q.q = r.qb;
+    convert_part(q, it, 2 * half + 1, o2);
+    out[2] = o2[0], out[3] = o2[1];
   }
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
     Raw r;
@@ -158,6 +224,10 @@ struct Q8_0Prefill {
   struct Raw {};
   __device__ __forceinline__ static void load(const uint8_t*, int, Raw&) {}
   __device__ __forceinline__ static void convert(const Raw&, int, uint4 (&)[8]) {}
+  struct RawQ {};
+  __device__ __forceinline__ static void load_part(const uint8_t*, int, int, RawQ&) {}
+  __device__ __forceinline__ static void convert_part(const RawQ&, int, int, uint4 (&)[2]) {}
+  __device__ __forceinline__ static void convert_half(const Raw&, int, int, uint4 (&)[4]) {}
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -183,6 +253,10 @@ struct Q6KPrefill {
   struct Raw {};
   __device__ __forceinline__ static void load(const uint8_t*, int, Raw&) {}
   __device__ __forceinline__ static void convert(const Raw&, int, uint4 (&)[8]) {}
+  struct RawQ {};
+  __device__ __forceinline__ static void load_part(const uint8_t*, int, int, RawQ&) {}
+  __device__ __forceinline__ static void convert_part(const RawQ&, int, int, uint4 (&)[2]) {}
+  __device__ __forceinline__ static void convert_half(const Raw&, int, int, uint4 (&)[4]) {}
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
     const int blk = it >> 2, half = (it >> 1) & 1, sub = it & 1;
     const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
@@ -208,7 +282,8 @@ struct Q6KPrefill {
 };
 
 struct PrefillSmem {
-  uint64_t full[kPfStages];
+  uint64_t full[kPfStages];   // weight tile of the stage written (the dequantizing threads)
+  uint64_t xfull[kPfStages];  // activation tile of the stage landed (tensor-map copy, counted in bytes)
   uint64_t empty[kPfStages];
   uint64_t accum;
   uint32_t tmem_base;
@@ -216,7 +291,7 @@ struct PrefillSmem {
 };
 
 template <class Fmt, int kTileM>
-__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t pf_smem[];
   // [stage][ weights 128 x 128 B | activations kTileM x 128 B ], each 1024-byte aligned; control block after
   constexpr int kWBytes = kPfTileN * 128, kXBytes = kTileM * 128, kStageBytes = kWBytes + kXBytes;
@@ -230,101 +305,94 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPfStages; ++s) {
-      mbar_init(&sm->full[s], 256);  // 128 weight-row threads + 128 activation-copy threads
+      mbar_init(&sm->full[s], 32 * kPfDequantWarps);  // the dequantizing threads
+      mbar_init(&sm->xfull[s], 1);                    // the thread that issues the activation copy (plus its bytes)
       mbar_init(&sm->empty[s], 1);   // one commit from the MMA thread
     }
     mbar_init(&sm->accum, 1);
     sm->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 8) tmem_alloc(&sm->tmem_base, kTileM);  // kTileM f32 accumulator columns x 128 lanes
+  if (warp == kPfDequantWarps) tmem_alloc(&sm->tmem_base, kTileM);  // kTileM f32 accumulator columns x 128 lanes
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = *reinterpret_cast<volatile uint32_t*>(&sm->tmem_base);
   volatile int* abort_flag = &sm->abort_flag;
 
-  if (warp < 4) {
-    // ---------------- weight producers: thread t owns weight row n0 + t
-    const int t = threadIdx.x;
-    const bool live = n0 + t < p.N;
-    const uint8_t* row = p.w + (size_t)(live ? n0 + t : 0) * p.row_bytes;
+  if (warp < kPfDequantWarps) {
+    // ---------------- weight producers: thread t owns part (t >> 7) of weight row n0 + (t & 127): a half or a quarter
+    const int t = threadIdx.x, r = t & 127, part = t >> 7;
+    const bool live = n0 + r < p.N;
+    const uint8_t* row = p.w + (size_t)(live ? n0 + r : 0) * p.row_bytes;
     int s = 0;
     uint32_t ph = 0;
+    int x_issued = 0;
     // the bytes of the next three stages, requested that far ahead: a stage takes less time than one trip to L2
-    typename Fmt::Raw r0, r1, r2;
+    constexpr bool kQuarters = kPfDequantWarps == 16;
+    using RawT = typename std::conditional<kQuarters, typename Fmt::RawQ, typename Fmt::Raw>::type;
+    auto load_raw = [&](int it, RawT& dst_raw) {
+      if constexpr (kQuarters) Fmt::load_part(row, it, part, dst_raw);
+      else Fmt::load(row, it, dst_raw);
+    };
+    RawT r0, r1, r2;
     if (Fmt::kSplitLoad && live) {
-      if (n_iter > 0) Fmt::load(row, 0, r0);
-      if (n_iter > 1) Fmt::load(row, 1, r1);
-      if (n_iter > 2) Fmt::load(row, 2, r2);
+      if (n_iter > 0) load_raw(0, r0);
+      if (n_iter > 1) load_raw(1, r1);
+      if (n_iter > 2) load_raw(2, r2);
     }
     for (int it = 0; it < n_iter && !*abort_flag; ++it) {
-      uint4 out[8];
-      if (live) {
-        if constexpr (Fmt::kSplitLoad) {
-          const typename Fmt::Raw cur = r0;
-          r0 = r1;
-          r1 = r2;
-          if (it + 3 < n_iter) Fmt::load(row, it + 3, r2);
-          Fmt::convert(cur, it, out);
-        } else {
-          Fmt::stage(row, it, out);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
-      }
       if (it >= kPfStages && !mbar_wait_bounded(&sm->empty[s], ph ^ 1u)) {
         record_dev_error(kErrEmptyWait);
         *abort_flag = 1;
         break;
       }
-      uint8_t* dst = base + s * kStageBytes + t * 128;
+      if (t == 0) {  // the stage is free: its activation tile, rows m0.. x columns 64*it.., as one copy
+        mbar_arrive_expect_tx(&sm->xfull[s], (uint32_t)kXBytes);
+        tma_load_2d(base_u32 + s * kStageBytes + kWBytes, &xmap, it * kPfTileK, m0, &sm->xfull[s]);
+        x_issued = it + 1;
+      }
+      uint8_t* dst = base + s * kStageBytes + r * 128;
+      if constexpr (Fmt::kSplitLoad) {
+        constexpr int kChunks = kQuarters ? 2 : 4;  // 16-byte chunks this thread writes
+        uint4 out[4];
+        if (live) {
+          const RawT cur = r0;
+          r0 = r1;
+          r1 = r2;
+          if (it + 3 < n_iter) load_raw(it + 3, r2);
+          if constexpr (kQuarters) {
+            uint4 o2[2];
+            Fmt::convert_part(cur, it, part, o2);
+            out[0] = o2[0], out[1] = o2[1];
+          } else {
+            Fmt::convert_half(cur, it, part, out);
+          }
+        } else {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (t & 7)) << 4)) = out[c];
+          for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) *reinterpret_cast<uint4*>(dst + (((kChunks * part + c) ^ (r & 7)) << 4)) = out[c];
+      } else if (part == 0) {  // formats without a split form: one thread per row does it all
+        uint4 out[8];
+        if (live) {
+          Fmt::stage(row, it, out);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = out[c];
+      }
       fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
       mbar_arrive(&sm->full[s]);
       if (++s == kPfStages) s = 0, ph ^= 1u;
     }
-  } else if (warp < 8) {
-    // ---------------- activation copies: kTileM rows x 8 chunks of 16 bytes per stage
-    const int t = threadIdx.x - 128;
-    constexpr int kChunks = kTileM * 8 / 128;  // per thread per stage
-    constexpr int kLag = 2;                    // stages a thread keeps in flight
-    int s = 0;
-    uint32_t ph = 0;
-    int pending[kLag + 1];
-    int n_pending = 0;
-    for (int it = 0; it < n_iter && !*abort_flag; ++it) {
-      if (it >= kPfStages && !mbar_wait_bounded(&sm->empty[s], ph ^ 1u)) {
-        record_dev_error(kErrEmptyWait);
-        *abort_flag = 1;
-        break;
-      }
-      const uint32_t dst0 = base_u32 + s * kStageBytes + kWBytes;
-#pragma unroll
-      for (int i = 0; i < kChunks; ++i) {
-        const int c = i * 128 + t, r = c >> 3, kc = c & 7;
-        const int m = m0 + r;
-        const bool ok = m < p.M;
-        const __nv_bfloat16* src = p.x + (size_t)(ok ? m : 0) * p.K + it * kPfTileK + kc * 8;
-        cp_async16(dst0 + r * 128 + ((kc ^ (r & 7)) << 4), src, ok ? 16u : 0u);  // rows past M are zero-filled
-      }
-      cp_async_commit();
-      pending[n_pending++] = s;
-      if (n_pending > kLag) {
-        cp_async_wait<kLag>();
-        fence_proxy_async();
-        mbar_arrive(&sm->full[pending[0]]);
-#pragma unroll
-        for (int j = 0; j < kLag; ++j) pending[j] = pending[j + 1];
-        --n_pending;
-      }
-      if (++s == kPfStages) s = 0, ph ^= 1u;
+    if (t == 0 && *abort_flag) {  // leaving early: let the copies already issued land first
+      for (int it = (x_issued > kPfStages ? x_issued - kPfStages : 0); it < x_issued; ++it)
+        if (!mbar_wait_bounded(&sm->xfull[it % kPfStages], (it / kPfStages) & 1)) record_dev_error(kErrDrainWait);
     }
-    cp_async_wait<0>();
-    fence_proxy_async();
-    for (int j = 0; j < n_pending; ++j) mbar_arrive(&sm->full[pending[j]]);
   } else if (lane == 0) {
     // ---------------- MMA issue: one thread
     constexpr uint32_t idesc = umma_idesc_bf16(kPfTileN, kTileM);
@@ -332,7 +400,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
     uint32_t ph = 0;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
-      if (*abort_flag || !mbar_wait_bounded(&sm->full[s], ph)) {
+      if (*abort_flag || !mbar_wait_bounded(&sm->full[s], ph) || !mbar_wait_bounded(&sm->xfull[s], ph)) {
         if (!*abort_flag) record_dev_error(kErrFullWait);
         *abort_flag = 1;
         ok = false;
@@ -377,7 +445,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem_d, kTileM);
+  if (warp == kPfDequantWarps) tmem_dealloc(tmem_d, kTileM);
 }
 
 // f32 -> bf16 activation pre-pass
