@@ -26,6 +26,14 @@ class Peers(ctypes.Structure):
 
 _pp = ctypes.POINTER(Peers)
 
+
+class Rope(ctypes.Structure):
+    """struct fuelq_rope of include/fuelq.h."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("k", "v", "cos_table", "sin_table", "kcache", "vcache")]
+
+
+_rp = ctypes.POINTER(Rope)
+
 # name -> (restype, argtypes); must list every symbol include/fuelq.h declares
 PROTOTYPES = {
     "fuelq_status_string": (ctypes.c_char_p, [_i32]),
@@ -52,10 +60,10 @@ PROTOTYPES = {
     "fuelq_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _vp]),
     "fuelq_rope_store": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "fuelq_attn_decode_workspace_bytes": (_sz, [_i32]),
-    "fuelq_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _vp]),
+    "fuelq_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _rp, _vp]),
     "fuelq_add_rmsnorm_q8k": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, _vp, _sz, _vp]),
     "fuelq_swiglu_q8k": (_i32, [_vp, _vp, _i64, _vp, _sz, _vp]),
-    "fuelq_attn_decode_q8k": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _vp, _sz, _vp]),
+    "fuelq_attn_decode_q8k": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _vp, _sz, _rp, _vp]),
     "fuelq_moe_route": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp]),
     "fuelq_moe_bucket": (_i32, [_vp, _i64, _i32, _vp, _vp, _vp]),
     "fuelq_moe_quantize_rows": (_i32, [_vp, _i64, _vp, _i32, _i64, _vp, _sz, _vp]),
@@ -72,7 +80,7 @@ PROTOTYPES = {
     "fuelq_add_rmsnorm_q8k_peer": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, _vp, _sz, _pp, _i32, _vp]),
     "fuelq_swiglu_q8k_peer": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _pp, _i32, _vp]),
     "fuelq_attn_decode_q8k_peer": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _i32, _i64,
-                                          _vp, _pp, _i32, _vp]),
+                                          _vp, _pp, _i32, _rp, _vp]),
     "fuelq_argmax_last_peer": (_i32, [_vp, _i64, _vp, _pp, _i32, _vp, _vp]),
     "fuelq_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "fuelq_argmax_last": (_i32, [_vp, _i64, _vp, _vp]),

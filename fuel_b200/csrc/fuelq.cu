@@ -872,20 +872,36 @@ int32_t fuelq_rope_store(float* q, const float* k, const float* v, float* kcache
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
+namespace {
+// null `rope`: q is rotated and the caches are up to date; otherwise the attention kernel does both itself
+bool make_attn_rope(const fuelq_rope* rope, AttnRope* out) {
+  *out = AttnRope{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  if (!rope) return true;
+  if (!rope->k || !rope->v || !rope->cos_table || !rope->sin_table || !rope->kcache || !rope->vcache) return false;
+  if (!aligned(rope->k, 16) || !aligned(rope->v, 16) || !aligned(rope->cos_table, 16) || !aligned(rope->sin_table, 16) ||
+      !aligned(rope->kcache, 16) || !aligned(rope->vcache, 16))
+    return false;
+  *out = AttnRope{rope->k, rope->v, rope->cos_table, rope->sin_table, rope->kcache, rope->vcache};
+  return true;
+}
+}  // namespace
+
 size_t fuelq_attn_decode_workspace_bytes(int32_t n_heads) {
   return n_heads > 0 ? (size_t)n_heads * kAttnSplits * kAttnPartStride * sizeof(float) : 0;
 }
 
 int32_t fuelq_attn_decode(const float* q, const float* kcache, const float* vcache, float* out, const int32_t* pos,
                           int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
-                          size_t workspace_bytes, void* stream) {
+                          size_t workspace_bytes, const fuelq_rope* rope, void* stream) {
   if (head_dim != 128) return kNotSupported;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
   if (!q || !kcache || !vcache || !out || !pos) return kInvalidProblem;
   if (!workspace || workspace_bytes < fuelq_attn_decode_workspace_bytes(n_heads)) return kWorkspace;
   if (!aligned(q, 16) || !aligned(kcache, 16) || !aligned(vcache, 16) || !aligned(workspace, 16)) return kMisaligned;
+  AttnRope ar;
+  if (!make_attn_rope(rope, &ar)) return kInvalidProblem;
   cudaError_t e = launch(attn_partial_kernel, dim3((unsigned)n_heads, kAttnSplits), dim3(256), 0, (cudaStream_t)stream, q,
-                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale, ar);
   if (e != cudaSuccess) return kLaunchFailure;
   e = launch(attn_combine_kernel, dim3((unsigned)n_heads), dim3(128), 0, (cudaStream_t)stream, (const float*)workspace, out);
   return e == cudaSuccess ? kOk : kLaunchFailure;
@@ -919,7 +935,7 @@ int32_t fuelq_swiglu_q8k(const float* gate, const float* up, int64_t n, void* pa
 
 int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* vcache, const int32_t* pos, int32_t n_heads,
                               int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
-                              size_t workspace_bytes, void* packed, size_t packed_bytes, void* stream) {
+                              size_t workspace_bytes, void* packed, size_t packed_bytes, const fuelq_rope* rope, void* stream) {
   if (head_dim != 128) return kNotSupported;
   if (n_heads <= 0 || n_heads % 2 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
   if (!q || !kcache || !vcache || !pos) return kInvalidProblem;
@@ -927,8 +943,10 @@ int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* 
   if (!packed || packed_bytes < act_packed_bytes(kQ4K, 1, (int64_t)n_heads * 128)) return kWorkspace;
   if (!aligned(q, 16) || !aligned(kcache, 16) || !aligned(vcache, 16) || !aligned(workspace, 16) || !aligned(packed, 16))
     return kMisaligned;
+  AttnRope ar;
+  if (!make_attn_rope(rope, &ar)) return kInvalidProblem;
   cudaError_t e = launch(attn_partial_kernel, dim3((unsigned)n_heads, kAttnSplits), dim3(256), 0, (cudaStream_t)stream, q,
-                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale, ar);
   if (e != cudaSuccess) return kLaunchFailure;
   const ActPlanes a = act_planes(packed, kQ4K, 1, (int64_t)n_heads * 128);
   e = launch(attn_combine_q8k_kernel, dim3((unsigned)(n_heads / 2)), dim3(32), 0, (cudaStream_t)stream,
@@ -1231,7 +1249,8 @@ int32_t fuelq_swiglu_q8k_peer(const float* gate, const float* up, int64_t n_loca
 int32_t fuelq_attn_decode_q8k_peer(const float* q, const float* kcache, const float* vcache, const int32_t* pos,
                                    int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale,
                                    void* workspace, size_t workspace_bytes, int32_t head0, int64_t k_total,
-                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream) {
+                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, const fuelq_rope* rope,
+                                   void* stream) {
   if (head_dim != 128) return kNotSupported;
   if (n_heads <= 0 || n_heads % 2 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
   if (head0 < 0 || head0 % 2 || k_total % 256 || (int64_t)(head0 + n_heads) * 128 > k_total) return kInvalidProblem;
@@ -1245,8 +1264,10 @@ int32_t fuelq_attn_decode_q8k_peer(const float* q, const float* kcache, const fl
   PeerStampedPlanes pp;
   sc = make_peer_planes(act_dst, k_total, c.world, &pp);
   if (sc != kOk) return sc;
+  AttnRope ar;
+  if (!make_attn_rope(rope, &ar)) return kInvalidProblem;
   cudaError_t e = launch(attn_partial_kernel, dim3((unsigned)n_heads, kAttnSplits), dim3(256), 0, (cudaStream_t)stream, q,
-                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale);
+                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale, ar);
   if (e != cudaSuccess) return kLaunchFailure;
   e = launch(attn_combine_q8k_peer_kernel, dim3((unsigned)(n_heads / 2)), dim3(32), 0, (cudaStream_t)stream,
              (const float*)workspace, (int)(head0 / 2), pp, c);

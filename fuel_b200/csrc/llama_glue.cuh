@@ -85,8 +85,8 @@ __global__ void __launch_bounds__(128) rope_store_kernel(float* q, const float* 
     float* x = q + (size_t)head * hd;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
       const float lo = x[i], hi = x[i + half];
-      x[i] = lo * cs[i] - hi * sn[i];
-      x[i + half] = hi * cs[i + half] + lo * sn[i + half];
+      x[i] = __fsub_rn(__fmul_rn(lo, cs[i]), __fmul_rn(hi, sn[i]));
+      x[i + half] = __fadd_rn(__fmul_rn(hi, cs[i + half]), __fmul_rn(lo, sn[i + half]));
     }
   } else {
     const int kh = head - n_heads;
@@ -96,8 +96,8 @@ __global__ void __launch_bounds__(128) rope_store_kernel(float* q, const float* 
     const float* vs = v + (size_t)kh * hd;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
       const float lo = x[i], hi = x[i + half];
-      kd[i] = lo * cs[i] - hi * sn[i];
-      kd[i + half] = hi * cs[i + half] + lo * sn[i + half];
+      kd[i] = __fsub_rn(__fmul_rn(lo, cs[i]), __fmul_rn(hi, sn[i]));
+      kd[i + half] = __fadd_rn(__fmul_rn(hi, cs[i + half]), __fmul_rn(lo, sn[i + half]));
       vd[i] = vs[i];
       vd[i + half] = vs[i + half];
     }
@@ -112,18 +112,48 @@ __global__ void __launch_bounds__(128) rope_store_kernel(float* q, const float* 
 constexpr int kAttnSplits = 8;
 constexpr int kAttnPartStride = 132;  // 128 outputs + max + sum (+ pad)
 
+// Rotate-half RoPE of a 128-wide head held four elements per lane (lane l: elements 4l..4l+3; the partner
+// element i +- 64 lives in lane l ^ 16). Same operations and roundings as rope_store_kernel.
+__device__ __forceinline__ float4 rope128(float4 x, float4 cs, float4 sn, int lane) {
+  float4 o;
+  o.x = __shfl_xor_sync(0xffffffffu, x.x, 16), o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+  o.z = __shfl_xor_sync(0xffffffffu, x.z, 16), o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+  float4 r;
+  if (lane < 16) {  // x[i] = lo * cos[i] - hi * sin[i]
+    r.x = __fsub_rn(__fmul_rn(x.x, cs.x), __fmul_rn(o.x, sn.x)), r.y = __fsub_rn(__fmul_rn(x.y, cs.y), __fmul_rn(o.y, sn.y));
+    r.z = __fsub_rn(__fmul_rn(x.z, cs.z), __fmul_rn(o.z, sn.z)), r.w = __fsub_rn(__fmul_rn(x.w, cs.w), __fmul_rn(o.w, sn.w));
+  } else {          // x[i + 64] = hi * cos[i + 64] + lo * sin[i + 64]
+    r.x = __fadd_rn(__fmul_rn(x.x, cs.x), __fmul_rn(o.x, sn.x)), r.y = __fadd_rn(__fmul_rn(x.y, cs.y), __fmul_rn(o.y, sn.y));
+    r.z = __fadd_rn(__fmul_rn(x.z, cs.z), __fmul_rn(o.z, sn.z)), r.w = __fadd_rn(__fmul_rn(x.w, cs.w), __fmul_rn(o.w, sn.w));
+  }
+  return r;
+}
+
+// With `rope` set the kernel also does rope_store_kernel's work: q arrives unrotated and is rotated on the fly; the
+// current token's k (rotated) and v come from `rope.k` / `rope.v` instead of the cache, and the first head of each
+// kv group appends them to the caches (nobody reads cache row *pos in this launch).
+struct AttnRope {
+  const float* k;     // [n_kv][128] unrotated, or null: q is already rotated and the caches hold position *pos
+  const float* v;     // [n_kv][128]
+  const float* cosT;  // [max_seq][128]
+  const float* sinT;
+  float* kc_w;        // the caches, writable
+  float* vc_w;
+};
+
 __global__ void __launch_bounds__(256) attn_partial_kernel(const float* q, const float* kc,
                                                            const float* vc, float* part,
                                                            const int* pos_p, int n_heads, int n_kv,
-                                                           int max_seq, float scale) {
+                                                           int max_seq, float scale, const AttnRope rope) {
   __shared__ float scores[1024];
   __shared__ float red[8];
   __shared__ float4 vacc[8][32];
   pdl_launch_dependents();
   pdl_wait();
   constexpr int hd = 128;
-  const int head = blockIdx.x, split = blockIdx.y, kvh = head / (n_heads / n_kv);
-  const int n_ctx = *pos_p + 1;
+  const int head = blockIdx.x, split = blockIdx.y, group = n_heads / n_kv, kvh = head / group;
+  const int pos = *pos_p;
+  const int n_ctx = pos + 1;
   const int chunk = (n_ctx + kAttnSplits - 1) / kAttnSplits;  // <= 1024 for max_seq <= 8192
   const int t0 = split * chunk, t1 = min(t0 + chunk, n_ctx);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,10 +163,23 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float* q, const
     if (threadIdx.x == 0) out[128] = -INFINITY, out[129] = 0.f;
     return;
   }
-  const float4 qv = reinterpret_cast<const float4*>(q + (size_t)head * hd)[lane];
+  float4 qv = reinterpret_cast<const float4*>(q + (size_t)head * hd)[lane];
+  float4 knew = make_float4(0.f, 0.f, 0.f, 0.f), vnew = knew;
+  const bool fused = rope.k != nullptr;
+  if (fused) {
+    const float4 cs = reinterpret_cast<const float4*>(rope.cosT + (size_t)pos * hd)[lane];
+    const float4 sn = reinterpret_cast<const float4*>(rope.sinT + (size_t)pos * hd)[lane];
+    qv = rope128(qv, cs, sn, lane);
+    knew = rope128(reinterpret_cast<const float4*>(rope.k + (size_t)kvh * hd)[lane], cs, sn, lane);
+    vnew = reinterpret_cast<const float4*>(rope.v + (size_t)kvh * hd)[lane];
+    if (warp == 0 && head == kvh * group && pos >= t0 && pos < t1) {  // one writer per kv head
+      reinterpret_cast<float4*>(rope.kc_w + ((size_t)kvh * max_seq + pos) * hd)[lane] = knew;
+      reinterpret_cast<float4*>(rope.vc_w + ((size_t)kvh * max_seq + pos) * hd)[lane] = vnew;
+    }
+  }
   const float* kbase = kc + (size_t)kvh * max_seq * hd;
   for (int t = t0 + warp; t < t1; t += 8) {
-    const float4 kv = reinterpret_cast<const float4*>(kbase + (size_t)t * hd)[lane];
+    const float4 kv = (fused && t == pos) ? knew : reinterpret_cast<const float4*>(kbase + (size_t)t * hd)[lane];
     float s = qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
@@ -162,7 +205,7 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float* q, const
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int t = t0 + warp; t < t1; t += 8) {  // a warp per V row, a lane per four columns
     const float pw = scores[t - t0];
-    const float4 vv = reinterpret_cast<const float4*>(vbase + (size_t)t * hd)[lane];
+    const float4 vv = (fused && t == pos) ? vnew : reinterpret_cast<const float4*>(vbase + (size_t)t * hd)[lane];
     a.x += pw * vv.x, a.y += pw * vv.y, a.z += pw * vv.z, a.w += pw * vv.w;
   }
   vacc[warp][lane] = a;

@@ -213,9 +213,11 @@ class QLlama:
             wd = rows(init_weight(c.dim, c.ffn_dim, s0 + 7, device), r * c.dim // g, (r + 1) * c.dim // g)
             tq, tv, to, tg, td = (mix("attn_q", li), mix("attn_v", li), mix("attn_output", li), mix("ffn_gate", li),
                                   mix("ffn_down", li))
+            # q, k (and v, where it has the same format) are one stacked matrix: one launch instead of two or three
+            qkv_rows = torch.cat([wq, wk, wv]) if tv == tq else torch.cat([wq, wk])
             self.layers.append(dict(
-                qk=_Linear(tq, _quantize(tq, torch.cat([wq, wk])), qd + kvd, c.dim),
-                v=_Linear(tv, _quantize(tv, wv), kvd, c.dim),
+                qk=_Linear(tq, _quantize(tq, qkv_rows), qkv_rows.shape[0], c.dim),
+                v=None if tv == tq else _Linear(tv, _quantize(tv, wv), kvd, c.dim),
                 o=_Linear(to, _quantize(to, wo), c.dim // g, c.dim),
                 gu=_Linear(tg, _quantize(tg, torch.cat([wg, wu])), 2 * fl, c.dim),
                 down=_Linear(td, _quantize(td, wd), c.dim // g, c.ffn_dim),
@@ -237,8 +239,9 @@ class QLlama:
         self.pos = torch.zeros(1, dtype=torch.int32, device=device)
         self.x = torch.zeros(c.dim, **f32)
         self.h = torch.zeros(c.dim, **f32)
-        self.qk = torch.zeros(qd + kvd, **f32)
-        self.v = torch.zeros(kvd, **f32)
+        self.qkv = torch.zeros(qd + 2 * kvd, **f32)   # q | k | v of the current token
+        self.qk = self.qkv[:qd + kvd]
+        self.v = self.qkv[qd + kvd:]
         self.attn_l = torch.zeros(qd, **f32)
         self.o_l = torch.zeros(c.dim // g, **f32)
         self.gu = torch.zeros(2 * fl, **f32)
@@ -256,12 +259,22 @@ class QLlama:
         nb = max(_L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.dim), _L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.ffn_dim))
         self.packed = torch.zeros(nb, dtype=torch.uint8, device=device)
         self.attn_ws = torch.zeros(max(_L.fuelq_attn_decode_workspace_bytes(self.hl), 16), dtype=torch.uint8, device=device)
+        # per layer: what the attention call needs to rotate q/k itself and append k, v to that layer's caches
+        import ctypes
+        self.ropes = []
+        for l in self.layers:
+            rp = _lib.Rope()
+            rp.k, rp.v = self.qkv.data_ptr() + 4 * qd, self.qkv.data_ptr() + 4 * (qd + kvd)
+            rp.cos_table, rp.sin_table = self.cos.data_ptr(), self.sin.data_ptr()
+            rp.kcache, rp.vcache = l["kc"].data_ptr(), l["vc"].data_ptr()
+            self.ropes.append(rp)
+        self.rope_refs = [ctypes.byref(rp) for rp in self.ropes]
         self.peer = None
         if comm == "peer":
             self._init_peer()
         self.graph = None
         self.fused = True  # single-GPU step uses the fused producers
-        self.weight_bytes = (sum(l[k].blocks.numel() for l in self.layers for k in ("qk", "v", "o", "gu", "down"))
+        self.weight_bytes = (sum(l[k].blocks.numel() for l in self.layers for k in ("qk", "v", "o", "gu", "down") if l[k] is not None)
                              + self.head.blocks.numel())
 
     # ---- one decode step: token, pos -> next_token; pos += 1; token = next_token
@@ -324,14 +337,12 @@ class QLlama:
             sq = 4 * li  # exchange points of this layer: attention, o, SwiGLU, down
             _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), delta, l["attn_norm"].data_ptr(), c.dim, c.norm_eps, pk, pkn,
                                                  pr, wait, st), "add_rmsnorm_q8k_peer")
-            l["qk"].matvec_packed(self.packed, self.qk, st)
-            l["v"].matvec_packed(self.packed, self.v, st)
-            _check(_L.fuelq_rope_store(self.qk.data_ptr(), self.qk.data_ptr() + 4 * qd, self.v.data_ptr(), l["kc"].data_ptr(),
-                                       l["vc"].data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
-                                       self.hl, self.kvl, c.head_dim, c.max_seq, st), "rope_store")
+            l["qk"].matvec_packed(self.packed, self.qkv if l["v"] is None else self.qk, st)
+            if l["v"] is not None:
+                l["v"].matvec_packed(self.packed, self.v, st)
             _check(_L.fuelq_attn_decode_q8k_peer(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.pos.data_ptr(),
                                                  self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
-                                                 self.attn_ws.numel(), r * self.hl, c.dim, self.dst_pattn, pr, sq, st),
+                                                 self.attn_ws.numel(), r * self.hl, c.dim, self.dst_pattn, pr, sq, self.rope_refs[li], st),
                    "attn_decode_q8k_peer")
             o = l["o"]
             _check(_L.fuelq_qmatmul_packed_peer(int(o.dtype), c.dim, dl, o.blocks.data_ptr(), self.own_pattn, self.dst_o, r * dl,
@@ -366,17 +377,15 @@ class QLlama:
                "fuelq_embed_rows")
         delta = None
         qd = self.hl * c.head_dim
-        for l in self.layers:
+        for li, l in enumerate(self.layers):
             _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), delta, l["attn_norm"].data_ptr(), c.dim, c.norm_eps, pk, pkn, st),
                    "add_rmsnorm_q8k")
-            l["qk"].matvec_packed(self.packed, self.qk, st)
-            l["v"].matvec_packed(self.packed, self.v, st)
-            _check(_L.fuelq_rope_store(self.qk.data_ptr(), self.qk.data_ptr() + 4 * qd, self.v.data_ptr(), l["kc"].data_ptr(),
-                                       l["vc"].data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
-                                       self.hl, self.kvl, c.head_dim, c.max_seq, st), "rope_store")
+            l["qk"].matvec_packed(self.packed, self.qkv if l["v"] is None else self.qk, st)
+            if l["v"] is not None:
+                l["v"].matvec_packed(self.packed, self.v, st)
             _check(_L.fuelq_attn_decode_q8k(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.pos.data_ptr(),
                                             self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
-                                            self.attn_ws.numel(), pk, pkn, st), "attn_decode_q8k")
+                                            self.attn_ws.numel(), pk, pkn, self.rope_refs[li], st), "attn_decode_q8k")
             l["o"].matvec_packed(self.packed, self.o_l, st)
             _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), self.o_l.data_ptr(), l["ffn_norm"].data_ptr(), c.dim, c.norm_eps,
                                             pk, pkn, st), "add_rmsnorm_q8k")
@@ -398,19 +407,17 @@ class QLlama:
         _check(_L.fuelq_embed_rows(int(T.Q4K), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
                "fuelq_embed_rows")
         delta = None
-        for l in self.layers:
+        for li, l in enumerate(self.layers):
             _check(_L.fuelq_add_rmsnorm(self.x.data_ptr(), delta.data_ptr() if delta is not None else None,
                                         l["attn_norm"].data_ptr(), self.h.data_ptr(), 1, c.dim, c.norm_eps, st), "add_rmsnorm")
             self._quant(self.h, c.dim, st)
-            l["qk"].matvec_packed(self.packed, self.qk, st)
-            l["v"].matvec_packed(self.packed, self.v, st)
+            l["qk"].matvec_packed(self.packed, self.qkv if l["v"] is None else self.qk, st)
+            if l["v"] is not None:
+                l["v"].matvec_packed(self.packed, self.v, st)
             qd = self.hl * c.head_dim
-            _check(_L.fuelq_rope_store(self.qk.data_ptr(), self.qk.data_ptr() + 4 * qd, self.v.data_ptr(), l["kc"].data_ptr(),
-                                       l["vc"].data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), self.pos.data_ptr(),
-                                       self.hl, self.kvl, c.head_dim, c.max_seq, st), "rope_store")
             _check(_L.fuelq_attn_decode(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.attn_l.data_ptr(),
                                         self.pos.data_ptr(), self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
-                                        self.attn_ws.numel(), st), "attn_decode")
+                                        self.attn_ws.numel(), self.rope_refs[li], st), "attn_decode")
             self._gather(self.attn, self.attn_l)
             self._quant(self.attn, c.dim, st)
             l["o"].matvec_packed(self.packed, self.o_l, st)

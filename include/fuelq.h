@@ -180,10 +180,21 @@ int32_t fuelq_rope_store(float* q, const float* k, const float* v, float* kcache
                          const float* sin_table, const int32_t* pos, int32_t n_heads, int32_t n_kv, int32_t head_dim,
                          int32_t max_seq, void* stream);
 /* out[h] = softmax(q[h] . K[kv(h)][0..*pos]^T * scale) . V, max-subtracted softmax (byte_kernels.rs:2259-2305). head_dim 128. */
+/* Optional fusion of fuelq_rope_store into the attention call: with a non-null `rope`, q arrives unrotated, the current
+ * token's k and v are read from rope->k / rope->v (k rotated on the fly), and the call appends them to the caches
+ * itself - same values as fuelq_rope_store followed by the call with rope = NULL, one launch fewer. */
+typedef struct fuelq_rope {
+  const float* k;         /* [n_kv][head_dim], unrotated */
+  const float* v;         /* [n_kv][head_dim] */
+  const float* cos_table; /* [max_seq][head_dim] */
+  const float* sin_table;
+  float* kcache;          /* the caches passed to the call, writable */
+  float* vcache;
+} fuelq_rope;
 size_t fuelq_attn_decode_workspace_bytes(int32_t n_heads);
 int32_t fuelq_attn_decode(const float* q, const float* kcache, const float* vcache, float* out, const int32_t* pos,
                           int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
-                          size_t workspace_bytes, void* stream);
+                          size_t workspace_bytes, const fuelq_rope* rope, void* stream);
 /* Fused forms for a single-GPU step: the plain call followed by fuelq_quantize_act_packed (k-quant weights,
  * m = 1), written straight into the packed planes with the same bytes, one launch instead of two.
  * dim / n multiples of 256. */
@@ -192,7 +203,7 @@ int32_t fuelq_add_rmsnorm_q8k(float* x, const float* delta, const float* gain, i
 int32_t fuelq_swiglu_q8k(const float* gate, const float* up, int64_t n, void* packed, size_t packed_bytes, void* stream);
 int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* vcache, const int32_t* pos, int32_t n_heads,
                               int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
-                              size_t workspace_bytes, void* packed, size_t packed_bytes, void* stream);
+                              size_t workspace_bytes, void* packed, size_t packed_bytes, const fuelq_rope* rope, void* stream);
 /* ---- Mixture-of-experts block with quantized experts (the grouped / indexed quantized mat-vec).
  * Replaces the slot the reference leaves empty (indexed_moe_forward, fuel-backend-contract/src/quantized.rs:29-103;
  * the CUDA implementation was retired and its grouped kernel is only named: fuel-cuda-backend/src/quantized.rs:292-304)
@@ -270,7 +281,8 @@ int32_t fuelq_swiglu_q8k_peer(const float* gate, const float* up, int64_t n_loca
 int32_t fuelq_attn_decode_q8k_peer(const float* q, const float* kcache, const float* vcache, const int32_t* pos,
                                    int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale,
                                    void* workspace, size_t workspace_bytes, int32_t head0, int64_t k_total,
-                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream);
+                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, const fuelq_rope* rope,
+                                   void* stream);
 /* fuelq_argmax_last over a vector buffer of n (even) words filled through wait_seq; then *epoch += 1
  * (epoch must be peers->epoch) */
 int32_t fuelq_argmax_last_peer(const void* x, int64_t n, int32_t* out_index, const fuelq_peers* peers, int32_t wait_seq,

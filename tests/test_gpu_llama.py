@@ -152,3 +152,50 @@ def test_exchange_wait_expires_with_an_error_code_and_the_context_stays_usable()
     y = ops.qmatmul(T.Q4K, torch.from_numpy(wb).cuda(), 64, torch.from_numpy(xa).cuda()).cpu().numpy()
     r = O.matmul(O.Q4K, xa, wb, 64)
     assert np.abs(y - r).max() <= 2e-6 * np.abs(r).max()
+
+
+@pytest.mark.parametrize("n_heads,n_kv,pos", [(4, 4, 0), (8, 2, 37), (4, 4, 300)])
+def test_rope_fused_into_attention_matches_rope_store(n_heads, n_kv, pos):
+    """fuelq_attn_decode with a rope argument = fuelq_rope_store followed by fuelq_attn_decode, bit for bit,
+    and leaves the same caches behind."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import ctypes
+
+    from fuel_b200 import _lib
+    from fuel_b200.llama import LlamaConfig, rope_tables
+    L = _lib.lib
+    hd, max_seq = 128, 512
+    cos, sin = rope_tables(LlamaConfig(max_seq=max_seq))
+    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    g = torch.Generator(device="cuda")
+    g.manual_seed(pos)
+    qkv = torch.randn((n_heads + 2 * n_kv) * hd, generator=g, device="cuda")
+    kc0 = torch.randn(n_kv, max_seq, hd, generator=g, device="cuda")
+    vc0 = torch.randn(n_kv, max_seq, hd, generator=g, device="cuda")
+    posd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    ws = torch.zeros(L.fuelq_attn_decode_workspace_bytes(n_heads), dtype=torch.uint8, device="cuda")
+    scale = 1.0 / np.sqrt(hd)
+    qd, kvd = n_heads * hd, n_kv * hd
+
+    def run(fused):
+        x, kc, vc = qkv.clone(), kc0.clone(), vc0.clone()
+        out = torch.zeros(qd, device="cuda")
+        rope = None
+        if fused:
+            rp = _lib.Rope()
+            rp.k, rp.v = x.data_ptr() + 4 * qd, x.data_ptr() + 4 * (qd + kvd)
+            rp.cos_table, rp.sin_table, rp.kcache, rp.vcache = cos.data_ptr(), sin.data_ptr(), kc.data_ptr(), vc.data_ptr()
+            rope = ctypes.byref(rp)
+        else:
+            _lib.check(L.fuelq_rope_store(x.data_ptr(), x.data_ptr() + 4 * qd, x.data_ptr() + 4 * (qd + kvd), kc.data_ptr(),
+                                          vc.data_ptr(), cos.data_ptr(), sin.data_ptr(), posd.data_ptr(), n_heads, n_kv, hd,
+                                          max_seq, None), "rope_store")
+        _lib.check(L.fuelq_attn_decode(x.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(), posd.data_ptr(), n_heads,
+                                       n_kv, hd, max_seq, scale, ws.data_ptr(), ws.numel(), rope, None), "attn_decode")
+        torch.cuda.synchronize()
+        return out, kc, vc
+
+    a, b = run(False), run(True)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert not torch.equal(a[1], kc0)      # the cache row was really appended
