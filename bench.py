@@ -186,6 +186,7 @@ def run_side_workload(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0)
+    L.fuelq_set_option(_lib.OPT_PREFILL_TF32, 1 if args.tf32 else 0)
     st = torch.cuda.Stream(dev)
     peak, peak_kind = _peaks()
     gen = torch.Generator(device=dev)
@@ -213,7 +214,9 @@ def run_side_workload(args):
                 for m in (1, 2, 4, 8, 16, 32, 64, 128):
                     print(json.dumps(matmul_case(t, name, n, k, m, 12, 20)), flush=True)
     elif args.workload == "prefill":
-        print(json.dumps(matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10)), flush=True)
+        line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10)
+        line["operands"] = "tf32" if args.tf32 else "bf16"
+        print(json.dumps(line), flush=True)
     else:
         E, H, F, K, N, copies = 128, 2048, 768, 8, 256, 4
         blocks = []
@@ -349,6 +352,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step (profiling runs use fewer)")
+    ap.add_argument("--tf32", action="store_true", help="--workload prefill: tensor-core path in tf32 instead of bf16")
+    ap.add_argument("--decode-grid", type=int, default=0, help="thread blocks of the decode mat-vec (0: the library's choice, two per SM)")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-architecture decode that is reported beside the metric")
     ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe"],
                     help="decode: the headline line (default). sweep / prefill / moe: BASELINE configs 2 / 3 / 5 on one GPU, "
@@ -377,6 +382,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     L = _lib.lib
     _lib.check(L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0), "set_option")
+    _lib.check(L.fuelq_set_option(_lib.OPT_DECODE_GRID, args.decode_grid), "set_option")
 
     ws = make_weights(torch, ops, T, device, rank)
     g = torch.Generator(device=device)

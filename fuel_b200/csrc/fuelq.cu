@@ -34,6 +34,7 @@ struct Options {
   int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
   int64_t moe_kernel = 0;     // development switch: 1 = grouped mat-vec on the dp4a kernel even where the tensor-core form fits
   int64_t peer_wait_ms = 4000; // deadline of the exchange polls in the tensor-parallel kernels
+  int64_t prefill_tf32 = 0;   // tensor-core path in tf32 instead of bf16
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
 };
 Options g_opt;
@@ -510,13 +511,13 @@ bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   if (type == kQ4K && max_m == 16 && g_opt.decode_kernel == 0 && g_opt.moe_kernel != 1 && mma_plan_fits(k)) max_m = 32;
   return (type == kQ4K || type == kQ6K || type == kQ8_0) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }
-size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * 2, 256); }
+size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * (g_opt.prefill_tf32 ? 4 : 2), 256); }
 
 // tensor map of the bf16 activation matrix [M][K]: boxes of 64 columns x tile_m rows, 128-byte swizzle, zero fill
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, CUtensorMap* map) {
+bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, bool f32, CUtensorMap* map) {
   static EncodeTiledFn encode = nullptr;
   if (!encode) {
     void* fn = nullptr;
@@ -527,19 +528,19 @@ bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, CUtensorMap* m
     encode = (EncodeTiledFn)fn;
   }
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
-  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kPfTileK, (cuuint32_t)tile_m};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * (f32 ? 4 : 2)};
+  const cuuint32_t box[2] = {(cuuint32_t)(f32 ? 32 : kPfTileK), (cuuint32_t)tile_m};  // 128 bytes x tile_m rows
   const cuuint32_t estr[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xb), dims, strides, box, estr,
+  return encode(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xb), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <class Fmt, int kTileM>
+template <class Fmt, int kTileM, bool kTf32 = false>
 cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t stream) {
   constexpr size_t smem = 1024 + (size_t)kPfStages * (kPfTileN * 128 + kTileM * 128) + sizeof(PrefillSmem) + 64;
   static bool attr_set[64] = {};
-  auto kern = prefill_gemm_kernel<Fmt, kTileM>;
+  auto kern = prefill_gemm_kernel<Fmt, kTileM, kTf32>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
@@ -549,7 +550,7 @@ cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t 
     attr_set[dev] = true;
   }
   CUtensorMap xmap;
-  if (!make_x_map(xb, p.M, p.K, kTileM, &xmap)) return cudaErrorUnknown;
+  if (!make_x_map(xb, p.M, p.K, kTileM, kTf32, &xmap)) return cudaErrorUnknown;
   const dim3 grid((unsigned)((p.N + kPfTileN - 1) / kPfTileN), (unsigned)((p.M + kTileM - 1) / kTileM));
   kern<<<grid, kPfThreads, smem, stream>>>(p, xmap);
   return cudaGetLastError();
@@ -557,9 +558,13 @@ cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t 
 
 int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const float* x, float* y, void* workspace,
                      cudaStream_t stream) {
-  __nv_bfloat16* xb = (__nv_bfloat16*)workspace;
+  const bool tf32 = g_opt.prefill_tf32 != 0;
+  void* xb = workspace;  // the activations in the tensor cores' operand type: bf16, or f32 rounded to tf32
   const int64_t n4 = m * k / 4;
-  f32_to_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, xb);
+  if (tf32)
+    f32_to_tf32_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, (float*)xb);
+  else
+    f32_to_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, (__nv_bfloat16*)xb);
   if (cudaGetLastError() != cudaSuccess) return kLaunchFailure;
   PrefillParams p;
   p.w = (const uint8_t*)w;
@@ -573,12 +578,16 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   DeviceInfo* di;
   if (!device_info(&di)) return kLaunchFailure;
   const bool wide = m > 128 && ((n + kPfTileN - 1) / kPfTileN) * ((m + 255) / 256) >= di->sm_count;
+#define FQ_PREFILL(FMT)                                                                                                   \
+  e = tf32 ? (wide ? launch_prefill<FMT, 256, true>(p, xb, stream) : launch_prefill<FMT, 128, true>(p, xb, stream))       \
+           : (wide ? launch_prefill<FMT, 256>(p, xb, stream) : launch_prefill<FMT, 128>(p, xb, stream))
   switch (type) {
-    case kQ4K: e = wide ? launch_prefill<Q4KPrefill, 256>(p, xb, stream) : launch_prefill<Q4KPrefill, 128>(p, xb, stream); break;
-    case kQ6K: e = wide ? launch_prefill<Q6KPrefill, 256>(p, xb, stream) : launch_prefill<Q6KPrefill, 128>(p, xb, stream); break;
-    case kQ8_0: e = wide ? launch_prefill<Q8_0Prefill, 256>(p, xb, stream) : launch_prefill<Q8_0Prefill, 128>(p, xb, stream); break;
+    case kQ4K: FQ_PREFILL(Q4KPrefill); break;
+    case kQ6K: FQ_PREFILL(Q6KPrefill); break;
+    case kQ8_0: FQ_PREFILL(Q8_0Prefill); break;
     default: return kNotSupported;
   }
+#undef FQ_PREFILL
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
@@ -637,6 +646,7 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 107: g_opt.moe_kernel = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
+    case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PEER_WAIT_MS:
       if (value < 1 || value > 60000) return kInvalidProblem;
       g_opt.peer_wait_ms = value;
@@ -654,6 +664,7 @@ int64_t fuelq_get_option(int32_t key) {
     case FUELQ_OPT_L2_PREFETCH: return g_opt.l2_prefetch;
     case FUELQ_OPT_FUSED_QUANT: return g_opt.fused_quant;
     case FUELQ_OPT_PEER_WAIT_MS: return g_opt.peer_wait_ms;
+    case FUELQ_OPT_PREFILL_TF32: return g_opt.prefill_tf32;
     default: return -1;
   }
 }

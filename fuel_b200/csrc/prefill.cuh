@@ -61,6 +61,19 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// same, operands read as tf32 (f32 words whose low 13 mantissa bits are ignored); K = 8 per instruction
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t to_tf32(float x) {  // round to nearest (ties away) at 10 mantissa bits
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -105,6 +118,10 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 // Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// the same with A and B as tf32 (format code 2)
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // ---- per-format dequantization of one weight row's 64-element K stage into 8 x 16-byte bf16 chunks ----
@@ -180,6 +197,31 @@ struct Q4KPrefill {
     convert_part(q, it, 2 * half + 1, o2);
     out[2] = o2[0], out[3] = o2[1];
   }
+  // tf32 form: stage `it` is ONE 32-element sub-block (block it / 8, sub-block it % 8); part = which 16 of them.
+  // Values are the exact f32 dequantization rounded to tf32.
+  __device__ __forceinline__ static void stage16(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
+    const int blk = it >> 3, j = it & 7, g = j >> 1, nib = j & 1;
+    const uint8_t* b = row + blk * Q4KL::kBytes;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(b);
+    const uint4 q = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16 * part);
+    const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
+    const uint32_t sh = 16 * (g & 1) + 8 * nib;
+    uint32_t sc, mn;
+    if (g < 2) {
+      sc = (hdr.y >> sh) & 0x3fu;
+      mn = (hdr.z >> sh) & 0x3fu;
+    } else {
+      sc = ((hdr.w >> sh) & 0x0fu) | (((hdr.y >> (sh + 6)) & 0x03u) << 4);
+      mn = ((hdr.w >> (sh + 4)) & 0x0fu) | (((hdr.z >> (sh + 6)) & 0x03u) << 4);
+    }
+    const float d1 = d * (float)sc, m1 = dmin * (float)mn;
+    const uint32_t w[4] = {q.x >> (4 * nib), q.y >> (4 * nib), q.z >> (4 * nib), q.w >> (4 * nib)};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      out[c].x = to_tf32(d1 * (float)(w[c] & 0xf) - m1), out[c].y = to_tf32(d1 * (float)((w[c] >> 8) & 0xf) - m1);
+      out[c].z = to_tf32(d1 * (float)((w[c] >> 16) & 0xf) - m1), out[c].w = to_tf32(d1 * (float)((w[c] >> 24) & 0xf) - m1);
+    }
+  }
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
     Raw r;
     load(row, it, r);
@@ -228,6 +270,17 @@ struct Q8_0Prefill {
   __device__ __forceinline__ static void load_part(const uint8_t*, int, int, RawQ&) {}
   __device__ __forceinline__ static void convert_part(const RawQ&, int, int, uint4 (&)[2]) {}
   __device__ __forceinline__ static void convert_half(const Raw&, int, int, uint4 (&)[4]) {}
+  // tf32 form: stage `it` is block `it`; part = which 16 of its 32 elements
+  __device__ __forceinline__ static void stage16(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
+    const uint8_t* b = row + (size_t)it * Q8_0L::kBytes;
+    const float d = h2f_bits(ldg_u16(b));
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t v0 = ldg_u16(b + Q8_0L::kOffQs + 16 * part + 4 * c), v1 = ldg_u16(b + Q8_0L::kOffQs + 16 * part + 4 * c + 2);
+      out[c].x = to_tf32((float)(int8_t)(v0 & 0xff) * d), out[c].y = to_tf32((float)(int8_t)(v0 >> 8) * d);
+      out[c].z = to_tf32((float)(int8_t)(v1 & 0xff) * d), out[c].w = to_tf32((float)(int8_t)(v1 >> 8) * d);
+    }
+  }
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -257,6 +310,31 @@ struct Q6KPrefill {
   __device__ __forceinline__ static void load_part(const uint8_t*, int, int, RawQ&) {}
   __device__ __forceinline__ static void convert_part(const RawQ&, int, int, uint4 (&)[2]) {}
   __device__ __forceinline__ static void convert_half(const Raw&, int, int, uint4 (&)[4]) {}
+  // tf32 form: stage `it` is 32 consecutive elements: block it / 8, half (it / 4) % 2, quad it % 4 (elements
+  // 128*half + 32*quad + l); part = which 16 of them (l = 16*part ..), which share one scale
+  __device__ __forceinline__ static void stage16(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
+    const int blk = it >> 3, half = (it >> 2) & 1, quad = it & 3;
+    const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
+    const float d = h2f_bits(ldg_u16(b + Q6KL::kOffD));
+    const uint8_t* ql = b + Q6KL::kOffQl + 64 * half + 32 * (quad & 1) + 16 * part;
+    const uint8_t* qh = b + Q6KL::kOffQh + 32 * half + 16 * part;
+    const int sci = 8 * half + 2 * quad + part;  // scale index: 8*half + l/16 + 2*quad
+    const uint32_t scw = ldg_u16(b + Q6KL::kOffScales + (sci & ~1));
+    const float s = d * (float)(int8_t)((scw >> (8 * (sci & 1))) & 0xff);
+    const int nsh = 4 * (quad >> 1), hsh = 2 * quad;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t vals[4];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const uint32_t a = ldg_u16(ql + 4 * c + 2 * h2), h = ldg_u16(qh + 4 * c + 2 * h2);
+        const int q0 = (int)(((a & 0xff) >> nsh) & 0xf) | (int)((((h & 0xff) >> hsh) & 3) << 4);
+        const int q1 = (int)(((a >> 8) >> nsh) & 0xf) | (int)((((h >> 8) >> hsh) & 3) << 4);
+        vals[2 * h2] = to_tf32(s * (float)(q0 - 32)), vals[2 * h2 + 1] = to_tf32(s * (float)(q1 - 32));
+      }
+      out[c] = make_uint4(vals[0], vals[1], vals[2], vals[3]);
+    }
+  }
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
     const int blk = it >> 2, half = (it >> 1) & 1, sub = it & 1;
     const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
@@ -290,7 +368,9 @@ struct PrefillSmem {
   int abort_flag;
 };
 
-template <class Fmt, int kTileM>
+// kTf32: operands in tf32 instead of bf16 - stages are 32 wide (one 128-byte row of f32), activations are the f32
+// matrix rounded to tf32 by the pre-pass, half the MMA rate, about eight times smaller rounding error.
+template <class Fmt, int kTileM, bool kTf32 = false>
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t pf_smem[];
   // [stage][ weights 128 x 128 B | activations kTileM x 128 B ], each 1024-byte aligned; control block after
@@ -301,7 +381,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kPfTileN, m0 = blockIdx.y * kTileM;
-  const int n_iter = p.K / kPfTileK;
+  constexpr int kStageK = kTf32 ? 32 : kPfTileK;  // elements per 128-byte row
+  const int n_iter = p.K / kStageK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPfStages; ++s) {
@@ -336,7 +417,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
       else Fmt::load(row, it, dst_raw);
     };
     RawT r0, r1, r2;
-    if (Fmt::kSplitLoad && live) {
+    if (!kTf32 && Fmt::kSplitLoad && live) {
       if (n_iter > 0) load_raw(0, r0);
       if (n_iter > 1) load_raw(1, r1);
       if (n_iter > 2) load_raw(2, r2);
@@ -349,11 +430,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
       }
       if (t == 0) {  // the stage is free: its activation tile, rows m0.. x columns 64*it.., as one copy
         mbar_arrive_expect_tx(&sm->xfull[s], (uint32_t)kXBytes);
-        tma_load_2d(base_u32 + s * kStageBytes + kWBytes, &xmap, it * kPfTileK, m0, &sm->xfull[s]);
+        tma_load_2d(base_u32 + s * kStageBytes + kWBytes, &xmap, it * kStageK, m0, &sm->xfull[s]);
         x_issued = it + 1;
       }
       uint8_t* dst = base + s * kStageBytes + r * 128;
-      if constexpr (Fmt::kSplitLoad) {
+      if constexpr (kTf32) {
+        static_assert(!kTf32 || kPfDequantWarps == 8, "the tf32 form splits a row's 32 elements between two threads");
+        uint4 out[4];
+        if (live) {
+          Fmt::stage16(row, it, part, out);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + (((4 * part + c) ^ (r & 7)) << 4)) = out[c];
+      } else if constexpr (Fmt::kSplitLoad) {
         constexpr int kChunks = kQuarters ? 2 : 4;  // 16-byte chunks this thread writes
         uint4 out[4];
         if (live) {
@@ -395,7 +487,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
     }
   } else if (lane == 0) {
     // ---------------- MMA issue: one thread
-    constexpr uint32_t idesc = umma_idesc_bf16(kPfTileN, kTileM);
+    constexpr uint32_t idesc = kTf32 ? umma_idesc_tf32(kPfTileN, kTileM) : umma_idesc_bf16(kPfTileN, kTileM);
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -409,8 +501,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
       tc_fence_after();
       const uint32_t a_addr = base_u32 + s * kStageBytes, b_addr = a_addr + kWBytes;
 #pragma unroll
-      for (int kk = 0; kk < kPfTileK / 16; ++kk)  // 16 bf16 = 32 bytes along K per instruction
-        umma_bf16(tmem_d, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc, (it | kk) != 0);
+      for (int kk = 0; kk < 4; ++kk) {  // 32 bytes along K per instruction: 16 bf16 or 8 tf32
+        if constexpr (kTf32)
+          umma_tf32(tmem_d, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc, (it | kk) != 0);
+        else
+          umma_bf16(tmem_d, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32), idesc, (it | kk) != 0);
+      }
       umma_commit(&sm->empty[s]);  // frees the stage once these MMAs have read it
       if (++s == kPfStages) s = 0, ph ^= 1u;
     }
@@ -446,6 +542,17 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
   tc_fence_before();
   __syncthreads();
   if (warp == kPfDequantWarps) tmem_dealloc(tmem_d, kTileM);
+}
+
+// f32 -> f32 rounded to tf32 (activation pre-pass of the tf32 form)
+__global__ void __launch_bounds__(256) f32_to_tf32_kernel(const float* x, int64_t n4, float* y) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n4) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    uint4 o;
+    o.x = to_tf32(v.x), o.y = to_tf32(v.y), o.z = to_tf32(v.z), o.w = to_tf32(v.w);
+    reinterpret_cast<uint4*>(y)[i] = o;
+  }
 }
 
 // f32 -> bf16 activation pre-pass

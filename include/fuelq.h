@@ -69,6 +69,12 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
 #define FUELQ_OPT_PEER_WAIT_MS 7  /* deadline, in milliseconds, of the exchange polls in the fuelq_*_peer kernels (default
                                     4000, 1..60000): a kernel whose peer never delivers records device error 6 after
                                     this long and carries on, so the context stays usable */
+#define FUELQ_OPT_PREFILL_TF32 8  /* 1: the tensor-core path (m_total above the integer crossover) multiplies in tf32
+                                    instead of bf16: weights dequantized to f32 and rounded to tf32, activations
+                                    rounded to tf32, f32 accumulation. Half the MMA rate, twice the workspace
+                                    (4 bytes per activation; ask fuelq_qmatmul_workspace_bytes after setting it),
+                                    and results within 1e-3 of the exact dequantized product where bf16 reaches
+                                    about 2.5e-3 (default 0) */
 int32_t fuelq_set_option(int32_t key, int64_t value);
 int64_t fuelq_get_option(int32_t key);
 
