@@ -181,7 +181,9 @@ def run_side_workload(args):
     L = _lib.lib
     rank, local_rank, world = _dist_env()
     if world > 1:
-        assert args.workload == "moe", "only the MoE block has a multi-GPU (expert-parallel) form here"
+        assert args.workload in ("moe", "prefill"), "multi-GPU forms: the MoE block (expert-parallel), the prefill GEMM (column-sharded)"
+        if args.workload == "prefill":
+            return run_prefill_sharded(args, rank, local_rank, world)
         return run_moe_expert_parallel(args, rank, local_rank, world)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -237,6 +239,60 @@ def run_side_workload(args):
                           "tokens_per_s": N / us * 1e6, "hbm_frac": wbytes / us / 1e3 / peak, "peak_kind": f"of {peak_kind}",
                           "weight_bytes": wbytes, "weight_copies": copies, "launches_per_block": 9}), flush=True)
     assert ops.device_error() == 0, "a kernel recorded an expired bounded wait"
+
+
+def run_prefill_sharded(args, rank, local_rank, world):
+    """BASELINE config 3 across GPUs: W [14336 x 4096] Q4_K split by rows (columns of Y) over the ranks, X [2048 x 4096]
+    on every rank; each rank's kernel writes its columns into every rank's Y (the all-gather is the kernel's epilogue).
+    CUDA events around the call on each rank, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    from fuel_b200.llama import shard_range
+    from fuel_b200.sharded import ShardedQMatMul
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    _lib.lib.fuelq_set_option(_lib.OPT_PREFILL_TF32, 1 if args.tf32 else 0)
+    n, k, m, copies = 14336, 4096, 2048, 4
+    lo, hi = shard_range(n, world, rank)
+    gen = torch.Generator(device=dev)
+    shards = []
+    for c in range(copies):
+        gen.manual_seed(100 * c + rank)
+        wb = ops.quantize_weights(T.Q4K, torch.randn(hi - lo, k, generator=gen, device=dev) * 0.02)
+        shards.append(ShardedQMatMul(T.Q4K, wb, n, k, m, rank, world))
+    gen.manual_seed(7)
+    x = torch.randn(m, k, generator=gen, device=dev)
+    try:
+        for sh in shards:
+            sh.forward(x)
+        shards[0].finish()
+        reps = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for sh in shards:
+                sh.forward(x)
+        e1.record()
+        shards[0].finish()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3 / (reps * copies)
+        assert ops.device_error() == 0
+        if rank == 0:
+            peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+            print(json.dumps({"workload": f"Q4_K_k{k}_n{n}_m{m}_column_sharded", "n_gpus": world, "us": us,
+                              "TFLOP/s": 2 * m * n * k / us / 1e6, "operands": "tf32" if args.tf32 else "bf16",
+                              "all_gather": "inside the kernel epilogue (stores into every GPU's Y over NVLink)",
+                              "y_bytes_stored_per_gpu": 4 * m * (hi - lo) * world,
+                              "bf16_tflops_measured_per_gpu": peak.get("bf16_tflops")}), flush=True)
+    finally:
+        for sh in shards:
+            sh.close()
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def run_moe_expert_parallel(args, rank, local_rank, world):

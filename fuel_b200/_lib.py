@@ -48,6 +48,7 @@ PROTOTYPES = {
     "fuelq_qmatmul_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul_can_implement": (_i32, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "fuelq_qmatmul_sharded": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _i64, _vp, _sz, _vp]),
     "fuelq_qmatmul_host_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul_host": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "fuelq_static_scratch_bytes": (_sz, []),

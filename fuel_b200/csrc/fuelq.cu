@@ -536,11 +536,11 @@ bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, bool f32, CUte
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <class Fmt, int kTileM, bool kTf32 = false>
-cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t stream) {
+template <class Fmt, int kTileM, bool kTf32, bool kMulti>
+cudaError_t launch_prefill_m(const PrefillParams& p, const void* xb, cudaStream_t stream) {
   constexpr size_t smem = 1024 + (size_t)kPfStages * (kPfTileN * 128 + kTileM * 128) + sizeof(PrefillSmem) + 64;
   static bool attr_set[64] = {};
-  auto kern = prefill_gemm_kernel<Fmt, kTileM, kTf32>;
+  auto kern = prefill_gemm_kernel<Fmt, kTileM, kTf32, kMulti>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
@@ -556,8 +556,15 @@ cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t 
   return cudaGetLastError();
 }
 
-int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const float* x, float* y, void* workspace,
-                     cudaStream_t stream) {
+template <class Fmt, int kTileM, bool kTf32 = false>
+cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t stream) {
+  return p.n_dst > 1 ? launch_prefill_m<Fmt, kTileM, kTf32, true>(p, xb, stream)
+                     : launch_prefill_m<Fmt, kTileM, kTf32, false>(p, xb, stream);
+}
+
+// y_dst / n_dst / ldy / n_off: see PrefillParams; the plain call passes one destination of width n
+int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const float* x, float* const* y_dst, int n_dst,
+                     int64_t ldy, int64_t n_off, void* workspace, cudaStream_t stream) {
   const bool tf32 = g_opt.prefill_tf32 != 0;
   void* xb = workspace;  // the activations in the tensor cores' operand type: bf16, or f32 rounded to tf32
   const int64_t n4 = m * k / 4;
@@ -568,7 +575,10 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   if (cudaGetLastError() != cudaSuccess) return kLaunchFailure;
   PrefillParams p;
   p.w = (const uint8_t*)w;
-  p.y = y;
+  for (int q = 0; q < 8; ++q) p.y[q] = q < n_dst ? y_dst[q] : nullptr;
+  p.n_dst = n_dst;
+  p.ldy = (int)ldy;
+  p.n_off = (int)n_off;
   p.M = (int)m;
   p.N = (int)n;
   p.K = (int)k;
@@ -741,7 +751,8 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   if (!aligned(workspace, 16)) return kMisaligned;
   if (prefill_available(ggml_type, m_total, n, k)) {
     if (m_total > (1 << 30) || n > (1 << 30)) return kNotSupported;
-    return prefill_impl(ggml_type, m_total, n, k, w, x, y, workspace, (cudaStream_t)stream);
+    float* const one[1] = {y};
+    return prefill_impl(ggml_type, m_total, n, k, w, x, one, 1, n, 0, workspace, (cudaStream_t)stream);
   }
   if (g_opt.l2_prefetch) {
     st = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
@@ -756,6 +767,27 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
   st = quantize_act_impl(ggml_type, m_total, k, x, nullptr, workspace, (cudaStream_t)stream);
   if (st != kOk) return st;
   return decode_chunked(ggml_type, m_total, n, k, w, workspace, y, (cudaStream_t)stream);
+}
+
+int32_t fuelq_qmatmul_sharded(int32_t ggml_type, int64_t m_total, int64_t n_local, int64_t k, const void* w_local,
+                              const float* x, float* const* y_dst, int32_t n_dst, int64_t n_total, int64_t n_offset,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+  const int32_t st = check_problem(ggml_type, m_total, n_local, k);
+  if (st != kOk) return st;
+  if (n_dst < 1 || n_dst > 8 || n_total <= 0 || n_offset < 0 || n_offset + n_local > n_total || n_total > (1 << 30) ||
+      m_total * n_total > ((int64_t)1 << 40))
+    return kInvalidProblem;
+  if (m_total == 0 || n_local == 0) return kOk;
+  if (!w_local || !x || !y_dst) return kInvalidProblem;
+  for (int q = 0; q < n_dst; ++q)
+    if (!y_dst[q]) return kInvalidProblem;
+  if (!aligned(w_local, 16) || !aligned(x, 16)) return kMisaligned;
+  if (!prefill_available(ggml_type, m_total, n_local, k)) return kNotSupported;  // the tensor-core path only
+  if (m_total > (1 << 30)) return kNotSupported;
+  if (!workspace || workspace_bytes < prefill_workspace_bytes(m_total, k)) return kWorkspace;
+  if (!aligned(workspace, 16)) return kMisaligned;
+  return prefill_impl(ggml_type, m_total, n_local, k, w_local, x, y_dst, n_dst, n_total, n_offset, workspace,
+                      (cudaStream_t)stream);
 }
 
 size_t fuelq_qmatmul_host_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {

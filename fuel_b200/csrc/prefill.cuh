@@ -37,7 +37,10 @@ constexpr int kPfThreads = 32 * (kPfDequantWarps + 1);
 
 struct PrefillParams {
   const uint8_t* w;          // GGUF blocks, [N][K / block]
-  float* y;                  // [M][N]
+  float* y[8];               // destinations: y[q] is an [M][ldy] matrix (this GPU's, or a peer's mapped here)
+  int n_dst;                 // how many of them (1 on a single GPU)
+  int ldy;                   // row stride of the destinations (N on a single GPU, the full width when column-sharded)
+  int n_off;                 // first column this launch produces within a destination row
   int M, N, K;
   int row_bytes;
 };
@@ -370,7 +373,8 @@ struct PrefillSmem {
 
 // kTf32: operands in tf32 instead of bf16 - stages are 32 wide (one 128-byte row of f32), activations are the f32
 // matrix rounded to tf32 by the pre-pass, half the MMA rate, about eight times smaller rounding error.
-template <class Fmt, int kTileM, bool kTf32 = false>
+// kMulti: the epilogue stores every tile into several destinations (column-sharded across GPUs).
+template <class Fmt, int kTileM, bool kTf32 = false, bool kMulti = false>
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t pf_smem[];
   // [stage][ weights 128 x 128 B | activations kTileM x 128 B ], each 1024-byte aligned; control block after
@@ -525,15 +529,51 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
     if (ready) {
       tc_fence_after();
       const int n = n0 + warp * 32 + lane;
+      // The accumulator arrives one weight row (output column) per lane; Y is row-major in the other direction. Each warp
+      // turns 32 x 32 pieces around in shared memory (the stage buffers are free by now) so that it stores 16 bytes per
+      // lane along a row of Y - four times fewer, four times larger stores, which matters most for the peers' copies.
+      float* tbuf = reinterpret_cast<float*>(base) + warp * (32 * 36);  // [32 m][36]: rows 16-byte aligned, shifted banks
+      // (measured: for a single local destination the direct 4-byte stores, already 128 bytes per warp, are faster)
+      bool vec_ok = kMulti && p.n_dst > 1 && (p.ldy & 3) == 0 && (p.n_off & 3) == 0 && n0 + warp * 32 + 32 <= p.N;
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (q < p.n_dst) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(p.y[q]) & 15) == 0;
+      const int sub_m = lane >> 3, n4 = (lane & 7) * 4;
 #pragma unroll 1
       for (int c = 0; c < kTileM / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
-        if (n < p.N) {
+        if (kMulti && vec_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tbuf[j * 36 + lane] = __uint_as_float(v[j]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int mm = sub_m + 4 * i, m = m0 + c * 32 + mm;
+            if (m < p.M) {
+              const float4 val = *reinterpret_cast<const float4*>(tbuf + mm * 36 + n4);
+              // column-sharded across GPUs: the piece goes straight into every GPU's copy of Y (plain stores over
+              // NVLink for the peers'), so the all-gather of the shards happens inside the epilogue
+              const size_t off = (size_t)m * p.ldy + p.n_off + n0 + warp * 32 + n4;
+#pragma unroll
+              for (int q = 0; q < 8; ++q)  // constant indices: a runtime index would copy the pointer table to local memory
+                if (q < p.n_dst) *reinterpret_cast<float4*>(p.y[q] + off) = val;
+            }
+          }
+          __syncwarp();
+        } else if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int m = m0 + c * 32 + j;
-            if (m < p.M) p.y[(size_t)m * p.N + n] = __uint_as_float(v[j]);
+            if (m < p.M) {
+              const size_t off = (size_t)m * p.ldy + p.n_off + n;
+              p.y[0][off] = __uint_as_float(v[j]);
+              if (kMulti && p.n_dst > 1) {
+#pragma unroll
+                for (int q = 1; q < 8; ++q)
+                  if (q < p.n_dst) p.y[q][off] = __uint_as_float(v[j]);
+              }
+            }
           }
         }
       }

@@ -210,6 +210,18 @@ int32_t fuelq_swiglu_q8k(const float* gate, const float* up, int64_t n, void* pa
 int32_t fuelq_attn_decode_q8k(const float* q, const float* kcache, const float* vcache, const int32_t* pos, int32_t n_heads,
                               int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale, void* workspace,
                               size_t workspace_bytes, void* packed, size_t packed_bytes, const fuelq_rope* rope, void* stream);
+/* Column-sharded form of fuelq_qmatmul for the tensor-core path (m_total above the integer crossover): this GPU
+ * holds rows [n_offset, n_offset + n_local) of the weight matrix and computes those columns of Y; the kernel's
+ * epilogue stores each output tile into EVERY destination y_dst[q] (an [m_total][n_total] matrix: this GPU's own, and
+ * the other GPUs' mapped with fuelq_ipc_open), so when all GPUs' calls have completed every GPU holds the full Y - the
+ * all-gather of the shards happens inside the kernel, as plain NVLink stores overlapped with the remaining tiles. The
+ * reference has no multi-GPU form (fuel-core/src/quantized/mod.rs:854-868). The caller orders "all calls completed"
+ * itself (stream sync + a process barrier, or an event per peer). Workspace: fuelq_qmatmul_workspace_bytes(type,
+ * m_total, n_local, k). */
+int32_t fuelq_qmatmul_sharded(int32_t ggml_type, int64_t m_total, int64_t n_local, int64_t k, const void* w_local,
+                              const float* x, float* const* y_dst, int32_t n_dst, int64_t n_total, int64_t n_offset,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- Mixture-of-experts block with quantized experts (the grouped / indexed quantized mat-vec).
  * Replaces the slot the reference leaves empty (indexed_moe_forward, fuel-backend-contract/src/quantized.rs:29-103;
  * the CUDA implementation was retired and its grouped kernel is only named: fuel-cuda-backend/src/quantized.rs:292-304)

@@ -49,3 +49,18 @@ def test_two_gpus_expert_parallel_block_equals_single_gpu_block():
     assert r.returncode == 0 and lines, (r.stdout[-2000:], r.stderr[-2000:])
     got = json.loads(lines[-1][len("EPRESULT "):])
     assert got["err"] == 0 and got["equal"], got
+
+
+def test_two_gpus_column_sharded_prefill_fills_every_copy_of_y():
+    """fuelq_qmatmul_sharded: each GPU computes its columns and its epilogue writes them into both GPUs' Y; after both
+    calls every GPU's Y equals the single-GPU product bit for bit."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29535", os.path.join(ROOT, "tests", "_shard_worker.py")]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=400)
+    lines = [l for l in r.stdout.splitlines() if l.startswith("SHRESULT ")]
+    assert r.returncode == 0 and lines, (r.stdout[-2000:], r.stderr[-2000:])
+    got = json.loads(lines[-1][len("SHRESULT "):])
+    assert got["err"] == 0 and got["equal_on_every_rank"] == 1, got
