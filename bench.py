@@ -393,7 +393,7 @@ def run_decode_7b(torch, dist, device, rank, world):
                 "exchange": "inside the kernels over peer-mapped memory" if world > 1 else "none (one GPU)",
                 "weight_bytes_per_gpu": model.weight_bytes, "kv_bytes_per_gpu_per_token": kv_bytes,
                 "hbm_frac_per_gpu": (model.weight_bytes + kv_bytes) / (ms_tok * 1e-3) / 1e9 / peak,
-                "peak_kind": f"of {peak_kind}", "cuda_graph": True, "launches_per_token": sum(10 if l["v"] is None else 11 for l in model.layers) + 6}
+                "peak_kind": f"of {peak_kind}", "cuda_graph": True, "launches_per_token": sum(9 if l["v"] is None else 10 for l in model.layers) + 6}
     finally:
         model.release()
 
