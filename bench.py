@@ -111,6 +111,16 @@ def make_weights(torch, ops, T, device, rank):
     return ws
 
 
+def host_threads(O) -> int:
+    """Threads for the CPU legs: every core this process may run on. A launcher that exports OMP_NUM_THREADS=1 for
+    its workers (torch.distributed.run does) must not turn the CPU baseline into a one-thread run."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(n, O.max_threads())
+
+
 def cpu_pass(O, w_host, x_host, threads):
     for wb, x in zip(w_host, x_host):
         O.matmul(O.Q4K, x, wb, N_OUT, O.AVX2, threads)
@@ -121,9 +131,15 @@ def run_reference(args):
     rank, local_rank, world = _dist_env()
     if rank != 0:
         return
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the OpenMP runtime reads it when it is loaded,
+    # so put the real core count back before the oracle library comes in
+    try:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import numpy as np
     from oracle import oracle as O
-    threads = O.max_threads()
+    threads = host_threads(O)
     rng = np.random.Generator(np.random.PCG64(0))
     # one quantized matrix per layer would cost ~1 s of host quantization each; the CPU timing
     # does not depend on the weight values, so LAYERS views of 4 distinct matrices are used,
@@ -587,7 +603,7 @@ def main():
     cpu_baseline = None
     if not args.no_cpu_baseline and world == 1:
         from oracle import oracle as O
-        threads = O.max_threads()
+        threads = host_threads(O)
         w_host = [ws[i].cpu().numpy() for i in range(4)]
         x_host = [xs[i].cpu().numpy() for i in range(4)]
         # parity spot check beside the timing: GPU output vs the CPU path on layer 0
