@@ -41,8 +41,6 @@ struct DecodeRegsParams {
   int pre_stages;                 // stages issued before the consumers hold their activations (0 = all)
   int rows_q, rows_rem;           // n / grid, n % grid: CTA c owns rows_q (+1 if c < rows_rem) rows
   int u_begin[9];                 // unit range of k-slice s: [u_begin[s], u_begin[s+1])
-  int debug_flags;                // bit 0: consumers skip the arithmetic (streaming-rate experiments)
-  unsigned long long* trace;      // optional: 24 global-timer stamps per CTA
   const float* x_f32;             // not null: f32 activations [m][k]; every CTA quantizes them itself (Q8_K) into
   int act_smem_off;               //   plain planes at this byte offset of its shared memory, instead of reading `act`
 };
@@ -57,12 +55,6 @@ struct DecodeRegsPeer {
   StampedPlanes act_ll;
   int act_smem_off;
 };
-
-__device__ __forceinline__ unsigned long long gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
@@ -341,7 +333,6 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
   const int r_begin = cta * p.rows_q + (cta < p.rows_rem ? cta : p.rows_rem);
   const int r_count = p.rows_q + (cta < p.rows_rem ? 1 : 0);
   const int n_iter = (int)(((unsigned)r_count + (unsigned)R - 1u) / (unsigned)R);
-  if (p.trace && threadIdx.x == 0) p.trace[24 * blockIdx.x] = gtimer();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -479,7 +470,6 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     if (lane == 0) mbar_arrive(&hd->acts_ready);
   }
   const uint32_t stages_u32 = smem_u32(stages);
-  if (p.trace && threadIdx.x == 0) p.trace[24 * blockIdx.x + 1] = gtimer();
   int s = 0;
   uint32_t ph = 0;
   for (int it = 0; it < n_iter; ++it) {
@@ -487,14 +477,12 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       record_dev_error(kErrFullWait);
       return;
     }
-    if (p.trace && threadIdx.x == 0 && (it == 0 || it == n_iter - 1)) p.trace[24 * blockIdx.x + (it == 0 ? 2 : 3)] = gtimer();
-    if (p.trace && threadIdx.x == 0 && it < 10) p.trace[24 * blockIdx.x + 4 + 2 * it] = gtimer();
     const int row0 = r_begin + it * R;
     const int rows_here = (r_count - it * R < R) ? r_count - it * R : R;
     const uint32_t skew = (uint32_t)(((int64_t)row0 * p.row_bytes) & 15);
     const uint32_t sbase = stages_u32 + (uint32_t)s * p.stage_stride + skew;
     const int buf = it & 1;
-    for (int r = rgroup; r < rows_here && !(p.debug_flags & 1); r += n_rgroups) {
+    for (int r = rgroup; r < rows_here; r += n_rgroups) {
       const uint32_t rowbase = sbase + (uint32_t)r * p.row_bytes;
       float acc[M];
 #pragma unroll
@@ -521,7 +509,6 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       }
     }
     __syncwarp();
-    if (p.trace && threadIdx.x == 0 && it < 10) p.trace[24 * blockIdx.x + 5 + 2 * it] = gtimer();
     if (lane == 0) mbar_arrive(&hd->empty[s]);
     if (ks > 1) {
       // all consumer warps meet here (bounded), then the k-slices of each row are summed in fixed order

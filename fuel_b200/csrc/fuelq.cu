@@ -25,8 +25,6 @@ struct Options {
   int64_t pdl = 0;
   int64_t decode_max_m = 16;  // larger m_total goes to the tensor-core path when the format has one
   int64_t decode_grid = 0;
-  int64_t debug_flags = 0;
-  int64_t trace_ptr = 0;
   int64_t dbg_stage_kb = 0, dbg_max_stages = 0, dbg_smem_kb = 0;
   int64_t l2_prefetch = 0;
   int64_t dbg_depth = 0;
@@ -320,8 +318,6 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
   p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
   if (staged && !reserve) p.pre_stages = pl.num_stages - 1;
-  p.debug_flags = (int)g_opt.debug_flags;
-  p.trace = (unsigned long long*)(uintptr_t)g_opt.trace_ptr;
   cudaError_t e;
   if (peer) {
 #define FQ_REGS_PEER(FMT) \
@@ -646,9 +642,8 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
       if (value < 0 || value > 2) return kInvalidProblem;
       g_opt.decode_kernel = value;
       return kOk;
-    case 100: g_opt.debug_flags = value; return kOk;  // development switches, not part of the contract
-    case 101: g_opt.trace_ptr = value; return kOk;
-    case 102: g_opt.dbg_stage_kb = value; return kOk;
+    case 102:  // 102-107: development switches for tuning runs, not part of the contract
+      g_opt.dbg_stage_kb = value; return kOk;
     case 103: g_opt.dbg_max_stages = value; return kOk;
     case 104: g_opt.dbg_smem_kb = value; return kOk;
     case 105: g_opt.dbg_depth = value; return kOk;

@@ -21,7 +21,6 @@
 #pragma once
 #include <cuda.h>
 
-#include <type_traits>
 #include <cuda_bf16.h>
 
 #include "dequantize.cuh"
@@ -32,7 +31,7 @@ namespace fq {
 constexpr int kPfTileN = 128;   // weight rows per CTA  (UMMA M)
 constexpr int kPfTileK = 64;    // K per stage: one 128-byte swizzle atom of bf16
 constexpr int kPfStages = 4;
-constexpr int kPfDequantWarps = 8;   // 8: two threads per weight row (halves); 16: four (quarters) - measured slower
+constexpr int kPfDequantWarps = 8;   // two threads per weight row (four were measured slower)
 constexpr int kPfThreads = 32 * (kPfDequantWarps + 1);
 
 struct PrefillParams {
@@ -92,12 +91,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 // 2-D tiled tensor-map copy global -> shared, completion in bytes on an mbarrier. x (innermost, in elements) times the
 // element size must be a multiple of 16 bytes; rows outside the tensor arrive as zeros.
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -269,9 +262,6 @@ struct Q8_0Prefill {
   struct Raw {};
   __device__ __forceinline__ static void load(const uint8_t*, int, Raw&) {}
   __device__ __forceinline__ static void convert(const Raw&, int, uint4 (&)[8]) {}
-  struct RawQ {};
-  __device__ __forceinline__ static void load_part(const uint8_t*, int, int, RawQ&) {}
-  __device__ __forceinline__ static void convert_part(const RawQ&, int, int, uint4 (&)[2]) {}
   __device__ __forceinline__ static void convert_half(const Raw&, int, int, uint4 (&)[4]) {}
   // tf32 form: stage `it` is block `it`; part = which 16 of its 32 elements
   __device__ __forceinline__ static void stage16(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
@@ -309,9 +299,6 @@ struct Q6KPrefill {
   struct Raw {};
   __device__ __forceinline__ static void load(const uint8_t*, int, Raw&) {}
   __device__ __forceinline__ static void convert(const Raw&, int, uint4 (&)[8]) {}
-  struct RawQ {};
-  __device__ __forceinline__ static void load_part(const uint8_t*, int, int, RawQ&) {}
-  __device__ __forceinline__ static void convert_part(const RawQ&, int, int, uint4 (&)[2]) {}
   __device__ __forceinline__ static void convert_half(const Raw&, int, int, uint4 (&)[4]) {}
   // tf32 form: stage `it` is 32 consecutive elements: block it / 8, half (it / 4) % 2, quad it % 4 (elements
   // 128*half + 32*quad + l); part = which 16 of them (l = 16*part ..), which share one scale
@@ -406,7 +393,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
   volatile int* abort_flag = &sm->abort_flag;
 
   if (warp < kPfDequantWarps) {
-    // ---------------- weight producers: thread t owns part (t >> 7) of weight row n0 + (t & 127): a half or a quarter
+    // ---------------- weight producers: thread t owns half (t >> 7) of weight row n0 + (t & 127)
     const int t = threadIdx.x, r = t & 127, part = t >> 7;
     const bool live = n0 + r < p.N;
     const uint8_t* row = p.w + (size_t)(live ? n0 + r : 0) * p.row_bytes;
@@ -414,12 +401,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
     uint32_t ph = 0;
     int x_issued = 0;
     // the bytes of the next three stages, requested that far ahead: a stage takes less time than one trip to L2
-    constexpr bool kQuarters = kPfDequantWarps == 16;
-    using RawT = typename std::conditional<kQuarters, typename Fmt::RawQ, typename Fmt::Raw>::type;
-    auto load_raw = [&](int it, RawT& dst_raw) {
-      if constexpr (kQuarters) Fmt::load_part(row, it, part, dst_raw);
-      else Fmt::load(row, it, dst_raw);
-    };
+    using RawT = typename Fmt::Raw;
+    auto load_raw = [&](int it, RawT& dst_raw) { Fmt::load(row, it, dst_raw); };
     RawT r0, r1, r2;
     if (!kTf32 && Fmt::kSplitLoad && live) {
       if (n_iter > 0) load_raw(0, r0);
@@ -450,20 +433,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
 #pragma unroll
         for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + (((4 * part + c) ^ (r & 7)) << 4)) = out[c];
       } else if constexpr (Fmt::kSplitLoad) {
-        constexpr int kChunks = kQuarters ? 2 : 4;  // 16-byte chunks this thread writes
+        constexpr int kChunks = 4;  // 16-byte chunks this thread writes
         uint4 out[4];
         if (live) {
           const RawT cur = r0;
           r0 = r1;
           r1 = r2;
           if (it + 3 < n_iter) load_raw(it + 3, r2);
-          if constexpr (kQuarters) {
-            uint4 o2[2];
-            Fmt::convert_part(cur, it, part, o2);
-            out[0] = o2[0], out[1] = o2[1];
-          } else {
-            Fmt::convert_half(cur, it, part, out);
-          }
+          Fmt::convert_half(cur, it, part, out);
         } else {
 #pragma unroll
           for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
