@@ -415,16 +415,22 @@ int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const Ac
   p.row_bytes = (int)(k / 256 * Q4KL::kBytes);
   const size_t header = align_up(sizeof(MmaSmemHeader), 128);
   const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
-  const size_t act_bytes = mma_act_bytes((int)k), part_bytes = kDecodeConsumerWarps * 128 * sizeof(float);
-  if (header + act_bytes + part_bytes >= per_cta) return kNotSupported;
-  const size_t ring = per_cta - header - act_bytes - part_bytes;
-  int R = 0;
-  size_t stride = 0;
-  for (int cand = 32; cand >= 8; cand >>= 1) {
-    stride = align_up((size_t)cand * (p.row_bytes + 16), 128);
-    if (2 * stride <= ring) {
-      R = cand;
-      break;
+  const size_t part_bytes = kDecodeConsumerWarps * 128 * sizeof(float);
+  // k in as few chunks as shared memory allows: one chunk of the activation rows plus two stages of eight weight rows
+  const int nblk = (int)(k / 256);
+  int R = 0, kc_blocks = 0;
+  size_t stride = 0, act_bytes = 0, ring = 0;
+  for (int chunks = 1; chunks <= 16 && !R; ++chunks) {
+    const int kc = (nblk + chunks - 1) / chunks;
+    const size_t ab = mma_act_bytes(kc);
+    if (header + ab + part_bytes >= per_cta) continue;
+    const size_t rg = per_cta - header - ab - part_bytes;
+    for (int cand = 32; cand >= 8; cand >>= 1) {
+      const size_t st = align_up((size_t)cand * (kc * Q4KL::kBytes + 16), 128);
+      if (2 * st <= rg) {
+        R = cand, stride = st, kc_blocks = kc, act_bytes = ab, ring = rg;
+        break;
+      }
     }
   }
   if (!R) return kNotSupported;
@@ -444,7 +450,8 @@ int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const Ac
   p.stage_stride = (int)stride;
   p.act_off = (int)(header + (size_t)stages * stride);
   p.part_off = (int)(p.act_off + act_bytes);
-  int per_group = (4 * di->sm_count + n_groups - 1) / n_groups;
+  p.kc_blocks = kc_blocks;
+  int per_group = ((kc_blocks < nblk ? 2 : 4) * di->sm_count + n_groups - 1) / n_groups;
   const int max_per = (int)((n + R - 1) / R);
   if (per_group > max_per) per_group = max_per;
   if (per_group < 1) per_group = 1;
@@ -467,7 +474,9 @@ int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const Ac
 int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
                        cudaStream_t stream) {
   const ActPlanes all = act_planes(packed_act, type, m_total, k);
-  if (type == kQ4K && m_total > 2 && g_opt.decode_kernel == 0 && g_opt.moe_kernel != 1 && n <= (1 << 24)) {
+  // (when k is so large that the tensor-core kernel sweeps it in chunks, two-row dp4a passes stay ahead up to 5 rows)
+  const bool mma_chunked = k / 256 > 16;
+  if (type == kQ4K && m_total > (mma_chunked ? 5 : 2) && g_opt.decode_kernel == 0 && g_opt.moe_kernel != 1 && n <= (1 << 24)) {
     // a few rows of Q4_K: one pass over the weights on the integer tensor cores (16 rows per pass)
     const int32_t st = moe_mma_impl(1, n, k, w, all, nullptr, (int)m_total, nullptr, y, stream);
     if (st != kNotSupported) return st;
@@ -496,8 +505,13 @@ bool mma_plan_fits(int64_t k) {
   DeviceInfo* di;
   if (k % 256 || k > (1 << 20) || !device_info(&di)) return false;
   const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
-  const size_t fixed = align_up(sizeof(MmaSmemHeader), 128) + mma_act_bytes((int)k) + kDecodeConsumerWarps * 128 * sizeof(float);
-  return fixed + 2 * align_up((size_t)8 * (k / 256 * Q4KL::kBytes + 16), 128) <= per_cta;
+  const size_t fixed = align_up(sizeof(MmaSmemHeader), 128) + kDecodeConsumerWarps * 128 * sizeof(float);
+  const int nblk = (int)(k / 256);
+  for (int chunks = 1; chunks <= 16; ++chunks) {
+    const int kc = (nblk + chunks - 1) / chunks;
+    if (fixed + mma_act_bytes(kc) + 2 * align_up((size_t)8 * (kc * Q4KL::kBytes + 16), 128) <= per_cta) return true;
+  }
+  return false;
 }
 
 bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {

@@ -16,7 +16,8 @@
 //     row_bytes + 16 for the same reason.
 // Work split inside a stage: R / 8 tiles of 8 weight rows, each tile shared by 64 / R warps that take
 // consecutive ranges of the 256-blocks along k; their partial sums meet in shared memory and are added in
-// a fixed order. Every wait is bounded.
+// a fixed order. When a row of activations does not fit (large k), k is cut into chunks of kc_blocks blocks and
+// the same rows are swept once per chunk, each sweep adding into y. Every wait is bounded.
 #pragma once
 #include "decode_regs.cuh"
 #include "fq_common.cuh"
@@ -36,6 +37,8 @@ struct MmaParams {
   int rows_per_stage;    // R: 8, 16 or 32
   int num_stages, stage_stride;
   int act_off, part_off; // shared-memory offsets of the activation area and of the partial-sum area
+  int kc_blocks;         // 256-blocks of k handled per sweep (all of k when it fits in shared memory; else the
+                         // sweeps' results are added into y in order, by the thread that wrote the first one)
 };
 
 constexpr int kMmaActRows = 16;
@@ -60,10 +63,10 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], const uint32_t (&a)[4]
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__host__ __device__ inline size_t mma_act_bytes(int k) {
-  // quants (padded rows), 32-element sums (int16), block scales (f32)
-  return align_up((size_t)kMmaActRows * (k + 16), 128) + align_up((size_t)kMmaActRows * ((k / 32) * 2 + 16), 128) +
-         align_up((size_t)kMmaActRows * (k / 256) * 4, 128);
+__host__ __device__ inline size_t mma_act_bytes(int kc_blocks) {
+  // one k-chunk of the activation rows: quants (padded rows), 32-element sums (int16), block scales (f32)
+  return align_up((size_t)kMmaActRows * (kc_blocks * 256 + 16), 128) + align_up((size_t)kMmaActRows * (kc_blocks * 16 + 16), 128) +
+         align_up((size_t)kMmaActRows * kc_blocks * 4, 128);
 }
 
 __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaParams p) {
@@ -72,7 +75,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
   uint8_t* stages = smem_raw + align_up(sizeof(MmaSmemHeader), 128);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.num_stages, R = p.rows_per_stage;
-  const int wstride = p.row_bytes + 16, astride = p.k + 16;
+  const int nblk = p.k >> 8, KC = p.kc_blocks, n_kc = (nblk + KC - 1) / KC;
+  const int wstride = KC * Q4KL::kBytes + 16, astride = KC * 256 + 16;  // rows of one k-chunk, padded
   const int grp = blockIdx.y;
   const int r_begin = (int)((int64_t)p.n * blockIdx.x / gridDim.x);
   const int r_end = (int)((int64_t)p.n * (blockIdx.x + 1) / gridDim.x);
@@ -92,13 +96,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
   const int m_count = p.offsets ? p.offsets[grp + 1] - m_begin : p.fixed_rows;
   if (m_count <= 0 || n_iter <= 0) return;  // nothing is streamed for a group without rows
   const int n_pass = (m_count + kMmaActRows - 1) / kMmaActRows;
-  const int total_iter = n_pass * n_iter;
+  const int total_iter = n_pass * n_kc * n_iter;
   const int64_t base = (int64_t)grp * p.group_bytes;
 
   if (warp == kDecodeConsumerWarps) {
     // ---------------- producer: one bulk copy per weight row, a lane per row
     bool ok = true;
-    int it = 0, issued = 0;
+    int it = 0, kc = 0, issued = 0;
     for (int g = 0; g < total_iter; ++g) {
       const int s = g % S;
       if (g >= S) {
@@ -111,13 +115,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
       }
       const int row0 = r_begin + it * R;
       const int rows_here = ((row0 + R < r_end) ? row0 + R : r_end) - row0;
-      if (lane == 0) mbar_arrive_expect_tx(&hd->full[s], (uint32_t)(rows_here * p.row_bytes));
+      const int cb0 = kc * KC, cbn = (nblk - cb0 < KC) ? nblk - cb0 : KC;  // this sweep's blocks of every row
+      const uint32_t cbytes = (uint32_t)cbn * Q4KL::kBytes;
+      if (lane == 0) mbar_arrive_expect_tx(&hd->full[s], (uint32_t)rows_here * cbytes);
       __syncwarp();
       if (lane < rows_here)
         bulk_g2s(stages + (size_t)s * p.stage_stride + (size_t)lane * wstride,
-                 p.w + base + (int64_t)(row0 + lane) * p.row_bytes, (uint32_t)p.row_bytes, &hd->full[s]);
+                 p.w + base + (int64_t)(row0 + lane) * p.row_bytes + (int64_t)cb0 * Q4KL::kBytes, cbytes, &hd->full[s]);
       issued = g + 1;
-      if (++it == n_iter) it = 0;
+      if (++it == n_iter) {
+        it = 0;
+        if (++kc == n_kc) kc = 0;
+      }
     }
     if (!ok && lane == 0) {
       for (int g = (issued > S ? issued - S : 0); g < issued; ++g)
@@ -129,44 +138,46 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
   // ---------------- consumers
   uint8_t* act_qs = smem_raw + p.act_off;
   int16_t* act_bs = reinterpret_cast<int16_t*>(act_qs + align_up((size_t)kMmaActRows * astride, 128));
-  const int bstride = (p.k >> 5) * 2 + 16;  // bytes per row of 32-sums (padded: rows fall in different banks)
+  const int bstride = KC * 16 + 16;  // bytes per row of 32-sums (padded: rows fall in different banks)
   float* act_d = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(act_bs) + align_up((size_t)kMmaActRows * bstride, 128));
   float* part = reinterpret_cast<float*>(smem_raw + p.part_off);  // [tile][k-part][128]
   const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
-  const int nblk = p.k >> 8;
   const int tiles = R >> 3;                      // 8-row tiles per stage
   const int ksplit = kDecodeConsumerWarps / tiles;  // warps sharing a tile
   const int tile = warp / ksplit, kpart = warp - tile * ksplit;
-  const int b_begin = nblk * kpart / ksplit, b_end = nblk * (kpart + 1) / ksplit;
   const int gid = lane >> 2, tig = lane & 3;
 
   int g = 0;
   for (int pass = 0; pass < n_pass; ++pass) {
     const int a0 = m_begin + pass * kMmaActRows;
     const int ac = (m_count - pass * kMmaActRows < kMmaActRows) ? m_count - pass * kMmaActRows : kMmaActRows;
-    if (pass > 0) asm volatile("bar.sync 8, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");  // previous rows are done with
+   for (int kc = 0; kc < n_kc; ++kc) {
+    const int cb0 = kc * KC, cbn = (nblk - cb0 < KC) ? nblk - cb0 : KC;  // this sweep's blocks
+    const int b_begin = cbn * kpart / ksplit, b_end = cbn * (kpart + 1) / ksplit;
+    if (pass > 0 || kc > 0) asm volatile("bar.sync 8, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");  // previous rows are done with
     {
-      // stage the activation rows: quants into padded rows, 16-sums folded to 32-sums, scales; rows past ac are zero
-      const int q16 = p.k >> 4;  // 16-byte pieces per row
+      // stage the activation rows (this sweep's columns): quants into padded rows, 16-sums folded to 32-sums, scales;
+      // rows past ac are zero
+      const int q16 = cbn * 16;  // 16-byte pieces per row
       for (int i = t; i < kMmaActRows * q16; i += nt) {
         const int r = i / q16, c = i - r * q16;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < ac) v = reinterpret_cast<const uint4*>(p.act.qs + (size_t)(a0 + r) * p.k)[c];
+        if (r < ac) v = reinterpret_cast<const uint4*>(p.act.qs + (size_t)(a0 + r) * p.k + (size_t)cb0 * 256)[c];
         reinterpret_cast<uint4*>(act_qs + (size_t)r * astride)[c] = v;
       }
-      const int s32 = p.k >> 5;
+      const int s32 = cbn * 8;
       for (int i = t; i < kMmaActRows * s32; i += nt) {
         const int r = i / s32, c = i - r * s32;
         int v = 0;
         if (r < ac) {
-          const int16_t* bs = p.act.bsums + (size_t)(a0 + r) * (p.k >> 4) + 2 * c;
+          const int16_t* bs = p.act.bsums + (size_t)(a0 + r) * (p.k >> 4) + cb0 * 16 + 2 * c;
           v = (int)bs[0] + (int)bs[1];
         }
         *reinterpret_cast<int16_t*>(reinterpret_cast<uint8_t*>(act_bs) + (size_t)r * bstride + 2 * c) = (int16_t)v;
       }
-      for (int i = t; i < kMmaActRows * nblk; i += nt) {
-        const int r = i / nblk, c = i - r * nblk;
-        act_d[i] = r < ac ? p.act.d[(size_t)(a0 + r) * nblk + c] : 0.f;
+      for (int i = t; i < kMmaActRows * cbn; i += nt) {
+        const int r = i / cbn, c = i - r * cbn;
+        act_d[r * KC + c] = r < ac ? p.act.d[(size_t)(a0 + r) * nblk + cb0 + c] : 0.f;
       }
     }
     asm volatile("bar.sync 8, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
@@ -188,7 +199,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
         // A fragments by ldmatrix: lane l addresses row (l & 7) + 8 * ((l >> 3) & 1), byte column 16 * (l >> 4)
         const uint32_t aq_s = smem_u32(act_qs) + (uint32_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * astride + 16 * (lane >> 4);
         const uint32_t bs_s = smem_u32(act_bs) + (uint32_t)gid * bstride;
-        const uint32_t d_s = smem_u32(act_d) + (uint32_t)gid * nblk * 4;
+        const uint32_t d_s = smem_u32(act_d) + (uint32_t)gid * KC * 4;
         for (int b = b_begin; b < b_end; ++b) {
           const uint4 h0 = lds128(wc_s + b * Q4KL::kBytes);
           const uint4 h1 = lds128(wc_s + wstride + b * Q4KL::kBytes);
@@ -225,7 +236,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
           T4[3] = __dp2a_hi((int)bh.w, (int)mn1[1], __dp2a_lo((int)bh.z, (int)mn1[1], __dp2a_hi((int)bh.y, (int)mn1[0], __dp2a_lo((int)bh.x, (int)mn1[0], 0))));
           const float d0 = h2f_bits(h0.x & 0xffffu), dm0 = h2f_bits(h0.x >> 16);
           const float d1 = h2f_bits(h1.x & 0xffffu), dm1 = h2f_bits(h1.x >> 16);
-          const float yl = __uint_as_float(lds32(d_s + 4 * b)), yh = __uint_as_float(lds32(d_s + 8 * nblk * 4 + 4 * b));
+          const float yl = __uint_as_float(lds32(d_s + 4 * b)), yh = __uint_as_float(lds32(d_s + 8 * KC * 4 + 4 * b));
           facc[0] += (d0 * yl) * (float)S4[0] - (dm0 * yl) * (float)T4[0];
           facc[1] += (d1 * yl) * (float)S4[1] - (dm1 * yl) * (float)T4[1];
           facc[2] += (d0 * yh) * (float)S4[2] - (dm0 * yh) * (float)T4[2];
@@ -255,7 +266,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
           if (m < ac && col < rows_here) {
             const int srow = a0 + m;
             const int orow = p.out_rows ? p.out_rows[srow] : srow;
-            p.y[(size_t)orow * p.n + row0 + col] = facc[i];
+            float* dst = p.y + (size_t)orow * p.n + row0 + col;
+            *dst = kc == 0 ? facc[i] : *dst + facc[i];  // later sweeps add, in order, by the same thread
           }
         }
       }
@@ -263,6 +275,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
       __syncwarp();
       if (lane == 0) mbar_arrive(&hd->empty[s]);
     }
+   }
   }
 }
 
