@@ -274,6 +274,20 @@ struct Q8_0Prefill {
       out[c].z = to_tf32((float)(int8_t)(v1 & 0xff) * d), out[c].w = to_tf32((float)(int8_t)(v1 >> 8) * d);
     }
   }
+  // half of a 64-wide stage = one 34-byte block: part p is block 2 * it + p -> chunks 4p .. 4p + 3
+  __device__ __forceinline__ static int chunk_id(int part, int c) { return 4 * part + c; }
+  __device__ __forceinline__ static void stage_half(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
+    const uint8_t* b = row + (size_t)(2 * it + part) * Q8_0L::kBytes;
+    const float d = h2f_bits(ldg_u16(b));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // 4 values per j -> two packed words
+      const uint32_t v0 = ldg_u16(b + Q8_0L::kOffQs + 4 * j), v1 = ldg_u16(b + Q8_0L::kOffQs + 4 * j + 2);
+      const float f0 = (float)(int8_t)(v0 & 0xff) * d, f1 = (float)(int8_t)(v0 >> 8) * d;
+      const float f2 = (float)(int8_t)(v1 & 0xff) * d, f3 = (float)(int8_t)(v1 >> 8) * d;
+      uint32_t* o = reinterpret_cast<uint32_t*>(&out[j >> 1]) + 2 * (j & 1);
+      o[0] = pack_bf16(f0, f1), o[1] = pack_bf16(f2, f3);
+    }
+  }
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -323,6 +337,28 @@ struct Q6KPrefill {
         vals[2 * h2] = to_tf32(s * (float)(q0 - 32)), vals[2 * h2 + 1] = to_tf32(s * (float)(q1 - 32));
       }
       out[c] = make_uint4(vals[0], vals[1], vals[2], vals[3]);
+    }
+  }
+  // half of a 64-wide stage: part p takes l = 16p .. 16p + 15, i.e. elements l of the first 32 (chunks 2p, 2p + 1)
+  // and the same l of the second 32 (chunks 4 + 2p, 5 + 2p); one scale each
+  __device__ __forceinline__ static int chunk_id(int part, int c) { return c < 2 ? 2 * part + c : 4 + 2 * part + (c - 2); }
+  __device__ __forceinline__ static void stage_half(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
+    const int blk = it >> 2, half = (it >> 1) & 1, sub = it & 1;
+    const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
+    const float d = h2f_bits(ldg_u16(b + Q6KL::kOffD));
+    const uint8_t* ql = b + Q6KL::kOffQl + 64 * half + 16 * part;
+    const uint8_t* qh = b + Q6KL::kOffQh + 32 * half + 16 * part;
+    const uint32_t scw0 = ldg_u16(b + Q6KL::kOffScales + 8 * half + 4 * sub), scw1 = ldg_u16(b + Q6KL::kOffScales + 8 * half + 4 * sub + 2);
+    const float sa = d * (float)(int8_t)((scw0 >> (8 * part)) & 0xff), sb = d * (float)(int8_t)((scw1 >> (8 * part)) & 0xff);
+    const int nsh = 4 * sub, hsh = 4 * sub;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // two l values per j
+      const uint32_t a = ldg_u16(ql + 2 * j), c = ldg_u16(ql + 32 + 2 * j), h = ldg_u16(qh + 2 * j);
+      const int a0 = a & 0xff, a1 = a >> 8, c0 = c & 0xff, c1 = c >> 8, h0 = h & 0xff, h1 = h >> 8;
+      const int qa0 = (((a0 >> nsh) & 0xF) | (((h0 >> hsh) & 3) << 4)) - 32, qa1 = (((a1 >> nsh) & 0xF) | (((h1 >> hsh) & 3) << 4)) - 32;
+      const int qc0 = (((c0 >> nsh) & 0xF) | (((h0 >> (hsh + 2)) & 3) << 4)) - 32, qc1 = (((c1 >> nsh) & 0xF) | (((h1 >> (hsh + 2)) & 3) << 4)) - 32;
+      reinterpret_cast<uint32_t*>(&out[j >> 2])[j & 3] = pack_bf16(sa * (float)qa0, sa * (float)qa1);
+      reinterpret_cast<uint32_t*>(&out[2 + (j >> 2)])[j & 3] = pack_bf16(sb * (float)qc0, sb * (float)qc1);
     }
   }
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
@@ -447,16 +483,16 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
         }
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) *reinterpret_cast<uint4*>(dst + (((kChunks * part + c) ^ (r & 7)) << 4)) = out[c];
-      } else if (part == 0) {  // formats without a split form: one thread per row does it all
-        uint4 out[8];
+      } else {  // the other formats: each of the row's two threads dequantizes half of the stage
+        uint4 out[4];
         if (live) {
-          Fmt::stage(row, it, out);
+          Fmt::stage_half(row, it, part, out);
         } else {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = out[c];
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + ((Fmt::chunk_id(part, c) ^ (r & 7)) << 4)) = out[c];
       }
       fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
       mbar_arrive(&sm->full[s]);
