@@ -34,6 +34,23 @@ class Rope(ctypes.Structure):
 
 _rp = ctypes.POINTER(Rope)
 
+
+class GgufTensor(ctypes.Structure):
+    """struct fuelq_gguf_tensor of include/fuelq_gguf.h."""
+    _fields_ = [("name", ctypes.c_char_p), ("ggml_type", ctypes.c_int32), ("n_dims", ctypes.c_int32),
+                ("dims", ctypes.c_int64 * 8), ("offset", ctypes.c_uint64), ("nbytes", ctypes.c_uint64),
+                ("data", ctypes.c_void_p)]
+
+
+class GgufValue(ctypes.Structure):
+    """struct fuelq_gguf_value of include/fuelq_gguf.h."""
+    _fields_ = [("key", ctypes.c_char_p), ("type", ctypes.c_int32), ("elem_type", ctypes.c_int32),
+                ("len", ctypes.c_uint64), ("i", ctypes.c_int64), ("f", ctypes.c_double), ("s", ctypes.c_void_p),
+                ("array", ctypes.c_void_p)]
+
+
+_u64 = ctypes.c_uint64
+
 # name -> (restype, argtypes); must list every symbol include/fuelq.h declares
 PROTOTYPES = {
     "fuelq_status_string": (ctypes.c_char_p, [_i32]),
@@ -96,6 +113,21 @@ PROTOTYPES = {
     "fuelq_qtensor_dequantize": (_i32, [_vp, _vp, _i32]),
     "fuelq_qmatmul_forward": (_i32, [_vp, _vp, _i64, _vp]),
     "fuelq_qmatmul_forward_host": (_i32, [_vp, _vp, _i64, _vp]),
+    # include/fuelq_gguf.h
+    "fuelq_gguf_open": (_i32, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "fuelq_gguf_open_memory": (_i32, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "fuelq_gguf_close": (_i32, [_vp]),
+    "fuelq_gguf_version": (_i32, [_vp]),
+    "fuelq_gguf_alignment": (_u64, [_vp]),
+    "fuelq_gguf_tensor_data_offset": (_u64, [_vp]),
+    "fuelq_gguf_tensor_count": (_i64, [_vp]),
+    "fuelq_gguf_find_tensor": (_i64, [_vp, ctypes.c_char_p]),
+    "fuelq_gguf_tensor_at": (_i32, [_vp, _i64, ctypes.POINTER(GgufTensor)]),
+    "fuelq_gguf_meta_count": (_i64, [_vp]),
+    "fuelq_gguf_find_meta": (_i64, [_vp, ctypes.c_char_p]),
+    "fuelq_gguf_meta_at": (_i32, [_vp, _i64, ctypes.POINTER(GgufValue)]),
+    "fuelq_gguf_meta_array_string": (_i32, [_vp, _i64, _u64, ctypes.POINTER(_vp), ctypes.POINTER(_u64)]),
+    "fuelq_gguf_load_tensor": (_i32, [_vp, _i64, _u64, _u64, _vp, _vp]),
 }
 
 

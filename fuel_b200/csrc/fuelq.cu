@@ -891,11 +891,16 @@ int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x,
 // ---- f32 glue of a LLaMA-style decode step (llama_glue.cuh) -----------------------------------------
 int32_t fuelq_embed_rows(int32_t ggml_type, const void* table, int64_t k, const int32_t* ids, int64_t n_ids, float* out,
                          void* stream) {
-  if (ggml_type != kQ4K) return kNotSupported;
+  if (ggml_type != kQ4K && ggml_type != kF32) return kNotSupported;
   if (k <= 0 || k % 256 || n_ids < 0) return kInvalidProblem;
   if (n_ids == 0) return kOk;
   if (!table || !ids || !out) return kInvalidProblem;
-  if (!aligned(table, 16) || !aligned(out, 4)) return kMisaligned;
+  if (!aligned(table, 16) || !aligned(out, ggml_type == kF32 ? 16 : 4)) return kMisaligned;
+  if (ggml_type == kF32) {  // a table the loader already dequantized (any other on-disk format)
+    const cudaError_t e = launch(embed_f32_kernel, dim3((unsigned)n_ids), dim3(256), 0, (cudaStream_t)stream, (const float*)table,
+                                 (int)k, (const int*)ids, out);
+    return e == cudaSuccess ? kOk : kLaunchFailure;
+  }
   const cudaError_t e = launch(embed_q4k_kernel, dim3((unsigned)n_ids), dim3(256), 0, (cudaStream_t)stream,
                                (const uint8_t*)table, (int)(k / 256 * 144), (int)k, (const int*)ids, out);
   return e == cudaSuccess ? kOk : kLaunchFailure;

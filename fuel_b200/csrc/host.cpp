@@ -239,6 +239,8 @@ struct QTensorHandle {
 };
 }  // namespace
 
+void fuelq::set_last_error(const std::string& message) { g_last_error = message; }
+
 extern "C" {
 
 const char* fuelq_last_error(void) { return g_last_error.c_str(); }

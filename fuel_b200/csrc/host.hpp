@@ -35,6 +35,9 @@ class Error : public std::runtime_error {
   int32_t status_;
 };
 
+// message of the calling thread's last failure, as fuelq_last_error() returns it
+void set_last_error(const std::string& message);
+
 using Shape = std::vector<int64_t>;
 int64_t elem_count(const Shape& s);
 

@@ -31,6 +31,15 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
   return t;
 }
 
+// token ids -> rows of an f32 embedding table (k a multiple of 4)
+__global__ void __launch_bounds__(256) embed_f32_kernel(const float* table, int k, const int* ids, float* out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float4* row = reinterpret_cast<const float4*>(table + (size_t)ids[blockIdx.x] * k);
+  float4* o = reinterpret_cast<float4*>(out + (size_t)blockIdx.x * k);
+  for (int i = threadIdx.x; i < (k >> 2); i += blockDim.x) o[i] = row[i];
+}
+
 // token ids -> dequantized Q4_K rows of the embedding table (one CTA per id, 16 threads per super-block)
 __global__ void __launch_bounds__(256) embed_q4k_kernel(const uint8_t* table, int row_bytes, int k,
                                                         const int* ids, float* out) {

@@ -171,8 +171,9 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
  * All device pointers; `pos` points at the current position on the device so a step can be replayed
  * from a CUDA graph. */
 
-/* token ids -> dequantized rows of a Q4_K embedding table [vocab][k] (the reference keeps embeddings
- * in f32, fuel-core/src/lazy.rs:8626-8636; BASELINE config 4 quantizes them). */
+/* token ids -> rows of an embedding table [vocab][k]: ggml_type 12 = Q4_K blocks, dequantized on the fly
+ * (the synthetic 7B-architecture workload quantizes its embeddings); 0 = f32, which is how the reference keeps
+ * every embedding table after loading (fuel-core/src/lazy.rs:8626-8636, lazy_quantized_llama.rs:287). */
 int32_t fuelq_embed_rows(int32_t ggml_type, const void* table, int64_t k, const int32_t* ids, int64_t n_ids, float* out,
                          void* stream);
 /* x += delta (delta may be null), then out = x / sqrt(mean(x^2) + eps) * gain, per row
