@@ -52,7 +52,7 @@ class LlamaConfig:
 
 
 def q4km_mix(name: str, layer: int) -> T:
-    """Q4_K_M-style mix of BASELINE config 4: Q6_K for the output head and for attn_v / ffn_down in
+    """Q4_K_M-style mix of the 7B-architecture benchmark workload: Q6_K for the output head and for attn_v / ffn_down in
     every other layer, Q4_K elsewhere (embeddings included)."""
     if name == "output":
         return T.Q6K
@@ -166,6 +166,140 @@ def _quantize(t: T, w: torch.Tensor) -> torch.Tensor:
     return ops.quantize_weights(t, w.contiguous())
 
 
+_SEED_SLOT = {"attn_q": 1, "attn_k": 2, "attn_v": 3, "attn_output": 4, "ffn_gate": 5, "ffn_up": 6, "ffn_down": 7}
+_K_QUANTS = (T.Q4K, T.Q6K)  # their activations are Q8_K blocks; Q8_0 / Q4_0 weights take Q8_0 activations
+
+
+class SyntheticWeights:
+    """Random-init N(0, 0.02) weights quantized on the device in a given format mix; norm gains are ones."""
+
+    def __init__(self, cfg: LlamaConfig, device: torch.device, seed: int = 0, mix=q4km_mix):
+        self.cfg, self.device, self.seed, self.mix = cfg, device, seed, mix
+
+    def _shape(self, name: str):
+        c = self.cfg
+        kv = c.n_kv_heads * c.head_dim
+        return {"attn_q": (c.dim, c.dim), "attn_k": (kv, c.dim), "attn_v": (kv, c.dim), "attn_output": (c.dim, c.dim),
+                "ffn_gate": (c.ffn_dim, c.dim), "ffn_up": (c.ffn_dim, c.dim), "ffn_down": (c.dim, c.ffn_dim),
+                "output": (c.vocab, c.dim), "token_embd": (c.vocab, c.dim)}[name]
+
+    def _seed(self, name: str, layer: int) -> int:
+        if name == "token_embd":
+            return self.seed * 100003 + 1
+        if name == "output":
+            return self.seed * 100003 + 2
+        return self.seed * 100003 + 1000 * (layer + 1) + _SEED_SLOT[name]
+
+    def dtype(self, name: str, layer: int) -> T:
+        return T.Q4K if name == "token_embd" else self.mix(name, layer)
+
+    def rows(self, name: str, layer: int, lo: int, hi: int) -> torch.Tensor:
+        """GGUF blocks of rows [lo, hi) of a linear's [n_out, k_in] weight (rows are quantized independently, so a
+        slice of the quantized matrix is the quantized slice)."""
+        n, k = self._shape(name)
+        return _quantize(self.dtype(name, layer), init_weight(n, k, self._seed(name, layer), self.device)[lo:hi])
+
+    def embedding(self):
+        return T.Q4K, self.rows("token_embd", -1, 0, self.cfg.vocab)
+
+    def norm(self, name: str, layer: int) -> torch.Tensor:
+        return torch.ones(self.cfg.dim, dtype=torch.float32, device=self.device)
+
+    def export_gguf(self, path, version: int = 3) -> None:
+        """Write the whole model as a GGUF file with the llama.cpp tensor names the reference's loader reads
+        (fuel-core/src/lazy_quantized_llama.rs:224-236)."""
+        from . import gguf as G
+        c = self.cfg
+        meta = [("general.architecture", G.STRING, "llama"), ("llama.block_count", G.U32, c.n_layers),
+                ("llama.embedding_length", G.U32, c.dim), ("llama.feed_forward_length", G.U32, c.ffn_dim),
+                ("llama.attention.head_count", G.U32, c.n_heads), ("llama.attention.head_count_kv", G.U32, c.n_kv_heads),
+                ("llama.attention.layer_norm_rms_epsilon", G.F32, c.norm_eps), ("llama.rope.freq_base", G.F32, c.rope_theta),
+                ("llama.rope.dimension_count", G.U32, c.head_dim), ("llama.vocab_size", G.U32, c.vocab)]
+        tensors = []
+
+        def lin(fname, name, layer):
+            n, k = self._shape(name)
+            tensors.append((fname, self.dtype(name, layer), (n, k), self.rows(name, layer, 0, n).cpu().numpy()))
+
+        def vec(fname, name, layer):
+            tensors.append((fname, T.F32, (c.dim,), self.norm(name, layer).cpu().numpy().view(np.uint8)))
+
+        lin("token_embd.weight", "token_embd", -1)
+        for li in range(c.n_layers):
+            for name in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"):
+                lin(f"blk.{li}.{name}.weight", name, li)
+            vec(f"blk.{li}.attn_norm.weight", "attn_norm", li)
+            vec(f"blk.{li}.ffn_norm.weight", "ffn_norm", li)
+        vec("output_norm.weight", "output_norm", -1)
+        lin("output.weight", "output", -1)
+        G.write_gguf(path, meta, tensors, version=version)
+
+
+class GgufWeights:
+    """Weights of a GGUF checkpoint with llama.cpp's LLaMA tensor names, as the reference's loader takes them
+    (fuel-core/src/lazy_quantized_llama.rs:224-330): linears stay in the file's block format — each rank copies just
+    its rows from the mapping to its GPU —, norm gains and the embedding table become f32; `output.weight` falls
+    back to `token_embd.weight` (tied embeddings) when absent."""
+
+    LINEAR_FORMATS = (T.Q4K, T.Q6K, T.Q8_0, T.Q4_0)
+
+    def __init__(self, path, device: torch.device):
+        from .gguf import GgufFile
+        self.file, self.device = GgufFile(path), device
+
+    def _fname(self, name: str, layer: int) -> str:
+        if name in ("token_embd", "output_norm"):
+            return f"{name}.weight"
+        if name == "output":
+            return "output.weight" if "output.weight" in self.file.tensor_infos else "token_embd.weight"
+        return f"blk.{layer}.{name}.weight"
+
+    def config(self, max_seq: int = 640) -> LlamaConfig:
+        """Architecture from the `llama.*` metadata keys and the tensor shapes."""
+        m, ti = self.file.metadata, self.file.tensor_infos
+        arch = m.get("general.architecture", "llama")
+        if arch != "llama":
+            raise ValueError(f"gguf: architecture {arch!r} is not the LLaMA layout")
+        vocab, dim = self.file.tensor_info("token_embd.weight").shape
+        n_heads = int(m["llama.attention.head_count"])
+        layers = int(m["llama.block_count"])
+        return LlamaConfig(dim=dim, n_layers=layers, n_heads=n_heads,
+                           n_kv_heads=int(m.get("llama.attention.head_count_kv", n_heads)), head_dim=dim // n_heads,
+                           ffn_dim=ti["blk.0.ffn_gate.weight"].shape[0], vocab=vocab,
+                           norm_eps=float(m.get("llama.attention.layer_norm_rms_epsilon", 1e-5)),
+                           rope_theta=float(m.get("llama.rope.freq_base", 10000.0)), max_seq=max_seq)
+
+    def check(self, cfg: LlamaConfig) -> None:
+        """Element counts as the reference checks them (lazy_quantized_llama.rs:271-277, 288-293)."""
+        kv = cfg.n_kv_heads * cfg.head_dim
+        want = {"attn_q": cfg.dim * cfg.dim, "attn_k": kv * cfg.dim, "attn_v": kv * cfg.dim, "attn_output": cfg.dim * cfg.dim,
+                "ffn_gate": cfg.ffn_dim * cfg.dim, "ffn_up": cfg.ffn_dim * cfg.dim, "ffn_down": cfg.dim * cfg.ffn_dim}
+        for li in range(cfg.n_layers):
+            for name, n in want.items():
+                info = self.file.tensor_info(self._fname(name, li))
+                if info.elem_count() != n:
+                    raise ValueError(f"gguf: tensor {self._fname(name, li)!r} has {info.elem_count()} elements, expected {n}")
+        if self.file.tensor_info("token_embd.weight").elem_count() != cfg.vocab * cfg.dim:
+            raise ValueError("gguf token_embd.weight: wrong element count")
+
+    def dtype(self, name: str, layer: int) -> T:
+        t = self.file.tensor_info(self._fname(name, layer)).ggml_dtype
+        if t not in self.LINEAR_FORMATS:
+            raise NotImplementedError(f"gguf: {self._fname(name, layer)!r} is {t.name}; the quantized mat-vec takes "
+                                      + ", ".join(x.name for x in self.LINEAR_FORMATS))
+        return t
+
+    def rows(self, name: str, layer: int, lo: int, hi: int) -> torch.Tensor:
+        self.dtype(name, layer)
+        return self.file.load(self._fname(name, layer), self.device, lo, hi)
+
+    def embedding(self):
+        return T.F32, self.file.load_f32("token_embd.weight", self.device).contiguous()
+
+    def norm(self, name: str, layer: int) -> torch.Tensor:
+        return self.file.load_f32(self._fname(name, layer), self.device).contiguous()
+
+
 class _Linear:
     """Rows [r0, r1) of a quantized [n, k] weight, kept as GGUF blocks on the device."""
 
@@ -179,7 +313,8 @@ class _Linear:
 
 class QLlama:
     def __init__(self, cfg: LlamaConfig, device: torch.device, rank: int = 0, world: int = 1, seed: int = 0,
-                 mix=q4km_mix, comm: str = "nccl"):
+                 mix=q4km_mix, comm: str = "nccl", weights=None):
+        """`weights`: a weight source (GgufWeights, SyntheticWeights); default: synthetic from `seed` and `mix`."""
         assert comm in ("nccl", "peer")
         assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0
         assert cfg.dim % world == 0 and cfg.vocab % world == 0 and cfg.head_dim == 128
@@ -197,39 +332,39 @@ class QLlama:
         qd, kvd = self.hl * c.head_dim, self.kvl * c.head_dim
         f32 = dict(dtype=torch.float32, device=device)
 
-        def rows(w, lo, hi):
-            return w[lo:hi]
+        src = weights if weights is not None else SyntheticWeights(cfg, device, seed, mix)
+        self.embed_dtype, self.embed = src.embedding()
+        k_quants_only = True
 
-        self.embed = _quantize(T.Q4K, init_weight(c.vocab, c.dim, seed * 100003 + 1, device))
+        def lin(names, li, lo_hi, k):
+            """One _Linear over the stacked rows of `names` (all the same format), each cut to its [lo, hi)."""
+            t = src.dtype(names[0], li)
+            parts = [src.rows(nm, li, lo, hi) for nm, (lo, hi) in zip(names, lo_hi)]
+            return _Linear(t, parts[0] if len(parts) == 1 else torch.cat(parts), sum(hi - lo for lo, hi in lo_hi), k)
+
+        d_rng = (r * c.dim // g, (r + 1) * c.dim // g)
+        q_rng, kv_rng, f_rng = (r * qd, (r + 1) * qd), (r * kvd, (r + 1) * kvd), (self.f_lo, self.f_hi)
         self.layers = []
         for li in range(c.n_layers):
-            s0 = seed * 100003 + 1000 * (li + 1)
-            wq = rows(init_weight(c.dim, c.dim, s0 + 1, device), r * qd, (r + 1) * qd)
-            wk = rows(init_weight(c.n_kv_heads * c.head_dim, c.dim, s0 + 2, device), r * kvd, (r + 1) * kvd)
-            wv = rows(init_weight(c.n_kv_heads * c.head_dim, c.dim, s0 + 3, device), r * kvd, (r + 1) * kvd)
-            wo = rows(init_weight(c.dim, c.dim, s0 + 4, device), r * c.dim // g, (r + 1) * c.dim // g)
-            wg = rows(init_weight(c.ffn_dim, c.dim, s0 + 5, device), self.f_lo, self.f_hi)
-            wu = rows(init_weight(c.ffn_dim, c.dim, s0 + 6, device), self.f_lo, self.f_hi)
-            wd = rows(init_weight(c.dim, c.ffn_dim, s0 + 7, device), r * c.dim // g, (r + 1) * c.dim // g)
-            tq, tv, to, tg, td = (mix("attn_q", li), mix("attn_v", li), mix("attn_output", li), mix("ffn_gate", li),
-                                  mix("ffn_down", li))
+            tq, tk, tv = src.dtype("attn_q", li), src.dtype("attn_k", li), src.dtype("attn_v", li)
+            assert tq == tk and src.dtype("ffn_gate", li) == src.dtype("ffn_up", li), "q/k and gate/up are stacked: one format each"
             # q, k (and v, where it has the same format) are one stacked matrix: one launch instead of two or three
-            qkv_rows = torch.cat([wq, wk, wv]) if tv == tq else torch.cat([wq, wk])
-            self.layers.append(dict(
-                qk=_Linear(tq, _quantize(tq, qkv_rows), qkv_rows.shape[0], c.dim),
-                v=None if tv == tq else _Linear(tv, _quantize(tv, wv), kvd, c.dim),
-                o=_Linear(to, _quantize(to, wo), c.dim // g, c.dim),
-                gu=_Linear(tg, _quantize(tg, torch.cat([wg, wu])), 2 * fl, c.dim),
-                down=_Linear(td, _quantize(td, wd), c.dim // g, c.ffn_dim),
-                attn_norm=torch.ones(c.dim, **f32), ffn_norm=torch.ones(c.dim, **f32),
+            stacked_v = tv == tq
+            layer = dict(
+                qk=lin(("attn_q", "attn_k", "attn_v") if stacked_v else ("attn_q", "attn_k"), li,
+                       (q_rng, kv_rng, kv_rng) if stacked_v else (q_rng, kv_rng), c.dim),
+                v=None if stacked_v else lin(("attn_v",), li, (kv_rng,), c.dim),
+                o=lin(("attn_output",), li, (d_rng,), c.dim),
+                gu=lin(("ffn_gate", "ffn_up"), li, (f_rng, f_rng), c.dim),
+                down=lin(("ffn_down",), li, (d_rng,), c.ffn_dim),
+                attn_norm=src.norm("attn_norm", li), ffn_norm=src.norm("ffn_norm", li),
                 kc=torch.zeros(self.kvl, c.max_seq, c.head_dim, **f32),
-                vc=torch.zeros(self.kvl, c.max_seq, c.head_dim, **f32)))
-            del wq, wk, wv, wo, wg, wu, wd
-        th = mix("output", -1)
-        wout = rows(init_weight(c.vocab, c.dim, seed * 100003 + 2, device), r * c.vocab // g, (r + 1) * c.vocab // g)
-        self.head = _Linear(th, _quantize(th, wout), c.vocab // g, c.dim)
-        del wout
-        self.out_norm = torch.ones(c.dim, **f32)
+                vc=torch.zeros(self.kvl, c.max_seq, c.head_dim, **f32))
+            k_quants_only &= all(layer[nm] is None or layer[nm].dtype in _K_QUANTS for nm in ("qk", "v", "o", "gu", "down"))
+            self.layers.append(layer)
+        self.head = lin(("output",), -1, ((r * c.vocab // g, (r + 1) * c.vocab // g),), c.dim)
+        k_quants_only &= self.head.dtype in _K_QUANTS
+        self.out_norm = src.norm("output_norm", -1)
         cos, sin = rope_tables(c)
         self.cos, self.sin = torch.from_numpy(cos).to(device), torch.from_numpy(sin).to(device)
 
@@ -256,7 +391,7 @@ class QLlama:
             self.logits = torch.zeros(c.vocab, **f32)
         else:
             self.attn, self.o, self.s, self.d, self.logits = self.attn_l, self.o_l, self.s_l, self.d_l, self.logits_l
-        nb = max(_L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.dim), _L.fuelq_act_packed_bytes(int(T.Q4K), 1, c.ffn_dim))
+        nb = max(_L.fuelq_act_packed_bytes(int(t), 1, k) for t in (T.Q4K, T.Q8_0) for k in (c.dim, c.ffn_dim))
         self.packed = torch.zeros(nb, dtype=torch.uint8, device=device)
         self.attn_ws = torch.zeros(max(_L.fuelq_attn_decode_workspace_bytes(self.hl), 16), dtype=torch.uint8, device=device)
         # per layer: what the attention call needs to rotate q/k itself and append k, v to that layer's caches
@@ -273,18 +408,47 @@ class QLlama:
         if comm == "peer":
             self._init_peer()
         self.graph = None
-        self.fused = True  # single-GPU step uses the fused producers
+        # The fused producers and the in-kernel exchange write Q8_K activation blocks, which is what k-quant weights
+        # take; a model with Q8_0 / Q4_0 linears runs the plain step, which quantizes per consumer.
+        self.fused = k_quants_only
+        if comm == "peer" and not k_quants_only:
+            raise NotImplementedError("comm='peer' needs k-quant (Q4_K / Q6_K) linears")
         self.weight_bytes = (sum(l[k].blocks.numel() for l in self.layers for k in ("qk", "v", "o", "gu", "down") if l[k] is not None)
                              + self.head.blocks.numel())
+
+    @classmethod
+    def from_gguf(cls, path, device: torch.device, rank: int = 0, world: int = 1, comm: str = "nccl", max_seq: int = 640,
+                  cfg: LlamaConfig | None = None) -> "QLlama":
+        """Load a GGUF checkpoint (the reference's `from_gguf`, fuel-core/src/lazy_quantized_llama.rs:241-330). The
+        architecture comes from the file's metadata unless `cfg` is given, as the reference's caller gives it."""
+        w = GgufWeights(path, device)
+        cfg = cfg or w.config(max_seq)
+        w.check(cfg)
+        model = cls(cfg, device, rank, world, comm=comm, weights=w)
+        w.file.close()
+        return model
 
     # ---- one decode step: token, pos -> next_token; pos += 1; token = next_token
     def _gather(self, full: torch.Tensor, local: torch.Tensor) -> None:
         if self.world > 1:
             dist.all_gather_into_tensor(full, local)
 
-    def _quant(self, x: torch.Tensor, k: int, stream: int) -> None:
-        _check(_L.fuelq_quantize_act_packed(int(T.Q4K), 1, k, x.data_ptr(), self.packed.data_ptr(), self.packed.numel(),
+    def _quant(self, x: torch.Tensor, k: int, stream: int, dtype: T = T.Q4K) -> None:
+        """Activation blocks for a consumer of weight format `dtype` (Q8_K for k-quants, Q8_0 for Q8_0 / Q4_0)."""
+        _check(_L.fuelq_quantize_act_packed(int(dtype), 1, k, x.data_ptr(), self.packed.data_ptr(), self.packed.numel(),
                                             stream), "fuelq_quantize_act_packed")
+
+    def _mv(self, lins, outs, x: torch.Tensor, k: int, stream: int) -> None:
+        """Plain step: mat-vecs of the same vector x, re-quantizing only when the activation format changes."""
+        fmt = None
+        for lin, out in zip(lins, outs):
+            if lin is None:
+                continue
+            want = lin.dtype in _K_QUANTS
+            if want != fmt:
+                self._quant(x, k, stream, lin.dtype)
+                fmt = want
+            lin.matvec_packed(self.packed, out, stream)
 
     def step(self) -> None:
         if self.comm == "peer":
@@ -330,7 +494,7 @@ class QLlama:
         pr = self.peers_ref
         dl, vl, fl = c.dim // self.world, c.vocab // self.world, self.f_hi - self.f_lo
         qd = self.hl * c.head_dim
-        _check(_L.fuelq_embed_rows(int(T.Q4K), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
+        _check(_L.fuelq_embed_rows(int(self.embed_dtype), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
                "fuelq_embed_rows")
         delta, wait = None, -1
         for li, l in enumerate(self.layers):
@@ -373,7 +537,7 @@ class QLlama:
         st = torch.cuda.current_stream().cuda_stream
         scale = 1.0 / math.sqrt(c.head_dim)
         pk, pkn = self.packed.data_ptr(), self.packed.numel()
-        _check(_L.fuelq_embed_rows(int(T.Q4K), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
+        _check(_L.fuelq_embed_rows(int(self.embed_dtype), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
                "fuelq_embed_rows")
         delta = None
         qd = self.hl * c.head_dim
@@ -404,39 +568,31 @@ class QLlama:
         c = self.cfg
         st = torch.cuda.current_stream().cuda_stream
         scale = 1.0 / math.sqrt(c.head_dim)
-        _check(_L.fuelq_embed_rows(int(T.Q4K), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
+        _check(_L.fuelq_embed_rows(int(self.embed_dtype), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
                "fuelq_embed_rows")
         delta = None
         for li, l in enumerate(self.layers):
             _check(_L.fuelq_add_rmsnorm(self.x.data_ptr(), delta.data_ptr() if delta is not None else None,
                                         l["attn_norm"].data_ptr(), self.h.data_ptr(), 1, c.dim, c.norm_eps, st), "add_rmsnorm")
-            self._quant(self.h, c.dim, st)
-            l["qk"].matvec_packed(self.packed, self.qkv if l["v"] is None else self.qk, st)
-            if l["v"] is not None:
-                l["v"].matvec_packed(self.packed, self.v, st)
-            qd = self.hl * c.head_dim
+            self._mv((l["qk"], l["v"]), (self.qkv if l["v"] is None else self.qk, self.v), self.h, c.dim, st)
             _check(_L.fuelq_attn_decode(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.attn_l.data_ptr(),
                                         self.pos.data_ptr(), self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
                                         self.attn_ws.numel(), self.rope_refs[li], st), "attn_decode")
             self._gather(self.attn, self.attn_l)
-            self._quant(self.attn, c.dim, st)
-            l["o"].matvec_packed(self.packed, self.o_l, st)
+            self._mv((l["o"],), (self.o_l,), self.attn, c.dim, st)
             self._gather(self.o, self.o_l)
             _check(_L.fuelq_add_rmsnorm(self.x.data_ptr(), self.o.data_ptr(), l["ffn_norm"].data_ptr(), self.h.data_ptr(), 1,
                                         c.dim, c.norm_eps, st), "add_rmsnorm")
-            self._quant(self.h, c.dim, st)
-            l["gu"].matvec_packed(self.packed, self.gu, st)
+            self._mv((l["gu"],), (self.gu,), self.h, c.dim, st)
             fl = self.f_hi - self.f_lo
             _check(_L.fuelq_swiglu(self.gu.data_ptr(), self.gu.data_ptr() + 4 * fl, self.s_l.data_ptr(), fl, st), "swiglu")
             self._gather(self.s, self.s_l)
-            self._quant(self.s, c.ffn_dim, st)
-            l["down"].matvec_packed(self.packed, self.d_l, st)
+            self._mv((l["down"],), (self.d_l,), self.s, c.ffn_dim, st)
             self._gather(self.d, self.d_l)
             delta = self.d
         _check(_L.fuelq_add_rmsnorm(self.x.data_ptr(), delta.data_ptr(), self.out_norm.data_ptr(), self.h.data_ptr(), 1, c.dim,
                                     c.norm_eps, st), "add_rmsnorm")
-        self._quant(self.h, c.dim, st)
-        self.head.matvec_packed(self.packed, self.logits_l, st)
+        self._mv((self.head,), (self.logits_l,), self.h, c.dim, st)
         self._gather(self.logits, self.logits_l)
         _check(_L.fuelq_argmax_last(self.logits.data_ptr(), c.vocab, self.next_token.data_ptr(), st), "argmax_last")
         self.pos.add_(1)

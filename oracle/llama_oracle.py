@@ -29,10 +29,13 @@ def _rope(x, cos, sin):               # x [heads, hd]
 
 
 class OracleLlama:
-    """weights: dict name -> (ggml type id, uint8 blocks, n, k); norm gains are ones."""
+    """weights: dict name -> (ggml type id, uint8 blocks, n, k). Norm gains are ones unless a layer dict holds
+    "attn_norm" / "ffn_norm" f32 vectors and `out_norm` is given. `embed_blocks` is the Q4_K block bytes of the
+    embedding table, or an f32 [vocab, dim] array (how the reference holds it after loading a checkpoint)."""
 
-    def __init__(self, cfg, embed_blocks, layers, head, cos, sin):
+    def __init__(self, cfg, embed_blocks, layers, head, cos, sin, out_norm=None):
         self.cfg, self.embed, self.layers, self.head, self.cos, self.sin = cfg, embed_blocks, layers, head, cos, sin
+        self.out_norm = out_norm
         c = cfg
         self.kc = np.zeros((c.n_layers, c.n_kv_heads, c.max_seq, c.head_dim), np.float32)
         self.vc = np.zeros_like(self.kc)
@@ -45,11 +48,14 @@ class OracleLlama:
 
     def step(self, token: int):
         c = self.cfg
-        rb = c.dim // 256 * 144
-        x = O.dequantize(O.Q4K, self.embed[token * rb:(token + 1) * rb]).astype(np.float32)
+        if self.embed.dtype == np.float32:
+            x = self.embed[token].astype(np.float32)
+        else:
+            rb = c.dim // 256 * 144
+            x = O.dequantize(O.Q4K, self.embed[token * rb:(token + 1) * rb]).astype(np.float32)
         ones = np.ones(c.dim, np.float32)
         for li, l in enumerate(self.layers):
-            h = _rmsnorm(x, ones, c.norm_eps)
+            h = _rmsnorm(x, l.get("attn_norm", ones), c.norm_eps)
             q = self._lin(l["q"], h).reshape(c.n_heads, c.head_dim)
             k = self._lin(l["k"], h).reshape(c.n_kv_heads, c.head_dim)
             v = self._lin(l["v"], h).reshape(c.n_kv_heads, c.head_dim)
@@ -65,11 +71,11 @@ class OracleLlama:
                 e = np.exp(s - s.max()).astype(np.float32)
                 out[hd] = (e / e.sum(dtype=np.float32)) @ vv
             x = (x + self._lin(l["o"], out.reshape(-1))).astype(np.float32)
-            h = _rmsnorm(x, ones, c.norm_eps)
+            h = _rmsnorm(x, l.get("ffn_norm", ones), c.norm_eps)
             g, u = self._lin(l["gate"], h), self._lin(l["up"], h)
             s = ((g / (np.float32(1.0) + np.exp(-g))) * u).astype(np.float32)
             x = (x + self._lin(l["down"], s)).astype(np.float32)
-        h = _rmsnorm(x, ones, c.norm_eps)
+        h = _rmsnorm(x, ones if self.out_norm is None else self.out_norm, c.norm_eps)
         logits = self._lin(self.head, h)
         self.pos += 1
         m = logits.max()
