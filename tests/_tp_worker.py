@@ -1,5 +1,6 @@
 """Worker for the multi-GPU tests: one rank per GPU under torch.distributed.run. Builds the small test model
-tensor-parallel over all ranks with the chosen exchange, decodes, and has rank 0 print one JSON line."""
+tensor-parallel over all ranks with the chosen exchange (argv[1]), decodes, and has rank 0 print one JSON line.
+With a path as argv[2], rank 0 first writes the model to that GGUF file and every rank loads its rows from it."""
 import faulthandler
 import json
 import os
@@ -20,9 +21,15 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from fuel_b200 import _lib, ops
-    from fuel_b200.llama import LlamaConfig, QLlama
+    from fuel_b200.llama import LlamaConfig, QLlama, SyntheticWeights
     cfg = LlamaConfig(vocab=512, dim=1024, n_layers=3, n_heads=8, n_kv_heads=8, ffn_dim=2816, max_seq=96)
-    model = QLlama(cfg, dev, rank, world, comm=comm)
+    if len(sys.argv) > 2:
+        if rank == 0:
+            SyntheticWeights(cfg, dev).export_gguf(sys.argv[2])
+        dist.barrier()
+        model = QLlama.from_gguf(sys.argv[2], dev, rank, world, comm=comm, max_seq=cfg.max_seq)
+    else:
+        model = QLlama(cfg, dev, rank, world, comm=comm)
     prompt = np.random.Generator(np.random.PCG64(4)).integers(0, 512, 20).tolist()
     out = {}
     try:

@@ -21,14 +21,17 @@ def _single_gpu_tokens():
     return model.generate(prompt, 12), float(model.logits.double().sum().item())
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl"])
-def test_two_gpus_decode_the_same_tokens(comm):
+@pytest.mark.parametrize("comm,from_file", [("peer", False), ("nccl", False), ("peer", True)])
+def test_two_gpus_decode_the_same_tokens(comm, from_file, tmp_path):
+    """from_file: the ranks load their row slices from a GGUF file that rank 0 wrote, instead of generating them."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     want, logits_sum = _single_gpu_tokens()
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(ROOT, "tests", "_tp_worker.py"), comm]
+    if from_file:
+        cmd.append(str(tmp_path / "tp.gguf"))
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=400)
     lines = [l for l in r.stdout.splitlines() if l.startswith("TPRESULT ")]
     assert r.returncode == 0 and lines, (r.stdout[-2000:], r.stderr[-2000:])
