@@ -23,11 +23,13 @@ struct BlkQ8K  { float d; int8_t qs[256]; int16_t bsums[16]; };                 
 static_assert(sizeof(BlkQ4_0) == 18, "Q4_0");
 static_assert(sizeof(BlkQ8_0) == 34, "Q8_0");
 static_assert(sizeof(BlkQ4K) == 144, "Q4_K");
+struct BlkQ5K  { uint16_t d; uint16_t dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; }; // k_quants.rs:142-148
+static_assert(sizeof(BlkQ5K) == 176, "Q5_K");
 static_assert(sizeof(BlkQ6K) == 210, "Q6_K");
 static_assert(sizeof(BlkQ8K) == 292, "Q8_K");
 
 // GGUF type ids, fuel-ir/src/quantized.rs:35-75.
-enum : int { GGML_Q4_0 = 2, GGML_Q8_0 = 8, GGML_Q4K = 12, GGML_Q6K = 14, GGML_Q8K = 15 };
+enum : int { GGML_Q4_0 = 2, GGML_Q8_0 = 8, GGML_Q4K = 12, GGML_Q5K = 13, GGML_Q6K = 14, GGML_Q8K = 15 };
 
 // IEEE binary16 <-> binary32, round-to-nearest-even, what `half::f16` does.
 static inline float h2f(uint16_t h) {

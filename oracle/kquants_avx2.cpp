@@ -119,6 +119,66 @@ float q4k_q8k_dot_avx2(int64_t n, const BlkQ4K* xs, const BlkQ8K* ys) {
   return reduce8(acc) + _mm_cvtss_f32(acc_m);
 }
 
+// avx.rs:684-793: as Q4_K's, with the fifth bits merged in before the multiply, and the mins term kept as one scalar
+// f32 sum (dmin * the block's integer total) instead of four lanes.
+float q5k_q8k_dot_avx2(int64_t n, const BlkQ5K* xs, const BlkQ8K* ys) {
+  const __m256i low4 = _mm256_set1_epi8(0xF);
+  __m256 acc = _mm256_setzero_ps();
+  float summs = 0.f;
+  for (int64_t ib = 0; ib < n / QK_K; ++ib) {
+    const BlkQ5K& x = xs[ib];
+    const BlkQ8K& y = ys[ib];
+    const float d = y.d * h2f(x.d);
+    const float dmin = -y.d * h2f(x.dmin);
+
+    uint32_t u[4];
+    std::memcpy(u, x.scales, 12);
+    u[3] = ((u[2] >> 4) & 0x0f0f0f0fu) | (((u[1] >> 6) & 0x03030303u) << 4);
+    const uint32_t keep = u[1] & 0x3f3f3f3fu;
+    u[1] = (u[2] & 0x0f0f0f0fu) | (((u[0] >> 6) & 0x03030303u) << 4);
+    u[2] = keep;
+    u[0] &= 0x3f3f3f3fu;
+    const __m256i sc_mn = _mm256_cvtepu8_epi16(_mm_set_epi32((int)u[3], (int)u[2], (int)u[1], (int)u[0]));
+
+    const __m256i bs = _mm256_loadu_si256((const __m256i*)y.bsums);
+    const __m128i pair_sums = _mm_hadd_epi16(_mm256_extracti128_si256(bs, 0), _mm256_extracti128_si256(bs, 1));
+    const __m128i mprod = _mm_madd_epi16(_mm256_extracti128_si256(sc_mn, 1), pair_sums);
+    const __m128i zero = _mm_setzero_si128();
+    const __m128i tot = _mm_hadd_epi32(_mm_hadd_epi32(mprod, zero), zero);
+    summs += dmin * (float)_mm_extract_epi32(tot, 0);
+
+    const __m128i sc128 = _mm256_extracti128_si256(sc_mn, 0);
+    const __m256i scales = _mm256_insertf128_si256(_mm256_castsi128_si256(sc128), sc128, 1);
+    const __m256i hbits = _mm256_loadu_si256((const __m256i*)x.qh);
+
+    __m256i sumi = _mm256_setzero_si256();
+    const uint8_t* q5 = x.qs;
+    const int8_t* q8 = y.qs;
+    for (int j = 0; j < QK_K / 64; ++j) {
+      const __m256i s_lo = bcast_word(scales, 2 * j);
+      const __m256i s_hi = bcast_word(scales, 2 * j + 1);
+      const __m256i bits = _mm256_loadu_si256((const __m256i*)q5);
+      q5 += 32;
+      // bit 2j (2j+1) of every qh byte moved to bit 4 of the same byte
+      const __m256i h0 = _mm256_slli_epi16(_mm256_srl_epi16(_mm256_and_si256(hbits, _mm256_set1_epi8((char)(1 << (2 * j)))),
+                                                            _mm_cvtsi32_si128(2 * j)), 4);
+      const __m256i h1 = _mm256_slli_epi16(_mm256_srl_epi16(_mm256_and_si256(hbits, _mm256_set1_epi8((char)(2 << (2 * j)))),
+                                                            _mm_cvtsi32_si128(2 * j + 1)), 4);
+      const __m256i lo = _mm256_add_epi8(_mm256_and_si256(bits, low4), h0);
+      const __m256i hi = _mm256_add_epi8(_mm256_and_si256(_mm256_srli_epi16(bits, 4), low4), h1);
+      const __m256i y_lo = _mm256_loadu_si256((const __m256i*)q8);
+      q8 += 32;
+      const __m256i y_hi = _mm256_loadu_si256((const __m256i*)q8);
+      q8 += 32;
+      const __m256i p0 = _mm256_madd_epi16(s_lo, _mm256_maddubs_epi16(lo, y_lo));
+      const __m256i p1 = _mm256_madd_epi16(s_hi, _mm256_maddubs_epi16(hi, y_hi));
+      sumi = _mm256_add_epi32(sumi, _mm256_add_epi32(p0, p1));
+    }
+    acc = _mm256_fmadd_ps(_mm256_set1_ps(d), _mm256_cvtepi32_ps(sumi), acc);
+  }
+  return reduce8(acc) + summs;
+}
+
 // Byte `b` of the 16 scales broadcast to 8 bytes, then the next one to the other
 // 8 — the 128-bit pattern {s[2i] x8, s[2i+1] x8} of avx.rs:246-255.
 static inline __m128i bcast_scale_pair(__m128i scales, int i) {

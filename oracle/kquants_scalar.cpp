@@ -290,6 +290,111 @@ float q4k_q8k_dot_scalar(int64_t n, const BlkQ4K* xs, const BlkQ8K* ys) {
   return sumf + s;
 }
 
+// ---------------------------------------------------------------- Q5_K
+// fuel-quantized/src/k_quants.rs:1729-1796: Q4_K's fit with 32 levels; the fifth bit of element 64g+t goes to bit 2g of
+// qh[t], that of element 64g+32+t to bit 2g+1.
+void q5k_from_float(const float* xs, int64_t k, BlkQ5K* ys) {
+  const int64_t nb = k / QK_K;
+  for (int64_t ib = 0; ib < nb; ++ib) {
+    const float* x = xs + ib * QK_K;
+    BlkQ5K& blk = ys[ib];
+    float mins[8], scales[8];
+    for (int j = 0; j < 8; ++j) make_qkx1(31, 5, x + 32 * j, 32, &scales[j], &mins[j]);
+    float max_scale = 0.f, max_min = 0.f;
+    for (int j = 0; j < 8; ++j) max_scale = fmaxf(scales[j], max_scale);
+    for (int j = 0; j < 8; ++j) max_min = fmaxf(mins[j], max_min);
+    const float inv_scale = max_scale > 0.f ? 63.0f / max_scale : 0.f;
+    const float inv_min = max_min > 0.f ? 63.0f / max_min : 0.f;
+    std::memset(blk.scales, 0, sizeof(blk.scales));
+    for (int j = 0; j < 8; ++j) {
+      const uint8_t ls = (uint8_t)std::min(nearest_int(inv_scale * scales[j]), 63);
+      const uint8_t lm = (uint8_t)std::min(nearest_int(inv_min * mins[j]), 63);
+      if (j < 4) {
+        blk.scales[j] = ls;
+        blk.scales[j + 4] = lm;
+      } else {
+        blk.scales[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+        blk.scales[j - 4] |= (uint8_t)((ls >> 4) << 6);
+        blk.scales[j] |= (uint8_t)((lm >> 4) << 6);
+      }
+    }
+    blk.d = f2h(max_scale / 63.0f);
+    blk.dmin = f2h(max_min / 63.0f);
+    uint8_t L[QK_K] = {0};
+    for (int j = 0; j < 8; ++j) {
+      uint8_t sc, m;
+      scale_min_k4(j, blk.scales, &sc, &m);
+      const float d = h2f(blk.d) * (float)sc;
+      if (d != 0.f) {
+        const float dm = h2f(blk.dmin) * (float)m;
+        for (int t = 0; t < 32; ++t)
+          L[32 * j + t] = (uint8_t)clampi(nearest_int((x[32 * j + t] + dm) / d), 0, 31);
+      }
+    }
+    std::memset(blk.qh, 0, sizeof(blk.qh));
+    for (int g = 0; g < 4; ++g)
+      for (int t = 0; t < 32; ++t) {
+        uint8_t l1 = L[64 * g + t], l2 = L[64 * g + 32 + t];
+        if (l1 > 15) { l1 -= 16; blk.qh[t] |= (uint8_t)(1u << (2 * g)); }
+        if (l2 > 15) { l2 -= 16; blk.qh[t] |= (uint8_t)(2u << (2 * g)); }
+        blk.qs[32 * g + t] = (uint8_t)(l1 | (l2 << 4));
+      }
+  }
+}
+
+// fuel-quantized/src/k_quants.rs:1889-1923: y = d1 * (nibble + 16*bit) - m1, the sum inside the brackets exact.
+void q5k_to_float(const BlkQ5K* xs, int64_t k, float* ys) {
+  for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+    const BlkQ5K& b = xs[ib];
+    float* y = ys + ib * QK_K;
+    const float d = h2f(b.d), mn = h2f(b.dmin);
+    int o = 0;
+    for (int g = 0; g < 4; ++g) {
+      const uint8_t* q = b.qs + 32 * g;
+      uint8_t sc, m;
+      scale_min_k4(2 * g, b.scales, &sc, &m);
+      const float d1 = d * (float)sc, m1 = mn * (float)m;
+      scale_min_k4(2 * g + 1, b.scales, &sc, &m);
+      const float d2 = d * (float)sc, m2 = mn * (float)m;
+      for (int t = 0; t < 32; ++t) y[o++] = d1 * ((float)(q[t] & 0xF) + ((b.qh[t] >> (2 * g)) & 1 ? 16.f : 0.f)) - m1;
+      for (int t = 0; t < 32; ++t) y[o++] = d2 * ((float)(q[t] >> 4) + ((b.qh[t] >> (2 * g + 1)) & 1 ? 16.f : 0.f)) - m2;
+    }
+  }
+}
+
+// fuel-quantized/src/k_quants.rs:1644-1727 (canonical summation order; Q4_K's with 5-bit values).
+float q5k_q8k_dot_scalar(int64_t n, const BlkQ5K* xs, const BlkQ8K* ys) {
+  int8_t a8[QK_K];
+  float lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float sumf = 0.f;
+  for (int64_t ib = 0; ib < n / QK_K; ++ib) {
+    const BlkQ5K& x = xs[ib];
+    const BlkQ8K& y = ys[ib];
+    for (int g = 0; g < 4; ++g)
+      for (int t = 0; t < 32; ++t) {
+        a8[64 * g + t] = (int8_t)((x.qs[32 * g + t] & 0xF) + (((x.qh[t] >> (2 * g)) & 1) ? 16 : 0));
+        a8[64 * g + 32 + t] = (int8_t)((x.qs[32 * g + t] >> 4) + (((x.qh[t] >> (2 * g + 1)) & 1) ? 16 : 0));
+      }
+    uint8_t sc[8], mn[8];
+    for (int j = 0; j < 8; ++j) scale_min_k4(j, x.scales, &sc[j], &mn[j]);
+    int32_t sumi = 0;
+    for (int j = 0; j < 16; ++j) sumi += (int32_t)y.bsums[j] * (int32_t)mn[j / 2];
+    int32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < 8; ++j)
+      for (int t = 0; t < 32; ++t) {
+        const int16_t p = (int16_t)((int16_t)y.qs[32 * j + t] * (int16_t)a8[32 * j + t]);
+        acc[t & 7] += (int32_t)sc[j] * (int32_t)p;
+      }
+    const float d = h2f(x.d) * y.d;
+    for (int l = 0; l < 8; ++l) lane[l] += d * (float)acc[l];
+    const float dmin = h2f(x.dmin) * y.d;
+    sumf -= dmin * (float)sumi;
+  }
+  float s = 0.f;
+  for (int l = 0; l < 8; ++l) s += lane[l];
+  return sumf + s;
+}
+
 // ---------------------------------------------------------------- Q6_K
 // fuel-quantized/src/utils.rs:62-191 with rmse_type=1, qw=null (weights x^2).
 // Writes L[i] in [0, 2*nmax) and returns the fitted scale.

@@ -24,12 +24,16 @@ void q8k_to_float(const BlkQ8K*, int64_t, float*);
 void q4k_from_float(const float*, int64_t, BlkQ4K*);
 void q4k_to_float(const BlkQ4K*, int64_t, float*);
 float q4k_q8k_dot_scalar(int64_t, const BlkQ4K*, const BlkQ8K*);
+void q5k_from_float(const float*, int64_t, BlkQ5K*);
+void q5k_to_float(const BlkQ5K*, int64_t, float*);
+float q5k_q8k_dot_scalar(int64_t, const BlkQ5K*, const BlkQ8K*);
 void q6k_from_float(const float*, int64_t, BlkQ6K*);
 void q6k_to_float(const BlkQ6K*, int64_t, float*);
 float q6k_q8k_dot_scalar(int64_t, const BlkQ6K*, const BlkQ8K*);
 float q4_0_q8_0_dot_avx2(int64_t, const BlkQ4_0*, const BlkQ8_0*);
 float q8_0_q8_0_dot_avx2(int64_t, const BlkQ8_0*, const BlkQ8_0*);
 float q4k_q8k_dot_avx2(int64_t, const BlkQ4K*, const BlkQ8K*);
+float q5k_q8k_dot_avx2(int64_t, const BlkQ5K*, const BlkQ8K*);
 float q6k_q8k_dot_avx2(int64_t, const BlkQ6K*, const BlkQ8K*);
 }  // namespace fq_oracle
 
@@ -48,6 +52,7 @@ bool fmt_of(int type, Fmt* f) {
     case GGML_Q4_0: *f = {32, 18, GGML_Q8_0}; return true;
     case GGML_Q8_0: *f = {32, 34, GGML_Q8_0}; return true;
     case GGML_Q4K: *f = {256, 144, GGML_Q8K}; return true;
+    case GGML_Q5K: *f = {256, 176, GGML_Q8K}; return true;
     case GGML_Q6K: *f = {256, 210, GGML_Q8K}; return true;
     case GGML_Q8K: *f = {256, 292, GGML_Q8K}; return true;
     default: return false;
@@ -59,6 +64,7 @@ void quantize_span(int type, const float* x, int64_t elems, void* out) {
     case GGML_Q4_0: q4_0_from_float(x, elems, (BlkQ4_0*)out); break;
     case GGML_Q8_0: q8_0_from_float(x, elems, (BlkQ8_0*)out); break;
     case GGML_Q4K: q4k_from_float(x, elems, (BlkQ4K*)out); break;
+    case GGML_Q5K: q5k_from_float(x, elems, (BlkQ5K*)out); break;
     case GGML_Q6K: q6k_from_float(x, elems, (BlkQ6K*)out); break;
     case GGML_Q8K: q8k_from_float(x, elems, (BlkQ8K*)out); break;
   }
@@ -69,6 +75,7 @@ void dequantize_span(int type, const void* in, int64_t elems, float* y) {
     case GGML_Q4_0: q4_0_to_float((const BlkQ4_0*)in, elems, y); break;
     case GGML_Q8_0: q8_0_to_float((const BlkQ8_0*)in, elems, y); break;
     case GGML_Q4K: q4k_to_float((const BlkQ4K*)in, elems, y); break;
+    case GGML_Q5K: q5k_to_float((const BlkQ5K*)in, elems, y); break;
     case GGML_Q6K: q6k_to_float((const BlkQ6K*)in, elems, y); break;
     case GGML_Q8K: q8k_to_float((const BlkQ8K*)in, elems, y); break;
   }
@@ -80,6 +87,7 @@ float dot(int type, int order, int64_t k, const void* w, const void* a) {
       case GGML_Q4_0: return q4_0_q8_0_dot_scalar(k, (const BlkQ4_0*)w, (const BlkQ8_0*)a);
       case GGML_Q8_0: return q8_0_q8_0_dot_scalar(k, (const BlkQ8_0*)w, (const BlkQ8_0*)a);
       case GGML_Q4K: return q4k_q8k_dot_scalar(k, (const BlkQ4K*)w, (const BlkQ8K*)a);
+      case GGML_Q5K: return q5k_q8k_dot_scalar(k, (const BlkQ5K*)w, (const BlkQ8K*)a);
       case GGML_Q6K: return q6k_q8k_dot_scalar(k, (const BlkQ6K*)w, (const BlkQ8K*)a);
     }
   } else {
@@ -87,6 +95,7 @@ float dot(int type, int order, int64_t k, const void* w, const void* a) {
       case GGML_Q4_0: return q4_0_q8_0_dot_avx2(k, (const BlkQ4_0*)w, (const BlkQ8_0*)a);
       case GGML_Q8_0: return q8_0_q8_0_dot_avx2(k, (const BlkQ8_0*)w, (const BlkQ8_0*)a);
       case GGML_Q4K: return q4k_q8k_dot_avx2(k, (const BlkQ4K*)w, (const BlkQ8K*)a);
+      case GGML_Q5K: return q5k_q8k_dot_avx2(k, (const BlkQ5K*)w, (const BlkQ8K*)a);
       case GGML_Q6K: return q6k_q8k_dot_avx2(k, (const BlkQ6K*)w, (const BlkQ8K*)a);
     }
   }
