@@ -13,11 +13,11 @@ import numpy as np
 import pytest
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "kquants_golden.npz")
-FORMATS = ("q4_0", "q8_0", "q4k", "q6k")
+FORMATS = ("q4_0", "q8_0", "q4k", "q5k", "q6k")
 
 
 def _t(O, name):
-    return {"q4_0": O.Q4_0, "q8_0": O.Q8_0, "q4k": O.Q4K, "q6k": O.Q6K}[name]
+    return {"q4_0": O.Q4_0, "q8_0": O.Q8_0, "q4k": O.Q4K, "q5k": O.Q5K, "q6k": O.Q6K}[name]
 
 
 def test_block_sizes(oracle):
@@ -95,7 +95,8 @@ def test_layout_matches_gguf_py(oracle, name):
     from gguf import quants
     O = oracle
     gt = {"q4_0": gguf.GGMLQuantizationType.Q4_0, "q8_0": gguf.GGMLQuantizationType.Q8_0,
-          "q4k": gguf.GGMLQuantizationType.Q4_K, "q6k": gguf.GGMLQuantizationType.Q6_K}[name]
+          "q4k": gguf.GGMLQuantizationType.Q4_K, "q5k": gguf.GGMLQuantizationType.Q5_K,
+          "q6k": gguf.GGMLQuantizationType.Q6_K}[name]
     w = np.random.Generator(np.random.PCG64(11)).standard_normal((16, 1024), dtype=np.float32) * np.float32(0.02)
     wb = O.quantize(_t(O, name), w)
     theirs = quants.dequantize(wb.reshape(16, -1), gt).reshape(-1)
@@ -107,7 +108,7 @@ def test_layout_matches_gguf_py(oracle, name):
     bb = O.block_bytes(_t(O, name))
     blocks = rb.reshape(-1, bb).copy()
     # keep the f16 scale fields finite
-    for off in ((0,) if name in ("q4_0", "q8_0") else (0, 2) if name == "q4k" else (208,)):
+    for off in ((0,) if name in ("q4_0", "q8_0") else (0, 2) if name in ("q4k", "q5k") else (208,)):
         blocks[:, off + 1] &= 0x3B
     rb = blocks.reshape(-1)
     assert np.array_equal(O.dequantize(_t(O, name), rb).view(np.uint32),
