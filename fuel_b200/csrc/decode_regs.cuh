@@ -152,6 +152,71 @@ struct Q4KRegs {
   }
 };
 
+// ---- Q5_K: Q4_K's unit (half a super-block, four sub-blocks) with the fifth bits merged in from qh: sub-block 4h+i
+// of half h takes bit 4h+i of every qh byte (fuel-quantized/src/k_quants.rs:1664-1680). The 5-bit values are built
+// once per unit as unsigned bytes, so the high nibbles are shifted down here (a 5-bit value times 16 overflows a byte).
+struct Q5KRegs : Q4KRegs {
+  struct Unit {
+    uint32_t off_hdr, off_qh, off_qs;
+    bool upper;
+  };
+  __device__ __forceinline__ static void make_unit(int u, bool valid, Unit& un) {
+    const int blk = valid ? (u >> 1) : 0, h = valid ? (u & 1) : 0;
+    un.off_hdr = blk * Q5KL::kBytes;
+    un.off_qh = blk * Q5KL::kBytes + Q5KL::kOffQh;
+    un.off_qs = blk * Q5KL::kBytes + Q5KL::kOffQs + 64 * h;
+    un.upper = h != 0;
+  }
+  template <int M>
+  __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
+    const uint4 hdr = lds128(rowbase + un.off_hdr);
+    uint32_t w[16], hq[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = lds128(rowbase + un.off_qs + 16 * i);
+      w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 v = lds128(rowbase + un.off_qh + 16 * i);
+      hq[4 * i] = v.x, hq[4 * i + 1] = v.y, hq[4 * i + 2] = v.z, hq[4 * i + 3] = v.w;
+    }
+    const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
+    const uint32_t sc_lo4 = hdr.y & 0x3f3f3f3fu, mn_lo4 = hdr.z & 0x3f3f3f3fu;
+    const uint32_t sc_hi4 = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+    const uint32_t mn_hi4 = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
+    const uint32_t sc4 = un.upper ? sc_hi4 : sc_lo4, mn4 = un.upper ? mn_hi4 : mn_lo4;
+    const int sc0 = sc4 & 0xff, sc1 = (sc4 >> 8) & 0xff, sc2 = (sc4 >> 16) & 0xff, sc3 = sc4 >> 24;
+    const uint32_t sh = un.upper ? 4u : 0u;
+    uint32_t v[32];  // 5-bit values in element order: sub-blocks 0..3 of the half, eight words each
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t hb = hq[j] >> sh;
+      v[j] = (w[j] & 0x0f0f0f0fu) | ((hb & 0x01010101u) << 4);
+      v[8 + j] = ((w[j] >> 4) & 0x0f0f0f0fu) | (((hb >> 1) & 0x01010101u) << 4);
+      v[16 + j] = (w[8 + j] & 0x0f0f0f0fu) | (((hb >> 2) & 0x01010101u) << 4);
+      v[24 + j] = ((w[8 + j] >> 4) & 0x0f0f0f0fu) | (((hb >> 3) & 0x01010101u) << 4);
+    }
+#pragma unroll
+    for (int i = 0; i < M; ++i) {
+      int dsum[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        int a = 0, b = 0;  // two independent chains per sub-block
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          a = dp4a_us(v[8 * s + j], ac[i].q[8 * s + j], a);
+          b = dp4a_us(v[8 * s + j + 1], ac[i].q[8 * s + j + 1], b);
+        }
+        dsum[s] = a + b;
+      }
+      const int si = sc0 * dsum[0] + sc1 * dsum[1] + sc2 * dsum[2] + sc3 * dsum[3];
+      const int mi = __dp2a_hi(ac[i].bs23, (int)mn4, __dp2a_lo(ac[i].bs01, (int)mn4, 0));
+      acc[i] += (d * ac[i].yd) * (float)si - (dmin * ac[i].yd) * (float)mi;
+    }
+  }
+};
+
 // ---- helpers for formats whose blocks are only 2-byte aligned in the stage --------------------
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;

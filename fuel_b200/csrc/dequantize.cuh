@@ -54,6 +54,44 @@ __global__ void __launch_bounds__(256) dequant_q4k_kernel(const uint8_t* __restr
   }
 }
 
+// Q5_K (fuel-quantized/src/k_quants.rs:1889-1923): Q4_K's layout and scale packing plus a fifth bit per element in qh —
+// bit 2g of qh[t] for element 64g + t, bit 2g+1 for element 64g + 32 + t. One thread per 16-byte nibble chunk.
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q5k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 3;
+  const int cc = (int)(u & 7), g = cc >> 1, h = cc & 1;
+  const uint8_t* b = w + blk * Q5KL::kBytes;
+  const uint4 hdr = *reinterpret_cast<const uint4*>(b);
+  const uint4 hv = *reinterpret_cast<const uint4*>(b + Q5KL::kOffQh + 16 * h);
+  const uint4 qv = *reinterpret_cast<const uint4*>(b + Q5KL::kOffQs + 16 * cc);
+  const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
+  uint32_t scw, mnw;
+  if (g < 2) {
+    scw = hdr.y & 0x3f3f3f3fu;
+    mnw = hdr.z & 0x3f3f3f3fu;
+  } else {
+    scw = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+    mnw = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
+  }
+  const int sh = (g & 1) * 16;
+  const float d1 = __fmul_rn(d, (float)((scw >> sh) & 0xff)), m1 = __fmul_rn(dmin, (float)((mnw >> sh) & 0xff));
+  const float d2 = __fmul_rn(d, (float)((scw >> (sh + 8)) & 0xff)), m2 = __fmul_rn(dmin, (float)((mnw >> (sh + 8)) & 0xff));
+  T* out = y + blk * 256 + 64 * g + 16 * h;
+  const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w}, hw[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const uint32_t byte = (qw[j] >> (8 * t)) & 0xff, hb = (hw[j] >> (8 * t)) & 0xff;
+      const uint32_t lo = (byte & 0xF) + (((hb >> (2 * g)) & 1u) << 4), hi = (byte >> 4) + (((hb >> (2 * g + 1)) & 1u) << 4);
+      out[4 * j + t] = cvt_out<T>(__fsub_rn(__fmul_rn(d1, (float)lo), m1));
+      out[32 + 4 * j + t] = cvt_out<T>(__fsub_rn(__fmul_rn(d2, (float)hi), m2));
+    }
+  }
+}
+
 // one thread per four consecutive l of one 128-half: 16 elements
 template <typename T>
 __global__ void __launch_bounds__(256) dequant_q6k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {

@@ -20,7 +20,7 @@ enum Status : int32_t {
 };
 
 // ---- GGUF type ids (fuel-ir/src/quantized.rs:35-75)
-enum GgmlType : int32_t { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ8_0 = 8, kQ4K = 12, kQ6K = 14, kQ8K = 15, kBF16 = 30 };
+enum GgmlType : int32_t { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ8_0 = 8, kQ4K = 12, kQ5K = 13, kQ6K = 14, kQ8K = 15, kBF16 = 30 };
 
 constexpr int QK_K = 256;
 constexpr int QK_S = 32;
@@ -30,13 +30,14 @@ constexpr int QK_S = 32;
 struct Q4_0L { static constexpr int kBytes = 18, kElems = 32, kOffD = 0, kOffQs = 2; };
 struct Q8_0L { static constexpr int kBytes = 34, kElems = 32, kOffD = 0, kOffQs = 2; };
 struct Q4KL { static constexpr int kBytes = 144, kElems = 256, kOffD = 0, kOffDmin = 2, kOffScales = 4, kOffQs = 16; };
+struct Q5KL { static constexpr int kBytes = 176, kElems = 256, kOffD = 0, kOffDmin = 2, kOffScales = 4, kOffQh = 16, kOffQs = 48; };
 struct Q6KL { static constexpr int kBytes = 210, kElems = 256, kOffQl = 0, kOffQh = 128, kOffScales = 192, kOffD = 208; };
 struct Q8KL { static constexpr int kBytes = 292, kElems = 256, kOffD = 0, kOffQs = 4, kOffBsums = 260; };
 
 __host__ __device__ inline int block_elems(int t) {
   switch (t) {
     case kQ4_0: case kQ8_0: return 32;
-    case kQ4K: case kQ6K: case kQ8K: return 256;
+    case kQ4K: case kQ5K: case kQ6K: case kQ8K: return 256;
     default: return 0;
   }
 }
@@ -45,6 +46,7 @@ __host__ __device__ inline int block_bytes(int t) {
     case kQ4_0: return 18;
     case kQ8_0: return 34;
     case kQ4K: return 144;
+    case kQ5K: return 176;
     case kQ6K: return 210;
     case kQ8K: return 292;
     default: return 0;
@@ -52,7 +54,7 @@ __host__ __device__ inline int block_bytes(int t) {
 }
 // The reference quantizes activations to the weight format's dot-product partner
 // (GgmlType::VecDotType, k_quants.rs:174,608,1372,1930): Q8_K for k-quants, Q8_0 otherwise.
-__host__ __device__ inline int act_type_for(int t) { return (t == kQ4K || t == kQ6K) ? kQ8K : kQ8_0; }
+__host__ __device__ inline int act_type_for(int t) { return (t == kQ4K || t == kQ5K || t == kQ6K) ? kQ8K : kQ8_0; }
 
 // ---- internal activation layout ("packed"): the same numbers as the reference's
 // Q8_K / Q8_0 blocks, split into planes so every plane is 16-byte aligned:

@@ -58,7 +58,7 @@ bool device_info(DeviceInfo** out) {
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-bool supported_weight(int t) { return t == kQ4_0 || t == kQ8_0 || t == kQ4K || t == kQ6K; }
+bool supported_weight(int t) { return t == kQ4_0 || t == kQ8_0 || t == kQ4K || t == kQ5K || t == kQ6K; }
 
 // launch with or without the programmatic-dependent-launch attribute
 template <typename... KArgs, typename... Args>
@@ -271,7 +271,8 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
                          cudaStream_t stream, const DecodeRegsPeer* peer = nullptr, const float* x_f32 = nullptr) {
   if (peer && m != 1) return kNotSupported;
   if (x_f32 && (peer || (type != kQ4K && type != kQ6K))) return kNotSupported;
-  if (m > 2 || (type != kQ4K && type != kQ6K && type != kQ8_0)) return kNotSupported;
+  if (peer && type == kQ5K) return kNotSupported;
+  if (m > 2 || (type != kQ4K && type != kQ5K && type != kQ6K && type != kQ8_0)) return kNotSupported;
   if (type == kQ8_0 && k % 128) return kNotSupported;  // its lane unit is four blocks
   DeviceInfo* di;
   if (!device_info(&di)) return kLaunchFailure;
@@ -339,6 +340,7 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   } while (0)
   switch (type) {
     case kQ4K: FQ_REGS_DISPATCH(Q4KRegs); break;
+    case kQ5K: FQ_REGS_DISPATCH(Q5KRegs); break;
     case kQ6K: FQ_REGS_DISPATCH(Q6KRegs); break;
     default: FQ_REGS_DISPATCH(Q8_0Regs); break;
   }
@@ -484,7 +486,7 @@ int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const vo
   const int abe = block_elems(act_type_for(type));
   // Two rows at a time through the register-resident kernel beats sixteen at a time through the generic
   // one when the matrix fits in L2 (every pass after the first streams from there).
-  const bool regs_ok = g_opt.decode_kernel != 1 && (type == kQ4K || type == kQ6K || (type == kQ8_0 && k % 128 == 0)) &&
+  const bool regs_ok = g_opt.decode_kernel != 1 && (type == kQ4K || type == kQ5K || type == kQ6K || (type == kQ8_0 && k % 128 == 0)) &&
                        (k / 128 + 7) / 8 <= 64 && m_total > 2;
   const int64_t step = regs_ok ? 2 : kDecodeMaxM;
   for (int64_t m0 = 0; m0 < m_total; m0 += step) {
@@ -1353,14 +1355,14 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
   if (out_type != kF32 && out_type != kF16 && out_type != kBF16) return kNotSupported;
   if (numel == 0) return kOk;
   if (!blocks || !y) return kInvalidProblem;
-  const size_t in_align = ggml_type == kQ4K ? 16 : (ggml_type == kQ8K ? 4 : 2);
+  const size_t in_align = (ggml_type == kQ4K || ggml_type == kQ5K) ? 16 : (ggml_type == kQ8K ? 4 : 2);
   if (!aligned(blocks, in_align) || !aligned(y, out_type == kF32 ? 4 : 2)) return kMisaligned;
   cudaStream_t stream = (cudaStream_t)stream_v;
   const int64_t nb = numel / be;
   const uint8_t* w = (const uint8_t*)blocks;
   int64_t units;
   switch (ggml_type) {
-    case kQ4K: units = nb * 8; break;
+    case kQ4K: case kQ5K: units = nb * 8; break;
     case kQ6K: units = nb * 16; break;
     case kQ8_0: units = nb * 4; break;
     case kQ4_0: units = nb * 4; break;
@@ -1379,6 +1381,7 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
   } while (0)
   switch (ggml_type) {
     case kQ4K: FQ_DEQ(dequant_q4k_kernel); break;
+    case kQ5K: FQ_DEQ(dequant_q5k_kernel); break;
     case kQ6K: FQ_DEQ(dequant_q6k_kernel); break;
     case kQ8_0: FQ_DEQ(dequant_q8_0_kernel); break;
     case kQ4_0: FQ_DEQ(dequant_q4_0_kernel); break;

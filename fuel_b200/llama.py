@@ -167,7 +167,7 @@ def _quantize(t: T, w: torch.Tensor) -> torch.Tensor:
 
 
 _SEED_SLOT = {"attn_q": 1, "attn_k": 2, "attn_v": 3, "attn_output": 4, "ffn_gate": 5, "ffn_up": 6, "ffn_down": 7}
-_K_QUANTS = (T.Q4K, T.Q6K)  # their activations are Q8_K blocks; Q8_0 / Q4_0 weights take Q8_0 activations
+_K_QUANTS = (T.Q4K, T.Q5K, T.Q6K)  # their activations are Q8_K blocks; Q8_0 / Q4_0 weights take Q8_0 activations
 
 
 class SyntheticWeights:
@@ -241,7 +241,7 @@ class GgufWeights:
     its rows from the mapping to its GPU —, norm gains and the embedding table become f32; `output.weight` falls
     back to `token_embd.weight` (tied embeddings) when absent."""
 
-    LINEAR_FORMATS = (T.Q4K, T.Q6K, T.Q8_0, T.Q4_0)
+    LINEAR_FORMATS = (T.Q4K, T.Q5K, T.Q6K, T.Q8_0, T.Q4_0)
 
     def __init__(self, path, device: torch.device):
         from .gguf import GgufFile
@@ -411,8 +411,9 @@ class QLlama:
         # The fused producers and the in-kernel exchange write Q8_K activation blocks, which is what k-quant weights
         # take; a model with Q8_0 / Q4_0 linears runs the plain step, which quantizes per consumer.
         self.fused = k_quants_only
-        if comm == "peer" and not k_quants_only:
-            raise NotImplementedError("comm='peer' needs k-quant (Q4_K / Q6_K) linears")
+        if comm == "peer" and not all(lin is None or lin.dtype in (T.Q4K, T.Q6K)
+                                      for lin in [self.head] + [l[nm] for l in self.layers for nm in ("qk", "v", "o", "gu", "down")]):
+            raise NotImplementedError("comm='peer' needs Q4_K / Q6_K linears")
         self.weight_bytes = (sum(l[k].blocks.numel() for l in self.layers for k in ("qk", "v", "o", "gu", "down") if l[k] is not None)
                              + self.head.blocks.numel())
 

@@ -38,7 +38,7 @@ def quantize_act(weight_dtype: GgmlDType, x: torch.Tensor) -> torch.Tensor:
     _need_cuda(x, "x")
     k = x.shape[-1]
     m = x.numel() // k
-    act = GgmlDType.Q8K if weight_dtype in (GgmlDType.Q4K, GgmlDType.Q6K) else GgmlDType.Q8_0
+    act = GgmlDType.Q8K if weight_dtype in (GgmlDType.Q4K, GgmlDType.Q5K, GgmlDType.Q6K) else GgmlDType.Q8_0
     if k % act.block_size():
         _lib.check(_lib.INVALID_PROBLEM, "quantize_act")
     out = torch.empty(storage_bytes(act, m * k), dtype=torch.uint8, device=x.device)

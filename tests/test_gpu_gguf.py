@@ -132,9 +132,9 @@ def test_loader_refusals(tmp_path):
     with G.GgufFile(path) as f:
         tensors = [(n, i.ggml_dtype, i.shape, f.tensor_bytes(n)) for n, i in f.tensor_infos.items() if n != "blk.1.attn_output.weight"]
         meta = [(k, f.metadata_types[k], v) for k, v in f.metadata.items()]
-    tensors.append(("blk.1.attn_output.weight", T.Q5K, (cfg.dim, cfg.dim), np.zeros(cfg.dim * cfg.dim // 256 * 176, np.uint8)))
+    tensors.append(("blk.1.attn_output.weight", T.Q3K, (cfg.dim, cfg.dim), np.zeros(cfg.dim * cfg.dim // 256 * 110, np.uint8)))
     G.write_gguf(bad, meta, tensors)
-    with pytest.raises(NotImplementedError, match="Q5K"):
+    with pytest.raises(NotImplementedError, match="Q3K"):
         QLlama.from_gguf(bad, dev)
     with pytest.raises(KeyError, match="missing tensor"):
         G.write_gguf(bad, meta, tensors[:-1])
