@@ -36,6 +36,7 @@ extern "C" {
 #define FUELQ_TYPE_Q4_0 2
 #define FUELQ_TYPE_Q8_0 8
 #define FUELQ_TYPE_Q4K 12
+#define FUELQ_TYPE_Q5K 13 /* mat-vec (every batch size through the exact-integer decode kernels) and dequantize only */
 #define FUELQ_TYPE_Q6K 14
 #define FUELQ_TYPE_Q8K 15
 #define FUELQ_TYPE_BF16 30
@@ -109,7 +110,8 @@ int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t 
  * fuel_quantized::matmul (k_quants.rs:2284-2331) and the CUDA entry it replaces,
  * baracuda_kernels_mmvq_<fmt>_batched_run (fuel-cuda-backend/src/quantized.rs:138-231).
  * Quantizes x, then runs the decode mat-vec (m_total <= DECODE_MAX_M) or the
- * tensor-core path. w must be 16-byte aligned, x and y 16-byte aligned. */
+ * tensor-core path. Weight formats: Q4_K, Q6_K, Q8_0 (both paths), Q4_0 and Q5_K (decode kernels at any m_total).
+ * w must be 16-byte aligned, x and y 16-byte aligned. */
 int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
                       float* y, void* workspace, size_t workspace_bytes, void* stream);
 
