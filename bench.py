@@ -210,8 +210,18 @@ def run_side_workload(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(0)
 
+    def random_blocks(t, n, k):
+        """Formats without a device quantizer: any bytes time the same; only the f16 scale fields are kept finite."""
+        b = torch.randint(0, 256, (n * k // t.block_size(), t.type_size()), generator=gen, device=dev, dtype=torch.uint8)
+        b[:, 1] &= 0x3B
+        b[:, 3] &= 0x3B
+        return b.reshape(-1)
+
     def matmul_case(t, name, n, k, m, copies, reps):
-        ws = [ops.quantize_weights(t, torch.randn(n, k, generator=gen, device=dev) * 0.02) for _ in range(copies)]
+        if t == T.Q5K:
+            ws = [random_blocks(t, n, k) for _ in range(copies)]
+        else:
+            ws = [ops.quantize_weights(t, torch.randn(n, k, generator=gen, device=dev) * 0.02) for _ in range(copies)]
         x = torch.randn(m, k, generator=gen, device=dev)
         y = torch.empty(m, n, device=dev)
         wsb = L.fuelq_qmatmul_workspace_bytes(int(t), m, n, k)
@@ -231,6 +241,10 @@ def run_side_workload(args):
             for n, k in ((11008, 4096), (4096, 11008)):
                 for m in (1, 2, 4, 8, 16, 32, 64, 128):
                     print(json.dumps(matmul_case(t, name, n, k, m, 12, 20)), flush=True)
+    elif args.workload == "q5k":
+        for n, k in ((11008, 4096), (4096, 11008)):
+            for m in (1, 2, 4, 8, 16):
+                print(json.dumps(matmul_case(T.Q5K, "Q5_K", n, k, m, 12, 20)), flush=True)
     elif args.workload == "prefill":
         line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10)
         line["operands"] = "tf32" if args.tf32 else "bf16"
@@ -427,7 +441,7 @@ def main():
     ap.add_argument("--tf32", action="store_true", help="--workload prefill: tensor-core path in tf32 instead of bf16")
     ap.add_argument("--decode-grid", type=int, default=0, help="thread blocks of the decode mat-vec (0: the library's choice, two per SM)")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-architecture decode that is reported beside the metric")
-    ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe", "q5k"],
                     help="decode: the headline line (default). sweep / prefill / moe: BASELINE configs 2 / 3 / 5 on one GPU, "
                          "one JSON line per case")
     args = ap.parse_args()
