@@ -114,15 +114,31 @@ struct Q4KRegs {
   }
   static constexpr bool kHasRaw = true;  // Q8_K activations: a stamped form exists
   __device__ __forceinline__ static int probe(const Act& ac) { return ac.q[0] ^ ac.q[31] ^ ac.bs23 ^ __float_as_int(ac.yd); }
-  template <int M>
-  __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
-    const uint4 hdr = lds128(rowbase + un.off_hdr);
+  // The shared-memory loads of a unit and the arithmetic on them are separate steps, so that a warp can have the
+  // loads of two weight rows in flight before it starts on the first (kSplit).
+  static constexpr bool kSplit = true;
+  struct Raw {
+    uint4 hdr;
     uint32_t w[16];
+  };
+  __device__ __forceinline__ static void load_raw(uint32_t rowbase, const Unit& un, Raw& raw) {
+    raw.hdr = lds128(rowbase + un.off_hdr);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint4 v = lds128(rowbase + un.off_qs + 16 * i);
-      w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+      raw.w[4 * i] = v.x, raw.w[4 * i + 1] = v.y, raw.w[4 * i + 2] = v.z, raw.w[4 * i + 3] = v.w;
     }
+  }
+  template <int M>
+  __device__ __forceinline__ static void compute(uint32_t rowbase, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
+    Raw raw;
+    load_raw(rowbase, un, raw);
+    math<M>(raw, un, ac, acc);
+  }
+  template <int M>
+  __device__ __forceinline__ static void math(const Raw& raw, const Unit& un, const Act (&ac)[M], float (&acc)[M]) {
+    const uint4 hdr = raw.hdr;
+    const uint32_t (&w)[16] = raw.w;
     const float d = h2f_bits(hdr.x & 0xffffu), dmin = h2f_bits(hdr.x >> 16);
     // four 6-bit scales and mins at once, one per byte (get_scale_min_k4, fuel-quantized/src/utils.rs:50-60)
     const uint32_t sc_lo4 = hdr.y & 0x3f3f3f3fu, mn_lo4 = hdr.z & 0x3f3f3f3fu;
@@ -156,6 +172,7 @@ struct Q4KRegs {
 // of half h takes bit 4h+i of every qh byte (fuel-quantized/src/k_quants.rs:1664-1680). The 5-bit values are built
 // once per unit as unsigned bytes, so the high nibbles are shifted down here (a 5-bit value times 16 overflows a byte).
 struct Q5KRegs : Q4KRegs {
+  static constexpr bool kSplit = false;
   struct Unit {
     uint32_t off_hdr, off_qh, off_qs;
     bool upper;
@@ -242,6 +259,7 @@ __device__ __forceinline__ void lds_words_2b(uint32_t addr, uint32_t (&w)[NW]) {
 // 32 * sum_g scale_g * (sum of the 16 activations of group g), from the activation block sums.
 struct Q6KRegs {
   static constexpr int kUnitsPerBlock = 2;
+  static constexpr bool kSplit = false;
   struct Unit {
     uint32_t off_blk;  // byte offset of the super-block from the row base
     uint32_t half;
@@ -323,6 +341,7 @@ struct Q6KRegs {
 
 // ---- Q8_0: unit = four 34-byte blocks (128 elements)
 struct Q8_0Regs {
+  static constexpr bool kSplit = false;
   static constexpr int kUnitsPerBlock = 0;  // units are counted per 128 elements, see the launcher
   struct Unit {
     uint32_t off;  // byte offset of the first of the four blocks
@@ -547,7 +566,43 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     const uint32_t skew = (uint32_t)(((int64_t)row0 * p.row_bytes) & 15);
     const uint32_t sbase = stages_u32 + (uint32_t)s * p.stage_stride + skew;
     const int buf = it & 1;
-    for (int r = rgroup; r < rows_here; r += n_rgroups) {
+    // lane 0 hands a finished row on: to y, to every rank's buffer, or to the k-slice partials
+    auto emit = [&](int r, const float (&acc)[M]) {
+#pragma unroll
+      for (int i = 0; i < M; ++i) {
+        if (ks == 1) {
+          if constexpr (kPeer) {
+            for (int q = 0; q < g->ctx.world; ++q) st_pair(g->dst[q] + row0 + r, __float_as_uint(acc[i]), push_stamp);
+          } else {
+            p.y[(size_t)i * p.n + row0 + r] = acc[i];
+          }
+        } else
+          hd->partial[buf][r][slice][i] = acc[i];
+      }
+    };
+    int r = rgroup;
+    if constexpr (Fmt::kSplit && NU == 1 && M == 1) {
+      // two rows at a time: both rows' shared-memory loads are issued before the arithmetic of the first, and the two
+      // shuffle reductions interleave (each row's own arithmetic and order are unchanged)
+      for (; r + n_rgroups < rows_here; r += 2 * n_rgroups) {
+        typename Fmt::Raw ra, rb;
+        Fmt::load_raw(sbase + (uint32_t)r * p.row_bytes, un[0], ra);
+        Fmt::load_raw(sbase + (uint32_t)(r + n_rgroups) * p.row_bytes, un[0], rb);
+        float acc0[M] = {0.f}, acc1[M] = {0.f};
+        Fmt::template math<M>(ra, un[0], ac[0], acc0);
+        Fmt::template math<M>(rb, un[0], ac[0], acc1);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          acc0[0] += __shfl_xor_sync(0xffffffffu, acc0[0], off);
+          acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], off);
+        }
+        if (lane == 0) {
+          emit(r, acc0);
+          emit(r + n_rgroups, acc1);
+        }
+      }
+    }
+    for (; r < rows_here; r += n_rgroups) {
       const uint32_t rowbase = sbase + (uint32_t)r * p.row_bytes;
       float acc[M];
 #pragma unroll
@@ -559,19 +614,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
       }
-      if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < M; ++i) {
-          if (ks == 1) {
-            if constexpr (kPeer) {
-              for (int q = 0; q < g->ctx.world; ++q) st_pair(g->dst[q] + row0 + r, __float_as_uint(acc[i]), push_stamp);
-            } else {
-              p.y[(size_t)i * p.n + row0 + r] = acc[i];
-            }
-          } else
-            hd->partial[buf][r][slice][i] = acc[i];
-        }
-      }
+      if (lane == 0) emit(r, acc);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->empty[s]);
