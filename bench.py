@@ -1,6 +1,6 @@
 """Benchmark of the quantized mat-vec hot path.
 
-Workload (BASELINE config 2, the Q4_K decode case): y[1, 11008] = x[1, 4096] . W^T with W a
+Workload (benchmark configuration 2, the Q4_K decode case): y[1, 11008] = x[1, 4096] . W^T with W a
 Q4_K matrix [11008 x 4096] (25 362 432 bytes of blocks). One step = one pass over LAYERS
 distinct weight matrices (each with its own activation row), i.e. LAYERS quantized
 mat-vec calls; cycling over 32 x 25.4 MB = 811 MB of weights keeps every read in HBM, not L2.
@@ -188,7 +188,7 @@ def _time_graph(torch, stream, fn, reps):
 
 
 def run_side_workload(args):
-    """BASELINE configs 2 (batch sweep), 3 (prefill GEMM) and 5 (MoE block) on one GPU: seeded synthetic tensors of the
+    """benchmark configurations 2 (batch sweep), 3 (prefill GEMM) and 5 (MoE block) on one GPU: seeded synthetic tensors of the
     stated shapes, distinct weight copies cycling through more than L2, CUDA-graph replay, one JSON line per case."""
     import torch
 
@@ -272,7 +272,7 @@ def run_side_workload(args):
 
 
 def run_prefill_sharded(args, rank, local_rank, world):
-    """BASELINE config 3 across GPUs: W [14336 x 4096] Q4_K split by rows (columns of Y) over the ranks, X [2048 x 4096]
+    """benchmark configuration 3 across GPUs: W [14336 x 4096] Q4_K split by rows (columns of Y) over the ranks, X [2048 x 4096]
     on every rank; each rank's kernel writes its columns into every rank's Y (the all-gather is the kernel's epilogue).
     CUDA events around the call on each rank, max over ranks."""
     import torch
@@ -326,7 +326,7 @@ def run_prefill_sharded(args, rank, local_rank, world):
 
 
 def run_moe_expert_parallel(args, rank, local_rank, world):
-    """BASELINE config 5 expert-parallel: 128 experts split over the ranks, 256 tokens split over the ranks, two NCCL
+    """benchmark configuration 5 expert-parallel: 128 experts split over the ranks, 256 tokens split over the ranks, two NCCL
     all-to-alls per block. Eager calls (the exchange sizes are read on the host), CUDA events, max over ranks."""
     import torch
     import torch.distributed as dist
@@ -442,7 +442,7 @@ def main():
     ap.add_argument("--decode-grid", type=int, default=0, help="thread blocks of the decode mat-vec (0: the library's choice, two per SM)")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-architecture decode that is reported beside the metric")
     ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe", "q5k"],
-                    help="decode: the headline line (default). sweep / prefill / moe: BASELINE configs 2 / 3 / 5 on one GPU, "
+                    help="decode: the headline line (default). sweep / prefill / moe: benchmark configurations 2 / 3 / 5 on one GPU, "
                          "one JSON line per case")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

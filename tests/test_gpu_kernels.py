@@ -1,7 +1,7 @@
 """GPU parity: every kernel is called through the C ABI and compared with the CPU
 restatement of the reference (oracle/) on the same seeded inputs.
 
-Bars (BASELINE north_star): activation blocks byte-identical; dequantization
+Bars (the stated parity bar): activation blocks byte-identical; dequantization
 bit-identical; mat-vec outputs within max relative error 1e-3 of the reference's CPU
 path. The integer dot products are exact on both sides, so the measured error is
 f32 summation order only and the tests hold a much tighter line:
@@ -191,7 +191,7 @@ def test_decode_batch_shapes_and_row_independence(ops, oracle):
                                       ("q6k", 11008, 4096), ("q6k", 4096, 11008),
                                       ("q8_0", 11008, 4096), ("q8_0", 4096, 11008)])
 def test_decode_benchmark_shapes(ops, oracle, name, n, k):
-    """BASELINE configs 1 and 2 at full size, M in {1, 16}."""
+    """benchmark configurations 1 and 2 at full size, M in {1, 16}."""
     wb = oracle.quantize(_ot(oracle, name), _weights(n, k))
     wd = _dev(wb)
     for m in (1, 16):

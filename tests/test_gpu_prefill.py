@@ -1,11 +1,11 @@
 """Tensor-core (tcgen05) path for large M, through the C ABI.
 
 Ground truth is the float oracle: exactly dequantized weights (the reference's to_float) times the
-f32 activations, accumulated in f64. The GPU path rounds BOTH operands to bf16 (BASELINE config 3
+f32 activations, accumulated in f64. The GPU path rounds BOTH operands to bf16 (benchmark configuration 3
 asks for exactly that), and that alone fixes the attainable error: a bf16 rounding is uniform in
 +-2^-9 relative, rms 1.13e-3 per operand, 1.6e-3 per product, and the products' errors add like a
 random walk just as the result does, so  ||y - r||_F / ||r||_F ~ 1.6e-3  whatever K is, and the
-largest of ~10^5 outputs sits near 2.5e-3 of max|r|. BASELINE's 1e-3 is therefore not reachable
+largest of ~10^5 outputs sits near 2.5e-3 of max|r|. The stated 1e-3 is therefore not reachable
 with bf16 operands by any kernel; the bars here are the ones bf16 allows, with margin:
     relative Frobenius error <= 2.5e-3,   max|y - r| / max|r| <= 5e-3,
 and the integer mat-vec path (tests/test_gpu_kernels.py) remains the one held to 1e-3 and tighter.
@@ -67,7 +67,7 @@ def test_prefill_other_formats_match_float_oracle(ops, oracle, name, m, n, k):
 
 
 def test_prefill_config3_shape_sampled_rows(ops, oracle):
-    """BASELINE config 3: W Q4_K [14336 x 4096], X [2048 x 4096]; the oracle is evaluated on sampled rows."""
+    """benchmark configuration 3: W Q4_K [14336 x 4096], X [2048 x 4096]; the oracle is evaluated on sampled rows."""
     from fuel_b200 import GgmlDType as T
     n, k, m = 14336, 4096, 2048
     g = torch.Generator(device="cuda")
