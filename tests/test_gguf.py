@@ -175,3 +175,47 @@ def test_truncated_and_out_of_range_files_are_errors_not_faults(tmp_path, tensor
             G.GgufFile(bad)
     with G.GgufFile(img) as f, pytest.raises(KeyError, match="missing tensor"):
         f.tensor_info("nope")
+
+
+def test_llama_loader_reads_architecture_and_checks_shapes(tmp_path):
+    """Host logic of QLlama.from_gguf that needs no GPU: the architecture from the llama.* keys and tensor shapes, the
+    element-count checks (fuel-core/src/lazy_quantized_llama.rs:271-277), tied embeddings, refused formats."""
+    torch = pytest.importorskip("torch")
+    import dataclasses
+    from fuel_b200.llama import GgufWeights, LlamaConfig
+    dim, ffn, vocab, layers = 256, 512, 64, 2
+
+    def blob(t, n, k):
+        return np.zeros(n * k // t.block_size() * t.type_size(), np.uint8)
+
+    tensors = [("token_embd.weight", T.Q6K, (vocab, dim), blob(T.Q6K, vocab, dim)),
+               ("output_norm.weight", T.F32, (dim,), np.zeros(dim * 4, np.uint8))]
+    for li in range(layers):
+        for nm, (n, k), t in (("attn_q", (dim, dim), T.Q4K), ("attn_k", (dim // 2, dim), T.Q4K), ("attn_v", (dim // 2, dim), T.Q6K),
+                              ("attn_output", (dim, dim), T.Q8_0), ("ffn_gate", (ffn, dim), T.Q5K), ("ffn_up", (ffn, dim), T.Q5K),
+                              ("ffn_down", (dim, ffn), T.Q3K if li == 1 else T.Q4_0)):
+            tensors.append((f"blk.{li}.{nm}.weight", t, (n, k), blob(t, n, k)))
+        for nm in ("attn_norm", "ffn_norm"):
+            tensors.append((f"blk.{li}.{nm}.weight", T.F32, (dim,), np.zeros(dim * 4, np.uint8)))
+    meta = [("general.architecture", G.STRING, "llama"), ("llama.block_count", G.U32, layers),
+            ("llama.attention.head_count", G.U32, 2), ("llama.attention.head_count_kv", G.U32, 1),
+            ("llama.attention.layer_norm_rms_epsilon", G.F32, 1e-6), ("llama.rope.freq_base", G.F32, 500000.0)]
+    path = str(tmp_path / "arch.gguf")
+    G.write_gguf(path, meta, tensors)
+    w = GgufWeights(path, torch.device("cpu"))
+    cfg = w.config(max_seq=128)
+    assert cfg == LlamaConfig(dim=dim, n_layers=layers, n_heads=2, n_kv_heads=1, head_dim=128, ffn_dim=ffn, vocab=vocab,
+                              norm_eps=float(np.float32(1e-6)), rope_theta=500000.0, max_seq=128)
+    w.check(cfg)
+    with pytest.raises(ValueError, match="elements, expected"):
+        w.check(dataclasses.replace(cfg, n_kv_heads=2))
+    assert w.dtype("attn_v", 0) == T.Q6K and w.dtype("ffn_gate", 1) == T.Q5K and w.dtype("ffn_down", 0) == T.Q4_0
+    assert w.dtype("output", -1) == T.Q6K            # no output.weight: the head is the embedding table
+    with pytest.raises(NotImplementedError, match="Q3K"):
+        w.dtype("ffn_down", 1)
+    with pytest.raises(KeyError, match="missing tensor"):
+        w.dtype("attn_q", 2)
+    w.file.close()
+    G.write_gguf(path, [("general.architecture", G.STRING, "qwen3moe")] + meta[1:], tensors)
+    with pytest.raises(ValueError, match="not the LLaMA layout"):
+        GgufWeights(path, torch.device("cpu")).config()
