@@ -164,3 +164,64 @@ def test_matmul_close_to_float_product(oracle, name):
     assert np.abs(y - yd).max() <= 2e-2 * np.abs(yd).max()
     # rows are independent of batch position
     assert np.array_equal(O.matmul(t, x[2:3], wb, 64), y[2:3])
+
+
+def _dequant_act_blocks(O, name, act, m, k):
+    """The activation blocks as real numbers, decoded here in numpy (not by the restatement):
+    Q8_K = {d: f32, qs: i8[256], bsums: i16[16]} -> d * qs (k_quants.rs:162-169);
+    Q8_0 = {d: f16, qs: i8[32]} -> d * qs (k_quants.rs:92-98). Also checks the Q8_K block sums."""
+    if name in ("q4k", "q5k", "q6k"):
+        b = act.reshape(m, k // 256, 292)
+        d = b[:, :, :4].copy().view(np.float32).astype(np.float64)
+        qs = b[:, :, 4:260].copy().view(np.int8).astype(np.float64)
+        bs = b[:, :, 260:].copy().view(np.int16).astype(np.int64)
+        assert np.array_equal(bs, qs.reshape(m, k // 256, 16, 16).sum(-1).astype(np.int64))
+        return (d * qs).reshape(m, k)
+    b = act.reshape(m, k // 32, 34)
+    d = b[:, :, :2].copy().view(np.float16).astype(np.float64)
+    qs = b[:, :, 2:].copy().view(np.int8).astype(np.float64)
+    return (d * qs).reshape(m, k)
+
+
+@pytest.mark.parametrize("source", ("quantizer", "random_bytes"))
+@pytest.mark.parametrize("name", FORMATS)
+def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
+    """Tight pin of the integer dot products (k_quants.rs:1388-1468 Q4_K, 1946-2003 Q6_K, 674-692 Q8_0,
+    252-269 Q4_0, 1770-1925 Q5_K and their AVX2 bodies): both operands of a vec_dot are exact integers
+    times scales, so the restated matmul must equal, up to f32 summation order, the f64 product of
+    gguf-py's dequantized weights with the activation blocks decoded in numpy. A wrong scale index,
+    nibble order or block-sum sign shows up at 1e-2 or worse; the bar is 2e-6 of the largest output."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    O = oracle
+    t = _t(O, name)
+    gt = {"q4_0": gguf.GGMLQuantizationType.Q4_0, "q8_0": gguf.GGMLQuantizationType.Q8_0,
+          "q4k": gguf.GGMLQuantizationType.Q4_K, "q5k": gguf.GGMLQuantizationType.Q5_K,
+          "q6k": gguf.GGMLQuantizationType.Q6_K}[name]
+    n, k, m = 48, 2048, 3
+    rng = np.random.Generator(np.random.PCG64(21))
+    if source == "quantizer":
+        wb = O.quantize(t, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    else:
+        bb = O.block_bytes(t)
+        blocks = rng.integers(0, 256, (n * k // O.block_elems(t), bb), dtype=np.uint8)
+        for off in ((0,) if name in ("q4_0", "q8_0") else (0, 2) if name in ("q4k", "q5k") else (208,)):
+            blocks[:, off + 1] &= 0x3B  # finite f16 scales
+        wb = blocks.reshape(-1)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    x[1, 256:512] = 0.0  # an all-zero activation block (d = 0 branch)
+    act = O.quantize_act(t, x)
+    xa = _dequant_act_blocks(O, name, act, m, k)
+    w = quants.dequantize(wb.reshape(n, -1), gt).astype(np.float64).reshape(n, k)
+    want = xa @ w.T
+    scale = np.abs(want).max()
+    for order in (O.SCALAR, O.AVX2):
+        got = O.matmul(t, x, wb, n, order).astype(np.float64)
+        assert np.abs(got - want).max() <= 2e-6 * scale, (name, source, order, np.abs(got - want).max() / scale)
+    # one vec_dot called directly on the blocks, not through the matmul driver
+    ab = act.reshape(m, -1)
+    rb = wb.reshape(n, -1)
+    for (i, j) in ((0, 0), (2, n - 1)):
+        for order in (O.SCALAR, O.AVX2):
+            v = O.vec_dot(t, order, k, np.ascontiguousarray(rb[j]), np.ascontiguousarray(ab[i]))
+            assert abs(v - want[i, j]) <= 2e-6 * scale
