@@ -15,9 +15,9 @@ from . import oracle as O
 
 
 def _rmsnorm(x, gain, eps):
-    ss = np.float32(0.0)
-    for v in x:                       # sequential f32 accumulation, as the reference loop
-        ss = np.float32(ss + v * v)
+    # sequential f32 accumulation, as the reference loop: ss = 0; for v in x: ss += v * v
+    # (np.add.accumulate adds left to right in the array's own type, one rounding per element)
+    ss = np.add.accumulate((x * x).astype(np.float32), dtype=np.float32)[-1]
     rinv = np.float32(1.0) / np.sqrt(np.float32(ss * (np.float32(1.0) / np.float32(x.size)) + np.float32(eps)))
     return (x * rinv * gain).astype(np.float32)
 
@@ -85,9 +85,9 @@ class OracleLlama:
         self.pos = 0
         tok = None
         for t in prompt:
-            tok, _ = self.step(int(t))
+            tok, self.last_logits = self.step(int(t))
         out = [tok]
         for _ in range(n_new - 1):
-            tok, _ = self.step(tok)
+            tok, self.last_logits = self.step(tok)
             out.append(tok)
         return out
