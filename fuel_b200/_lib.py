@@ -12,6 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfuelq.so")
 
 OK, MISALIGNED, INVALID_PROBLEM, NOT_SUPPORTED, WORKSPACE, LAUNCH_FAILURE = range(6)
+NUMERICS_INTEGER, NUMERICS_BF16, NUMERICS_TF32 = range(3)
 OPT_PDL, OPT_DECODE_MAX_M, OPT_DECODE_GRID, OPT_DECODE_KERNEL, OPT_L2_PREFETCH, OPT_FUSED_QUANT, OPT_PEER_WAIT_MS, OPT_PREFILL_TF32 = 1, 2, 3, 4, 5, 6, 7, 8
 
 _i32, _i64, _vp, _sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
@@ -64,6 +65,7 @@ PROTOTYPES = {
     "fuelq_quantize_act_packed": (_i32, [_i32, _i64, _i64, _vp, _vp, _sz, _vp]),
     "fuelq_qmatmul_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul_can_implement": (_i32, [_i32, _i64, _i64, _i64]),
+    "fuelq_qmatmul_numerics": (_i32, [_i32, _i64, _i64, _i64]),
     "fuelq_qmatmul": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "fuelq_qmatmul_sharded": (_i32, [_i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _i64, _vp, _sz, _vp]),
     "fuelq_qmatmul_host_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),

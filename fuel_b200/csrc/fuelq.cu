@@ -727,6 +727,13 @@ size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t
   return act_packed_bytes(ggml_type, m_total, k);
 }
 
+int32_t fuelq_qmatmul_numerics(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
+  const int32_t st = check_problem(ggml_type, m_total, n, k);
+  if (st != kOk) return -st;
+  if (!prefill_available(ggml_type, m_total, n, k)) return 0;
+  return g_opt.prefill_tf32 ? 2 : 1;
+}
+
 int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
   const int32_t st = check_problem(ggml_type, m_total, n, k);
   if (st != kOk) return st;

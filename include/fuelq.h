@@ -102,6 +102,20 @@ int32_t fuelq_quantize_act_packed(int32_t weight_type, int64_t m_total, int64_t 
  * follows passes (workspace, workspace_bytes) on every call, quantized.rs:193-195). */
 size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
 
+/* Which arithmetic fuelq_qmatmul uses for this problem under the current options. The reference's CPU path
+ * (fuel_quantized::matmul, k_quants.rs:2284-2331) has ONE arithmetic for every batch size: activations
+ * re-quantized to 8-bit blocks, exact integer dot products per sub-block, f32 block sums. This library keeps that
+ * arithmetic up to the crossover batch size and multiplies dequantized weights with bf16 (or tf32) activations
+ * on the tensor cores above it, so RESULTS CHANGE CLASS AT THE CROSSOVER: integer results sit within f32
+ * summation order (~1e-6) of the reference's, tensor-core results differ from them by the activation
+ * quantization the reference applies and this path does not (up to ~2e-2 of the largest output) and from the
+ * exact dequantized product by ~2.5e-3 (bf16) or ~1e-3 (tf32). Callers that need the reference's numbers at any
+ * batch size raise FUELQ_OPT_DECODE_MAX_M. Returns one of the values below, or a negative status (-FUELQ_...). */
+#define FUELQ_NUMERICS_INTEGER 0 /* the reference's arithmetic */
+#define FUELQ_NUMERICS_BF16 1
+#define FUELQ_NUMERICS_TF32 2
+int32_t fuelq_qmatmul_numerics(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
+
 /* 0 if fuelq_qmatmul handles (type, m_total, n, k), else the status it would return. */
 int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
 

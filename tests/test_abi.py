@@ -75,6 +75,12 @@ def test_argument_validation_needs_no_device(L):
     # workspace sizing is pure arithmetic
     assert f.fuelq_qmatmul_workspace_bytes(Q4K, 1, 4096, 4096) == f.fuelq_act_packed_bytes(Q4K, 1, 4096) >= 4096 + 64 + 512
     assert f.fuelq_qmatmul_workspace_bytes(Q4K, 1, 4096, 100) == 0
+    # which arithmetic a problem gets: the reference's integer path up to the crossover, tensor cores above
+    assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 4096) == L.NUMERICS_INTEGER
+    assert f.fuelq_qmatmul_numerics(Q8_0, 16, 4096, 4096) == L.NUMERICS_INTEGER
+    assert f.fuelq_qmatmul_numerics(Q8_0, 2048, 4096, 4096) == L.NUMERICS_BF16
+    assert f.fuelq_qmatmul_numerics(2, 2048, 4096, 4096) == L.NUMERICS_INTEGER   # Q4_0 has no tensor-core form
+    assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 100) == -L.INVALID_PROBLEM
 
 
 def test_options_round_trip(L):

@@ -23,7 +23,8 @@ def _split(blocks, E):
     return [b[e * per:(e + 1) * per] for e in range(E)]
 
 
-@pytest.mark.parametrize("E,H,F,K,N", [(8, 512, 256, 2, 33), (16, 256, 256, 4, 3), (128, 2048, 768, 8, 40), (4, 256, 512, 1, 70)])
+@pytest.mark.parametrize("E,H,F,K,N", [(8, 512, 256, 2, 33), (16, 256, 256, 4, 3), (128, 2048, 768, 8, 40), (4, 256, 512, 1, 70),
+                                       (128, 2048, 768, 8, 256)])   # the last: benchmark configuration 5 at its full 256 tokens
 def test_moe_block_matches_reference_order(E, H, F, K, N):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")

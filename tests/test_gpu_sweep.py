@@ -1,0 +1,66 @@
+"""Benchmark configuration 2 at full size: Q4_K, Q6_K and Q8_0 weights [4096 -> 11008] and [11008 -> 4096],
+every batch size M in {1, 2, 4, 8, 16, 32, 64, 128}, against the CPU path on the same seeded inputs.
+
+Which bar applies is asked of the library (fuelq_qmatmul_numerics):
+  * integer arithmetic (the reference's own): max|y - r| / max|r| <= 2e-6 and per-element 1e-3 against the
+    reference's matmul in scalar order (all rows up to M = 16, every row in AVX2 order plus a column sample in
+    scalar order above — the two orders differ by f32 summation order only);
+  * bf16 tensor-core path: against the exact dequantized f64 product, max-norm <= 5e-3 and Frobenius <= 2.5e-3
+    (what bf16 operands allow over k = 4096..11008), and against the reference's integer path <= 2e-2 (the gap is
+    the 8-bit activation quantization the reference applies and this path does not).
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+MS = (1, 2, 4, 8, 16, 32, 64, 128)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuel_b200 import ops as _ops
+    yield _ops
+    assert _ops.device_error() == 0, "a kernel recorded an expired bounded wait"
+
+
+@pytest.mark.parametrize("n,k", [(11008, 4096), (4096, 11008)])
+@pytest.mark.parametrize("name", ["q4k", "q6k", "q8_0"])
+def test_batch_sweep_full_size(ops, oracle, name, n, k):
+    from fuel_b200 import GgmlDType as T, _lib
+    from test_gpu_kernels import assert_matmul_close
+    O = oracle
+    t, ot = {"q4k": (T.Q4K, O.Q4K), "q6k": (T.Q6K, O.Q6K), "q8_0": (T.Q8_0, O.Q8_0)}[name]
+    w = np.random.Generator(np.random.PCG64(0)).standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    wb = O.quantize(ot, w)
+    del w
+    wd = torch.from_numpy(wb).cuda()
+    x_all = np.random.Generator(np.random.PCG64(1)).standard_normal((max(MS), k), dtype=np.float32)
+    cols = np.random.Generator(np.random.PCG64(2)).choice(n, 256, replace=False)
+    rb = wb.size // n
+    w_cols = np.ascontiguousarray(wb.reshape(n, rb)[cols]).reshape(-1)
+    exact = None
+    for m in MS:
+        x = x_all[:m]
+        got = ops.qmatmul(t, wd, n, torch.from_numpy(x).cuda()).cpu().numpy()
+        kind = _lib.lib.fuelq_qmatmul_numerics(int(t), m, n, k)
+        what = f"{name} {k}->{n} m={m}"
+        ref = O.matmul(ot, x, wb, n, O.SCALAR if m <= 16 else O.AVX2)
+        if kind == _lib.NUMERICS_INTEGER:
+            assert_matmul_close(got, ref, what)
+            if m > 16:
+                assert_matmul_close(got[:, cols], O.matmul(ot, x, w_cols, cols.size, O.SCALAR), what + " (scalar order, sampled)")
+        else:
+            assert kind == _lib.NUMERICS_BF16
+            if exact is None:
+                wf = O.dequantize(ot, wb).reshape(n, k).astype(np.float64)
+                exact = x_all.astype(np.float64) @ wf.T
+                del wf
+            r = exact[:m]
+            scale = np.abs(r).max()
+            assert np.abs(got - r).max() <= 5e-3 * scale, (what, np.abs(got - r).max() / scale)
+            assert np.linalg.norm(got - r) <= 2.5e-3 * np.linalg.norm(r), what
+            assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max(), what
