@@ -115,6 +115,8 @@ PROTOTYPES = {
     "fuelq_qtensor_dequantize": (_i32, [_vp, _vp, _i32]),
     "fuelq_qmatmul_forward": (_i32, [_vp, _vp, _i64, _vp]),
     "fuelq_qmatmul_forward_host": (_i32, [_vp, _vp, _i64, _vp]),
+    # include/fuelq_seam.h
+    "fuelq_seam_hello": (ctypes.c_int, [_vp]),
     # include/fuelq_gguf.h
     "fuelq_gguf_open": (_i32, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "fuelq_gguf_open_memory": (_i32, [_vp, _sz, ctypes.POINTER(_vp)]),

@@ -43,7 +43,16 @@ struct DecodeRegsParams {
   int u_begin[9];                 // unit range of k-slice s: [u_begin[s], u_begin[s+1])
   const float* x_f32;             // not null: f32 activations [m][k]; every CTA quantizes them itself (Q8_K) into
   int act_smem_off;               //   plain planes at this byte offset of its shared memory, instead of reading `act`
+#ifdef FQ_TRACE
+  unsigned long long* trace;
+#endif
 };
+#ifdef FQ_TRACE
+__device__ __forceinline__ unsigned long long fq_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define FQ_TR(i) do { if (p.trace) p.trace[(size_t)blockIdx.x * 8 + (i)] = fq_gtime(); } while (0)
+#else
+#define FQ_TR(i) do {} while (0)
+#endif
 
 // Extra arguments of the tensor-parallel form (kPeer): the output rows go, as stamped pairs of exchange
 // point ctx.push_seq, to dst[q] on every rank q (already offset to this rank's slice); with
@@ -430,6 +439,12 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
   }
   __syncthreads();
   pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    FQ_TR(0);
+#ifdef FQ_TRACE
+    if (p.trace) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); p.trace[(size_t)blockIdx.x * 8 + 7] = sm; }
+#endif
+  }
 
   if (warp == kDecodeConsumerWarps) {
     // ---------------- producer (weights do not depend on the previous kernel: no pdl_wait before loading)
@@ -480,8 +495,10 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
           mbar_arrive(&hd->full[s]);
         }
         issued = it + 1;
+        if (it == 0) FQ_TR(1);
         if (++s == S) s = 0, ph ^= 1u;
       }
+      FQ_TR(6);
       if (!ok) {  // consumers stopped releasing stages: let our own copies land before leaving
         for (int it = (issued > S ? issued - S : 0); it < issued; ++it)
           if (!mbar_wait_bounded(&hd->full[it % S], (it / S) & 1)) record_dev_error(kErrDrainWait);
@@ -500,6 +517,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
   typename Fmt::Act ac[NU][M];
   uint32_t push_stamp = 0;
   pdl_wait();  // activation planes are written by the preceding kernel
+  if (threadIdx.x == 0) FQ_TR(2);
   ActPlanes planes = p.act;
   if (Fmt::kHasRaw && p.x_f32) {
     // fused activation quantization: the consumer warps take the 256-element blocks of the M rows in turn
@@ -552,6 +570,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     asm volatile("" ::"r"(probe));
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->acts_ready);
+    if (threadIdx.x == 0) FQ_TR(3);
   }
   const uint32_t stages_u32 = smem_u32(stages);
   int s = 0;
@@ -561,6 +580,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       record_dev_error(kErrFullWait);
       return;
     }
+    if (it == 0 && threadIdx.x == 0) FQ_TR(4);
     const int row0 = r_begin + it * R;
     const int rows_here = (r_count - it * R < R) ? r_count - it * R : R;
     const uint32_t skew = (uint32_t)(((int64_t)row0 * p.row_bytes) & 15);
@@ -639,6 +659,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     }
     if (++s == S) s = 0, ph ^= 1u;
   }
+  if (threadIdx.x == 0) FQ_TR(5);
 }
 
 template <class Fmt, int M, int NU>

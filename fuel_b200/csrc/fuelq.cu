@@ -37,6 +37,10 @@ struct Options {
 };
 Options g_opt;
 
+#ifdef FQ_TRACE
+unsigned long long* g_trace = nullptr;
+int g_trace_slot = 0;
+#endif
 struct DeviceInfo {
   int sm_count = 0;
   int max_smem_optin = 0;
@@ -319,6 +323,9 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
   p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
   if (staged && !reserve) p.pre_stages = pl.num_stages - 1;
+#ifdef FQ_TRACE
+  p.trace = g_trace ? g_trace + (size_t)(g_trace_slot++) * 512 * 8 : nullptr;
+#endif
   cudaError_t e;
   if (peer) {
 #define FQ_REGS_PEER(FMT) \
@@ -640,6 +647,9 @@ const char* fuelq_status_string(int32_t status) {
   }
 }
 
+#ifdef FQ_TRACE
+void fuelq_trace_set(void* p) { g_trace = (unsigned long long*)p; g_trace_slot = 0; }
+#endif
 int32_t fuelq_block_elems(int32_t t) { return block_elems(t); }
 int32_t fuelq_block_bytes(int32_t t) { return block_bytes(t); }
 

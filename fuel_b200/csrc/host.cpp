@@ -4,9 +4,11 @@
 
 #include <cuda_runtime.h>
 
+#include <cstddef>
 #include <cstring>
 
 #include "../../include/fuelq.h"
+#include "../../include/fuelq_seam.h"
 
 namespace fuelq {
 
@@ -241,7 +243,23 @@ struct QTensorHandle {
 
 void fuelq::set_last_error(const std::string& message) { g_last_error = message; }
 
+static_assert(sizeof(fuelq_seam_hello_t) == 56 && offsetof(fuelq_seam_hello_t, envelope_version) == 4 &&
+                  offsetof(fuelq_seam_hello_t, profiles_len) == 8 && offsetof(fuelq_seam_hello_t, profiles) == 10 &&
+                  offsetof(fuelq_seam_hello_t, reserved1) == 42 && offsetof(fuelq_seam_hello_t, capabilities) == 48,
+              "the handshake envelope is a frozen 56-byte layout");
+
 extern "C" {
+
+int fuelq_seam_hello(fuelq_seam_hello_t* out) {
+  if (!out) return 2;
+  std::memset(out, 0, sizeof(*out));
+  out->magic = FUELQ_SEAM_MAGIC;
+  out->envelope_version = FUELQ_SEAM_ENVELOPE_VERSION;
+  out->profiles_len = 1;
+  out->profiles[0] = FUELQ_SEAM_PROFILE_V1;
+  out->capabilities = FUELQ_SEAM_CAP_FDX_V1 | FUELQ_SEAM_CAP_FDX_GGML;
+  return 0;
+}
 
 const char* fuelq_last_error(void) { return g_last_error.c_str(); }
 
