@@ -225,7 +225,12 @@ struct fuelq_gguf {
       if (!di) throw Error("unknown dtype for tensor " + std::to_string(dt), FUELQ_INVALID_PROBLEM);
       t.ggml_type = di->id;
       t.offset = c.get<uint64_t>();
-      t.nbytes = elems / di->block * di->bytes;  // lazy_quantized_llama.rs:255-257
+      // elems / block * bytes as in lazy_quantized_llama.rs:255-257, but a header is not trusted: a count that is
+      // not whole blocks, or a byte size that wraps or exceeds the file, is an error here, not a short tensor
+      if (elems % di->block) bad("tensor " + t.name + ": " + std::to_string(elems) + " elements is not a whole number of blocks");
+      const uint64_t nblocks = elems / di->block;
+      if (nblocks > (uint64_t)len / di->bytes) bad("tensor " + t.name + " is larger than the file");
+      t.nbytes = nblocks * di->bytes;
       const auto it = tensor_index.find(t.name);
       if (it != tensor_index.end()) {
         tensors[it->second] = std::move(t);

@@ -175,6 +175,14 @@ def test_truncated_and_out_of_range_files_are_errors_not_faults(tmp_path, tensor
             G.GgufFile(bad)
     with G.GgufFile(img) as f, pytest.raises(KeyError, match="missing tensor"):
         f.tensor_info("nope")
+    # sizes a hostile header can declare: an element count that is not whole blocks (would be truncated
+    # silently), and dims whose byte size wraps 64 bits to something small (2^62 F32 elements -> 2^64 bytes)
+    with pytest.raises(G.GgufError, match="whole number of blocks"):
+        G.GgufFile(_hdr(n_tensors=1) + _s(b"t") + struct.pack("<IQIQ", 1, 300, int(T.Q4K), 0))
+    with pytest.raises(G.GgufError, match="larger than the file"):
+        G.GgufFile(_hdr(n_tensors=1) + _s(b"t") + struct.pack("<IQQIQ", 2, 2 ** 31, 2 ** 31, 0, 0))
+    with pytest.raises(G.GgufError, match="larger than the file"):
+        G.GgufFile(_hdr(n_tensors=1) + _s(b"t") + struct.pack("<IQIQ", 1, 2 ** 62, 0, 0) + b"\0" * 64)
 
 
 def test_llama_loader_reads_architecture_and_checks_shapes(tmp_path):
