@@ -411,7 +411,7 @@ struct DecodeRegsSmemHeader {
   float partial[2][32][8][2];  // [buffer][row in stage][k-slice][m]
 };
 
-template <class Fmt, int M, int NU, bool kPeer>
+template <class Fmt, int M, int NU, bool kPeer, int NCW = kDecodeConsumerWarps, bool kPairRows = true>
 __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, const DecodeRegsPeer* g) {
   static_assert(!kPeer || M == 1, "the tensor-parallel form is a single-row mat-vec");
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -430,11 +430,11 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&hd->full[s], 1);
-      mbar_init(&hd->empty[s], kDecodeConsumerWarps);
+      mbar_init(&hd->empty[s], NCW);
     }
-    mbar_init(&hd->part_ready[0], kDecodeConsumerWarps);
-    mbar_init(&hd->part_ready[1], kDecodeConsumerWarps);
-    mbar_init(&hd->acts_ready, kDecodeConsumerWarps);
+    mbar_init(&hd->part_ready[0], NCW);
+    mbar_init(&hd->part_ready[1], NCW);
+    mbar_init(&hd->acts_ready, NCW);
     mbar_init_fence();
   }
   __syncthreads();
@@ -446,7 +446,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
 #endif
   }
 
-  if (warp == kDecodeConsumerWarps) {
+  if (warp == NCW) {
     // ---------------- producer (weights do not depend on the previous kernel: no pdl_wait before loading)
     if (lane == 0) {
       const int64_t tma_limit = p.total_bytes & ~(int64_t)15;
@@ -510,7 +510,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
 
   // ---------------- consumers
   const int ks = p.ks;
-  const int slice = warp & (ks - 1), rgroup = warp / ks, n_rgroups = kDecodeConsumerWarps / ks;  // ks is a power of two
+  const int slice = warp & (ks - 1), rgroup = warp / ks, n_rgroups = NCW / ks;  // ks is a power of two
   const int u_begin = p.u_begin[slice], u_end = p.u_begin[slice + 1];
 
   typename Fmt::Unit un[NU];
@@ -524,8 +524,8 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     // (the same routine as the stand-alone kernel, so the same bytes), while the producer streams weights
     planes = act_planes(smem_raw + p.act_smem_off, kQ4K, M, p.k);
     const int nblk = M * (p.k >> 8);
-    for (int b = warp; b < nblk; b += 2 * kDecodeConsumerWarps) {  // two blocks per round: both loads in flight at once
-      const int b2 = b + kDecodeConsumerWarps;
+    for (int b = warp; b < nblk; b += 2 * NCW) {  // two blocks per round: both loads in flight at once
+      const int b2 = b + NCW;
       const bool two = b2 < nblk;
       const float4* s0 = reinterpret_cast<const float4*>(p.x_f32 + (size_t)b * 256);
       const float4* s1 = reinterpret_cast<const float4*>(p.x_f32 + (size_t)(two ? b2 : b) * 256);
@@ -535,7 +535,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       q8k_block_from_regs(e0, lane, b, (int8_t*)planes.qs, (float*)planes.d, (int16_t*)planes.bsums);
       if (two) q8k_block_from_regs(e1, lane, b2, (int8_t*)planes.qs, (float*)planes.d, (int16_t*)planes.bsums);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * NCW) : "memory");
   }
   if constexpr (kPeer) {
     push_stamp = peer_stamp(g->ctx, g->ctx.push_seq);
@@ -544,11 +544,11 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       // into shared memory (each thread polling its own pairs), then load from there
       planes = act_planes(smem_raw + g->act_smem_off, kQ4K, 1, p.k);
       const uint32_t want = peer_stamp(g->ctx, g->ctx.wait_seq);
-      const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
+      const int t = threadIdx.x, nt = 32 * NCW;
       peer_copy_words(g->act_ll.qs, (uint32_t*)planes.qs, p.k >> 2, want, t, nt, g->ctx.wait_ns);
       peer_copy_words(g->act_ll.bs, (uint32_t*)planes.bsums, p.k >> 5, want, t, nt, g->ctx.wait_ns);
       peer_copy_words1(g->act_ll.d, (uint32_t*)planes.d, p.k >> 8, want, t, nt, g->ctx.wait_ns);
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * NCW) : "memory");
     }
   }
 #pragma unroll
@@ -601,7 +601,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       }
     };
     int r = rgroup;
-    if constexpr (Fmt::kSplit && NU == 1 && M == 1) {
+    if constexpr (kPairRows && Fmt::kSplit && NU == 1 && M == 1) {
       // two rows at a time: both rows' shared-memory loads are issued before the arithmetic of the first, and the two
       // shuffle reductions interleave (each row's own arithmetic and order are unchanged)
       for (; r + n_rgroups < rows_here; r += 2 * n_rgroups) {
@@ -646,7 +646,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
         record_dev_error(kErrFullWait);
         return;
       }
-      for (int t = threadIdx.x; t < rows_here * M; t += 32 * kDecodeConsumerWarps) {
+      for (int t = threadIdx.x; t < rows_here * M; t += 32 * NCW) {
         const int r = t / M, i = t - r * M;
         float sum = hd->partial[buf][r][0][i];
         for (int sg = 1; sg < ks; ++sg) sum += hd->partial[buf][r][sg][i];
@@ -665,6 +665,14 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
 template <class Fmt, int M, int NU>
 __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const DecodeRegsParams p) {
   decode_regs_body<Fmt, M, NU, false>(p, nullptr);
+}
+
+// Half-SM form: one thread block per SM with NCW consumer warps and at most half of the SM's registers and
+// shared memory, so that the thread blocks of the NEXT launch (programmatic dependent launch) are resident
+// beside it and fill their rings while this launch's consumers still compute.
+template <class Fmt, int NU, int NCW>
+__global__ void __launch_bounds__(32 * (NCW + 1), 2) decode_regs_co_kernel(const DecodeRegsParams p) {
+  decode_regs_body<Fmt, 1, NU, false, NCW, false>(p, nullptr);
 }
 
 // Tensor-parallel form: same arithmetic and order, output scattered to every rank.

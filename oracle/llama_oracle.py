@@ -85,9 +85,10 @@ class OracleLlama:
         self.pos = 0
         tok = None
         for t in prompt:
-            tok, self.last_logits = self.step(int(t))
-        out = [tok]
+            tok, logits = self.step(int(t))
+        out, self.logits_trace = [tok], [logits]     # logits_trace[i] are the logits that picked out[i]
         for _ in range(n_new - 1):
-            tok, self.last_logits = self.step(tok)
+            tok, logits = self.step(tok)
             out.append(tok)
+            self.logits_trace.append(logits)
         return out
