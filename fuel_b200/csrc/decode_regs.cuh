@@ -43,16 +43,7 @@ struct DecodeRegsParams {
   int u_begin[9];                 // unit range of k-slice s: [u_begin[s], u_begin[s+1])
   const float* x_f32;             // not null: f32 activations [m][k]; every CTA quantizes them itself (Q8_K) into
   int act_smem_off;               //   plain planes at this byte offset of its shared memory, instead of reading `act`
-#ifdef FQ_TRACE
-  unsigned long long* trace;
-#endif
 };
-#ifdef FQ_TRACE
-__device__ __forceinline__ unsigned long long fq_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define FQ_TR(i) do { if (p.trace) p.trace[(size_t)blockIdx.x * 8 + (i)] = fq_gtime(); } while (0)
-#else
-#define FQ_TR(i) do {} while (0)
-#endif
 
 // Extra arguments of the tensor-parallel form (kPeer): the output rows go, as stamped pairs of exchange
 // point ctx.push_seq, to dst[q] on every rank q (already offset to this rank's slice); with
@@ -411,7 +402,7 @@ struct DecodeRegsSmemHeader {
   float partial[2][32][8][2];  // [buffer][row in stage][k-slice][m]
 };
 
-template <class Fmt, int M, int NU, bool kPeer, int NCW = kDecodeConsumerWarps, bool kPairRows = true>
+template <class Fmt, int M, int NU, bool kPeer>
 __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, const DecodeRegsPeer* g) {
   static_assert(!kPeer || M == 1, "the tensor-parallel form is a single-row mat-vec");
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -430,23 +421,17 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&hd->full[s], 1);
-      mbar_init(&hd->empty[s], NCW);
+      mbar_init(&hd->empty[s], kDecodeConsumerWarps);
     }
-    mbar_init(&hd->part_ready[0], NCW);
-    mbar_init(&hd->part_ready[1], NCW);
-    mbar_init(&hd->acts_ready, NCW);
+    mbar_init(&hd->part_ready[0], kDecodeConsumerWarps);
+    mbar_init(&hd->part_ready[1], kDecodeConsumerWarps);
+    mbar_init(&hd->acts_ready, kDecodeConsumerWarps);
     mbar_init_fence();
   }
   __syncthreads();
   pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    FQ_TR(0);
-#ifdef FQ_TRACE
-    if (p.trace) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); p.trace[(size_t)blockIdx.x * 8 + 7] = sm; }
-#endif
-  }
 
-  if (warp == NCW) {
+  if (warp == kDecodeConsumerWarps) {
     // ---------------- producer (weights do not depend on the previous kernel: no pdl_wait before loading)
     if (lane == 0) {
       const int64_t tma_limit = p.total_bytes & ~(int64_t)15;
@@ -455,14 +440,14 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       int s = 0, js = 0;          // ring slot of stage `it`, and of stage `it - depth`
       uint32_t ph = 0, jph = 0;   // their phase parities
       for (int it = 0; it < n_iter; ++it) {
-        if (it >= S && !mbar_wait_bounded(&hd->empty[s], ph ^ 1u)) {
+        if (it >= S && !mbar_poll_bounded(&hd->empty[s], ph ^ 1u)) {
           record_dev_error(kErrEmptyWait);
           ok = false;
           break;
         }
         // Activation loads queue behind whatever bulk traffic this SM has outstanding; hold the
         // rest of the stream back until the consumers have theirs.
-        if (p.pre_stages && it == p.pre_stages && !mbar_wait_bounded(&hd->acts_ready, 0)) {
+        if (p.pre_stages && it == p.pre_stages && !mbar_poll_bounded(&hd->acts_ready, 0)) {
           record_dev_error(kErrFullWait);
           ok = false;
           break;
@@ -470,7 +455,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
         // Keep at most `depth` copies of this CTA in flight, so stages complete in order and the
         // consumers can start on the first while the rest stream in.
         if (it >= p.depth) {
-          if (!mbar_wait_bounded(&hd->full[js], jph)) {
+          if (!mbar_poll_bounded(&hd->full[js], jph)) {
             record_dev_error(kErrFullWait);
             ok = false;
             break;
@@ -495,13 +480,11 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
           mbar_arrive(&hd->full[s]);
         }
         issued = it + 1;
-        if (it == 0) FQ_TR(1);
         if (++s == S) s = 0, ph ^= 1u;
       }
-      FQ_TR(6);
       if (!ok) {  // consumers stopped releasing stages: let our own copies land before leaving
         for (int it = (issued > S ? issued - S : 0); it < issued; ++it)
-          if (!mbar_wait_bounded(&hd->full[it % S], (it / S) & 1)) record_dev_error(kErrDrainWait);
+          if (!mbar_poll_bounded(&hd->full[it % S], (it / S) & 1)) record_dev_error(kErrDrainWait);
       }
     }
     pdl_wait();
@@ -510,22 +493,21 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
 
   // ---------------- consumers
   const int ks = p.ks;
-  const int slice = warp & (ks - 1), rgroup = warp / ks, n_rgroups = NCW / ks;  // ks is a power of two
+  const int slice = warp & (ks - 1), rgroup = warp / ks, n_rgroups = kDecodeConsumerWarps / ks;  // ks is a power of two
   const int u_begin = p.u_begin[slice], u_end = p.u_begin[slice + 1];
 
   typename Fmt::Unit un[NU];
   typename Fmt::Act ac[NU][M];
   uint32_t push_stamp = 0;
   pdl_wait();  // activation planes are written by the preceding kernel
-  if (threadIdx.x == 0) FQ_TR(2);
   ActPlanes planes = p.act;
   if (Fmt::kHasRaw && p.x_f32) {
     // fused activation quantization: the consumer warps take the 256-element blocks of the M rows in turn
     // (the same routine as the stand-alone kernel, so the same bytes), while the producer streams weights
     planes = act_planes(smem_raw + p.act_smem_off, kQ4K, M, p.k);
     const int nblk = M * (p.k >> 8);
-    for (int b = warp; b < nblk; b += 2 * NCW) {  // two blocks per round: both loads in flight at once
-      const int b2 = b + NCW;
+    for (int b = warp; b < nblk; b += 2 * kDecodeConsumerWarps) {  // two blocks per round: both loads in flight at once
+      const int b2 = b + kDecodeConsumerWarps;
       const bool two = b2 < nblk;
       const float4* s0 = reinterpret_cast<const float4*>(p.x_f32 + (size_t)b * 256);
       const float4* s1 = reinterpret_cast<const float4*>(p.x_f32 + (size_t)(two ? b2 : b) * 256);
@@ -535,7 +517,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       q8k_block_from_regs(e0, lane, b, (int8_t*)planes.qs, (float*)planes.d, (int16_t*)planes.bsums);
       if (two) q8k_block_from_regs(e1, lane, b2, (int8_t*)planes.qs, (float*)planes.d, (int16_t*)planes.bsums);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * NCW) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
   }
   if constexpr (kPeer) {
     push_stamp = peer_stamp(g->ctx, g->ctx.push_seq);
@@ -544,11 +526,11 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       // into shared memory (each thread polling its own pairs), then load from there
       planes = act_planes(smem_raw + g->act_smem_off, kQ4K, 1, p.k);
       const uint32_t want = peer_stamp(g->ctx, g->ctx.wait_seq);
-      const int t = threadIdx.x, nt = 32 * NCW;
+      const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
       peer_copy_words(g->act_ll.qs, (uint32_t*)planes.qs, p.k >> 2, want, t, nt, g->ctx.wait_ns);
       peer_copy_words(g->act_ll.bs, (uint32_t*)planes.bsums, p.k >> 5, want, t, nt, g->ctx.wait_ns);
       peer_copy_words1(g->act_ll.d, (uint32_t*)planes.d, p.k >> 8, want, t, nt, g->ctx.wait_ns);
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * NCW) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
     }
   }
 #pragma unroll
@@ -570,7 +552,6 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     asm volatile("" ::"r"(probe));
     __syncwarp();
     if (lane == 0) mbar_arrive(&hd->acts_ready);
-    if (threadIdx.x == 0) FQ_TR(3);
   }
   const uint32_t stages_u32 = smem_u32(stages);
   int s = 0;
@@ -580,7 +561,6 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       record_dev_error(kErrFullWait);
       return;
     }
-    if (it == 0 && threadIdx.x == 0) FQ_TR(4);
     const int row0 = r_begin + it * R;
     const int rows_here = (r_count - it * R < R) ? r_count - it * R : R;
     const uint32_t skew = (uint32_t)(((int64_t)row0 * p.row_bytes) & 15);
@@ -601,7 +581,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       }
     };
     int r = rgroup;
-    if constexpr (kPairRows && Fmt::kSplit && NU == 1 && M == 1) {
+    if constexpr (Fmt::kSplit && NU == 1 && M == 1) {
       // two rows at a time: both rows' shared-memory loads are issued before the arithmetic of the first, and the two
       // shuffle reductions interleave (each row's own arithmetic and order are unchanged)
       for (; r + n_rgroups < rows_here; r += 2 * n_rgroups) {
@@ -646,7 +626,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
         record_dev_error(kErrFullWait);
         return;
       }
-      for (int t = threadIdx.x; t < rows_here * M; t += 32 * NCW) {
+      for (int t = threadIdx.x; t < rows_here * M; t += 32 * kDecodeConsumerWarps) {
         const int r = t / M, i = t - r * M;
         float sum = hd->partial[buf][r][0][i];
         for (int sg = 1; sg < ks; ++sg) sum += hd->partial[buf][r][sg][i];
@@ -659,20 +639,11 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     }
     if (++s == S) s = 0, ph ^= 1u;
   }
-  if (threadIdx.x == 0) FQ_TR(5);
 }
 
 template <class Fmt, int M, int NU>
 __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_kernel(const DecodeRegsParams p) {
   decode_regs_body<Fmt, M, NU, false>(p, nullptr);
-}
-
-// Half-SM form: one thread block per SM with NCW consumer warps and at most half of the SM's registers and
-// shared memory, so that the thread blocks of the NEXT launch (programmatic dependent launch) are resident
-// beside it and fill their rings while this launch's consumers still compute.
-template <class Fmt, int NU, int NCW>
-__global__ void __launch_bounds__(32 * (NCW + 1), 2) decode_regs_co_kernel(const DecodeRegsParams p) {
-  decode_regs_body<Fmt, 1, NU, false, NCW, false>(p, nullptr);
 }
 
 // Tensor-parallel form: same arithmetic and order, output scattered to every rank.

@@ -116,16 +116,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll may suspend up to the hint above, so
+// Bounded wait: gives up after `limit` polls (each poll may suspend up to the hint above and then backs off, so
 // the default bound is about two seconds) and reports failure instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 100000u) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 1500000u) {
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i >= 2) __nanosleep(i < 64 ? 40 : 400);  // back off: waiting warps should not eat issue slots
+  }
+  return false;
+}
+// The same for a producer thread that must react at once: a thread suspended on the long hint above was measured
+// to wake only when other warps of its thread block became active (microseconds after the phase completed, while
+// they sat in griddepcontrol.wait), which left rings half empty. Short suspends, polled; about two seconds in all.
+__device__ __forceinline__ bool mbar_try_wait_short(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(200u)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_poll_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < 8000000u; ++i) {
+    if (mbar_try_wait_short(bar, parity)) return true;
+    if (i > 64) __nanosleep(64);
   }
   return false;
 }

@@ -34,14 +34,9 @@ struct Options {
   int64_t peer_wait_ms = 4000; // deadline of the exchange polls in the tensor-parallel kernels
   int64_t prefill_tf32 = 0;   // tensor-core path in tf32 instead of bf16
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
-  int64_t dbg_co_warps = 0;
 };
 Options g_opt;
 
-#ifdef FQ_TRACE
-unsigned long long* g_trace = nullptr;
-int g_trace_slot = 0;
-#endif
 struct DeviceInfo {
   int sm_count = 0;
   int max_smem_optin = 0;
@@ -205,16 +200,14 @@ struct RegsPlan {
 };
 
 // `reserve`: bytes of shared memory kept free after the stage ring (the tensor-parallel form stages its activations there)
-int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl, size_t reserve = 0,
-                         int ncw = kDecodeConsumerWarps) {
+int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl, size_t reserve = 0) {
   int ks = 1;
   while (ks < 8 && (units_per_row + ks - 1) / ks > 32) ks *= 2;  // one unit per lane if eight slices allow it
   if ((units_per_row + ks - 1) / ks > 64) return kNotSupported;
   const int per_slice = (units_per_row + ks - 1) / ks;
   pl->ks = ks;
   pl->nu = per_slice > 32 ? 2 : 1;
-  if (ncw % ks) return kNotSupported;
-  const int n_rgroups = ncw / ks;
+  const int n_rgroups = kDecodeConsumerWarps / ks;
   const size_t header = align_up(sizeof(DecodeRegsSmemHeader), 128);
   const size_t per_cta_budget = ((size_t)di.max_smem_optin + 1024) / 2 - 1024 - 512;
   if (reserve + header + 4096 > per_cta_budget) return kNotSupported;
@@ -228,7 +221,7 @@ int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const Devi
   if (stages < 2) return kNotSupported;
   if (stages > kDecodeMaxStages) stages = kDecodeMaxStages;
   if (g_opt.dbg_max_stages && stages > g_opt.dbg_max_stages) stages = (int)g_opt.dbg_max_stages;
-  int grid = g_opt.decode_grid > 0 ? (int)g_opt.decode_grid : (ncw != kDecodeConsumerWarps ? 1 : 2) * di.sm_count;
+  int grid = g_opt.decode_grid > 0 ? (int)g_opt.decode_grid : 2 * di.sm_count;
   if (grid > n) grid = (int)n;
   pl->rows_per_stage = R;
   pl->num_stages = stages;
@@ -236,23 +229,6 @@ int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const Devi
   pl->grid = grid;
   pl->smem = header + (size_t)stages * stride + reserve;
   return kOk;
-}
-
-template <class Fmt, int NU, int NCW>
-cudaError_t launch_decode_regs_co(const DecodeRegsParams& p, const RegsPlan& pl, cudaStream_t stream) {
-  static bool attr_set[64] = {};
-  auto kern = decode_regs_co_kernel<Fmt, NU, NCW>;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!attr_set[dev]) {
-    DeviceInfo* di;
-    if (!device_info(&di)) return cudaErrorInvalidDevice;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
-  return launch(kern, dim3(pl.grid), dim3(32 * (NCW + 1)), pl.smem, stream, p);
 }
 
 template <class Fmt, int M, int NU>
@@ -308,28 +284,6 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   // once the consumers hold them in registers, so they borrow the LAST stage buffer of the ring: the
   // producer fills that stage only after the consumers report their activations loaded.
   const size_t staged = ((peer && peer->ctx.wait_seq >= 0) || x_f32) ? align_up(act_packed_bytes(kQ4K, m, k), 128) : 0;
-  const int co = (int)g_opt.dbg_co_warps;
-  if (co && m == 1 && !peer && !x_f32 && type == kQ4K) {
-    int32_t sc = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, 0, co);
-    if (sc == kOk && pl.nu == 1) {
-      p.w = (const uint8_t*)w; p.act = planes; p.x_f32 = nullptr; p.act_smem_off = 0; p.y = y; p.n = n; p.k = (int)k; p.m = 1;
-      p.total_bytes = n * (int64_t)p.row_bytes; p.rows_per_stage = pl.rows_per_stage; p.ks = pl.ks; p.num_stages = pl.num_stages;
-      p.stage_stride = pl.stage_stride; p.rows_q = (int)(n / pl.grid); p.rows_rem = (int)(n % pl.grid);
-      for (int sl = 0; sl <= 8; ++sl) p.u_begin[sl] = sl <= pl.ks ? (int)((int64_t)p.units_per_row * sl / pl.ks) : p.units_per_row;
-      p.depth = g_opt.dbg_depth ? (int)g_opt.dbg_depth : 3;
-      if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
-      p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
-#ifdef FQ_TRACE
-      p.trace = g_trace ? g_trace + (size_t)(g_trace_slot++) * 512 * 8 : nullptr;
-#endif
-      cudaError_t e = co == 12 ? launch_decode_regs_co<Q4KRegs, 1, 12>(p, pl, stream)
-                    : co == 10 ? launch_decode_regs_co<Q4KRegs, 1, 10>(p, pl, stream)
-                    : co == 14 ? launch_decode_regs_co<Q4KRegs, 1, 14>(p, pl, stream)
-                    : co == 16 ? launch_decode_regs_co<Q4KRegs, 1, 16>(p, pl, stream)
-                               : launch_decode_regs_co<Q4KRegs, 1, 8>(p, pl, stream);
-      return e == cudaSuccess ? kOk : kLaunchFailure;
-    }
-  }
   int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, 0);
   if (st != kOk) return st;
   size_t reserve = 0;
@@ -365,9 +319,6 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
   p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
   if (staged && !reserve) p.pre_stages = pl.num_stages - 1;
-#ifdef FQ_TRACE
-  p.trace = g_trace ? g_trace + (size_t)(g_trace_slot++) * 512 * 8 : nullptr;
-#endif
   cudaError_t e;
   if (peer) {
 #define FQ_REGS_PEER(FMT) \
@@ -689,9 +640,6 @@ const char* fuelq_status_string(int32_t status) {
   }
 }
 
-#ifdef FQ_TRACE
-void fuelq_trace_set(void* p) { g_trace = (unsigned long long*)p; g_trace_slot = 0; }
-#endif
 int32_t fuelq_block_elems(int32_t t) { return block_elems(t); }
 int32_t fuelq_block_bytes(int32_t t) { return block_bytes(t); }
 
@@ -717,7 +665,6 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 105: g_opt.dbg_depth = value; return kOk;
     case 106: g_opt.dbg_pre = value; return kOk;
     case 107: g_opt.moe_kernel = value; return kOk;
-    case 108: g_opt.dbg_co_warps = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;
