@@ -11,6 +11,7 @@
 #include "dequantize.cuh"
 #include "fq_common.cuh"
 #include "llama_glue.cuh"
+#include "mma_batch.cuh"
 #include "moe.cuh"
 #include "moe_mma.cuh"
 #include "prefill.cuh"
@@ -23,7 +24,7 @@ namespace {
 
 struct Options {
   int64_t pdl = 0;
-  int64_t decode_max_m = 16;  // larger m_total goes to the tensor-core path when the format has one
+  int64_t decode_max_m = 0;   // crossover to the bf16 tensor-core path; 0 = the library's choice (see prefill_available)
   int64_t decode_grid = 0;
   int64_t dbg_stage_kb = 0, dbg_max_stages = 0, dbg_smem_kb = 0;
   int64_t l2_prefetch = 0;
@@ -34,9 +35,14 @@ struct Options {
   int64_t peer_wait_ms = 4000; // deadline of the exchange polls in the tensor-parallel kernels
   int64_t prefill_tf32 = 0;   // tensor-core path in tf32 instead of bf16
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
+  int64_t dbg_mb_groups = 0, dbg_mb_min_m = 2;
 };
 Options g_opt;
 
+#ifdef FQ_TRACE
+unsigned long long* g_trace = nullptr;
+int g_trace_slot = 0;
+#endif
 struct DeviceInfo {
   int sm_count = 0;
   int max_smem_optin = 0;
@@ -471,11 +477,112 @@ int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const Ac
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
+// ---- small batches on the integer tensor cores (mma_batch.cuh): Q4_K, Q6_K, Q8_0; k a multiple of 256
+template <class F, int MT>
+cudaError_t launch_mma_batch(const MmaBatchParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  auto kern = mma_batch_kernel<F, MT>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    DeviceInfo* di;
+    if (!device_info(&di)) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  return launch(kern, grid, dim3(kMbThreads), smem, stream, p);
+}
+
+template <class F>
+int32_t mma_batch_fmt(int n_groups, int64_t n, int64_t k, const void* w, const ActPlanes& act, const int* offsets, int fixed_rows,
+                      const int* out_rows, float* y, bool wide, cudaStream_t stream) {
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  const int nblk = (int)(k / 256);
+  const int act_rows = wide ? 16 : 8;
+  const size_t header = align_up(sizeof(MmaBatchHeader), 128);
+  const size_t part_bytes = (size_t)kMbConsumerWarps * (wide ? 2 : 1) * 128 * sizeof(float);
+  const size_t total = (size_t)di->max_smem_optin;
+  // k in as few sweeps as shared memory allows: the activation rows of one sweep plus at least two (preferably four) stages of 16 weight rows
+  MmaBatchParams p;
+  const int R = 16;
+  int kc_blocks = 0, stages = 0;
+  size_t stride = 0, act_bytes = 0;
+  int wstride = 0;
+  // fewest sweeps over k first; within that, at least three stages (two at the very least)
+  for (int chunks = 1; chunks <= 64 && !kc_blocks; ++chunks) {
+    const int kc = (nblk + chunks - 1) / chunks;
+    const size_t ab = (size_t)mb_act_layout<F>(kc, act_rows).bytes;
+    // a staged weight row: the chunk widened to 16-byte boundaries, placed so that consecutive rows are 16 bytes apart modulo 128
+    const int ws = (int)align_up((size_t)kc * F::kBytes256 + 32, 128) + 16;
+    const size_t st = align_up((size_t)R * ws, 128);
+    const int min_stages = chunks < 4 ? 3 : 2;
+    if (header + ab + part_bytes + (size_t)min_stages * st <= total) {
+      kc_blocks = kc, act_bytes = ab, wstride = ws, stride = st;
+      stages = (int)((total - header - ab - part_bytes) / st);
+    }
+  }
+  if (!kc_blocks) return kNotSupported;
+  if (stages > kMbMaxStages) stages = kMbMaxStages;
+  if (g_opt.dbg_max_stages && stages > g_opt.dbg_max_stages) stages = (int)g_opt.dbg_max_stages;
+  p.w = (const uint8_t*)w;
+  p.act = act;
+  p.offsets = offsets;
+  p.fixed_rows = fixed_rows;
+  p.out_rows = out_rows;
+  p.y = y;
+  p.n = (int)n;
+  p.k = (int)k;
+  p.row_bytes = nblk * F::kBytes256;
+  p.group_bytes = n * (int64_t)p.row_bytes;
+  p.total_bytes = (int64_t)n_groups * p.group_bytes;
+  p.num_stages = stages;
+  p.n_wgroups = g_opt.dbg_mb_groups ? (int)g_opt.dbg_mb_groups : (stages >= 4 ? 4 : stages >= 2 ? 2 : 1);
+  p.stage_stride = (int)stride;
+  p.wstride = wstride;
+  p.act_off = (int)(header + (size_t)stages * stride);
+  p.part_off = (int)(p.act_off + act_bytes);
+  p.kc_blocks = kc_blocks;
+#ifdef FQ_TRACE
+  p.trace = g_trace ? g_trace + (size_t)(g_trace_slot++) * 512 * 64 : nullptr;
+#endif
+  const int n_tiles = (int)((n + 15) / 16);
+  int per_group = (di->sm_count + n_groups - 1) / n_groups;
+  if (n_groups > 1) per_group = (2 * di->sm_count + n_groups - 1) / n_groups;
+  if (g_opt.decode_grid > 0) per_group = (int)g_opt.decode_grid;
+  const int max_per = n_tiles;
+  if (per_group > max_per) per_group = max_per;
+  if (per_group < 1) per_group = 1;
+  const size_t smem = header + (size_t)stages * stride + act_bytes + part_bytes;
+  const dim3 grid((unsigned)per_group, (unsigned)n_groups);
+  const cudaError_t e = wide ? launch_mma_batch<F, 2>(p, grid, smem, stream) : launch_mma_batch<F, 1>(p, grid, smem, stream);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// kNotSupported when the format or shape has no plan here (the caller falls back)
+int32_t mma_batch_impl(int type, int n_groups, int64_t n, int64_t k, const void* w, const ActPlanes& act, const int* offsets,
+                       int fixed_rows, const int* out_rows, float* y, bool wide, cudaStream_t stream) {
+  if (k % 256 || k > (1 << 20) || n > (1 << 24) || n_groups > 65535) return kNotSupported;
+  switch (type) {
+    case kQ4K: return mma_batch_fmt<MbQ4K>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
+    case kQ6K: return mma_batch_fmt<MbQ6K>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
+    case kQ8_0: return mma_batch_fmt<MbQ8_0>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
+    default: return kNotSupported;
+  }
+}
+
 // Any m_total through the decode kernels: activation rows are taken kDecodeMaxM at a time, each
 // chunk streaming the weights once. Exactly the integer arithmetic of the small-M path.
 int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
                        cudaStream_t stream) {
   const ActPlanes all = act_planes(packed_act, type, m_total, k);
+  if (m_total >= g_opt.dbg_mb_min_m && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0) {
+    // a few rows: one pass over the weights on the integer tensor cores (up to 16 rows per pass)
+    const int32_t st = mma_batch_impl(type, 1, n, k, w, all, nullptr, (int)m_total, nullptr, y, m_total > 8, stream);
+    if (st != kNotSupported) return st;
+  }
   // (when k is so large that the tensor-core kernel sweeps it in chunks, two-row dp4a passes stay ahead up to 5 rows)
   const bool mma_chunked = k / 256 > 16;
   if (type == kQ4K && m_total > (mma_chunked ? 5 : 2) && g_opt.decode_kernel == 0 && g_opt.moe_kernel != 1 && n <= (1 << 24)) {
@@ -519,8 +626,12 @@ bool mma_plan_fits(int64_t k) {
 bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   (void)n;
   int64_t max_m = g_opt.decode_max_m;
-  // Q4_K rows go through the integer tensor-core kernel 16 at a time; two such passes still beat the bf16 GEMM
-  if (type == kQ4K && max_m == 16 && g_opt.decode_kernel == 0 && g_opt.moe_kernel != 1 && mma_plan_fits(k)) max_m = 32;
+  if (max_m == 0) {
+    // The library's choice: 16 rows; 64 where the integer tensor-core kernel applies (16 rows per pass over the weights,
+    // the later passes from L2) - still faster there than the bf16 GEMM, and the reference's own arithmetic.
+    max_m = 16;
+    if ((type == kQ4K || type == kQ6K || type == kQ8_0) && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0 && k % 256 == 0) max_m = 64;
+  }
   return (type == kQ4K || type == kQ6K || type == kQ8_0) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }
 size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * (g_opt.prefill_tf32 ? 4 : 2), 256); }
@@ -640,6 +751,9 @@ const char* fuelq_status_string(int32_t status) {
   }
 }
 
+#ifdef FQ_TRACE
+void fuelq_trace_set(void* p) { g_trace = (unsigned long long*)p; g_trace_slot = 0; }
+#endif
 int32_t fuelq_block_elems(int32_t t) { return block_elems(t); }
 int32_t fuelq_block_bytes(int32_t t) { return block_bytes(t); }
 
@@ -665,6 +779,8 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 105: g_opt.dbg_depth = value; return kOk;
     case 106: g_opt.dbg_pre = value; return kOk;
     case 107: g_opt.moe_kernel = value; return kOk;
+    case 111: g_opt.dbg_mb_groups = value; return kOk;
+    case 112: g_opt.dbg_mb_min_m = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;
@@ -1118,7 +1234,12 @@ int32_t fuelq_moe_qmatmul(int32_t ggml_type, int32_t n_experts, int64_t n, int64
   if (n_rows == 0) return kOk;
   if (!w || !packed_act || !expert_offsets || !y) return kInvalidProblem;
   if (!aligned(w, 16) || !aligned(packed_act, 16)) return kMisaligned;
-  if (ggml_type == kQ4K && g_opt.moe_kernel != 1) {
+  if ((g_opt.moe_kernel == 0 && ggml_type != kQ4K) || g_opt.moe_kernel == 3) {
+    const int32_t sm = mma_batch_impl(ggml_type, n_experts, n, k, w, act_planes(const_cast<void*>(packed_act), ggml_type, n_rows, k),
+                                      (const int*)expert_offsets, 0, (const int*)out_rows, y, true, (cudaStream_t)stream);
+    if (sm != kNotSupported) return sm;
+  }
+  if (ggml_type == kQ4K && (g_opt.moe_kernel == 0 || g_opt.moe_kernel == 2)) {
     const int32_t sm = moe_mma_impl(n_experts, n, k, w, act_planes(const_cast<void*>(packed_act), ggml_type, n_rows, k),
                                     (const int*)expert_offsets, 0, (const int*)out_rows, y, (cudaStream_t)stream);
     if (sm != kNotSupported) return sm;

@@ -21,6 +21,7 @@
 #pragma once
 #include "decode_regs.cuh"
 #include "fq_common.cuh"
+#include "mma_batch.cuh"
 #include "moe.cuh"
 
 namespace fq {
@@ -47,14 +48,6 @@ struct MmaSmemHeader {
   uint64_t full[kDecodeMaxStages];
   uint64_t empty[kDecodeMaxStages];
 };
-
-// four 8x8 (16-byte-row) matrices: exactly the A fragment of m16n8k32 for 8-bit operands when the lanes
-// address rows 0-7 / 8-15 at byte columns 0-15 / 16-31 of a 16 x 32-byte tile
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
 
 __device__ __forceinline__ void mma_s8_16832(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(

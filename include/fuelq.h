@@ -52,10 +52,11 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
 /* Options. key: */
 #define FUELQ_OPT_PDL 1          /* 1: launch kernels with programmatic dependent launch so a kernel's weight
                                     prefetch overlaps its predecessor's tail (default 0) */
-#define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the integer kernels (default 16); above it the bf16
-                                    tensor-core GEMM runs for formats that have one. While the value is the default,
-                                    Q4_K with k small enough for the integer tensor-core kernel (k <= 4096 on B200)
-                                    stays on the exact integer path up to m_total = 32, where it is still faster */
+#define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the integer kernels; above it the bf16 tensor-core GEMM
+                                    runs for formats that have one. 0 (default) = the library's choice: 16, and 64 for
+                                    Q4_K / Q6_K / Q8_0 with k a multiple of 256 (the integer tensor-core kernel, 16 rows
+                                    per pass over the weights, is still the faster of the two there). Any positive
+                                    value is taken as given */
 #define FUELQ_OPT_DECODE_GRID 3  /* CTAs for the decode kernel; 0 = two per SM (default) */
 #define FUELQ_OPT_DECODE_KERNEL 4 /* 0 = pick per problem (default); 1 = generic decode kernel (activations read
                                     through L1, any M <= 16); 2 = register-resident kernel only (M <= 2) */

@@ -78,6 +78,8 @@ def test_argument_validation_needs_no_device(L):
     # which arithmetic a problem gets: the reference's integer path up to the crossover, tensor cores above
     assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 4096) == L.NUMERICS_INTEGER
     assert f.fuelq_qmatmul_numerics(Q8_0, 16, 4096, 4096) == L.NUMERICS_INTEGER
+    assert f.fuelq_qmatmul_numerics(Q8_0, 64, 4096, 4096) == L.NUMERICS_INTEGER     # the library's choice: up to 64 rows
+    assert f.fuelq_qmatmul_numerics(Q8_0, 65, 4096, 4096) == L.NUMERICS_BF16
     assert f.fuelq_qmatmul_numerics(Q8_0, 2048, 4096, 4096) == L.NUMERICS_BF16
     assert f.fuelq_qmatmul_numerics(2, 2048, 4096, 4096) == L.NUMERICS_INTEGER   # Q4_0 has no tensor-core form
     assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 100) == -L.INVALID_PROBLEM

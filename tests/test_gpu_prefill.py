@@ -23,8 +23,12 @@ torch = pytest.importorskip("torch")
 def ops():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
-    from fuel_b200 import ops as _ops
+    from fuel_b200 import _lib, ops as _ops
+    # these tests are about the tensor-core path: put the crossover at 16 rows explicitly (the library's own choice keeps
+    # batches of up to 64 rows on the integer kernels)
+    _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 16), "set_option")
     yield _ops
+    _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 0)
     assert _ops.device_error() == 0, "a kernel recorded an expired bounded wait"
 
 
