@@ -10,8 +10,11 @@ Weights are N(0, 0.02) from a seeded generator, quantized by the library's devic
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Metric: achieved HBM GB/s = algorithmic bytes (W blocks + 4*M*k + 4*M*n per mat-vec) / time.
-N > 1 (torchrun): every rank runs the same pass over its own matrices — the path has no
-exchange step, so scaling is weak and there is no collective.
+N > 1 (torchrun): the SAME 32 matrices, each split by output rows over the N GPUs (strong scaling): a rank
+streams its rows, its kernel stores its slice of y into every GPU's copy over NVLink, and a consumer kernel on every
+GPU waits for the whole vector (takes its argmax) before the next mat-vec — the exchange is inside the kernels, no
+library collective. Beside the headline the N-GPU line carries the 7B-architecture decode (tensor-parallel), the
+column-sharded prefill GEMM and the expert-parallel MoE block at the same N.
 --impl reference: the reference's CPU path (its arithmetic restated under oracle/, AVX2 order,
 all host threads) on the same step.
 """
@@ -40,14 +43,15 @@ REF_MIN_SECONDS = 5.0
 
 
 def bench_scaling(world: int) -> str:
-    return "weak"
+    return "strong"   # the same 32 matrices at every GPU count
 
 
 def bench_config(world: int, pdl: bool) -> dict:
     """The workload description both arms print (the driver compares the two dicts)."""
     return {"workload": WORKLOAD, "m": M_ROWS, "k": K_IN, "n": N_OUT, "format": "Q4_K", "layers": LAYERS,
             "l2": f"inputs larger than L2: {LAYERS * W_BYTES / 1e6:.0f} MB of distinct weights per step", "cuda_graph": True,
-            "pdl": pdl, "parallelism": f"independent matrices per rank x{world}"}
+            "pdl": pdl, "parallelism": "one GPU" if world == 1 else
+            f"each matrix split by output rows over {world} GPUs; every GPU receives the whole y inside the kernels"}
 
 
 def _peaks():
@@ -114,13 +118,14 @@ def _dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
-def make_weights(torch, ops, T, device, rank):
+def make_weights(torch, ops, T, device, lo, hi):
+    """Rows [lo, hi) of the LAYERS seeded matrices (the same matrices at every GPU count)."""
     ws = []
     g = torch.Generator(device=device)
     for i in range(LAYERS):
-        g.manual_seed(1000 * rank + i)
+        g.manual_seed(i)
         w = torch.randn(N_OUT, K_IN, generator=g, device=device, dtype=torch.float32) * 0.02
-        ws.append(ops.quantize_weights(T.Q4K, w))
+        ws.append(ops.quantize_weights(T.Q4K, w[lo:hi].contiguous()))
         del w
     return ws
 
@@ -296,7 +301,7 @@ def run_side_workload(args):
     assert ops.device_error() == 0, "a kernel recorded an expired bounded wait"
 
 
-def run_prefill_sharded(args, rank, local_rank, world):
+def run_prefill_sharded(args, rank, local_rank, world, own_group=True):
     """benchmark configuration 3 across GPUs: W [14336 x 4096] Q4_K split by rows (columns of Y) over the ranks, X [2048 x 4096]
     on every rank; each rank's kernel writes its columns into every rank's Y (the all-gather is the kernel's epilogue).
     CUDA events around the call on each rank, max over ranks."""
@@ -308,7 +313,9 @@ def run_prefill_sharded(args, rank, local_rank, world):
     from fuel_b200.sharded import ShardedQMatMul
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=dev)
+    if own_group:
+        dist.init_process_group("nccl", device_id=dev)
+    result = None
     _lib.lib.fuelq_set_option(_lib.OPT_PREFILL_TF32, 1 if args.tf32 else 0)
     n, k, m, copies = 14336, 4096, 2048, 4
     lo, hi = shard_range(n, world, rank)
@@ -338,19 +345,23 @@ def run_prefill_sharded(args, rank, local_rank, world):
         assert ops.device_error() == 0
         if rank == 0:
             peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
-            print(json.dumps({"workload": f"Q4_K_k{k}_n{n}_m{m}_column_sharded", "n_gpus": world, "us": us,
-                              "TFLOP/s": 2 * m * n * k / us / 1e6, "operands": "tf32" if args.tf32 else "bf16",
-                              "all_gather": "inside the kernel epilogue (stores into every GPU's Y over NVLink)",
-                              "y_bytes_stored_per_gpu": 4 * m * (hi - lo) * world,
-                              "bf16_tflops_measured_per_gpu": peak.get("bf16_tflops")}), flush=True)
+            result = {"workload": f"Q4_K_k{k}_n{n}_m{m}_column_sharded", "n_gpus": world, "us": us,
+                      "TFLOP/s": 2 * m * n * k / us / 1e6, "operands": "tf32" if args.tf32 else "bf16",
+                      "all_gather": "inside the kernel epilogue (stores into every GPU's Y over NVLink)",
+                      "y_bytes_stored_per_gpu": 4 * m * (hi - lo) * world,
+                      "bf16_tflops_measured_per_gpu": peak.get("bf16_tflops")}
+            if own_group:
+                print(json.dumps(result), flush=True)
     finally:
         for sh in shards:
             sh.close()
     dist.barrier()
-    dist.destroy_process_group()
+    if own_group:
+        dist.destroy_process_group()
+    return result
 
 
-def run_moe_expert_parallel(args, rank, local_rank, world):
+def run_moe_expert_parallel(args, rank, local_rank, world, own_group=True):
     """benchmark configuration 5 expert-parallel: 128 experts split over the ranks, 256 tokens split over the ranks, two NCCL
     all-to-alls per block. Eager calls (the exchange sizes are read on the host), CUDA events, max over ranks."""
     import torch
@@ -360,7 +371,9 @@ def run_moe_expert_parallel(args, rank, local_rank, world):
     from fuel_b200.moe import QMoeExpertParallel
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=dev)
+    if own_group:
+        dist.init_process_group("nccl", device_id=dev)
+    result = None
     _lib.lib.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0)
     E, H, F, K, N, copies = 128, 2048, 768, 8, 256, 4
     El, nl = E // world, N // world
@@ -392,19 +405,68 @@ def run_moe_expert_parallel(args, rank, local_rank, world):
     assert ops.device_error() == 0
     if rank == 0:
         wbytes = E * 3 * F * H // 256 * 144
-        print(json.dumps({"workload": f"moe_block_e{E}_h{H}_f{F}_top{K}_tokens{N}_q4k_expert_parallel", "n_gpus": world, "us": us,
-                          "tokens_per_s": N / us * 1e6, "GB/s": wbytes / us / 1e3, "weight_bytes_per_gpu": wbytes // world,
-                          "exchange": "two NCCL all-to-alls per block + one host read of the routing counts",
-                          "cuda_graph": False}), flush=True)
+        result = {"workload": f"moe_block_e{E}_h{H}_f{F}_top{K}_tokens{N}_q4k_expert_parallel", "n_gpus": world, "us": us,
+                  "tokens_per_s": N / us * 1e6, "GB/s": wbytes / us / 1e3, "weight_bytes_per_gpu": wbytes // world,
+                  "exchange": "four NCCL all-to-all calls (row counts, rows, results, order) and two host reads of the counts per block",
+                  "cuda_graph": False}
+        if own_group:
+            print(json.dumps(result), flush=True)
     dist.barrier()
-    dist.destroy_process_group()
+    if own_group:
+        dist.destroy_process_group()
+    return result
+
+
+def run_config0(torch, device, pdl):
+    """Benchmark configuration 0, the CPU-runnable case: Q4_K weight [4096 x 4096] from N(0, 0.02) seed 0, activation
+    [1, 4096] from N(0, 1) seed 1, checked against the CPU path; then timed as 64 distinct matrices of that shape
+    (604 MB of blocks, larger than L2; matrix 0 is the seeded one) replayed from a CUDA graph."""
+    import numpy as np
+
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    from oracle import oracle as O
+    L = _lib.lib
+    n = k = 4096
+    copies = 64
+    g = torch.Generator(device=device)
+    ws = []
+    for i in range(copies):
+        g.manual_seed(0 if i == 0 else 100 + i)
+        ws.append(ops.quantize_weights(T.Q4K, torch.randn(n, k, generator=g, device=device, dtype=torch.float32) * 0.02))
+    g.manual_seed(1)
+    x = torch.randn(1, k, generator=g, device=device)
+    ys = torch.empty(copies, n, device=device)
+    wsb = L.fuelq_qmatmul_workspace_bytes(int(T.Q4K), 1, n, k)
+    scratch = torch.empty(copies, wsb, dtype=torch.uint8, device=device)
+    stream = torch.cuda.Stream(device)
+    sp = stream.cuda_stream
+
+    def one_pass():
+        for i in range(copies):
+            _lib.check(L.fuelq_qmatmul(int(T.Q4K), 1, n, k, ws[i].data_ptr(), x.data_ptr(), ys[i].data_ptr(), scratch[i].data_ptr(),
+                                       wsb, sp), "fuelq_qmatmul")
+
+    with torch.cuda.stream(stream):
+        one_pass()
+        stream.synchronize()
+        us = _time_graph(torch, stream, one_pass, 50) / copies
+    ref = O.matmul(O.Q4K, x.cpu().numpy(), ws[0].cpu().numpy(), n, O.SCALAR)
+    err = float(np.abs(ys[0].cpu().numpy() - ref[0]).max() / np.abs(ref).max())
+    assert err <= 2e-6, f"configuration 0: GPU result off the CPU path by {err}"
+    algo = n * (k // 256) * 144 + 4 * k + 4 * n
+    peak, peak_kind = _peaks()
+    return {"workload": "q4k_qmatmul_m1_k4096_n4096 (seed 0 weights, seed 1 activation), timed over 64 distinct matrices",
+            "avg_launch_us": us, "algorithmic_bytes_per_launch": algo, "gbs": algo / (us * 1e-6) / 1e9,
+            "hbm_frac": algo / (us * 1e-6) / 1e9 / peak, "peak_kind": f"of {peak_kind}", "pdl": bool(pdl),
+            "max_rel_err_vs_cpu_path": err}
 
 
 def run_decode_7b(torch, dist, device, rank, world):
     """LLaMA-2-7B-architecture greedy decode, batch 1 (Q4_K_M-style mix, random-init weights, f32 KV cache):
     a 512-token seeded prompt fed one token at a time, then 128 new tokens timed with CUDA events on a replayed
-    CUDA graph. With more than one GPU the model is tensor-parallel over all of them, every linear split by
-    output rows and the slices exchanged inside the kernels; the token hash must not depend on the GPU count."""
+    CUDA graph. With more than one GPU the model is tensor-parallel over all of them (column-parallel q/k/v, gate/up
+    and head; row-parallel o and down, their partial vectors exchanged inside the kernels and summed by one fixed
+    tree); the token hash must not depend on the GPU count."""
     import hashlib
 
     import numpy as np
@@ -445,7 +507,9 @@ def run_decode_7b(torch, dist, device, rank, world):
         kv_bytes = 2 * 32 * 576 * 4096 * 4 // world
         return {"tok_s": 1e3 / ms_tok, "ms_per_token": ms_tok, "n_gpus": world, "prompt_tokens": 512, "new_tokens": 128,
                 "timed_tokens": 127, "tokens_sha256": hashlib.sha256(str(out).encode()).hexdigest()[:16],
-                "exchange": "inside the kernels over peer-mapped memory" if world > 1 else "none (one GPU)",
+                "exchange": "none (one GPU)" if world == 1 else
+                            "column-parallel q/k/v, gate/up, head; row-parallel o, down summed by a fixed tree; two exchanges per layer, "
+                            "as stamped stores inside the kernels over peer-mapped memory",
                 "weight_bytes_per_gpu": model.weight_bytes, "kv_bytes_per_gpu_per_token": kv_bytes,
                 "hbm_frac_per_gpu": (model.weight_bytes + kv_bytes) / (ms_tok * 1e-3) / 1e9 / peak,
                 "peak_kind": f"of {peak_kind}", "cuda_graph": True, "launches_per_token": sum(9 if l["v"] is None else 10 for l in model.layers) + 6}
@@ -495,29 +559,53 @@ def main():
     _lib.check(L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0), "set_option")
     _lib.check(L.fuelq_set_option(_lib.OPT_DECODE_GRID, args.decode_grid), "set_option")
 
-    ws = make_weights(torch, ops, T, device, rank)
+    from fuel_b200.llama import PeerRegion, shard_range
+    lo, hi = shard_range(N_OUT, world, rank)
+    n_loc = hi - lo
+    ws = make_weights(torch, ops, T, device, lo, hi)
     g = torch.Generator(device=device)
-    g.manual_seed(7 + rank)
+    g.manual_seed(7)
     xs = [torch.randn(M_ROWS, K_IN, generator=g, device=device) for _ in range(LAYERS)]
-    ys = [torch.empty(M_ROWS, N_OUT, device=device) for _ in range(LAYERS)]
-    ws_bytes = L.fuelq_qmatmul_workspace_bytes(int(T.Q4K), M_ROWS, N_OUT, K_IN)
+    ys = [torch.empty(M_ROWS, n_loc, device=device) for _ in range(LAYERS)]
+    ws_bytes = L.fuelq_qmatmul_workspace_bytes(int(T.Q4K), M_ROWS, n_loc, K_IN)
     scratch = [torch.empty(ws_bytes, dtype=torch.uint8, device=device) for _ in range(LAYERS)]
 
     stream = torch.cuda.Stream(device)
     sptr = stream.cuda_stream
 
+    region = None
+    if world > 1:
+        # one destination vector per matrix on every GPU ({value, stamp} pairs), mapped into every rank
+        region = PeerRegion({f"y{i}": L.fuelq_peer_vec_bytes(N_OUT) for i in range(LAYERS)}, device, rank, world)
+        epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        picks = torch.zeros(LAYERS, dtype=torch.int32, device=device)
+        peers = _lib.Peers()
+        peers.world, peers.rank, peers.epoch = world, rank, epoch.data_ptr()
+        peers_ref = ctypes.byref(peers)
+        dsts = [region.ptrs(f"y{i}") for i in range(LAYERS)]
+        owns = [region.own + region.off[f"y{i}"] for i in range(LAYERS)]
+
     def one_pass():
+        if world > 1:
+            for i, (w, x, s) in enumerate(zip(ws, xs, scratch)):
+                _lib.check(L.fuelq_quantize_act_packed(int(T.Q4K), M_ROWS, K_IN, x.data_ptr(), s.data_ptr(), ws_bytes, sptr), "quantize")
+                _lib.check(L.fuelq_qmatmul_packed_peer(int(T.Q4K), K_IN, n_loc, w.data_ptr(), s.data_ptr(), dsts[i], lo, peers_ref, 0,
+                                                       sptr), "fuelq_qmatmul_packed_peer")
+                # the consumer: waits until every rank's slice of y has arrived here, takes the arg-max, ends the exchange step
+                _lib.check(L.fuelq_argmax_last_peer(owns[i], N_OUT, picks.data_ptr() + 4 * i, peers_ref, 0, epoch.data_ptr(), sptr),
+                           "fuelq_argmax_last_peer")
+            return
         for w, x, y, s in zip(ws, xs, ys, scratch):
-            st = L.fuelq_qmatmul(int(T.Q4K), M_ROWS, N_OUT, K_IN, w.data_ptr(), x.data_ptr(), y.data_ptr(),
+            st = L.fuelq_qmatmul(int(T.Q4K), M_ROWS, n_loc, K_IN, w.data_ptr(), x.data_ptr(), y.data_ptr(),
                                  s.data_ptr(), ws_bytes, sptr)
             if st:
                 _lib.check(st, "fuelq_qmatmul")
 
-    ys_mv = [torch.empty(M_ROWS, N_OUT, device=device) for _ in range(LAYERS)]
+    ys_mv = [torch.empty(M_ROWS, n_loc, device=device) for _ in range(LAYERS)]
 
     def matvec_only_pass():  # activations quantized beforehand into `scratch`: the mat-vec arithmetic alone
         for w, y, s in zip(ws, ys_mv, scratch):
-            st = L.fuelq_qmatmul_packed(int(T.Q4K), M_ROWS, N_OUT, K_IN, w.data_ptr(), s.data_ptr(), y.data_ptr(), sptr)
+            st = L.fuelq_qmatmul_packed(int(T.Q4K), M_ROWS, n_loc, K_IN, w.data_ptr(), s.data_ptr(), y.data_ptr(), sptr)
             if st:
                 _lib.check(st, "fuelq_qmatmul_packed")
 
@@ -588,14 +676,15 @@ def main():
         fused = L.fuelq_get_option(_lib.OPT_FUSED_QUANT) == 1
 
         # end to end through the host-buffer entry point: pinned x in, y out, every mat-vec
-        hws_bytes = L.fuelq_qmatmul_host_workspace_bytes(int(T.Q4K), M_ROWS, N_OUT, K_IN)
+        # (with several GPUs every rank does this for its rows; the host ends up with its slice of each y)
+        hws_bytes = L.fuelq_qmatmul_host_workspace_bytes(int(T.Q4K), M_ROWS, n_loc, K_IN)
         hws = [torch.empty(hws_bytes, dtype=torch.uint8, device=device) for _ in range(LAYERS)]
         xh = [x.cpu().pin_memory() for x in xs]
-        yh = [torch.empty(M_ROWS, N_OUT).pin_memory() for _ in range(LAYERS)]
+        yh = [torch.empty(M_ROWS, n_loc).pin_memory() for _ in range(LAYERS)]
 
         def host_pass():
             for w, x, y, s in zip(ws, xh, yh, hws):
-                st = L.fuelq_qmatmul_host(int(T.Q4K), M_ROWS, N_OUT, K_IN, w.data_ptr(), x.data_ptr(), y.data_ptr(),
+                st = L.fuelq_qmatmul_host(int(T.Q4K), M_ROWS, n_loc, K_IN, w.data_ptr(), x.data_ptr(), y.data_ptr(),
                                           s.data_ptr(), hws_bytes, sptr)
                 if st:
                     _lib.check(st, "fuelq_qmatmul_host")
@@ -617,22 +706,44 @@ def main():
     torch.cuda.synchronize()
     assert ops.device_error() == 0, "a kernel recorded an expired bounded wait"
     # the graph path and the host path must agree bit for bit on the last layer
-    assert torch.equal(ys[-1].cpu(), yh[-1]), "graph and host-buffer results differ"
-    assert torch.equal(ys[-1], ys_mv[-1]), "one-kernel and two-kernel results differ"
+    assert torch.equal(ys_mv[-1].cpu(), yh[-1]), "graph and host-buffer results differ"
+    if world == 1:
+        assert torch.equal(ys[-1], ys_mv[-1]), "one-kernel and two-kernel results differ"
+    else:
+        # the gathered vector of the last matrix: this rank's rows are its own product, and every rank holds the same vector
+        y_all = region.view(f"y{LAYERS - 1}", 8 * N_OUT, torch.float32)[0::2].clone()
+        assert torch.equal(y_all[lo:hi], ys_mv[-1][0]), "the gathered y does not hold this rank's rows"
+        chk = torch.stack([y_all.double().sum(), picks[-1].double()])
+        every = [torch.empty_like(chk) for _ in range(world)]
+        dist.all_gather(every, chk)
+        assert all(torch.equal(e, every[0]) for e in every), "ranks disagree on the gathered y"
 
-    decode_7b = None
-    if not args.no_model:
-        del hws, scratch
+    decode_7b, prefill_sharded, moe_ep, config0 = None, None, None, None
+    del hws, scratch
+    if region is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+        region.close()
+    torch.cuda.empty_cache()
+    if world == 1 and not args.no_cpu_baseline:
+        config0 = run_config0(torch, device, args.pdl)
         torch.cuda.empty_cache()
+    if not args.no_model:
         decode_7b = run_decode_7b(torch, dist, device, rank, world)
+        if world > 1:  # the other two multi-GPU forms at the same GPU count
+            torch.cuda.empty_cache()
+            prefill_sharded = run_prefill_sharded(args, rank, local_rank, world, own_group=False)
+            torch.cuda.empty_cache()
+            moe_ep = run_moe_expert_parallel(args, rank, local_rank, world, own_group=False)
 
     ms_per_step = ms_total / args.steps
-    value = world * LAYERS * ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
-    e2e_value = world * LAYERS * ALGO_BYTES / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    value = LAYERS * ALGO_BYTES / (ms_per_step * 1e-3) / 1e9      # the whole job: the same 32 matrices at every GPU count
+    e2e_value = LAYERS * ALGO_BYTES / (e2e_ms / e2e_steps * 1e-3) / 1e9
     peak, peak_kind = _peaks()
     # the dominant kernel: with in-kernel activation quantization the step IS one kernel per matrix, timed above
-    kern_us = ms_per_step * 1e3 / LAYERS if fused else mv_only_us
-    achieved = ALGO_BYTES / (kern_us * 1e-6) / 1e9
+    kern_us = ms_per_step * 1e3 / LAYERS if (fused and world == 1) else mv_only_us
+    algo_launch = W_BYTES // N_OUT * n_loc + 4 * M_ROWS * K_IN + 4 * M_ROWS * n_loc   # this GPU's rows of one matrix
+    achieved = algo_launch / (kern_us * 1e-6) / 1e9
 
     if rank != 0:
         if world > 1:
@@ -671,20 +782,28 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": bench_scaling(world),
         "vs_baseline": None, "dtype": "i8", "data": "synthetic",
         "config": bench_config(world, bool(args.pdl)),
-        "pct_of_8tbs": value / world / 8000.0 * 100.0,
+        "pct_of_8tbs": value / world / 8000.0 * 100.0,   # per GPU
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_regs_kernel<Q4KRegs,1,1>",
-                     "avg_launch_us": kern_us, "algorithmic_bytes_per_launch": ALGO_BYTES,
+                     "avg_launch_us": kern_us, "algorithmic_bytes_per_launch": algo_launch,
                      "activation_quantization": "inside the kernel" if fused else "separate kernel, not in this figure",
                      "prequantized_activations_avg_launch_us": mv_only_us},
         "cpu_baseline": cpu_baseline,
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * M_ROWS * K_IN * 4,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": world * LAYERS * M_ROWS * K_IN * 4,
                 "d2h_bytes_per_step": LAYERS * M_ROWS * N_OUT * 4, "ms_per_step": e2e_ms / e2e_steps,
-                "api": "fuelq_qmatmul_host (pinned host x in, host y out, per mat-vec)"},
-        "gpu_launches": args.steps * LAYERS * (1 if fused else 2),
+                "api": "fuelq_qmatmul_host (pinned host x in, host y out, per mat-vec" +
+                       ("" if world == 1 else "; every rank its rows of each matrix, no exchange") + ")"},
+        "gpu_launches": args.steps * LAYERS * (3 if world > 1 else 1 if fused else 2) * world,
         "clocks": clocks,
         "decode_7b": decode_7b,
     }
+    if config0 is not None:
+        line["config0"] = config0
+    if world > 1:
+        line["exchange"] = ("per mat-vec: each rank's kernel stores its rows of y as stamped 8-byte pairs into every GPU's copy over "
+                            "NVLink; a consumer kernel on every GPU polls its copy until complete (no collective, no multicast)")
+        line["prefill_sharded"] = prefill_sharded
+        line["moe_ep"] = moe_ep
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

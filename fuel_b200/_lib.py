@@ -90,17 +90,16 @@ PROTOTYPES = {
     "fuelq_moe_swiglu_quantize": (_i32, [_vp, _i64, _i64, _vp, _sz, _vp]),
     "fuelq_moe_qmatmul": (_i32, [_i32, _i32, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp]),
     "fuelq_moe_combine": (_i32, [_vp, _vp, _vp, _i64, _i32, _i64, _vp, _vp]),
-    "fuelq_peer_act_bytes": (_sz, [_i64]),
     "fuelq_peer_vec_bytes": (_sz, [_i64]),
     "fuelq_ipc_alloc": (_i32, [_sz, ctypes.POINTER(_vp), _vp]),
     "fuelq_ipc_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
     "fuelq_ipc_close": (_i32, [_vp]),
     "fuelq_ipc_free": (_i32, [_vp]),
-    "fuelq_qmatmul_packed_peer": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp, _i64, _pp, _i32, _i32, _vp]),
-    "fuelq_add_rmsnorm_q8k_peer": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, _vp, _sz, _pp, _i32, _vp]),
-    "fuelq_swiglu_q8k_peer": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _pp, _i32, _vp]),
-    "fuelq_attn_decode_q8k_peer": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _sz, _i32, _i64,
-                                          _vp, _pp, _i32, _rp, _vp]),
+    "fuelq_qmatmul_packed_peer": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp, _i64, _pp, _i32, _vp]),
+    "fuelq_add_rmsnorm_q8k_peer": (_i32, [_vp, _vp, _i32, _vp, _i64, ctypes.c_float, _vp, _sz, _pp, _i32, _vp]),
+    "fuelq_add_rmsnorm_q8k_parts": (_i32, [_vp, _vp, _i32, _vp, _i64, ctypes.c_float, _vp, _sz, _vp]),
+    "fuelq_qmatmul_packed_tree": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _vp]),
+    "fuelq_qmatmul_packed_tree_peer": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp, _i64, _pp, _i32, _i32, _vp, _vp]),
     "fuelq_argmax_last_peer": (_i32, [_vp, _i64, _vp, _pp, _i32, _vp, _vp]),
     "fuelq_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "fuelq_argmax_last": (_i32, [_vp, _i64, _vp, _vp]),

@@ -43,17 +43,19 @@ struct DecodeRegsParams {
   int u_begin[9];                 // unit range of k-slice s: [u_begin[s], u_begin[s+1])
   const float* x_f32;             // not null: f32 activations [m][k]; every CTA quantizes them itself (Q8_K) into
   int act_smem_off;               //   plain planes at this byte offset of its shared memory, instead of reading `act`
+  float* host_y;                  // not null (M = 1): the last CTA to finish copies y[0..n) here (device-mapped host memory)
+  unsigned* host_done;            //   device word, zero at kernel start, counting finished CTAs
+  // Tree form (kTree kernels): the row's k range is cut into n_leaves leaves (1, 2, 4 or 8) of leaf_u0[l+1] - leaf_u0[l]
+  // units each; leaf l sits on lanes [l * leaf_lw, (l + 1) * leaf_lw) of the row's warps.
+  int n_leaves, leaf_lw;
+  int leaf_u0[9];
 };
 
 // Extra arguments of the tensor-parallel form (kPeer): the output rows go, as stamped pairs of exchange
-// point ctx.push_seq, to dst[q] on every rank q (already offset to this rank's slice); with
-// ctx.wait_seq >= 0 the activations are the stamped planes `act_ll` that exchange point filled, which
-// the CTA first copies (polling) into plain planes at byte act_smem_off of its shared memory.
+// point ctx.push_seq, to dst[q] on every rank q (already offset to this rank's slice).
 struct DecodeRegsPeer {
   PeerCtx ctx;
   uint2* dst[kPeerMaxWorld];
-  StampedPlanes act_ll;
-  int act_smem_off;
 };
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -399,12 +401,22 @@ struct DecodeRegsSmemHeader {
   uint64_t empty[kDecodeMaxStages];
   uint64_t part_ready[2];
   uint64_t acts_ready;
+  uint64_t rows_stored, host_go;  // write-back to a host buffer: consumer warps done / thread 0 has counted this CTA
+  int host_last;
   float partial[2][32][8][2];  // [buffer][row in stage][k-slice][m]
 };
 
-template <class Fmt, int M, int NU, bool kPeer>
+// kTree: the dot product of a row is summed as a balanced binary tree over (up to) eight fixed ranges of k ("leaves"),
+// each leaf summed in an order that depends on nothing but the leaf: leaf l occupies leaf_lw consecutive lanes, the
+// lanes of a leaf are added pairwise from the lowest lane bit up, then leaves pairwise, in registers and (for rows
+// spread over several warps) in shared memory. A matrix cut along k into 2, 4 or 8 aligned groups of leaves (one per
+// GPU) therefore gives partial results whose pairwise sum, in the same tree, is BIT-IDENTICAL to the one-GPU result:
+// each GPU computes a complete subtree. This is what lets the row-parallel layers of a tensor-parallel model produce
+// the same tokens at every GPU count.
+template <class Fmt, int M, int NU, bool kPeer, bool kTree = false>
 __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, const DecodeRegsPeer* g) {
   static_assert(!kPeer || M == 1, "the tensor-parallel form is a single-row mat-vec");
+  static_assert(!kTree || (M == 1 && NU == 1), "the tree form is a single-row mat-vec with one unit per lane");
   extern __shared__ __align__(128) uint8_t smem_raw[];
   DecodeRegsSmemHeader* hd = reinterpret_cast<DecodeRegsSmemHeader*>(smem_raw);
   uint8_t* stages = smem_raw + align_up(sizeof(DecodeRegsSmemHeader), 128);
@@ -426,6 +438,8 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
     mbar_init(&hd->part_ready[0], kDecodeConsumerWarps);
     mbar_init(&hd->part_ready[1], kDecodeConsumerWarps);
     mbar_init(&hd->acts_ready, kDecodeConsumerWarps);
+    mbar_init(&hd->rows_stored, kDecodeConsumerWarps);
+    mbar_init(&hd->host_go, 1);
     mbar_init_fence();
   }
   __syncthreads();
@@ -521,22 +535,16 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
   }
   if constexpr (kPeer) {
     push_stamp = peer_stamp(g->ctx, g->ctx.push_seq);
-    if (Fmt::kHasRaw && g->ctx.wait_seq >= 0) {
-      // ... or arrive from the peers' kernels as stamped planes: the consumer warps copy them once per CTA
-      // into shared memory (each thread polling its own pairs), then load from there
-      planes = act_planes(smem_raw + g->act_smem_off, kQ4K, 1, p.k);
-      const uint32_t want = peer_stamp(g->ctx, g->ctx.wait_seq);
-      const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
-      peer_copy_words(g->act_ll.qs, (uint32_t*)planes.qs, p.k >> 2, want, t, nt, g->ctx.wait_ns);
-      peer_copy_words(g->act_ll.bs, (uint32_t*)planes.bsums, p.k >> 5, want, t, nt, g->ctx.wait_ns);
-      peer_copy_words1(g->act_ll.d, (uint32_t*)planes.d, p.k >> 8, want, t, nt, g->ctx.wait_ns);
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * kDecodeConsumerWarps) : "memory");
-    }
   }
 #pragma unroll
   for (int j = 0; j < NU; ++j) {
-    const int u = u_begin + lane + 32 * j;
-    const bool valid = u < u_end;
+    int u = u_begin + lane + 32 * j;
+    bool valid = u < u_end;
+    if constexpr (kTree) {
+      const int slot = slice * 32 + lane, leaf = slot / p.leaf_lw, pos = slot - leaf * p.leaf_lw;
+      valid = leaf < p.n_leaves && pos < p.leaf_u0[leaf < 8 ? leaf + 1 : 8] - p.leaf_u0[leaf < 8 ? leaf : 8];
+      u = valid ? p.leaf_u0[leaf] + pos : 0;
+    }
     Fmt::make_unit(u, valid, un[j]);
 #pragma unroll
     for (int i = 0; i < M; ++i) Fmt::load_act(u, valid, planes, p.k, i, ac[j][i]);
@@ -592,7 +600,8 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
         Fmt::template math<M>(ra, un[0], ac[0], acc0);
         Fmt::template math<M>(rb, un[0], ac[0], acc1);
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
+        for (int lv = 0; lv < 5; ++lv) {
+          const int off = kTree ? (1 << lv) : (16 >> lv);  // tree form: lowest lane bit first
           acc0[0] += __shfl_xor_sync(0xffffffffu, acc0[0], off);
           acc1[0] += __shfl_xor_sync(0xffffffffu, acc1[0], off);
         }
@@ -612,7 +621,7 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
 #pragma unroll
       for (int i = 0; i < M; ++i) {
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+        for (int lv = 0; lv < 5; ++lv) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], kTree ? (1 << lv) : (16 >> lv));
       }
       if (lane == 0) emit(r, acc);
     }
@@ -628,8 +637,21 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       }
       for (int t = threadIdx.x; t < rows_here * M; t += 32 * kDecodeConsumerWarps) {
         const int r = t / M, i = t - r * M;
-        float sum = hd->partial[buf][r][0][i];
-        for (int sg = 1; sg < ks; ++sg) sum += hd->partial[buf][r][sg][i];
+        float sum;
+        if constexpr (kTree) {  // pairwise, continuing the tree of the lanes
+          float v[8];
+#pragma unroll
+          for (int sg = 0; sg < 8; ++sg) v[sg] = sg < ks ? hd->partial[buf][r][sg][i] : 0.f;
+#pragma unroll
+          for (int w = 1; w < 8; w <<= 1)
+#pragma unroll
+            for (int sg = 0; sg < 8; sg += 2 * w)
+              if (sg + w < ks) v[sg] += v[sg + w];
+          sum = v[0];
+        } else {
+          sum = hd->partial[buf][r][0][i];
+          for (int sg = 1; sg < ks; ++sg) sum += hd->partial[buf][r][sg][i];
+        }
         if constexpr (kPeer) {
           for (int q = 0; q < g->ctx.world; ++q) st_pair(g->dst[q] + row0 + r, __float_as_uint(sum), push_stamp);
         } else {
@@ -638,6 +660,37 @@ __device__ __forceinline__ void decode_regs_body(const DecodeRegsParams& p, cons
       }
     }
     if (++s == S) s = 0, ph ^= 1u;
+  }
+  if constexpr (!kPeer && !kTree && M == 1) {
+    if (p.host_y) {
+      // Result wanted in host memory: every CTA counts itself once its rows are stored (fence, then a device-wide
+      // counter); the CTA that counts last sees all of y and copies it out, 16 bytes per thread. Waits are bounded.
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hd->rows_stored);
+      if (warp == 0) {
+        const bool met = mbar_wait_bounded(&hd->rows_stored, 0);
+        if (lane == 0) {
+          hd->host_last = met && atomicAdd(p.host_done, 1u) == gridDim.x - 1u;
+          if (!met) record_dev_error(kErrFullWait);
+          __threadfence();
+          mbar_arrive(&hd->host_go);
+        }
+      }
+      __syncwarp();
+      if (!mbar_wait_bounded(&hd->host_go, 0)) {
+        record_dev_error(kErrFullWait);
+        return;
+      }
+      if (hd->host_last) {
+        __threadfence();
+        const int t = threadIdx.x, nt = 32 * kDecodeConsumerWarps;
+        const int n = (int)p.n, n4 = (((reinterpret_cast<uintptr_t>(p.host_y) | reinterpret_cast<uintptr_t>(p.y)) & 15) == 0) ? (n >> 2) : 0;
+        for (int i = t; i < n4; i += nt)
+          reinterpret_cast<float4*>(p.host_y)[i] = __ldcg(reinterpret_cast<const float4*>(p.y) + i);
+        for (int i = (n4 << 2) + t; i < n; i += nt) p.host_y[i] = __ldcg(p.y + i);
+      }
+    }
   }
 }
 
@@ -651,6 +704,17 @@ template <class Fmt, int NU>
 __global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_peer_kernel(const DecodeRegsParams p,
                                                                              const DecodeRegsPeer g) {
   decode_regs_body<Fmt, 1, NU, true>(p, &g);
+}
+
+// Tree-ordered forms (see kTree above): plain output, and output scattered to every rank.
+template <class Fmt>
+__global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_tree_kernel(const DecodeRegsParams p) {
+  decode_regs_body<Fmt, 1, 1, false, true>(p, nullptr);
+}
+template <class Fmt>
+__global__ void __launch_bounds__(kDecodeThreads, 2) decode_regs_tree_peer_kernel(const DecodeRegsParams p,
+                                                                                  const DecodeRegsPeer g) {
+  decode_regs_body<Fmt, 1, 1, true, true>(p, &g);
 }
 
 }  // namespace fq

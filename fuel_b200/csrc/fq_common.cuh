@@ -194,6 +194,22 @@ __global__ void __launch_bounds__(32) prefetch_l2_kernel(const uint8_t* __restri
 }
 
 
+// n f32 words from device memory to a device-mapped host buffer (or any other place), 16 bytes per thread where
+// both addresses allow it: the write-back of a small result without a copy-engine hand-off.
+__global__ void __launch_bounds__(256) copy_out_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, long long n,
+                                                           int vec) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x, nt = (long long)gridDim.x * blockDim.x;
+  if (vec) {
+    const long long n4 = n >> 2;
+    for (long long i = t; i < n4; i += nt) reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
+    for (long long i = (n4 << 2) + t; i < n; i += nt) dst[i] = src[i];
+  } else {
+    for (long long i = t; i < n; i += nt) dst[i] = src[i];
+  }
+}
+
 __device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
 
 // unaligned-by-2 32-bit read from shared memory: two aligned words and a funnel shift

@@ -35,14 +35,10 @@ struct Options {
   int64_t peer_wait_ms = 4000; // deadline of the exchange polls in the tensor-parallel kernels
   int64_t prefill_tf32 = 0;   // tensor-core path in tf32 instead of bf16
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
-  int64_t dbg_mb_groups = 0, dbg_mb_min_m = 2;
+  int64_t dbg_mb_groups = 0, dbg_mb_min_m = 2, dbg_mb_rpc = 0, dbg_host_wb = 0, dbg_host_early = 1;  // host write-back: 0 = by launch mode, 1 = own kernel, 2 = inside the mat-vec kernel
 };
 Options g_opt;
 
-#ifdef FQ_TRACE
-unsigned long long* g_trace = nullptr;
-int g_trace_slot = 0;
-#endif
 struct DeviceInfo {
   int sm_count = 0;
   int max_smem_optin = 0;
@@ -84,7 +80,7 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
 
 // ------------------------------------------------------------------ activation quantization
 int32_t quantize_act_impl(int weight_type, int64_t m, int64_t k, const float* x, void* ref_out, void* packed,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, unsigned* zero_word = nullptr, bool early_x = false) {
   if (!supported_weight(weight_type)) return kNotSupported;
   const int at = act_type_for(weight_type);
   const int be = block_elems(at);
@@ -101,11 +97,11 @@ int32_t quantize_act_impl(int weight_type, int64_t m, int64_t k, const float* x,
     if (ref_out) {
       if (!aligned(ref_out, 4)) return kMisaligned;
       e = launch(quantize_q8k_kernel<true>, grid, block, 0, stream, x, nb, (uint8_t*)ref_out, (int8_t*)nullptr,
-                 (float*)nullptr, (int16_t*)nullptr);
+                 (float*)nullptr, (int16_t*)nullptr, zero_word, (int)early_x);
     } else {
       ActPlanes a = act_planes(packed, weight_type, m, k);
       e = launch(quantize_q8k_kernel<false>, grid, block, 0, stream, x, nb, (uint8_t*)nullptr, (int8_t*)a.qs,
-                 (float*)a.d, (int16_t*)a.bsums);
+                 (float*)a.d, (int16_t*)a.bsums, zero_word, (int)early_x);
     }
     return e == cudaSuccess ? kOk : kLaunchFailure;
   }
@@ -116,11 +112,11 @@ int32_t quantize_act_impl(int weight_type, int64_t m, int64_t k, const float* x,
   if (ref_out) {
     if (!aligned(ref_out, 2)) return kMisaligned;
     e = launch(quantize_q8_0_kernel<true>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)ref_out, (int8_t*)nullptr,
-               (float*)nullptr);
+               (float*)nullptr, zero_word, (int)early_x);
   } else {
     ActPlanes a = act_planes(packed, weight_type, m, k);
     e = launch(quantize_q8_0_kernel<false>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)nullptr, (int8_t*)a.qs,
-               (float*)a.d);
+               (float*)a.d, zero_word, (int)early_x);
   }
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
@@ -206,13 +202,15 @@ struct RegsPlan {
 };
 
 // `reserve`: bytes of shared memory kept free after the stage ring (the tensor-parallel form stages its activations there)
-int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl, size_t reserve = 0) {
+int32_t plan_decode_regs(int units_per_row, int row_bytes, int64_t n, const DeviceInfo& di, RegsPlan* pl, size_t reserve = 0,
+                         int force_ks = 0) {
   int ks = 1;
   while (ks < 8 && (units_per_row + ks - 1) / ks > 32) ks *= 2;  // one unit per lane if eight slices allow it
   if ((units_per_row + ks - 1) / ks > 64) return kNotSupported;
   const int per_slice = (units_per_row + ks - 1) / ks;
   pl->ks = ks;
   pl->nu = per_slice > 32 ? 2 : 1;
+  if (force_ks) pl->ks = ks = force_ks, pl->nu = 1;  // the tree form lays the lanes out itself
   const int n_rgroups = kDecodeConsumerWarps / ks;
   const size_t header = align_up(sizeof(DecodeRegsSmemHeader), 128);
   const size_t per_cta_budget = ((size_t)di.max_smem_optin + 1024) / 2 - 1024 - 512;
@@ -273,9 +271,13 @@ cudaError_t launch_decode_regs_peer(const DecodeRegsParams& p, const DecodeRegsP
 }
 
 // returns kNotSupported when this variant does not cover the problem (the caller falls back)
+// host_y / host_done: the last thread block to finish also copies y (n words) to the device-mapped host buffer host_y;
+// *host_done is a device word that is zero when the kernel starts.
 int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const ActPlanes& planes, float* y,
-                         cudaStream_t stream, const DecodeRegsPeer* peer = nullptr, const float* x_f32 = nullptr) {
+                         cudaStream_t stream, const DecodeRegsPeer* peer = nullptr, const float* x_f32 = nullptr,
+                         float* host_y = nullptr, unsigned* host_done = nullptr) {
   if (peer && m != 1) return kNotSupported;
+  if (host_y && (peer || m != 1 || !host_done)) return kNotSupported;
   if (x_f32 && (peer || (type != kQ4K && type != kQ6K))) return kNotSupported;
   if (peer && type == kQ5K) return kNotSupported;
   if (m > 2 || (type != kQ4K && type != kQ5K && type != kQ6K && type != kQ8_0)) return kNotSupported;
@@ -286,10 +288,10 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   p.units_per_row = (int)(k / 128);  // every format's lane unit covers 128 elements
   p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
   RegsPlan pl;
-  // Activations staged in shared memory (quantized in the kernel, or copied from stamped planes) are dead
+  // Activations staged in shared memory (quantized in the kernel) are dead
   // once the consumers hold them in registers, so they borrow the LAST stage buffer of the ring: the
   // producer fills that stage only after the consumers report their activations loaded.
-  const size_t staged = ((peer && peer->ctx.wait_seq >= 0) || x_f32) ? align_up(act_packed_bytes(kQ4K, m, k), 128) : 0;
+  const size_t staged = x_f32 ? align_up(act_packed_bytes(kQ4K, m, k), 128) : 0;
   int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, 0);
   if (st != kOk) return st;
   size_t reserve = 0;
@@ -299,16 +301,12 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
     if (st != kOk) return st;
   }
   const int staged_off = reserve ? (int)(pl.smem - reserve) : (int)(pl.smem - pl.stage_stride);
-  DecodeRegsPeer peer_args;
-  if (peer) {
-    peer_args = *peer;
-    peer_args.act_smem_off = staged_off;
-    peer = &peer_args;
-  }
   p.w = (const uint8_t*)w;
   p.act = planes;
   p.x_f32 = x_f32;
   p.act_smem_off = staged_off;
+  p.host_y = host_y;
+  p.host_done = host_done;
   p.y = y;
   p.n = n;
   p.k = (int)k;
@@ -351,6 +349,91 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
     default: FQ_REGS_DISPATCH(Q8_0Regs); break;
   }
 #undef FQ_REGS_DISPATCH
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// ---- tree-ordered mat-vec (decode_regs.cuh, kTree): m = 1, the row's k range cut into n_leaves leaves of
+// leaf_blocks[l] 256-element blocks; `peer` scatters the result to every rank
+template <class Fmt>
+cudaError_t launch_decode_tree(const DecodeRegsParams& p, const DecodeRegsPeer* g, const RegsPlan& pl, cudaStream_t stream) {
+  static bool attr_set[2][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  DeviceInfo* di;
+  if (!device_info(&di)) return cudaErrorInvalidDevice;
+  if (g) {
+    auto kern = decode_regs_tree_peer_kernel<Fmt>;
+    if (!attr_set[1][dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+      if (e != cudaSuccess) return e;
+      attr_set[1][dev] = true;
+    }
+    return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p, *g);
+  }
+  auto kern = decode_regs_tree_kernel<Fmt>;
+  if (!attr_set[0][dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+    if (e != cudaSuccess) return e;
+    attr_set[0][dev] = true;
+  }
+  return launch(kern, dim3(pl.grid), dim3(kDecodeThreads), pl.smem, stream, p);
+}
+
+int32_t decode_tree_impl(int type, int64_t n, int64_t k, const void* w, const ActPlanes& planes, float* y, int n_leaves,
+                         const int32_t* leaf_blocks, const DecodeRegsPeer* peer, cudaStream_t stream) {
+  if (type != kQ4K && type != kQ6K) return kNotSupported;
+  if (n_leaves != 1 && n_leaves != 2 && n_leaves != 4 && n_leaves != 8) return kInvalidProblem;
+  if (!leaf_blocks || k % 256) return kInvalidProblem;
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  DecodeRegsParams p;
+  int64_t blocks = 0;
+  int max_units = 1;
+  p.leaf_u0[0] = 0;
+  for (int l = 0; l < 8; ++l) {
+    const int b = l < n_leaves ? leaf_blocks[l] : 0;
+    if (b < 0) return kInvalidProblem;
+    blocks += b;
+    p.leaf_u0[l + 1] = p.leaf_u0[l] + 2 * b;  // a lane unit is half a 256-block
+    if (2 * b > max_units) max_units = 2 * b;
+  }
+  if (blocks * 256 != k) return kInvalidProblem;
+  if (max_units > 32) return kNotSupported;
+  int lw = 1;
+  while (lw < max_units) lw *= 2;
+  const int lanes = lw * n_leaves;
+  const int ks = lanes <= 32 ? 1 : lanes / 32;
+  p.n_leaves = n_leaves;
+  p.leaf_lw = lw;
+  p.units_per_row = (int)(k / 128);
+  p.row_bytes = (int)(k / 256 * block_bytes(type));
+  RegsPlan pl;
+  const int32_t st = plan_decode_regs(p.units_per_row, p.row_bytes, n, *di, &pl, 0, ks);
+  if (st != kOk) return st;
+  p.w = (const uint8_t*)w;
+  p.act = planes;
+  p.x_f32 = nullptr;
+  p.host_y = nullptr;
+  p.host_done = nullptr;
+  p.act_smem_off = 0;
+  p.y = y;
+  p.n = n;
+  p.k = (int)k;
+  p.m = 1;
+  p.total_bytes = n * (int64_t)p.row_bytes;
+  p.rows_per_stage = pl.rows_per_stage;
+  p.ks = pl.ks;
+  p.num_stages = pl.num_stages;
+  p.stage_stride = pl.stage_stride;
+  p.rows_q = (int)(n / pl.grid);
+  p.rows_rem = (int)(n % pl.grid);
+  for (int sl = 0; sl <= 8; ++sl) p.u_begin[sl] = 0;
+  p.depth = g_opt.dbg_depth ? (int)g_opt.dbg_depth : 3;
+  if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
+  p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
+  const cudaError_t e = type == kQ4K ? launch_decode_tree<Q4KRegs>(p, peer, pl, stream)
+                                     : launch_decode_tree<Q6KRegs>(p, peer, pl, stream);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
@@ -400,6 +483,18 @@ int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, co
       return kNotSupported;
   }
   return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+// The address at which kernels on the current device can read or write a host buffer in place: non-null only for
+// page-locked memory that is mapped into the device's address space. Pageable memory (and anything the driver
+// does not know) gives null, and the caller copies instead.
+void* mapped_alias(const void* host_ptr) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, host_ptr) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
 }
 
 // Weight stream-in ahead of use (see prefetch_l2_kernel). One small CTA per SM.
@@ -512,12 +607,15 @@ int32_t mma_batch_fmt(int n_groups, int64_t n, int64_t k, const void* w, const A
   size_t stride = 0, act_bytes = 0;
   int wstride = 0;
   // fewest sweeps over k first; within that, at least three stages (two at the very least)
+  int rpc = 1;
   for (int chunks = 1; chunks <= 64 && !kc_blocks; ++chunks) {
     const int kc = (nblk + chunks - 1) / chunks;
     const size_t ab = (size_t)mb_act_layout<F>(kc, act_rows).bytes;
-    // a staged weight row: the chunk widened to 16-byte boundaries, placed so that consecutive rows are 16 bytes apart modulo 128
-    const int ws = (int)align_up((size_t)kc * F::kBytes256 + 32, 128) + 16;
-    const size_t st = align_up((size_t)R * ws, 128);
+    // whole rows staged: consecutive rows travel in one bulk copy (2 per copy; 4 for short rows)
+    rpc = chunks == 1 ? (g_opt.dbg_mb_rpc ? (int)g_opt.dbg_mb_rpc : (nblk * F::kBytes256 <= 1536 ? 4 : 2)) : 1;
+    // a staged copy: its bytes widened to 16-byte boundaries, placed so that consecutive copies are 16 bytes apart modulo 128
+    const int ws = (int)align_up((size_t)(rpc - 1) * nblk * F::kBytes256 + (size_t)kc * F::kBytes256 + 32, 128) + 16;
+    const size_t st = align_up((size_t)(R / rpc) * ws, 128);
     const int min_stages = chunks < 4 ? 3 : 2;
     if (header + ab + part_bytes + (size_t)min_stages * st <= total) {
       kc_blocks = kc, act_bytes = ab, wstride = ws, stride = st;
@@ -539,15 +637,15 @@ int32_t mma_batch_fmt(int n_groups, int64_t n, int64_t k, const void* w, const A
   p.group_bytes = n * (int64_t)p.row_bytes;
   p.total_bytes = (int64_t)n_groups * p.group_bytes;
   p.num_stages = stages;
-  p.n_wgroups = g_opt.dbg_mb_groups ? (int)g_opt.dbg_mb_groups : (stages >= 4 ? 4 : stages >= 2 ? 2 : 1);
+  // (never more groups than stages: a group must not wait for a slot's next phase before the slot's first use)
+  p.n_wgroups = stages >= 4 ? 4 : stages >= 2 ? 2 : 1;
+  if (g_opt.dbg_mb_groups && g_opt.dbg_mb_groups <= p.n_wgroups) p.n_wgroups = (int)g_opt.dbg_mb_groups;
   p.stage_stride = (int)stride;
   p.wstride = wstride;
+  p.rows_per_copy = rpc;
   p.act_off = (int)(header + (size_t)stages * stride);
   p.part_off = (int)(p.act_off + act_bytes);
   p.kc_blocks = kc_blocks;
-#ifdef FQ_TRACE
-  p.trace = g_trace ? g_trace + (size_t)(g_trace_slot++) * 512 * 64 : nullptr;
-#endif
   const int n_tiles = (int)((n + 15) / 16);
   int per_group = (di->sm_count + n_groups - 1) / n_groups;
   if (n_groups > 1) per_group = (2 * di->sm_count + n_groups - 1) / n_groups;
@@ -609,20 +707,6 @@ int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const vo
 }
 
 // ---- tensor-core path (prefill.cuh)
-// whether the integer tensor-core kernel (moe_mma.cuh) has a shared-memory plan for this k
-bool mma_plan_fits(int64_t k) {
-  DeviceInfo* di;
-  if (k % 256 || k > (1 << 20) || !device_info(&di)) return false;
-  const size_t per_cta = ((size_t)di->max_smem_optin + 1024) / 2 - 1024 - 512;
-  const size_t fixed = align_up(sizeof(MmaSmemHeader), 128) + kDecodeConsumerWarps * 128 * sizeof(float);
-  const int nblk = (int)(k / 256);
-  for (int chunks = 1; chunks <= 16; ++chunks) {
-    const int kc = (nblk + chunks - 1) / chunks;
-    if (fixed + mma_act_bytes(kc) + 2 * align_up((size_t)8 * (kc * Q4KL::kBytes + 16), 128) <= per_cta) return true;
-  }
-  return false;
-}
-
 bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   (void)n;
   int64_t max_m = g_opt.decode_max_m;
@@ -751,9 +835,6 @@ const char* fuelq_status_string(int32_t status) {
   }
 }
 
-#ifdef FQ_TRACE
-void fuelq_trace_set(void* p) { g_trace = (unsigned long long*)p; g_trace_slot = 0; }
-#endif
 int32_t fuelq_block_elems(int32_t t) { return block_elems(t); }
 int32_t fuelq_block_bytes(int32_t t) { return block_bytes(t); }
 
@@ -781,6 +862,9 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 107: g_opt.moe_kernel = value; return kOk;
     case 111: g_opt.dbg_mb_groups = value; return kOk;
     case 112: g_opt.dbg_mb_min_m = value; return kOk;
+    case 113: g_opt.dbg_mb_rpc = value; return kOk;
+    case 114: g_opt.dbg_host_wb = value; return kOk;
+    case 115: g_opt.dbg_host_early = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;
@@ -945,13 +1029,42 @@ int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_
   p += align_up((size_t)m_total * k * 4, 256);
   float* y_dev = (float*)p;
   p += align_up((size_t)m_total * n * 4, 256);
-  if (cudaMemcpyAsync(x_dev, x_host, (size_t)m_total * k * 4, cudaMemcpyHostToDevice, stream) != cudaSuccess)
-    return kLaunchFailure;
+  // Small activations held in page-locked, device-mapped host memory (cudaHostAlloc, cudaHostRegister with the
+  // mapped flag, a framework's pinned tensors): the quantizing kernel reads x in place over PCIe and a small kernel
+  // writes y in place, so the chain is three kernels on one stream with no copy-engine hand-off in between.
+  const size_t xb = (size_t)m_total * k * 4, yb = (size_t)m_total * n * 4;
+  if (!prefill_available(ggml_type, m_total, n, k) && xb <= (256u << 10) && yb <= (1u << 20)) {
+    const float* xm = (const float*)mapped_alias(x_host);
+    float* ym = (float*)mapped_alias(y_host);
+    if (xm && ym && aligned(xm, 16) && aligned(ym, 4)) {
+      int32_t s1 = kOk;
+      if (g_opt.l2_prefetch)
+        s1 = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), stream);
+      unsigned* done = (unsigned*)x_dev;  // the staging area for x is free on this path: its first word counts thread blocks
+      if (s1 == kOk) s1 = quantize_act_impl(ggml_type, m_total, k, xm, nullptr, p, stream, done, g_opt.dbg_host_early != 0);
+      if (s1 != kOk) return s1;
+      // One row in plain launches: the mat-vec kernel's last thread block writes y to the host buffer itself (one launch
+      // fewer). With programmatic dependent launch the separate write-back kernel measured faster: it is resident
+      // before the mat-vec ends, and sixteen thread blocks share the copy.
+      const bool wb_inside = g_opt.dbg_host_wb == 2 || (g_opt.dbg_host_wb == 0 && !g_opt.pdl);
+      if (m_total == 1 && wb_inside && g_opt.decode_kernel != 1) {
+        s1 = decode_regs_impl(ggml_type, 1, n, k, w, act_planes(p, ggml_type, 1, k), y_dev, stream, nullptr, nullptr, ym, done);
+        if (s1 != kNotSupported) return s1;
+      }
+      s1 = decode_chunked(ggml_type, m_total, n, k, w, p, y_dev, stream);
+      if (s1 != kOk) return s1;
+      const long long words = (long long)m_total * n;
+      const unsigned grid = (unsigned)std::min<long long>((words / 4 + 255) / 256 + 1, 16);
+      const cudaError_t e = launch(copy_out_f32_kernel, dim3(grid), dim3(256), 0, stream, (const float*)y_dev, ym, words,
+                                   aligned(ym, 16) ? 1 : 0);
+      return e == cudaSuccess ? kOk : kLaunchFailure;
+    }
+  }
+  if (cudaMemcpyAsync(x_dev, x_host, xb, cudaMemcpyHostToDevice, stream) != cudaSuccess) return kLaunchFailure;
   const int32_t s2 = fuelq_qmatmul(ggml_type, m_total, n, k, w, x_dev, y_dev, p,
                                    workspace_bytes - (size_t)(p - (uint8_t*)workspace), stream_v);
   if (s2 != kOk) return s2;
-  if (cudaMemcpyAsync(y_host, y_dev, (size_t)m_total * n * 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess)
-    return kLaunchFailure;
+  if (cudaMemcpyAsync(y_host, y_dev, yb, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return kLaunchFailure;
   return kOk;
 }
 
@@ -1317,20 +1430,8 @@ int32_t make_peer_ctx(const fuelq_peers* peers, int32_t wait_seq, int32_t push_s
   c->wait_ns = (unsigned long long)g_opt.peer_wait_ms * 1000000ull;
   return kOk;
 }
-int32_t make_peer_planes(void* const* act_dst, int64_t k_total, int world, PeerStampedPlanes* out) {
-  if (!act_dst) return kInvalidProblem;
-  for (int q = 0; q < kPeerMaxWorld; ++q) {
-    out->r[q] = StampedPlanes{nullptr, nullptr, nullptr};
-    if (q >= world) continue;
-    if (!act_dst[q]) return kInvalidProblem;
-    if (!aligned(act_dst[q], 16)) return kMisaligned;
-    out->r[q] = stamped_planes(act_dst[q], k_total);
-  }
-  return kOk;
-}
 }  // namespace
 
-size_t fuelq_peer_act_bytes(int64_t k) { return (k > 0 && k % 256 == 0) ? stamped_planes_bytes(k) : 0; }
 size_t fuelq_peer_vec_bytes(int64_t n) { return n > 0 ? (size_t)n * 8 : 0; }
 
 int32_t fuelq_ipc_alloc(size_t bytes, void** dev_ptr, void* handle64) {
@@ -1367,15 +1468,15 @@ int32_t fuelq_ipc_free(void* dev_ptr) {
 }
 
 int32_t fuelq_qmatmul_packed_peer(int32_t ggml_type, int64_t k, int64_t n_local, const void* w, const void* act,
-                                  void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t wait_seq,
-                                  int32_t push_seq, void* stream) {
+                                  void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t push_seq,
+                                  void* stream) {
   const int32_t st = check_problem(ggml_type, 1, n_local, k);
   if (st != kOk) return st;
   if (n_local == 0 || dst_offset < 0) return kInvalidProblem;  // every rank contributes to an exchange point
   if (!w || !act || !dst) return kInvalidProblem;
   if (!aligned(w, 16) || !aligned(act, 16)) return kMisaligned;
   DecodeRegsPeer g;
-  const int32_t sc = make_peer_ctx(peers, wait_seq, push_seq, &g.ctx);
+  const int32_t sc = make_peer_ctx(peers, -1, push_seq, &g.ctx);
   if (sc != kOk) return sc;
   if (g.ctx.push_seq < 0) return kInvalidProblem;
   for (int q = 0; q < kPeerMaxWorld; ++q) {
@@ -1385,20 +1486,59 @@ int32_t fuelq_qmatmul_packed_peer(int32_t ggml_type, int64_t k, int64_t n_local,
     if (!aligned(dst[q], 16)) return kMisaligned;
     g.dst[q] = (uint2*)dst[q] + dst_offset;
   }
-  ActPlanes planes = {};
-  g.act_ll = StampedPlanes{nullptr, nullptr, nullptr};
-  g.act_smem_off = 0;
-  if (g.ctx.wait_seq >= 0) {
-    if (ggml_type != kQ4K && ggml_type != kQ6K) return kNotSupported;  // stamped planes are Q8_K activations
-    g.act_ll = stamped_planes(const_cast<void*>(act), k);
-  } else {
-    planes = act_planes(const_cast<void*>(act), ggml_type, 1, k);
-  }
+  const ActPlanes planes = act_planes(const_cast<void*>(act), ggml_type, 1, k);
   return decode_regs_impl(ggml_type, 1, n_local, k, w, planes, nullptr, (cudaStream_t)stream, &g);
 }
 
-int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, const float* gain, int64_t dim, float eps, void* packed,
-                                   size_t packed_bytes, const fuelq_peers* peers, int32_t wait_seq, void* stream) {
+int32_t fuelq_qmatmul_packed_tree(int32_t ggml_type, int64_t n, int64_t k, const void* w, const void* packed_act, float* y,
+                                  int32_t n_leaves, const int32_t* leaf_blocks, void* stream) {
+  const int32_t st = check_problem(ggml_type, 1, n, k);
+  if (st != kOk) return st;
+  if (n == 0) return kOk;
+  if (!w || !packed_act || !y) return kInvalidProblem;
+  if (!aligned(w, 16) || !aligned(packed_act, 16) || !aligned(y, 4)) return kMisaligned;
+  return decode_tree_impl(ggml_type, n, k, w, act_planes(const_cast<void*>(packed_act), ggml_type, 1, k), y, n_leaves, leaf_blocks,
+                          nullptr, (cudaStream_t)stream);
+}
+
+int32_t fuelq_qmatmul_packed_tree_peer(int32_t ggml_type, int64_t n, int64_t k, const void* w, const void* packed_act,
+                                       void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t push_seq,
+                                       int32_t n_leaves, const int32_t* leaf_blocks, void* stream) {
+  const int32_t st = check_problem(ggml_type, 1, n, k);
+  if (st != kOk) return st;
+  if (n == 0 || dst_offset < 0) return kInvalidProblem;
+  if (!w || !packed_act || !dst) return kInvalidProblem;
+  if (!aligned(w, 16) || !aligned(packed_act, 16)) return kMisaligned;
+  DecodeRegsPeer g;
+  const int32_t sc = make_peer_ctx(peers, -1, push_seq, &g.ctx);
+  if (sc != kOk) return sc;
+  if (g.ctx.push_seq < 0) return kInvalidProblem;
+  for (int q = 0; q < kPeerMaxWorld; ++q) {
+    g.dst[q] = nullptr;
+    if (q >= g.ctx.world) continue;
+    if (!dst[q]) return kInvalidProblem;
+    if (!aligned(dst[q], 16)) return kMisaligned;
+    g.dst[q] = (uint2*)dst[q] + dst_offset;
+  }
+  return decode_tree_impl(ggml_type, n, k, w, act_planes(const_cast<void*>(packed_act), ggml_type, 1, k), nullptr, n_leaves,
+                          leaf_blocks, &g, (cudaStream_t)stream);
+}
+
+int32_t fuelq_add_rmsnorm_q8k_parts(float* x, const float* parts, int32_t n_parts, const float* gain, int64_t dim, float eps,
+                                    void* packed, size_t packed_bytes, void* stream) {
+  if (dim <= 0 || dim % 256 || dim > 8192) return kInvalidProblem;
+  if (n_parts != 1 && n_parts != 2 && n_parts != 4 && n_parts != 8) return kInvalidProblem;
+  if (!x || !gain || !parts) return kInvalidProblem;
+  if (!packed || packed_bytes < act_packed_bytes(kQ4K, 1, dim)) return kWorkspace;
+  if (!aligned(x, 16) || !aligned(gain, 16) || !aligned(parts, 16) || !aligned(packed, 16)) return kMisaligned;
+  const ActPlanes a = act_planes(packed, kQ4K, 1, dim);
+  const cudaError_t e = launch(add_rmsnorm_q8k_parts_kernel, dim3(1), dim3((unsigned)(dim / 256 * 32)), 0, (cudaStream_t)stream, x,
+                               parts, (int)n_parts, gain, (int)dim, eps, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, int32_t n_parts, const float* gain, int64_t dim, float eps,
+                                   void* packed, size_t packed_bytes, const fuelq_peers* peers, int32_t wait_seq, void* stream) {
   if (dim <= 0 || dim % 256 || dim > 8192) return kInvalidProblem;
   if (!x || !gain) return kInvalidProblem;
   if (!packed || packed_bytes < act_packed_bytes(kQ4K, 1, dim)) return kWorkspace;
@@ -1407,57 +1547,11 @@ int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, const float* gai
   const int32_t sc = make_peer_ctx(peers, wait_seq, -1, &c);
   if (sc != kOk) return sc;
   if ((delta != nullptr) != (c.wait_seq >= 0)) return kInvalidProblem;
+  if (delta && n_parts != 1 && n_parts != 2 && n_parts != 4 && n_parts != 8) return kInvalidProblem;
   const ActPlanes a = act_planes(packed, kQ4K, 1, dim);
   const cudaError_t e = launch(add_rmsnorm_q8k_peer_kernel, dim3(1), dim3((unsigned)(dim / 256 * 32)), 0, (cudaStream_t)stream,
-                               x, (const uint2*)delta, gain, (int)dim, eps, (int8_t*)a.qs, (float*)a.d, (int16_t*)a.bsums, c);
-  return e == cudaSuccess ? kOk : kLaunchFailure;
-}
-
-int32_t fuelq_swiglu_q8k_peer(const float* gate, const float* up, int64_t n_local, int64_t col0, int64_t k_total,
-                              void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream) {
-  if (n_local <= 0 || n_local % 256 || col0 < 0 || col0 % 256 || k_total % 256 || col0 + n_local > k_total ||
-      k_total > (1 << 30))
-    return kInvalidProblem;
-  if (!gate || !up) return kInvalidProblem;
-  if (!aligned(gate, 16) || !aligned(up, 16)) return kMisaligned;
-  PeerCtx c;
-  int32_t sc = make_peer_ctx(peers, -1, push_seq, &c);
-  if (sc != kOk) return sc;
-  if (c.push_seq < 0) return kInvalidProblem;
-  PeerStampedPlanes pp;
-  sc = make_peer_planes(act_dst, k_total, c.world, &pp);
-  if (sc != kOk) return sc;
-  const int nb = (int)(n_local / 256);
-  const cudaError_t e = launch(swiglu_q8k_peer_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, gate,
-                               up, nb, (int)(col0 / 256), pp, c);
-  return e == cudaSuccess ? kOk : kLaunchFailure;
-}
-
-int32_t fuelq_attn_decode_q8k_peer(const float* q, const float* kcache, const float* vcache, const int32_t* pos,
-                                   int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale,
-                                   void* workspace, size_t workspace_bytes, int32_t head0, int64_t k_total,
-                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, const fuelq_rope* rope,
-                                   void* stream) {
-  if (head_dim != 128) return kNotSupported;
-  if (n_heads <= 0 || n_heads % 2 || n_kv <= 0 || n_heads % n_kv || max_seq <= 0 || max_seq > 8192) return kInvalidProblem;
-  if (head0 < 0 || head0 % 2 || k_total % 256 || (int64_t)(head0 + n_heads) * 128 > k_total) return kInvalidProblem;
-  if (!q || !kcache || !vcache || !pos) return kInvalidProblem;
-  if (!workspace || workspace_bytes < fuelq_attn_decode_workspace_bytes(n_heads)) return kWorkspace;
-  if (!aligned(q, 16) || !aligned(kcache, 16) || !aligned(vcache, 16) || !aligned(workspace, 16)) return kMisaligned;
-  PeerCtx c;
-  int32_t sc = make_peer_ctx(peers, -1, push_seq, &c);
-  if (sc != kOk) return sc;
-  if (c.push_seq < 0) return kInvalidProblem;
-  PeerStampedPlanes pp;
-  sc = make_peer_planes(act_dst, k_total, c.world, &pp);
-  if (sc != kOk) return sc;
-  AttnRope ar;
-  if (!make_attn_rope(rope, &ar)) return kInvalidProblem;
-  cudaError_t e = launch(attn_partial_kernel, dim3((unsigned)n_heads, kAttnSplits), dim3(256), 0, (cudaStream_t)stream, q,
-                         kcache, vcache, (float*)workspace, (const int*)pos, (int)n_heads, (int)n_kv, (int)max_seq, scale, ar);
-  if (e != cudaSuccess) return kLaunchFailure;
-  e = launch(attn_combine_q8k_peer_kernel, dim3((unsigned)(n_heads / 2)), dim3(32), 0, (cudaStream_t)stream,
-             (const float*)workspace, (int)(head0 / 2), pp, c);
+                               x, (const uint2*)delta, (int)(delta ? n_parts : 0), gain, (int)dim, eps, (int8_t*)a.qs, (float*)a.d,
+                               (int16_t*)a.bsums, c);
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 

@@ -254,8 +254,11 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* part, fl
 // residual add (x += delta, written back), then RMSNorm with gain. kQuant = false stores the f32 row to
 // `out`; kQuant = true (one row) quantizes it into the activation planes. Both forms share every
 // arithmetic step and its order, so they produce the same values.
+// n_parts > 1: the residual delta arrives as n_parts partial vectors (one per GPU of a row-parallel layer, `dim` words
+// apart) and is their sum in the balanced pairwise order ((p0 + p1) + (p2 + p3)) + ... — the top of the summation tree
+// whose lower levels each GPU's tree-ordered mat-vec has already done, so the value is the one-GPU value bit for bit.
 template <bool kQuant, bool kPeer>
-__device__ __forceinline__ void add_rmsnorm_body(float* x, const void* delta_v,
+__device__ __forceinline__ void add_rmsnorm_body(float* x, const void* delta_v, int n_parts,
                                                  const float* gain, float* out, int dim, float eps,
                                                  int8_t* out_qs, float* out_d,
                                                  int16_t* out_bsums, const PeerCtx* pc) {
@@ -270,18 +273,37 @@ __device__ __forceinline__ void add_rmsnorm_body(float* x, const void* delta_v,
     float4* xr = reinterpret_cast<float4*>(x + base);
     float4 v0 = xr[lane], v1 = xr[32 + lane];
     if (delta_v) {
-      float4 d0, d1;
-      if constexpr (kPeer) {
-        // delta arrives from the peers' kernels as stamped pairs (one row)
-        const uint2* dl = reinterpret_cast<const uint2*>(delta_v) + warp * 256;
-        const uint32_t want = peer_stamp(*pc, pc->wait_seq);
-        uint32_t a[4], b[4];
-        peer_load_words2<4, 4>(dl + 4 * lane, dl + 128 + 4 * lane, want, a, b, pc->wait_ns);
-        d0 = make_float4(__uint_as_float(a[0]), __uint_as_float(a[1]), __uint_as_float(a[2]), __uint_as_float(a[3]));
-        d1 = make_float4(__uint_as_float(b[0]), __uint_as_float(b[1]), __uint_as_float(b[2]), __uint_as_float(b[3]));
-      } else {
-        const float4* dr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(delta_v) + base);
-        d0 = dr[lane], d1 = dr[32 + lane];
+      // parts are taken in order and merged like a binary counter: lv0[l] / lv1[l] hold the sum of a complete subtree of
+      // 2^l parts waiting for its sibling
+      float4 lv0[3], lv1[3], d0 = make_float4(0.f, 0.f, 0.f, 0.f), d1 = d0;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (q < n_parts) {
+          float4 c0, c1;
+          if constexpr (kPeer) {
+            // delta arrives from the peers' kernels as stamped pairs (one row per part)
+            const uint2* dl = reinterpret_cast<const uint2*>(delta_v) + (size_t)q * dim + warp * 256;
+            const uint32_t want = peer_stamp(*pc, pc->wait_seq);
+            uint32_t a[4], b[4];
+            peer_load_words2<4, 4>(dl + 4 * lane, dl + 128 + 4 * lane, want, a, b, pc->wait_ns);
+            c0 = make_float4(__uint_as_float(a[0]), __uint_as_float(a[1]), __uint_as_float(a[2]), __uint_as_float(a[3]));
+            c1 = make_float4(__uint_as_float(b[0]), __uint_as_float(b[1]), __uint_as_float(b[2]), __uint_as_float(b[3]));
+          } else {
+            const float4* dr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(delta_v) + (size_t)q * dim + base);
+            c0 = dr[lane], c1 = dr[32 + lane];
+          }
+#pragma unroll
+          for (int l = 0; l < 3; ++l) {
+            if ((q >> l) & 1) {  // a left sibling of this size is waiting: left + right
+              c0.x = lv0[l].x + c0.x, c0.y = lv0[l].y + c0.y, c0.z = lv0[l].z + c0.z, c0.w = lv0[l].w + c0.w;
+              c1.x = lv1[l].x + c1.x, c1.y = lv1[l].y + c1.y, c1.z = lv1[l].z + c1.z, c1.w = lv1[l].w + c1.w;
+            } else {
+              lv0[l] = c0, lv1[l] = c1;
+              break;
+            }
+          }
+          d0 = c0, d1 = c1;  // after the last part (n_parts a power of two) this is the whole tree
+        }
       }
       v0.x += d0.x, v0.y += d0.y, v0.z += d0.z, v0.w += d0.w;
       v1.x += d1.x, v1.y += d1.y, v1.z += d1.z, v1.w += d1.w;
@@ -317,39 +339,22 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* x, const float
                                                            const float* gain, float* out, int dim,
                                                            float eps, int8_t* out_qs, float* out_d,
                                                            int16_t* out_bsums) {
-  add_rmsnorm_body<kQuant, false>(x, delta, gain, out, dim, eps, out_qs, out_d, out_bsums, nullptr);
+  add_rmsnorm_body<kQuant, false>(x, delta, 1, gain, out, dim, eps, out_qs, out_d, out_bsums, nullptr);
+}
+
+// quantizing form whose residual delta is the pairwise sum of n_parts partial vectors [n_parts][dim]
+__global__ void __launch_bounds__(1024) add_rmsnorm_q8k_parts_kernel(float* x, const float* parts, int n_parts,
+                                                                     const float* gain, int dim, float eps,
+                                                                     int8_t* out_qs, float* out_d, int16_t* out_bsums) {
+  add_rmsnorm_body<true, false>(x, parts, n_parts, gain, nullptr, dim, eps, out_qs, out_d, out_bsums, nullptr);
 }
 
 // quantizing form whose residual delta (stamped pairs) arrives through exchange point pc.wait_seq
-__global__ void __launch_bounds__(1024) add_rmsnorm_q8k_peer_kernel(float* x, const uint2* delta,
+__global__ void __launch_bounds__(1024) add_rmsnorm_q8k_peer_kernel(float* x, const uint2* delta, int n_parts,
                                                                     const float* gain, int dim, float eps,
                                                                     int8_t* out_qs, float* out_d,
                                                                     int16_t* out_bsums, const PeerCtx pc) {
-  add_rmsnorm_body<true, true>(x, delta, gain, nullptr, dim, eps, out_qs, out_d, out_bsums, &pc);
-}
-
-// Stamped activation planes of every rank, for producers that quantize their slice and store it everywhere.
-struct PeerStampedPlanes {
-  StampedPlanes r[kPeerMaxWorld];
-};
-
-// One warp stores its quantized 256-block `blk` as stamped pairs into every rank's planes.
-__device__ __forceinline__ void q8k_block_store_stamped(const Q8KLaneBlock& b, int lane, int blk, const PeerStampedPlanes& out,
-                                                        int world, uint32_t stamp) {
-  // 16-sums as int16 pairs: word j < 4 holds sums 2j, 2j+1 (lanes 8j, 8j+4, first half), word 4+j the second half
-  const uint32_t lo0 = (uint32_t)b.s0 & 0xffffu, lo1 = (uint32_t)b.s1 & 0xffffu;
-  const uint32_t hi0 = (uint32_t)__shfl_down_sync(0xffffffffu, b.s0, 4) & 0xffffu;
-  const uint32_t hi1 = (uint32_t)__shfl_down_sync(0xffffffffu, b.s1, 4) & 0xffffu;
-  for (int q = 0; q < world; ++q) {
-    const StampedPlanes& sp = out.r[q];
-    st_pair(sp.qs + (size_t)blk * 64 + lane, b.p0, stamp);
-    st_pair(sp.qs + (size_t)blk * 64 + 32 + lane, b.p1, stamp);
-    if ((lane & 7) == 0) {
-      st_pair(sp.bs + (size_t)blk * 8 + (lane >> 3), lo0 | (hi0 << 16), stamp);
-      st_pair(sp.bs + (size_t)blk * 8 + 4 + (lane >> 3), lo1 | (hi1 << 16), stamp);
-    }
-    if (lane == 0) st_pair(sp.d + blk, __float_as_uint(b.d), stamp);
-  }
+  add_rmsnorm_body<true, true>(x, delta, n_parts, gain, nullptr, dim, eps, out_qs, out_d, out_bsums, &pc);
 }
 
 // silu(gate) * up, quantized; one warp per 256 elements
@@ -395,53 +400,6 @@ __global__ void __launch_bounds__(32) attn_combine_q8k_kernel(const float* part,
     for (int i = 0; i < 4; ++i) e[4 * hsel + i] = num[i] / den;
   }
   q8k_block_from_regs(e, lane, blk, out_qs, out_d, out_bsums);
-}
-
-// Tensor-parallel forms of the two kernels above: this rank's blocks [blk0, blk0 + n_blocks) of the full
-// vector are quantized once and stored, as stamped pairs of exchange point pc.push_seq, into every rank's planes.
-__global__ void __launch_bounds__(256) swiglu_q8k_peer_kernel(const float* gate, const float* up,
-                                                              int n_blocks, int blk0, const PeerStampedPlanes out,
-                                                              const PeerCtx pc) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const uint32_t stamp = peer_stamp(pc, pc.push_seq);
-  const int lane = threadIdx.x & 31;
-  const int blk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (blk >= n_blocks) return;
-  const float4* gp = reinterpret_cast<const float4*>(gate + (size_t)blk * 256);
-  const float4* up4 = reinterpret_cast<const float4*>(up + (size_t)blk * 256);
-  const float4 a0 = gp[lane], a1 = gp[32 + lane], b0 = up4[lane], b1 = up4[32 + lane];
-  const float g[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-  const float u[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-  float e[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) e[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
-  q8k_block_store_stamped(q8k_block_quantize(e, lane), lane, blk0 + blk, out, pc.world, stamp);
-}
-
-__global__ void __launch_bounds__(32) attn_combine_q8k_peer_kernel(const float* part, int blk0,
-                                                                   const PeerStampedPlanes out, const PeerCtx pc) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const uint32_t stamp = peer_stamp(pc, pc.push_seq);
-  const int lane = threadIdx.x, blk = blockIdx.x;
-  float e[8];
-#pragma unroll
-  for (int hsel = 0; hsel < 2; ++hsel) {
-    const float* p = part + (size_t)(2 * blk + hsel) * kAttnSplits * kAttnPartStride;
-    float M = -INFINITY;
-    for (int s = 0; s < kAttnSplits; ++s) M = fmaxf(M, p[s * kAttnPartStride + 128]);
-    float num[4] = {0, 0, 0, 0}, den = 0.f;
-    for (int s = 0; s < kAttnSplits; ++s) {
-      const float w = expf(p[s * kAttnPartStride + 128] - M);
-      const float4 v = reinterpret_cast<const float4*>(p + s * kAttnPartStride)[lane];
-      num[0] += w * v.x, num[1] += w * v.y, num[2] += w * v.z, num[3] += w * v.w;
-      den += w * p[s * kAttnPartStride + 129];
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) e[4 * hsel + i] = num[i] / den;
-  }
-  q8k_block_store_stamped(q8k_block_quantize(e, lane), lane, blk0 + blk, out, pc.world, stamp);
 }
 
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* gate, const float* up,

@@ -50,23 +50,17 @@ struct MmaBatchParams {
   int n, k, row_bytes;
   int n_wgroups;         // consumer warp groups (1, 2 or 4): group g takes stages g, g + n_wgroups, ... and its warps split k
   int num_stages, stage_stride;
-  int wstride;           // bytes between staged weight rows (chunk bytes + skew room + bank padding)
+  int wstride;           // bytes between staged copies (rows_per_copy rows' bytes + skew room + bank padding)
+  int rows_per_copy;     // 1, 2 or 4 consecutive rows per bulk copy (more than 1 only when whole rows are staged)
   int act_off, part_off; // shared-memory offsets of the activation area and of the partial-sum area
   int kc_blocks;         // 256-element blocks of k per sweep
-#ifdef FQ_TRACE
-  unsigned long long* trace;
-#endif
 };
 
-#ifdef FQ_TRACE
-#define MB_TR(i) do { if (p.trace && threadIdx.x == (i >= 100 ? 32 * kMbConsumerWarps : 0)) p.trace[(size_t)blockIdx.x * 64 + ((i) % 100)] = peer_now_ns(); } while (0)
-#else
-#define MB_TR(i) do {} while (0)
-#endif
 
 struct MmaBatchHeader {
   uint64_t full[kMbMaxStages];
   uint64_t empty[kMbMaxStages];
+  uint64_t acts;      // the first sweep's activation rows have landed (bulk copies issued by the producer)
   volatile int dead;  // a bounded wait expired somewhere in this block
 };
 
@@ -79,27 +73,29 @@ __device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 // c = A(16x32 u8, weights) * B(32x8 s8, activations); fresh accumulators
+// (the MMA wrappers are pure functions of their operands: not volatile, so the compiler may schedule them among the
+// surrounding arithmetic; the shared-memory loads stay volatile and keep their order against the barriers)
 __device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
 __device__ __forceinline__ void mma_s8s8_k32(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
 __device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
       : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
       : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
 // accumulating form, s8 x s8
 __device__ __forceinline__ void mma_s8s8_k16_acc(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a0), "r"(a1), "r"(b0));
@@ -149,9 +145,15 @@ __host__ __device__ inline MbActLayout mb_act_layout(int kc_blocks, int rows) {
 struct MbCtx {
   uint32_t tile_s;   // shared address of the tile's first weight row (chunk start)
   uint32_t act_s;    // shared address of the activation area
-  int wstride;
+  int wstride;       // bytes between staged copies
+  int rpc_shift;     // log2(rows per copy)
+  int row_bytes;     // bytes between the rows of one copy
   int lane, gid, tig;
   MbActLayout L;
+  // byte offset of tile row i from tile_s (before the copy's skew)
+  __device__ __forceinline__ uint32_t row_off(int i) const {
+    return (uint32_t)(i >> rpc_shift) * (uint32_t)wstride + (uint32_t)(i & ((1 << rpc_shift) - 1)) * (uint32_t)row_bytes;
+  }
 };
 
 // ------------------------------------------------------------------------------------------------ Q4_K
@@ -183,8 +185,8 @@ struct MbQ4K {
   template <int MT>
   __device__ __forceinline__ static void block_step(const MbCtx& cx, int b, uint32_t, uint32_t, float (&facc)[MT][4]) {
     const uint32_t blk = (uint32_t)b * 144u;
-    const uint4 h0 = lds128(cx.tile_s + (uint32_t)cx.gid * cx.wstride + blk);
-    const uint4 h1 = lds128(cx.tile_s + (uint32_t)(cx.gid + 8) * cx.wstride + blk);
+    const uint4 h0 = lds128(cx.tile_s + cx.row_off(cx.gid) + blk);
+    const uint4 h1 = lds128(cx.tile_s + cx.row_off(cx.gid + 8) + blk);
     // eight 6-bit scales / mins per row as bytes of two words (get_scale_min_k4, fuel-quantized/src/utils.rs:50-60)
     const uint32_t sc0[2] = {h0.y & 0x3f3f3f3fu, (h0.w & 0x0f0f0f0fu) | (((h0.y >> 6) & 0x03030303u) << 4)};
     const uint32_t mn0[2] = {h0.z & 0x3f3f3f3fu, ((h0.w >> 4) & 0x0f0f0f0fu) | (((h0.z >> 6) & 0x03030303u) << 4)};
@@ -192,31 +194,44 @@ struct MbQ4K {
     const uint32_t mn1[2] = {h1.z & 0x3f3f3f3fu, ((h1.w >> 4) & 0x0f0f0f0fu) | (((h1.z >> 6) & 0x03030303u) << 4)};
     // ldmatrix addresses: weights, rows (lane & 7) + 8 * bit 3, byte column 16 * bit 4 of the 32 bytes of a nibble group;
     // activations, rows (lane & 7), the four 16-byte pieces of the group's 64 elements
-    const uint32_t wq = cx.tile_s + (uint32_t)((cx.lane & 7) + 8 * ((cx.lane >> 3) & 1)) * cx.wstride + blk + 16u + 16u * (cx.lane >> 4);
+    const uint32_t wq = cx.tile_s + cx.row_off((cx.lane & 7) + 8 * ((cx.lane >> 3) & 1)) + blk + 16u + 16u * (cx.lane >> 4);
     const uint32_t aq = cx.act_s + (uint32_t)(cx.lane & 7) * cx.L.astride + (uint32_t)b * 256u + 16u * (cx.lane >> 3);
     int Slo[MT][4], Shi[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) Slo[mt][i] = 0, Shi[mt][i] = 0;
+    // Four groups of 64 elements (low nibbles = sub-block 2g, high nibbles = 2g + 1). The fragment loads of group g + 1 are
+    // issued before the arithmetic of group g, and a group's MMAs all issue before the first use of their results, so a
+    // warp pays the load and tensor-pipe latencies once per group instead of once per instruction.
+    uint32_t r[2][4], q[2][MT][4];
+    ldmatrix_x4(r[0], wq);
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {  // 64 elements: low nibbles = sub-block 2g, high nibbles = 2g + 1
-      uint32_t r[4], alo[4], ahi[4];
-      ldmatrix_x4(r, wq + 32u * g);
+    for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(q[0][mt], aq + (uint32_t)(8 * mt) * cx.L.astride);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) alo[i] = r[i] & 0x0f0f0f0fu, ahi[i] = r[i] & 0xf0f0f0f0u;
+    for (int g = 0; g < 4; ++g) {
+      const int cur = g & 1, nxt = cur ^ 1;
+      if (g < 3) {
+        ldmatrix_x4(r[nxt], wq + 32u * (g + 1));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(q[nxt][mt], aq + (uint32_t)(8 * mt) * cx.L.astride + 64u * (g + 1));
+      }
+      uint32_t alo[4], ahi[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) alo[i] = r[cur][i] & 0x0f0f0f0fu, ahi[i] = r[cur][i] & 0xf0f0f0f0u;
+      int cl[MT][4], ch[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma_u8s8_k32(cl[mt], alo, q[cur][mt][0], q[cur][mt][1]);
+        mma_u8s8_k32(ch[mt], ahi, q[cur][mt][2], q[cur][mt][3]);  // 16 x the high-nibble dots
+      }
       const int sh = 16 * (g & 1);
       const int s0l = (int)((sc0[g >> 1] >> sh) & 0xff), s0h = (int)((sc0[g >> 1] >> (sh + 8)) & 0xff);
       const int s1l = (int)((sc1[g >> 1] >> sh) & 0xff), s1h = (int)((sc1[g >> 1] >> (sh + 8)) & 0xff);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        uint32_t q[4];
-        ldmatrix_x4(q, aq + (uint32_t)(8 * mt) * cx.L.astride + 64u * g);
-        int c[4];
-        mma_u8s8_k32(c, alo, q[0], q[1]);
-        Slo[mt][0] += c[0] * s0l, Slo[mt][1] += c[1] * s0l, Slo[mt][2] += c[2] * s1l, Slo[mt][3] += c[3] * s1l;
-        mma_u8s8_k32(c, ahi, q[2], q[3]);  // 16 x the high-nibble dots
-        Shi[mt][0] += c[0] * s0h, Shi[mt][1] += c[1] * s0h, Shi[mt][2] += c[2] * s1h, Shi[mt][3] += c[3] * s1h;
+        Slo[mt][0] += cl[mt][0] * s0l, Slo[mt][1] += cl[mt][1] * s0l, Slo[mt][2] += cl[mt][2] * s1l, Slo[mt][3] += cl[mt][3] * s1l;
+        Shi[mt][0] += ch[mt][0] * s0h, Shi[mt][1] += ch[mt][1] * s0h, Shi[mt][2] += ch[mt][2] * s1h, Shi[mt][3] += ch[mt][3] * s1h;
       }
     }
     const float d0 = h2f_bits(h0.x & 0xffffu), dm0 = h2f_bits(h0.x >> 16);
@@ -260,8 +275,8 @@ struct MbQ8_0 {
   }
   template <int MT>
   __device__ __forceinline__ static void block_step(const MbCtx& cx, int b, uint32_t, uint32_t, float (&facc)[MT][4]) {
-    const uint32_t r0 = cx.tile_s + (uint32_t)cx.gid * cx.wstride + (uint32_t)b * 272u;
-    const uint32_t r1 = r0 + 8u * cx.wstride;
+    const uint32_t r0 = cx.tile_s + cx.row_off(cx.gid) + (uint32_t)b * 272u;
+    const uint32_t r1 = cx.tile_s + cx.row_off(cx.gid + 8) + (uint32_t)b * 272u;
     // B fragments: MT == 2: rows (lane & 7) + 8 * bit 4, byte column 16 * bit 3; MT == 1: lanes 0-15 address rows and columns
     const uint32_t aq = cx.act_s + (uint32_t)((cx.lane & 7) + (MT == 2 ? 8 * (cx.lane >> 4) : 0)) * cx.L.astride + (uint32_t)b * 256u +
                         16u * ((cx.lane >> 3) & 1);
@@ -324,8 +339,8 @@ struct MbQ6K {
   // skew0 / skew1: byte offsets (0..14, even) of rows gid and gid + 8 inside their staged slots
   template <int MT>
   __device__ __forceinline__ static void block_step(const MbCtx& cx, int b, uint32_t skew0, uint32_t skew1, float (&facc)[MT][4]) {
-    const uint32_t r0 = cx.tile_s + (uint32_t)cx.gid * cx.wstride + skew0 + (uint32_t)b * 210u;
-    const uint32_t r1 = cx.tile_s + (uint32_t)(cx.gid + 8) * cx.wstride + skew1 + (uint32_t)b * 210u;
+    const uint32_t r0 = cx.tile_s + cx.row_off(cx.gid) + skew0 + (uint32_t)b * 210u;
+    const uint32_t r1 = cx.tile_s + cx.row_off(cx.gid + 8) + skew1 + (uint32_t)b * 210u;
     // scales: 16 signed bytes per row; this lane's word holds groups 4 tig .. 4 tig + 3 (the A fragment of the correction)
     const uint32_t scw0 = lds_u32_2b_addr(r0 + 192u + 4u * cx.tig), scw1 = lds_u32_2b_addr(r1 + 192u + 4u * cx.tig);
     uint32_t sc0[4], sc1[4];  // all 16, for the per-group scaling
@@ -433,16 +448,16 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
       mbar_init(&hd->full[s], 1);
       mbar_init(&hd->empty[s], GW);
     }
+    mbar_init(&hd->acts, 1);
     hd->dead = 0;
     mbar_init_fence();
   }
   __syncthreads();
   pdl_launch_dependents();
-  MB_TR(0);
   // Row ranges and activations come from the preceding kernels; the weights do not, so with one group of fixed size
   // (a dense batch) the producer starts streaming before the predecessor has finished.
-  if (warp != kMbConsumerWarps || p.offsets) pdl_wait();
-  MB_TR(1);
+  const bool early = warp == kMbConsumerWarps && !p.offsets;  // the producer of a dense batch
+  if (!early) pdl_wait();
   const int m_begin = p.offsets ? p.offsets[grp] : 0;
   const int m_count = p.offsets ? p.offsets[grp + 1] - m_begin : p.fixed_rows;
   if (m_count <= 0 || n_iter <= 0) return;  // nothing is streamed for a group without rows
@@ -451,8 +466,12 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
   const int64_t base = (int64_t)grp * p.group_bytes;
 
   if (warp == kMbConsumerWarps) {
-    // ---------------- producer: one bulk copy per weight row, a lane per row
+    // ---------------- producer: one bulk copy per group of rows_per_copy consecutive weight rows, a lane per copy.
+    // Issuing a bulk copy costs ~60-90 ns whatever its size, so one copy per 1-2 KB row caps the stream well below HBM
+    // speed; when whole rows are staged (no k chunks) consecutive rows are contiguous in memory and travel together,
+    // at the price of a rows_per_copy-way bank conflict on the weight fragment loads, which are few.
     const int64_t tma_limit = p.total_bytes & ~(int64_t)15;
+    const int RPC = p.rows_per_copy;
     bool ok = true;
     int it = 0, kc = 0, issued = 0;
     for (int g = 0; g < total_iter; ++g) {
@@ -468,13 +487,14 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
       const int row0 = r_begin + it * 16;
       const int rows_here = ((row0 + 16 < r_end) ? row0 + 16 : r_end) - row0;
       const int cb0 = kc * KC, cbn = (nblk - cb0 < KC) ? nblk - cb0 : KC;  // this sweep's blocks of every row
-      // byte range of a row's chunk, widened to 16-byte boundaries (the consumer re-derives the skew)
+      // byte range of a copy (rows lane * RPC ..), widened to 16-byte boundaries (the consumer re-derives the skew)
       uint32_t my_bytes = 0;
       int64_t a0 = 0;
       uint8_t* dst = nullptr;
-      if (lane < rows_here) {
-        const int64_t b0 = base + (int64_t)(row0 + lane) * p.row_bytes + (int64_t)cb0 * F::kBytes256;
-        const int64_t b1 = b0 + (int64_t)cbn * F::kBytes256;
+      if (lane * RPC < rows_here) {
+        const int nr = rows_here - lane * RPC < RPC ? rows_here - lane * RPC : RPC;
+        const int64_t b0 = base + (int64_t)(row0 + lane * RPC) * p.row_bytes + (int64_t)cb0 * F::kBytes256;
+        const int64_t b1 = b0 + (int64_t)(nr - 1) * p.row_bytes + (int64_t)cbn * F::kBytes256;
         a0 = b0 & ~(int64_t)15;
         int64_t a1 = (b1 + 15) & ~(int64_t)15;
         if (a1 > tma_limit) a1 = tma_limit;
@@ -496,7 +516,19 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
       }
       __syncwarp();
       if (my_bytes) bulk_g2s(dst, p.w + a0, my_bytes, &hd->full[s]);
-      if (g < 16) MB_TR(140 + g);
+      if (g == 0) {
+        // The first sweep's activation rows, one bulk copy per row, right behind the first weight tile: requested any
+        // later they would queue behind every weight copy in flight (the rows of later sweeps are staged by the consumers).
+        if (early) pdl_wait();
+        const int ac0 = m_count < kActRows ? m_count : kActRows;
+        const int cbn0 = nblk < KC ? nblk : KC;
+        const MbActLayout L0 = mb_act_layout<F>(KC, kActRows);
+        if (lane == 0) mbar_arrive_expect_tx(&hd->acts, (uint32_t)ac0 * (uint32_t)cbn0 * 256u);
+        __syncwarp();
+        if (lane < ac0)
+          bulk_g2s(smem_raw + p.act_off + (size_t)lane * L0.astride, p.act.qs + (size_t)(m_begin + lane) * p.k, (uint32_t)cbn0 * 256u,
+                   &hd->acts);
+      }
       issued = g + 1;
       if (++it == n_iter) {
         it = 0;
@@ -520,6 +552,8 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
   MbCtx cx;
   cx.lane = lane, cx.gid = lane >> 2, cx.tig = lane & 3;
   cx.wstride = p.wstride;
+  cx.rpc_shift = p.rows_per_copy == 4 ? 2 : p.rows_per_copy == 2 ? 1 : 0;
+  cx.row_bytes = p.row_bytes;
   cx.L = mb_act_layout<F>(KC, kActRows);
   cx.act_s = smem_u32(act_area);
   bool dead = false;  // uniform within a warp group
@@ -539,13 +573,19 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
         constexpr int kTpr = nt_const / kActRows;
         const int r = t / kTpr, c0 = t - r * kTpr;
         const int q16 = cbn * 16;  // 16-byte pieces per row
-        const uint4* src = reinterpret_cast<const uint4*>(p.act.qs + (size_t)(a0 + (r < ac ? r : 0)) * p.k + (size_t)cb0 * 256);
-        uint4* dstq = reinterpret_cast<uint4*>(act_area + (size_t)r * cx.L.astride);
-        for (int c = c0; c < q16; c += kTpr) dstq[c] = r < ac ? src[c] : make_uint4(0, 0, 0, 0);
+        const bool by_producer = pass == 0 && kc == 0;  // rows < ac arrive by bulk copy (see the producer)
+        if (!by_producer || r >= ac) {
+          const uint4* src = reinterpret_cast<const uint4*>(p.act.qs + (size_t)(a0 + (r < ac ? r : 0)) * p.k + (size_t)cb0 * 256);
+          uint4* dstq = reinterpret_cast<uint4*>(act_area + (size_t)r * cx.L.astride);
+          for (int c = c0; c < q16; c += kTpr) dstq[c] = r < ac ? src[c] : make_uint4(0, 0, 0, 0);
+        }
         F::stage_aux(p.act, p.k, a0, ac, kActRows, cb0, cbn, act_area, cx.L, t, nt);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(32 * kMbConsumerWarps) : "memory");
-      MB_TR(2);
+      if (pass == 0 && kc == 0 && !dead && !mbar_wait_bounded(&hd->acts, 0)) {
+        record_dev_error(kErrFullWait);
+        hd->dead = 1;  // every group sees it at its next barrier
+      }
 
       for (int it = gi; it < n_iter && !dead; it += NG) {
         const int g = g_base + it, s = g % S;
@@ -555,7 +595,6 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
           hd->dead = 1;
           bad = true;
         }
-        if (it < 8) MB_TR(8 + 4 * it);
         const int row0 = r_begin + it * 16;
         const int rows_here = ((row0 + 16 < r_end) ? row0 + 16 : r_end) - row0;
         float facc[MT][4];
@@ -567,7 +606,9 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
           cx.tile_s = smem_u32(stages) + (uint32_t)s * p.stage_stride;
           uint32_t skew0 = 0, skew1 = 0;
           if (!F::kRowsAligned) {
-            const int64_t c0 = base + (int64_t)(row0 + cx.gid) * p.row_bytes + (int64_t)cb0 * F::kBytes256;
+            // the skew of a staged copy is that of its first row
+            const int first = cx.gid & ~(p.rows_per_copy - 1);
+            const int64_t c0 = base + (int64_t)(row0 + first) * p.row_bytes + (int64_t)cb0 * F::kBytes256;
             skew0 = (uint32_t)(c0 & 15);
             skew1 = (uint32_t)((c0 + 8 * (int64_t)p.row_bytes) & 15);
           }
@@ -579,9 +620,7 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int i = 0; i < 4; ++i) my[(mt * 4 + i) * 32 + lane] = facc[mt][i];
-        if (it < 8) MB_TR(9 + 4 * it);
         dead = bar_or(2 + gi, gnt, bad || hd->dead != 0);
-        if (it < 8) MB_TR(10 + 4 * it);
         if (!dead) {
           // slot = (mt * 4 + i) * 32 + lane of the accumulator fragment layout
           for (int slot = gt; slot < MT * 128; slot += gnt) {
@@ -600,11 +639,9 @@ __global__ void __launch_bounds__(kMbThreads, 1) mma_batch_kernel(const MmaBatch
         asm volatile("bar.sync %0, %1;" ::"r"(2 + gi), "r"(gnt) : "memory");  // partials consumed
         __syncwarp();
         if (lane == 0) mbar_arrive(&hd->empty[s]);
-        if (it < 8) MB_TR(11 + 4 * it);
       }
     }
   }
-  MB_TR(3);
 }
 
 }  // namespace fq

@@ -114,56 +114,4 @@ __device__ __forceinline__ void peer_load_words(const uint2* src, uint32_t want,
   peer_load_words2<NW, 0>(src, src, want, out, none, limit_ns);
 }
 
-// n_words words (even count, 16-byte aligned source, 8-byte aligned destination) from a stamped buffer into
-// plain words at dst (shared or global), by `nthreads` cooperating threads of which this is thread t. Each
-// thread polls its own pairs; the caller synchronizes the threads afterwards.
-__device__ __forceinline__ void peer_copy_words(const uint2* src, uint32_t* dst, int n_words, uint32_t want, int t,
-                                                int nthreads, unsigned long long limit_ns) {
-  for (int i = t; i < n_words / 2; i += nthreads) {
-    PeerPoll poll(limit_ns);
-    for (;;) {
-      const uint4 v = ld_pair2(src + 2 * i);
-      if ((((v.y ^ want) | (v.w ^ want)) == 0u) || !poll.again()) {
-        *reinterpret_cast<uint2*>(dst + 2 * i) = make_uint2(v.x, v.z);
-        break;
-      }
-    }
-  }
-}
-// same for any count, one pair at a time
-__device__ __forceinline__ void peer_copy_words1(const uint2* src, uint32_t* dst, int n_words, uint32_t want, int t,
-                                                 int nthreads, unsigned long long limit_ns) {
-  for (int i = t; i < n_words; i += nthreads) {
-    PeerPoll poll(limit_ns);
-    for (;;) {
-      const uint2 v = ld_pair(src + i);
-      if (v.y == want || !poll.again()) {
-        dst[i] = v.x;
-        break;
-      }
-    }
-  }
-}
-
-// Stamped form of the Q8_K activation planes of a k-wide vector, as laid out in a destination buffer:
-// qs words [k/4], then 16-sums as int16 pairs [k/32], then block scales [k/256]; each part 256-byte aligned.
-struct StampedPlanes {
-  uint2* qs;
-  uint2* bs;
-  uint2* d;
-};
-__host__ __device__ inline size_t stamped_planes_bytes(int64_t k) {
-  return align_up((size_t)(k / 4) * 8, 256) + align_up((size_t)(k / 32) * 8, 256) + align_up((size_t)(k / 256) * 8, 256);
-}
-__host__ __device__ inline StampedPlanes stamped_planes(void* base, int64_t k) {
-  StampedPlanes s;
-  uint8_t* p = (uint8_t*)base;
-  s.qs = (uint2*)p;
-  p += align_up((size_t)(k / 4) * 8, 256);
-  s.bs = (uint2*)p;
-  p += align_up((size_t)(k / 32) * 8, 256);
-  s.d = (uint2*)p;
-  return s;
-}
-
 }  // namespace fq

@@ -101,9 +101,13 @@ __device__ __forceinline__ void q8k_block_from_regs(const float (&e)[8], int lan
 template <bool kRefLayout>
 __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* x, int64_t n_blocks,
                                                            uint8_t* out_ref, int8_t* out_qs,
-                                                           float* out_d, int16_t* out_bsums) {
+                                                           float* out_d, int16_t* out_bsums, unsigned* zero_word,
+                                                           int early_x) {
+  // early_x: x does not come from an earlier kernel of the stream (host data, final when the call was made), so it is
+  // loaded before the wait for the predecessors and only the stores are ordered after them: a slow read (host memory
+  // over PCIe) then runs beside the previous kernels.
   pdl_launch_dependents();
-  pdl_wait();
+  if (!early_x) pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (blk >= n_blocks) return;
@@ -111,6 +115,8 @@ __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* x, int64
   const float4 v0 = src[lane];       // elements 4*lane .. 4*lane+3
   const float4 v1 = src[32 + lane];  // elements 128 + 4*lane ..
   const float e[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  if (early_x) pdl_wait();
+  if (zero_word && blockIdx.x == 0 && threadIdx.x == 0) *zero_word = 0u;  // a counter the next kernel starts from
 
   // first-max-wins scan, in index order within the lane
   float amax = 0.f, smax = 0.f;
@@ -190,9 +196,10 @@ __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* x, int64
 template <bool kRefLayout>
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* x, int64_t n_groups /* of 256 */,
                                                             int64_t n_blocks32, uint8_t* out_ref,
-                                                            int8_t* out_qs, float* out_d) {
+                                                            int8_t* out_qs, float* out_d, unsigned* zero_word,
+                                                            int early_x) {
   pdl_launch_dependents();
-  pdl_wait();
+  if (!early_x) pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t grp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (grp >= n_groups) return;
@@ -205,6 +212,8 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* x, int6
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4 v0 = ok0 ? src[lane] : z;
   const float4 v1 = ok1 ? src[32 + lane] : z;
+  if (early_x) pdl_wait();
+  if (zero_word && blockIdx.x == 0 && threadIdx.x == 0) *zero_word = 0u;
   float a0 = fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w)));
   float a1 = fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w)));
 #pragma unroll

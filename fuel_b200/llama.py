@@ -4,18 +4,21 @@ Model glue in the shape of the reference's (fuel-core/src/lazy.rs:7363-7447: RMS
 rotate-half RoPE -> attention over an f32 KV cache -> o -> residual -> RMSNorm -> SwiGLU FFN ->
 residual; greedy pick = last maximal index), every op one call into libfuelq.so.
 
-Tensor parallelism, one process per GPU: every linear is split along its OUTPUT rows (whole weight
-rows, no block is cut) and the pieces are put back with an all-gather; heads are split the same
-way, so attention is local. Nothing is ever summed across ranks, which makes every value — and so
-every greedy token — bit-identical for 1, 2, 4 or 8 GPUs by construction. The price is four small
-all-gathers per layer instead of the usual two all-reduces.
+Tensor parallelism, one process per GPU, split as the reference's fuel-parallel does
+(fuel-parallel/src/tensor_parallel.rs:283-343): q/k/v, gate/up and the output head are COLUMN-parallel (a rank
+holds whole weight rows: its heads, its FFN channels, its slice of the vocabulary), o and down are ROW-parallel
+(a rank holds its k columns of every row, the columns its own attention heads / FFN channels feed) and their
+partial results are summed across ranks — one exchange per row-parallel layer, two per transformer layer.
 
-Two ways to do those gathers: comm="nccl" calls the library all-gather between the kernels (the
-baseline), comm="peer" does the exchange inside the kernels themselves: the mat-vec, the attention
-merge and the SwiGLU kernel store their slice straight into every GPU's buffer over NVLink and stamp
-a flag, and the next kernel polls its own flags before it reads (include/fuelq.h, fuelq_*_peer).
-The peer form also keeps the fused activation quantizers, so a layer is the same eleven launches as
-on one GPU.
+That sum follows one fixed tree at every GPU count, so every value — and every greedy token — has the same
+bits on 1, 2, 4 or 8 GPUs: the k axis of a row-parallel layer is cut into eight leaves of whole 256-blocks
+(leaf_split), a rank owns an aligned group of 8 / world leaves, its mat-vec sums its leaves pairwise
+(fuelq_qmatmul_packed_tree), and the consumer adds the ranks' vectors pairwise in rank order
+(fuelq_add_rmsnorm_q8k_peer / _parts). One GPU runs the same tree over all eight leaves.
+
+Two ways to move the partial vectors: comm="nccl" all-gathers them with the library between the kernels (the
+baseline), comm="peer" has the mat-vec kernel store its vector straight into every GPU's buffer over NVLink
+as stamped pairs, and the consuming norm kernel polls its own buffer (include/fuelq.h, fuelq_*_peer).
 """
 from __future__ import annotations
 
@@ -86,6 +89,22 @@ def shard_range(total: int, world: int, rank: int, unit: int = 1):
     q, rem = divmod(blocks, world)
     lo = rank * q + min(rank, rem)
     return lo * unit, (lo + q + (1 if rank < rem else 0)) * unit
+
+
+def leaf_split(n_blocks: int) -> list:
+    """The eight leaves of a row-parallel layer's k axis, in 256-element blocks: halve, floor on the left,
+    three times (43 -> 21 | 22 -> 10, 11 | 11, 11 -> 5,5, 5,6, 5,6, 5,6). Leaves may be empty for a short axis."""
+    def rec(n, depth):
+        return [n] if depth == 0 else rec(n // 2, depth - 1) + rec(n - n // 2, depth - 1)
+    return rec(n_blocks, 3)
+
+
+def rank_leaves(n_blocks: int, world: int, rank: int):
+    """(first block, list of leaf sizes) of the aligned group of 8 / world leaves that `rank` owns."""
+    assert world in (1, 2, 4, 8)
+    leaves = leaf_split(n_blocks)
+    per = 8 // world
+    return sum(leaves[:rank * per]), leaves[rank * per:(rank + 1) * per]
 
 
 class _RawCuda:
@@ -311,30 +330,55 @@ class _Linear:
                                        out.data_ptr(), stream), "fuelq_qmatmul_packed")
 
 
+class _RowParallel(_Linear):
+    """This rank's k columns [first_block * 256, ...) of every row of a quantized [n, k_total] weight, repacked
+    contiguous, with the sizes of the leaves it covers (row-parallel layer; summed by the fixed tree)."""
+
+    def __init__(self, dtype: T, full_rows: torch.Tensor, n: int, k_total: int, first_block: int, leaves):
+        import ctypes
+        bb = dtype.type_size()
+        nb = sum(leaves)
+        slab = full_rows.view(n, k_total // 256, bb)[:, first_block:first_block + nb].contiguous().view(-1)
+        super().__init__(dtype, slab, n, nb * 256)
+        self.n_leaves = len(leaves)
+        self.leaves = (ctypes.c_int32 * 8)(*leaves)
+
+    def matvec_tree(self, packed: torch.Tensor, out: torch.Tensor, stream: int) -> None:
+        _check(_L.fuelq_qmatmul_packed_tree(int(self.dtype), self.n, self.k, self.blocks.data_ptr(), packed.data_ptr(),
+                                            out.data_ptr(), self.n_leaves, self.leaves, stream), "fuelq_qmatmul_packed_tree")
+
+    def matvec_tree_peer(self, packed: torch.Tensor, dst, dst_offset: int, peers_ref, push_seq: int, stream: int) -> None:
+        _check(_L.fuelq_qmatmul_packed_tree_peer(int(self.dtype), self.n, self.k, self.blocks.data_ptr(), packed.data_ptr(),
+                                                 dst, dst_offset, peers_ref, push_seq, self.n_leaves, self.leaves, stream),
+               "fuelq_qmatmul_packed_tree_peer")
+
+
 class QLlama:
     def __init__(self, cfg: LlamaConfig, device: torch.device, rank: int = 0, world: int = 1, seed: int = 0,
                  mix=q4km_mix, comm: str = "nccl", weights=None):
         """`weights`: a weight source (GgufWeights, SyntheticWeights); default: synthetic from `seed` and `mix`."""
         assert comm in ("nccl", "peer")
+        assert world in (1, 2, 4, 8)
         assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0
-        assert cfg.dim % world == 0 and cfg.vocab % world == 0 and cfg.head_dim == 128
+        assert cfg.dim % 256 == 0 and cfg.ffn_dim % 256 == 0 and cfg.vocab % world == 0 and cfg.head_dim == 128
         self.cfg, self.device, self.rank, self.world, self.comm = cfg, device, rank, world, comm
         c, g, r = cfg, world, rank
-        # FFN rows: equal parts for the library all-gather; whole 256-blocks (so a rank can quantize its own
-        # part of the SwiGLU output) for the in-kernel exchange
-        self.f_lo, self.f_hi = shard_range(c.ffn_dim, g, r, 256 if comm == "peer" else 1)
-        if comm == "nccl":
-            assert c.ffn_dim % g == 0
-        else:
-            assert (c.n_heads // g) % 2 == 0 and world <= _lib.PEER_MAX_WORLD and 4 * c.n_layers + 1 <= _lib.PEER_MAX_SEQ
-        fl = self.f_hi - self.f_lo
         self.hl, self.kvl = c.n_heads // g, c.n_kv_heads // g
         qd, kvd = self.hl * c.head_dim, self.kvl * c.head_dim
+        # row-parallel layers: this rank's leaves of the k axis. o's columns are the outputs of this rank's heads,
+        # down's are this rank's FFN channels (so gate/up are cut at the same channels)
+        o_b0, o_leaves = rank_leaves(c.n_heads * c.head_dim // 256, g, r)
+        d_b0, d_leaves = rank_leaves(c.ffn_dim // 256, g, r)
+        assert o_b0 * 256 == r * qd and sum(o_leaves) * 256 == qd, "the heads of a rank must cover whole leaves of o's k axis"
+        self.f_lo, self.f_hi = d_b0 * 256, (d_b0 + sum(d_leaves)) * 256
+        fl = self.f_hi - self.f_lo
+        assert g == 1 or (fl > 0 and qd % 256 == 0), "every rank needs FFN channels and whole activation blocks"
         f32 = dict(dtype=torch.float32, device=device)
 
         src = weights if weights is not None else SyntheticWeights(cfg, device, seed, mix)
         self.embed_dtype, self.embed = src.embedding()
         k_quants_only = True
+        tree_ok = True
 
         def lin(names, li, lo_hi, k):
             """One _Linear over the stacked rows of `names` (all the same format), each cut to its [lo, hi)."""
@@ -342,7 +386,12 @@ class QLlama:
             parts = [src.rows(nm, li, lo, hi) for nm, (lo, hi) in zip(names, lo_hi)]
             return _Linear(t, parts[0] if len(parts) == 1 else torch.cat(parts), sum(hi - lo for lo, hi in lo_hi), k)
 
-        d_rng = (r * c.dim // g, (r + 1) * c.dim // g)
+        def rowpar(name, li, k_total, b0, leaves):
+            t = src.dtype(name, li)
+            if t not in (T.Q4K, T.Q6K):   # no tree form: the whole matrix, plain mat-vec (one GPU only)
+                return lin((name,), li, ((0, c.dim),), k_total)
+            return _RowParallel(t, src.rows(name, li, 0, c.dim), c.dim, k_total, b0, leaves)
+
         q_rng, kv_rng, f_rng = (r * qd, (r + 1) * qd), (r * kvd, (r + 1) * kvd), (self.f_lo, self.f_hi)
         self.layers = []
         for li in range(c.n_layers):
@@ -354,13 +403,14 @@ class QLlama:
                 qk=lin(("attn_q", "attn_k", "attn_v") if stacked_v else ("attn_q", "attn_k"), li,
                        (q_rng, kv_rng, kv_rng) if stacked_v else (q_rng, kv_rng), c.dim),
                 v=None if stacked_v else lin(("attn_v",), li, (kv_rng,), c.dim),
-                o=lin(("attn_output",), li, (d_rng,), c.dim),
+                o=rowpar("attn_output", li, c.n_heads * c.head_dim, o_b0, o_leaves),
                 gu=lin(("ffn_gate", "ffn_up"), li, (f_rng, f_rng), c.dim),
-                down=lin(("ffn_down",), li, (d_rng,), c.ffn_dim),
+                down=rowpar("ffn_down", li, c.ffn_dim, d_b0, d_leaves),
                 attn_norm=src.norm("attn_norm", li), ffn_norm=src.norm("ffn_norm", li),
                 kc=torch.zeros(self.kvl, c.max_seq, c.head_dim, **f32),
                 vc=torch.zeros(self.kvl, c.max_seq, c.head_dim, **f32))
             k_quants_only &= all(layer[nm] is None or layer[nm].dtype in _K_QUANTS for nm in ("qk", "v", "o", "gu", "down"))
+            tree_ok &= isinstance(layer["o"], _RowParallel) and isinstance(layer["down"], _RowParallel)
             self.layers.append(layer)
         self.head = lin(("output",), -1, ((r * c.vocab // g, (r + 1) * c.vocab // g),), c.dim)
         k_quants_only &= self.head.dtype in _K_QUANTS
@@ -378,19 +428,12 @@ class QLlama:
         self.qk = self.qkv[:qd + kvd]
         self.v = self.qkv[qd + kvd:]
         self.attn_l = torch.zeros(qd, **f32)
-        self.o_l = torch.zeros(c.dim // g, **f32)
         self.gu = torch.zeros(2 * fl, **f32)
         self.s_l = torch.zeros(fl, **f32)
-        self.d_l = torch.zeros(c.dim // g, **f32)
+        self.part = torch.zeros(c.dim, **f32)            # this rank's partial result of a row-parallel layer
+        self.parts = torch.zeros(g, c.dim, **f32) if g > 1 else self.part.view(1, c.dim)   # every rank's, in rank order
         self.logits_l = torch.zeros(c.vocab // g, **f32)
-        if g > 1:
-            self.attn = torch.zeros(c.dim, **f32)
-            self.o = torch.zeros(c.dim, **f32)
-            self.s = torch.zeros(c.ffn_dim, **f32)
-            self.d = torch.zeros(c.dim, **f32)
-            self.logits = torch.zeros(c.vocab, **f32)
-        else:
-            self.attn, self.o, self.s, self.d, self.logits = self.attn_l, self.o_l, self.s_l, self.d_l, self.logits_l
+        self._logits = torch.zeros(c.vocab, **f32) if g > 1 else self.logits_l
         nb = max(_L.fuelq_act_packed_bytes(int(t), 1, k) for t in (T.Q4K, T.Q8_0) for k in (c.dim, c.ffn_dim))
         self.packed = torch.zeros(nb, dtype=torch.uint8, device=device)
         self.attn_ws = torch.zeros(max(_L.fuelq_attn_decode_workspace_bytes(self.hl), 16), dtype=torch.uint8, device=device)
@@ -405,15 +448,15 @@ class QLlama:
             self.ropes.append(rp)
         self.rope_refs = [ctypes.byref(rp) for rp in self.ropes]
         self.peer = None
-        if comm == "peer":
-            self._init_peer()
         self.graph = None
-        # The fused producers and the in-kernel exchange write Q8_K activation blocks, which is what k-quant weights
-        # take; a model with Q8_0 / Q4_0 linears runs the plain step, which quantizes per consumer.
-        self.fused = k_quants_only
-        if comm == "peer" and not all(lin is None or lin.dtype in (T.Q4K, T.Q6K)
-                                      for lin in [self.head] + [l[nm] for l in self.layers for nm in ("qk", "v", "o", "gu", "down")]):
-            raise NotImplementedError("comm='peer' needs Q4_K / Q6_K linears")
+        # The fused producers write Q8_K activation blocks, which is what k-quant weights take; a model with other
+        # linears runs the plain step on one GPU. The tree-ordered row-parallel mat-vec exists for Q4_K / Q6_K: a
+        # k-quant model whose o / down have another format (Q5_K) runs the fused step on one GPU with plain mat-vecs there.
+        self.fused = k_quants_only and (tree_ok or g == 1)
+        if g > 1 and not self.fused:
+            raise NotImplementedError("tensor parallelism needs k-quant linears with Q4_K / Q6_K o and down projections")
+        if comm == "peer" and self.fused and tree_ok:
+            self._init_peer()
         self.weight_bytes = (sum(l[k].blocks.numel() for l in self.layers for k in ("qk", "v", "o", "gu", "down") if l[k] is not None)
                              + self.head.blocks.numel())
 
@@ -430,10 +473,6 @@ class QLlama:
         return model
 
     # ---- one decode step: token, pos -> next_token; pos += 1; token = next_token
-    def _gather(self, full: torch.Tensor, local: torch.Tensor) -> None:
-        if self.world > 1:
-            dist.all_gather_into_tensor(full, local)
-
     def _quant(self, x: torch.Tensor, k: int, stream: int, dtype: T = T.Q4K) -> None:
         """Activation blocks for a consumer of weight format `dtype` (Q8_K for k-quants, Q8_0 for Q8_0 / Q4_0)."""
         _check(_L.fuelq_quantize_act_packed(int(dtype), 1, k, x.data_ptr(), self.packed.data_ptr(), self.packed.numel(),
@@ -452,27 +491,25 @@ class QLlama:
             lin.matvec_packed(self.packed, out, stream)
 
     def step(self) -> None:
-        if self.comm == "peer":
-            return self._step_peer()
-        if self.world == 1 and self.fused:
-            return self._step_fused()
+        if self.peer is not None:
+            return self._step_tp(True)
+        if self.fused:
+            return self._step_tp(False)
         return self._step_plain()
 
     # ---- in-kernel exchange over peer-mapped memory
     def _init_peer(self) -> None:
         import ctypes
         c, g, r = self.cfg, self.world, self.rank
-        self.peer = PeerRegion({"pattn": _L.fuelq_peer_act_bytes(c.dim), "ps": _L.fuelq_peer_act_bytes(c.ffn_dim),
-                                "o": _L.fuelq_peer_vec_bytes(c.dim), "d": _L.fuelq_peer_vec_bytes(c.dim),
+        assert 2 * c.n_layers + 1 <= _lib.PEER_MAX_SEQ
+        self.peer = PeerRegion({"o": _L.fuelq_peer_vec_bytes(g * c.dim), "d": _L.fuelq_peer_vec_bytes(g * c.dim),
                                 "logits": _L.fuelq_peer_vec_bytes(c.vocab)}, self.device, r, g)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.peers = _lib.Peers()
         self.peers.world, self.peers.rank, self.peers.epoch = g, r, self.epoch.data_ptr()
         self.peers_ref = ctypes.byref(self.peers)
-        self.dst_pattn, self.dst_ps = self.peer.ptrs("pattn"), self.peer.ptrs("ps")
         self.dst_o, self.dst_d, self.dst_logits = self.peer.ptrs("o"), self.peer.ptrs("d"), self.peer.ptrs("logits")
         own = self.peer.own
-        self.own_pattn, self.own_ps = own + self.peer.off["pattn"], own + self.peer.off["ps"]
         self.own_o, self.own_d = own + self.peer.off["o"], own + self.peer.off["d"]
         self.own_logits = own + self.peer.off["logits"]
         self.logits_pairs = self.peer.view("logits", 8 * c.vocab, torch.float32)  # {value, stamp} pairs
@@ -487,88 +524,80 @@ class QLlama:
     def logits(self, t: torch.Tensor) -> None:
         self._logits = t
 
-    def _step_peer(self) -> None:
-        c, r = self.cfg, self.rank
+    def _step_tp(self, peer: bool) -> None:
+        """The decode step of a k-quant model on any number of GPUs: column-parallel q/k/v, gate/up and head,
+        row-parallel o and down summed by the fixed tree. `peer`: the partial vectors and the logits travel as
+        stamped stores inside the kernels; otherwise through the library's all-gather (nothing travels on one GPU).
+        Norm, attention merge and SwiGLU write the next mat-vec's quantized activations directly."""
+        c, r, g = self.cfg, self.rank, self.world
         st = torch.cuda.current_stream().cuda_stream
         scale = 1.0 / math.sqrt(c.head_dim)
         pk, pkn = self.packed.data_ptr(), self.packed.numel()
-        pr = self.peers_ref
-        dl, vl, fl = c.dim // self.world, c.vocab // self.world, self.f_hi - self.f_lo
-        qd = self.hl * c.head_dim
+        fl = self.f_hi - self.f_lo
+        vl = c.vocab // g
+        pr = self.peers_ref if peer else None
+
+        def norm(delta_own, wait_seq, gain):
+            """x += (sum of the ranks' partial vectors); packed = Q8_K(rmsnorm(x) * gain)"""
+            if peer:
+                _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), delta_own, g, gain.data_ptr(), c.dim, c.norm_eps, pk, pkn,
+                                                     pr, wait_seq, st), "add_rmsnorm_q8k_peer")
+            elif delta_own is None:
+                _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), None, gain.data_ptr(), c.dim, c.norm_eps, pk, pkn, st),
+                       "add_rmsnorm_q8k")
+            else:
+                if g > 1:
+                    dist.all_gather_into_tensor(self.parts.view(-1), self.part)
+                _check(_L.fuelq_add_rmsnorm_q8k_parts(self.x.data_ptr(), self.parts.data_ptr(), g, gain.data_ptr(), c.dim,
+                                                      c.norm_eps, pk, pkn, st), "add_rmsnorm_q8k_parts")
+
+        def rowpar(lin, dst, seq):
+            if peer:
+                lin.matvec_tree_peer(self.packed, dst, r * c.dim, pr, seq, st)
+            elif isinstance(lin, _RowParallel):
+                lin.matvec_tree(self.packed, self.part, st)
+            else:                       # one GPU, a format without the tree form
+                lin.matvec_packed(self.packed, self.part, st)
+
         _check(_L.fuelq_embed_rows(int(self.embed_dtype), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
                "fuelq_embed_rows")
         delta, wait = None, -1
         for li, l in enumerate(self.layers):
-            sq = 4 * li  # exchange points of this layer: attention, o, SwiGLU, down
-            _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), delta, l["attn_norm"].data_ptr(), c.dim, c.norm_eps, pk, pkn,
-                                                 pr, wait, st), "add_rmsnorm_q8k_peer")
-            l["qk"].matvec_packed(self.packed, self.qkv if l["v"] is None else self.qk, st)
-            if l["v"] is not None:
-                l["v"].matvec_packed(self.packed, self.v, st)
-            _check(_L.fuelq_attn_decode_q8k_peer(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.pos.data_ptr(),
-                                                 self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
-                                                 self.attn_ws.numel(), r * self.hl, c.dim, self.dst_pattn, pr, sq, self.rope_refs[li], st),
-                   "attn_decode_q8k_peer")
-            o = l["o"]
-            _check(_L.fuelq_qmatmul_packed_peer(int(o.dtype), c.dim, dl, o.blocks.data_ptr(), self.own_pattn, self.dst_o, r * dl,
-                                                pr, sq, sq + 1, st), "qmatmul_packed_peer")
-            _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), self.own_o, l["ffn_norm"].data_ptr(), c.dim, c.norm_eps, pk,
-                                                 pkn, pr, sq + 1, st), "add_rmsnorm_q8k_peer")
-            l["gu"].matvec_packed(self.packed, self.gu, st)
-            _check(_L.fuelq_swiglu_q8k_peer(self.gu.data_ptr(), self.gu.data_ptr() + 4 * fl, fl, self.f_lo, c.ffn_dim,
-                                            self.dst_ps, pr, sq + 2, st), "swiglu_q8k_peer")
-            dn = l["down"]
-            _check(_L.fuelq_qmatmul_packed_peer(int(dn.dtype), c.ffn_dim, dl, dn.blocks.data_ptr(), self.own_ps, self.dst_d,
-                                                r * dl, pr, sq + 2, sq + 3, st), "qmatmul_packed_peer")
-            delta, wait = self.own_d, sq + 3
-        last = 4 * len(self.layers)
-        _check(_L.fuelq_add_rmsnorm_q8k_peer(self.x.data_ptr(), delta, self.out_norm.data_ptr(), c.dim, c.norm_eps, pk, pkn, pr,
-                                             wait, st), "add_rmsnorm_q8k_peer")
-        h = self.head
-        _check(_L.fuelq_qmatmul_packed_peer(int(h.dtype), c.dim, vl, h.blocks.data_ptr(), pk, self.dst_logits, r * vl, pr, -1,
-                                            last, st), "qmatmul_packed_peer")
-        _check(_L.fuelq_argmax_last_peer(self.own_logits, c.vocab, self.next_token.data_ptr(), pr, last, self.epoch.data_ptr(),
-                                         st), "argmax_last_peer")
-        self.pos.add_(1)
-        self.token.copy_(self.next_token)
-
-    def _step_fused(self) -> None:
-        """Single-GPU step: norm / attention merge / SwiGLU write the quantized activations directly."""
-        c = self.cfg
-        st = torch.cuda.current_stream().cuda_stream
-        scale = 1.0 / math.sqrt(c.head_dim)
-        pk, pkn = self.packed.data_ptr(), self.packed.numel()
-        _check(_L.fuelq_embed_rows(int(self.embed_dtype), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
-               "fuelq_embed_rows")
-        delta = None
-        qd = self.hl * c.head_dim
-        for li, l in enumerate(self.layers):
-            _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), delta, l["attn_norm"].data_ptr(), c.dim, c.norm_eps, pk, pkn, st),
-                   "add_rmsnorm_q8k")
+            norm(delta, wait, l["attn_norm"])
             l["qk"].matvec_packed(self.packed, self.qkv if l["v"] is None else self.qk, st)
             if l["v"] is not None:
                 l["v"].matvec_packed(self.packed, self.v, st)
             _check(_L.fuelq_attn_decode_q8k(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.pos.data_ptr(),
                                             self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
                                             self.attn_ws.numel(), pk, pkn, self.rope_refs[li], st), "attn_decode_q8k")
-            l["o"].matvec_packed(self.packed, self.o_l, st)
-            _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), self.o_l.data_ptr(), l["ffn_norm"].data_ptr(), c.dim, c.norm_eps,
-                                            pk, pkn, st), "add_rmsnorm_q8k")
+            rowpar(l["o"], self.dst_o if peer else None, 2 * li)
+            norm(self.own_o if peer else self.part, 2 * li, l["ffn_norm"])
             l["gu"].matvec_packed(self.packed, self.gu, st)
-            _check(_L.fuelq_swiglu_q8k(self.gu.data_ptr(), self.gu.data_ptr() + 4 * c.ffn_dim, c.ffn_dim, pk, pkn, st), "swiglu_q8k")
-            l["down"].matvec_packed(self.packed, self.d_l, st)
-            delta = self.d_l.data_ptr()
-        _check(_L.fuelq_add_rmsnorm_q8k(self.x.data_ptr(), delta, self.out_norm.data_ptr(), c.dim, c.norm_eps, pk, pkn, st),
-               "add_rmsnorm_q8k")
-        self.head.matvec_packed(self.packed, self.logits_l, st)
-        _check(_L.fuelq_argmax_last(self.logits.data_ptr(), c.vocab, self.next_token.data_ptr(), st), "argmax_last")
+            _check(_L.fuelq_swiglu_q8k(self.gu.data_ptr(), self.gu.data_ptr() + 4 * fl, fl, pk, pkn, st), "swiglu_q8k")
+            rowpar(l["down"], self.dst_d if peer else None, 2 * li + 1)
+            delta, wait = (self.own_d if peer else self.part), 2 * li + 1
+        last = 2 * len(self.layers)
+        norm(delta, wait, self.out_norm)
+        h = self.head
+        if peer:
+            _check(_L.fuelq_qmatmul_packed_peer(int(h.dtype), c.dim, vl, h.blocks.data_ptr(), pk, self.dst_logits, r * vl, pr, last,
+                                                st), "qmatmul_packed_peer")
+            _check(_L.fuelq_argmax_last_peer(self.own_logits, c.vocab, self.next_token.data_ptr(), pr, last, self.epoch.data_ptr(),
+                                             st), "argmax_last_peer")
+        else:
+            h.matvec_packed(self.packed, self.logits_l, st)
+            if g > 1:
+                dist.all_gather_into_tensor(self._logits, self.logits_l)
+            _check(_L.fuelq_argmax_last(self._logits.data_ptr(), c.vocab, self.next_token.data_ptr(), st), "argmax_last")
         self.pos.add_(1)
         self.token.copy_(self.next_token)
 
     def _step_plain(self) -> None:
+        """One GPU, any supported linear formats: every op its own call, activations quantized per consumer."""
         c = self.cfg
         st = torch.cuda.current_stream().cuda_stream
         scale = 1.0 / math.sqrt(c.head_dim)
+        fl = c.ffn_dim
         _check(_L.fuelq_embed_rows(int(self.embed_dtype), self.embed.data_ptr(), c.dim, self.token.data_ptr(), 1, self.x.data_ptr(), st),
                "fuelq_embed_rows")
         delta = None
@@ -579,23 +608,17 @@ class QLlama:
             _check(_L.fuelq_attn_decode(self.qk.data_ptr(), l["kc"].data_ptr(), l["vc"].data_ptr(), self.attn_l.data_ptr(),
                                         self.pos.data_ptr(), self.hl, self.kvl, c.head_dim, c.max_seq, scale, self.attn_ws.data_ptr(),
                                         self.attn_ws.numel(), self.rope_refs[li], st), "attn_decode")
-            self._gather(self.attn, self.attn_l)
-            self._mv((l["o"],), (self.o_l,), self.attn, c.dim, st)
-            self._gather(self.o, self.o_l)
-            _check(_L.fuelq_add_rmsnorm(self.x.data_ptr(), self.o.data_ptr(), l["ffn_norm"].data_ptr(), self.h.data_ptr(), 1,
+            self._mv((l["o"],), (self.part,), self.attn_l, c.dim, st)
+            _check(_L.fuelq_add_rmsnorm(self.x.data_ptr(), self.part.data_ptr(), l["ffn_norm"].data_ptr(), self.h.data_ptr(), 1,
                                         c.dim, c.norm_eps, st), "add_rmsnorm")
             self._mv((l["gu"],), (self.gu,), self.h, c.dim, st)
-            fl = self.f_hi - self.f_lo
             _check(_L.fuelq_swiglu(self.gu.data_ptr(), self.gu.data_ptr() + 4 * fl, self.s_l.data_ptr(), fl, st), "swiglu")
-            self._gather(self.s, self.s_l)
-            self._mv((l["down"],), (self.d_l,), self.s, c.ffn_dim, st)
-            self._gather(self.d, self.d_l)
-            delta = self.d
+            self._mv((l["down"],), (self.part,), self.s_l, c.ffn_dim, st)
+            delta = self.part
         _check(_L.fuelq_add_rmsnorm(self.x.data_ptr(), delta.data_ptr(), self.out_norm.data_ptr(), self.h.data_ptr(), 1, c.dim,
                                     c.norm_eps, st), "add_rmsnorm")
         self._mv((self.head,), (self.logits_l,), self.h, c.dim, st)
-        self._gather(self.logits, self.logits_l)
-        _check(_L.fuelq_argmax_last(self.logits.data_ptr(), c.vocab, self.next_token.data_ptr(), st), "argmax_last")
+        _check(_L.fuelq_argmax_last(self._logits.data_ptr(), c.vocab, self.next_token.data_ptr(), st), "argmax_last")
         self.pos.add_(1)
         self.token.copy_(self.next_token)
 

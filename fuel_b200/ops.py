@@ -82,6 +82,27 @@ def qmatmul(dtype: GgmlDType, w_blocks: torch.Tensor, n: int, x: torch.Tensor,
     return out
 
 
+def qmatmul_host(dtype: GgmlDType, w_blocks: torch.Tensor, n: int, x_host: torch.Tensor,
+                 out_host: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """qmatmul for HOST activations and a HOST result (CPU tensors; pinned ones keep the call asynchronous and, when
+    small, are read and written in place by the kernels). Enqueued on the current stream of the weights' device;
+    synchronize that stream before reading the result."""
+    _need_cuda(w_blocks, "w_blocks")
+    if x_host.is_cuda or x_host.dtype != torch.float32 or not x_host.is_contiguous():
+        raise ValueError("x_host must be a contiguous float32 CPU tensor")
+    k = x_host.shape[-1]
+    m = x_host.numel() // k if k else 0
+    if out_host is None:
+        out_host = torch.empty(*x_host.shape[:-1], n, dtype=torch.float32, pin_memory=x_host.is_pinned())
+    ws_bytes = _L.fuelq_qmatmul_host_workspace_bytes(int(dtype), m, n, k)
+    if workspace is None:
+        workspace = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=w_blocks.device)
+    with torch.cuda.device(w_blocks.device):
+        _lib.check(_L.fuelq_qmatmul_host(int(dtype), m, n, k, w_blocks.data_ptr(), x_host.data_ptr(), out_host.data_ptr(),
+                                         workspace.data_ptr(), workspace.numel(), _stream()), "fuelq_qmatmul_host")
+    return out_host
+
+
 def qmatmul_packed(dtype: GgmlDType, w_blocks: torch.Tensor, n: int, k: int, m: int, packed_act: torch.Tensor,
                    out: torch.Tensor) -> torch.Tensor:
     with torch.cuda.device(out.device):

@@ -135,8 +135,13 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
  * asynchronous); the caller synchronizes the stream before reading y_host. This is the
  * shape of the reference's eager CUDA forward, which stages small host arrays and reads
  * results back around every call (fuel-cuda-backend/src/quantized.rs:170-231), without
- * its per-call allocations and device synchronize. workspace: device, 256-byte aligned,
- * fuelq_qmatmul_host_workspace_bytes() bytes. */
+ * its per-call allocations and device synchronize. On the integer path, when both host buffers
+ * are page-locked and mapped into the device's address space (cudaHostAlloc, cudaHostRegister
+ * with the mapped flag) and small (x <= 256 KiB, y <= 1 MiB), no copy is enqueued at all: the
+ * quantizing kernel reads x in place and a small kernel writes y in place, same bits either way.
+ * x_host must hold its final contents when the call is made: it is read at some time between the
+ * call and the completion of the enqueued work, not necessarily after earlier work of the stream.
+ * workspace: device, 256-byte aligned, fuelq_qmatmul_host_workspace_bytes() bytes. */
 size_t fuelq_qmatmul_host_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
 int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
                            const float* x_host, float* y_host, void* workspace, size_t workspace_bytes,
@@ -291,34 +296,44 @@ typedef struct fuelq_peers {
   int32_t world, rank;
   const uint32_t* epoch; /* device word on this rank, starts at 0 */
 } fuelq_peers;
-/* bytes of a destination buffer for the stamped Q8_K activation planes of a k-wide vector / for n f32 words */
-size_t fuelq_peer_act_bytes(int64_t k);
+/* bytes of a destination buffer for n f32 words */
 size_t fuelq_peer_vec_bytes(int64_t n);
 /* zeroed device memory that other processes of this node can map: handle64 receives 64 opaque bytes */
 int32_t fuelq_ipc_alloc(size_t bytes, void** dev_ptr, void* handle64);
 int32_t fuelq_ipc_open(const void* handle64, void** dev_ptr);
 int32_t fuelq_ipc_close(void* dev_ptr);
 int32_t fuelq_ipc_free(void* dev_ptr);
-/* y_local = W_local · act (m = 1, integer path), stored as stamped pairs of push_seq at word dst_offset of the
- * vector buffer dst[q] of every rank q. wait_seq < 0: `act` is this rank's packed planes
- * (fuelq_quantize_act_packed layout; Q4_K / Q6_K / Q8_0). wait_seq >= 0: `act` is this rank's stamped-planes
- * buffer filled through that exchange point (Q4_K / Q6_K). */
+/* Column-parallel layer: y_local = W_local . act (m = 1, integer path; W_local is this rank's band of output rows),
+ * stored as stamped pairs of push_seq at word dst_offset of the vector buffer dst[q] of every rank q. `act` is this
+ * rank's packed planes of the whole input vector (fuelq_quantize_act_packed layout; Q4_K / Q6_K / Q8_0). */
 int32_t fuelq_qmatmul_packed_peer(int32_t ggml_type, int64_t k, int64_t n_local, const void* w, const void* act,
-                                  void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t wait_seq,
-                                  int32_t push_seq, void* stream);
-/* fuelq_add_rmsnorm_q8k whose delta is a vector buffer filled through wait_seq (null and -1: no delta) */
-int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, const float* gain, int64_t dim, float eps, void* packed,
-                                   size_t packed_bytes, const fuelq_peers* peers, int32_t wait_seq, void* stream);
-/* fuelq_swiglu_q8k over this rank's columns [col0, col0 + n_local) of a k_total-wide vector (multiples of 256),
- * quantized blocks stored as stamped pairs of push_seq into every rank's stamped-planes buffer act_dst[q] */
-int32_t fuelq_swiglu_q8k_peer(const float* gate, const float* up, int64_t n_local, int64_t col0, int64_t k_total,
-                              void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, void* stream);
-/* fuelq_attn_decode_q8k over this rank's heads [head0, head0 + n_heads), stored into every rank's planes */
-int32_t fuelq_attn_decode_q8k_peer(const float* q, const float* kcache, const float* vcache, const int32_t* pos,
-                                   int32_t n_heads, int32_t n_kv, int32_t head_dim, int32_t max_seq, float scale,
-                                   void* workspace, size_t workspace_bytes, int32_t head0, int64_t k_total,
-                                   void* const* act_dst, const fuelq_peers* peers, int32_t push_seq, const fuelq_rope* rope,
-                                   void* stream);
+                                  void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t push_seq,
+                                  void* stream);
+/* fuelq_add_rmsnorm_q8k whose delta is the sum of n_parts (1, 2, 4 or 8) partial vectors filled through wait_seq:
+ * `delta` is a vector buffer of n_parts * dim words, part q at word q * dim (null and -1: no delta). The parts
+ * are added pairwise, ((p0 + p1) + (p2 + p3)) + ..., the top levels of the tree fuelq_qmatmul_packed_tree sums by. */
+int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, int32_t n_parts, const float* gain, int64_t dim, float eps,
+                                   void* packed, size_t packed_bytes, const fuelq_peers* peers, int32_t wait_seq, void* stream);
+/* The same with the parts as plain f32 vectors [n_parts][dim] in this GPU's memory (after a library all-gather). */
+int32_t fuelq_add_rmsnorm_q8k_parts(float* x, const float* parts, int32_t n_parts, const float* gain, int64_t dim, float eps,
+                                    void* packed, size_t packed_bytes, void* stream);
+
+/* ---- Row-parallel layers: y = W . act with W cut along k (the reference's RowParallel::forward is a local matmul
+ * followed by an all-reduce, fuel-parallel/src/tensor_parallel.rs:321-343, its sum folded in rank order,
+ * fuel-parallel/src/device_group.rs:100-118). Here the sum over k follows ONE fixed tree at every GPU count: the k axis
+ * of the whole layer is cut into eight leaves (ranges of whole 256-element blocks), a leaf is summed in an order of its
+ * own, and leaves are added pairwise, ((l0 + l1) + (l2 + l3)) + ((l4 + l5) + (l6 + l7)). A GPU holds an aligned group of
+ * 8 / world leaves, so its mat-vec yields a complete subtree, and adding the GPUs' results pairwise in rank order
+ * (fuelq_add_rmsnorm_q8k_peer / _parts) finishes the same tree: the result has the same bits on 1, 2, 4 or 8 GPUs.
+ * m = 1; Q4_K / Q6_K; w is this GPU's slab [n][k] (its k columns of every row, contiguous); leaf_blocks[l] is the
+ * number of 256-element blocks of its leaf l (n_leaves = 1, 2, 4 or 8; at most 16 blocks per leaf). */
+int32_t fuelq_qmatmul_packed_tree(int32_t ggml_type, int64_t n, int64_t k, const void* w, const void* packed_act, float* y,
+                                  int32_t n_leaves, const int32_t* leaf_blocks, void* stream);
+/* The same, the n results stored as stamped pairs of push_seq at word dst_offset of the vector buffer dst[q] of every rank q
+ * (a rank of a row-parallel layer passes dst_offset = rank * n: part `rank` of the consumer's delta). */
+int32_t fuelq_qmatmul_packed_tree_peer(int32_t ggml_type, int64_t n, int64_t k, const void* w, const void* packed_act,
+                                       void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t push_seq,
+                                       int32_t n_leaves, const int32_t* leaf_blocks, void* stream);
 /* fuelq_argmax_last over a vector buffer of n (even) words filled through wait_seq; then *epoch += 1
  * (epoch must be peers->epoch) */
 int32_t fuelq_argmax_last_peer(const void* x, int64_t n, int32_t* out_index, const fuelq_peers* peers, int32_t wait_seq,

@@ -31,20 +31,24 @@ def _rope(x, cos, sin):               # x [heads, hd]
 class OracleLlama:
     """weights: dict name -> (ggml type id, uint8 blocks, n, k). Norm gains are ones unless a layer dict holds
     "attn_norm" / "ffn_norm" f32 vectors and `out_norm` is given. `embed_blocks` is the Q4_K block bytes of the
-    embedding table, or an f32 [vocab, dim] array (how the reference holds it after loading a checkpoint)."""
+    embedding table, or an f32 [vocab, dim] array (how the reference holds it after loading a checkpoint).
+    `order` picks the scalar or the AVX2 summation order of the reference's dot products; the two give logits that
+    differ at the 1e-7 level per linear, and (through the 8-bit re-quantization of every linear's input, which turns
+    such a difference into an occasional flipped quant) by far more after many layers: the spread between the two is
+    the yardstick for what "the same forward pass" can mean at depth."""
 
-    def __init__(self, cfg, embed_blocks, layers, head, cos, sin, out_norm=None):
+    def __init__(self, cfg, embed_blocks, layers, head, cos, sin, out_norm=None, order=O.SCALAR):
         self.cfg, self.embed, self.layers, self.head, self.cos, self.sin = cfg, embed_blocks, layers, head, cos, sin
         self.out_norm = out_norm
+        self.order = order      # which of the reference's two f32 summation orders the linears use (scalar / AVX2)
         c = cfg
         self.kc = np.zeros((c.n_layers, c.n_kv_heads, c.max_seq, c.head_dim), np.float32)
         self.vc = np.zeros_like(self.kc)
         self.pos = 0
 
-    @staticmethod
-    def _lin(w, x):
+    def _lin(self, w, x):
         t, blocks, n, k = w
-        return O.matmul(t, x[None, :], blocks, n, O.SCALAR)[0]
+        return O.matmul(t, x[None, :], blocks, n, self.order)[0]
 
     def step(self, token: int):
         c = self.cfg

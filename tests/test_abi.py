@@ -116,7 +116,7 @@ def test_argument_validation_of_moe_and_peer_entries_needs_no_gpu():
     assert L.fuelq_moe_combine(None, None, None, 4, 99, 64, None, None) == INV
     peers = _lib.Peers()
     peers.world, peers.rank, peers.epoch = 9, 0, 16
-    assert L.fuelq_add_rmsnorm_q8k_peer(16, None, 16, 256, 1e-5, 16, 1 << 20, ctypes.byref(peers), -1, None) == INV  # world > 8
+    assert L.fuelq_add_rmsnorm_q8k_peer(16, None, 1, 16, 256, 1e-5, 16, 1 << 20, ctypes.byref(peers), -1, None) == INV  # world > 8
     peers.world, peers.rank = 2, 2
     assert L.fuelq_argmax_last_peer(16, 8, 16, ctypes.byref(peers), 0, 16, None) == INV                              # rank >= world
-    assert L.fuelq_peer_act_bytes(100) == 0 and L.fuelq_peer_act_bytes(256) > 0 and L.fuelq_peer_vec_bytes(10) == 80
+    assert L.fuelq_peer_vec_bytes(10) == 80

@@ -255,6 +255,38 @@ def test_fused_quantization_gives_same_bits(ops, oracle, name, m, n, k):
     assert_matmul_close(y_fused.cpu().numpy(), oracle.matmul(_ot(oracle, name), x.cpu().numpy(), wb.cpu().numpy(), n))
 
 
+@pytest.mark.parametrize("name,m,n,k", [("q4k", 1, 11008, 4096), ("q6k", 3, 1000, 1024), ("q8_0", 16, 515, 2048),
+                                        ("q4k", 40, 256, 4096)])
+def test_host_buffers_pinned_or_pageable_give_the_device_path_bits(ops, oracle, name, m, n, k):
+    """fuelq_qmatmul_host: pageable host memory is copied, small pinned (device-mapped) memory is read and written in
+    place by the kernels; either way the result has the bits of the device-buffer call. (m = 40 x 4096 x 4 bytes is
+    above the in-place limit: pinned, but copied.)"""
+    wb = _dev(oracle.quantize(_ot(oracle, name), _weights(n, k)))
+    x = torch.from_numpy(_acts(m, k))
+    want = ops.qmatmul(_T(name), wb, n, x.cuda()).cpu()
+    y_page = ops.qmatmul_host(_T(name), wb, n, x)
+    torch.cuda.synchronize()
+    assert torch.equal(y_page, want)
+    from fuel_b200 import _lib
+    xp = x.pin_memory()
+    for pdl in (0, 1):      # one row: the write-back is inside the mat-vec kernel in plain launches, a kernel of its own with PDL
+        y_pin = torch.full((m, n), float("nan")).pin_memory()
+        try:
+            _lib.lib.fuelq_set_option(_lib.OPT_PDL, pdl)
+            for _ in range(3):   # back to back: a call's early read of x runs beside the previous call's kernels
+                ops.qmatmul_host(_T(name), wb, n, xp, out_host=y_pin)
+            torch.cuda.synchronize()
+        finally:
+            _lib.lib.fuelq_set_option(_lib.OPT_PDL, 0)
+        assert torch.equal(y_pin, want), pdl
+    # an odd (4-byte aligned only) pinned output address takes the scalar write-back
+    base = torch.full((m * n + 1,), float("nan")).pin_memory()
+    ops.qmatmul_host(_T(name), wb, n, xp, out_host=base[1:].view(m, n))
+    torch.cuda.synchronize()
+    assert torch.equal(base[1:].view(m, n), want) and torch.isnan(base[0])
+    assert ops.device_error() == 0
+
+
 def test_error_statuses_on_device(ops):
     from fuel_b200 import GgmlDType as T, _lib
     x = torch.zeros(1, 100, device="cuda")

@@ -10,6 +10,51 @@ torch = pytest.importorskip("torch")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def test_leaf_split_is_nested_and_rank_groups_tile_the_axis():
+    """The eight leaves of a row-parallel layer's k axis: aligned groups of 8 / world leaves tile the axis for every
+    world size, and a group at world w is the union of its two groups at world 2w (so each rank's result is a complete
+    subtree of the one summation tree)."""
+    from fuel_b200.llama import leaf_split, rank_leaves
+    assert leaf_split(16) == [2] * 8 and leaf_split(43) == [5, 5, 5, 6, 5, 6, 5, 6] and leaf_split(4) == [0, 1, 0, 1, 0, 1, 0, 1]
+    for nb in (1, 4, 11, 16, 43, 56, 100):
+        leaves = leaf_split(nb)
+        assert len(leaves) == 8 and sum(leaves) == nb and max(leaves) - min(leaves) <= 1
+        for world in (1, 2, 4, 8):
+            pos = 0
+            for r in range(world):
+                b0, mine = rank_leaves(nb, world, r)
+                assert b0 == pos and mine == leaves[r * (8 // world):(r + 1) * (8 // world)]
+                pos += sum(mine)
+            assert pos == nb
+        for world in (1, 2, 4):
+            for r in range(world):
+                b0, mine = rank_leaves(nb, world, r)
+                lo, hi = rank_leaves(nb, 2 * world, 2 * r), rank_leaves(nb, 2 * world, 2 * r + 1)
+                assert lo[0] == b0 and lo[1] + hi[1] == mine and hi[0] == b0 + sum(lo[1])
+
+
+def test_pairwise_tree_over_ranks_equals_the_tree_over_all_leaves():
+    """f32 model of the row-parallel sum: leaf values added pairwise give the same bits whether one rank adds all
+    eight or 2 / 4 / 8 ranks each add their aligned group and the groups are then added pairwise in rank order."""
+    rng = np.random.Generator(np.random.PCG64(5))
+    leaves = [rng.standard_normal(1000).astype(np.float32) * np.float32(10.0 ** rng.integers(-3, 4)) for _ in range(8)]
+
+    def tree(vals):
+        vals = list(vals)
+        while len(vals) > 1:
+            vals = [(vals[i] + vals[i + 1]).astype(np.float32) for i in range(0, len(vals), 2)]
+        return vals[0]
+
+    one = tree(leaves)
+    chain = leaves[0]
+    for v in leaves[1:]:
+        chain = (chain + v).astype(np.float32)
+    assert not np.array_equal(one, chain)          # the order matters in f32: that is why it is fixed
+    for world in (2, 4, 8):
+        per = 8 // world
+        assert np.array_equal(tree([tree(leaves[r * per:(r + 1) * per]) for r in range(world)]), one)
+
+
 def test_shard_range_tiles_the_rows_in_whole_units():
     from fuel_b200.llama import shard_range
     for total, unit in ((11008, 256), (4096, 1), (32000, 1), (2816, 256), (256, 256)):
