@@ -235,6 +235,7 @@ def run_side_workload(args):
     torch.cuda.set_device(0)
     L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0)
     L.fuelq_set_option(_lib.OPT_PREFILL_TF32, 1 if args.tf32 else 0)
+    L.fuelq_set_option(_lib.OPT_PREFILL_BF16, 1 if args.bf16 else 0)
     st = torch.cuda.Stream(dev)
     peak, peak_kind = _peaks()
     gen = torch.Generator(device=dev)
@@ -277,7 +278,7 @@ def run_side_workload(args):
                 print(json.dumps(matmul_case(T.Q5K, "Q5_K", n, k, m, 12, 20)), flush=True)
     elif args.workload == "prefill":
         line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10)
-        line["operands"] = "tf32" if args.tf32 else "bf16"
+        line["operands"] = "tf32" if args.tf32 else "bf16" if args.bf16 else "f16"
         print(json.dumps(line), flush=True)
     else:
         E, H, F, K, N, copies = 128, 2048, 768, 8, 256, 4
@@ -317,6 +318,7 @@ def run_prefill_sharded(args, rank, local_rank, world, own_group=True):
         dist.init_process_group("nccl", device_id=dev)
     result = None
     _lib.lib.fuelq_set_option(_lib.OPT_PREFILL_TF32, 1 if args.tf32 else 0)
+    _lib.lib.fuelq_set_option(_lib.OPT_PREFILL_BF16, 1 if args.bf16 else 0)
     n, k, m, copies = 14336, 4096, 2048, 4
     lo, hi = shard_range(n, world, rank)
     gen = torch.Generator(device=dev)
@@ -346,7 +348,7 @@ def run_prefill_sharded(args, rank, local_rank, world, own_group=True):
         if rank == 0:
             peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
             result = {"workload": f"Q4_K_k{k}_n{n}_m{m}_column_sharded", "n_gpus": world, "us": us,
-                      "TFLOP/s": 2 * m * n * k / us / 1e6, "operands": "tf32" if args.tf32 else "bf16",
+                      "TFLOP/s": 2 * m * n * k / us / 1e6, "operands": "tf32" if args.tf32 else "bf16" if args.bf16 else "f16",
                       "all_gather": "inside the kernel epilogue (stores into every GPU's Y over NVLink)",
                       "y_bytes_stored_per_gpu": 4 * m * (hi - lo) * world,
                       "bf16_tflops_measured_per_gpu": peak.get("bf16_tflops")}
@@ -527,7 +529,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step (profiling runs use fewer)")
-    ap.add_argument("--tf32", action="store_true", help="--workload prefill: tensor-core path in tf32 instead of bf16")
+    ap.add_argument("--tf32", action="store_true", help="--workload prefill: tensor-core path in tf32 instead of f16")
+    ap.add_argument("--bf16", action="store_true", help="--workload prefill: 16-bit operands as bf16 instead of f16")
     ap.add_argument("--decode-grid", type=int, default=0, help="thread blocks of the decode mat-vec (0: the library's choice, two per SM)")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-architecture decode that is reported beside the metric")
     ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe", "q5k"],

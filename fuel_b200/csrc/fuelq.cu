@@ -33,7 +33,8 @@ struct Options {
   int64_t decode_kernel = 0;  // 0 auto, 1 generic (activations through L1), 2 register-resident only
   int64_t moe_kernel = 0;     // development switch: 1 = grouped mat-vec on the dp4a kernel even where the tensor-core form fits
   int64_t peer_wait_ms = 4000; // deadline of the exchange polls in the tensor-parallel kernels
-  int64_t prefill_tf32 = 0;   // tensor-core path in tf32 instead of bf16
+  int64_t prefill_tf32 = 0;   // tensor-core path in tf32 instead of 16-bit operands
+  int64_t prefill_bf16 = 0;   // 16-bit operands as bf16 instead of f16
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
   int64_t dbg_mb_groups = 0, dbg_mb_min_m = 2, dbg_mb_rpc = 0, dbg_host_wb = 0, dbg_host_early = 1;  // host write-back: 0 = by launch mode, 1 = own kernel, 2 = inside the mat-vec kernel
 };
@@ -718,13 +719,16 @@ bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   }
   return (type == kQ4K || type == kQ6K || type == kQ8_0) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }
-size_t prefill_workspace_bytes(int64_t m, int64_t k) { return align_up((size_t)m * k * (g_opt.prefill_tf32 ? 4 : 2), 256); }
+// the activations in the operand type, then (f16 operands) one unscale factor per row
+size_t prefill_workspace_bytes(int64_t m, int64_t k) {
+  return align_up((size_t)m * k * (g_opt.prefill_tf32 ? 4 : 2), 256) + align_up((size_t)m * 4, 256);
+}
 
 // tensor map of the bf16 activation matrix [M][K]: boxes of 64 columns x tile_m rows, 128-byte swizzle, zero fill
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, bool f32, CUtensorMap* map) {
+bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, bool f32, bool f16, CUtensorMap* map) {
   static EncodeTiledFn encode = nullptr;
   if (!encode) {
     void* fn = nullptr;
@@ -738,16 +742,16 @@ bool make_x_map(const void* xb, int64_t m, int64_t k, int tile_m, bool f32, CUte
   const cuuint64_t strides[1] = {(cuuint64_t)k * (f32 ? 4 : 2)};
   const cuuint32_t box[2] = {(cuuint32_t)(f32 ? 32 : kPfTileK), (cuuint32_t)tile_m};  // 128 bytes x tile_m rows
   const cuuint32_t estr[2] = {1, 1};
-  return encode(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xb), dims, strides, box, estr,
+  return encode(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xb), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <class Fmt, int kTileM, bool kTf32, bool kMulti>
+template <class Fmt, int kTileM, bool kTf32, bool kMulti, bool kF16>
 cudaError_t launch_prefill_m(const PrefillParams& p, const void* xb, cudaStream_t stream) {
   constexpr size_t smem = 1024 + (size_t)kPfStages * (kPfTileN * 128 + kTileM * 128) + sizeof(PrefillSmem) + 64;
   static bool attr_set[64] = {};
-  auto kern = prefill_gemm_kernel<Fmt, kTileM, kTf32, kMulti>;
+  auto kern = prefill_gemm_kernel<Fmt, kTileM, kTf32, kMulti, kF16>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
@@ -757,30 +761,34 @@ cudaError_t launch_prefill_m(const PrefillParams& p, const void* xb, cudaStream_
     attr_set[dev] = true;
   }
   CUtensorMap xmap;
-  if (!make_x_map(xb, p.M, p.K, kTileM, kTf32, &xmap)) return cudaErrorUnknown;
+  if (!make_x_map(xb, p.M, p.K, kTileM, kTf32, kF16, &xmap)) return cudaErrorUnknown;
   const dim3 grid((unsigned)((p.N + kPfTileN - 1) / kPfTileN), (unsigned)((p.M + kTileM - 1) / kTileM));
   kern<<<grid, kPfThreads, smem, stream>>>(p, xmap);
   return cudaGetLastError();
 }
 
-template <class Fmt, int kTileM, bool kTf32 = false>
+template <class Fmt, int kTileM, bool kTf32 = false, bool kF16 = false>
 cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t stream) {
-  return p.n_dst > 1 ? launch_prefill_m<Fmt, kTileM, kTf32, true>(p, xb, stream)
-                     : launch_prefill_m<Fmt, kTileM, kTf32, false>(p, xb, stream);
+  return p.n_dst > 1 ? launch_prefill_m<Fmt, kTileM, kTf32, true, kF16>(p, xb, stream)
+                     : launch_prefill_m<Fmt, kTileM, kTf32, false, kF16>(p, xb, stream);
 }
 
 // y_dst / n_dst / ldy / n_off: see PrefillParams; the plain call passes one destination of width n
 int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const float* x, float* const* y_dst, int n_dst,
                      int64_t ldy, int64_t n_off, void* workspace, cudaStream_t stream) {
-  const bool tf32 = g_opt.prefill_tf32 != 0;
-  void* xb = workspace;  // the activations in the tensor cores' operand type: bf16, or f32 rounded to tf32
+  const bool tf32 = g_opt.prefill_tf32 != 0, f16 = !tf32 && !g_opt.prefill_bf16;
+  void* xb = workspace;  // the activations in the tensor cores' operand type: f16 (rows scaled), bf16, or f32 rounded to tf32
+  float* unscale = (float*)((uint8_t*)workspace + align_up((size_t)m * k * (tf32 ? 4 : 2), 256));
   const int64_t n4 = m * k / 4;
   if (tf32)
     f32_to_tf32_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, (float*)xb);
+  else if (f16)
+    f32_to_f16_rows_kernel<<<(unsigned)m, 256, 0, stream>>>(x, (int)k, (__half*)xb, unscale);
   else
     f32_to_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, (__nv_bfloat16*)xb);
   if (cudaGetLastError() != cudaSuccess) return kLaunchFailure;
   PrefillParams p;
+  p.row_unscale = f16 ? unscale : nullptr;
   p.w = (const uint8_t*)w;
   for (int q = 0; q < 8; ++q) p.y[q] = q < n_dst ? y_dst[q] : nullptr;
   p.n_dst = n_dst;
@@ -796,8 +804,10 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   if (!device_info(&di)) return kLaunchFailure;
   const bool wide = m > 128 && ((n + kPfTileN - 1) / kPfTileN) * ((m + 255) / 256) >= di->sm_count;
 #define FQ_PREFILL(FMT)                                                                                                   \
-  e = tf32 ? (wide ? launch_prefill<FMT, 256, true>(p, xb, stream) : launch_prefill<FMT, 128, true>(p, xb, stream))       \
-           : (wide ? launch_prefill<FMT, 256>(p, xb, stream) : launch_prefill<FMT, 128>(p, xb, stream))
+  e = tf32  ? (wide ? launch_prefill<FMT, 256, true>(p, xb, stream) : launch_prefill<FMT, 128, true>(p, xb, stream))      \
+      : f16 ? (wide ? launch_prefill<FMT, 256, false, true>(p, xb, stream)                                                \
+                    : launch_prefill<FMT, 128, false, true>(p, xb, stream))                                               \
+            : (wide ? launch_prefill<FMT, 256>(p, xb, stream) : launch_prefill<FMT, 128>(p, xb, stream))
   switch (type) {
     case kQ4K: FQ_PREFILL(Q4KPrefill); break;
     case kQ6K: FQ_PREFILL(Q6KPrefill); break;
@@ -868,6 +878,7 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;
+    case FUELQ_OPT_PREFILL_BF16: g_opt.prefill_bf16 = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PEER_WAIT_MS:
       if (value < 1 || value > 60000) return kInvalidProblem;
       g_opt.peer_wait_ms = value;
@@ -886,6 +897,7 @@ int64_t fuelq_get_option(int32_t key) {
     case FUELQ_OPT_FUSED_QUANT: return g_opt.fused_quant;
     case FUELQ_OPT_PEER_WAIT_MS: return g_opt.peer_wait_ms;
     case FUELQ_OPT_PREFILL_TF32: return g_opt.prefill_tf32;
+    case FUELQ_OPT_PREFILL_BF16: return g_opt.prefill_bf16;
     default: return -1;
   }
 }
@@ -931,7 +943,7 @@ int32_t fuelq_qmatmul_numerics(int32_t ggml_type, int64_t m_total, int64_t n, in
   const int32_t st = check_problem(ggml_type, m_total, n, k);
   if (st != kOk) return -st;
   if (!prefill_available(ggml_type, m_total, n, k)) return 0;
-  return g_opt.prefill_tf32 ? 2 : 1;
+  return g_opt.prefill_tf32 ? FUELQ_NUMERICS_TF32 : g_opt.prefill_bf16 ? FUELQ_NUMERICS_BF16 : FUELQ_NUMERICS_F16;
 }
 
 int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {

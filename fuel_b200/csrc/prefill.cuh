@@ -22,6 +22,7 @@
 #include <cuda.h>
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "dequantize.cuh"
 #include "fq_common.cuh"
@@ -42,6 +43,7 @@ struct PrefillParams {
   int n_off;                 // first column this launch produces within a destination row
   int M, N, K;
   int row_bytes;
+  const float* row_unscale;  // f16 operands: factor per activation row that undoes the row's scaling (else null)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -115,6 +117,10 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+// the same with A and B as f16 (format code 0)
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 // the same with A and B as tf32 (format code 2)
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
@@ -124,6 +130,16 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);
+}
+// two f32 -> the packed 16-bit operand pair: bf16, or f16 (finite values beyond its range saturate to +-65504)
+__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+template <bool kF16>
+__device__ __forceinline__ uint32_t pack_op(float a, float b) {
+  return kF16 ? pack_f16(a, b) : pack_bf16(a, b);
 }
 // exact small-integer -> float without a conversion instruction: 0x43000000 | q << 16 is 128 + q
 __device__ __forceinline__ float small_int_f32(uint32_t q_at_bit16) { return __uint_as_float(0x43000000u | q_at_bit16); }
@@ -147,6 +163,7 @@ struct Q4KPrefill {
     r.q = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16 * (part & 1));
   }
   // -> two 16-byte chunks: elements 32 * half + 16 * quarter + (0..15) of the stage
+  template <bool kF16>
   __device__ __forceinline__ static void convert_part(const RawQ& r, int it, int part, uint4 (&out)[2]) {
     const int g = it & 3, half = part >> 1;
     const uint4 hdr = r.hdr;
@@ -170,7 +187,7 @@ struct Q4KPrefill {
       const float l0 = fmaf(d1, small_int_f32((v << 16) & 0x000f0000u), c1), l1 = fmaf(d1, small_int_f32((v << 8) & 0x000f0000u), c1);
       const float l2 = fmaf(d1, small_int_f32(v & 0x000f0000u), c1), l3 = fmaf(d1, small_int_f32((v >> 8) & 0x000f0000u), c1);
       uint32_t* o = reinterpret_cast<uint32_t*>(&out[j >> 1]) + 2 * (j & 1);
-      o[0] = pack_bf16(l0, l1), o[1] = pack_bf16(l2, l3);
+      o[0] = pack_op<kF16>(l0, l1), o[1] = pack_op<kF16>(l2, l3);
     }
   }
   // k0 = 64 * it: block it / 4, group it % 4; row points at the weight row's first block
@@ -182,15 +199,16 @@ struct Q4KPrefill {
     r.qb = *reinterpret_cast<const uint4*>(b + Q4KL::kOffQs + 32 * g + 16);
   }
   // one 32-element half of the stage (half 0: low nibbles, elements 0..31; half 1: high nibbles) -> 4 chunks
+  template <bool kF16>
   __device__ __forceinline__ static void convert_half(const Raw& r, int it, int half, uint4 (&out)[4]) {
     RawQ q;
     q.hdr = r.hdr;
     uint4 o2[2];
     q.q = r.qa;
-    convert_part(q, it, 2 * half, o2);
+    convert_part<kF16>(q, it, 2 * half, o2);
     out[0] = o2[0], out[1] = o2[1];
     q.q = r.qb;
-    convert_part(q, it, 2 * half + 1, o2);
+    convert_part<kF16>(q, it, 2 * half + 1, o2);
     out[2] = o2[0], out[3] = o2[1];
   }
   // tf32 form: stage `it` is ONE 32-element sub-block (block it / 8, sub-block it % 8); part = which 16 of them.
@@ -221,8 +239,9 @@ struct Q4KPrefill {
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
     Raw r;
     load(row, it, r);
-    convert(r, it, out);
+    convert<false>(r, it, out);
   }
+  template <bool kF16>
   __device__ __forceinline__ static void convert(const Raw& r, int it, uint4 (&out)[8]) {
     const int g = it & 3;
     const uint4 hdr = r.hdr, qa = r.qa, qb = r.qb;
@@ -249,8 +268,8 @@ struct Q4KPrefill {
       const float h2 = fmaf(d2, small_int_f32((v >> 4) & 0x000f0000u), c2), h3 = fmaf(d2, small_int_f32((v >> 12) & 0x000f0000u), c2);
       uint32_t* lo = reinterpret_cast<uint32_t*>(&out[j >> 1]) + 2 * (j & 1);       // chunk j/2 (k = 8*(j/2)..)
       uint32_t* hi = reinterpret_cast<uint32_t*>(&out[4 + (j >> 1)]) + 2 * (j & 1);  // chunk 4 + j/2
-      lo[0] = pack_bf16(l0, l1), lo[1] = pack_bf16(l2, l3);
-      hi[0] = pack_bf16(h0, h1), hi[1] = pack_bf16(h2, h3);
+      lo[0] = pack_op<kF16>(l0, l1), lo[1] = pack_op<kF16>(l2, l3);
+      hi[0] = pack_op<kF16>(h0, h1), hi[1] = pack_op<kF16>(h2, h3);
     }
   }
 };
@@ -276,6 +295,7 @@ struct Q8_0Prefill {
   }
   // half of a 64-wide stage = one 34-byte block: part p is block 2 * it + p -> chunks 4p .. 4p + 3
   __device__ __forceinline__ static int chunk_id(int part, int c) { return 4 * part + c; }
+  template <bool kF16>
   __device__ __forceinline__ static void stage_half(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
     const uint8_t* b = row + (size_t)(2 * it + part) * Q8_0L::kBytes;
     const float d = h2f_bits(ldg_u16(b));
@@ -285,9 +305,10 @@ struct Q8_0Prefill {
       const float f0 = (float)(int8_t)(v0 & 0xff) * d, f1 = (float)(int8_t)(v0 >> 8) * d;
       const float f2 = (float)(int8_t)(v1 & 0xff) * d, f3 = (float)(int8_t)(v1 >> 8) * d;
       uint32_t* o = reinterpret_cast<uint32_t*>(&out[j >> 1]) + 2 * (j & 1);
-      o[0] = pack_bf16(f0, f1), o[1] = pack_bf16(f2, f3);
+      o[0] = pack_op<kF16>(f0, f1), o[1] = pack_op<kF16>(f2, f3);
     }
   }
+  template <bool kF16>
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -299,7 +320,7 @@ struct Q8_0Prefill {
         const float f0 = (float)(int8_t)(v0 & 0xff) * d, f1 = (float)(int8_t)(v0 >> 8) * d;
         const float f2 = (float)(int8_t)(v1 & 0xff) * d, f3 = (float)(int8_t)(v1 >> 8) * d;
         uint32_t* o = reinterpret_cast<uint32_t*>(&out[4 * h + (j >> 1)]) + 2 * (j & 1);
-        o[0] = pack_bf16(f0, f1), o[1] = pack_bf16(f2, f3);
+        o[0] = pack_op<kF16>(f0, f1), o[1] = pack_op<kF16>(f2, f3);
       }
     }
   }
@@ -342,6 +363,7 @@ struct Q6KPrefill {
   // half of a 64-wide stage: part p takes l = 16p .. 16p + 15, i.e. elements l of the first 32 (chunks 2p, 2p + 1)
   // and the same l of the second 32 (chunks 4 + 2p, 5 + 2p); one scale each
   __device__ __forceinline__ static int chunk_id(int part, int c) { return c < 2 ? 2 * part + c : 4 + 2 * part + (c - 2); }
+  template <bool kF16>
   __device__ __forceinline__ static void stage_half(const uint8_t* row, int it, int part, uint4 (&out)[4]) {
     const int blk = it >> 2, half = (it >> 1) & 1, sub = it & 1;
     const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
@@ -357,10 +379,11 @@ struct Q6KPrefill {
       const int a0 = a & 0xff, a1 = a >> 8, c0 = c & 0xff, c1 = c >> 8, h0 = h & 0xff, h1 = h >> 8;
       const int qa0 = (((a0 >> nsh) & 0xF) | (((h0 >> hsh) & 3) << 4)) - 32, qa1 = (((a1 >> nsh) & 0xF) | (((h1 >> hsh) & 3) << 4)) - 32;
       const int qc0 = (((c0 >> nsh) & 0xF) | (((h0 >> (hsh + 2)) & 3) << 4)) - 32, qc1 = (((c1 >> nsh) & 0xF) | (((h1 >> (hsh + 2)) & 3) << 4)) - 32;
-      reinterpret_cast<uint32_t*>(&out[j >> 2])[j & 3] = pack_bf16(sa * (float)qa0, sa * (float)qa1);
-      reinterpret_cast<uint32_t*>(&out[2 + (j >> 2)])[j & 3] = pack_bf16(sb * (float)qc0, sb * (float)qc1);
+      reinterpret_cast<uint32_t*>(&out[j >> 2])[j & 3] = pack_op<kF16>(sa * (float)qa0, sa * (float)qa1);
+      reinterpret_cast<uint32_t*>(&out[2 + (j >> 2)])[j & 3] = pack_op<kF16>(sb * (float)qc0, sb * (float)qc1);
     }
   }
+  template <bool kF16>
   __device__ __forceinline__ static void stage(const uint8_t* row, int it, uint4 (&out)[8]) {
     const int blk = it >> 2, half = (it >> 1) & 1, sub = it & 1;
     const uint8_t* b = row + (size_t)blk * Q6KL::kBytes;
@@ -379,8 +402,8 @@ struct Q6KPrefill {
       const int qc0 = (((c0 >> nsh) & 0xF) | (((h0 >> (hsh + 2)) & 3) << 4)) - 32, qc1 = (((c1 >> nsh) & 0xF) | (((h1 >> (hsh + 2)) & 3) << 4)) - 32;
       const float sa = j < 8 ? s00 : s01, sb = j < 8 ? s10 : s11;
       // first 32 elements of the stage: l = 2j, 2j+1 ; second 32: the same l from the other ql half
-      reinterpret_cast<uint32_t*>(&out[j >> 2])[j & 3] = pack_bf16(sa * (float)qa0, sa * (float)qa1);
-      reinterpret_cast<uint32_t*>(&out[4 + (j >> 2)])[j & 3] = pack_bf16(sb * (float)qc0, sb * (float)qc1);
+      reinterpret_cast<uint32_t*>(&out[j >> 2])[j & 3] = pack_op<kF16>(sa * (float)qa0, sa * (float)qa1);
+      reinterpret_cast<uint32_t*>(&out[4 + (j >> 2)])[j & 3] = pack_op<kF16>(sb * (float)qc0, sb * (float)qc1);
     }
   }
 };
@@ -397,7 +420,10 @@ struct PrefillSmem {
 // kTf32: operands in tf32 instead of bf16 - stages are 32 wide (one 128-byte row of f32), activations are the f32
 // matrix rounded to tf32 by the pre-pass, half the MMA rate, about eight times smaller rounding error.
 // kMulti: the epilogue stores every tile into several destinations (column-sharded across GPUs).
-template <class Fmt, int kTileM, bool kTf32 = false, bool kMulti = false>
+// kF16 (not with kTf32): 16-bit operands are f16 instead of bf16 - three more mantissa bits at the same MMA rate. The
+// weights' range fits (finite values saturate at +-65504); the activation rows arrive scaled by a power of two
+// into f16's range and p.row_unscale[m] undoes it in the epilogue.
+template <class Fmt, int kTileM, bool kTf32 = false, bool kMulti = false, bool kF16 = false>
 __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t pf_smem[];
   // [stage][ weights 128 x 128 B | activations kTileM x 128 B ], each 1024-byte aligned; control block after
@@ -476,7 +502,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
           r0 = r1;
           r1 = r2;
           if (it + 3 < n_iter) load_raw(it + 3, r2);
-          Fmt::convert_half(cur, it, part, out);
+          Fmt::template convert_half<kF16>(cur, it, part, out);
         } else {
 #pragma unroll
           for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
@@ -486,7 +512,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
       } else {  // the other formats: each of the row's two threads dequantizes half of the stage
         uint4 out[4];
         if (live) {
-          Fmt::stage_half(row, it, part, out);
+          Fmt::template stage_half<kF16>(row, it, part, out);
         } else {
 #pragma unroll
           for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
@@ -504,7 +530,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
     }
   } else if (lane == 0) {
     // ---------------- MMA issue: one thread
-    constexpr uint32_t idesc = kTf32 ? umma_idesc_tf32(kPfTileN, kTileM) : umma_idesc_bf16(kPfTileN, kTileM);
+    constexpr uint32_t idesc = kTf32 ? umma_idesc_tf32(kPfTileN, kTileM) : kF16 ? umma_idesc_f16(kPfTileN, kTileM) : umma_idesc_bf16(kPfTileN, kTileM);
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -556,6 +582,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
       for (int c = 0; c < kTileM / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), v);
+        if constexpr (kF16) {  // undo the scaling of activation row m0 + 32c + j (a power of two: exact)
+          const int ml = m0 + c * 32 + lane;
+          const float mine = ml < p.M ? p.row_unscale[ml] : 1.0f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * __shfl_sync(0xffffffffu, mine, j));
+        }
         if (kMulti && vec_ok) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) tbuf[j * 36 + lane] = __uint_as_float(v[j]);
@@ -605,6 +637,46 @@ __global__ void __launch_bounds__(256) f32_to_tf32_kernel(const float* x, int64_
     uint4 o;
     o.x = to_tf32(v.x), o.y = to_tf32(v.y), o.z = to_tf32(v.z), o.w = to_tf32(v.w);
     reinterpret_cast<uint4*>(y)[i] = o;
+  }
+}
+
+// f32 -> f16 activation pre-pass, one thread block per row: the row is scaled by the power of two that brings its
+// largest magnitude into [2^13, 2^14) (exact; keeps large rows finite and small rows out of the subnormals), and
+// unscale[row] holds the inverse for the epilogue. Rows of zeros or with non-finite values are left unscaled.
+__global__ void __launch_bounds__(256) f32_to_f16_rows_kernel(const float* __restrict__ x, int K, __half* __restrict__ y,
+                                                              float* __restrict__ unscale) {
+  __shared__ float red[8];
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * K);
+  const int n4 = K >> 2;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < n4; i += 256) {
+    const float4 v = src[i];
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  float scale = 1.0f, inv = 1.0f;
+  if (amax > 0.f && amax <= 3.0e38f) {
+    int e;
+    frexpf(amax, &e);            // amax = f * 2^e, f in [0.5, 1)
+    int sh = 14 - e;             // amax * 2^sh in [2^13, 2^14)
+    sh = sh > 100 ? 100 : (sh < -100 ? -100 : sh);
+    scale = ldexpf(1.0f, sh);
+    inv = ldexpf(1.0f, -sh);
+  }
+  if (threadIdx.x == 0) unscale[blockIdx.x] = inv;
+  uint2* dst = reinterpret_cast<uint2*>(y + (size_t)blockIdx.x * K);
+  for (int i = threadIdx.x; i < n4; i += 256) {
+    const float4 v = src[i];
+    uint2 o;
+    o.x = pack_f16(v.x * scale, v.y * scale);
+    o.y = pack_f16(v.z * scale, v.w * scale);
+    dst[i] = o;
   }
 }
 

@@ -72,11 +72,15 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
                                     4000, 1..60000): a kernel whose peer never delivers records device error 6 after
                                     this long and carries on, so the context stays usable */
 #define FUELQ_OPT_PREFILL_TF32 8  /* 1: the tensor-core path (m_total above the integer crossover) multiplies in tf32
-                                    instead of bf16: weights dequantized to f32 and rounded to tf32, activations
-                                    rounded to tf32, f32 accumulation. Half the MMA rate, twice the workspace
-                                    (4 bytes per activation; ask fuelq_qmatmul_workspace_bytes after setting it),
-                                    and results within 1e-3 of the exact dequantized product where bf16 reaches
-                                    about 2.5e-3 (default 0) */
+                                    instead of 16-bit operands: weights dequantized to f32 and rounded to tf32,
+                                    activations rounded to tf32, f32 accumulation. Half the MMA rate, twice the
+                                    workspace (4 bytes per activation; ask fuelq_qmatmul_workspace_bytes after
+                                    setting it); the same 10 mantissa bits as the default f16 operands (default 0) */
+#define FUELQ_OPT_PREFILL_BF16 9  /* 1: the tensor-core path's 16-bit operands are bf16 (7 mantissa bits: results about
+                                    2.5e-3 from the exact dequantized product). 0 (default): f16 (10 mantissa bits,
+                                    about 4e-4, same MMA rate): weights dequantized straight to f16 (finite values
+                                    saturate at +-65504, far beyond any GGUF weight), every activation row scaled
+                                    by a power of two into f16's range and the result row scaled back, both exact */
 int32_t fuelq_set_option(int32_t key, int64_t value);
 int64_t fuelq_get_option(int32_t key);
 
@@ -106,15 +110,16 @@ size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t
 /* Which arithmetic fuelq_qmatmul uses for this problem under the current options. The reference's CPU path
  * (fuel_quantized::matmul, k_quants.rs:2284-2331) has ONE arithmetic for every batch size: activations
  * re-quantized to 8-bit blocks, exact integer dot products per sub-block, f32 block sums. This library keeps that
- * arithmetic up to the crossover batch size and multiplies dequantized weights with bf16 (or tf32) activations
+ * arithmetic up to the crossover batch size and multiplies dequantized weights with f16 (or bf16, tf32) activations
  * on the tensor cores above it, so RESULTS CHANGE CLASS AT THE CROSSOVER: integer results sit within f32
  * summation order (~1e-6) of the reference's, tensor-core results differ from them by the activation
  * quantization the reference applies and this path does not (up to ~2e-2 of the largest output) and from the
- * exact dequantized product by ~2.5e-3 (bf16) or ~1e-3 (tf32). Callers that need the reference's numbers at any
+ * exact dequantized product by ~4e-4 (f16, the default, and tf32) or ~2.5e-3 (bf16). Callers that need the reference's numbers at any
  * batch size raise FUELQ_OPT_DECODE_MAX_M. Returns one of the values below, or a negative status (-FUELQ_...). */
 #define FUELQ_NUMERICS_INTEGER 0 /* the reference's arithmetic */
 #define FUELQ_NUMERICS_BF16 1
 #define FUELQ_NUMERICS_TF32 2
+#define FUELQ_NUMERICS_F16 3
 int32_t fuelq_qmatmul_numerics(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k);
 
 /* 0 if fuelq_qmatmul handles (type, m_total, n, k), else the status it would return. */

@@ -15,6 +15,7 @@ pub const FUELQ_OPT_PREFILL_TF32: i32 = 8;
 pub const FUELQ_NUMERICS_INTEGER: i32 = 0;
 pub const FUELQ_NUMERICS_BF16: i32 = 1;
 pub const FUELQ_NUMERICS_TF32: i32 = 2;
+pub const FUELQ_NUMERICS_F16: i32 = 3;
 
 /// The handshake envelope, `fuel_kernel_seam_announce::SeamHello` field for field (56 bytes).
 #[repr(C)]

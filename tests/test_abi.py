@@ -79,8 +79,16 @@ def test_argument_validation_needs_no_device(L):
     assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 4096) == L.NUMERICS_INTEGER
     assert f.fuelq_qmatmul_numerics(Q8_0, 16, 4096, 4096) == L.NUMERICS_INTEGER
     assert f.fuelq_qmatmul_numerics(Q8_0, 64, 4096, 4096) == L.NUMERICS_INTEGER     # the library's choice: up to 64 rows
-    assert f.fuelq_qmatmul_numerics(Q8_0, 65, 4096, 4096) == L.NUMERICS_BF16
-    assert f.fuelq_qmatmul_numerics(Q8_0, 2048, 4096, 4096) == L.NUMERICS_BF16
+    assert f.fuelq_qmatmul_numerics(Q8_0, 65, 4096, 4096) == L.NUMERICS_F16       # tensor cores, f16 operands by default
+    assert f.fuelq_qmatmul_numerics(Q8_0, 2048, 4096, 4096) == L.NUMERICS_F16
+    try:
+        assert f.fuelq_set_option(L.OPT_PREFILL_BF16, 1) == L.OK
+        assert f.fuelq_qmatmul_numerics(Q8_0, 2048, 4096, 4096) == L.NUMERICS_BF16
+        assert f.fuelq_set_option(L.OPT_PREFILL_TF32, 1) == L.OK
+        assert f.fuelq_qmatmul_numerics(Q8_0, 2048, 4096, 4096) == L.NUMERICS_TF32
+    finally:
+        f.fuelq_set_option(L.OPT_PREFILL_BF16, 0)
+        f.fuelq_set_option(L.OPT_PREFILL_TF32, 0)
     assert f.fuelq_qmatmul_numerics(2, 2048, 4096, 4096) == L.NUMERICS_INTEGER   # Q4_0 has no tensor-core form
     assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 100) == -L.INVALID_PROBLEM
 

@@ -1,16 +1,18 @@
 """Tensor-core (tcgen05) path for large M, through the C ABI.
 
 Ground truth is the float oracle: exactly dequantized weights (the reference's to_float) times the
-f32 activations, accumulated in f64. The GPU path rounds BOTH operands to bf16 (benchmark configuration 3
-asks for exactly that), and that alone fixes the attainable error: a bf16 rounding is uniform in
-+-2^-9 relative, rms 1.13e-3 per operand, 1.6e-3 per product, and the products' errors add like a
-random walk just as the result does, so  ||y - r||_F / ||r||_F ~ 1.6e-3  whatever K is, and the
-largest of ~10^5 outputs sits near 2.5e-3 of max|r|. The stated 1e-3 is therefore not reachable
-with bf16 operands by any kernel; the bars here are the ones bf16 allows, with margin:
-    relative Frobenius error <= 2.5e-3,   max|y - r| / max|r| <= 5e-3,
-and the integer mat-vec path (tests/test_gpu_kernels.py) remains the one held to 1e-3 and tighter.
-Also checked: agreement with the integer path within the activation-quantization gap, tile edges,
-exact linearity under power-of-two scaling.
+f32 activations, accumulated in f64. The bar is the one stated for benchmark configuration 3: every output
+within 1e-3 of the tensor's largest value (and the relative Frobenius error within 1e-3).
+
+What the operand type allows. A rounding to p mantissa bits is uniform in +-2^-(p+1) relative, rms 2^-(p+1)/sqrt(3)
+per operand, sqrt(2) times that per product, and the products' errors add like a random walk just as the result
+does, so ||y - r||_F / ||r||_F is about that figure whatever K is: 1.6e-3 for bf16 (p = 7; the largest of ~10^5
+outputs near 2.5e-3 of max|r|), 4e-4 for f16 and tf32 (p = 10). The default path therefore uses f16 operands
+(FUELQ_NUMERICS_F16: weights dequantized straight to f16, activation rows scaled by a power of two into f16's range
+and the output rows scaled back, both exact) and is held to 1e-3 here; bf16 operands are an option
+(FUELQ_OPT_PREFILL_BF16), tested to the bars bf16 allows (max 5e-3, Frobenius 2.5e-3); tf32 is the third.
+Also checked: agreement with the integer path within the activation-quantization gap, tile edges, rows of very
+large and very small magnitude, exact linearity under power-of-two scaling.
 """
 import numpy as np
 import pytest
@@ -50,8 +52,8 @@ def test_prefill_q4k_matches_float_oracle(ops, oracle, m, n, k):
     y = torch.full((m, n), float("nan"), device="cuda")
     got = ops.qmatmul(T.Q4K, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda(), out=y).cpu().numpy()
     assert np.isfinite(got).all()
-    assert np.abs(got - want).max() / np.abs(want).max() <= 5e-3
-    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2.5e-3
+    assert np.abs(got - want).max() / np.abs(want).max() <= 1e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 6e-4
     # and it tells the same story as the integer path (8-bit activations) on the same inputs
     ref_int = oracle.matmul(oracle.Q4K, x[:4], wb, n)
     assert np.abs(got[:4] - ref_int).max() / np.abs(ref_int).max() <= 2e-2
@@ -66,8 +68,8 @@ def test_prefill_other_formats_match_float_oracle(ops, oracle, name, m, n, k):
     x = _x(m, k, seed=m)
     want = oracle.matmul_dequant_f64(ot, x, wb, n)
     got = ops.qmatmul(t, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda()).cpu().numpy()
-    assert np.abs(got - want).max() / np.abs(want).max() <= 5e-3
-    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2.5e-3
+    assert np.abs(got - want).max() / np.abs(want).max() <= 1e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 6e-4
 
 
 def test_prefill_config3_shape_sampled_rows(ops, oracle):
@@ -85,9 +87,10 @@ def test_prefill_config3_shape_sampled_rows(ops, oracle):
     rows = np.array([0, 1, 127, 128, 255, 256, 1000, 2047])
     want = oracle.matmul_dequant_f64(oracle.Q4K, x[rows].cpu().numpy(), wq.cpu().numpy(), n)
     got = y[rows].cpu().numpy()
-    assert np.abs(got - want).max() / np.abs(want).max() <= 5e-3
-    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2.5e-3
-    # linearity, a size-independent property: f(2x) == 2 f(x) exactly (powers of two commute with bf16 rounding)
+    assert np.abs(got - want).max() / np.abs(want).max() <= 1e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 6e-4
+    # linearity, a size-independent property: f(2x) == 2 f(x) exactly (powers of two commute with the operand rounding
+    # and with the row scaling)
     y2 = ops.qmatmul(T.Q4K, wq, n, x * 2.0)
     assert torch.equal(y2, y * 2.0)
 
@@ -125,3 +128,42 @@ def test_prefill_tf32_option_meets_the_1e3_bar(ops, oracle, name, m, n, k):
     assert np.isfinite(got).all()
     assert np.abs(got - want).max() / np.abs(want).max() <= 1e-3
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 5e-4
+
+
+
+@pytest.mark.parametrize("name,m,n,k", [("q4k", 200, 300, 1024), ("q6k", 130, 129, 2048), ("q8_0", 257, 300, 1024)])
+def test_prefill_bf16_option_lands_where_bf16_can(ops, oracle, name, m, n, k):
+    """FUELQ_OPT_PREFILL_BF16: the operand type benchmark configuration 3 names. Its bars are the ones 7 mantissa bits allow."""
+    from fuel_b200 import GgmlDType as T, _lib
+    t, ot = {"q4k": (T.Q4K, oracle.Q4K), "q6k": (T.Q6K, oracle.Q6K), "q8_0": (T.Q8_0, oracle.Q8_0)}[name]
+    wb = oracle.quantize(ot, _w(n, k, seed=n))
+    x = _x(m, k, seed=m)
+    want = oracle.matmul_dequant_f64(ot, x, wb, n)
+    try:
+        _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_PREFILL_BF16, 1), "set_option")
+        assert _lib.lib.fuelq_qmatmul_numerics(int(t), m, n, k) == _lib.NUMERICS_BF16
+        got = ops.qmatmul(t, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda()).cpu().numpy()
+    finally:
+        _lib.lib.fuelq_set_option(_lib.OPT_PREFILL_BF16, 0)
+    assert _lib.lib.fuelq_qmatmul_numerics(int(t), m, n, k) == _lib.NUMERICS_F16
+    assert np.abs(got - want).max() / np.abs(want).max() <= 5e-3
+    err = np.linalg.norm(got - want) / np.linalg.norm(want)
+    assert 6e-4 < err <= 2.5e-3     # and it really is the coarser operand type
+
+
+def test_prefill_rows_of_any_magnitude(ops, oracle):
+    """f16 operands: each activation row is scaled by a power of two into f16's range and its output row scaled back, so
+    rows far outside f16's range (1e7, 1e-9) come out as accurately as ordinary ones; a row of zeros stays zero."""
+    from fuel_b200 import GgmlDType as T
+    m, n, k = 96, 256, 1024
+    wb = oracle.quantize(oracle.Q4K, _w(n, k, seed=5))
+    x = _x(m, k, seed=6)
+    mags = np.ones(m, np.float32)
+    mags[1], mags[2], mags[3], mags[4], mags[5] = 1e7, 1e-9, 70000.0, 3e-5, 0.0
+    x = x * mags[:, None]
+    want = oracle.matmul_dequant_f64(oracle.Q4K, x, wb, n)
+    got = ops.qmatmul(T.Q4K, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.isfinite(got).all() and not got[5].any()
+    for r in range(m):
+        if mags[r] != 0.0:
+            assert np.abs(got[r] - want[r]).max() / np.abs(want[r]).max() <= 1.5e-3, (r, mags[r])
