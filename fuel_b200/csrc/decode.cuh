@@ -203,6 +203,66 @@ struct Q4_0Decode {
   }
 };
 
+// The other 32-element formats (k_quants.rs:285-313 Q4_1, :401-422 Q5_0, :501-533 Q5_1): nibble j is element j (low)
+// / j + 16 (high); Q5 adds bit j of the little-endian word qh as the fifth bit of element j; Q4_1 / Q5_1 are
+// unsigned with a per-block minimum m, whose share of the dot product is m * s with the activation block's
+// s = d * sum(q) (Q8_1, kept as an f32 plane in the slot Q8_K uses for its block sums).
+template <class L, bool kFive, bool kMin>
+struct Legacy32Decode {
+  static constexpr int kUnitsPerBlock = 1;
+  static constexpr int kBlockElems = 32;
+  template <int MT>
+  __device__ __forceinline__ static void unit(const uint8_t* rowp, int u, const ActPlanes& a, int k, int m0, int mc,
+                                              float (&acc)[MT]) {
+    const uint8_t* b = rowp + u * L::kBytes;
+    const float d = h2f_bits(lds_u16(b));
+    float mval = 0.f;
+    if constexpr (kMin) mval = h2f_bits(lds_u16(b + 2));
+    uint32_t qh = 0;
+    if constexpr (kFive) qh = lds_u32_2b(b + L::kBytes - 20);  // the four bytes before the nibbles
+    int lo[4], hi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t v = lds_u32_2b(b + L::kBytes - 16 + 4 * j);
+      uint32_t l = v & 0x0f0f0f0fu, h = (v >> 4) & 0x0f0f0f0fu;
+      if constexpr (kFive) {
+        // bits 4j..4j+3 of qh -> bit 4 of bytes 0..3 (elements 4j..4j+3); bits 16+4j.. for the high nibbles
+        const uint32_t bl = (qh >> (4 * j)) & 0xfu, bh = (qh >> (16 + 4 * j)) & 0xfu;
+        l |= ((bl & 1u) << 4) | ((bl & 2u) << 11) | ((bl & 4u) << 18) | ((bl & 8u) << 25);
+        h |= ((bh & 1u) << 4) | ((bh & 2u) << 11) | ((bh & 4u) << 18) | ((bh & 8u) << 25);
+      }
+      if constexpr (kFive && !kMin) {  // Q5_0: value - 16 per byte, as signed bytes (0..31 -> -16..15)
+        l = ((l | 0x80808080u) - 0x10101010u) ^ 0x80808080u;
+        h = ((h | 0x80808080u) - 0x10101010u) ^ 0x80808080u;
+      }
+      lo[j] = (int)l, hi[j] = (int)h;
+    }
+    const int nblk = k >> 5;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      if (i < mc) {
+        const int m = m0 + i;
+        const int4* q8 = reinterpret_cast<const int4*>(a.qs + (size_t)m * k + u * 32);
+        const int4 a0 = q8[0], a1 = q8[1];
+        int s = dp4a_ss(lo[0], a0.x, 0);
+        s = dp4a_ss(lo[1], a0.y, s);
+        s = dp4a_ss(lo[2], a0.z, s);
+        s = dp4a_ss(lo[3], a0.w, s);
+        s = dp4a_ss(hi[0], a1.x, s);
+        s = dp4a_ss(hi[1], a1.y, s);
+        s = dp4a_ss(hi[2], a1.z, s);
+        s = dp4a_ss(hi[3], a1.w, s);
+        float t = ((float)s * d) * a.d[(size_t)m * nblk + u];
+        if constexpr (kMin) t += mval * reinterpret_cast<const float*>(a.bsums)[(size_t)m * nblk + u];
+        acc[i] += t;
+      }
+    }
+  }
+};
+using Q4_1Decode = Legacy32Decode<Q4_1L, false, true>;
+using Q5_0Decode = Legacy32Decode<Q5_0L, true, false>;
+using Q5_1Decode = Legacy32Decode<Q5_1L, true, true>;
+
 // ------------------------------------------------------------------ the kernel
 struct DecodeSmemHeader {
   uint64_t full[kDecodeMaxStages];

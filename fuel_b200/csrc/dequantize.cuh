@@ -159,6 +159,31 @@ __global__ void __launch_bounds__(256) dequant_q4_0_kernel(const uint8_t* __rest
   }
 }
 
+// Q4_1 / Q5_0 / Q5_1 (k_quants.rs:354-374, 463-485, 578-602): one thread per 4 bytes of nibbles, elements 4p..4p+3
+// and 16+4p..; q*d + m as a product and a sum (two roundings), (q - 16)*d for Q5_0
+template <typename T, class L, bool kFive, bool kMin>
+__global__ void __launch_bounds__(256) dequant_legacy32_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 2;
+  const int part = (int)(u & 3);
+  const uint8_t* b = w + blk * L::kBytes;
+  const float d = h2f_bits(ldg_u16(b));
+  const float m = kMin ? h2f_bits(ldg_u16(b + 2)) : 0.f;
+  const uint32_t qh = kFive ? ldg_u32_2b(b + L::kBytes - 20) : 0u;
+  const uint32_t v = ldg_u32_2b(b + L::kBytes - 16 + 4 * part);
+  T* out = y + blk * 32 + 4 * part;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int byte = (v >> (8 * t)) & 0xff, j = 4 * part + t;
+    int q0 = byte & 0xF, q1 = byte >> 4;
+    if (kFive) q0 |= (int)((qh >> j) & 1u) << 4, q1 |= (int)((qh >> (j + 16)) & 1u) << 4;
+    if (kFive && !kMin) q0 -= 16, q1 -= 16;
+    const float p0 = __fmul_rn((float)q0, d), p1 = __fmul_rn((float)q1, d);
+    out[t] = cvt_out<T>(kMin ? __fadd_rn(p0, m) : p0);
+    out[16 + t] = cvt_out<T>(kMin ? __fadd_rn(p1, m) : p1);
+  }
+}
 // Q8_K blocks back to f32 (x.d * q, k_quants.rs:2269-2280); one thread per 4 elements
 template <typename T>
 __global__ void __launch_bounds__(256) dequant_q8k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {

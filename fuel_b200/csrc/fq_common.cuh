@@ -20,7 +20,7 @@ enum Status : int32_t {
 };
 
 // ---- GGUF type ids (fuel-ir/src/quantized.rs:35-75)
-enum GgmlType : int32_t { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ8_0 = 8, kQ4K = 12, kQ5K = 13, kQ6K = 14, kQ8K = 15, kBF16 = 30 };
+enum GgmlType : int32_t { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ4_1 = 3, kQ5_0 = 6, kQ5_1 = 7, kQ8_0 = 8, kQ8_1 = 9, kQ4K = 12, kQ5K = 13, kQ6K = 14, kQ8K = 15, kBF16 = 30 };
 
 constexpr int QK_K = 256;
 constexpr int QK_S = 32;
@@ -28,7 +28,11 @@ constexpr int QK_S = 32;
 // Byte layouts (fuel-quantized/src/k_quants.rs:56-169). Offsets only; the kernels
 // address blocks by byte because Q6_K / Q8_0 / Q4_0 rows are only 2-byte aligned.
 struct Q4_0L { static constexpr int kBytes = 18, kElems = 32, kOffD = 0, kOffQs = 2; };
+struct Q4_1L { static constexpr int kBytes = 20, kElems = 32, kOffD = 0, kOffM = 2, kOffQs = 4; };
+struct Q5_0L { static constexpr int kBytes = 22, kElems = 32, kOffD = 0, kOffQh = 2, kOffQs = 6; };
+struct Q5_1L { static constexpr int kBytes = 24, kElems = 32, kOffD = 0, kOffM = 2, kOffQh = 4, kOffQs = 8; };
 struct Q8_0L { static constexpr int kBytes = 34, kElems = 32, kOffD = 0, kOffQs = 2; };
+struct Q8_1L { static constexpr int kBytes = 36, kElems = 32, kOffD = 0, kOffS = 2, kOffQs = 4; };
 struct Q4KL { static constexpr int kBytes = 144, kElems = 256, kOffD = 0, kOffDmin = 2, kOffScales = 4, kOffQs = 16; };
 struct Q5KL { static constexpr int kBytes = 176, kElems = 256, kOffD = 0, kOffDmin = 2, kOffScales = 4, kOffQh = 16, kOffQs = 48; };
 struct Q6KL { static constexpr int kBytes = 210, kElems = 256, kOffQl = 0, kOffQh = 128, kOffScales = 192, kOffD = 208; };
@@ -36,7 +40,7 @@ struct Q8KL { static constexpr int kBytes = 292, kElems = 256, kOffD = 0, kOffQs
 
 __host__ __device__ inline int block_elems(int t) {
   switch (t) {
-    case kQ4_0: case kQ8_0: return 32;
+    case kQ4_0: case kQ4_1: case kQ5_0: case kQ5_1: case kQ8_0: case kQ8_1: return 32;
     case kQ4K: case kQ5K: case kQ6K: case kQ8K: return 256;
     default: return 0;
   }
@@ -44,6 +48,10 @@ __host__ __device__ inline int block_elems(int t) {
 __host__ __device__ inline int block_bytes(int t) {
   switch (t) {
     case kQ4_0: return 18;
+    case kQ4_1: return 20;
+    case kQ5_0: return 22;
+    case kQ5_1: return 24;
+    case kQ8_1: return 36;
     case kQ8_0: return 34;
     case kQ4K: return 144;
     case kQ5K: return 176;
@@ -53,14 +61,19 @@ __host__ __device__ inline int block_bytes(int t) {
   }
 }
 // The reference quantizes activations to the weight format's dot-product partner
-// (GgmlType::VecDotType, k_quants.rs:174,608,1372,1930): Q8_K for k-quants, Q8_0 otherwise.
-__host__ __device__ inline int act_type_for(int t) { return (t == kQ4K || t == kQ5K || t == kQ6K) ? kQ8K : kQ8_0; }
+// (GgmlType::VecDotType, k_quants.rs:174,275,380,491,608,1372,1930): Q8_K for k-quants, Q8_1 for the formats with a
+// per-block minimum (Q4_1, Q5_1), Q8_0 otherwise.
+__host__ __device__ inline int act_type_for(int t) {
+  return (t == kQ4K || t == kQ5K || t == kQ6K) ? kQ8K : (t == kQ4_1 || t == kQ5_1) ? kQ8_1 : kQ8_0;
+}
 
 // ---- internal activation layout ("packed"): the same numbers as the reference's
 // Q8_K / Q8_0 blocks, split into planes so every plane is 16-byte aligned:
 //   qs    int8  [m][k]
 //   d     f32   [m][k / act_block]      (for Q8_0: the f16-rounded scale widened to f32)
 //   bsums int16 [m][k / 16]             (Q8_K only)
+//         Q8_1 instead keeps, in the same slot, f32 [m][k / 32]: the block's s = d * sum(q), f16-rounded as the
+//         reference stores it (k_quants.rs:728-757), widened to f32 (same byte count as the int16 plane)
 struct ActPlanes {
   const int8_t* qs;
   const float* d;
@@ -71,7 +84,7 @@ __host__ __device__ inline size_t act_packed_bytes(int weight_type, int64_t m, i
   const int at = act_type_for(weight_type);
   const int be = block_elems(at);
   size_t b = align_up((size_t)m * k, 256) + align_up((size_t)m * (k / be) * 4, 256);
-  if (at == kQ8K) b += align_up((size_t)m * (k / 16) * 2, 256);
+  if (at == kQ8K || at == kQ8_1) b += align_up((size_t)m * (k / 16) * 2, 256);
   return b;
 }
 __host__ __device__ inline ActPlanes act_planes(void* base, int weight_type, int64_t m, int64_t k) {
@@ -83,7 +96,7 @@ __host__ __device__ inline ActPlanes act_planes(void* base, int weight_type, int
   p += align_up((size_t)m * k, 256);
   a.d = (const float*)p;
   p += align_up((size_t)m * (k / be) * 4, 256);
-  a.bsums = (at == kQ8K) ? (const int16_t*)p : nullptr;
+  a.bsums = (at == kQ8K || at == kQ8_1) ? (const int16_t*)p : nullptr;
   return a;
 }
 

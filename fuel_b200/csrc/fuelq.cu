@@ -61,7 +61,9 @@ bool device_info(DeviceInfo** out) {
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-bool supported_weight(int t) { return t == kQ4_0 || t == kQ8_0 || t == kQ4K || t == kQ5K || t == kQ6K; }
+bool supported_weight(int t) {
+  return t == kQ4_0 || t == kQ4_1 || t == kQ5_0 || t == kQ5_1 || t == kQ8_0 || t == kQ4K || t == kQ5K || t == kQ6K;
+}
 
 // launch with or without the programmatic-dependent-launch attribute
 template <typename... KArgs, typename... Args>
@@ -110,14 +112,24 @@ int32_t quantize_act_impl(int weight_type, int64_t m, int64_t k, const float* x,
   const int64_t ng = (total + QK_K - 1) / QK_K;
   const dim3 grid((unsigned)((ng + warps_per_cta - 1) / warps_per_cta)), block(32 * warps_per_cta);
   cudaError_t e;
-  if (ref_out) {
+  if (at == kQ8_1) {
+    if (ref_out) {
+      if (!aligned(ref_out, 4)) return kMisaligned;
+      e = launch(quantize_q8_0_kernel<true, true>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)ref_out, (int8_t*)nullptr,
+                 (float*)nullptr, zero_word, (int)early_x, (float*)nullptr);
+    } else {
+      ActPlanes a = act_planes(packed, weight_type, m, k);
+      e = launch(quantize_q8_0_kernel<false, true>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)nullptr, (int8_t*)a.qs,
+                 (float*)a.d, zero_word, (int)early_x, (float*)a.bsums);
+    }
+  } else if (ref_out) {
     if (!aligned(ref_out, 2)) return kMisaligned;
-    e = launch(quantize_q8_0_kernel<true>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)ref_out, (int8_t*)nullptr,
-               (float*)nullptr, zero_word, (int)early_x);
+    e = launch(quantize_q8_0_kernel<true, false>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)ref_out, (int8_t*)nullptr,
+               (float*)nullptr, zero_word, (int)early_x, (float*)nullptr);
   } else {
     ActPlanes a = act_planes(packed, weight_type, m, k);
-    e = launch(quantize_q8_0_kernel<false>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)nullptr, (int8_t*)a.qs,
-               (float*)a.d, zero_word, (int)early_x);
+    e = launch(quantize_q8_0_kernel<false, false>, grid, block, 0, stream, x, ng, nb32, (uint8_t*)nullptr, (int8_t*)a.qs,
+               (float*)a.d, zero_word, (int)early_x, (float*)nullptr);
   }
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
@@ -479,6 +491,18 @@ int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, co
     case kQ4_0:
       p.units_per_row = (int)(k / 32);
       e = launch_decode_fmt<Q4_0Decode>(p, pl, stream);
+      break;
+    case kQ4_1:
+      p.units_per_row = (int)(k / 32);
+      e = launch_decode_fmt<Q4_1Decode>(p, pl, stream);
+      break;
+    case kQ5_0:
+      p.units_per_row = (int)(k / 32);
+      e = launch_decode_fmt<Q5_0Decode>(p, pl, stream);
+      break;
+    case kQ5_1:
+      p.units_per_row = (int)(k / 32);
+      e = launch_decode_fmt<Q5_1Decode>(p, pl, stream);
       break;
     default:
       return kNotSupported;
@@ -1131,6 +1155,9 @@ int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x,
   switch (ggml_type) {
     case kQ8_0: quantize_w_q8_0_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ4_0: quantize_w_q4_0_kernel<<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ4_1: quantize_w_legacy32_kernel<Q4_1L, false, true><<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ5_0: quantize_w_legacy32_kernel<Q5_0L, true, false><<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ5_1: quantize_w_legacy32_kernel<Q5_1L, true, true><<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ4K: quantize_w_q4k_kernel<<<(unsigned)((nb * 8 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ6K: quantize_w_q6k_kernel<<<(unsigned)((nb * 16 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     default: return kNotSupported;
@@ -1599,7 +1626,7 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
     case kQ4K: case kQ5K: units = nb * 8; break;
     case kQ6K: units = nb * 16; break;
     case kQ8_0: units = nb * 4; break;
-    case kQ4_0: units = nb * 4; break;
+    case kQ4_0: case kQ4_1: case kQ5_0: case kQ5_1: units = nb * 4; break;
     case kQ8K: units = nb * 64; break;
     default: return kNotSupported;
   }
@@ -1619,6 +1646,19 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
     case kQ6K: FQ_DEQ(dequant_q6k_kernel); break;
     case kQ8_0: FQ_DEQ(dequant_q8_0_kernel); break;
     case kQ4_0: FQ_DEQ(dequant_q4_0_kernel); break;
+#define FQ_DEQ_L(L, FIVE, MIN)                                                                                  \
+  do {                                                                                                          \
+    if (out_type == kF32)                                                                                       \
+      dequant_legacy32_kernel<float, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (float*)y);            \
+    else if (out_type == kF16)                                                                                  \
+      dequant_legacy32_kernel<__half, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (__half*)y);          \
+    else                                                                                                        \
+      dequant_legacy32_kernel<__nv_bfloat16, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (__nv_bfloat16*)y); \
+  } while (0)
+    case kQ4_1: FQ_DEQ_L(Q4_1L, false, true); break;
+    case kQ5_0: FQ_DEQ_L(Q5_0L, true, false); break;
+    case kQ5_1: FQ_DEQ_L(Q5_1L, true, true); break;
+#undef FQ_DEQ_L
     case kQ8K: FQ_DEQ(dequant_q8k_kernel); break;
   }
 #undef FQ_DEQ

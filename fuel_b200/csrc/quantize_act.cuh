@@ -193,11 +193,14 @@ __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float* x, int64
 }
 
 // One warp per 256 elements = eight Q8_0 blocks; a block is 8 neighbouring lanes of one half.
-template <bool kRefLayout>
+// kQ81: Q8_1 blocks instead (BlockQ8_1::from_float, k_quants.rs:728-757): the same d and quants, plus
+// s = f16(sum of the quants) * d in half arithmetic (both factors f16, their f32 product rounded to f16); 36-byte
+// blocks {d, s, qs} in the reference layout, or a third plane out_s (f32) beside qs and d.
+template <bool kRefLayout, bool kQ81 = false>
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* x, int64_t n_groups /* of 256 */,
                                                             int64_t n_blocks32, uint8_t* out_ref,
                                                             int8_t* out_qs, float* out_d, unsigned* zero_word,
-                                                            int early_x) {
+                                                            int early_x, float* out_s = nullptr) {
   pdl_launch_dependents();
   if (!early_x) pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -233,6 +236,44 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* x, int6
   const uint32_t p1 = qz(v1.x, id1) | (qz(v1.y, id1) << 8) | (qz(v1.z, id1) << 16) | (qz(v1.w, id1) << 24);
   const __half h0 = __float2half_rn(d0), h1 = __float2half_rn(d1);
   const int sub = lane & 7;
+  if constexpr (kQ81) {
+    int s0 = __dp4a((int)p0, 0x01010101, 0), s1 = __dp4a((int)p1, 0x01010101, 0);  // sum of the four signed quants
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) {
+      s0 += __shfl_xor_sync(0xffffffffu, s0, off);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+    }
+    // (a block whose scale overflows f16 and whose quants sum to zero gives 0 * inf: the reference's x86 build stores
+    // the default NaN of that product, sign bit set, 0xFE00 as f16)
+    auto s_field = [](int sum, __half d) -> __half {
+      const float prod = __half2float(__float2half_rn((float)sum)) * __half2float(d);
+      return prod != prod ? __ushort_as_half((unsigned short)0xFE00u) : __float2half_rn(prod);
+    };
+    const __half sh0 = s_field(s0, h0), sh1 = s_field(s1, h1);
+    if (kRefLayout) {  // 36-byte blocks are 4-byte aligned
+      if (ok0) {
+        uint32_t* b = reinterpret_cast<uint32_t*>(out_ref + blk0 * Q8_1L::kBytes);
+        if (sub == 0) b[0] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(sh0) << 16);
+        b[1 + sub] = p0;
+      }
+      if (ok1) {
+        uint32_t* b = reinterpret_cast<uint32_t*>(out_ref + blk1 * Q8_1L::kBytes);
+        if (sub == 0) b[0] = (uint32_t)__half_as_ushort(h1) | ((uint32_t)__half_as_ushort(sh1) << 16);
+        b[1 + sub] = p1;
+      }
+    } else {
+      uint32_t* qs = reinterpret_cast<uint32_t*>(out_qs + base);
+      if (ok0) {
+        qs[lane] = p0;
+        if (sub == 0) out_d[blk0] = __half2float(h0), out_s[blk0] = __half2float(sh0);
+      }
+      if (ok1) {
+        qs[32 + lane] = p1;
+        if (sub == 0) out_d[blk1] = __half2float(h1), out_s[blk1] = __half2float(sh1);
+      }
+    }
+    return;
+  }
   if (kRefLayout) {
     // 34-byte blocks: 2-byte aligned only -> 16-bit stores
     if (ok0) {

@@ -78,6 +78,72 @@ __global__ void __launch_bounds__(128) quantize_w_q4_0_kernel(const float* __res
   }
 }
 
+// Q4_1 / Q5_0 / Q5_1 (BlockQ4_1::from_float k_quants.rs:315-351, BlockQ5_0 :424-460, BlockQ5_1 :535-575): one thread
+// per block. kFive: a fifth bit per element collected in the 32-bit word qh; kMin: scale over [min, max] with the
+// minimum stored, values unsigned. Rust's float -> integer casts saturate and truncate; the additions and products
+// are separate roundings.
+template <class L, bool kFive, bool kMin>
+__global__ void __launch_bounds__(128) quantize_w_legacy32_kernel(const float* __restrict__ x, int64_t nb,
+                                                                  uint8_t* __restrict__ out) {
+  const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nb) return;
+  float v[32];
+  const float4* src = reinterpret_cast<const float4*>(x + b * 32);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float4 t = src[j];
+    v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
+  }
+  float d, mn = 0.f;
+  if constexpr (kMin) {
+    float mx = -INFINITY;
+    mn = INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) mn = fminf(v[j], mn), mx = fmaxf(v[j], mx);
+    d = __fdiv_rn(__fsub_rn(mx, mn), kFive ? 31.0f : 15.0f);
+  } else {
+    float amax = 0.f, mx = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float a = fabsf(v[j]);
+      if (amax < a) amax = a, mx = v[j];
+    }
+    d = __fdiv_rn(mx, -16.0f);
+  }
+  const float id = d != 0.f ? __fdiv_rn(1.0f, d) : 0.f;
+  uint16_t* o = reinterpret_cast<uint16_t*>(out + b * L::kBytes);
+  o[0] = __half_as_ushort(__float2half_rn(d));
+  if constexpr (kMin) o[1] = __half_as_ushort(__float2half_rn(mn));
+  auto quant = [&](float xv) -> uint32_t {
+    if constexpr (kMin) {
+      // ((x - min) * id + 0.5) as u8 (saturating); Q4_1 then takes min(15, .), Q5_1 keeps the low five bits
+      const int t = qw_clamp(__float2int_rz(__fadd_rn(__fmul_rn(__fsub_rn(xv, mn), id), 0.5f)), 0, 255);
+      return (uint32_t)(kFive ? t : (t < 15 ? t : 15));
+    } else {
+      // ((x * id + 16.5) as i8).min(31) as u8
+      const int t = qw_clamp(__float2int_rz(__fadd_rn(__fmul_rn(xv, id), 16.5f)), -128, 127);
+      return (uint32_t)((t < 31 ? t : 31) & 0xff);
+    }
+  };
+  uint32_t qh = 0;
+  uint16_t* qs = reinterpret_cast<uint16_t*>(out + b * L::kBytes + L::kBytes - 16);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t a0 = quant(v[2 * j]), a1 = quant(v[16 + 2 * j]), c0 = quant(v[2 * j + 1]), c1 = quant(v[16 + 2 * j + 1]);
+    qs[j] = (uint16_t)(((a0 & 0xf) | ((a1 & 0xf) << 4)) | (((c0 & 0xf) | ((c1 & 0xf) << 4)) << 8));
+    if constexpr (kFive) {
+      qh |= ((a0 & 0x10) >> 4) << (2 * j);
+      qh |= ((a1 & 0x10) >> 4) << (2 * j + 16);
+      qh |= ((c0 & 0x10) >> 4) << (2 * j + 1);
+      qh |= ((c1 & 0x10) >> 4) << (2 * j + 17);
+    }
+  }
+  if constexpr (kFive) {
+    uint16_t* h = reinterpret_cast<uint16_t*>(out + b * L::kBytes + L::kBytes - 20);
+    h[0] = (uint16_t)(qh & 0xffff), h[1] = (uint16_t)(qh >> 16);
+  }
+}
+
 // ---------------------------------------------------------------- Q4_K: one thread per 32-element sub-block
 // total order on floats (Rust total_cmp): only matters for -0.0 < +0.0 on finite data
 __device__ __forceinline__ bool qw_total_less(float a, float b) {

@@ -34,11 +34,12 @@ def storage_bytes(dtype: GgmlDType, elem_count: int) -> int:
 
 
 def quantize_act(weight_dtype: GgmlDType, x: torch.Tensor) -> torch.Tensor:
-    """Rows of x [.., k] -> the reference's Q8_K / Q8_0 activation blocks (uint8 stream)."""
+    """Rows of x [.., k] -> the reference's Q8_K / Q8_1 / Q8_0 activation blocks (uint8 stream)."""
     _need_cuda(x, "x")
     k = x.shape[-1]
     m = x.numel() // k
-    act = GgmlDType.Q8K if weight_dtype in (GgmlDType.Q4K, GgmlDType.Q5K, GgmlDType.Q6K) else GgmlDType.Q8_0
+    act = (GgmlDType.Q8K if weight_dtype in (GgmlDType.Q4K, GgmlDType.Q5K, GgmlDType.Q6K)
+           else GgmlDType.Q8_1 if weight_dtype in (GgmlDType.Q4_1, GgmlDType.Q5_1) else GgmlDType.Q8_0)
     if k % act.block_size():
         _lib.check(_lib.INVALID_PROBLEM, "quantize_act")
     out = torch.empty(storage_bytes(act, m * k), dtype=torch.uint8, device=x.device)

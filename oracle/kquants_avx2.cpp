@@ -6,7 +6,7 @@
 // timed CPU baseline uses; it differs from the scalar order only in f32
 // rounding of the running sums.
 //
-// Follows fuel-quantized/src/avx.rs:13-48 (helpers), :51-88 (Q4_0, Q8_0),
+// Follows fuel-quantized/src/avx.rs:13-48 (helpers), :51-88 (Q4_0, Q8_0), :92-243 (Q4_1, Q5_0, Q5_1),
 // :287-372 (Q6_K), :599-681 (Q4_K).
 #include "blocks.h"
 
@@ -56,6 +56,60 @@ float q8_0_q8_0_dot_avx2(int64_t n, const BlkQ8_0* xs, const BlkQ8_0* ys) {
     acc = _mm256_fmadd_ps(d, dot_i8_quads(qx, qy), acc);
   }
   return reduce8(acc);
+}
+
+// unsigned u8 x signed i8, adjacent groups of four summed to i32 then converted, avx.rs:14-24
+static inline __m256 dot_u8_quads(__m256i ux, __m256i y) {
+  const __m256i p16 = _mm256_maddubs_epi16(ux, y);
+  return _mm256_cvtepi32_ps(_mm256_madd_epi16(_mm256_set1_epi16(1), p16));
+}
+// 16 bytes of nibbles -> 32 bytes: low nibbles (elements 0..15), then high nibbles (16..31), avx.rs:36-41
+static inline __m256i nibbles32(const uint8_t* qs) {
+  const __m128i raw = _mm_loadu_si128((const __m128i*)qs);
+  const __m256i b = _mm256_insertf128_si256(_mm256_castsi128_si256(raw), _mm_srli_epi16(raw, 4), 1);
+  return _mm256_and_si256(_mm256_set1_epi8(0xF), b);
+}
+// bit i of the 32-bit word -> 0x10 in byte i (the fifth bit of element i), avx.rs:92-124
+static inline __m256i fifth_bits32(const uint8_t* qh) {
+  uint8_t b[32];
+  const uint32_t w = (uint32_t)qh[0] | ((uint32_t)qh[1] << 8) | ((uint32_t)qh[2] << 16) | ((uint32_t)qh[3] << 24);
+  for (int i = 0; i < 32; ++i) b[i] = (uint8_t)(((w >> i) & 1u) << 4);
+  return _mm256_loadu_si256((const __m256i*)b);
+}
+
+// avx.rs:148-173
+float q4_1_q8_1_dot_avx2(int64_t n, const BlkQ4_1* xs, const BlkQ8_1* ys) {
+  __m256 acc = _mm256_setzero_ps();
+  float summs = 0.f;
+  for (int64_t b = 0; b < n / QK_S; ++b) {
+    const __m256 d = _mm256_set1_ps(h2f(xs[b].d) * h2f(ys[b].d));
+    summs += h2f(xs[b].m) * h2f(ys[b].s);
+    acc = _mm256_fmadd_ps(d, dot_u8_quads(nibbles32(xs[b].qs), _mm256_loadu_si256((const __m256i*)ys[b].qs)), acc);
+  }
+  return reduce8(acc) + summs;
+}
+// avx.rs:176-209
+float q5_0_q8_0_dot_avx2(int64_t n, const BlkQ5_0* xs, const BlkQ8_0* ys) {
+  __m256 acc = _mm256_setzero_ps();
+  for (int64_t b = 0; b < n / QK_S; ++b) {
+    const __m256 d = _mm256_set1_ps(h2f(xs[b].d) * h2f(ys[b].d));
+    __m256i q = _mm256_or_si256(nibbles32(xs[b].qs), fifth_bits32(xs[b].qh));
+    q = _mm256_sub_epi8(q, _mm256_set1_epi8(16));
+    acc = _mm256_fmadd_ps(d, dot_i8_quads(q, _mm256_loadu_si256((const __m256i*)ys[b].qs)), acc);
+  }
+  return reduce8(acc);
+}
+// avx.rs:212-243
+float q5_1_q8_1_dot_avx2(int64_t n, const BlkQ5_1* xs, const BlkQ8_1* ys) {
+  __m256 acc = _mm256_setzero_ps();
+  float summs = 0.f;
+  for (int64_t b = 0; b < n / QK_S; ++b) {
+    const __m256 d = _mm256_set1_ps(h2f(xs[b].d) * h2f(ys[b].d));
+    summs += h2f(xs[b].m) * h2f(ys[b].s);
+    const __m256i q = _mm256_or_si256(nibbles32(xs[b].qs), fifth_bits32(xs[b].qh));
+    acc = _mm256_fmadd_ps(d, dot_u8_quads(q, _mm256_loadu_si256((const __m256i*)ys[b].qs)), acc);
+  }
+  return reduce8(acc) + summs;
 }
 
 // Broadcast scale pair (2j, 2j+1 as 16-bit words) across a 256-bit register:

@@ -69,6 +69,177 @@ float q4_0_q8_0_dot_scalar(int64_t n, const BlkQ4_0* xs, const BlkQ8_0* ys) {
   return sumf;
 }
 
+// ---------------------------------------------------------------- Q4_1 (partner: Q8_1)
+static inline uint32_t qh_word(const uint8_t* qh) { return (uint32_t)qh[0] | ((uint32_t)qh[1] << 8) | ((uint32_t)qh[2] << 16) | ((uint32_t)qh[3] << 24); }
+
+// fuel-quantized/src/k_quants.rs:315-351
+void q4_1_from_float(const float* xs, int64_t k, BlkQ4_1* ys) {
+  for (int64_t i = 0; i < k / QK_S; ++i) {
+    const float* x = xs + i * QK_S;
+    float mn = INFINITY, mx = -INFINITY;
+    for (int j = 0; j < QK_S; ++j) {
+      mn = fminf(x[j], mn);
+      mx = fmaxf(x[j], mx);
+    }
+    const float d = (mx - mn) / 15.0f;
+    const float id = d != 0.f ? 1.0f / d : 0.f;
+    ys[i].d = f2h(d);
+    ys[i].m = f2h(mn);
+    for (int j = 0; j < QK_S / 2; ++j) {
+      const float x0 = (x[j] - mn) * id, x1 = (x[QK_S / 2 + j] - mn) * id;
+      const uint8_t a = std::min<uint8_t>(15, sat_u8(x0 + 0.5f)), b = std::min<uint8_t>(15, sat_u8(x1 + 0.5f));
+      ys[i].qs[j] = (uint8_t)(a | (b << 4));
+    }
+  }
+}
+// k_quants.rs:354-374
+void q4_1_to_float(const BlkQ4_1* xs, int64_t k, float* ys) {
+  for (int64_t i = 0; i < k / QK_S; ++i) {
+    const float d = h2f(xs[i].d), m = h2f(xs[i].m);
+    for (int j = 0; j < QK_S / 2; ++j) {
+      ys[i * QK_S + j] = (float)(xs[i].qs[j] & 0x0F) * d + m;
+      ys[i * QK_S + j + QK_S / 2] = (float)(xs[i].qs[j] >> 4) * d + m;
+    }
+  }
+}
+// k_quants.rs:285-313
+float q4_1_q8_1_dot_scalar(int64_t n, const BlkQ4_1* xs, const BlkQ8_1* ys) {
+  float sumf = 0.f;
+  for (int64_t b = 0; b < n / QK_S; ++b) {
+    int32_t s = 0;
+    for (int j = 0; j < QK_S / 2; ++j) s += (xs[b].qs[j] & 0x0F) * ys[b].qs[j] + (xs[b].qs[j] >> 4) * ys[b].qs[j + QK_S / 2];
+    sumf += (float)s * h2f(xs[b].d) * h2f(ys[b].d) + h2f(xs[b].m) * h2f(ys[b].s);
+  }
+  return sumf;
+}
+
+// ---------------------------------------------------------------- Q5_0 (partner: Q8_0)
+// k_quants.rs:424-460. (x + 16.5) as i8 saturates, then min(31), then reinterpreted as u8.
+void q5_0_from_float(const float* xs, int64_t k, BlkQ5_0* ys) {
+  for (int64_t i = 0; i < k / QK_S; ++i) {
+    const float* x = xs + i * QK_S;
+    float amax = 0.f, mx = 0.f;
+    for (int j = 0; j < QK_S; ++j) {
+      const float a = fabsf(x[j]);
+      if (amax < a) { amax = a; mx = x[j]; }
+    }
+    const float d = mx / -16.0f;
+    const float id = d != 0.f ? 1.0f / d : 0.f;
+    ys[i].d = f2h(d);
+    uint32_t qh = 0;
+    for (int j = 0; j < QK_S / 2; ++j) {
+      const uint8_t a = (uint8_t)std::min<int8_t>(sat_i8(x[j] * id + 16.5f), 31);
+      const uint8_t b = (uint8_t)std::min<int8_t>(sat_i8(x[j + QK_S / 2] * id + 16.5f), 31);
+      ys[i].qs[j] = (uint8_t)((a & 0x0F) | ((b & 0x0F) << 4));
+      qh |= (((uint32_t)a & 0x10) >> 4) << j;
+      qh |= (((uint32_t)b & 0x10) >> 4) << (j + QK_S / 2);
+    }
+    ys[i].qh[0] = (uint8_t)qh, ys[i].qh[1] = (uint8_t)(qh >> 8), ys[i].qh[2] = (uint8_t)(qh >> 16), ys[i].qh[3] = (uint8_t)(qh >> 24);
+  }
+}
+// k_quants.rs:463-485
+void q5_0_to_float(const BlkQ5_0* xs, int64_t k, float* ys) {
+  for (int64_t i = 0; i < k / QK_S; ++i) {
+    const float d = h2f(xs[i].d);
+    const uint32_t qh = qh_word(xs[i].qh);
+    for (int j = 0; j < QK_S / 2; ++j) {
+      const int h0 = ((qh >> j) << 4) & 0x10, h1 = (qh >> (j + 12)) & 0x10;
+      ys[i * QK_S + j] = (float)(((xs[i].qs[j] & 0x0F) | h0) - 16) * d;
+      ys[i * QK_S + j + QK_S / 2] = (float)(((xs[i].qs[j] >> 4) | h1) - 16) * d;
+    }
+  }
+}
+// k_quants.rs:401-422
+float q5_0_q8_0_dot_scalar(int64_t n, const BlkQ5_0* xs, const BlkQ8_0* ys) {
+  float sumf = 0.f;
+  for (int64_t b = 0; b < n / QK_S; ++b) {
+    const uint32_t qh = qh_word(xs[b].qh);
+    int32_t s = 0;
+    for (int j = 0; j < QK_S / 2; ++j) {
+      const int h0 = (int)(((qh >> j) & 1u) << 4), h1 = (int)((qh >> (j + 12)) & 0x10u);
+      const int x0 = ((xs[b].qs[j] & 0x0F) | h0) - 16, x1 = ((xs[b].qs[j] >> 4) | h1) - 16;
+      s += x0 * ys[b].qs[j] + x1 * ys[b].qs[j + QK_S / 2];
+    }
+    sumf += (float)s * h2f(xs[b].d) * h2f(ys[b].d);
+  }
+  return sumf;
+}
+
+// ---------------------------------------------------------------- Q5_1 (partner: Q8_1)
+// k_quants.rs:535-575
+void q5_1_from_float(const float* xs, int64_t k, BlkQ5_1* ys) {
+  for (int64_t i = 0; i < k / QK_S; ++i) {
+    const float* x = xs + i * QK_S;
+    float mn = INFINITY, mx = -INFINITY;
+    for (int j = 0; j < QK_S; ++j) {
+      mn = fminf(x[j], mn);
+      mx = fmaxf(x[j], mx);
+    }
+    const float d = (mx - mn) / 31.0f;
+    const float id = d != 0.f ? 1.0f / d : 0.f;
+    ys[i].d = f2h(d);
+    ys[i].m = f2h(mn);
+    uint32_t qh = 0;
+    for (int j = 0; j < QK_S / 2; ++j) {
+      const uint8_t a = sat_u8((x[j] - mn) * id + 0.5f), b = sat_u8((x[QK_S / 2 + j] - mn) * id + 0.5f);
+      ys[i].qs[j] = (uint8_t)((a & 0x0F) | ((b & 0x0F) << 4));
+      qh |= (((uint32_t)a & 0x10) >> 4) << j;
+      qh |= (((uint32_t)b & 0x10) >> 4) << (j + QK_S / 2);
+    }
+    ys[i].qh[0] = (uint8_t)qh, ys[i].qh[1] = (uint8_t)(qh >> 8), ys[i].qh[2] = (uint8_t)(qh >> 16), ys[i].qh[3] = (uint8_t)(qh >> 24);
+  }
+}
+// k_quants.rs:578-602
+void q5_1_to_float(const BlkQ5_1* xs, int64_t k, float* ys) {
+  for (int64_t i = 0; i < k / QK_S; ++i) {
+    const float d = h2f(xs[i].d), m = h2f(xs[i].m);
+    const uint32_t qh = qh_word(xs[i].qh);
+    for (int j = 0; j < QK_S / 2; ++j) {
+      const int h0 = ((qh >> j) << 4) & 0x10, h1 = (qh >> (j + 12)) & 0x10;
+      ys[i * QK_S + j] = (float)((xs[i].qs[j] & 0x0F) | h0) * d + m;
+      ys[i * QK_S + j + QK_S / 2] = (float)((xs[i].qs[j] >> 4) | h1) * d + m;
+    }
+  }
+}
+// k_quants.rs:501-533
+float q5_1_q8_1_dot_scalar(int64_t n, const BlkQ5_1* xs, const BlkQ8_1* ys) {
+  float sumf = 0.f;
+  for (int64_t b = 0; b < n / QK_S; ++b) {
+    const uint32_t qh = qh_word(xs[b].qh);
+    int32_t s = 0;
+    for (int j = 0; j < QK_S / 2; ++j) {
+      const int h0 = (int)(((qh >> j) << 4) & 0x10u), h1 = (int)((qh >> (j + 12)) & 0x10u);
+      s += ((xs[b].qs[j] & 0xF) | h0) * ys[b].qs[j] + ((xs[b].qs[j] >> 4) | h1) * ys[b].qs[j + QK_S / 2];
+    }
+    sumf += (float)s * h2f(xs[b].d) * h2f(ys[b].d) + h2f(xs[b].m) * h2f(ys[b].s);
+  }
+  return sumf;
+}
+
+// ---------------------------------------------------------------- Q8_1 (activation partner of Q4_1 / Q5_1)
+// k_quants.rs:728-757. s = f16(sum) * d in half arithmetic: both factors rounded to f16, the f32 product rounded to f16.
+void q8_1_from_float(const float* xs, int64_t k, BlkQ8_1* ys) {
+  for (int64_t i = 0; i < k / QK_S; ++i) {
+    const float* x = xs + i * QK_S;
+    float amax = 0.f;
+    for (int j = 0; j < QK_S; ++j) amax = fmaxf(amax, fabsf(x[j]));
+    const float d = amax / 127.0f;
+    const float id = d != 0.f ? 1.0f / d : 0.f;
+    ys[i].d = f2h(d);
+    int32_t sum = 0;
+    for (int j = 0; j < QK_S / 2; ++j) {
+      ys[i].qs[j] = sat_i8(roundf(x[j] * id));
+      ys[i].qs[j + QK_S / 2] = sat_i8(roundf(x[j + QK_S / 2] * id));
+      sum += ys[i].qs[j] + ys[i].qs[j + QK_S / 2];
+    }
+    ys[i].s = f2h(h2f(f2h((float)sum)) * h2f(ys[i].d));
+  }
+}
+void q8_1_to_float(const BlkQ8_1* xs, int64_t k, float* ys) {  // not in the reference (its to_float is unimplemented); for the pins
+  for (int64_t i = 0; i < k / QK_S; ++i)
+    for (int j = 0; j < QK_S; ++j) ys[i * QK_S + j] = (float)xs[i].qs[j] * h2f(xs[i].d);
+}
+
 // ---------------------------------------------------------------- Q8_0
 // fuel-quantized/src/k_quants.rs:629-658. The scale is stored as RNE f16 but the
 // elements are quantized with the unrounded f32 reciprocal.

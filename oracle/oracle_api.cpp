@@ -16,6 +16,20 @@ namespace fq_oracle {
 void q4_0_from_float(const float*, int64_t, BlkQ4_0*);
 void q4_0_to_float(const BlkQ4_0*, int64_t, float*);
 float q4_0_q8_0_dot_scalar(int64_t, const BlkQ4_0*, const BlkQ8_0*);
+void q4_1_from_float(const float*, int64_t, BlkQ4_1*);
+void q4_1_to_float(const BlkQ4_1*, int64_t, float*);
+float q4_1_q8_1_dot_scalar(int64_t, const BlkQ4_1*, const BlkQ8_1*);
+float q4_1_q8_1_dot_avx2(int64_t, const BlkQ4_1*, const BlkQ8_1*);
+void q5_0_from_float(const float*, int64_t, BlkQ5_0*);
+void q5_0_to_float(const BlkQ5_0*, int64_t, float*);
+float q5_0_q8_0_dot_scalar(int64_t, const BlkQ5_0*, const BlkQ8_0*);
+float q5_0_q8_0_dot_avx2(int64_t, const BlkQ5_0*, const BlkQ8_0*);
+void q5_1_from_float(const float*, int64_t, BlkQ5_1*);
+void q5_1_to_float(const BlkQ5_1*, int64_t, float*);
+float q5_1_q8_1_dot_scalar(int64_t, const BlkQ5_1*, const BlkQ8_1*);
+float q5_1_q8_1_dot_avx2(int64_t, const BlkQ5_1*, const BlkQ8_1*);
+void q8_1_from_float(const float*, int64_t, BlkQ8_1*);
+void q8_1_to_float(const BlkQ8_1*, int64_t, float*);
 void q8_0_from_float(const float*, int64_t, BlkQ8_0*);
 void q8_0_to_float(const BlkQ8_0*, int64_t, float*);
 float q8_0_q8_0_dot_scalar(int64_t, const BlkQ8_0*, const BlkQ8_0*);
@@ -50,6 +64,10 @@ struct Fmt {
 bool fmt_of(int type, Fmt* f) {
   switch (type) {
     case GGML_Q4_0: *f = {32, 18, GGML_Q8_0}; return true;
+    case GGML_Q4_1: *f = {32, 20, GGML_Q8_1}; return true;
+    case GGML_Q5_0: *f = {32, 22, GGML_Q8_0}; return true;
+    case GGML_Q5_1: *f = {32, 24, GGML_Q8_1}; return true;
+    case GGML_Q8_1: *f = {32, 36, GGML_Q8_1}; return true;
     case GGML_Q8_0: *f = {32, 34, GGML_Q8_0}; return true;
     case GGML_Q4K: *f = {256, 144, GGML_Q8K}; return true;
     case GGML_Q5K: *f = {256, 176, GGML_Q8K}; return true;
@@ -62,6 +80,10 @@ bool fmt_of(int type, Fmt* f) {
 void quantize_span(int type, const float* x, int64_t elems, void* out) {
   switch (type) {
     case GGML_Q4_0: q4_0_from_float(x, elems, (BlkQ4_0*)out); break;
+    case GGML_Q4_1: q4_1_from_float(x, elems, (BlkQ4_1*)out); break;
+    case GGML_Q5_0: q5_0_from_float(x, elems, (BlkQ5_0*)out); break;
+    case GGML_Q5_1: q5_1_from_float(x, elems, (BlkQ5_1*)out); break;
+    case GGML_Q8_1: q8_1_from_float(x, elems, (BlkQ8_1*)out); break;
     case GGML_Q8_0: q8_0_from_float(x, elems, (BlkQ8_0*)out); break;
     case GGML_Q4K: q4k_from_float(x, elems, (BlkQ4K*)out); break;
     case GGML_Q5K: q5k_from_float(x, elems, (BlkQ5K*)out); break;
@@ -73,6 +95,10 @@ void quantize_span(int type, const float* x, int64_t elems, void* out) {
 void dequantize_span(int type, const void* in, int64_t elems, float* y) {
   switch (type) {
     case GGML_Q4_0: q4_0_to_float((const BlkQ4_0*)in, elems, y); break;
+    case GGML_Q4_1: q4_1_to_float((const BlkQ4_1*)in, elems, y); break;
+    case GGML_Q5_0: q5_0_to_float((const BlkQ5_0*)in, elems, y); break;
+    case GGML_Q5_1: q5_1_to_float((const BlkQ5_1*)in, elems, y); break;
+    case GGML_Q8_1: q8_1_to_float((const BlkQ8_1*)in, elems, y); break;
     case GGML_Q8_0: q8_0_to_float((const BlkQ8_0*)in, elems, y); break;
     case GGML_Q4K: q4k_to_float((const BlkQ4K*)in, elems, y); break;
     case GGML_Q5K: q5k_to_float((const BlkQ5K*)in, elems, y); break;
@@ -85,6 +111,9 @@ float dot(int type, int order, int64_t k, const void* w, const void* a) {
   if (order == 0) {
     switch (type) {
       case GGML_Q4_0: return q4_0_q8_0_dot_scalar(k, (const BlkQ4_0*)w, (const BlkQ8_0*)a);
+      case GGML_Q4_1: return q4_1_q8_1_dot_scalar(k, (const BlkQ4_1*)w, (const BlkQ8_1*)a);
+      case GGML_Q5_0: return q5_0_q8_0_dot_scalar(k, (const BlkQ5_0*)w, (const BlkQ8_0*)a);
+      case GGML_Q5_1: return q5_1_q8_1_dot_scalar(k, (const BlkQ5_1*)w, (const BlkQ8_1*)a);
       case GGML_Q8_0: return q8_0_q8_0_dot_scalar(k, (const BlkQ8_0*)w, (const BlkQ8_0*)a);
       case GGML_Q4K: return q4k_q8k_dot_scalar(k, (const BlkQ4K*)w, (const BlkQ8K*)a);
       case GGML_Q5K: return q5k_q8k_dot_scalar(k, (const BlkQ5K*)w, (const BlkQ8K*)a);
@@ -93,6 +122,9 @@ float dot(int type, int order, int64_t k, const void* w, const void* a) {
   } else {
     switch (type) {
       case GGML_Q4_0: return q4_0_q8_0_dot_avx2(k, (const BlkQ4_0*)w, (const BlkQ8_0*)a);
+      case GGML_Q4_1: return q4_1_q8_1_dot_avx2(k, (const BlkQ4_1*)w, (const BlkQ8_1*)a);
+      case GGML_Q5_0: return q5_0_q8_0_dot_avx2(k, (const BlkQ5_0*)w, (const BlkQ8_0*)a);
+      case GGML_Q5_1: return q5_1_q8_1_dot_avx2(k, (const BlkQ5_1*)w, (const BlkQ8_1*)a);
       case GGML_Q8_0: return q8_0_q8_0_dot_avx2(k, (const BlkQ8_0*)w, (const BlkQ8_0*)a);
       case GGML_Q4K: return q4k_q8k_dot_avx2(k, (const BlkQ4K*)w, (const BlkQ8K*)a);
       case GGML_Q5K: return q5k_q8k_dot_avx2(k, (const BlkQ5K*)w, (const BlkQ8K*)a);

@@ -13,11 +13,20 @@ import numpy as np
 import pytest
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "kquants_golden.npz")
-FORMATS = ("q4_0", "q8_0", "q4k", "q5k", "q6k")
+FORMATS = ("q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q4k", "q5k", "q6k")
+# byte offsets of the f16 fields of a block (kept finite when blocks are drawn from random bytes)
+F16_FIELDS = {"q4_0": (0,), "q4_1": (0, 2), "q5_0": (0,), "q5_1": (0, 2), "q8_0": (0,), "q4k": (0, 2), "q5k": (0, 2), "q6k": (208,)}
 
 
 def _t(O, name):
-    return {"q4_0": O.Q4_0, "q8_0": O.Q8_0, "q4k": O.Q4K, "q5k": O.Q5K, "q6k": O.Q6K}[name]
+    return {"q4_0": O.Q4_0, "q4_1": O.Q4_1, "q5_0": O.Q5_0, "q5_1": O.Q5_1, "q8_0": O.Q8_0, "q4k": O.Q4K, "q5k": O.Q5K,
+            "q6k": O.Q6K}[name]
+
+
+def _gt(gguf, name):
+    G = gguf.GGMLQuantizationType
+    return {"q4_0": G.Q4_0, "q4_1": G.Q4_1, "q5_0": G.Q5_0, "q5_1": G.Q5_1, "q8_0": G.Q8_0, "q4k": G.Q4_K, "q5k": G.Q5_K,
+            "q6k": G.Q6_K}[name]
 
 
 def test_block_sizes(oracle):
@@ -94,21 +103,19 @@ def test_layout_matches_gguf_py(oracle, name):
     gguf = pytest.importorskip("gguf")
     from gguf import quants
     O = oracle
-    gt = {"q4_0": gguf.GGMLQuantizationType.Q4_0, "q8_0": gguf.GGMLQuantizationType.Q8_0,
-          "q4k": gguf.GGMLQuantizationType.Q4_K, "q5k": gguf.GGMLQuantizationType.Q5_K,
-          "q6k": gguf.GGMLQuantizationType.Q6_K}[name]
+    gt = _gt(gguf, name)
     w = np.random.Generator(np.random.PCG64(11)).standard_normal((16, 1024), dtype=np.float32) * np.float32(0.02)
     wb = O.quantize(_t(O, name), w)
     theirs = quants.dequantize(wb.reshape(16, -1), gt).reshape(-1)
     assert np.array_equal(O.dequantize(_t(O, name), wb).view(np.uint32), theirs.view(np.uint32))
-    if name in ("q4_0", "q8_0"):  # gguf-py quantizes only the simple formats
+    if not name.endswith("k"):  # gguf-py quantizes only the 32-element formats
         assert np.array_equal(quants.quantize(w, gt).reshape(-1), wb)
     # random bytes decode identically too (no reliance on what the quantizer emits)
     rb = np.random.Generator(np.random.PCG64(12)).integers(0, 256, wb.size, dtype=np.uint8)
     bb = O.block_bytes(_t(O, name))
     blocks = rb.reshape(-1, bb).copy()
     # keep the f16 scale fields finite
-    for off in ((0,) if name in ("q4_0", "q8_0") else (0, 2) if name in ("q4k", "q5k") else (208,)):
+    for off in F16_FIELDS[name]:
         blocks[:, off + 1] &= 0x3B
     rb = blocks.reshape(-1)
     assert np.array_equal(O.dequantize(_t(O, name), rb).view(np.uint32),
@@ -177,6 +184,11 @@ def _dequant_act_blocks(O, name, act, m, k):
         bs = b[:, :, 260:].copy().view(np.int16).astype(np.int64)
         assert np.array_equal(bs, qs.reshape(m, k // 256, 16, 16).sum(-1).astype(np.int64))
         return (d * qs).reshape(m, k)
+    if name in ("q4_1", "q5_1"):   # Q8_1 = {d: f16, s: f16, qs: i8[32]} (k_quants.rs:100-107); s is checked by the caller
+        b = act.reshape(m, k // 32, 36)
+        d = b[:, :, :2].copy().view(np.float16).astype(np.float64)
+        qs = b[:, :, 4:].copy().view(np.int8).astype(np.float64)
+        return (d * qs).reshape(m, k)
     b = act.reshape(m, k // 32, 34)
     d = b[:, :, :2].copy().view(np.float16).astype(np.float64)
     qs = b[:, :, 2:].copy().view(np.int8).astype(np.float64)
@@ -195,9 +207,7 @@ def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
     from gguf import quants
     O = oracle
     t = _t(O, name)
-    gt = {"q4_0": gguf.GGMLQuantizationType.Q4_0, "q8_0": gguf.GGMLQuantizationType.Q8_0,
-          "q4k": gguf.GGMLQuantizationType.Q4_K, "q5k": gguf.GGMLQuantizationType.Q5_K,
-          "q6k": gguf.GGMLQuantizationType.Q6_K}[name]
+    gt = _gt(gguf, name)
     n, k, m = 48, 2048, 3
     rng = np.random.Generator(np.random.PCG64(21))
     if source == "quantizer":
@@ -205,7 +215,7 @@ def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
     else:
         bb = O.block_bytes(t)
         blocks = rng.integers(0, 256, (n * k // O.block_elems(t), bb), dtype=np.uint8)
-        for off in ((0,) if name in ("q4_0", "q8_0") else (0, 2) if name in ("q4k", "q5k") else (208,)):
+        for off in F16_FIELDS[name]:
             blocks[:, off + 1] &= 0x3B  # finite f16 scales
         wb = blocks.reshape(-1)
     x = rng.standard_normal((m, k), dtype=np.float32)
@@ -214,6 +224,19 @@ def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
     xa = _dequant_act_blocks(O, name, act, m, k)
     w = quants.dequantize(wb.reshape(n, -1), gt).astype(np.float64).reshape(n, k)
     want = xa @ w.T
+    if name in ("q4_1", "q5_1"):
+        # Formats with a per-block minimum m: the reference adds m * s per block, s being the activation block's stored
+        # f16 field (k_quants.rs:285-313, 501-533), where the product of the dequantized operands has m * (d * sum(q)).
+        # s itself is restated here in numpy: f16(sum) * d in half arithmetic (k_quants.rs:728-757).
+        ab = act.reshape(m, k // 32, 36)
+        dy = ab[:, :, :2].copy().view(np.float16)[..., 0]
+        s_stored = ab[:, :, 2:4].copy().view(np.float16)[..., 0]
+        sums = ab[:, :, 4:].copy().view(np.int8).astype(np.int32).sum(-1)
+        s_np = (sums.astype(np.float32).astype(np.float16).astype(np.float32) * dy.astype(np.float32)).astype(np.float16)
+        assert np.array_equal(s_stored.view(np.uint16), s_np.view(np.uint16))
+        mw = wb.reshape(n, k // 32, -1)[:, :, 2:4].copy().view(np.float16)[..., 0].astype(np.float64)    # [n, blocks]
+        exact_ms = dy.astype(np.float64) * sums                                                              # [m, blocks]
+        want = want + (s_stored.astype(np.float64) - exact_ms) @ mw.T
     scale = np.abs(want).max()
     for order in (O.SCALAR, O.AVX2):
         got = O.matmul(t, x, wb, n, order).astype(np.float64)
