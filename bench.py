@@ -271,6 +271,8 @@ def run_side_workload(args):
         for t, name in ((T.Q4K, "Q4_K"), (T.Q6K, "Q6_K"), (T.Q8_0, "Q8_0")):
             for n, k in ((11008, 4096), (4096, 11008)):
                 for m in (1, 2, 4, 8, 16, 32, 64, 128):
+                    if args.only and args.only not in f"{name}_k{k}_n{n}_m{m}":
+                        continue
                     print(json.dumps(matmul_case(t, name, n, k, m, 12, 20)), flush=True)
     elif args.workload == "q5k":
         for n, k in ((11008, 4096), (4096, 11008)):
@@ -530,6 +532,7 @@ def main():
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step (profiling runs use fewer)")
     ap.add_argument("--tf32", action="store_true", help="--workload prefill: tensor-core path in tf32 instead of f16")
+    ap.add_argument("--only", default="", help="--workload sweep: run only the cases whose name contains this text, e.g. Q4_K_k4096_n11008_m8")
     ap.add_argument("--bf16", action="store_true", help="--workload prefill: 16-bit operands as bf16 instead of f16")
     ap.add_argument("--decode-grid", type=int, default=0, help="thread blocks of the decode mat-vec (0: the library's choice, two per SM)")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-architecture decode that is reported beside the metric")
