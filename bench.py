@@ -248,7 +248,7 @@ def run_side_workload(args):
         b[:, 3] &= 0x3B
         return b.reshape(-1)
 
-    def matmul_case(t, name, n, k, m, copies, reps):
+    def matmul_case(t, name, n, k, m, copies, reps, parity_rows=0):
         if t == T.Q5K:
             ws = [random_blocks(t, n, k) for _ in range(copies)]
         else:
@@ -264,8 +264,26 @@ def run_side_workload(args):
                                            st.cuda_stream), "fuelq_qmatmul")
         us = _time_graph(torch, st, p, reps) / copies
         algo = ws[0].numel() + 4 * m * k + 4 * m * n
-        return {"workload": f"{name}_k{k}_n{n}_m{m}", "us": us, "GB/s": algo / us / 1e3, "TFLOP/s": 2 * m * n * k / us / 1e6,
+        line = {"workload": f"{name}_k{k}_n{n}_m{m}", "us": us, "GB/s": algo / us / 1e3, "TFLOP/s": 2 * m * n * k / us / 1e6,
                 "hbm_frac": algo / us / 1e3 / peak, "peak_kind": f"of {peak_kind}", "weight_copies": copies}
+        if parity_rows:
+            # observed error of the last copy's product on a sample of activation rows: against the exact dequantized
+            # product (f64) and against the reference's CPU path (8-bit activation blocks, integer dot products)
+            import numpy as np
+            from oracle import oracle as O
+            ot = {T.Q4K: O.Q4K, T.Q6K: O.Q6K, T.Q8_0: O.Q8_0}[t]
+            rows = np.unique(np.linspace(0, m - 1, parity_rows).astype(np.int64))
+            wb = ws[-1].cpu().numpy()
+            xs_ = x[torch.from_numpy(rows).to(dev)].cpu().numpy()
+            got = y[torch.from_numpy(rows).to(dev)].cpu().numpy().astype(np.float64)
+            exact = O.matmul_dequant_f64(ot, xs_, wb, n)
+            ref = O.matmul(ot, xs_, wb, n, O.AVX2).astype(np.float64)
+            line["parity"] = {"rows_sampled": int(rows.size), "numerics": int(L.fuelq_qmatmul_numerics(int(t), m, n, k)),
+                              "max_err_vs_exact_dequant_over_max": float(np.abs(got - exact).max() / np.abs(exact).max()),
+                              "frobenius_vs_exact_dequant": float(np.linalg.norm(got - exact) / np.linalg.norm(exact)),
+                              "max_err_vs_cpu_path_over_max": float(np.abs(got - ref).max() / np.abs(ref).max()),
+                              "frobenius_vs_cpu_path": float(np.linalg.norm(got - ref) / np.linalg.norm(ref))}
+        return line
 
     if args.workload == "sweep":
         for t, name in ((T.Q4K, "Q4_K"), (T.Q6K, "Q6_K"), (T.Q8_0, "Q8_0")):
@@ -279,7 +297,7 @@ def run_side_workload(args):
             for m in (1, 2, 4, 8, 16):
                 print(json.dumps(matmul_case(T.Q5K, "Q5_K", n, k, m, 12, 20)), flush=True)
     elif args.workload == "prefill":
-        line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10)
+        line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10, parity_rows=0 if args.no_cpu_baseline else 32)
         line["operands"] = "tf32" if args.tf32 else "bf16" if args.bf16 else "f16"
         print(json.dumps(line), flush=True)
     else:

@@ -47,6 +47,7 @@ constexpr int kMmaActRows = 16;
 struct MmaSmemHeader {
   uint64_t full[kDecodeMaxStages];
   uint64_t empty[kDecodeMaxStages];
+  int dead;  // a consumer warp's bounded wait expired: every warp skips the remaining work but keeps meeting the barriers
 };
 
 __device__ __forceinline__ void mma_s8_16832(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -80,6 +81,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
       mbar_init(&hd->full[s], 1);
       mbar_init(&hd->empty[s], kDecodeConsumerWarps);
     }
+    hd->dead = 0;
     mbar_init_fence();
   }
   __syncthreads();
@@ -141,6 +143,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
   const int gid = lane >> 2, tig = lane & 3;
 
   int g = 0;
+  bool dead = false;
   for (int pass = 0; pass < n_pass; ++pass) {
     const int a0 = m_begin + pass * kMmaActRows;
     const int ac = (m_count - pass * kMmaActRows < kMmaActRows) ? m_count - pass * kMmaActRows : kMmaActRows;
@@ -177,14 +180,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
 
     for (int it = 0; it < n_iter; ++it, ++g) {
       const int s = g % S;
-      if (!mbar_wait_bounded(&hd->full[s], (g / S) & 1)) {
+      // A wait that runs out must not strand the other warps at the named barriers below (their thread counts are
+      // fixed): the warp marks the CTA dead and carries on through every barrier, skipping loads, math and stores.
+      if (!dead && !mbar_wait_bounded(&hd->full[s], (g / S) & 1)) {
         record_dev_error(kErrFullWait);
-        return;
+        *reinterpret_cast<volatile int*>(&hd->dead) = 1;
       }
+      dead = dead || *reinterpret_cast<volatile int*>(&hd->dead) != 0;
       const int row0 = r_begin + it * R;
       const int rows_here = ((row0 + R < r_end) ? row0 + R : r_end) - row0;
       float facc[4] = {0.f, 0.f, 0.f, 0.f};  // (row gid, col 2tig) (gid, 2tig+1) (gid+8, 2tig) (gid+8, 2tig+1)
-      if (tile * 8 < rows_here) {
+      if (!dead && tile * 8 < rows_here) {
         // 32-bit shared addresses, so every load below is one ld.shared with an immediate offset
         const uint32_t tile_s = smem_u32(stages) + (uint32_t)s * p.stage_stride + (uint32_t)(tile * 8) * wstride;
         const uint32_t wb_s = tile_s + (uint32_t)gid * wstride + Q4KL::kOffQs + 4 * tig;  // B fragments: weight row gid
@@ -252,7 +258,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) mma_q4k_kernel(const MmaPar
           }
         }
       }
-      if (kpart == 0 && tile * 8 < rows_here) {
+      if (!dead && kpart == 0 && tile * 8 < rows_here) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int m = gid + 8 * (i >> 1), col = tile * 8 + 2 * tig + (i & 1);
