@@ -263,6 +263,104 @@ using Q4_1Decode = Legacy32Decode<Q4_1L, false, true>;
 using Q5_0Decode = Legacy32Decode<Q5_0L, true, false>;
 using Q5_1Decode = Legacy32Decode<Q5_1L, true, true>;
 
+// Q2_K and Q3_K (k_quants.rs:783-833, 1013-1133). Element e of a block sits in qs[32 * (e / 128) + e % 32] at bits
+// 2 * ((e % 128) / 32); every 16 elements share scale e / 16. A unit is 16 bytes of qs = half a 128-element chunk:
+// four 16-element runs (bit pairs j = 0..3) with scale indices 8c + 2j + h, against activation bytes 128c + 32j + 16h.
+struct Q2KDecode {
+  static constexpr int kUnitsPerBlock = 4;
+  static constexpr int kBlockElems = 256;
+  template <int MT>
+  __device__ __forceinline__ static void unit(const uint8_t* rowp, int u, const ActPlanes& a, int k, int m0, int mc,
+                                              float (&acc)[MT]) {
+    const int blk = u >> 2, c = (u >> 1) & 1, h = u & 1;
+    const uint8_t* b = rowp + blk * Q2KL::kBytes;   // 84-byte blocks: 4-byte aligned
+    const uint32_t dd = *reinterpret_cast<const uint32_t*>(b + Q2KL::kOffD);
+    const float d = h2f_bits(dd & 0xffffu), dmin = h2f_bits(dd >> 16);
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint32_t*>(b + Q2KL::kOffQs + 32 * c + 16 * h + 4 * i);
+    int sc[4], mn[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t s = b[8 * c + 2 * j + h];
+      sc[j] = (int)(s & 0xFu), mn[j] = (int)(s >> 4);
+    }
+    const int nblk = k >> 8;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      if (i < mc) {
+        const int m = m0 + i;
+        const int8_t* q8 = a.qs + (size_t)m * k + (size_t)blk * 256 + 128 * c + 16 * h;
+        const int16_t* bs = a.bsums + (size_t)m * (k >> 4) + blk * 16 + 8 * c + h;
+        int isum = 0, msum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int4 av = *reinterpret_cast<const int4*>(q8 + 32 * j);
+          int s = dp4a_ss((int)((w[0] >> (2 * j)) & 0x03030303u), av.x, 0);
+          s = dp4a_ss((int)((w[1] >> (2 * j)) & 0x03030303u), av.y, s);
+          s = dp4a_ss((int)((w[2] >> (2 * j)) & 0x03030303u), av.z, s);
+          s = dp4a_ss((int)((w[3] >> (2 * j)) & 0x03030303u), av.w, s);
+          isum += sc[j] * s;
+          msum += mn[j] * (int)bs[2 * j];
+        }
+        const float yd = a.d[(size_t)m * nblk + blk];
+        acc[i] += (yd * d) * (float)isum - (yd * dmin) * (float)msum;
+      }
+    }
+  }
+};
+
+struct Q3KDecode {
+  static constexpr int kUnitsPerBlock = 4;
+  static constexpr int kBlockElems = 256;
+  template <int MT>
+  __device__ __forceinline__ static void unit(const uint8_t* rowp, int u, const ActPlanes& a, int k, int m0, int mc,
+                                              float (&acc)[MT]) {
+    const int blk = u >> 2, c = (u >> 1) & 1, h = u & 1;
+    const uint8_t* b = rowp + blk * Q3KL::kBytes;   // 110-byte blocks: 2-byte aligned
+    const float d = h2f_bits(lds_u16(b + Q3KL::kOffD));
+    uint32_t w[4], hm[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w[i] = lds_u32_2b(b + Q3KL::kOffQs + 32 * c + 16 * h + 4 * i);
+      hm[i] = lds_u32_2b(b + Q3KL::kOffHmask + 16 * h + 4 * i);
+    }
+    // 6-bit scales (k_quants.rs:1095-1103): index is < 8: low nibble of byte is, else high nibble of byte is - 8;
+    // two more bits from byte 8 + is % 4 at 2 * (is / 4)
+    int sc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int is = 8 * c + 2 * j + h;
+      const uint32_t lo = is < 8 ? (b[Q3KL::kOffScales + is] & 0xFu) : (uint32_t)(b[Q3KL::kOffScales + is - 8] >> 4);
+      const uint32_t hi = (b[Q3KL::kOffScales + 8 + (is & 3)] >> (2 * (is >> 2))) & 3u;
+      sc[j] = (int)(lo | (hi << 4)) - 32;
+    }
+    const int nblk = k >> 8;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      if (i < mc) {
+        const int m = m0 + i;
+        const int8_t* q8 = a.qs + (size_t)m * k + (size_t)blk * 256 + 128 * c + 16 * h;
+        const int16_t* bs = a.bsums + (size_t)m * (k >> 4) + blk * 16 + 8 * c + h;
+        int isum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // value = low two bits - (high bit set ? 0 : 4) = (low | high << 2) - 4: unsigned bytes 0..7 against the
+          // activations, minus four times the run's activation sum
+          const int bit = 4 * c + j;
+          const int4 av = *reinterpret_cast<const int4*>(q8 + 32 * j);
+          int s = dp4a_ss((int)(((w[0] >> (2 * j)) & 0x03030303u) | (((hm[0] >> bit) & 0x01010101u) << 2)), av.x, 0);
+          s = dp4a_ss((int)(((w[1] >> (2 * j)) & 0x03030303u) | (((hm[1] >> bit) & 0x01010101u) << 2)), av.y, s);
+          s = dp4a_ss((int)(((w[2] >> (2 * j)) & 0x03030303u) | (((hm[2] >> bit) & 0x01010101u) << 2)), av.z, s);
+          s = dp4a_ss((int)(((w[3] >> (2 * j)) & 0x03030303u) | (((hm[3] >> bit) & 0x01010101u) << 2)), av.w, s);
+          isum += sc[j] * (s - 4 * (int)bs[2 * j]);
+        }
+        acc[i] += (d * a.d[(size_t)m * nblk + blk]) * (float)isum;
+      }
+    }
+  }
+};
+
 // ------------------------------------------------------------------ the kernel
 struct DecodeSmemHeader {
   uint64_t full[kDecodeMaxStages];

@@ -184,6 +184,45 @@ __global__ void __launch_bounds__(256) dequant_legacy32_kernel(const uint8_t* __
     out[16 + t] = cvt_out<T>(kMin ? __fadd_rn(p1, m) : p1);
   }
 }
+// Q2_K (k_quants.rs:958-994): y = (d * sc_lo) * q - dmin * sc_hi; Q3_K (:1314-1366): y = (d * (sc - 32)) * q with
+// q = low two bits - (high bit set ? 0 : 4). One thread per 4 bytes of qs of one bit pair: 4 elements.
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q2k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 6;
+  const int e0 = (int)(u & 63) * 4;                       // first of four consecutive elements
+  const int c = e0 >> 7, j = (e0 >> 5) & 3, bb = e0 & 31;  // chunk, bit pair, byte within the chunk's 32
+  const uint8_t* b = w + blk * Q2KL::kBytes;
+  const float d = h2f_bits(ldg_u16(b + Q2KL::kOffD)), mn = h2f_bits(ldg_u16(b + Q2KL::kOffDmin));
+  const uint32_t sc = b[e0 >> 4];
+  const float dl = __fmul_rn(d, (float)(sc & 0xFu)), ml = __fmul_rn(mn, (float)(sc >> 4));
+  const uint32_t v = ldg_u32_2b(b + Q2KL::kOffQs + 32 * c + bb);
+  T* out = y + blk * 256 + e0;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) out[t] = cvt_out<T>(__fsub_rn(__fmul_rn(dl, (float)((v >> (8 * t + 2 * j)) & 3u)), ml));
+}
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_q3k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {
+  const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t blk = u >> 6;
+  const int e0 = (int)(u & 63) * 4;
+  const int c = e0 >> 7, j = (e0 >> 5) & 3, bb = e0 & 31, is = e0 >> 4;
+  const uint8_t* b = w + blk * Q3KL::kBytes;
+  const float d = h2f_bits(ldg_u16(b + Q3KL::kOffD));
+  const uint32_t lo = is < 8 ? (b[Q3KL::kOffScales + is] & 0xFu) : (uint32_t)(b[Q3KL::kOffScales + is - 8] >> 4);
+  const uint32_t hi = (b[Q3KL::kOffScales + 8 + (is & 3)] >> (2 * (is >> 2))) & 3u;
+  const float dl = __fmul_rn(d, __fsub_rn((float)(int8_t)(lo | (hi << 4)), 32.0f));
+  const uint32_t v = ldg_u32_2b(b + Q3KL::kOffQs + 32 * c + bb), hm = ldg_u32_2b(b + Q3KL::kOffHmask + bb);
+  T* out = y + blk * 256 + e0;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int q = (int)((v >> (8 * t + 2 * j)) & 3u) - (((hm >> (8 * t + 4 * c + j)) & 1u) ? 0 : 4);
+    out[t] = cvt_out<T>(__fmul_rn(dl, (float)q));
+  }
+}
+
 // Q8_K blocks back to f32 (x.d * q, k_quants.rs:2269-2280); one thread per 4 elements
 template <typename T>
 __global__ void __launch_bounds__(256) dequant_q8k_kernel(const uint8_t* __restrict__ w, int64_t n_units, T* __restrict__ y) {

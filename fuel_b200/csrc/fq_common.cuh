@@ -20,7 +20,7 @@ enum Status : int32_t {
 };
 
 // ---- GGUF type ids (fuel-ir/src/quantized.rs:35-75)
-enum GgmlType : int32_t { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ4_1 = 3, kQ5_0 = 6, kQ5_1 = 7, kQ8_0 = 8, kQ8_1 = 9, kQ4K = 12, kQ5K = 13, kQ6K = 14, kQ8K = 15, kBF16 = 30 };
+enum GgmlType : int32_t { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ4_1 = 3, kQ5_0 = 6, kQ5_1 = 7, kQ8_0 = 8, kQ8_1 = 9, kQ2K = 10, kQ3K = 11, kQ4K = 12, kQ5K = 13, kQ6K = 14, kQ8K = 15, kBF16 = 30 };
 
 constexpr int QK_K = 256;
 constexpr int QK_S = 32;
@@ -33,6 +33,8 @@ struct Q5_0L { static constexpr int kBytes = 22, kElems = 32, kOffD = 0, kOffQh 
 struct Q5_1L { static constexpr int kBytes = 24, kElems = 32, kOffD = 0, kOffM = 2, kOffQh = 4, kOffQs = 8; };
 struct Q8_0L { static constexpr int kBytes = 34, kElems = 32, kOffD = 0, kOffQs = 2; };
 struct Q8_1L { static constexpr int kBytes = 36, kElems = 32, kOffD = 0, kOffS = 2, kOffQs = 4; };
+struct Q2KL { static constexpr int kBytes = 84, kElems = 256, kOffScales = 0, kOffQs = 16, kOffD = 80, kOffDmin = 82; };
+struct Q3KL { static constexpr int kBytes = 110, kElems = 256, kOffHmask = 0, kOffQs = 32, kOffScales = 96, kOffD = 108; };
 struct Q4KL { static constexpr int kBytes = 144, kElems = 256, kOffD = 0, kOffDmin = 2, kOffScales = 4, kOffQs = 16; };
 struct Q5KL { static constexpr int kBytes = 176, kElems = 256, kOffD = 0, kOffDmin = 2, kOffScales = 4, kOffQh = 16, kOffQs = 48; };
 struct Q6KL { static constexpr int kBytes = 210, kElems = 256, kOffQl = 0, kOffQh = 128, kOffScales = 192, kOffD = 208; };
@@ -41,7 +43,7 @@ struct Q8KL { static constexpr int kBytes = 292, kElems = 256, kOffD = 0, kOffQs
 __host__ __device__ inline int block_elems(int t) {
   switch (t) {
     case kQ4_0: case kQ4_1: case kQ5_0: case kQ5_1: case kQ8_0: case kQ8_1: return 32;
-    case kQ4K: case kQ5K: case kQ6K: case kQ8K: return 256;
+    case kQ2K: case kQ3K: case kQ4K: case kQ5K: case kQ6K: case kQ8K: return 256;
     default: return 0;
   }
 }
@@ -53,6 +55,8 @@ __host__ __device__ inline int block_bytes(int t) {
     case kQ5_1: return 24;
     case kQ8_1: return 36;
     case kQ8_0: return 34;
+    case kQ2K: return 84;
+    case kQ3K: return 110;
     case kQ4K: return 144;
     case kQ5K: return 176;
     case kQ6K: return 210;
@@ -64,7 +68,7 @@ __host__ __device__ inline int block_bytes(int t) {
 // (GgmlType::VecDotType, k_quants.rs:174,275,380,491,608,1372,1930): Q8_K for k-quants, Q8_1 for the formats with a
 // per-block minimum (Q4_1, Q5_1), Q8_0 otherwise.
 __host__ __device__ inline int act_type_for(int t) {
-  return (t == kQ4K || t == kQ5K || t == kQ6K) ? kQ8K : (t == kQ4_1 || t == kQ5_1) ? kQ8_1 : kQ8_0;
+  return (t == kQ2K || t == kQ3K || t == kQ4K || t == kQ5K || t == kQ6K) ? kQ8K : (t == kQ4_1 || t == kQ5_1) ? kQ8_1 : kQ8_0;
 }
 
 // ---- internal activation layout ("packed"): the same numbers as the reference's

@@ -62,7 +62,8 @@ bool device_info(DeviceInfo** out) {
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 bool supported_weight(int t) {
-  return t == kQ4_0 || t == kQ4_1 || t == kQ5_0 || t == kQ5_1 || t == kQ8_0 || t == kQ4K || t == kQ5K || t == kQ6K;
+  return t == kQ4_0 || t == kQ4_1 || t == kQ5_0 || t == kQ5_1 || t == kQ8_0 || t == kQ2K || t == kQ3K || t == kQ4K || t == kQ5K ||
+         t == kQ6K;
 }
 
 // launch with or without the programmatic-dependent-launch attribute
@@ -491,6 +492,14 @@ int32_t decode_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, co
     case kQ4_0:
       p.units_per_row = (int)(k / 32);
       e = launch_decode_fmt<Q4_0Decode>(p, pl, stream);
+      break;
+    case kQ2K:
+      p.units_per_row = (int)(k / 256) * Q2KDecode::kUnitsPerBlock;
+      e = launch_decode_fmt<Q2KDecode>(p, pl, stream);
+      break;
+    case kQ3K:
+      p.units_per_row = (int)(k / 256) * Q3KDecode::kUnitsPerBlock;
+      e = launch_decode_fmt<Q3KDecode>(p, pl, stream);
       break;
     case kQ4_1:
       p.units_per_row = (int)(k / 32);
@@ -1627,7 +1636,7 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
     case kQ6K: units = nb * 16; break;
     case kQ8_0: units = nb * 4; break;
     case kQ4_0: case kQ4_1: case kQ5_0: case kQ5_1: units = nb * 4; break;
-    case kQ8K: units = nb * 64; break;
+    case kQ8K: case kQ2K: case kQ3K: units = nb * 64; break;
     default: return kNotSupported;
   }
   const dim3 block(256), grid((unsigned)((units + 255) / 256));
@@ -1660,6 +1669,8 @@ int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, v
     case kQ5_1: FQ_DEQ_L(Q5_1L, true, true); break;
 #undef FQ_DEQ_L
     case kQ8K: FQ_DEQ(dequant_q8k_kernel); break;
+    case kQ2K: FQ_DEQ(dequant_q2k_kernel); break;
+    case kQ3K: FQ_DEQ(dequant_q3k_kernel); break;
   }
 #undef FQ_DEQ
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailure;

@@ -186,7 +186,12 @@ def _quantize(t: T, w: torch.Tensor) -> torch.Tensor:
 
 
 _SEED_SLOT = {"attn_q": 1, "attn_k": 2, "attn_v": 3, "attn_output": 4, "ffn_gate": 5, "ffn_up": 6, "ffn_down": 7}
-_K_QUANTS = (T.Q4K, T.Q5K, T.Q6K)  # their activations are Q8_K blocks; Q8_0 / Q4_0 weights take Q8_0 activations
+_K_QUANTS = (T.Q2K, T.Q3K, T.Q4K, T.Q5K, T.Q6K)  # their activations are Q8_K blocks
+
+
+def _act_kind(t: T) -> T:
+    """The activation block format a weight format takes (GgmlType::VecDotType in the reference)."""
+    return T.Q8K if t in _K_QUANTS else T.Q8_1 if t in (T.Q4_1, T.Q5_1) else T.Q8_0
 
 
 class SyntheticWeights:
@@ -260,7 +265,7 @@ class GgufWeights:
     its rows from the mapping to its GPU —, norm gains and the embedding table become f32; `output.weight` falls
     back to `token_embd.weight` (tied embeddings) when absent."""
 
-    LINEAR_FORMATS = (T.Q4K, T.Q5K, T.Q6K, T.Q8_0, T.Q4_0)
+    LINEAR_FORMATS = (T.Q4K, T.Q5K, T.Q6K, T.Q8_0, T.Q4_0, T.Q4_1, T.Q5_0, T.Q5_1, T.Q2K, T.Q3K)
 
     def __init__(self, path, device: torch.device):
         from .gguf import GgufFile
@@ -434,7 +439,7 @@ class QLlama:
         self.parts = torch.zeros(g, c.dim, **f32) if g > 1 else self.part.view(1, c.dim)   # every rank's, in rank order
         self.logits_l = torch.zeros(c.vocab // g, **f32)
         self._logits = torch.zeros(c.vocab, **f32) if g > 1 else self.logits_l
-        nb = max(_L.fuelq_act_packed_bytes(int(t), 1, k) for t in (T.Q4K, T.Q8_0) for k in (c.dim, c.ffn_dim))
+        nb = max(_L.fuelq_act_packed_bytes(int(t), 1, k) for t in (T.Q4K, T.Q8_0, T.Q4_1) for k in (c.dim, c.ffn_dim))
         self.packed = torch.zeros(nb, dtype=torch.uint8, device=device)
         self.attn_ws = torch.zeros(max(_L.fuelq_attn_decode_workspace_bytes(self.hl), 16), dtype=torch.uint8, device=device)
         # per layer: what the attention call needs to rotate q/k itself and append k, v to that layer's caches
@@ -484,7 +489,7 @@ class QLlama:
         for lin, out in zip(lins, outs):
             if lin is None:
                 continue
-            want = lin.dtype in _K_QUANTS
+            want = _act_kind(lin.dtype)
             if want != fmt:
                 self._quant(x, k, stream, lin.dtype)
                 fmt = want

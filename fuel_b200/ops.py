@@ -38,7 +38,7 @@ def quantize_act(weight_dtype: GgmlDType, x: torch.Tensor) -> torch.Tensor:
     _need_cuda(x, "x")
     k = x.shape[-1]
     m = x.numel() // k
-    act = (GgmlDType.Q8K if weight_dtype in (GgmlDType.Q4K, GgmlDType.Q5K, GgmlDType.Q6K)
+    act = (GgmlDType.Q8K if weight_dtype in (GgmlDType.Q2K, GgmlDType.Q3K, GgmlDType.Q4K, GgmlDType.Q5K, GgmlDType.Q6K)
            else GgmlDType.Q8_1 if weight_dtype in (GgmlDType.Q4_1, GgmlDType.Q5_1) else GgmlDType.Q8_0)
     if k % act.block_size():
         _lib.check(_lib.INVALID_PROBLEM, "quantize_act")

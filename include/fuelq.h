@@ -39,6 +39,8 @@ extern "C" {
 #define FUELQ_TYPE_Q5_1 7
 #define FUELQ_TYPE_Q8_0 8
 #define FUELQ_TYPE_Q8_1 9 /* activation blocks only (the dot-product partner of Q4_1 / Q5_1) */
+#define FUELQ_TYPE_Q2K 10 /* Q2_K, Q3_K: mat-vec at every batch size through the exact-integer decode kernel, and dequantize */
+#define FUELQ_TYPE_Q3K 11
 #define FUELQ_TYPE_Q4K 12
 #define FUELQ_TYPE_Q5K 13 /* mat-vec (every batch size through the exact-integer decode kernels) and dequantize only */
 #define FUELQ_TYPE_Q6K 14
@@ -93,7 +95,7 @@ int64_t fuelq_get_option(int32_t key);
 int32_t fuelq_device_error(int32_t* host_code_out, int32_t clear);
 
 /* Activation quantization to the weight format's dot-product partner: Q8_K blocks for
- * Q4K/Q5K/Q6K weights, Q8_1 blocks (BlockQ8_1::from_float, k_quants.rs:728-757) for Q4_1/Q5_1, Q8_0 blocks otherwise — the first half of the reference's
+ * Q2K/Q3K/Q4K/Q5K/Q6K weights, Q8_1 blocks (BlockQ8_1::from_float, k_quants.rs:728-757) for Q4_1/Q5_1, Q8_0 blocks otherwise — the first half of the reference's
  * matmul (fuel-quantized/src/k_quants.rs:2303-2313, BlockQ8K::from_float :2230-2267,
  * BlockQ8_0::from_float :629-658). Output bytes are identical to the reference's.
  * x: f32 [m_total, k]; q8_blocks: m_total * k / block * block_bytes bytes, 4-byte aligned. */
@@ -134,8 +136,8 @@ int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t 
  * fuel_quantized::matmul (k_quants.rs:2284-2331) and the CUDA entry it replaces,
  * baracuda_kernels_mmvq_<fmt>_batched_run (fuel-cuda-backend/src/quantized.rs:138-231).
  * Quantizes x, then runs the decode mat-vec (m_total <= DECODE_MAX_M) or the
- * tensor-core path. Weight formats: Q4_K, Q6_K, Q8_0 (both paths); Q4_0, Q4_1, Q5_0, Q5_1 and Q5_K (decode kernels at
- * any m_total).
+ * tensor-core path. Weight formats: Q4_K, Q6_K, Q8_0 (both paths); Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K and Q5_K (decode
+ * kernels at any m_total).
  * w must be 16-byte aligned, x and y 16-byte aligned. */
 int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
                       float* y, void* workspace, size_t workspace_bytes, void* stream);

@@ -20,6 +20,8 @@ struct BlkQ5_0 { uint16_t d; uint8_t qh[4]; uint8_t qs[16]; };                  
 struct BlkQ5_1 { uint16_t d; uint16_t m; uint8_t qh[4]; uint8_t qs[16]; };        // k_quants.rs:84-90
 struct BlkQ8_0 { uint16_t d; int8_t qs[32]; };                                    // k_quants.rs:94-98
 struct BlkQ8_1 { uint16_t d; uint16_t s; int8_t qs[32]; };                        // k_quants.rs:102-107
+struct BlkQ2K  { uint8_t scales[16]; uint8_t qs[64]; uint16_t d; uint16_t dmin; };   // k_quants.rs:110-116
+struct BlkQ3K  { uint8_t hmask[32]; uint8_t qs[64]; uint8_t scales[12]; uint16_t d; }; // k_quants.rs:120-126
 struct BlkQ4K  { uint16_t d; uint16_t dmin; uint8_t scales[12]; uint8_t qs[128]; }; // k_quants.rs:132-138
 struct BlkQ6K  { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; uint16_t d; }; // k_quants.rs:154-160
 struct BlkQ8K  { float d; int8_t qs[256]; int16_t bsums[16]; };                   // k_quants.rs:164-169
@@ -27,6 +29,7 @@ struct BlkQ8K  { float d; int8_t qs[256]; int16_t bsums[16]; };                 
 static_assert(sizeof(BlkQ4_0) == 18, "Q4_0");
 static_assert(sizeof(BlkQ8_0) == 34, "Q8_0");
 static_assert(sizeof(BlkQ4_1) == 20 && sizeof(BlkQ5_0) == 22 && sizeof(BlkQ5_1) == 24 && sizeof(BlkQ8_1) == 36, "legacy blocks");
+static_assert(sizeof(BlkQ2K) == 84 && sizeof(BlkQ3K) == 110, "Q2_K / Q3_K");
 static_assert(sizeof(BlkQ4K) == 144, "Q4_K");
 struct BlkQ5K  { uint16_t d; uint16_t dmin; uint8_t scales[12]; uint8_t qh[32]; uint8_t qs[128]; }; // k_quants.rs:142-148
 static_assert(sizeof(BlkQ5K) == 176, "Q5_K");
@@ -34,7 +37,7 @@ static_assert(sizeof(BlkQ6K) == 210, "Q6_K");
 static_assert(sizeof(BlkQ8K) == 292, "Q8_K");
 
 // GGUF type ids, fuel-ir/src/quantized.rs:35-75.
-enum : int { GGML_Q4_0 = 2, GGML_Q4_1 = 3, GGML_Q5_0 = 6, GGML_Q5_1 = 7, GGML_Q8_0 = 8, GGML_Q8_1 = 9, GGML_Q4K = 12, GGML_Q5K = 13, GGML_Q6K = 14, GGML_Q8K = 15 };
+enum : int { GGML_Q4_0 = 2, GGML_Q4_1 = 3, GGML_Q5_0 = 6, GGML_Q5_1 = 7, GGML_Q8_0 = 8, GGML_Q8_1 = 9, GGML_Q2K = 10, GGML_Q3K = 11, GGML_Q4K = 12, GGML_Q5K = 13, GGML_Q6K = 14, GGML_Q8K = 15 };
 
 // IEEE binary16 <-> binary32, round-to-nearest-even, what `half::f16` does.
 static inline float h2f(uint16_t h) {

@@ -6,11 +6,13 @@
 // timed CPU baseline uses; it differs from the scalar order only in f32
 // rounding of the running sums.
 //
-// Follows fuel-quantized/src/avx.rs:13-48 (helpers), :51-88 (Q4_0, Q8_0), :92-243 (Q4_1, Q5_0, Q5_1),
+// Follows fuel-quantized/src/avx.rs:13-48 (helpers), :51-88 (Q4_0, Q8_0), :92-243 (Q4_1, Q5_0, Q5_1), :380-596 (Q2_K, Q3_K),
 // :287-372 (Q6_K), :599-681 (Q4_K).
 #include "blocks.h"
 
 #include <immintrin.h>
+
+#include <cstring>
 
 namespace fq_oracle {
 
@@ -110,6 +112,57 @@ float q5_1_q8_1_dot_avx2(int64_t n, const BlkQ5_1* xs, const BlkQ8_1* ys) {
     acc = _mm256_fmadd_ps(d, dot_u8_quads(q, _mm256_loadu_si256((const __m256i*)ys[b].qs)), acc);
   }
   return reduce8(acc) + summs;
+}
+
+// Q2_K and Q3_K in the AVX2 order (avx.rs:380-455, 463-596). Both build, per block, eight i32 lanes: the 32 bytes of
+// a quant register cover elements b = 0..31 of a 32-element group, adjacent bytes are paired and adjacent pairs
+// added, so lane u holds bytes 4u..4u+3 (lanes 0-3: the group's first 16-element scale, lanes 4-7: its second), summed
+// over the eight groups of the block; then one fused multiply-add of the block scale into eight f32 lanes.
+static inline __m256 lanes_to_ps(const int32_t (&v)[8]) {
+  return _mm256_cvtepi32_ps(_mm256_loadu_si256((const __m256i*)v));
+}
+float q2k_q8k_dot_avx2(int64_t n, const BlkQ2K* xs, const BlkQ8K* ys) {
+  __m256 acc = _mm256_setzero_ps();
+  for (int64_t ib = 0; ib < n / QK_K; ++ib) {
+    const BlkQ2K& x = xs[ib];
+    const BlkQ8K& y = ys[ib];
+    const float d = y.d * h2f(x.d), dmin = -y.d * h2f(x.dmin);
+    int32_t mins[8], sumi[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int u = 0; u < 8; ++u)
+      mins[u] = (int32_t)(x.scales[2 * u] >> 4) * y.bsums[2 * u] + (int32_t)(x.scales[2 * u + 1] >> 4) * y.bsums[2 * u + 1];
+    acc = _mm256_fmadd_ps(_mm256_set1_ps(dmin), lanes_to_ps(mins), acc);
+    for (int g = 0; g < 8; ++g)       // 32-element groups: chunk g / 4, bit pair g % 4
+      for (int b = 0; b < 32; ++b) {
+        const int q = (x.qs[32 * (g / 4) + b] >> (2 * (g % 4))) & 3;
+        sumi[b / 4] += (int32_t)(x.scales[2 * g + b / 16] & 0xF) * q * (int32_t)y.qs[32 * g + b];
+      }
+    acc = _mm256_fmadd_ps(_mm256_set1_ps(d), lanes_to_ps(sumi), acc);
+  }
+  return reduce8(acc);
+}
+float q3k_q8k_dot_avx2(int64_t n, const BlkQ3K* xs, const BlkQ8K* ys) {
+  __m256 acc = _mm256_setzero_ps();
+  for (int64_t ib = 0; ib < n / QK_K; ++ib) {
+    const BlkQ3K& x = xs[ib];
+    const BlkQ8K& y = ys[ib];
+    const float d = y.d * h2f(x.d);
+    uint32_t a[3];
+    std::memcpy(a, x.scales, 12);
+    const uint32_t m1 = 0x03030303u, m2 = 0x0f0f0f0fu;
+    const uint32_t w[4] = {(a[0] & m2) | ((a[2] & m1) << 4), (a[1] & m2) | (((a[2] >> 2) & m1) << 4),
+                           ((a[0] >> 4) & m2) | (((a[2] >> 4) & m1) << 4), ((a[1] >> 4) & m2) | (((a[2] >> 6) & m1) << 4)};
+    int8_t sc[16];
+    std::memcpy(sc, w, 16);
+    int32_t sumi[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int g = 0; g < 8; ++g)
+      for (int b = 0; b < 32; ++b) {
+        const int low = (x.qs[32 * (g / 4) + b] >> (2 * (g % 4))) & 3;
+        const int q = low - (((x.hmask[b] >> g) & 1) ? 0 : 4);
+        sumi[b / 4] += ((int32_t)sc[2 * g + b / 16] - 32) * q * (int32_t)y.qs[32 * g + b];
+      }
+    acc = _mm256_fmadd_ps(_mm256_set1_ps(d), lanes_to_ps(sumi), acc);
+  }
+  return reduce8(acc);
 }
 
 // Broadcast scale pair (2j, 2j+1 as 16-bit words) across a 256-bit register:

@@ -566,6 +566,96 @@ float q5k_q8k_dot_scalar(int64_t n, const BlkQ5K* xs, const BlkQ8K* ys) {
   return sumf + s;
 }
 
+// ---------------------------------------------------------------- Q2_K, Q3_K (dequantizers and dot products; the
+// reference's quantizers for these two are not restated: blocks come from files or, in the tests, from random bytes)
+// Element e of a block sits in qs[32 * (e / 128) + e % 32], bits 2 * ((e % 128) / 32) .. +1; every 16 elements share
+// scale index e / 16.
+
+// fuel-quantized/src/k_quants.rs:958-994: y = (d * sc_lo) * q - (dmin * sc_hi), product and difference rounded separately
+void q2k_to_float(const BlkQ2K* xs, int64_t k, float* ys) {
+  for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+    const BlkQ2K& x = xs[ib];
+    const float d = h2f(x.d), mn = h2f(x.dmin);
+    for (int e = 0; e < QK_K; ++e) {
+      const uint8_t sc = x.scales[e / 16];
+      const float dl = d * (float)(sc & 0xF), ml = mn * (float)(sc >> 4);
+      const int q = (x.qs[32 * (e / 128) + e % 32] >> (2 * ((e % 128) / 32))) & 3;
+      ys[ib * QK_K + e] = dl * (float)q - ml;
+    }
+  }
+}
+// k_quants.rs:783-833
+float q2k_q8k_dot_scalar(int64_t n, const BlkQ2K* xs, const BlkQ8K* ys) {
+  float sumf = 0.f;
+  for (int64_t ib = 0; ib < n / QK_K; ++ib) {
+    const BlkQ2K& x = xs[ib];
+    const BlkQ8K& y = ys[ib];
+    int32_t summs = 0;
+    for (int j = 0; j < 16; ++j) summs += (int32_t)y.bsums[j] * (int32_t)(x.scales[j] >> 4);
+    const float dall = y.d * h2f(x.d), dmin = y.d * h2f(x.dmin);
+    int32_t isum = 0;
+    for (int g = 0; g < 16; ++g) {  // groups of 16 elements in index order
+      int32_t part = 0;
+      for (int l = 0; l < 16; ++l) {
+        const int e = 16 * g + l;
+        part += (int32_t)y.qs[e] * (int32_t)((x.qs[32 * (e / 128) + e % 32] >> (2 * ((e % 128) / 32))) & 3);
+      }
+      isum += (int32_t)(x.scales[g] & 0xF) * part;
+    }
+    sumf += dall * (float)isum - dmin * (float)summs;
+  }
+  return sumf;
+}
+
+// the sixteen 6-bit scales of a Q3_K block, still offset by 32 (k_quants.rs:1095-1103, 1319-1327)
+static inline void q3k_scales(const uint8_t* sc12, int8_t out[16]) {
+  uint32_t a[3];
+  std::memcpy(a, sc12, 12);
+  const uint32_t m1 = 0x03030303u, m2 = 0x0f0f0f0fu, tmp = a[2];
+  const uint32_t w[4] = {(a[0] & m2) | ((tmp & m1) << 4), (a[1] & m2) | (((tmp >> 2) & m1) << 4),
+                         ((a[0] >> 4) & m2) | (((tmp >> 4) & m1) << 4), ((a[1] >> 4) & m2) | (((tmp >> 6) & m1) << 4)};
+  std::memcpy(out, w, 16);
+}
+static inline int q3k_value(const BlkQ3K& x, int e) {  // in [-4, 3]
+  const int low = (x.qs[32 * (e / 128) + e % 32] >> (2 * ((e % 128) / 32))) & 3;
+  const int bit = 4 * (e / 128) + (e % 128) / 32;
+  return low - (((x.hmask[e % 32] >> bit) & 1) ? 0 : 4);
+}
+// k_quants.rs:1314-1366
+void q3k_to_float(const BlkQ3K* xs, int64_t k, float* ys) {
+  for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+    const BlkQ3K& x = xs[ib];
+    int8_t sc[16];
+    q3k_scales(x.scales, sc);
+    const float d = h2f(x.d);
+    for (int e = 0; e < QK_K; ++e) {
+      const float dl = d * ((float)sc[e / 16] - 32.0f);
+      ys[ib * QK_K + e] = dl * (float)q3k_value(x, e);
+    }
+  }
+}
+// k_quants.rs:1013-1133: eight running integer lanes per block (element e adds to lane e % 8), scaled by d per block
+// into eight f32 lanes, summed in index order at the end
+float q3k_q8k_dot_scalar(int64_t n, const BlkQ3K* xs, const BlkQ8K* ys) {
+  float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int64_t ib = 0; ib < n / QK_K; ++ib) {
+    const BlkQ3K& x = xs[ib];
+    const BlkQ8K& y = ys[ib];
+    int8_t sc[16];
+    q3k_scales(x.scales, sc);
+    int32_t aux32[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int e = 0; e < QK_K; ++e) {
+      const int16_t p = (int16_t)((int16_t)y.qs[e] * (int16_t)q3k_value(x, e));
+      aux32[e % 8] += ((int32_t)sc[e / 16] - 32) * (int32_t)p;
+    }
+    const float d = h2f(x.d) * y.d;
+    for (int l = 0; l < 8; ++l) sums[l] += d * (float)aux32[l];
+  }
+  float s = 0.f;
+  for (int l = 0; l < 8; ++l) s += sums[l];
+  return s;
+}
+
 // ---------------------------------------------------------------- Q6_K
 // fuel-quantized/src/utils.rs:62-191 with rmse_type=1, qw=null (weights x^2).
 // Writes L[i] in [0, 2*nmax) and returns the fitted scale.

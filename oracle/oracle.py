@@ -16,7 +16,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libfuelq_oracle.so")
 
-Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, Q4K, Q5K, Q6K, Q8K = 2, 3, 6, 7, 8, 9, 12, 13, 14, 15  # GGUF ids, fuel-ir/src/quantized.rs:35-75
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, Q2K, Q3K, Q4K, Q5K, Q6K, Q8K = 2, 3, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15  # GGUF ids, fuel-ir/src/quantized.rs:35-75
 SCALAR, AVX2 = 0, 1
 
 _lib = None

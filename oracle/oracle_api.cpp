@@ -30,6 +30,12 @@ float q5_1_q8_1_dot_scalar(int64_t, const BlkQ5_1*, const BlkQ8_1*);
 float q5_1_q8_1_dot_avx2(int64_t, const BlkQ5_1*, const BlkQ8_1*);
 void q8_1_from_float(const float*, int64_t, BlkQ8_1*);
 void q8_1_to_float(const BlkQ8_1*, int64_t, float*);
+void q2k_to_float(const BlkQ2K*, int64_t, float*);
+float q2k_q8k_dot_scalar(int64_t, const BlkQ2K*, const BlkQ8K*);
+float q2k_q8k_dot_avx2(int64_t, const BlkQ2K*, const BlkQ8K*);
+void q3k_to_float(const BlkQ3K*, int64_t, float*);
+float q3k_q8k_dot_scalar(int64_t, const BlkQ3K*, const BlkQ8K*);
+float q3k_q8k_dot_avx2(int64_t, const BlkQ3K*, const BlkQ8K*);
 void q8_0_from_float(const float*, int64_t, BlkQ8_0*);
 void q8_0_to_float(const BlkQ8_0*, int64_t, float*);
 float q8_0_q8_0_dot_scalar(int64_t, const BlkQ8_0*, const BlkQ8_0*);
@@ -69,6 +75,8 @@ bool fmt_of(int type, Fmt* f) {
     case GGML_Q5_1: *f = {32, 24, GGML_Q8_1}; return true;
     case GGML_Q8_1: *f = {32, 36, GGML_Q8_1}; return true;
     case GGML_Q8_0: *f = {32, 34, GGML_Q8_0}; return true;
+    case GGML_Q2K: *f = {256, 84, GGML_Q8K}; return true;
+    case GGML_Q3K: *f = {256, 110, GGML_Q8K}; return true;
     case GGML_Q4K: *f = {256, 144, GGML_Q8K}; return true;
     case GGML_Q5K: *f = {256, 176, GGML_Q8K}; return true;
     case GGML_Q6K: *f = {256, 210, GGML_Q8K}; return true;
@@ -100,6 +108,8 @@ void dequantize_span(int type, const void* in, int64_t elems, float* y) {
     case GGML_Q5_1: q5_1_to_float((const BlkQ5_1*)in, elems, y); break;
     case GGML_Q8_1: q8_1_to_float((const BlkQ8_1*)in, elems, y); break;
     case GGML_Q8_0: q8_0_to_float((const BlkQ8_0*)in, elems, y); break;
+    case GGML_Q2K: q2k_to_float((const BlkQ2K*)in, elems, y); break;
+    case GGML_Q3K: q3k_to_float((const BlkQ3K*)in, elems, y); break;
     case GGML_Q4K: q4k_to_float((const BlkQ4K*)in, elems, y); break;
     case GGML_Q5K: q5k_to_float((const BlkQ5K*)in, elems, y); break;
     case GGML_Q6K: q6k_to_float((const BlkQ6K*)in, elems, y); break;
@@ -115,6 +125,8 @@ float dot(int type, int order, int64_t k, const void* w, const void* a) {
       case GGML_Q5_0: return q5_0_q8_0_dot_scalar(k, (const BlkQ5_0*)w, (const BlkQ8_0*)a);
       case GGML_Q5_1: return q5_1_q8_1_dot_scalar(k, (const BlkQ5_1*)w, (const BlkQ8_1*)a);
       case GGML_Q8_0: return q8_0_q8_0_dot_scalar(k, (const BlkQ8_0*)w, (const BlkQ8_0*)a);
+      case GGML_Q2K: return q2k_q8k_dot_scalar(k, (const BlkQ2K*)w, (const BlkQ8K*)a);
+      case GGML_Q3K: return q3k_q8k_dot_scalar(k, (const BlkQ3K*)w, (const BlkQ8K*)a);
       case GGML_Q4K: return q4k_q8k_dot_scalar(k, (const BlkQ4K*)w, (const BlkQ8K*)a);
       case GGML_Q5K: return q5k_q8k_dot_scalar(k, (const BlkQ5K*)w, (const BlkQ8K*)a);
       case GGML_Q6K: return q6k_q8k_dot_scalar(k, (const BlkQ6K*)w, (const BlkQ8K*)a);
@@ -126,6 +138,8 @@ float dot(int type, int order, int64_t k, const void* w, const void* a) {
       case GGML_Q5_0: return q5_0_q8_0_dot_avx2(k, (const BlkQ5_0*)w, (const BlkQ8_0*)a);
       case GGML_Q5_1: return q5_1_q8_1_dot_avx2(k, (const BlkQ5_1*)w, (const BlkQ8_1*)a);
       case GGML_Q8_0: return q8_0_q8_0_dot_avx2(k, (const BlkQ8_0*)w, (const BlkQ8_0*)a);
+      case GGML_Q2K: return q2k_q8k_dot_avx2(k, (const BlkQ2K*)w, (const BlkQ8K*)a);
+      case GGML_Q3K: return q3k_q8k_dot_avx2(k, (const BlkQ3K*)w, (const BlkQ8K*)a);
       case GGML_Q4K: return q4k_q8k_dot_avx2(k, (const BlkQ4K*)w, (const BlkQ8K*)a);
       case GGML_Q5K: return q5k_q8k_dot_avx2(k, (const BlkQ5K*)w, (const BlkQ8K*)a);
       case GGML_Q6K: return q6k_q8k_dot_avx2(k, (const BlkQ6K*)w, (const BlkQ8K*)a);
@@ -159,6 +173,7 @@ float fq_oracle_f16_to_f32(uint16_t v) { return h2f(v); }
 int fq_oracle_quantize(int type, const float* x, int64_t elems, void* out, int nthreads) {
   Fmt f;
   if (!fmt_of(type, &f) || elems % f.block_elems) return 2;
+  if (type == GGML_Q2K || type == GGML_Q3K) return 3;  // their quantizers are not restated
   const int64_t nb = elems / f.block_elems;
   const int64_t chunk = 64;
   if (nthreads <= 0) nthreads = omp_get_max_threads();

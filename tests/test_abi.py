@@ -41,10 +41,10 @@ def test_status_strings_and_block_tables(L):
     assert "unknown" in L.status_string(99)
     # fuel-ir/src/quantized.rs:77-103
     from fuel_b200 import GgmlDType as T
-    for t in (T.Q4_0, T.Q8_0, T.Q4K, T.Q5K, T.Q6K, T.Q8K):
+    for t in (T.Q4_0, T.Q4_1, T.Q5_0, T.Q5_1, T.Q8_0, T.Q8_1, T.Q2K, T.Q3K, T.Q4K, T.Q5K, T.Q6K, T.Q8K):
         assert L.lib.fuelq_block_elems(int(t)) == t.block_size()
         assert L.lib.fuelq_block_bytes(int(t)) == t.type_size()
-    assert L.lib.fuelq_block_elems(11) == 0  # Q3K: not handled
+    assert L.lib.fuelq_block_elems(5) == 0 and L.lib.fuelq_block_bytes(16) == 0  # ids GGUF does not assign to these formats
     assert T.from_u32(12) is T.Q4K and T.Q6K.to_u32() == 14
     with pytest.raises(ValueError):
         T.from_u32(99)
@@ -57,7 +57,7 @@ def test_argument_validation_needs_no_device(L):
     assert f.fuelq_qmatmul(Q4K, 1, 8, 255, 16, 16, 16, 16, 1 << 20, None) == L.INVALID_PROBLEM
     assert f.fuelq_qmatmul(Q8_0, 1, 8, 33, 16, 16, 16, 16, 1 << 20, None) == L.INVALID_PROBLEM
     assert f.fuelq_qmatmul(Q4K, -1, 8, 256, 16, 16, 16, 16, 1 << 20, None) == L.INVALID_PROBLEM
-    assert f.fuelq_qmatmul(11, 1, 8, 256, 16, 16, 16, 16, 1 << 20, None) == L.NOT_SUPPORTED
+    assert f.fuelq_qmatmul(9, 1, 8, 256, 16, 16, 16, 16, 1 << 20, None) == L.NOT_SUPPORTED   # Q8_1: activation blocks only
     # empty problems succeed without touching anything (byte_kernels.rs:4805-4807)
     assert f.fuelq_qmatmul(Q4K, 0, 8, 256, None, None, None, None, 0, None) == L.OK
     assert f.fuelq_qmatmul(Q4K, 1, 0, 256, None, None, None, None, 0, None) == L.OK

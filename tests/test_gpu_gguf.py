@@ -127,14 +127,14 @@ def test_loader_refusals(tmp_path):
     import dataclasses
     with pytest.raises(ValueError, match="elements, expected"):   # a config that does not fit the file
         QLlama.from_gguf(path, dev, cfg=dataclasses.replace(cfg, ffn_dim=768))
-    # a linear in a format the mat-vec does not take
+    # a linear in a format the mat-vec does not take (Q8_K is an activation format)
     bad = str(tmp_path / "bad.gguf")
     with G.GgufFile(path) as f:
         tensors = [(n, i.ggml_dtype, i.shape, f.tensor_bytes(n)) for n, i in f.tensor_infos.items() if n != "blk.1.attn_output.weight"]
         meta = [(k, f.metadata_types[k], v) for k, v in f.metadata.items()]
-    tensors.append(("blk.1.attn_output.weight", T.Q3K, (cfg.dim, cfg.dim), np.zeros(cfg.dim * cfg.dim // 256 * 110, np.uint8)))
+    tensors.append(("blk.1.attn_output.weight", T.Q8K, (cfg.dim, cfg.dim), np.zeros(cfg.dim * cfg.dim // 256 * 292, np.uint8)))
     G.write_gguf(bad, meta, tensors)
-    with pytest.raises(NotImplementedError, match="Q3K"):
+    with pytest.raises(NotImplementedError, match="Q8K"):
         QLlama.from_gguf(bad, dev)
     with pytest.raises(KeyError, match="missing tensor"):
         G.write_gguf(bad, meta, tensors[:-1])

@@ -131,3 +131,52 @@ def test_golden_fixture(ops):
         assert np.abs(y - g[f"{name}_y_scalar"]).max() <= 2e-6 * np.abs(g[f"{name}_y_scalar"]).max()
         got = ops.dequantize(_T(name), _dev(g[f"{name}_blocks"]), g["w"].size).cpu().numpy()
         assert np.array_equal(got.view(np.uint32), g[f"{name}_dequant"].view(np.uint32))
+
+
+def test_model_with_mixed_legacy_linears_from_gguf(tmp_path, oracle):
+    """A GGUF file whose linears are Q4_1 / Q5_0 / Q5_1 / Q4_0 / Q8_0 (three activation block formats in one layer: Q8_1, Q8_0
+    and, for the Q6_K ffn_down, Q8_K) loads and decodes the CPU path's greedy tokens (the plain step: one quantization per
+    activation format per input vector)."""
+    from fuel_b200 import gguf as G, ops as _ops
+    from fuel_b200.ggml import GgmlDType as T
+    from fuel_b200.llama import LlamaConfig, QLlama, rope_tables
+    from oracle.llama_oracle import OracleLlama
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    O = oracle
+    c = LlamaConfig(dim=256, n_layers=2, n_heads=2, n_kv_heads=2, head_dim=128, ffn_dim=512, vocab=512, max_seq=48)
+    rng = np.random.Generator(np.random.PCG64(23))
+    shapes = {"attn_q": ("q", c.dim, c.dim, T.Q4_1, O.Q4_1), "attn_k": ("k", c.dim, c.dim, T.Q4_1, O.Q4_1),
+              "attn_v": ("v", c.dim, c.dim, T.Q5_0, O.Q5_0), "attn_output": ("o", c.dim, c.dim, T.Q5_1, O.Q5_1),
+              "ffn_gate": ("gate", c.ffn_dim, c.dim, T.Q4_0, O.Q4_0), "ffn_up": ("up", c.ffn_dim, c.dim, T.Q4_0, O.Q4_0),
+              "ffn_down": ("down", c.dim, c.ffn_dim, T.Q6K, O.Q6K)}
+
+    def qb(ot, n, k):
+        return np.asarray(O.quantize(ot, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.05)), np.uint8).reshape(-1)
+
+    emb = qb(O.Q8_0, c.vocab, c.dim)
+    tensors, olayers = [("token_embd.weight", T.Q8_0, (c.vocab, c.dim), emb)], []
+    for li in range(c.n_layers):
+        ol = {}
+        for nm, (short, n, k, t, ot) in shapes.items():
+            b = qb(ot, n, k)
+            tensors.append((f"blk.{li}.{nm}.weight", t, (n, k), b))
+            ol[short] = (ot, b, n, k)
+        for nm in ("attn_norm", "ffn_norm"):
+            tensors.append((f"blk.{li}.{nm}.weight", T.F32, (c.dim,), np.ones(c.dim, np.float32).view(np.uint8)))
+        olayers.append(ol)
+    tensors.append(("output_norm.weight", T.F32, (c.dim,), np.ones(c.dim, np.float32).view(np.uint8)))
+    head = qb(O.Q5_1, c.vocab, c.dim)
+    tensors.append(("output.weight", T.Q5_1, (c.vocab, c.dim), head))
+    meta = [("general.architecture", G.STRING, "llama"), ("llama.block_count", G.U32, c.n_layers),
+            ("llama.attention.head_count", G.U32, c.n_heads)]
+    path = str(tmp_path / "legacy.gguf")
+    G.write_gguf(path, meta, tensors)
+    model = QLlama.from_gguf(path, torch.device("cuda", 0), max_seq=c.max_seq)
+    assert not model.fused and model.head.dtype == T.Q5_1
+    cos, sin = rope_tables(model.cfg)
+    emb_f32 = O.dequantize(O.Q8_0, emb).reshape(c.vocab, c.dim)
+    twin = OracleLlama(model.cfg, emb_f32, olayers, (O.Q5_1, head, c.vocab, c.dim), cos, sin)
+    prompt = rng.integers(0, c.vocab, 6).tolist()
+    assert model.generate(prompt, 8) == twin.generate(prompt, 8)
+    assert _ops.device_error() == 0

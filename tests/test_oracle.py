@@ -15,18 +15,20 @@ import pytest
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "kquants_golden.npz")
 FORMATS = ("q4_0", "q4_1", "q5_0", "q5_1", "q8_0", "q4k", "q5k", "q6k")
 # byte offsets of the f16 fields of a block (kept finite when blocks are drawn from random bytes)
-F16_FIELDS = {"q4_0": (0,), "q4_1": (0, 2), "q5_0": (0,), "q5_1": (0, 2), "q8_0": (0,), "q4k": (0, 2), "q5k": (0, 2), "q6k": (208,)}
+# formats whose quantizer is not restated: their blocks are random bytes in every test
+NO_QUANTIZER = ("q2k", "q3k")
+F16_FIELDS = {"q2k": (80, 82), "q3k": (108,), "q4_0": (0,), "q4_1": (0, 2), "q5_0": (0,), "q5_1": (0, 2), "q8_0": (0,), "q4k": (0, 2), "q5k": (0, 2), "q6k": (208,)}
 
 
 def _t(O, name):
-    return {"q4_0": O.Q4_0, "q4_1": O.Q4_1, "q5_0": O.Q5_0, "q5_1": O.Q5_1, "q8_0": O.Q8_0, "q4k": O.Q4K, "q5k": O.Q5K,
-            "q6k": O.Q6K}[name]
+    return {"q4_0": O.Q4_0, "q4_1": O.Q4_1, "q5_0": O.Q5_0, "q5_1": O.Q5_1, "q8_0": O.Q8_0, "q2k": O.Q2K, "q3k": O.Q3K,
+            "q4k": O.Q4K, "q5k": O.Q5K, "q6k": O.Q6K}[name]
 
 
 def _gt(gguf, name):
     G = gguf.GGMLQuantizationType
-    return {"q4_0": G.Q4_0, "q4_1": G.Q4_1, "q5_0": G.Q5_0, "q5_1": G.Q5_1, "q8_0": G.Q8_0, "q4k": G.Q4_K, "q5k": G.Q5_K,
-            "q6k": G.Q6_K}[name]
+    return {"q4_0": G.Q4_0, "q4_1": G.Q4_1, "q5_0": G.Q5_0, "q5_1": G.Q5_1, "q8_0": G.Q8_0, "q2k": G.Q2_K, "q3k": G.Q3_K,
+            "q4k": G.Q4_K, "q5k": G.Q5_K, "q6k": G.Q6_K}[name]
 
 
 def test_block_sizes(oracle):
@@ -177,7 +179,7 @@ def _dequant_act_blocks(O, name, act, m, k):
     """The activation blocks as real numbers, decoded here in numpy (not by the restatement):
     Q8_K = {d: f32, qs: i8[256], bsums: i16[16]} -> d * qs (k_quants.rs:162-169);
     Q8_0 = {d: f16, qs: i8[32]} -> d * qs (k_quants.rs:92-98). Also checks the Q8_K block sums."""
-    if name in ("q4k", "q5k", "q6k"):
+    if name.endswith("k"):
         b = act.reshape(m, k // 256, 292)
         d = b[:, :, :4].copy().view(np.float32).astype(np.float64)
         qs = b[:, :, 4:260].copy().view(np.int8).astype(np.float64)
@@ -196,7 +198,7 @@ def _dequant_act_blocks(O, name, act, m, k):
 
 
 @pytest.mark.parametrize("source", ("quantizer", "random_bytes"))
-@pytest.mark.parametrize("name", FORMATS)
+@pytest.mark.parametrize("name", FORMATS + NO_QUANTIZER)
 def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
     """Tight pin of the integer dot products (k_quants.rs:1388-1468 Q4_K, 1946-2003 Q6_K, 674-692 Q8_0,
     252-269 Q4_0, 1770-1925 Q5_K and their AVX2 bodies): both operands of a vec_dot are exact integers
@@ -210,6 +212,8 @@ def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
     gt = _gt(gguf, name)
     n, k, m = 48, 2048, 3
     rng = np.random.Generator(np.random.PCG64(21))
+    if source == "quantizer" and name in NO_QUANTIZER:
+        pytest.skip("no restated quantizer for this format")
     if source == "quantizer":
         wb = O.quantize(t, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
     else:
@@ -248,3 +252,20 @@ def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
         for order in (O.SCALAR, O.AVX2):
             v = O.vec_dot(t, order, k, np.ascontiguousarray(rb[j]), np.ascontiguousarray(ab[i]))
             assert abs(v - want[i, j]) <= 2e-6 * scale
+
+
+@pytest.mark.parametrize("name", NO_QUANTIZER)
+def test_q2k_q3k_dequantize_like_gguf_py(oracle, name):
+    """Q2_K / Q3_K (k_quants.rs:958-994, 1314-1366): to_float bit-identical to gguf-py's on random block bytes, and the
+    block sizes of fuel-ir/src/quantized.rs:77-103."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    O = oracle
+    t = _t(O, name)
+    assert (O.block_elems(t), O.block_bytes(t)) == {"q2k": (256, 84), "q3k": (256, 110)}[name]
+    blocks = np.random.Generator(np.random.PCG64(31)).integers(0, 256, (64, O.block_bytes(t)), dtype=np.uint8)
+    for off in F16_FIELDS[name]:
+        blocks[:, off + 1] &= 0x3B
+    ours = O.dequantize(t, blocks.reshape(-1))
+    theirs = quants.dequantize(blocks.reshape(4, -1), _gt(gguf, name)).reshape(-1)
+    assert np.array_equal(ours.view(np.uint32), theirs.view(np.uint32))
