@@ -335,7 +335,7 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
   for (int sl = 0; sl <= 8; ++sl) p.u_begin[sl] = sl <= pl.ks ? (int)((int64_t)p.units_per_row * sl / pl.ks) : p.units_per_row;
   p.depth = g_opt.dbg_depth ? (int)g_opt.dbg_depth : 3;
   if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
-  p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
+  p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 1;  // one weight stage in flight until the activations are held
   if (staged && !reserve) p.pre_stages = pl.num_stages - 1;
   cudaError_t e;
   if (peer) {
@@ -445,7 +445,7 @@ int32_t decode_tree_impl(int type, int64_t n, int64_t k, const void* w, const Ac
   for (int sl = 0; sl <= 8; ++sl) p.u_begin[sl] = 0;
   p.depth = g_opt.dbg_depth ? (int)g_opt.dbg_depth : 3;
   if (p.depth >= pl.num_stages) p.depth = pl.num_stages - 1;
-  p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 0;
+  p.pre_stages = g_opt.dbg_pre >= 0 ? (int)g_opt.dbg_pre : 1;  // one weight stage in flight until the activations are held
   const cudaError_t e = type == kQ4K ? launch_decode_tree<Q4KRegs>(p, peer, pl, stream)
                                      : launch_decode_tree<Q6KRegs>(p, peer, pl, stream);
   return e == cudaSuccess ? kOk : kLaunchFailure;
