@@ -201,7 +201,7 @@ def test_llama_loader_reads_architecture_and_checks_shapes(tmp_path):
     for li in range(layers):
         for nm, (n, k), t in (("attn_q", (dim, dim), T.Q4K), ("attn_k", (dim // 2, dim), T.Q4K), ("attn_v", (dim // 2, dim), T.Q6K),
                               ("attn_output", (dim, dim), T.Q8_0), ("ffn_gate", (ffn, dim), T.Q5K), ("ffn_up", (ffn, dim), T.Q5K),
-                              ("ffn_down", (dim, ffn), T.Q3K if li == 1 else T.Q4_0)):
+                              ("ffn_down", (dim, ffn), T.Q8K if li == 1 else T.Q4_0)):
             tensors.append((f"blk.{li}.{nm}.weight", t, (n, k), blob(t, n, k)))
         for nm in ("attn_norm", "ffn_norm"):
             tensors.append((f"blk.{li}.{nm}.weight", T.F32, (dim,), np.zeros(dim * 4, np.uint8)))
@@ -219,7 +219,7 @@ def test_llama_loader_reads_architecture_and_checks_shapes(tmp_path):
         w.check(dataclasses.replace(cfg, n_kv_heads=2))
     assert w.dtype("attn_v", 0) == T.Q6K and w.dtype("ffn_gate", 1) == T.Q5K and w.dtype("ffn_down", 0) == T.Q4_0
     assert w.dtype("output", -1) == T.Q6K            # no output.weight: the head is the embedding table
-    with pytest.raises(NotImplementedError, match="Q3K"):
+    with pytest.raises(NotImplementedError, match="Q8K"):
         w.dtype("ffn_down", 1)
     with pytest.raises(KeyError, match="missing tensor"):
         w.dtype("attn_q", 2)
