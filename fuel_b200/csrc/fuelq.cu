@@ -1330,6 +1330,21 @@ int32_t fuelq_moe_bucket(const int32_t* topk_ids, int64_t n_pairs, int32_t n_exp
                          int32_t* expert_offsets, void* stream) {
   if (n_pairs < 0 || n_pairs > (1 << 24) || n_experts <= 0 || n_experts > 8192) return kInvalidProblem;
   if (!expert_offsets || (n_pairs > 0 && (!topk_ids || !sorted_ids))) return kInvalidProblem;
+  // per-chunk count table in shared memory when it fits (config 5: 64 chunks x 128 experts = 32 KB)
+  const size_t table = ((size_t)((n_pairs + 31) / 32) * n_experts + n_experts + 1) * sizeof(int);
+  if (n_pairs > 0 && table <= 160 * 1024) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      if (cudaFuncSetAttribute(moe_bucket_chunks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+        return kLaunchFailure;
+      attr_set[dev] = true;
+    }
+    const cudaError_t e = launch(moe_bucket_chunks_kernel, dim3(1), dim3(1024), table, (cudaStream_t)stream, (const int*)topk_ids,
+                                 (int)n_pairs, (int)n_experts, (int*)sorted_ids, (int*)expert_offsets);
+    return e == cudaSuccess ? kOk : kLaunchFailure;
+  }
   const int in_smem = (size_t)(n_experts + 1 + n_pairs) * sizeof(int) <= 48 * 1024 ? 1 : 0;  // default dynamic limit
   const size_t bsm = (size_t)(n_experts + 1 + (in_smem ? n_pairs : 0)) * sizeof(int);
   const cudaError_t e = launch(moe_bucket_kernel, dim3(1), dim3(1024), bsm,

@@ -142,6 +142,67 @@ __global__ void __launch_bounds__(1024) moe_bucket_kernel(const int* topk_ids, i
   }
 }
 
+// The same result in O(pairs) work when a table of per-chunk counts fits shared memory (a chunk = 32 consecutive
+// pairs, one warp pass): a pair's place inside its expert is (pairs of that expert in earlier chunks) + (matching
+// lanes below it in its own chunk), both independent of timing. One CTA.
+__global__ void __launch_bounds__(1024) moe_bucket_chunks_kernel(const int* topk_ids, int n_pairs, int n_experts,
+                                                                 int* sorted_ids, int* offsets) {
+  extern __shared__ int bsm[];  // cnt [n_chunks][n_experts], then start [n_experts + 1]
+  const int n_chunks = (n_pairs + 31) >> 5;
+  int* cnt = bsm;
+  int* start = bsm + n_chunks * n_experts;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < n_chunks * n_experts; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  for (int c = warp; c < n_chunks; c += nwarps) {
+    const int p = 32 * c + lane;
+    int id = p < n_pairs ? topk_ids[p] : -1;
+    if (id < 0 || id >= n_experts) id = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, id);
+    if (id >= 0 && lane == __ffs(same) - 1) cnt[c * n_experts + id] = __popc(same);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {  // per expert: counts -> pairs in earlier chunks
+    int run = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int t = cnt[c * n_experts + e];
+      cnt[c * n_experts + e] = run;
+      run += t;
+    }
+    start[e] = run;
+  }
+  __syncthreads();
+  if (warp == 0) {  // exclusive scan of the per-expert totals: a contiguous segment per lane, then across lanes
+    const int seg = (n_experts + 31) >> 5, e0 = lane * seg, e1 = min(e0 + seg, n_experts);
+    int sum = 0;
+    for (int e = e0; e < e1; ++e) sum += start[e];
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    int run = incl - sum;
+    for (int e = e0; e < e1; ++e) {
+      const int t = start[e];
+      start[e] = run;
+      offsets[e] = run;
+      run += t;
+    }
+    if (lane == 31) start[n_experts] = incl, offsets[n_experts] = incl;
+  }
+  __syncthreads();
+  for (int c = warp; c < n_chunks; c += nwarps) {
+    const int p = 32 * c + lane;
+    int id = p < n_pairs ? topk_ids[p] : -1;
+    if (id < 0 || id >= n_experts) id = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, id);
+    if (id >= 0) sorted_ids[start[id] + cnt[c * n_experts + id] + __popc(same & ((1u << lane) - 1u))] = p;
+  }
+}
+
 // ---- gather + Q8_K quantization: sorted row i <- x[row_ids[i] / divisor] (k a multiple of 256)
 __global__ void __launch_bounds__(256) moe_gather_quantize_kernel(const float* x, int k, const int* row_ids, int divisor,
                                                                   int64_t n_blocks, int8_t* out_qs, float* out_d,
@@ -329,26 +390,45 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) moe_decode_kernel(const Moe
 // ---- combine: out[t] = ((0 + w*y of the lowest expert id) + next ...) over the token's top_k pairs
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y_pairs, const int* topk_ids, const float* topk_w,
                                                           int top_k, int n, float* out) {
+  __shared__ int ord_s[kMoeMaxTopK];
+  __shared__ float w_s[kMoeMaxTopK];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  int ord[kMoeMaxTopK];
-  for (int s = 0; s < top_k; ++s) ord[s] = s;
-  for (int a = 1; a < top_k; ++a) {  // insertion sort of the slots by expert id (ids are distinct)
-    const int sa = ord[a], ea = topk_ids[(size_t)t * top_k + sa];
-    int b = a - 1;
-    while (b >= 0 && topk_ids[(size_t)t * top_k + ord[b]] > ea) {
-      ord[b + 1] = ord[b];
-      --b;
+  if (threadIdx.x == 0) {
+    int ord[kMoeMaxTopK];
+    for (int s = 0; s < top_k; ++s) ord[s] = s;
+    for (int a = 1; a < top_k; ++a) {  // insertion sort of the slots by expert id (ids are distinct)
+      const int sa = ord[a], ea = topk_ids[(size_t)t * top_k + sa];
+      int b = a - 1;
+      while (b >= 0 && topk_ids[(size_t)t * top_k + ord[b]] > ea) {
+        ord[b + 1] = ord[b];
+        --b;
+      }
+      ord[b + 1] = sa;
     }
-    ord[b + 1] = sa;
+    for (int s = 0; s < top_k; ++s) ord_s[s] = ord[s], w_s[s] = topk_w[(size_t)t * top_k + ord[s]];
+  }
+  __syncthreads();
+  const float* base = y_pairs + (size_t)t * top_k * n;
+  if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(y_pairs) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    for (int c = threadIdx.x; c < (n >> 2); c += blockDim.x) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < top_k; ++s) {
+        const float4 v = reinterpret_cast<const float4*>(base + (size_t)ord_s[s] * n)[c];
+        const float w = w_s[s];
+        acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, w));  // scale, then add: two roundings
+        acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, w));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, w));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, w));
+      }
+      reinterpret_cast<float4*>(out + (size_t)t * n)[c] = acc;
+    }
+    return;
   }
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < top_k; ++s) {
-      const size_t pair = (size_t)t * top_k + ord[s];
-      acc = __fadd_rn(acc, __fmul_rn(y_pairs[pair * n + c], topk_w[pair]));  // scale, then add: two roundings
-    }
+    for (int s = 0; s < top_k; ++s) acc = __fadd_rn(acc, __fmul_rn(base[(size_t)ord_s[s] * n + c], w_s[s]));
     out[(size_t)t * n + c] = acc;
   }
 }

@@ -131,3 +131,24 @@ def test_tensor_core_grouped_kernel_matches_dp4a_grouped_kernel(E, n, k, rows):
         assert not torch.isnan(y).any()
         assert (y - want).abs().max().item() <= 2e-6 * want.abs().max().item()
     assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize("P,E", [(0, 8), (1, 4), (31, 128), (33, 5), (2048, 128), (10000, 128), (20000, 128), (4096, 1024), (777, 3)])
+def test_bucketing_is_a_stable_sort_by_expert(P, E):
+    """fuelq_moe_bucket: pair ids ordered by expert, ascending inside an expert, offsets = prefix sums of the counts -
+    for sizes that take the per-chunk count table in shared memory and for sizes that take the scanning kernel."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuel_b200 import _lib
+    ids = np.random.Generator(np.random.PCG64(P + E)).integers(0, E, P).astype(np.int32)
+    if P > 40:
+        ids[7:39] = 2 % E                      # a whole warp pass of one expert
+    d_ids = torch.from_numpy(ids).cuda()
+    sorted_ids = torch.full((max(P, 1),), -1, dtype=torch.int32, device="cuda")
+    offsets = torch.full((E + 1,), -1, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.lib.fuelq_moe_bucket(d_ids.data_ptr() if P else None, P, E, sorted_ids.data_ptr() if P else None,
+                                         offsets.data_ptr(), torch.cuda.current_stream().cuda_stream), "fuelq_moe_bucket")
+    torch.cuda.synchronize()
+    want = np.argsort(ids, kind="stable").astype(np.int32)
+    assert np.array_equal(sorted_ids.cpu().numpy()[:P], want)
+    assert np.array_equal(offsets.cpu().numpy(), np.concatenate([[0], np.cumsum(np.bincount(ids, minlength=E))]).astype(np.int32))
