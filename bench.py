@@ -384,8 +384,9 @@ def run_prefill_sharded(args, rank, local_rank, world, own_group=True):
 
 
 def run_moe_expert_parallel(args, rank, local_rank, world, own_group=True):
-    """benchmark configuration 5 expert-parallel: 128 experts split over the ranks, 256 tokens split over the ranks, two NCCL
-    all-to-alls per block. Eager calls (the exchange sizes are read on the host), CUDA events, max over ranks."""
+    """benchmark configuration 5 expert-parallel: 128 experts split over the ranks, 256 tokens split over the ranks, one NCCL
+    all-to-all with equal splits each way per block, nothing read on the host (eager, stream-ordered calls). CUDA events,
+    max over ranks."""
     import torch
     import torch.distributed as dist
 
@@ -405,7 +406,7 @@ def run_moe_expert_parallel(args, rank, local_rank, world, own_group=True):
         gen.manual_seed(1000 * c + rank)
         bgu = ops.quantize_weights(T.Q4K, torch.randn(El * 2 * F, H, generator=gen, device=dev) * 0.02)
         bd = ops.quantize_weights(T.Q4K, torch.randn(El * H, F, generator=gen, device=dev) * 0.02)
-        blocks.append(QMoeExpertParallel(E, H, F, K, bgu, bd, rank, world, max_local_tokens=nl, max_recv_rows=N * K))
+        blocks.append(QMoeExpertParallel(E, H, F, K, bgu, bd, rank, world, max_local_tokens=nl))
     gen.manual_seed(77 + rank)
     x = torch.randn(nl, H, generator=gen, device=dev)
     logits = torch.randn(nl, E, generator=gen, device=dev)
@@ -429,7 +430,8 @@ def run_moe_expert_parallel(args, rank, local_rank, world, own_group=True):
         wbytes = E * 3 * F * H // 256 * 144
         result = {"workload": f"moe_block_e{E}_h{H}_f{F}_top{K}_tokens{N}_q4k_expert_parallel", "n_gpus": world, "us": us,
                   "tokens_per_s": N / us * 1e6, "GB/s": wbytes / us / 1e3, "weight_bytes_per_gpu": wbytes // world,
-                  "exchange": "four NCCL all-to-all calls (row counts, rows, results, order) and two host reads of the counts per block",
+                  "exchange": "one NCCL all-to-all with equal splits each way per block (fixed-capacity chunks, expert ids in the chunk's "
+                              "last row); no host reads",
                   "cuda_graph": False}
         if own_group:
             print(json.dumps(result), flush=True)

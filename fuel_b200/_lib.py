@@ -100,6 +100,9 @@ PROTOTYPES = {
     "fuelq_add_rmsnorm_q8k_parts": (_i32, [_vp, _vp, _i32, _vp, _i64, ctypes.c_float, _vp, _sz, _vp]),
     "fuelq_qmatmul_packed_tree": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp, _i32, _vp, _vp]),
     "fuelq_qmatmul_packed_tree_peer": (_i32, [_i32, _i64, _i64, _vp, _vp, _vp, _i64, _pp, _i32, _i32, _vp, _vp]),
+    "fuelq_moe_ep_pack": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i64, _vp, _vp]),
+    "fuelq_moe_ep_local_ids": (_i32, [_vp, _i64, _i64, _i32, _i32, _vp, _vp]),
+    "fuelq_moe_ep_unpack": (_i32, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i64, _vp, _vp]),
     "fuelq_argmax_last_peer": (_i32, [_vp, _i64, _vp, _pp, _i32, _vp, _vp]),
     "fuelq_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "fuelq_argmax_last": (_i32, [_vp, _i64, _vp, _vp]),

@@ -1467,6 +1467,54 @@ int32_t fuelq_moe_qmatmul(int32_t ggml_type, int32_t n_experts, int64_t n, int64
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
+namespace {
+int32_t check_ep(int64_t hidden, int64_t n_pairs, int32_t experts_per_rank, int32_t world, int64_t capacity) {
+  if (hidden <= 0 || hidden % 4 || hidden > (1 << 24) || n_pairs < 0 || experts_per_rank <= 0 || world < 1 || world > 64 ||
+      capacity < 1 || capacity > hidden || n_pairs > capacity)
+    return kInvalidProblem;
+  return kOk;
+}
+}  // namespace
+
+int32_t fuelq_moe_ep_pack(const float* x, int64_t hidden, const int32_t* sorted_ids, const int32_t* expert_offsets,
+                          const int32_t* topk_ids, int32_t top_k, int64_t n_pairs, int32_t experts_per_rank, int32_t world,
+                          int64_t capacity, float* send, void* stream) {
+  const int32_t st = check_ep(hidden, n_pairs, experts_per_rank, world, capacity);
+  if (st != kOk) return st;
+  if (top_k <= 0 || !x || !sorted_ids || !expert_offsets || !topk_ids || !send) return kInvalidProblem;
+  if (!aligned(x, 16) || !aligned(send, 16)) return kMisaligned;
+  const cudaError_t e = launch(moe_ep_pack_kernel, dim3((unsigned)(n_pairs + world)), dim3(128), 0, (cudaStream_t)stream, x,
+                               (int)hidden, (const int*)sorted_ids, (const int*)expert_offsets, (const int*)topk_ids, (int)top_k,
+                               (int)n_pairs, (int)experts_per_rank, (int)world, (int)capacity, send);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_moe_ep_local_ids(const float* recv, int64_t hidden, int64_t capacity, int32_t world, int32_t first_expert,
+                               int32_t* local_ids, void* stream) {
+  const int32_t st = check_ep(hidden, 0, 1, world, capacity);
+  if (st != kOk) return st;
+  if (!recv || !local_ids || first_expert < 0) return kInvalidProblem;
+  if (!aligned(recv, 16)) return kMisaligned;
+  const int64_t slots = (int64_t)world * (capacity + 1);
+  const cudaError_t e = launch(moe_ep_local_ids_kernel, dim3((unsigned)((slots + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                               recv, (int)hidden, (int)capacity, (int)world, (int)first_expert, (int*)local_ids);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+int32_t fuelq_moe_ep_unpack(const float* y_back, int64_t hidden, const int32_t* sorted_ids, const int32_t* expert_offsets,
+                            int64_t n_pairs, int32_t experts_per_rank, int32_t world, int64_t capacity, float* y_pairs,
+                            void* stream) {
+  const int32_t st = check_ep(hidden, n_pairs, experts_per_rank, world, capacity);
+  if (st != kOk) return st;
+  if (n_pairs == 0) return kOk;
+  if (!y_back || !sorted_ids || !expert_offsets || !y_pairs) return kInvalidProblem;
+  if (!aligned(y_back, 16) || !aligned(y_pairs, 16)) return kMisaligned;
+  const cudaError_t e = launch(moe_ep_unpack_kernel, dim3((unsigned)n_pairs), dim3(128), 0, (cudaStream_t)stream, y_back,
+                               (int)hidden, (const int*)sorted_ids, (const int*)expert_offsets, (int)n_pairs, (int)experts_per_rank,
+                               (int)world, (int)capacity, y_pairs);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
 int32_t fuelq_moe_combine(const float* y_pairs, const int32_t* topk_ids, const float* topk_weights, int64_t n_tokens,
                           int32_t top_k, int64_t n, float* out, void* stream) {
   if (n_tokens < 0 || n_tokens > (1 << 24) || top_k <= 0 || top_k > kMoeMaxTopK || n <= 0 || n > (1 << 24))

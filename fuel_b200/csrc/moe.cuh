@@ -387,6 +387,67 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) moe_decode_kernel(const Moe
   }
 }
 
+// ---- expert parallelism with fixed-capacity chunks. A (source, destination) pair of ranks owns a chunk of
+// capacity + 1 rows of `hidden` floats: the rows for that destination, sorted by expert, then one row that holds
+// their expert ids as int32 (-1 = unused slot). Sorted position s of this rank's pairs belongs to rank
+// q = (the rank whose experts contain it) at place j = s - offsets[q * experts_per_rank].
+__device__ __forceinline__ int moe_ep_dest(const int* offsets, int experts_per_rank, int world, int s, int* first) {
+  int q = 0;
+  while (q + 1 < world && offsets[(q + 1) * experts_per_rank] <= s) ++q;
+  *first = offsets[q * experts_per_rank];
+  return q;
+}
+// grid = n_pairs + world blocks: block s < n_pairs copies the row of sorted position s into its slot and writes its
+// expert id; block n_pairs + q marks the unused slots of chunk q
+__global__ void __launch_bounds__(128) moe_ep_pack_kernel(const float* x, int hidden, const int* sorted_ids, const int* offsets,
+                                                          const int* topk_ids, int top_k, int n_pairs, int experts_per_rank,
+                                                          int world, int capacity, float* send) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t chunk = (size_t)(capacity + 1) * hidden;
+  if ((int)blockIdx.x >= n_pairs) {
+    const int q = blockIdx.x - n_pairs;
+    const int used = offsets[(q + 1) * experts_per_rank] - offsets[q * experts_per_rank];
+    int* ids = reinterpret_cast<int*>(send + q * chunk + (size_t)capacity * hidden);
+    for (int j = used + threadIdx.x; j < capacity; j += blockDim.x) ids[j] = -1;
+    return;
+  }
+  const int s = blockIdx.x;
+  int first;
+  const int q = moe_ep_dest(offsets, experts_per_rank, world, s, &first);
+  const int j = s - first, pair = sorted_ids[s];
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(pair / top_k) * hidden);
+  float4* dst = reinterpret_cast<float4*>(send + q * chunk + (size_t)j * hidden);
+  for (int c = threadIdx.x; c < (hidden >> 2); c += blockDim.x) dst[c] = src[c];
+  if (threadIdx.x == 0) reinterpret_cast<int*>(send + q * chunk + (size_t)capacity * hidden)[j] = topk_ids[pair];
+}
+// received chunks -> one local expert id per slot (id rows and unused slots: -1)
+__global__ void __launch_bounds__(256) moe_ep_local_ids_kernel(const float* recv, int hidden, int capacity, int world,
+                                                               int first_expert, int* local_ids) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x, per = capacity + 1;
+  if (i >= world * per) return;
+  const int q = i / per, j = i - q * per;
+  int id = -1;
+  if (j < capacity) id = reinterpret_cast<const int*>(recv + ((size_t)q * per + capacity) * hidden)[j];
+  local_ids[i] = id >= 0 ? id - first_expert : -1;
+}
+// returned chunks -> y_pairs in pair order: one block per sorted position
+__global__ void __launch_bounds__(128) moe_ep_unpack_kernel(const float* y_back, int hidden, const int* sorted_ids,
+                                                            const int* offsets, int n_pairs, int experts_per_rank, int world,
+                                                            int capacity, float* y_pairs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int s = blockIdx.x;
+  if (s >= n_pairs) return;
+  int first;
+  const int q = moe_ep_dest(offsets, experts_per_rank, world, s, &first);
+  const float4* src = reinterpret_cast<const float4*>(y_back + ((size_t)q * (capacity + 1) + (s - first)) * hidden);
+  float4* dst = reinterpret_cast<float4*>(y_pairs + (size_t)sorted_ids[s] * hidden);
+  for (int c = threadIdx.x; c < (hidden >> 2); c += blockDim.x) dst[c] = src[c];
+}
+
 // ---- combine: out[t] = ((0 + w*y of the lowest expert id) + next ...) over the token's top_k pairs
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* y_pairs, const int* topk_ids, const float* topk_w,
                                                           int top_k, int n, float* out) {

@@ -81,63 +81,66 @@ class QMoeBlock:
 class QMoeExpertParallel:
     """Expert parallelism over the ranks of a process group: rank r holds experts [r*E/g, (r+1)*E/g) and a share of the
     tokens. A forward routes the local tokens over ALL experts, sends each (token, slot) row to the rank that owns its
-    expert with one all-to-all (rows travel sorted by expert, so they arrive grouped by source rank), runs the local
-    experts over what arrived, returns the results with a second all-to-all and combines on the home rank in ascending
-    expert id - the order of the single-GPU block, whose output it reproduces bit for bit (every row's products do not
-    depend on which other rows share its expert pass). The two exchanges need their split sizes on the host, so this
-    path has one device-to-host read of the routing counts per block; everything else is stream-ordered."""
+    expert, runs the local experts over what arrived, returns the results and combines on the home rank in ascending
+    expert id - the order of the single-GPU block, whose output it reproduces bit for bit (a row's products do not
+    depend on which other rows share its expert pass).
+
+    Nothing is read on the host and every size is fixed, so a forward is a fixed sequence of stream-ordered calls that a
+    CUDA graph can capture: each exchange is ONE all-to-all with equal splits. A (source, destination) pair of ranks owns
+    a chunk of C + 1 rows of `hidden` floats, C = max_local_tokens * top_k being the most rows a rank can send anywhere;
+    the rows travel sorted by expert in the chunk's first rows, and its last row carries their expert ids as int32
+    (-1 = unused). The receiver buckets all chunk slots by local expert (unused slots drop out there), the grouped
+    mat-vecs touch only the rows the bucketing lists, and the results go back in the same slots."""
 
     def __init__(self, n_experts_total: int, hidden: int, ffn: int, top_k: int, local_gate_up_blocks: torch.Tensor,
                  local_down_blocks: torch.Tensor, rank: int, world: int, group=None, dtype: T = T.Q4K,
-                 max_local_tokens: int = 256, max_recv_rows: int = 4096):
+                 max_local_tokens: int = 256):
         import torch.distributed as dist
         assert n_experts_total % world == 0
         self.dist, self.group, self.rank, self.world = dist, group, rank, world
         self.E, self.El, self.H, self.F, self.K = n_experts_total, n_experts_total // world, hidden, ffn, top_k
         dev = local_gate_up_blocks.device
         self.device = dev
-        # routing state of the local tokens (all experts), and the local experts as a block of their own
+        self.C = max_local_tokens * top_k
+        assert self.C <= hidden, "the chunk's id row holds one int32 per row slot"
+        self.Sg = self.C + 1
+        S = world * self.Sg
+        # routing state of the local tokens (all experts), and the local experts as a block over every chunk slot
         self.home = QMoeBlock(self.El, hidden, ffn, top_k, local_gate_up_blocks, local_down_blocks, dtype, max_local_tokens,
                               first_expert=rank * self.El, n_experts_total=n_experts_total)
-        self.local = QMoeBlock(self.El, hidden, ffn, 1, local_gate_up_blocks, local_down_blocks, dtype, max_recv_rows)
-        self.max_recv = max_recv_rows
+        self.local = QMoeBlock(self.El, hidden, ffn, 1, local_gate_up_blocks, local_down_blocks, dtype, S)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.send = torch.zeros(S, hidden, **f32)
+        self.recv = torch.zeros(S, hidden, **f32)
+        self.y_back = torch.zeros(S, hidden, **f32)
+        self.local_ids = torch.full((S,), -1, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(max_local_tokens, hidden, **f32)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
-        dist, h, g = self.dist, self.home, self.world
+        dist, h, g, C, Sg, H = self.dist, self.home, self.world, self.C, self.Sg, self.H
         n = x.shape[0]
         P = n * self.K
+        assert P <= C
         st = torch.cuda.current_stream().cuda_stream
         _check(_L.fuelq_moe_route(logits.data_ptr(), n, self.E, self.K, h.topk_ids.data_ptr(), h.topk_w.data_ptr(), st),
                "fuelq_moe_route")
         _check(_L.fuelq_moe_bucket(h.topk_ids.data_ptr(), P, self.E, h.sorted_ids.data_ptr(), h.offsets.data_ptr(), st),
                "fuelq_moe_bucket")
-        sorted_ids = h.sorted_ids[:P].long()
-        edges = h.offsets[0:self.E + 1:self.El].cpu().tolist()          # the one host read: rows per destination rank
-        send_counts = [edges[q + 1] - edges[q] for q in range(g)]
-        send_x = x.index_select(0, sorted_ids // self.K)
-        send_e = h.topk_ids[:n].reshape(-1).index_select(0, sorted_ids)
-        counts_in = torch.tensor(send_counts, dtype=torch.int64, device=self.device)
-        counts_out = torch.empty_like(counts_in)
-        dist.all_to_all_single(counts_out, counts_in, group=self.group)
-        recv_counts = counts_out.cpu().tolist()
-        R = sum(recv_counts)
-        assert R <= self.max_recv, "more rows routed to this rank than its buffers hold"
-        recv_x = torch.empty(R, self.H, dtype=torch.float32, device=self.device)
-        recv_e = torch.empty(R, dtype=torch.int32, device=self.device)
-        dist.all_to_all_single(recv_x, send_x, recv_counts, send_counts, group=self.group)
-        dist.all_to_all_single(recv_e, send_e, recv_counts, send_counts, group=self.group)
-        # local experts over the received rows (grouped by source rank; bucketed again by local expert)
+        _check(_L.fuelq_moe_ep_pack(x.data_ptr(), H, h.sorted_ids.data_ptr(), h.offsets.data_ptr(), h.topk_ids.data_ptr(), self.K,
+                                    P, self.El, g, C, self.send.data_ptr(), st), "fuelq_moe_ep_pack")
+        dist.all_to_all_single(self.recv, self.send, group=self.group)
+        # local experts over every slot that carries a row (bucketed by local expert; unused slots have id -1)
         loc = self.local
-        y_recv = loc.y_pairs[:R]
-        if R:
-            local_ids = recv_e - self.rank * self.El
-            _check(_L.fuelq_moe_bucket(local_ids.data_ptr(), R, self.El, loc.sorted_ids.data_ptr(), loc.offsets.data_ptr(), st),
-                   "fuelq_moe_bucket")
-            loc.experts(recv_x, R, st, divisor=1)
-        y_back = torch.empty(P, self.H, dtype=torch.float32, device=self.device)
-        dist.all_to_all_single(y_back, y_recv.contiguous(), send_counts, recv_counts, group=self.group)
-        h.y_pairs[:P].index_copy_(0, sorted_ids, y_back)               # sorted order -> pair order
-        out = torch.empty(n, self.H, dtype=torch.float32, device=self.device)
+        S = g * Sg
+        _check(_L.fuelq_moe_ep_local_ids(self.recv.data_ptr(), H, C, g, self.rank * self.El, self.local_ids.data_ptr(), st),
+               "fuelq_moe_ep_local_ids")
+        _check(_L.fuelq_moe_bucket(self.local_ids.data_ptr(), S, self.El, loc.sorted_ids.data_ptr(), loc.offsets.data_ptr(), st),
+               "fuelq_moe_bucket")
+        loc.experts(self.recv, g * C, st, divisor=1)      # rows past the bucketed count repeat old slots: in bounds, unused
+        dist.all_to_all_single(self.y_back, loc.y_pairs, group=self.group)
+        _check(_L.fuelq_moe_ep_unpack(self.y_back.data_ptr(), H, h.sorted_ids.data_ptr(), h.offsets.data_ptr(), P, self.El, g, C,
+                                      h.y_pairs.data_ptr(), st), "fuelq_moe_ep_unpack")
+        out = self.out[:n]
         _check(_L.fuelq_moe_combine(h.y_pairs.data_ptr(), h.topk_ids.data_ptr(), h.topk_w.data_ptr(), n, self.K, self.H,
                                     out.data_ptr(), st), "fuelq_moe_combine")
         return out

@@ -287,11 +287,29 @@ int32_t fuelq_moe_qmatmul(int32_t ggml_type, int32_t n_experts, int64_t n, int64
 int32_t fuelq_moe_combine(const float* y_pairs, const int32_t* topk_ids, const float* topk_weights, int64_t n_tokens,
                           int32_t top_k, int64_t n, float* out, void* stream);
 
+/* Expert parallelism inside one node, fixed sizes, nothing read on the host (fuel_b200/moe.py: QMoeExpertParallel). A
+ * (source, destination) pair of ranks owns a chunk of capacity + 1 rows of `hidden` floats in the send / receive buffers
+ * [world][capacity + 1][hidden]: the rows for that destination sorted by expert, then one row with their expert ids
+ * as int32 (-1 = unused); capacity <= hidden. fuelq_moe_ep_pack fills the send buffer from the bucketed pairs of the
+ * local tokens (expert_offsets over ALL experts, experts_per_rank consecutive experts per rank); after the
+ * all-to-all, fuelq_moe_ep_local_ids turns the received id rows into one local expert id per slot (what
+ * fuelq_moe_bucket takes; the slot index is the row index in the receive buffer); after the local experts and the
+ * all-to-all back, fuelq_moe_ep_unpack moves every result row from its slot to its pair's row of y_pairs. */
+int32_t fuelq_moe_ep_pack(const float* x, int64_t hidden, const int32_t* sorted_ids, const int32_t* expert_offsets,
+                          const int32_t* topk_ids, int32_t top_k, int64_t n_pairs, int32_t experts_per_rank, int32_t world,
+                          int64_t capacity, float* send, void* stream);
+int32_t fuelq_moe_ep_local_ids(const float* recv, int64_t hidden, int64_t capacity, int32_t world, int32_t first_expert,
+                               int32_t* local_ids, void* stream);
+int32_t fuelq_moe_ep_unpack(const float* y_back, int64_t hidden, const int32_t* sorted_ids, const int32_t* expert_offsets,
+                            int64_t n_pairs, int32_t experts_per_rank, int32_t world, int64_t capacity, float* y_pairs,
+                            void* stream);
+
 /* ---- Tensor-parallel decode step over peer-mapped memory.
- * The reference has no multi-GPU form of this path (its QMatMul runs on one device,
- * fuel-core/src/quantized/mod.rs:854-868); these entry points are how the 7B decode of the benchmark is
- * split over the GPUs of one node. Every linear layer is split along its OUTPUT rows, so no sum crosses a
- * GPU and the result has the same bits for any GPU count. The slices are exchanged inside the producing and
+ * The reference's quantized mat-vec runs on one device (fuel-core/src/quantized/mod.rs:854-868); these entry points are
+ * how the 7B decode of the benchmark is split over the GPUs of one node, in the shape of the reference's tensor-parallel
+ * layers (fuel-parallel/src/tensor_parallel.rs:283-343): column-parallel layers split by output rows, row-parallel layers
+ * by k with their partial results summed by one fixed tree (see fuelq_qmatmul_packed_tree below), so the result has the
+ * same bits for any GPU count. The slices are exchanged inside the producing and
  * consuming kernels: every 32-bit word that crosses GPUs is stored as an 8-byte pair {word, stamp} with one
  * store, straight into a destination buffer on every rank over NVLink; the consumer re-reads the pairs it
  * needs from its own buffer until all carry the expected stamp (with a deadline of a few seconds, after which

@@ -30,9 +30,11 @@ def main():
     El, nl = E // world, N // world
     pgu, pd = bgu.numel() // E, bd.numel() // E
     ep = QMoeExpertParallel(E, H, F, K, bgu[rank * El * pgu:(rank + 1) * El * pgu].contiguous(),
-                            bd[rank * El * pd:(rank + 1) * El * pd].contiguous(), rank, world, max_local_tokens=nl,
-                            max_recv_rows=N * K)
-    out_local = ep.forward(x[rank * nl:(rank + 1) * nl].contiguous(), logits[rank * nl:(rank + 1) * nl].contiguous())
+                            bd[rank * El * pd:(rank + 1) * El * pd].contiguous(), rank, world, max_local_tokens=nl)
+    xl, ll = x[rank * nl:(rank + 1) * nl].contiguous(), logits[rank * nl:(rank + 1) * nl].contiguous()
+    out_local = ep.forward(xl, ll).clone()
+    out_again = ep.forward(xl, ll)            # a second call over the same buffers: stale slots must not matter
+    assert torch.equal(out_again, out_local)
     full = torch.empty(N, H, device=dev)
     dist.all_gather_into_tensor(full, out_local)
     torch.cuda.synchronize()
