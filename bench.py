@@ -385,8 +385,8 @@ def run_prefill_sharded(args, rank, local_rank, world, own_group=True):
 
 def run_moe_expert_parallel(args, rank, local_rank, world, own_group=True):
     """benchmark configuration 5 expert-parallel: 128 experts split over the ranks, 256 tokens split over the ranks, one NCCL
-    all-to-all with equal splits each way per block, nothing read on the host (eager, stream-ordered calls). CUDA events,
-    max over ranks."""
+    all-to-all with equal splits each way per block, nothing read on the host; replayed from a CUDA graph when the capture
+    succeeds on every rank, else eager. CUDA events, max over ranks."""
     import torch
     import torch.distributed as dist
 
@@ -414,13 +414,42 @@ def run_moe_expert_parallel(args, rank, local_rank, world, own_group=True):
         b.forward(x, logits)
     torch.cuda.synchronize()
     dist.barrier()
+    # The block is a fixed sequence of stream-ordered calls, so it replays from a CUDA graph (collectives included).
+    # The graph is destroyed before anything else touches the process group: a communicator must outlive the
+    # graphs that captured its collectives.
+    graph = None
+    stream = torch.cuda.Stream(dev)
+    if not os.environ.get("FUELQ_BENCH_EP_EAGER"):
+        try:
+            with torch.cuda.stream(stream):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for b in blocks:
+                        b.forward(x, logits)
+                graph.replay()
+                stream.synchronize()
+        except Exception:
+            graph = None
+    ok = torch.tensor([1 if graph is not None else 0], device=dev)
+    torch.cuda.synchronize()
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)     # every rank replays, or none does
+    if int(ok.item()) == 0:
+        graph = None
+    captured = graph is not None
     reps = 10
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        for b in blocks:
-            b.forward(x, logits)
-    e1.record()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            if captured:
+                graph.replay()
+            else:
+                for b in blocks:
+                    b.forward(x, logits)
+        e1.record(stream)
+        stream.synchronize()
+    torch.cuda.synchronize()
+    del graph
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -432,7 +461,7 @@ def run_moe_expert_parallel(args, rank, local_rank, world, own_group=True):
                   "tokens_per_s": N / us * 1e6, "GB/s": wbytes / us / 1e3, "weight_bytes_per_gpu": wbytes // world,
                   "exchange": "one NCCL all-to-all with equal splits each way per block (fixed-capacity chunks, expert ids in the chunk's "
                               "last row); no host reads",
-                  "cuda_graph": False}
+                  "cuda_graph": captured}
         if own_group:
             print(json.dumps(result), flush=True)
     dist.barrier()

@@ -35,6 +35,23 @@ def main():
     out_local = ep.forward(xl, ll).clone()
     out_again = ep.forward(xl, ll)            # a second call over the same buffers: stale slots must not matter
     assert torch.equal(out_again, out_local)
+    # the block has no host reads and fixed sizes: captured once, replayed as a CUDA graph (collectives included). The
+    # graph is destroyed before the process group is touched again: a communicator must outlive the graphs that use it.
+    graph_equal = None
+    stream = torch.cuda.Stream(dev)
+    try:
+        with torch.cuda.stream(stream):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                out_g = ep.forward(xl, ll)
+            out_g.zero_()
+            gr.replay()
+            stream.synchronize()
+        graph_equal = bool(torch.equal(out_g, out_local))
+        del gr
+    except Exception as e:
+        graph_equal = f"not captured: {type(e).__name__}"
+    torch.cuda.synchronize()
     full = torch.empty(N, H, device=dev)
     dist.all_gather_into_tensor(full, out_local)
     torch.cuda.synchronize()
@@ -43,6 +60,7 @@ def main():
         want = QMoeBlock(E, H, F, K, bgu, bd, max_tokens=N).forward(x, logits)
         torch.cuda.synchronize()
         res["equal"] = bool(torch.equal(full, want))
+        res["graph_equal"] = graph_equal
         res["max_abs_diff"] = float((full - want).abs().max().item())
         print("EPRESULT " + json.dumps(res), flush=True)
     dist.barrier()
