@@ -315,6 +315,8 @@ int32_t decode_regs_impl(int type, int64_t m, int64_t n, int64_t k, const void* 
     if (st != kOk) return st;
   }
   const int staged_off = reserve ? (int)(pl.smem - reserve) : (int)(pl.smem - pl.stage_stride);
+  // in-kernel quantization of a small matrix: one thread block per SM (half as many blocks repeat the quantization)
+  if (x_f32 && g_opt.decode_grid == 0 && n * (int64_t)p.row_bytes <= (12 << 20) && pl.grid > di->sm_count) pl.grid = di->sm_count;
   p.w = (const uint8_t*)w;
   p.act = planes;
   p.x_f32 = x_f32;
@@ -1021,7 +1023,12 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
     st = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
     if (st != kOk) return st;
   }
-  if (m_total <= 2 && g_opt.fused_quant && g_opt.decode_kernel != 1) {
+  // One row of a small matrix (a few microseconds of streaming): the separate quantizer launch is a large share of the
+  // time, so the mat-vec's thread blocks quantize the row themselves, one block per SM (measured 5.4 against 6.0 us per
+  // call for 4096 x 4096 Q4_K in a chain of launches; larger matrices measured faster with the two-kernel form).
+  const bool small_one_row = m_total == 1 && (ggml_type == kQ4K || ggml_type == kQ6K) && g_opt.decode_grid == 0 &&
+                             n * (k / 256) * block_bytes(ggml_type) <= (12 << 20);
+  if (m_total <= 2 && (g_opt.fused_quant || small_one_row) && g_opt.decode_kernel != 1) {
     // one kernel: every thread block quantizes the activation rows itself while its weights stream in
     const ActPlanes none = {};
     st = decode_regs_impl(ggml_type, m_total, n, k, w, none, y, (cudaStream_t)stream, nullptr, x);

@@ -71,9 +71,10 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
                                     kernels, so the transfer overlaps their work (default 0) */
 #define FUELQ_OPT_FUSED_QUANT 6   /* 1: fuelq_qmatmul with m_total <= 2 and Q4_K / Q6_K weights runs as ONE kernel
                                     whose thread blocks quantize the activation rows themselves (same bytes as
-                                    fuelq_quantize_act). 0 (default): quantize kernel, then mat-vec kernel, which
-                                    measured faster in a chain of launches (the small kernel overlaps the
-                                    previous mat-vec's tail; in-kernel quantization sits on the critical path) */
+                                    fuelq_quantize_act). 0 (default): the library's choice - one kernel for one row
+                                    of a small matrix (up to 12 MiB of blocks), else quantize kernel, then mat-vec
+                                    kernel, which measured faster in a chain of launches (the small kernel overlaps
+                                    the previous mat-vec's tail). Same bits either way */
 #define FUELQ_OPT_PEER_WAIT_MS 7  /* deadline, in milliseconds, of the exchange polls in the fuelq_*_peer kernels (default
                                     4000, 1..60000): a kernel whose peer never delivers records device error 6 after
                                     this long and carries on, so the context stays usable */
