@@ -249,7 +249,7 @@ def run_side_workload(args):
         return b.reshape(-1)
 
     def matmul_case(t, name, n, k, m, copies, reps, parity_rows=0):
-        if t == T.Q5K:
+        if t == T.Q5K:       # (random block bytes: timing does not depend on the values)
             ws = [random_blocks(t, n, k) for _ in range(copies)]
         else:
             ws = [ops.quantize_weights(t, torch.randn(n, k, generator=gen, device=dev) * 0.02) for _ in range(copies)]

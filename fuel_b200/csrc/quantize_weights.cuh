@@ -153,8 +153,14 @@ __device__ __forceinline__ bool qw_total_less(float a, float b) {
   return ia < ib;
 }
 
+// kFive: Q5_K (BlockQ5K::from_float, k_quants.rs:1732-1887): the same fit with 32 levels, the fifth bit of element t of
+// sub-block s kept as bit s of qh[t].
+template <bool kFive>
 __global__ void __launch_bounds__(128) quantize_w_q4k_kernel(const float* __restrict__ x, int64_t nb,
                                                              uint8_t* __restrict__ out) {
+  constexpr int kNmax = kFive ? 31 : 15;
+  constexpr int kBlockBytes = kFive ? Q5KL::kBytes : Q4KL::kBytes;
+  constexpr int kQsOff = kFive ? Q5KL::kOffQs : Q4KL::kOffQs;
   const int64_t sub = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // global sub-block index
   const int64_t blk = sub >> 3;
   const int j = (int)(sub & 7);
@@ -173,7 +179,7 @@ __global__ void __launch_bounds__(128) quantize_w_q4k_kernel(const float* __rest
 #pragma unroll
     for (int t = 0; t < 32; ++t) v[t] = 0.f;
   }
-  // make_qkx1_quants(15, 5, x) -> (scale, -min)
+  // make_qkx1_quants(nmax, 5, x) -> (scale, -min)
   float scale = 0.f, negmin = 0.f;
   {
     float mn = v[0], mx = v[0];
@@ -184,7 +190,7 @@ __global__ void __launch_bounds__(128) quantize_w_q4k_kernel(const float* __rest
     }
     if (mx != mn) {
       if (mn > 0.f) mn = 0.f;
-      float iscale = __fdiv_rn(15.0f, __fsub_rn(mx, mn));
+      float iscale = __fdiv_rn((float)kNmax, __fsub_rn(mx, mn));
       scale = __fdiv_rn(1.0f, iscale);
       uint32_t Lp[8];  // 32 levels, 4 bits used of each byte
 #pragma unroll
@@ -196,7 +202,7 @@ __global__ void __launch_bounds__(128) quantize_w_q4k_kernel(const float* __rest
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
           const float xm = __fsub_rn(v[t], mn);
-          const int li = qw_clamp(qw_nearest_int(__fmul_rn(iscale, xm)), 0, 15);
+          const int li = qw_clamp(qw_nearest_int(__fmul_rn(iscale, xm)), 0, kNmax);
           const uint32_t old = (Lp[t >> 2] >> (8 * (t & 3))) & 0xff;
           if ((uint32_t)li != old) {
             Lp[t >> 2] = (Lp[t >> 2] & ~(0xffu << (8 * (t & 3)))) | ((uint32_t)li << (8 * (t & 3)));
@@ -249,16 +255,27 @@ __global__ void __launch_bounds__(128) quantize_w_q4k_kernel(const float* __rest
     const float dm = __fmul_rn(__half2float(hm), (float)lm);
 #pragma unroll
     for (int t = 0; t < 32; ++t) {
-      const int l = qw_clamp(qw_nearest_int(__fdiv_rn(__fadd_rn(v[t], dm), dsub)), 0, 15);
+      const int l = qw_clamp(qw_nearest_int(__fdiv_rn(__fadd_rn(v[t], dm), dsub)), 0, kNmax);
       Lq[t >> 2] |= (uint32_t)l << (8 * (t & 3));
     }
+  }
+  // fifth bits: bit t of `high` says element t of this sub-block is above 15; every thread then holds all eight masks
+  uint32_t highs[8];
+  if constexpr (kFive) {
+    uint32_t high = 0;
+#pragma unroll
+    for (int t = 0; t < 32; ++t) high |= ((Lq[t >> 2] >> (8 * (t & 3) + 4)) & 1u) << t;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) Lq[t] &= 0x0f0f0f0fu;
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2) highs[s2] = __shfl_sync(gmask, high, (lane & ~7u) + s2);
   }
   // nibble packing: byte t of group g = L[64g + t] | L[64g + 32 + t] << 4: even sub-block (low) pairs with odd (high)
   uint32_t partner[8];
 #pragma unroll
   for (int t = 0; t < 8; ++t) partner[t] = __shfl_xor_sync(gmask, Lq[t], 1);
   if (!live) return;
-  uint8_t* ob = out + blk * Q4KL::kBytes;
+  uint8_t* ob = out + blk * kBlockBytes;
   if (j == 0) {
     uint8_t sc[12];
 #pragma unroll
@@ -273,8 +290,19 @@ __global__ void __launch_bounds__(128) quantize_w_q4k_kernel(const float* __rest
     o32[2] = sc[4] | (sc[5] << 8) | (sc[6] << 16) | ((uint32_t)sc[7] << 24);
     o32[3] = sc[8] | (sc[9] << 8) | (sc[10] << 16) | ((uint32_t)sc[11] << 24);
   }
+  if constexpr (kFive) {  // thread j writes qh[4j .. 4j + 3]: bit s of qh[t] = fifth bit of element t of sub-block s
+    uint32_t word = 0;
+#pragma unroll
+    for (int tt = 0; tt < 4; ++tt) {
+      uint32_t byte = 0;
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) byte |= ((highs[s2] >> (4 * j + tt)) & 1u) << s2;
+      word |= byte << (8 * tt);
+    }
+    reinterpret_cast<uint32_t*>(ob + Q5KL::kOffQh)[j] = word;
+  }
   // each thread of a pair writes half of the pair's 32 bytes: even -> bytes 0..15, odd -> 16..31
-  uint32_t* oq = reinterpret_cast<uint32_t*>(ob + Q4KL::kOffQs + 32 * (j >> 1) + 16 * (j & 1));
+  uint32_t* oq = reinterpret_cast<uint32_t*>(ob + kQsOff + 32 * (j >> 1) + 16 * (j & 1));
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
     const int src = 4 * (j & 1) + t;  // words 0..3 or 4..7 of the 32 levels

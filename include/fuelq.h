@@ -42,7 +42,7 @@ extern "C" {
 #define FUELQ_TYPE_Q2K 10 /* Q2_K, Q3_K: mat-vec at every batch size through the exact-integer decode kernel, and dequantize */
 #define FUELQ_TYPE_Q3K 11
 #define FUELQ_TYPE_Q4K 12
-#define FUELQ_TYPE_Q5K 13 /* mat-vec (every batch size through the exact-integer decode kernels) and dequantize only */
+#define FUELQ_TYPE_Q5K 13 /* mat-vec (every batch size through the exact-integer decode kernels), dequantize, weight quantizer */
 #define FUELQ_TYPE_Q6K 14
 #define FUELQ_TYPE_Q8K 15
 #define FUELQ_TYPE_BF16 30

@@ -56,10 +56,22 @@ def test_golden_fixture_and_benchmark_shape(ops, oracle):
         assert_matmul_close(ops.qmatmul(T.Q5K, _dev(wb), n, _dev(x)).cpu().numpy(), oracle.matmul(oracle.Q5K, x, wb, n), f"m={m}")
 
 
-def test_device_weight_quantizer_is_refused(ops):
+def test_device_weight_quantizer_byte_identical(ops, oracle):
+    """BlockQ5K::from_float (k_quants.rs:1732-1887) on the device: the bytes of the CPU path's quantizer, edge cases included."""
     from fuel_b200 import GgmlDType as T, _lib
-    with pytest.raises(_lib.FuelqError) as e:
-        ops.quantize_weights(T.Q5K, torch.zeros(4, 256, device="cuda"))
+    from test_gpu_kernels import _weight_edge_cases
+    for k in (256, 1024, 4096):
+        w = _weight_edge_cases(k)
+        got = ops.quantize_weights(T.Q5K, _dev(w)).cpu().numpy()
+        want = oracle.quantize(oracle.Q5K, w)
+        diff = np.nonzero(got != want)[0]
+        assert diff.size == 0, f"k={k}: {diff.size} bytes differ, first at block {diff[0] // 176}"
+    w = _weights(512, 4096, seed=12)
+    assert np.array_equal(ops.quantize_weights(T.Q5K, _dev(w)).cpu().numpy(), oracle.quantize(oracle.Q5K, w))
+    g = np.load(GOLDEN)
+    assert np.array_equal(ops.quantize_weights(T.Q5K, _dev(g["w"])).cpu().numpy(), g["q5k_blocks"])
+    with pytest.raises(_lib.FuelqError) as e:      # formats whose quantizer is not built are refused, not approximated
+        ops.quantize_weights(T.Q3K, torch.zeros(4, 256, device="cuda"))
     assert e.value.status == _lib.NOT_SUPPORTED
 
 
