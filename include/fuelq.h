@@ -95,9 +95,9 @@ int64_t fuelq_get_option(int32_t key);
  * bounded wait expired. Synchronizes the device. 0 = no error recorded. */
 int32_t fuelq_device_error(int32_t* host_code_out, int32_t clear);
 
-/* Activation quantization to the weight format's dot-product partner: Q8_K blocks for
- * Q2K/Q3K/Q4K/Q5K/Q6K weights, Q8_1 blocks (BlockQ8_1::from_float, k_quants.rs:728-757) for Q4_1/Q5_1, Q8_0 blocks otherwise — the first half of the reference's
- * matmul (fuel-quantized/src/k_quants.rs:2303-2313, BlockQ8K::from_float :2230-2267,
+/* Activation quantization to the weight format's dot-product partner: Q8_K blocks for Q2K / Q3K / Q4K / Q5K / Q6K
+ * weights, Q8_1 blocks for Q4_1 / Q5_1, Q8_0 blocks otherwise - the first half of the reference's matmul
+ * (fuel-quantized/src/k_quants.rs:2303-2313; BlockQ8K::from_float :2230-2267, BlockQ8_1::from_float :728-757,
  * BlockQ8_0::from_float :629-658). Output bytes are identical to the reference's.
  * x: f32 [m_total, k]; q8_blocks: m_total * k / block * block_bytes bytes, 4-byte aligned. */
 int32_t fuelq_quantize_act(int32_t weight_type, int64_t m_total, int64_t k, const float* x, void* q8_blocks,
@@ -187,8 +187,9 @@ int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int6
                              const void* packed_act, float* y, void* stream);
 
 /* f32 -> GGUF blocks on the device, byte-identical to the reference's host quantizers
- * (GgmlType::from_float: Q8_0 k_quants.rs:629-658, Q4_0 :199-235, Q4_K :1470-1528 with
- * make_qkx1_quants utils.rs:229-286, Q6_K :2005-2075 with make_qx_quants utils.rs:62-191).
+ * (GgmlType::from_float: Q8_0 k_quants.rs:629-658, Q4_0 :199-235, Q4_1 :315-351, Q5_0 :424-460, Q5_1 :535-575,
+ * Q4_K :1470-1528 and Q5_K :1732-1887 with make_qkx1_quants utils.rs:229-286, Q6_K :2005-2075 with make_qx_quants
+ * utils.rs:62-191). Q2_K, Q3_K and the importance-matrix quantizers: status 3.
  * This is DynQuantizedStorage::quantize (fuel-backend-contract/src/quantized.rs:34-35); the
  * reference's CUDA backend does it on the CPU and uploads (fuel-cuda-backend/src/quantized.rs:389-412).
  * x: f32 [numel] device, 16-byte aligned; numel a multiple of the block size. */
