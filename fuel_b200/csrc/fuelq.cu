@@ -24,7 +24,7 @@ namespace {
 
 struct Options {
   int64_t pdl = 0;
-  int64_t decode_max_m = 0;   // crossover to the bf16 tensor-core path; 0 = the library's choice (see prefill_available)
+  int64_t decode_max_m = 0;   // crossover to the tensor-core GEMM; 0 = the library's choice (see prefill_available)
   int64_t decode_grid = 0;
   int64_t dbg_stage_kb = 0, dbg_max_stages = 0, dbg_smem_kb = 0;
   int64_t l2_prefetch = 0;
@@ -36,7 +36,9 @@ struct Options {
   int64_t prefill_tf32 = 0;   // tensor-core path in tf32 instead of 16-bit operands
   int64_t prefill_bf16 = 0;   // 16-bit operands as bf16 instead of f16
   int64_t fused_quant = 0;    // f32 activations with m <= 2: quantize inside the mat-vec kernel
-  int64_t dbg_mb_groups = 0, dbg_mb_min_m = 2, dbg_mb_rpc = 0, dbg_host_wb = 0, dbg_host_early = 1;  // host write-back: 0 = by launch mode, 1 = own kernel, 2 = inside the mat-vec kernel
+  int64_t dbg_mb_groups = 0, dbg_mb_min_m = 2, dbg_mb_rpc = 0;
+  int64_t dbg_host_wb = 0;     // write-back to a host buffer: 0 = by launch mode, 1 = own kernel, 2 = inside the mat-vec kernel
+  int64_t dbg_host_early = 1;  // host activations loaded before the wait for earlier kernels
 };
 Options g_opt;
 
@@ -898,8 +900,9 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
       if (value < 0 || value > 2) return kInvalidProblem;
       g_opt.decode_kernel = value;
       return kOk;
-    case 102:  // 102-107: development switches for tuning runs, not part of the contract
-      g_opt.dbg_stage_kb = value; return kOk;
+    // keys >= 100: development switches for tuning runs (stage size, ring depth, warp groups, which write-back form ...);
+    // not part of the contract, every default is what measured best
+    case 102: g_opt.dbg_stage_kb = value; return kOk;
     case 103: g_opt.dbg_max_stages = value; return kOk;
     case 104: g_opt.dbg_smem_kb = value; return kOk;
     case 105: g_opt.dbg_depth = value; return kOk;
