@@ -103,6 +103,7 @@ PROTOTYPES = {
     "fuelq_moe_ep_pack": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i64, _vp, _vp]),
     "fuelq_moe_ep_local_ids": (_i32, [_vp, _i64, _i64, _i32, _i32, _vp, _vp]),
     "fuelq_moe_ep_unpack": (_i32, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i64, _vp, _vp]),
+    "fuelq_rowpar_reduce": (_i32, [_vp, _i32, _i64, _vp, _pp, _i32, _vp]),
     "fuelq_argmax_last_peer": (_i32, [_vp, _i64, _vp, _pp, _i32, _vp, _vp]),
     "fuelq_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "fuelq_argmax_last": (_i32, [_vp, _i64, _vp, _vp]),

@@ -1677,6 +1677,21 @@ int32_t fuelq_add_rmsnorm_q8k_peer(float* x, const void* delta, int32_t n_parts,
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
+int32_t fuelq_rowpar_reduce(const void* own_parts, int32_t n_parts, int64_t n, float* y, const fuelq_peers* peers,
+                            int32_t wait_seq, void* stream) {
+  if (n <= 0 || n % 4 || n > (1 << 24)) return kInvalidProblem;
+  if (n_parts != 1 && n_parts != 2 && n_parts != 4 && n_parts != 8) return kInvalidProblem;
+  if (!own_parts || !y) return kInvalidProblem;
+  if (!aligned(own_parts, 16) || !aligned(y, 16)) return kMisaligned;
+  PeerCtx c;
+  const int32_t sc = make_peer_ctx(peers, wait_seq, -1, &c);
+  if (sc != kOk) return sc;
+  if (c.wait_seq < 0) return kInvalidProblem;
+  const cudaError_t e = launch(rowpar_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                               (const uint2*)own_parts, (int)n_parts, (int)n, y, c);
+  return e == cudaSuccess ? kOk : kLaunchFailure;
+}
+
 int32_t fuelq_argmax_last_peer(const void* x, int64_t n, int32_t* out_index, const fuelq_peers* peers, int32_t wait_seq,
                                uint32_t* epoch, void* stream) {
   if (n <= 0 || n % 2 || n > (1 << 30)) return kInvalidProblem;

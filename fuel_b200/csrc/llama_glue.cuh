@@ -463,6 +463,37 @@ __global__ void __launch_bounds__(1024) argmax_last_kernel(const float* x, int n
   argmax_last_body<false>(x, n, out, nullptr, nullptr);
 }
 
+// The reduction of a row-parallel layer by itself: y = the pairwise sum, in rank order, of n_parts partial vectors
+// (stamped pairs in this rank's buffer, filled through exchange point pc.wait_seq) - the value add_rmsnorm_q8k_peer adds
+// to the residual, for callers whose next op is not that norm. Four words per thread.
+__global__ void __launch_bounds__(256) rowpar_reduce_kernel(const uint2* parts, int n_parts, int n, float* y, const PeerCtx pc) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  const uint32_t want = peer_stamp(pc, pc.wait_seq);
+  float4 lv[3], d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    if (q < n_parts) {
+      uint32_t a[4];
+      peer_load_words<4>(parts + (size_t)q * n + i, want, a, pc.wait_ns);
+      float4 c = make_float4(__uint_as_float(a[0]), __uint_as_float(a[1]), __uint_as_float(a[2]), __uint_as_float(a[3]));
+#pragma unroll
+      for (int l = 0; l < 3; ++l) {
+        if ((q >> l) & 1) {
+          c.x = lv[l].x + c.x, c.y = lv[l].y + c.y, c.z = lv[l].z + c.z, c.w = lv[l].w + c.w;
+        } else {
+          lv[l] = c;
+          break;
+        }
+      }
+      d = c;
+    }
+  }
+  *reinterpret_cast<float4*>(y + i) = d;
+}
+
 // logits arrive as stamped pairs through exchange point pc.wait_seq; also advances this rank's step counter
 __global__ void __launch_bounds__(1024) argmax_last_peer_kernel(const float* x, int n, int* out,
                                                                 const PeerCtx pc, uint32_t* epoch) {

@@ -366,6 +366,13 @@ int32_t fuelq_qmatmul_packed_tree(int32_t ggml_type, int64_t n, int64_t k, const
 int32_t fuelq_qmatmul_packed_tree_peer(int32_t ggml_type, int64_t n, int64_t k, const void* w, const void* packed_act,
                                        void* const* dst, int64_t dst_offset, const fuelq_peers* peers, int32_t push_seq,
                                        int32_t n_leaves, const int32_t* leaf_blocks, void* stream);
+/* The all-reduce of a row-parallel layer by itself (the reference's RowParallel::forward ends in one,
+ * fuel-parallel/src/tensor_parallel.rs:321-343): y[0..n) = ((p0 + p1) + (p2 + p3)) + ... over the n_parts (1, 2, 4 or 8)
+ * partial vectors that the ranks' fuelq_qmatmul_packed_tree_peer calls stored into this rank's buffer own_parts through
+ * exchange point wait_seq (part q at word q * n). The same value fuelq_add_rmsnorm_q8k_peer adds to the residual, for a
+ * caller whose next op is something else; the same bits on every rank and at every GPU count. n a multiple of 4. */
+int32_t fuelq_rowpar_reduce(const void* own_parts, int32_t n_parts, int64_t n, float* y, const fuelq_peers* peers,
+                            int32_t wait_seq, void* stream);
 /* fuelq_argmax_last over a vector buffer of n (even) words filled through wait_seq; then *epoch += 1
  * (epoch must be peers->epoch) */
 int32_t fuelq_argmax_last_peer(const void* x, int64_t n, int32_t* out_index, const fuelq_peers* peers, int32_t wait_seq,

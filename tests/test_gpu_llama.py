@@ -203,6 +203,36 @@ def test_exchange_wait_expires_with_an_error_code_and_the_context_stays_usable()
     assert np.abs(y - r).max() <= 2e-6 * np.abs(r).max()
 
 
+@pytest.mark.parametrize("n_parts", [1, 2, 4, 8])
+def test_rowpar_reduce_sums_the_parts_pairwise_in_rank_order(n_parts):
+    """fuelq_rowpar_reduce on a buffer of stamped pairs written here by hand (what n_parts ranks' mat-vecs would have stored):
+    the result is the balanced pairwise sum ((p0 + p1) + (p2 + p3)) + ..., bit for bit, not the left-to-right one."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import ctypes
+
+    from fuel_b200 import _lib, ops
+    L = _lib.lib
+    n, seq = 1000, 5
+    parts = np.random.Generator(np.random.PCG64(n_parts)).standard_normal((n_parts, n), dtype=np.float32)
+    parts[:, 0] = [1e8, 1.0, -1e8, 1.0, 3.0, 1e-3, -3.0, 7.0][:n_parts]      # an element where the order of the sum shows
+    pairs = np.zeros((n_parts, n, 2), np.uint32)
+    pairs[:, :, 0] = parts.view(np.uint32)
+    pairs[:, :, 1] = 0 * _lib.PEER_MAX_SEQ + seq + 1                          # stamp of exchange point `seq` in step 0
+    buf = torch.from_numpy(pairs.view(np.int32)).cuda()
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    peers = _lib.Peers()
+    peers.world, peers.rank, peers.epoch = 1, 0, epoch.data_ptr()
+    y = torch.full((n,), float("nan"), device="cuda")
+    _lib.check(L.fuelq_rowpar_reduce(buf.data_ptr(), n_parts, n, y.data_ptr(), ctypes.byref(peers), seq, None), "fuelq_rowpar_reduce")
+    torch.cuda.synchronize()
+    level = [parts[q] for q in range(n_parts)]
+    while len(level) > 1:
+        level = [(level[i] + level[i + 1]).astype(np.float32) for i in range(0, len(level), 2)]
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), level[0].view(np.uint32))
+    assert ops.device_error() == 0
+
+
 @pytest.mark.parametrize("n_heads,n_kv,pos", [(4, 4, 0), (8, 2, 37), (4, 4, 300)])
 def test_rope_fused_into_attention_matches_rope_store(n_heads, n_kv, pos):
     """fuelq_attn_decode with a rope argument = fuelq_rope_store followed by fuelq_attn_decode, bit for bit,
