@@ -1167,7 +1167,7 @@ int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x,
   if (numel < 0 || numel % be) return kInvalidProblem;
   if (numel == 0) return kOk;
   if (!x || !blocks) return kInvalidProblem;
-  if (!aligned(x, 16) || !aligned(blocks, (ggml_type == kQ4K || ggml_type == kQ5K) ? 4 : 2)) return kMisaligned;
+  if (!aligned(x, 16) || !aligned(blocks, (ggml_type == kQ4K || ggml_type == kQ5K || ggml_type == kQ2K) ? 4 : 2)) return kMisaligned;
   cudaStream_t stream = (cudaStream_t)stream_v;
   const int64_t nb = numel / be;
   uint8_t* out = (uint8_t*)blocks;
@@ -1177,6 +1177,8 @@ int32_t fuelq_quantize_weights(int32_t ggml_type, int64_t numel, const float* x,
     case kQ4_1: quantize_w_legacy32_kernel<Q4_1L, false, true><<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ5_0: quantize_w_legacy32_kernel<Q5_0L, true, false><<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ5_1: quantize_w_legacy32_kernel<Q5_1L, true, true><<<(unsigned)((nb + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ2K: quantize_w_q2k_kernel<<<(unsigned)((nb * 16 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
+    case kQ3K: quantize_w_q3k_kernel<<<(unsigned)((nb * 16 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ4K: quantize_w_q4k_kernel<false><<<(unsigned)((nb * 8 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ5K: quantize_w_q4k_kernel<true><<<(unsigned)((nb * 8 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;
     case kQ6K: quantize_w_q6k_kernel<<<(unsigned)((nb * 16 + 127) / 128), 128, 0, stream>>>(x, nb, out); break;

@@ -5,6 +5,7 @@
 //   Q4_0  BlockQ4_0::from_float   k_quants.rs:199-235
 //   Q4_K  BlockQ4K::from_float    k_quants.rs:1470-1528 + make_qkx1_quants, utils.rs:229-286
 //   Q6_K  BlockQ6K::from_float    k_quants.rs:2005-2075 + make_qx_quants,   utils.rs:62-191
+//   (and Q4_1, Q5_0, Q5_1, Q5_K, Q2_K, Q3_K further down, each cited at its kernel)
 // One thread per sub-block runs the reference's sequential fit in the reference's order;
 // the few cross-sub-block steps (max scale, packing) go through warp shuffles.
 // Every float operation is an explicit round-to-nearest intrinsic so nothing contracts into
@@ -310,6 +311,265 @@ __global__ void __launch_bounds__(128) quantize_w_q4k_kernel(const float* __rest
     const uint32_t hi = (j & 1) ? Lq[src] : partner[src];
     oq[t] = lo | (hi << 4);
   }
+}
+
+// ---------------------------------------------------------------- Q2_K, Q3_K: one thread per 16-element sub-block,
+// the sixteen threads of a super-block are half a warp (BlockQ2K::from_float k_quants.rs:836-895 with
+// make_qkx1_quants(3, 5, .); BlockQ3K::from_float :1135-1216 with make_q3_quants(., 4, true), utils.rs:289-354)
+__device__ __forceinline__ void qw_load16(const float* x, int64_t sub, bool live, float (&v)[16]) {
+  if (live) {
+    const float4* src = reinterpret_cast<const float4*>(x + sub * 16);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float4 q = src[t];
+      v[4 * t] = q.x, v[4 * t + 1] = q.y, v[4 * t + 2] = q.z, v[4 * t + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 16; ++t) v[t] = 0.f;
+  }
+}
+// 16 two-bit levels (bits 2i of lv) of the four sub-blocks that share 16 bytes of qs -> those bytes, written by the
+// thread of the first of the four (bit pair 0); sub-block j = 8c + 2g + h supplies bit pair g of bytes 32c + 16h + i
+__device__ __forceinline__ void qw_store_qs2(uint32_t lv, int j, unsigned gmask, unsigned base_lane, bool live, uint8_t* qs) {
+  const int c = j >> 3, g = (j >> 1) & 3, h = j & 1;
+  const uint32_t l1 = __shfl_sync(gmask, lv, base_lane + ((j + 2) & 15));
+  const uint32_t l2 = __shfl_sync(gmask, lv, base_lane + ((j + 4) & 15));
+  const uint32_t l3 = __shfl_sync(gmask, lv, base_lane + ((j + 6) & 15));
+  if (!live || g != 0) return;
+  uint32_t* o = reinterpret_cast<uint32_t*>(qs + 32 * c + 16 * h);
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int bb = 0; bb < 4; ++bb) {
+      const int i = 4 * wd + bb;
+      const uint32_t byte = ((lv >> (2 * i)) & 3u) | (((l1 >> (2 * i)) & 3u) << 2) | (((l2 >> (2 * i)) & 3u) << 4) |
+                            (((l3 >> (2 * i)) & 3u) << 6);
+      word |= byte << (8 * bb);
+    }
+    o[wd] = word;
+  }
+}
+
+__global__ void __launch_bounds__(128) quantize_w_q2k_kernel(const float* __restrict__ x, int64_t nb, uint8_t* __restrict__ out) {
+  const int64_t sub = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t blk = sub >> 4;
+  const int j = (int)(sub & 15);
+  const bool live = blk < nb;
+  const unsigned lane = threadIdx.x & 31, base_lane = lane & ~15u;
+  const unsigned gmask = 0xffffu << base_lane;
+  float v[16];
+  qw_load16(x, sub, live, v);
+  // make_qkx1_quants(3, 5, x) -> (scale, -min)
+  float scale = 0.f, negmin = 0.f;
+  {
+    float mn = v[0], mx = v[0];
+#pragma unroll
+    for (int t = 1; t < 16; ++t) {
+      if (qw_total_less(v[t], mn)) mn = v[t];
+      if (!qw_total_less(v[t], mx)) mx = v[t];
+    }
+    if (mx != mn) {
+      if (mn > 0.f) mn = 0.f;
+      float iscale = __fdiv_rn(3.0f, __fsub_rn(mx, mn));
+      scale = __fdiv_rn(1.0f, iscale);
+      uint32_t Lp = 0;  // 16 levels, two bits each
+      for (int it = 0; it < 5; ++it) {
+        float sumlx = 0.f;
+        int suml2 = 0;
+        bool changed = false;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          const float xm = __fsub_rn(v[t], mn);
+          const int li = qw_clamp(qw_nearest_int(__fmul_rn(iscale, xm)), 0, 3);
+          if ((uint32_t)li != ((Lp >> (2 * t)) & 3u)) {
+            Lp = (Lp & ~(3u << (2 * t))) | ((uint32_t)li << (2 * t));
+            changed = true;
+          }
+          sumlx = __fadd_rn(sumlx, __fmul_rn(xm, (float)li));
+          suml2 += li * li;
+        }
+        scale = __fdiv_rn(sumlx, (float)suml2);
+        float sum = 0.f;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) sum = __fadd_rn(sum, __fsub_rn(v[t], __fmul_rn(scale, (float)((Lp >> (2 * t)) & 3u))));
+        mn = __fdiv_rn(sum, 16.0f);
+        if (mn > 0.f) mn = 0.f;
+        iscale = __fdiv_rn(1.0f, scale);
+        if (!changed) break;
+      }
+      negmin = -mn;
+    }
+  }
+  float max_scale = 0.f, max_min = 0.f;
+#pragma unroll
+  for (int s2 = 0; s2 < 16; ++s2) {
+    max_scale = fmaxf(__shfl_sync(gmask, scale, base_lane + s2), max_scale);
+    max_min = fmaxf(__shfl_sync(gmask, negmin, base_lane + s2), max_min);
+  }
+  int ls = 0, lm = 0;
+  __half hd = __float2half_rn(0.f), hm = __float2half_rn(0.f);
+  if (max_scale > 0.f) {
+    ls = qw_nearest_int(__fmul_rn(__fdiv_rn(15.0f, max_scale), scale)) & 0xff;   // 'as u8'
+    hd = __float2half_rn(__fdiv_rn(max_scale, 15.0f));
+  }
+  if (max_min > 0.f) {
+    lm = qw_nearest_int(__fmul_rn(__fdiv_rn(15.0f, max_min), negmin)) & 0xff;
+    hm = __float2half_rn(__fdiv_rn(max_min, 15.0f));
+  }
+  const uint32_t sc_byte = ((uint32_t)ls | ((uint32_t)lm << 4)) & 0xffu;  // scales[j] |= l << 4 in u8 arithmetic
+  const float dsub = __fmul_rn(__half2float(hd), (float)(sc_byte & 0xFu));
+  uint32_t lv = 0;
+  if (dsub != 0.f) {
+    const float dm = __fmul_rn(__half2float(hm), (float)(sc_byte >> 4));
+#pragma unroll
+    for (int t = 0; t < 16; ++t)
+      lv |= (uint32_t)qw_clamp(qw_nearest_int(__fdiv_rn(__fadd_rn(v[t], dm), dsub)), 0, 3) << (2 * t);
+  }
+  uint8_t* ob = out + (live ? blk : 0) * Q2KL::kBytes;
+  qw_store_qs2(lv, j, gmask, base_lane, live, ob + Q2KL::kOffQs);
+  if (!live) return;
+  ob[Q2KL::kOffScales + j] = (uint8_t)sc_byte;
+  if (j == 0)
+    *reinterpret_cast<uint32_t*>(ob + Q2KL::kOffD) = (uint32_t)__half_as_ushort(hd) | ((uint32_t)__half_as_ushort(hm) << 16);
+}
+
+// make_q3_quants(x, 4, true): levels -4 .. 3, weights x^2, up to five refinement sweeps; returns the scale
+__device__ __forceinline__ float qw_make_q3_16(const float (&x)[16]) {
+  const int nmax = 4;
+  float mx = 0.f, amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float ax = fabsf(x[i]);
+    if (ax > amax) amax = ax, mx = x[i];
+  }
+  if (amax == 0.f) return 0.f;
+  const float iscale = __fdiv_rn(-(float)nmax, mx);
+  int L[16];
+  float sumlx = 0.f, suml2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int li = qw_clamp(qw_nearest_int(__fmul_rn(iscale, x[i])), -nmax, nmax - 1);
+    L[i] = li;
+    const float w = __fmul_rn(x[i], x[i]);
+    sumlx = __fadd_rn(sumlx, __fmul_rn(__fmul_rn(w, x[i]), (float)li));
+    suml2 = __fadd_rn(suml2, __fmul_rn(w, (float)(li * li)));
+  }
+  for (int it = 0; it < 5; ++it) {
+    int changed = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float w = __fmul_rn(x[i], x[i]);
+      float slx = __fsub_rn(sumlx, __fmul_rn(__fmul_rn(w, x[i]), (float)L[i]));
+      if (slx > 0.f) {
+        float sl2 = __fsub_rn(suml2, __fmul_rn(w, (float)(L[i] * L[i])));
+        const int nl = qw_clamp(qw_nearest_int(__fdiv_rn(__fmul_rn(x[i], sl2), slx)), -nmax, nmax - 1);
+        if (nl != L[i]) {
+          slx = __fadd_rn(slx, __fmul_rn(__fmul_rn(w, x[i]), (float)nl));
+          sl2 = __fadd_rn(sl2, __fmul_rn(w, (float)(nl * nl)));
+          if (sl2 > 0.f && __fmul_rn(__fmul_rn(slx, slx), suml2) > __fmul_rn(__fmul_rn(sumlx, sumlx), sl2)) {
+            L[i] = nl;
+            sumlx = slx;
+            suml2 = sl2;
+            ++changed;
+          }
+        }
+      }
+    }
+    if (!changed) break;
+  }
+  return __fdiv_rn(sumlx, suml2);
+}
+
+__global__ void __launch_bounds__(128) quantize_w_q3k_kernel(const float* __restrict__ x, int64_t nb, uint8_t* __restrict__ out) {
+  const int64_t sub = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t blk = sub >> 4;
+  const int j = (int)(sub & 15);
+  const bool live = blk < nb;
+  const unsigned lane = threadIdx.x & 31, base_lane = lane & ~15u;
+  const unsigned gmask = 0xffffu << base_lane;
+  float v[16];
+  qw_load16(x, sub, live, v);
+  const float scale = qw_make_q3_16(v);
+  // the scale of largest magnitude, first one wins
+  float max_scale = 0.f;
+#pragma unroll
+  for (int s2 = 0; s2 < 16; ++s2) {
+    const float sc = __shfl_sync(gmask, scale, base_lane + s2);
+    if (fabsf(sc) > fabsf(max_scale)) max_scale = sc;
+  }
+  int l6 = 0;
+  __half hd = __float2half_rn(0.f);
+  if (max_scale != 0.f) {
+    const float iscale = __fdiv_rn(-32.0f, max_scale);
+    l6 = qw_clamp(qw_nearest_int(__fmul_rn(iscale, scale)), -32, 31) + 32;
+    hd = __float2half_rn(__fdiv_rn(1.0f, iscale));
+  }
+  uint32_t l6v[16];
+#pragma unroll
+  for (int s2 = 0; s2 < 16; ++s2) l6v[s2] = (uint32_t)__shfl_sync(gmask, l6, base_lane + s2);
+  const float dsub = __fmul_rn(__half2float(hd), (float)(l6 - 32));
+  uint32_t lv = 0, hb = 0;   // low two bits of every level; bit i: level of element i is above 3
+  if (dsub != 0.f) {
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const int l = qw_clamp(qw_nearest_int(__fdiv_rn(v[t], dsub)), -4, 3) + 4;
+      lv |= (uint32_t)(l & 3) << (2 * t);
+      hb |= (uint32_t)(l >> 2) << t;
+    }
+  }
+  uint32_t hbv[16];
+#pragma unroll
+  for (int s2 = 0; s2 < 16; ++s2) hbv[s2] = __shfl_sync(gmask, hb, base_lane + s2);
+  uint8_t* ob = out + (live ? blk : 0) * Q3KL::kBytes;   // 110-byte blocks: 2-byte aligned
+  {
+    // qs as in Q2_K, but through 16-bit stores
+    const int c = j >> 3, g = (j >> 1) & 3, h = j & 1;
+    const uint32_t l1 = __shfl_sync(gmask, lv, base_lane + ((j + 2) & 15));
+    const uint32_t l2 = __shfl_sync(gmask, lv, base_lane + ((j + 4) & 15));
+    const uint32_t l3 = __shfl_sync(gmask, lv, base_lane + ((j + 6) & 15));
+    if (live && g == 0) {
+      uint16_t* o = reinterpret_cast<uint16_t*>(ob + Q3KL::kOffQs + 32 * c + 16 * h);
+#pragma unroll
+      for (int hw = 0; hw < 8; ++hw) {
+        uint32_t half = 0;
+#pragma unroll
+        for (int bb = 0; bb < 2; ++bb) {
+          const int i = 2 * hw + bb;
+          const uint32_t byte = ((lv >> (2 * i)) & 3u) | (((l1 >> (2 * i)) & 3u) << 2) | (((l2 >> (2 * i)) & 3u) << 4) |
+                                (((l3 >> (2 * i)) & 3u) << 6);
+          half |= byte << (8 * bb);
+        }
+        o[hw] = (uint16_t)half;
+      }
+    }
+  }
+  if (!live) return;
+  {
+    // hmask[m] bit t = high bit of element m + 32 t = element m % 16 of sub-block 2 t + (m >= 16); thread j writes m = 2j, 2j + 1
+    uint32_t half = 0;
+#pragma unroll
+    for (int bb = 0; bb < 2; ++bb) {
+      const int m = 2 * j + bb, par = m >> 4, ii = m & 15;
+      uint32_t byte = 0;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) byte |= ((hbv[2 * t + par] >> ii) & 1u) << t;
+      half |= byte << (8 * bb);
+    }
+    reinterpret_cast<uint16_t*>(ob + Q3KL::kOffHmask)[j] = (uint16_t)half;
+  }
+  if (j < 12) {
+    uint32_t byte;
+    if (j < 8) {
+      byte = (l6v[j] & 0xFu) | ((l6v[j + 8] & 0xFu) << 4);
+    } else {
+      const int i = j - 8;
+      byte = ((l6v[i] >> 4) & 3u) | (((l6v[i + 4] >> 4) & 3u) << 2) | (((l6v[i + 8] >> 4) & 3u) << 4) | (((l6v[i + 12] >> 4) & 3u) << 6);
+    }
+    ob[Q3KL::kOffScales + j] = (uint8_t)byte;
+  }
+  if (j == 0) *reinterpret_cast<uint16_t*>(ob + Q3KL::kOffD) = __half_as_ushort(hd);
 }
 
 // ---------------------------------------------------------------- Q6_K: one thread per 16-element sub-block

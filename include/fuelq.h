@@ -39,7 +39,7 @@ extern "C" {
 #define FUELQ_TYPE_Q5_1 7
 #define FUELQ_TYPE_Q8_0 8
 #define FUELQ_TYPE_Q8_1 9 /* activation blocks only (the dot-product partner of Q4_1 / Q5_1) */
-#define FUELQ_TYPE_Q2K 10 /* Q2_K, Q3_K: mat-vec at every batch size through the exact-integer decode kernel, and dequantize */
+#define FUELQ_TYPE_Q2K 10 /* Q2_K, Q3_K: mat-vec at every batch size through the exact-integer decode kernel, dequantize, quantizer */
 #define FUELQ_TYPE_Q3K 11
 #define FUELQ_TYPE_Q4K 12
 #define FUELQ_TYPE_Q5K 13 /* mat-vec (every batch size through the exact-integer decode kernels), dequantize, weight quantizer */
@@ -189,7 +189,8 @@ int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int6
 /* f32 -> GGUF blocks on the device, byte-identical to the reference's host quantizers
  * (GgmlType::from_float: Q8_0 k_quants.rs:629-658, Q4_0 :199-235, Q4_1 :315-351, Q5_0 :424-460, Q5_1 :535-575,
  * Q4_K :1470-1528 and Q5_K :1732-1887 with make_qkx1_quants utils.rs:229-286, Q6_K :2005-2075 with make_qx_quants
- * utils.rs:62-191). Q2_K, Q3_K and the importance-matrix quantizers: status 3.
+ * utils.rs:62-191, Q2_K :836-895, Q3_K :1135-1216 with make_q3_quants utils.rs:289-354). The importance-matrix
+ * quantizers are not built.
  * This is DynQuantizedStorage::quantize (fuel-backend-contract/src/quantized.rs:34-35); the
  * reference's CUDA backend does it on the CPU and uploads (fuel-cuda-backend/src/quantized.rs:389-412).
  * x: f32 [numel] device, 16-byte aligned; numel a multiple of the block size. */

@@ -566,10 +566,136 @@ float q5k_q8k_dot_scalar(int64_t n, const BlkQ5K* xs, const BlkQ8K* ys) {
   return sumf + s;
 }
 
-// ---------------------------------------------------------------- Q2_K, Q3_K (dequantizers and dot products; the
-// reference's quantizers for these two are not restated: blocks come from files or, in the tests, from random bytes)
+// ---------------------------------------------------------------- Q2_K, Q3_K
 // Element e of a block sits in qs[32 * (e / 128) + e % 32], bits 2 * ((e % 128) / 32) .. +1; every 16 elements share
 // scale index e / 16.
+
+// fuel-quantized/src/k_quants.rs:836-895: sixteen (scale, min) fits of 16 elements (make_qkx1_quants(3, 5, .)), 4-bit
+// scales and mins against the block's largest, then the elements against the stored f16 values
+void q2k_from_float(const float* xs, int64_t k, BlkQ2K* ys) {
+  for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+    const float* x = xs + ib * QK_K;
+    BlkQ2K& blk = ys[ib];
+    float mins[16], scales[16];
+    for (int j = 0; j < 16; ++j) make_qkx1(3, 5, x + 16 * j, 16, &scales[j], &mins[j]);
+    float max_scale = 0.f, max_min = 0.f;
+    for (int j = 0; j < 16; ++j) max_scale = fmaxf(scales[j], max_scale);
+    for (int j = 0; j < 16; ++j) max_min = fmaxf(mins[j], max_min);
+    if (max_scale > 0.f) {
+      const float iscale = 15.0f / max_scale;
+      for (int j = 0; j < 16; ++j) blk.scales[j] = (uint8_t)nearest_int(iscale * scales[j]);
+      blk.d = f2h(max_scale / 15.0f);
+    } else {
+      for (int j = 0; j < 16; ++j) blk.scales[j] = 0;
+      blk.d = f2h(0.f);
+    }
+    if (max_min > 0.f) {
+      const float iscale = 15.0f / max_min;
+      for (int j = 0; j < 16; ++j) blk.scales[j] |= (uint8_t)((uint8_t)nearest_int(iscale * mins[j]) << 4);
+      blk.dmin = f2h(max_min / 15.0f);
+    } else {
+      blk.dmin = f2h(0.f);
+    }
+    uint8_t L[QK_K] = {0};
+    for (int j = 0; j < 16; ++j) {
+      const float d = h2f(blk.d) * (float)(blk.scales[j] & 0xF);
+      if (d == 0.f) continue;
+      const float dm = h2f(blk.dmin) * (float)(blk.scales[j] >> 4);
+      for (int t = 0; t < 16; ++t) L[16 * j + t] = (uint8_t)clampi(nearest_int((x[16 * j + t] + dm) / d), 0, 3);
+    }
+    for (int j = 0; j < QK_K; j += 128)
+      for (int l = 0; l < 32; ++l)
+        blk.qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+  }
+}
+
+// fuel-quantized/src/utils.rs:289-354 with do_rmse: the scale of 16 elements for levels -nmax .. nmax-1, refined by
+// moving one level at a time while the weighted fit improves (weights x^2)
+static float make_q3(const float* x, int n, int nmax) {
+  float mx = 0.f, amax = 0.f;
+  for (int i = 0; i < n; ++i) {
+    const float ax = fabsf(x[i]);
+    if (ax > amax) { amax = ax; mx = x[i]; }
+  }
+  if (amax == 0.f) return 0.f;
+  const float iscale = -(float)nmax / mx;
+  int8_t L[32];
+  float sumlx = 0.f, suml2 = 0.f;
+  for (int i = 0; i < n; ++i) {
+    const int32_t li = clampi(sat_i32(roundf(iscale * x[i])), -nmax, nmax - 1);
+    L[i] = (int8_t)li;
+    const float w = x[i] * x[i];
+    sumlx += w * x[i] * (float)li;
+    suml2 += w * (float)(li * li);
+  }
+  for (int it = 0; it < 5; ++it) {
+    int changed = 0;
+    for (int i = 0; i < n; ++i) {
+      const float w = x[i] * x[i];
+      float slx = sumlx - w * x[i] * (float)L[i];
+      if (slx > 0.f) {
+        float sl2 = suml2 - w * (float)((int32_t)L[i] * (int32_t)L[i]);
+        int32_t nl = clampi(sat_i32(roundf(x[i] * sl2 / slx)), -nmax, nmax - 1);
+        if (nl != (int32_t)L[i]) {
+          slx += w * x[i] * (float)nl;
+          sl2 += w * (float)(nl * nl);
+          if (sl2 > 0.f && slx * slx * suml2 > sumlx * sumlx * sl2) {
+            L[i] = (int8_t)nl;
+            sumlx = slx;
+            suml2 = sl2;
+            ++changed;
+          }
+        }
+      }
+    }
+    if (!changed) break;
+  }
+  return sumlx / suml2;
+}
+
+// fuel-quantized/src/k_quants.rs:1135-1216
+void q3k_from_float(const float* xs, int64_t k, BlkQ3K* ys) {
+  for (int64_t ib = 0; ib < k / QK_K; ++ib) {
+    const float* x = xs + ib * QK_K;
+    BlkQ3K& blk = ys[ib];
+    float scales[16];
+    for (int j = 0; j < 16; ++j) scales[j] = make_q3(x + 16 * j, 16, 4);
+    float max_scale = 0.f;
+    for (int j = 0; j < 16; ++j)
+      if (fabsf(scales[j]) > fabsf(max_scale)) max_scale = scales[j];
+    std::memset(blk.scales, 0, sizeof(blk.scales));
+    if (max_scale != 0.f) {
+      const float iscale = -32.0f / max_scale;
+      for (int j = 0; j < 16; ++j) {
+        int32_t l = clampi(nearest_int(iscale * scales[j]), -32, 31) + 32;
+        if (j < 8) blk.scales[j] = (uint8_t)(l & 0xF);
+        else blk.scales[j - 8] |= (uint8_t)((l & 0xF) << 4);
+        l >>= 4;
+        blk.scales[j % 4 + 8] |= (uint8_t)(l << (2 * (j / 4)));
+      }
+      blk.d = f2h(1.0f / iscale);
+    } else {
+      blk.d = f2h(0.f);
+    }
+    int8_t L[QK_K] = {0};
+    for (int j = 0; j < 16; ++j) {
+      int sc = j < 8 ? (blk.scales[j] & 0xF) : (blk.scales[j - 8] >> 4);
+      sc = (int)(int8_t)(sc | (((blk.scales[8 + j % 4] >> (2 * (j / 4))) & 3) << 4)) - 32;
+      const float d = h2f(blk.d) * (float)sc;
+      if (d != 0.f)
+        for (int t = 0; t < 16; ++t) L[16 * j + t] = (int8_t)(clampi(nearest_int(x[16 * j + t] / d), -4, 3) + 4);
+    }
+    std::memset(blk.hmask, 0, sizeof(blk.hmask));
+    for (int e = 0; e < QK_K; ++e)
+      if (L[e] > 3) {
+        blk.hmask[e % 32] |= (uint8_t)(1u << (e / 32));
+        L[e] -= 4;
+      }
+    for (int j = 0; j < QK_K; j += 128)
+      for (int l = 0; l < 32; ++l)
+        blk.qs[j / 4 + l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+  }
+}
 
 // fuel-quantized/src/k_quants.rs:958-994: y = (d * sc_lo) * q - (dmin * sc_hi), product and difference rounded separately
 void q2k_to_float(const BlkQ2K* xs, int64_t k, float* ys) {

@@ -30,6 +30,8 @@ float q5_1_q8_1_dot_scalar(int64_t, const BlkQ5_1*, const BlkQ8_1*);
 float q5_1_q8_1_dot_avx2(int64_t, const BlkQ5_1*, const BlkQ8_1*);
 void q8_1_from_float(const float*, int64_t, BlkQ8_1*);
 void q8_1_to_float(const BlkQ8_1*, int64_t, float*);
+void q2k_from_float(const float*, int64_t, BlkQ2K*);
+void q3k_from_float(const float*, int64_t, BlkQ3K*);
 void q2k_to_float(const BlkQ2K*, int64_t, float*);
 float q2k_q8k_dot_scalar(int64_t, const BlkQ2K*, const BlkQ8K*);
 float q2k_q8k_dot_avx2(int64_t, const BlkQ2K*, const BlkQ8K*);
@@ -93,6 +95,8 @@ void quantize_span(int type, const float* x, int64_t elems, void* out) {
     case GGML_Q5_1: q5_1_from_float(x, elems, (BlkQ5_1*)out); break;
     case GGML_Q8_1: q8_1_from_float(x, elems, (BlkQ8_1*)out); break;
     case GGML_Q8_0: q8_0_from_float(x, elems, (BlkQ8_0*)out); break;
+    case GGML_Q2K: q2k_from_float(x, elems, (BlkQ2K*)out); break;
+    case GGML_Q3K: q3k_from_float(x, elems, (BlkQ3K*)out); break;
     case GGML_Q4K: q4k_from_float(x, elems, (BlkQ4K*)out); break;
     case GGML_Q5K: q5k_from_float(x, elems, (BlkQ5K*)out); break;
     case GGML_Q6K: q6k_from_float(x, elems, (BlkQ6K*)out); break;
@@ -173,7 +177,6 @@ float fq_oracle_f16_to_f32(uint16_t v) { return h2f(v); }
 int fq_oracle_quantize(int type, const float* x, int64_t elems, void* out, int nthreads) {
   Fmt f;
   if (!fmt_of(type, &f) || elems % f.block_elems) return 2;
-  if (type == GGML_Q2K || type == GGML_Q3K) return 3;  // their quantizers are not restated
   const int64_t nb = elems / f.block_elems;
   const int64_t chunk = 64;
   if (nthreads <= 0) nthreads = omp_get_max_threads();

@@ -40,7 +40,7 @@ def inputs():
 def main():
     w, x = inputs()
     out = {"w": w, "x": x}
-    for name, t in (("q4_0", O.Q4_0), ("q4_1", O.Q4_1), ("q5_0", O.Q5_0), ("q5_1", O.Q5_1), ("q8_0", O.Q8_0), ("q4k", O.Q4K),
+    for name, t in (("q4_0", O.Q4_0), ("q4_1", O.Q4_1), ("q5_0", O.Q5_0), ("q5_1", O.Q5_1), ("q8_0", O.Q8_0), ("q2k", O.Q2K), ("q3k", O.Q3K), ("q4k", O.Q4K),
                     ("q5k", O.Q5K), ("q6k", O.Q6K)):
         wb = O.quantize(t, w, nthreads=1)
         out[f"{name}_blocks"] = wb

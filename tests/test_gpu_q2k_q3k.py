@@ -1,7 +1,9 @@
 """Q2_K and Q3_K (fuel-quantized/src/k_quants.rs:764-1367) through the C ABI: the dequantizer is bit-identical to the
 CPU path's, and the mat-vec (the exact-integer decode kernel at every batch size, Q8_K activation blocks) matches the
-CPU path's matmul within f32 summation order. Blocks are drawn from random bytes with finite f16 fields (the reference's
-quantizers for these two formats are not restated), so every bit pattern of quants, high bits and scales occurs."""
+CPU path's matmul within f32 summation order, on blocks drawn from random bytes with finite f16 fields (every bit pattern of
+quants, high bits and scales occurs) and on quantizer output; the device weight quantizers (BlockQ2K / BlockQ3K::from_float,
+:836-895, :1135-1216) emit the CPU path's bytes."""
+import os
 import numpy as np
 import pytest
 
@@ -9,6 +11,7 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 NAMES = ("q2k", "q3k")
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kquants_golden.npz")
 F16_FIELDS = {"q2k": (80, 82), "q3k": (108,)}
 
 
@@ -85,3 +88,24 @@ def test_benchmark_shapes(ops, oracle, name):
 def test_activation_blocks_are_q8k(ops, oracle, name):
     x = _acts(4, 1024)
     assert np.array_equal(ops.quantize_act(_T(name), _dev(x)).cpu().numpy(), oracle.quantize_act(oracle.Q4K, x))
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_weight_quantizer_byte_identical(ops, oracle, name):
+    from test_gpu_kernels import _weight_edge_cases
+    for k in (256, 1024, 4096):
+        w = _weight_edge_cases(k)
+        got = ops.quantize_weights(_T(name), _dev(w)).cpu().numpy()
+        want = oracle.quantize(_ot(oracle, name), w)
+        diff = np.nonzero(got != want)[0]
+        assert diff.size == 0, f"{name} k={k}: {diff.size} bytes differ, first at block {diff[0] // _T(name).type_size()}"
+    w = np.random.Generator(np.random.PCG64(12)).standard_normal((512, 4096), dtype=np.float32) * np.float32(0.02)
+    wb = oracle.quantize(_ot(oracle, name), w)
+    assert np.array_equal(ops.quantize_weights(_T(name), _dev(w)).cpu().numpy(), wb)
+    g = np.load(GOLDEN)
+    assert np.array_equal(ops.quantize_weights(_T(name), _dev(g["w"])).cpu().numpy(), g[f"{name}_blocks"])
+    # and the quantizer's own blocks through the mat-vec
+    from test_gpu_kernels import assert_matmul_close
+    x = _acts(3, 4096, seed=9)
+    y = ops.qmatmul(_T(name), _dev(wb), 512, _dev(x)).cpu().numpy()
+    assert_matmul_close(y, oracle.matmul(_ot(oracle, name), x, wb, 512), name)

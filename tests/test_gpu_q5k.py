@@ -70,8 +70,8 @@ def test_device_weight_quantizer_byte_identical(ops, oracle):
     assert np.array_equal(ops.quantize_weights(T.Q5K, _dev(w)).cpu().numpy(), oracle.quantize(oracle.Q5K, w))
     g = np.load(GOLDEN)
     assert np.array_equal(ops.quantize_weights(T.Q5K, _dev(g["w"])).cpu().numpy(), g["q5k_blocks"])
-    with pytest.raises(_lib.FuelqError) as e:      # formats whose quantizer is not built are refused, not approximated
-        ops.quantize_weights(T.Q3K, torch.zeros(4, 256, device="cuda"))
+    with pytest.raises(_lib.FuelqError) as e:      # an activation block format is not a weight format: refused
+        ops.quantize_weights(T.Q8_1, torch.zeros(4, 256, device="cuda"))
     assert e.value.status == _lib.NOT_SUPPORTED
 
 

@@ -198,7 +198,7 @@ def _dequant_act_blocks(O, name, act, m, k):
 
 
 @pytest.mark.parametrize("source", ("quantizer", "random_bytes"))
-@pytest.mark.parametrize("name", FORMATS + NO_QUANTIZER)
+@pytest.mark.parametrize("name", FORMATS)
 def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
     """Tight pin of the integer dot products (k_quants.rs:1388-1468 Q4_K, 1946-2003 Q6_K, 674-692 Q8_0,
     252-269 Q4_0, 1770-1925 Q5_K and their AVX2 bodies): both operands of a vec_dot are exact integers
@@ -212,8 +212,6 @@ def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
     gt = _gt(gguf, name)
     n, k, m = 48, 2048, 3
     rng = np.random.Generator(np.random.PCG64(21))
-    if source == "quantizer" and name in NO_QUANTIZER:
-        pytest.skip("no restated quantizer for this format")
     if source == "quantizer":
         wb = O.quantize(t, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
     else:
@@ -254,7 +252,7 @@ def test_vec_dot_pinned_by_independent_dequantizers(oracle, name, source):
             assert abs(v - want[i, j]) <= 2e-6 * scale
 
 
-@pytest.mark.parametrize("name", NO_QUANTIZER)
+@pytest.mark.parametrize("name", ("q2k", "q3k"))
 def test_q2k_q3k_dequantize_like_gguf_py(oracle, name):
     """Q2_K / Q3_K (k_quants.rs:958-994, 1314-1366): to_float bit-identical to gguf-py's on random block bytes, and the
     block sizes of fuel-ir/src/quantized.rs:77-103."""
@@ -269,3 +267,26 @@ def test_q2k_q3k_dequantize_like_gguf_py(oracle, name):
     ours = O.dequantize(t, blocks.reshape(-1))
     theirs = quants.dequantize(blocks.reshape(4, -1), _gt(gguf, name)).reshape(-1)
     assert np.array_equal(ours.view(np.uint32), theirs.view(np.uint32))
+
+
+@pytest.mark.parametrize("name,bound", [("q2k", 0.45), ("q3k", 0.25), ("q4k", 0.12), ("q5k", 0.06), ("q6k", 0.03)])
+def test_kquant_quantizers_round_trip(oracle, name, bound):
+    """The K-quant weight quantizers have no independent implementation to compare bytes with; what can be checked is
+    that to_float(from_float(w)) comes back within the format's resolution (rms error / rms of w, N(0, 0.02) weights),
+    that constant and all-zero blocks behave as the reference's fit says (make_qkx1_quants returns (0, 0) when max == min,
+    utils.rs:240-243: a constant block decodes to zeros in Q2_K / Q4_K / Q5_K), and that finer formats are more accurate."""
+    O = oracle
+    t = _t(O, name)
+    w = np.random.Generator(np.random.PCG64(5)).standard_normal((64, 1024), dtype=np.float32) * np.float32(0.02)
+    back = O.dequantize(t, O.quantize(t, w)).reshape(w.shape)
+    rel = float(np.sqrt(((back - w) ** 2).mean()) / w.std())
+    assert rel <= bound, rel
+    assert rel >= bound / 6          # and it is this format's resolution, not a finer one's
+    z = np.zeros((1, 256), np.float32)
+    assert not O.dequantize(t, O.quantize(t, z)).any()
+    c = np.full((1, 256), 0.25, np.float32)
+    cb = O.dequantize(t, O.quantize(t, c))
+    if name in ("q2k", "q4k", "q5k"):
+        assert not cb.any()
+    else:
+        assert np.abs(cb - 0.25).max() <= 0.02
