@@ -22,7 +22,10 @@
 namespace fuelq {
 
 // fuel-ir/src/quantized.rs:16-104
-enum class GgmlDType : int32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q8_0 = 8, Q4K = 12, Q6K = 14, Q8K = 15, BF16 = 30 };
+enum class GgmlDType : int32_t {
+  F32 = 0, F16 = 1, Q4_0 = 2, Q4_1 = 3, Q5_0 = 6, Q5_1 = 7, Q8_0 = 8, Q8_1 = 9, Q2K = 10, Q3K = 11, Q4K = 12, Q5K = 13, Q6K = 14,
+  Q8K = 15, BF16 = 30
+};
 size_t type_size(GgmlDType t);
 size_t block_size(GgmlDType t);
 

@@ -21,11 +21,13 @@ def Q():
 
 def _T(name):
     from fuel_b200 import GgmlDType as T
-    return {"q4k": T.Q4K, "q6k": T.Q6K, "q8_0": T.Q8_0, "q4_0": T.Q4_0}[name]
+    return {"q4k": T.Q4K, "q6k": T.Q6K, "q8_0": T.Q8_0, "q4_0": T.Q4_0, "q4_1": T.Q4_1, "q5_0": T.Q5_0, "q5_1": T.Q5_1, "q2k": T.Q2K,
+            "q3k": T.Q3K, "q5k": T.Q5K}[name]
 
 
 def _ot(O, name):
-    return {"q4k": O.Q4K, "q6k": O.Q6K, "q8_0": O.Q8_0, "q4_0": O.Q4_0}[name]
+    return {"q4k": O.Q4K, "q6k": O.Q6K, "q8_0": O.Q8_0, "q4_0": O.Q4_0, "q4_1": O.Q4_1, "q5_0": O.Q5_0, "q5_1": O.Q5_1, "q2k": O.Q2K,
+            "q3k": O.Q3K, "q5k": O.Q5K}[name]
 
 
 def _close(y, r):
@@ -33,7 +35,7 @@ def _close(y, r):
     assert np.abs(y - r).max() <= 2e-6 * np.abs(r).max()
 
 
-@pytest.mark.parametrize("name", ["q4k", "q6k", "q8_0", "q4_0"])
+@pytest.mark.parametrize("name", ["q4k", "q6k", "q8_0", "q4_0", "q4_1", "q5_0", "q5_1", "q2k", "q3k", "q5k"])
 def test_quantize_data_dequantize_forward(Q, oracle, name):
     n, k = 96, 1024
     w = np.random.Generator(np.random.PCG64(0)).standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
