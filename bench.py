@@ -296,6 +296,10 @@ def run_side_workload(args):
         for n, k in ((11008, 4096), (4096, 11008)):
             for m in (1, 2, 4, 8, 16):
                 print(json.dumps(matmul_case(T.Q5K, "Q5_K", n, k, m, 12, 20)), flush=True)
+    elif args.workload == "formats":     # the formats served by the generic exact-integer decode kernel
+        for t, name in ((T.Q4_0, "Q4_0"), (T.Q4_1, "Q4_1"), (T.Q5_0, "Q5_0"), (T.Q5_1, "Q5_1"), (T.Q2K, "Q2_K"), (T.Q3K, "Q3_K")):
+            for m in (1, 4, 16):
+                print(json.dumps(matmul_case(t, name, 11008, 4096, m, 12, 20)), flush=True)
     elif args.workload == "prefill":
         line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10, parity_rows=0 if args.no_cpu_baseline else 32)
         line["operands"] = "tf32" if args.tf32 else "bf16" if args.bf16 else "f16"
@@ -585,7 +589,7 @@ def main():
     ap.add_argument("--bf16", action="store_true", help="--workload prefill: 16-bit operands as bf16 instead of f16")
     ap.add_argument("--decode-grid", type=int, default=0, help="thread blocks of the decode mat-vec (0: the library's choice, two per SM)")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-architecture decode that is reported beside the metric")
-    ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe", "q5k"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "sweep", "prefill", "moe", "q5k", "formats"],
                     help="decode: the headline line (default). sweep / prefill / moe: benchmark configurations 2 / 3 / 5 on one GPU, "
                          "one JSON line per case")
     args = ap.parse_args()
