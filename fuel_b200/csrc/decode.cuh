@@ -215,15 +215,25 @@ struct Legacy32Decode {
   __device__ __forceinline__ static void unit(const uint8_t* rowp, int u, const ActPlanes& a, int k, int m0, int mc,
                                               float (&acc)[MT]) {
     const uint8_t* b = rowp + u * L::kBytes;
-    const float d = h2f_bits(lds_u16(b));
-    float mval = 0.f;
-    if constexpr (kMin) mval = h2f_bits(lds_u16(b + 2));
+    // blocks of 20 and 24 bytes keep every field 4-byte aligned (rows and stage skews are multiples of 4): whole-word loads
+    constexpr bool kWord = L::kBytes % 4 == 0;
+    auto word = [&](int off) -> uint32_t {
+      if constexpr (kWord) return *reinterpret_cast<const uint32_t*>(b + off);
+      else return lds_u32_2b(b + off);
+    };
+    float d, mval = 0.f;
+    if constexpr (kMin) {
+      const uint32_t dm = word(0);
+      d = h2f_bits(dm & 0xffffu), mval = h2f_bits(dm >> 16);
+    } else {
+      d = h2f_bits(lds_u16(b));
+    }
     uint32_t qh = 0;
-    if constexpr (kFive) qh = lds_u32_2b(b + L::kBytes - 20);  // the four bytes before the nibbles
+    if constexpr (kFive) qh = word(L::kBytes - 20);  // the four bytes before the nibbles
     int lo[4], hi[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint32_t v = lds_u32_2b(b + L::kBytes - 16 + 4 * j);
+      const uint32_t v = word(L::kBytes - 16 + 4 * j);
       uint32_t l = v & 0x0f0f0f0fu, h = (v >> 4) & 0x0f0f0f0fu;
       if constexpr (kFive) {
         // bits 4j..4j+3 of qh -> bit 4 of bytes 0..3 (elements 4j..4j+3); bits 16+4j.. for the high nibbles

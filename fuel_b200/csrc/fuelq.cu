@@ -153,6 +153,7 @@ int32_t plan_decode(int type, int64_t n, int64_t k, const DeviceInfo& di, Decode
   const size_t ring_budget = per_cta_budget - header;
   const int stage_target = 24 * 1024;
   int fit = (stage_target - 32) / row_bytes;
+  if (fit < 8 && 8 * row_bytes + 32 <= 32 * 1024) fit = 8;  // a row per consumer warp beats splitting rows along k (3 KB rows)
   int R, nseg;
   if (fit >= 8) {
     R = fit & ~7;
