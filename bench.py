@@ -241,18 +241,8 @@ def run_side_workload(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(0)
 
-    def random_blocks(t, n, k):
-        """Formats without a device quantizer: any bytes time the same; only the f16 scale fields are kept finite."""
-        b = torch.randint(0, 256, (n * k // t.block_size(), t.type_size()), generator=gen, device=dev, dtype=torch.uint8)
-        b[:, 1] &= 0x3B
-        b[:, 3] &= 0x3B
-        return b.reshape(-1)
-
     def matmul_case(t, name, n, k, m, copies, reps, parity_rows=0):
-        if t == T.Q5K:       # (random block bytes: timing does not depend on the values)
-            ws = [random_blocks(t, n, k) for _ in range(copies)]
-        else:
-            ws = [ops.quantize_weights(t, torch.randn(n, k, generator=gen, device=dev) * 0.02) for _ in range(copies)]
+        ws = [ops.quantize_weights(t, torch.randn(n, k, generator=gen, device=dev) * 0.02) for _ in range(copies)]
         x = torch.randn(m, k, generator=gen, device=dev)
         y = torch.empty(m, n, device=dev)
         wsb = L.fuelq_qmatmul_workspace_bytes(int(t), m, n, k)
@@ -271,7 +261,8 @@ def run_side_workload(args):
             # product (f64) and against the reference's CPU path (8-bit activation blocks, integer dot products)
             import numpy as np
             from oracle import oracle as O
-            ot = {T.Q4K: O.Q4K, T.Q6K: O.Q6K, T.Q8_0: O.Q8_0}[t]
+            ot = {T.Q4K: O.Q4K, T.Q6K: O.Q6K, T.Q8_0: O.Q8_0, T.Q5K: O.Q5K, T.Q4_0: O.Q4_0, T.Q4_1: O.Q4_1, T.Q5_0: O.Q5_0,
+                  T.Q5_1: O.Q5_1, T.Q2K: O.Q2K, T.Q3K: O.Q3K}[t]
             rows = np.unique(np.linspace(0, m - 1, parity_rows).astype(np.int64))
             wb = ws[-1].cpu().numpy()
             xs_ = x[torch.from_numpy(rows).to(dev)].cpu().numpy()
@@ -296,10 +287,16 @@ def run_side_workload(args):
         for n, k in ((11008, 4096), (4096, 11008)):
             for m in (1, 2, 4, 8, 16):
                 print(json.dumps(matmul_case(T.Q5K, "Q5_K", n, k, m, 12, 20)), flush=True)
-    elif args.workload == "formats":     # the formats served by the generic exact-integer decode kernel
-        for t, name in ((T.Q4_0, "Q4_0"), (T.Q4_1, "Q4_1"), (T.Q5_0, "Q5_0"), (T.Q5_1, "Q5_1"), (T.Q2K, "Q2_K"), (T.Q3K, "Q3_K")):
-            for m in (1, 4, 16):
-                print(json.dumps(matmul_case(t, name, 11008, 4096, m, 12, 20)), flush=True)
+    elif args.workload == "formats":
+        # the formats served by the generic exact-integer decode kernel up to 16 rows, and above that by the tensor-core
+        # kernel on slabs of rows dequantized into its operand type (512 rows here, with the observed error)
+        for t, name in ((T.Q4_0, "Q4_0"), (T.Q4_1, "Q4_1"), (T.Q5_0, "Q5_0"), (T.Q5_1, "Q5_1"), (T.Q2K, "Q2_K"), (T.Q3K, "Q3_K"),
+                        (T.Q5K, "Q5_K")):
+            for m in (1, 4, 16, 512):
+                if args.only and args.only not in f"{name}_k4096_n11008_m{m}":
+                    continue
+                parity = 8 if m == 512 and not args.no_cpu_baseline else 0
+                print(json.dumps(matmul_case(t, name, 11008, 4096, m, 12 if m < 512 else 4, 20, parity_rows=parity)), flush=True)
     elif args.workload == "prefill":
         line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10, parity_rows=0 if args.no_cpu_baseline else 32)
         line["operands"] = "tf32" if args.tf32 else "bf16" if args.bf16 else "f16"

@@ -39,6 +39,8 @@ struct Options {
   int64_t dbg_mb_groups = 0, dbg_mb_min_m = 2, dbg_mb_rpc = 0;
   int64_t dbg_host_wb = 0;     // write-back to a host buffer: 0 = by launch mode, 1 = own kernel, 2 = inside the mat-vec kernel
   int64_t dbg_host_early = 1;  // host activations loaded before the wait for earlier kernels
+  int64_t dbg_slab_kb = 0;     // tensor-core path through dequantized slabs: slab size in KiB (0 = 128 MiB)
+  int64_t dbg_slab_native = 0; // Q4_K / Q6_K / Q8_0 on that path: 0 = by batch size, 1 = never, 2 = always
 };
 Options g_opt;
 
@@ -745,7 +747,83 @@ int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const vo
   return kOk;
 }
 
+// ---- block -> float dequantization (dequantize.cuh)
+// out_type: kF32, kF16, kBF16, or the tensor-core path's operands: kF16Sat (f16 with finite overflow saturated) and
+// kTf32 (f32 rounded to tf32)
+constexpr int kF16Sat = -16, kTf32Out = -32;
+int32_t dequantize_impl(int ggml_type, int64_t numel, const void* blocks, void* y, int out_type, cudaStream_t stream) {
+  const int be = block_elems(ggml_type);
+  if (be == 0) return kNotSupported;
+  if (numel < 0 || numel % be) return kInvalidProblem;
+  if (out_type != kF32 && out_type != kF16 && out_type != kBF16 && out_type != kF16Sat && out_type != kTf32Out) return kNotSupported;
+  if (numel == 0) return kOk;
+  if (!blocks || !y) return kInvalidProblem;
+  const size_t in_align = (ggml_type == kQ4K || ggml_type == kQ5K) ? 16 : (ggml_type == kQ8K ? 4 : 2);
+  if (!aligned(blocks, in_align) || !aligned(y, (out_type == kF32 || out_type == kTf32Out) ? 4 : 2)) return kMisaligned;
+  const int64_t nb = numel / be;
+  const uint8_t* w = (const uint8_t*)blocks;
+  int64_t units;
+  switch (ggml_type) {
+    case kQ4K: case kQ5K: units = nb * 8; break;
+    case kQ6K: units = nb * 16; break;
+    case kQ8_0: units = nb * 4; break;
+    case kQ4_0: case kQ4_1: case kQ5_0: case kQ5_1: units = nb * 4; break;
+    case kQ8K: case kQ2K: case kQ3K: units = nb * 64; break;
+    default: return kNotSupported;
+  }
+  const dim3 block(256), grid((unsigned)((units + 255) / 256));
+#define FQ_DEQ(KERNEL)                                                                        \
+  do {                                                                                        \
+    if (out_type == kF32)                                                                     \
+      KERNEL<float><<<grid, block, 0, stream>>>(w, units, (float*)y);                         \
+    else if (out_type == kF16)                                                                \
+      KERNEL<__half><<<grid, block, 0, stream>>>(w, units, (__half*)y);                       \
+    else if (out_type == kF16Sat)                                                             \
+      KERNEL<half_sat><<<grid, block, 0, stream>>>(w, units, (half_sat*)y);                   \
+    else if (out_type == kTf32Out)                                                            \
+      KERNEL<f32_tf32><<<grid, block, 0, stream>>>(w, units, (f32_tf32*)y);                   \
+    else                                                                                      \
+      KERNEL<__nv_bfloat16><<<grid, block, 0, stream>>>(w, units, (__nv_bfloat16*)y);         \
+  } while (0)
+  switch (ggml_type) {
+    case kQ4K: FQ_DEQ(dequant_q4k_kernel); break;
+    case kQ5K: FQ_DEQ(dequant_q5k_kernel); break;
+    case kQ6K: FQ_DEQ(dequant_q6k_kernel); break;
+    case kQ8_0: FQ_DEQ(dequant_q8_0_kernel); break;
+    case kQ4_0: FQ_DEQ(dequant_q4_0_kernel); break;
+#define FQ_DEQ_L(L, FIVE, MIN)                                                                                  \
+  do {                                                                                                          \
+    if (out_type == kF32)                                                                                       \
+      dequant_legacy32_kernel<float, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (float*)y);            \
+    else if (out_type == kF16)                                                                                  \
+      dequant_legacy32_kernel<__half, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (__half*)y);          \
+    else if (out_type == kF16Sat)                                                                               \
+      dequant_legacy32_kernel<half_sat, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (half_sat*)y);      \
+    else if (out_type == kTf32Out)                                                                              \
+      dequant_legacy32_kernel<f32_tf32, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (f32_tf32*)y);      \
+    else                                                                                                        \
+      dequant_legacy32_kernel<__nv_bfloat16, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (__nv_bfloat16*)y); \
+  } while (0)
+    case kQ4_1: FQ_DEQ_L(Q4_1L, false, true); break;
+    case kQ5_0: FQ_DEQ_L(Q5_0L, true, false); break;
+    case kQ5_1: FQ_DEQ_L(Q5_1L, true, true); break;
+#undef FQ_DEQ_L
+    case kQ8K: FQ_DEQ(dequant_q8k_kernel); break;
+    case kQ2K: FQ_DEQ(dequant_q2k_kernel); break;
+    case kQ3K: FQ_DEQ(dequant_q3k_kernel); break;
+  }
+#undef FQ_DEQ
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailure;
+}
+
+
 // ---- tensor-core path (prefill.cuh)
+// Formats with a dequantizing stage of their own inside the GEMM kernel ...
+bool prefill_native_type(int type) { return type == kQ4K || type == kQ6K || type == kQ8_0; }
+// ... and those that reach it through a slab of rows dequantized into the operand type by their stand-alone kernels
+bool prefill_slab_type(int type) {
+  return type == kQ4_0 || type == kQ4_1 || type == kQ5_0 || type == kQ5_1 || type == kQ2K || type == kQ3K || type == kQ5K;
+}
 bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   (void)n;
   int64_t max_m = g_opt.decode_max_m;
@@ -753,16 +831,39 @@ bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
     // The library's choice: 16 rows; 64 where the integer tensor-core kernel applies (16 rows per pass over the weights,
     // the later passes from L2) - still faster there than the bf16 GEMM, and the reference's own arithmetic.
     max_m = 16;
-    if ((type == kQ4K || type == kQ6K || type == kQ8_0) && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0 && k % 256 == 0) max_m = 64;
+    if (prefill_native_type(type) && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0 && k % 256 == 0) max_m = 64;
   }
-  return (type == kQ4K || type == kQ6K || type == kQ8_0) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
+  return (prefill_native_type(type) || prefill_slab_type(type)) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }
-// the activations in the operand type, then (f16 operands) one unscale factor per row
-size_t prefill_workspace_bytes(int64_t m, int64_t k) {
+// Whether a tensor-core problem goes through a slab. The formats above always do. The three with in-kernel stages do
+// from the batch size at which the two-kernel form was measured faster (4096 -> 11008: Q4_K 102 against 122 us at 512
+// rows, 232 against 306 us at 2048; Q6_K 110 against 258 us at 512): the GEMM fed by tensor-map copies alone runs near
+// 900 TFLOP/s, which the dequantizing threads of the one-kernel form do not sustain.
+bool prefill_uses_slab(int type, int64_t m) {
+  if (prefill_slab_type(type)) return true;
+  if (g_opt.dbg_slab_native) return g_opt.dbg_slab_native == 2;
+  return type == kQ4K ? m > 128 : m > 64;
+}
+// Rows of the dequantized slab: the whole matrix when it fits 128 MiB, else as many 128-row tiles as do
+int64_t prefill_slab_rows(int64_t n, int64_t k) {
+  const int64_t esz = g_opt.prefill_tf32 ? 4 : 2;
+  const int64_t budget = g_opt.dbg_slab_kb ? g_opt.dbg_slab_kb << 10 : (int64_t)128 << 20;
+  int64_t rows = budget / (k * esz) / kPfTileN * kPfTileN;
+  if (rows < kPfTileN) rows = kPfTileN;
+  return rows < n ? rows : n;
+}
+// the activations in the operand type, then (f16 operands) one unscale factor per row, then the slab
+size_t prefill_x_bytes(int64_t m, int64_t k) {
   return align_up((size_t)m * k * (g_opt.prefill_tf32 ? 4 : 2), 256) + align_up((size_t)m * 4, 256);
 }
+size_t prefill_workspace_bytes(int type, int64_t m, int64_t n, int64_t k) {
+  size_t b = prefill_x_bytes(m, k);
+  if (prefill_uses_slab(type, m)) b += align_up((size_t)prefill_slab_rows(n, k) * k * (g_opt.prefill_tf32 ? 4 : 2), 256);
+  return b;
+}
 
-// tensor map of the bf16 activation matrix [M][K]: boxes of 64 columns x tile_m rows, 128-byte swizzle, zero fill
+// tensor map of a row-major [rows][K] matrix in the operand type (the activations; weights dequantized into a slab):
+// boxes of 128 bytes x tile_m rows, 128-byte swizzle, zero fill
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -798,10 +899,15 @@ cudaError_t launch_prefill_m(const PrefillParams& p, const void* xb, cudaStream_
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  CUtensorMap xmap;
+  CUtensorMap xmap, wmap;
   if (!make_x_map(xb, p.M, p.K, kTileM, kTf32, kF16, &xmap)) return cudaErrorUnknown;
+  if constexpr (Fmt::kTmaWeights) {  // weights already in the operand type: the same kind of map over their rows
+    if (!make_x_map(p.w, p.N, p.K, kPfTileN, kTf32, kF16, &wmap)) return cudaErrorUnknown;
+  } else {
+    wmap = xmap;  // not read
+  }
   const dim3 grid((unsigned)((p.N + kPfTileN - 1) / kPfTileN), (unsigned)((p.M + kTileM - 1) / kTileM));
-  kern<<<grid, kPfThreads, smem, stream>>>(p, xmap);
+  kern<<<grid, kPfThreads, smem, stream>>>(p, xmap, wmap);
   return cudaGetLastError();
 }
 
@@ -809,6 +915,44 @@ template <class Fmt, int kTileM, bool kTf32 = false, bool kF16 = false>
 cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t stream) {
   return p.n_dst > 1 ? launch_prefill_m<Fmt, kTileM, kTf32, true, kF16>(p, xb, stream)
                      : launch_prefill_m<Fmt, kTileM, kTf32, false, kF16>(p, xb, stream);
+}
+
+// type < 0: `w` is a slab of rows already in the operand type (PlainWPrefill); the activations are in the workspace
+int32_t prefill_gemm(int type, int64_t m, int64_t n, int64_t k, const void* w, float* const* y_dst, int n_dst, int64_t ldy,
+                     int64_t n_off, void* workspace, cudaStream_t stream) {
+  const bool tf32 = g_opt.prefill_tf32 != 0, f16 = !tf32 && !g_opt.prefill_bf16;
+  const void* xb = workspace;
+  const float* unscale = (const float*)((const uint8_t*)workspace + align_up((size_t)m * k * (tf32 ? 4 : 2), 256));
+  PrefillParams p;
+  p.row_unscale = f16 ? unscale : nullptr;
+  p.w = (const uint8_t*)w;
+  for (int q = 0; q < 8; ++q) p.y[q] = q < n_dst ? y_dst[q] : nullptr;
+  p.n_dst = n_dst;
+  p.ldy = (int)ldy;
+  p.n_off = (int)n_off;
+  p.M = (int)m;
+  p.N = (int)n;
+  p.K = (int)k;
+  p.row_bytes = type < 0 ? (int)(k * (tf32 ? 4 : 2)) : (int)(k / block_elems(type) * block_bytes(type));
+  cudaError_t e;
+  // the wide tile halves the weight dequantization per flop, but only pays once it still fills the SMs
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  const bool wide = m > 128 && ((n + kPfTileN - 1) / kPfTileN) * ((m + 255) / 256) >= di->sm_count;
+#define FQ_PREFILL(FMT)                                                                                                   \
+  e = tf32  ? (wide ? launch_prefill<FMT, 256, true>(p, xb, stream) : launch_prefill<FMT, 128, true>(p, xb, stream))      \
+      : f16 ? (wide ? launch_prefill<FMT, 256, false, true>(p, xb, stream)                                                \
+                    : launch_prefill<FMT, 128, false, true>(p, xb, stream))                                               \
+            : (wide ? launch_prefill<FMT, 256>(p, xb, stream) : launch_prefill<FMT, 128>(p, xb, stream))
+  switch (type) {
+    case kQ4K: FQ_PREFILL(Q4KPrefill); break;
+    case kQ6K: FQ_PREFILL(Q6KPrefill); break;
+    case kQ8_0: FQ_PREFILL(Q8_0Prefill); break;
+    case -1: FQ_PREFILL(PlainWPrefill); break;
+    default: return kNotSupported;
+  }
+#undef FQ_PREFILL
+  return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
 // y_dst / n_dst / ldy / n_off: see PrefillParams; the plain call passes one destination of width n
@@ -825,35 +969,21 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   else
     f32_to_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, (__nv_bfloat16*)xb);
   if (cudaGetLastError() != cudaSuccess) return kLaunchFailure;
-  PrefillParams p;
-  p.row_unscale = f16 ? unscale : nullptr;
-  p.w = (const uint8_t*)w;
-  for (int q = 0; q < 8; ++q) p.y[q] = q < n_dst ? y_dst[q] : nullptr;
-  p.n_dst = n_dst;
-  p.ldy = (int)ldy;
-  p.n_off = (int)n_off;
-  p.M = (int)m;
-  p.N = (int)n;
-  p.K = (int)k;
-  p.row_bytes = (int)(k / block_elems(type) * block_bytes(type));
-  cudaError_t e;
-  // the wide tile halves the weight dequantization per flop, but only pays once it still fills the SMs
-  DeviceInfo* di;
-  if (!device_info(&di)) return kLaunchFailure;
-  const bool wide = m > 128 && ((n + kPfTileN - 1) / kPfTileN) * ((m + 255) / 256) >= di->sm_count;
-#define FQ_PREFILL(FMT)                                                                                                   \
-  e = tf32  ? (wide ? launch_prefill<FMT, 256, true>(p, xb, stream) : launch_prefill<FMT, 128, true>(p, xb, stream))      \
-      : f16 ? (wide ? launch_prefill<FMT, 256, false, true>(p, xb, stream)                                                \
-                    : launch_prefill<FMT, 128, false, true>(p, xb, stream))                                               \
-            : (wide ? launch_prefill<FMT, 256>(p, xb, stream) : launch_prefill<FMT, 128>(p, xb, stream))
-  switch (type) {
-    case kQ4K: FQ_PREFILL(Q4KPrefill); break;
-    case kQ6K: FQ_PREFILL(Q6KPrefill); break;
-    case kQ8_0: FQ_PREFILL(Q8_0Prefill); break;
-    default: return kNotSupported;
+  if (!prefill_uses_slab(type, m)) return prefill_gemm(type, m, n, k, w, y_dst, n_dst, ldy, n_off, workspace, stream);
+  // Dequantize a slab of rows into the operand type (the reference's to_float values in f32, then one rounding), multiply
+  // it, take the next slab. Kernels on one stream, so the slab is reused.
+  uint8_t* slab = (uint8_t*)workspace + prefill_x_bytes(m, k);
+  const int64_t slab_rows = prefill_slab_rows(n, k);
+  const int64_t row_bytes = k / block_elems(type) * block_bytes(type);
+  const int out_type = tf32 ? kTf32Out : f16 ? kF16Sat : (int)kBF16;
+  for (int64_t r0 = 0; r0 < n; r0 += slab_rows) {
+    const int64_t rows = n - r0 < slab_rows ? n - r0 : slab_rows;
+    int32_t st = dequantize_impl(type, rows * k, (const uint8_t*)w + r0 * row_bytes, slab, out_type, stream);
+    if (st != kOk) return st;
+    st = prefill_gemm(-1, m, rows, k, slab, y_dst, n_dst, ldy, n_off + r0, workspace, stream);
+    if (st != kOk) return st;
   }
-#undef FQ_PREFILL
-  return e == cudaSuccess ? kOk : kLaunchFailure;
+  return kOk;
 }
 
 int32_t check_problem(int type, int64_t m, int64_t n, int64_t k) {
@@ -914,6 +1044,8 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 113: g_opt.dbg_mb_rpc = value; return kOk;
     case 114: g_opt.dbg_host_wb = value; return kOk;
     case 115: g_opt.dbg_host_early = value; return kOk;
+    case 116: g_opt.dbg_slab_kb = value > 0 ? value : 0; return kOk;
+    case 117: g_opt.dbg_slab_native = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;
@@ -974,7 +1106,7 @@ int32_t fuelq_quantize_act_packed(int32_t weight_type, int64_t m_total, int64_t 
 
 size_t fuelq_qmatmul_workspace_bytes(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k) {
   if (check_problem(ggml_type, m_total, n, k) != kOk) return 0;
-  if (prefill_available(ggml_type, m_total, n, k)) return prefill_workspace_bytes(m_total, k);
+  if (prefill_available(ggml_type, m_total, n, k)) return prefill_workspace_bytes(ggml_type, m_total, n, k);
   return act_packed_bytes(ggml_type, m_total, k);
 }
 
@@ -1058,7 +1190,7 @@ int32_t fuelq_qmatmul_sharded(int32_t ggml_type, int64_t m_total, int64_t n_loca
   if (!aligned(w_local, 16) || !aligned(x, 16)) return kMisaligned;
   if (!prefill_available(ggml_type, m_total, n_local, k)) return kNotSupported;  // the tensor-core path only
   if (m_total > (1 << 30)) return kNotSupported;
-  if (!workspace || workspace_bytes < prefill_workspace_bytes(m_total, k)) return kWorkspace;
+  if (!workspace || workspace_bytes < prefill_workspace_bytes(ggml_type, m_total, n_local, k)) return kWorkspace;
   if (!aligned(workspace, 16)) return kMisaligned;
   return prefill_impl(ggml_type, m_total, n_local, k, w_local, x, y_dst, n_dst, n_total, n_offset, workspace,
                       (cudaStream_t)stream);
@@ -1711,61 +1843,8 @@ int32_t fuelq_argmax_last_peer(const void* x, int64_t n, int32_t* out_index, con
 
 int32_t fuelq_dequantize(int32_t ggml_type, int64_t numel, const void* blocks, void* y, int32_t out_type,
                          void* stream_v) {
-  const int be = block_elems(ggml_type);
-  if (be == 0) return kNotSupported;
-  if (numel < 0 || numel % be) return kInvalidProblem;
   if (out_type != kF32 && out_type != kF16 && out_type != kBF16) return kNotSupported;
-  if (numel == 0) return kOk;
-  if (!blocks || !y) return kInvalidProblem;
-  const size_t in_align = (ggml_type == kQ4K || ggml_type == kQ5K) ? 16 : (ggml_type == kQ8K ? 4 : 2);
-  if (!aligned(blocks, in_align) || !aligned(y, out_type == kF32 ? 4 : 2)) return kMisaligned;
-  cudaStream_t stream = (cudaStream_t)stream_v;
-  const int64_t nb = numel / be;
-  const uint8_t* w = (const uint8_t*)blocks;
-  int64_t units;
-  switch (ggml_type) {
-    case kQ4K: case kQ5K: units = nb * 8; break;
-    case kQ6K: units = nb * 16; break;
-    case kQ8_0: units = nb * 4; break;
-    case kQ4_0: case kQ4_1: case kQ5_0: case kQ5_1: units = nb * 4; break;
-    case kQ8K: case kQ2K: case kQ3K: units = nb * 64; break;
-    default: return kNotSupported;
-  }
-  const dim3 block(256), grid((unsigned)((units + 255) / 256));
-#define FQ_DEQ(KERNEL)                                                                        \
-  do {                                                                                        \
-    if (out_type == kF32)                                                                     \
-      KERNEL<float><<<grid, block, 0, stream>>>(w, units, (float*)y);                         \
-    else if (out_type == kF16)                                                                \
-      KERNEL<__half><<<grid, block, 0, stream>>>(w, units, (__half*)y);                       \
-    else                                                                                      \
-      KERNEL<__nv_bfloat16><<<grid, block, 0, stream>>>(w, units, (__nv_bfloat16*)y);         \
-  } while (0)
-  switch (ggml_type) {
-    case kQ4K: FQ_DEQ(dequant_q4k_kernel); break;
-    case kQ5K: FQ_DEQ(dequant_q5k_kernel); break;
-    case kQ6K: FQ_DEQ(dequant_q6k_kernel); break;
-    case kQ8_0: FQ_DEQ(dequant_q8_0_kernel); break;
-    case kQ4_0: FQ_DEQ(dequant_q4_0_kernel); break;
-#define FQ_DEQ_L(L, FIVE, MIN)                                                                                  \
-  do {                                                                                                          \
-    if (out_type == kF32)                                                                                       \
-      dequant_legacy32_kernel<float, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (float*)y);            \
-    else if (out_type == kF16)                                                                                  \
-      dequant_legacy32_kernel<__half, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (__half*)y);          \
-    else                                                                                                        \
-      dequant_legacy32_kernel<__nv_bfloat16, L, FIVE, MIN><<<grid, block, 0, stream>>>(w, units, (__nv_bfloat16*)y); \
-  } while (0)
-    case kQ4_1: FQ_DEQ_L(Q4_1L, false, true); break;
-    case kQ5_0: FQ_DEQ_L(Q5_0L, true, false); break;
-    case kQ5_1: FQ_DEQ_L(Q5_1L, true, true); break;
-#undef FQ_DEQ_L
-    case kQ8K: FQ_DEQ(dequant_q8k_kernel); break;
-    case kQ2K: FQ_DEQ(dequant_q2k_kernel); break;
-    case kQ3K: FQ_DEQ(dequant_q3k_kernel); break;
-  }
-#undef FQ_DEQ
-  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailure;
+  return dequantize_impl(ggml_type, numel, blocks, y, out_type, (cudaStream_t)stream_v);
 }
 
 }  // extern "C"

@@ -89,7 +89,13 @@ def test_argument_validation_needs_no_device(L):
     finally:
         f.fuelq_set_option(L.OPT_PREFILL_BF16, 0)
         f.fuelq_set_option(L.OPT_PREFILL_TF32, 0)
-    assert f.fuelq_qmatmul_numerics(2, 2048, 4096, 4096) == L.NUMERICS_INTEGER   # Q4_0 has no tensor-core form
+    # Q4_0 and the other formats dequantized by slabs: tensor cores above 16 rows; the workspace then also holds one slab
+    assert f.fuelq_qmatmul_numerics(2, 16, 4096, 4096) == L.NUMERICS_INTEGER
+    assert f.fuelq_qmatmul_numerics(2, 17, 4096, 4096) == L.NUMERICS_F16
+    assert f.fuelq_qmatmul_numerics(13, 2048, 4096, 4096) == L.NUMERICS_F16
+    assert f.fuelq_qmatmul_workspace_bytes(13, 2048, 4096, 4096) == 2048 * 4096 * 2 + 2048 * 4 + 4096 * 4096 * 2
+    assert f.fuelq_qmatmul_workspace_bytes(13, 32, 1 << 20, 4096) == 32 * 4096 * 2 + 256 + (128 << 20)   # slab capped at 128 MiB
+    assert f.fuelq_qmatmul_numerics(2, 2048, 4096, 4096 + 32) == L.NUMERICS_INTEGER   # k not a multiple of 64: integer path
     assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 100) == -L.INVALID_PROBLEM
 
 
