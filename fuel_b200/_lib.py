@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libfuelq.so")
 
 OK, MISALIGNED, INVALID_PROBLEM, NOT_SUPPORTED, WORKSPACE, LAUNCH_FAILURE = range(6)
 NUMERICS_INTEGER, NUMERICS_BF16, NUMERICS_TF32, NUMERICS_F16 = range(4)
-OPT_PDL, OPT_DECODE_MAX_M, OPT_DECODE_GRID, OPT_DECODE_KERNEL, OPT_L2_PREFETCH, OPT_FUSED_QUANT, OPT_PEER_WAIT_MS, OPT_PREFILL_TF32, OPT_PREFILL_BF16 = 1, 2, 3, 4, 5, 6, 7, 8, 9
+OPT_PDL, OPT_DECODE_MAX_M, OPT_DECODE_GRID, OPT_DECODE_KERNEL, OPT_L2_PREFETCH, OPT_FUSED_QUANT, OPT_PEER_WAIT_MS, OPT_PREFILL_TF32, OPT_PREFILL_BF16, OPT_PREFILL_ONE_KERNEL = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10
 
 _i32, _i64, _vp, _sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
 

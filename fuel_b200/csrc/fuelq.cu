@@ -14,6 +14,7 @@
 #include "mma_batch.cuh"
 #include "moe.cuh"
 #include "moe_mma.cuh"
+#include "plain_gemm.cuh"
 #include "prefill.cuh"
 #include "quantize_act.cuh"
 #include "quantize_weights.cuh"
@@ -40,7 +41,8 @@ struct Options {
   int64_t dbg_host_wb = 0;     // write-back to a host buffer: 0 = by launch mode, 1 = own kernel, 2 = inside the mat-vec kernel
   int64_t dbg_host_early = 1;  // host activations loaded before the wait for earlier kernels
   int64_t dbg_slab_kb = 0;     // tensor-core path through dequantized slabs: slab size in KiB (0 = 128 MiB)
-  int64_t dbg_slab_native = 0; // Q4_K / Q6_K / Q8_0 on that path: 0 = by batch size, 1 = never, 2 = always
+  int64_t prefill_one_kernel = 0;  // Q4_K / Q6_K / Q8_0 dequantized inside the GEMM kernel instead of by slabs
+  int64_t dbg_no_split = 0, dbg_old_plain = 0;
 };
 Options g_opt;
 
@@ -835,14 +837,13 @@ bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
   }
   return (prefill_native_type(type) || prefill_slab_type(type)) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }
-// Whether a tensor-core problem goes through a slab. The formats above always do. The three with in-kernel stages do
-// from the batch size at which the two-kernel form was measured faster (4096 -> 11008: Q4_K 102 against 122 us at 512
-// rows, 232 against 306 us at 2048; Q6_K 110 against 258 us at 512): the GEMM fed by tensor-map copies alone runs near
-// 900 TFLOP/s, which the dequantizing threads of the one-kernel form do not sustain.
+// Whether a tensor-core problem goes through a slab: always, unless the caller asked for the one-kernel form of the
+// three formats that have in-kernel stages. Measured on 4096 -> 11008, slab against one kernel: Q4_K 59 / 61 us at 128
+// rows, 102 / 122 at 512, 232 / 306 at 2048; Q6_K 60 / 124 at 128, 110 / 258 at 512 - the GEMM fed by tensor-map copies
+// alone runs near 900 TFLOP/s, which the dequantizing threads of the one-kernel form do not sustain.
 bool prefill_uses_slab(int type, int64_t m) {
-  if (prefill_slab_type(type)) return true;
-  if (g_opt.dbg_slab_native) return g_opt.dbg_slab_native == 2;
-  return type == kQ4K ? m > 128 : m > 64;
+  (void)m;
+  return prefill_slab_type(type) || !g_opt.prefill_one_kernel;
 }
 // Rows of the dequantized slab: the whole matrix when it fits 128 MiB, else as many 128-row tiles as do
 int64_t prefill_slab_rows(int64_t n, int64_t k) {
@@ -917,12 +918,74 @@ cudaError_t launch_prefill(const PrefillParams& p, const void* xb, cudaStream_t 
                      : launch_prefill_m<Fmt, kTileM, kTf32, false, kF16>(p, xb, stream);
 }
 
+template <int kTileM, int kStages, bool kTf32, bool kF16, bool kMulti>
+cudaError_t launch_plain_gemm_t(PlainGemmParams p, const void* xb, const void* w, int sm_count, cudaStream_t stream) {
+  constexpr size_t smem = 1024 + (size_t)kStages * (kPfTileN * 128 + kTileM * 128) + kPgEpilogueWarps * 32 * 36 * 4 +
+                          sizeof(PlainGemmSmem<kTileM, kStages>) + 64;
+  static bool attr_set[64] = {};
+  auto kern = plain_gemm_kernel<kTileM, kStages, kTf32, kF16, kMulti>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  CUtensorMap xmap, wmap;
+  if (!make_x_map(xb, p.M, p.K, kTileM, kTf32, kF16, &xmap)) return cudaErrorUnknown;
+  if (!make_x_map(w, p.N, p.K, kPfTileN, kTf32, kF16, &wmap)) return cudaErrorUnknown;
+  // Work items: whole tiles for the full rounds of thread blocks; the tiles of a last, partly filled round are cut along M
+  // into 2 or 4 pieces (at least 64 activation rows each) while the pieces still fit one round.
+  const int tiles_n = (p.N + kPfTileN - 1) / kPfTileN;
+  p.tiles_m = (p.M + kTileM - 1) / kTileM;
+  const int64_t tiles = (int64_t)tiles_n * p.tiles_m;
+  const int64_t rounds = tiles / sm_count, rest = tiles % sm_count;
+  int split = 0;
+  constexpr int kMaxSplit = kTileM == 256 ? 2 : 1;
+  if (rest && !g_opt.dbg_no_split)
+    while (split < kMaxSplit && (rest << (split + 1)) <= sm_count) ++split;
+  const int64_t whole = split ? rounds * sm_count : tiles;
+  const int64_t items = whole + ((tiles - whole) << split);
+  if (items > INT32_MAX) return cudaErrorInvalidValue;
+  p.whole_tiles = (int)whole;
+  p.split_log2 = split;
+  p.n_items = (int)items;
+  const unsigned grid = (unsigned)(items < sm_count ? items : sm_count);
+  kern<<<grid, kPgThreads, smem, stream>>>(p, xmap, wmap);
+  return cudaGetLastError();
+}
+
 // type < 0: `w` is a slab of rows already in the operand type (PlainWPrefill); the activations are in the workspace
 int32_t prefill_gemm(int type, int64_t m, int64_t n, int64_t k, const void* w, float* const* y_dst, int n_dst, int64_t ldy,
                      int64_t n_off, void* workspace, cudaStream_t stream) {
   const bool tf32 = g_opt.prefill_tf32 != 0, f16 = !tf32 && !g_opt.prefill_bf16;
   const void* xb = workspace;
   const float* unscale = (const float*)((const uint8_t*)workspace + align_up((size_t)m * k * (tf32 ? 4 : 2), 256));
+  DeviceInfo* di;
+  if (!device_info(&di)) return kLaunchFailure;
+  if (type < 0 && !g_opt.dbg_old_plain) {
+    PlainGemmParams g;
+    for (int q = 0; q < 8; ++q) g.y[q] = q < n_dst ? y_dst[q] : nullptr;
+    g.n_dst = n_dst, g.ldy = (int)ldy, g.n_off = (int)n_off;
+    g.M = (int)m, g.N = (int)n, g.K = (int)k;
+    g.row_unscale = f16 ? unscale : nullptr;
+    cudaError_t e;
+    const bool multi = n_dst > 1, narrow = m <= 128;
+#define FQ_PLAIN(TF32, F16)                                                                                             \
+  e = narrow ? (multi ? launch_plain_gemm_t<128, 6, TF32, F16, true>(g, xb, w, di->sm_count, stream)                    \
+                      : launch_plain_gemm_t<128, 6, TF32, F16, false>(g, xb, w, di->sm_count, stream))                  \
+             : (multi ? launch_plain_gemm_t<256, 4, TF32, F16, true>(g, xb, w, di->sm_count, stream)                    \
+                      : launch_plain_gemm_t<256, 4, TF32, F16, false>(g, xb, w, di->sm_count, stream))
+    if (tf32)
+      FQ_PLAIN(true, false);
+    else if (f16)
+      FQ_PLAIN(false, true);
+    else
+      FQ_PLAIN(false, false);
+#undef FQ_PLAIN
+    return e == cudaSuccess ? kOk : kLaunchFailure;
+  }
   PrefillParams p;
   p.row_unscale = f16 ? unscale : nullptr;
   p.w = (const uint8_t*)w;
@@ -936,8 +999,6 @@ int32_t prefill_gemm(int type, int64_t m, int64_t n, int64_t k, const void* w, f
   p.row_bytes = type < 0 ? (int)(k * (tf32 ? 4 : 2)) : (int)(k / block_elems(type) * block_bytes(type));
   cudaError_t e;
   // the wide tile halves the weight dequantization per flop, but only pays once it still fills the SMs
-  DeviceInfo* di;
-  if (!device_info(&di)) return kLaunchFailure;
   const bool wide = m > 128 && ((n + kPfTileN - 1) / kPfTileN) * ((m + 255) / 256) >= di->sm_count;
 #define FQ_PREFILL(FMT)                                                                                                   \
   e = tf32  ? (wide ? launch_prefill<FMT, 256, true>(p, xb, stream) : launch_prefill<FMT, 128, true>(p, xb, stream))      \
@@ -1045,11 +1106,13 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 114: g_opt.dbg_host_wb = value; return kOk;
     case 115: g_opt.dbg_host_early = value; return kOk;
     case 116: g_opt.dbg_slab_kb = value > 0 ? value : 0; return kOk;
-    case 117: g_opt.dbg_slab_native = value; return kOk;
+    case 117: g_opt.dbg_no_split = value; return kOk;
+    case 118: g_opt.dbg_old_plain = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_BF16: g_opt.prefill_bf16 = value ? 1 : 0; return kOk;
+    case FUELQ_OPT_PREFILL_ONE_KERNEL: g_opt.prefill_one_kernel = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PEER_WAIT_MS:
       if (value < 1 || value > 60000) return kInvalidProblem;
       g_opt.peer_wait_ms = value;
@@ -1069,6 +1132,7 @@ int64_t fuelq_get_option(int32_t key) {
     case FUELQ_OPT_PEER_WAIT_MS: return g_opt.peer_wait_ms;
     case FUELQ_OPT_PREFILL_TF32: return g_opt.prefill_tf32;
     case FUELQ_OPT_PREFILL_BF16: return g_opt.prefill_bf16;
+    case FUELQ_OPT_PREFILL_ONE_KERNEL: return g_opt.prefill_one_kernel;
     default: return -1;
   }
 }

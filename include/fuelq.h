@@ -58,11 +58,11 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
 /* Options. key: */
 #define FUELQ_OPT_PDL 1          /* 1: launch kernels with programmatic dependent launch so a kernel's weight
                                     prefetch overlaps its predecessor's tail (default 0) */
-#define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the integer kernels; above it the bf16 tensor-core GEMM
-                                    runs for formats that have one. 0 (default) = the library's choice: 16, and 64 for
-                                    Q4_K / Q6_K / Q8_0 with k a multiple of 256 (the integer tensor-core kernel, 16 rows
-                                    per pass over the weights, is still the faster of the two there). Any positive
-                                    value is taken as given */
+#define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the integer kernels; above it the tensor-core GEMM runs
+                                    (every block format, k a multiple of 64). 0 (default) = the library's choice: 16,
+                                    and 64 for Q4_K / Q6_K / Q8_0 with k a multiple of 256 (the integer tensor-core
+                                    kernel, 16 rows per pass over the weights, is still the faster of the two there).
+                                    Any positive value is taken as given */
 #define FUELQ_OPT_DECODE_GRID 3  /* CTAs for the decode kernel; 0 = two per SM (default) */
 #define FUELQ_OPT_DECODE_KERNEL 4 /* 0 = pick per problem (default); 1 = generic decode kernel (activations read
                                     through L1, any M <= 16); 2 = register-resident kernel only (M <= 2) */
@@ -88,6 +88,15 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
                                     about 4e-4, same MMA rate): weights dequantized straight to f16 (finite values
                                     saturate at +-65504, far beyond any GGUF weight), every activation row scaled
                                     by a power of two into f16's range and the result row scaled back, both exact */
+#define FUELQ_OPT_PREFILL_ONE_KERNEL 10 /* The tensor-core path takes the weights as a slab of rows dequantized into the
+                                    operand type by the stand-alone dequantizing kernels (the slab, at most 128 MiB,
+                                    is part of the workspace fuelq_qmatmul_workspace_bytes reports) and multiplies
+                                    slab by slab; both operands then reach the tensor cores by tensor-map copies.
+                                    1: Q4_K / Q6_K / Q8_0 are instead dequantized inside the GEMM kernel - no slab
+                                    in the workspace, measured slower above ~100 rows (Q4_K 4096 -> 14336 at 2048
+                                    rows: 575 against 746 TFLOP/s). Same operand values either way for Q6_K and
+                                    Q8_0; Q4_K's in-kernel form fuses d*sc*q - dmin*m into one rounding where the
+                                    slab form has the reference's two (default 0) */
 int32_t fuelq_set_option(int32_t key, int64_t value);
 int64_t fuelq_get_option(int32_t key);
 

@@ -13,6 +13,7 @@ pub const FUELQ_OPT_PDL: i32 = 1;
 pub const FUELQ_OPT_DECODE_MAX_M: i32 = 2;
 pub const FUELQ_OPT_PREFILL_TF32: i32 = 8;
 pub const FUELQ_OPT_PREFILL_BF16: i32 = 9;
+pub const FUELQ_OPT_PREFILL_ONE_KERNEL: i32 = 10;
 pub const FUELQ_NUMERICS_INTEGER: i32 = 0;
 pub const FUELQ_NUMERICS_BF16: i32 = 1;
 pub const FUELQ_NUMERICS_TF32: i32 = 2;

@@ -89,7 +89,15 @@ def test_argument_validation_needs_no_device(L):
     finally:
         f.fuelq_set_option(L.OPT_PREFILL_BF16, 0)
         f.fuelq_set_option(L.OPT_PREFILL_TF32, 0)
-    # Q4_0 and the other formats dequantized by slabs: tensor cores above 16 rows; the workspace then also holds one slab
+    # the tensor-core path's workspace: activations in the operand type, one factor per row, and a slab of dequantized rows
+    assert f.fuelq_qmatmul_workspace_bytes(Q4K, 2048, 4096, 4096) == 2048 * 4096 * 2 + 2048 * 4 + 4096 * 4096 * 2
+    try:   # ... unless Q4_K / Q6_K / Q8_0 are asked to dequantize inside the GEMM kernel
+        assert f.fuelq_set_option(L.OPT_PREFILL_ONE_KERNEL, 1) == L.OK and f.fuelq_get_option(L.OPT_PREFILL_ONE_KERNEL) == 1
+        assert f.fuelq_qmatmul_workspace_bytes(Q4K, 2048, 4096, 4096) == 2048 * 4096 * 2 + 2048 * 4
+        assert f.fuelq_qmatmul_workspace_bytes(13, 2048, 4096, 4096) == 2048 * 4096 * 2 + 2048 * 4 + 4096 * 4096 * 2
+    finally:
+        f.fuelq_set_option(L.OPT_PREFILL_ONE_KERNEL, 0)
+    # Q4_0 and the other formats without in-kernel stages: tensor cores above 16 rows; the workspace then also holds one slab
     assert f.fuelq_qmatmul_numerics(2, 16, 4096, 4096) == L.NUMERICS_INTEGER
     assert f.fuelq_qmatmul_numerics(2, 17, 4096, 4096) == L.NUMERICS_F16
     assert f.fuelq_qmatmul_numerics(13, 2048, 4096, 4096) == L.NUMERICS_F16

@@ -72,6 +72,32 @@ def test_prefill_other_formats_match_float_oracle(ops, oracle, name, m, n, k):
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 6e-4
 
 
+@pytest.mark.parametrize("name", ["q4k", "q6k", "q8_0"])
+@pytest.mark.parametrize("m,n,k", [(200, 300, 1024), (257, 129, 768), (512, 1024, 4096)])
+def test_prefill_one_kernel_option(ops, oracle, name, m, n, k):
+    """FUELQ_OPT_PREFILL_ONE_KERNEL: the weights are dequantized inside the GEMM kernel instead of through a slab in the
+    workspace. Same bars; for Q6_K and Q8_0 the operand values are the same, so the results are bit-identical."""
+    from fuel_b200 import GgmlDType as T, _lib
+    t, ot = {"q4k": (T.Q4K, oracle.Q4K), "q6k": (T.Q6K, oracle.Q6K), "q8_0": (T.Q8_0, oracle.Q8_0)}[name]
+    wb = torch.from_numpy(oracle.quantize(ot, _w(n, k, seed=n))).cuda()
+    x = _x(m, k, seed=m)
+    xd = torch.from_numpy(x).cuda()
+    want = oracle.matmul_dequant_f64(ot, x, wb.cpu().numpy(), n)
+    slab = ops.qmatmul(t, wb, n, xd)
+    ws_slab = _lib.lib.fuelq_qmatmul_workspace_bytes(int(t), m, n, k)
+    try:
+        _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_PREFILL_ONE_KERNEL, 1), "set_option")
+        assert _lib.lib.fuelq_qmatmul_workspace_bytes(int(t), m, n, k) < ws_slab
+        one = ops.qmatmul(t, wb, n, xd)
+    finally:
+        _lib.lib.fuelq_set_option(_lib.OPT_PREFILL_ONE_KERNEL, 0)
+    for got in (slab.cpu().numpy(), one.cpu().numpy()):
+        assert np.abs(got - want).max() / np.abs(want).max() <= 1e-3
+        assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 6e-4
+    if name != "q4k":
+        assert torch.equal(slab, one)
+
+
 def test_prefill_config3_shape_sampled_rows(ops, oracle):
     """benchmark configuration 3: W Q4_K [14336 x 4096], X [2048 x 4096]; the oracle is evaluated on sampled rows."""
     from fuel_b200 import GgmlDType as T
