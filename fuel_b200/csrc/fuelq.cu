@@ -42,7 +42,7 @@ struct Options {
   int64_t dbg_host_early = 1;  // host activations loaded before the wait for earlier kernels
   int64_t dbg_slab_kb = 0;     // tensor-core path through dequantized slabs: slab size in KiB (0 = 128 MiB)
   int64_t prefill_one_kernel = 0;  // Q4_K / Q6_K / Q8_0 dequantized inside the GEMM kernel instead of by slabs
-  int64_t dbg_no_split = 0, dbg_old_plain = 0;
+  int64_t dbg_no_split = 0;    // the slab GEMM's last partial round of tiles is not cut into pieces
 };
 Options g_opt;
 
@@ -900,15 +900,10 @@ cudaError_t launch_prefill_m(const PrefillParams& p, const void* xb, cudaStream_
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  CUtensorMap xmap, wmap;
+  CUtensorMap xmap;
   if (!make_x_map(xb, p.M, p.K, kTileM, kTf32, kF16, &xmap)) return cudaErrorUnknown;
-  if constexpr (Fmt::kTmaWeights) {  // weights already in the operand type: the same kind of map over their rows
-    if (!make_x_map(p.w, p.N, p.K, kPfTileN, kTf32, kF16, &wmap)) return cudaErrorUnknown;
-  } else {
-    wmap = xmap;  // not read
-  }
   const dim3 grid((unsigned)((p.N + kPfTileN - 1) / kPfTileN), (unsigned)((p.M + kTileM - 1) / kTileM));
-  kern<<<grid, kPfThreads, smem, stream>>>(p, xmap, wmap);
+  kern<<<grid, kPfThreads, smem, stream>>>(p, xmap);
   return cudaGetLastError();
 }
 
@@ -956,7 +951,8 @@ cudaError_t launch_plain_gemm_t(PlainGemmParams p, const void* xb, const void* w
   return cudaGetLastError();
 }
 
-// type < 0: `w` is a slab of rows already in the operand type (PlainWPrefill); the activations are in the workspace
+// type < 0: `w` is a slab of rows already in the operand type (plain_gemm.cuh); else GGUF blocks dequantized inside the
+// kernel (prefill.cuh). The activations are in the workspace
 int32_t prefill_gemm(int type, int64_t m, int64_t n, int64_t k, const void* w, float* const* y_dst, int n_dst, int64_t ldy,
                      int64_t n_off, void* workspace, cudaStream_t stream) {
   const bool tf32 = g_opt.prefill_tf32 != 0, f16 = !tf32 && !g_opt.prefill_bf16;
@@ -964,7 +960,7 @@ int32_t prefill_gemm(int type, int64_t m, int64_t n, int64_t k, const void* w, f
   const float* unscale = (const float*)((const uint8_t*)workspace + align_up((size_t)m * k * (tf32 ? 4 : 2), 256));
   DeviceInfo* di;
   if (!device_info(&di)) return kLaunchFailure;
-  if (type < 0 && !g_opt.dbg_old_plain) {
+  if (type < 0) {
     PlainGemmParams g;
     for (int q = 0; q < 8; ++q) g.y[q] = q < n_dst ? y_dst[q] : nullptr;
     g.n_dst = n_dst, g.ldy = (int)ldy, g.n_off = (int)n_off;
@@ -1009,7 +1005,6 @@ int32_t prefill_gemm(int type, int64_t m, int64_t n, int64_t k, const void* w, f
     case kQ4K: FQ_PREFILL(Q4KPrefill); break;
     case kQ6K: FQ_PREFILL(Q6KPrefill); break;
     case kQ8_0: FQ_PREFILL(Q8_0Prefill); break;
-    case -1: FQ_PREFILL(PlainWPrefill); break;
     default: return kNotSupported;
   }
 #undef FQ_PREFILL
@@ -1107,7 +1102,6 @@ int32_t fuelq_set_option(int32_t key, int64_t value) {
     case 115: g_opt.dbg_host_early = value; return kOk;
     case 116: g_opt.dbg_slab_kb = value > 0 ? value : 0; return kOk;
     case 117: g_opt.dbg_no_split = value; return kOk;
-    case 118: g_opt.dbg_old_plain = value; return kOk;
     case FUELQ_OPT_L2_PREFETCH: g_opt.l2_prefetch = value ? 1 : 0; return kOk;
     case FUELQ_OPT_FUSED_QUANT: g_opt.fused_quant = value ? 1 : 0; return kOk;
     case FUELQ_OPT_PREFILL_TF32: g_opt.prefill_tf32 = value ? 1 : 0; return kOk;

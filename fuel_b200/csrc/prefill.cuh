@@ -1,3 +1,6 @@
+// One-kernel form of the tensor-core path (FUELQ_OPT_PREFILL_ONE_KERNEL: no dequantized slab in the workspace; the
+// default form, faster from about 100 rows up, is plain_gemm.cuh, which also uses the PTX wrappers, descriptors and
+// activation pre-passes of this file).
 // Prefill path (large M): Y[M, N] = X[M, K] . W[N, K]^T as a dense bf16 contraction on the
 // 5th-generation tensor cores. The reference has no tensor-core quantized path: its CUDA forward
 // runs the mat-vec kernel for every M (fuel-cuda-backend/src/quantized.rs:452-473,543-587) and its
@@ -145,7 +148,6 @@ __device__ __forceinline__ uint32_t pack_op(float a, float b) {
 __device__ __forceinline__ float small_int_f32(uint32_t q_at_bit16) { return __uint_as_float(0x43000000u | q_at_bit16); }
 
 struct Q4KPrefill {
-  static constexpr bool kTmaWeights = false;
   static constexpr int kType = kQ4K;
   static constexpr bool kSplitLoad = true;
   // the bytes of one 64-wide stage of a row: block header and 32 bytes of nibbles
@@ -277,7 +279,6 @@ struct Q4KPrefill {
 
 // Q8_0: a 64-wide stage is two 34-byte blocks (2-byte aligned): y = q * d
 struct Q8_0Prefill {
-  static constexpr bool kTmaWeights = false;
   static constexpr int kType = kQ8_0;
   static constexpr bool kSplitLoad = false;
   struct Raw {};
@@ -331,7 +332,6 @@ struct Q8_0Prefill {
 // Q6_K: a 64-wide stage is a quarter super-block: half = elements 128*half.., sub selects low (l, l+32)
 // or high (l+64, l+96) nibbles of the same 64 ql bytes; y = d * sc * (q - 32)
 struct Q6KPrefill {
-  static constexpr bool kTmaWeights = false;
   static constexpr int kType = kQ6K;
   static constexpr bool kSplitLoad = false;
   struct Raw {};
@@ -411,17 +411,6 @@ struct Q6KPrefill {
   }
 };
 
-// Weights that are already in the tensor cores' operand type, [N][K] row-major: f16 or bf16 for the 16-bit forms, f32 for
-// the tf32 form (whose low mantissa bits the tensor cores ignore). The formats without a dequantizing stage of their own
-// above reach the tensor cores this way: their stand-alone dequantizing kernels (GgmlType::to_float arithmetic) fill a
-// slab of rows, and a stage's weight tile arrives like its activation tile, by one tensor-map copy with the 128-byte
-// swizzle; no thread touches the weights.
-struct PlainWPrefill {
-  static constexpr bool kTmaWeights = true;
-  static constexpr bool kSplitLoad = false;
-  struct Raw {};
-};
-
 struct PrefillSmem {
   uint64_t full[kPfStages];   // weight tile of the stage written (the dequantizing threads)
   uint64_t xfull[kPfStages];  // activation tile of the stage landed (tensor-map copy, counted in bytes)
@@ -438,8 +427,7 @@ struct PrefillSmem {
 // weights' range fits (finite values saturate at +-65504); the activation rows arrive scaled by a power of two
 // into f16's range and p.row_unscale[m] undoes it in the epilogue.
 template <class Fmt, int kTileM, bool kTf32 = false, bool kMulti = false, bool kF16 = false>
-__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap xmap,
-                                                                      const __grid_constant__ CUtensorMap wmap) {
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t pf_smem[];
   // [stage][ weights 128 x 128 B | activations kTileM x 128 B ], each 1024-byte aligned; control block after
   constexpr int kWBytes = kPfTileN * 128, kXBytes = kTileM * 128, kStageBytes = kWBytes + kXBytes;
@@ -469,106 +457,79 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
   const uint32_t tmem_d = *reinterpret_cast<volatile uint32_t*>(&sm->tmem_base);
   volatile int* abort_flag = &sm->abort_flag;
 
-  if (Fmt::kTmaWeights && warp < kPfDequantWarps) {
-    // ---------------- both tiles of a stage by tensor-map copies (rows past the end of either matrix arrive as zeros),
-    // issued by one thread and counted in bytes on the stage's xfull barrier
-    if constexpr (Fmt::kTmaWeights) {
-      if (threadIdx.x == 0) {
-        int s = 0, issued = 0;
-        uint32_t ph = 0;
-        for (int it = 0; it < n_iter && !*abort_flag; ++it) {
-          if (it >= kPfStages && !mbar_wait_bounded(&sm->empty[s], ph ^ 1u)) {
-            record_dev_error(kErrEmptyWait);
-            *abort_flag = 1;
-            break;
-          }
-          mbar_arrive_expect_tx(&sm->xfull[s], (uint32_t)(kXBytes + kWBytes));
-          tma_load_2d(base_u32 + s * kStageBytes, &wmap, it * kStageK, n0, &sm->xfull[s]);
-          tma_load_2d(base_u32 + s * kStageBytes + kWBytes, &xmap, it * kStageK, m0, &sm->xfull[s]);
-          issued = it + 1;
-          if (++s == kPfStages) s = 0, ph ^= 1u;
-        }
-        if (*abort_flag) {  // leaving early: let the copies already issued land first
-          for (int it = (issued > kPfStages ? issued - kPfStages : 0); it < issued; ++it)
-            if (!mbar_wait_bounded(&sm->xfull[it % kPfStages], (it / kPfStages) & 1)) record_dev_error(kErrDrainWait);
-        }
-      }
+  if (warp < kPfDequantWarps) {
+    // ---------------- weight producers: thread t owns half (t >> 7) of weight row n0 + (t & 127)
+    const int t = threadIdx.x, r = t & 127, part = t >> 7;
+    const bool live = n0 + r < p.N;
+    const uint8_t* row = p.w + (size_t)(live ? n0 + r : 0) * p.row_bytes;
+    int s = 0;
+    uint32_t ph = 0;
+    int x_issued = 0;
+    // the bytes of the next three stages, requested that far ahead: a stage takes less time than one trip to L2
+    using RawT = typename Fmt::Raw;
+    auto load_raw = [&](int it, RawT& dst_raw) { Fmt::load(row, it, dst_raw); };
+    RawT r0, r1, r2;
+    if (!kTf32 && Fmt::kSplitLoad && live) {
+      if (n_iter > 0) load_raw(0, r0);
+      if (n_iter > 1) load_raw(1, r1);
+      if (n_iter > 2) load_raw(2, r2);
     }
-  } else if (warp < kPfDequantWarps) {
-    if constexpr (!Fmt::kTmaWeights) {
-      // ---------------- weight producers: thread t owns half (t >> 7) of weight row n0 + (t & 127)
-      const int t = threadIdx.x, r = t & 127, part = t >> 7;
-      const bool live = n0 + r < p.N;
-      const uint8_t* row = p.w + (size_t)(live ? n0 + r : 0) * p.row_bytes;
-      int s = 0;
-      uint32_t ph = 0;
-      int x_issued = 0;
-      // the bytes of the next three stages, requested that far ahead: a stage takes less time than one trip to L2
-      using RawT = typename Fmt::Raw;
-      auto load_raw = [&](int it, RawT& dst_raw) { Fmt::load(row, it, dst_raw); };
-      RawT r0, r1, r2;
-      if (!kTf32 && Fmt::kSplitLoad && live) {
-        if (n_iter > 0) load_raw(0, r0);
-        if (n_iter > 1) load_raw(1, r1);
-        if (n_iter > 2) load_raw(2, r2);
+    for (int it = 0; it < n_iter && !*abort_flag; ++it) {
+      if (it >= kPfStages && !mbar_wait_bounded(&sm->empty[s], ph ^ 1u)) {
+        record_dev_error(kErrEmptyWait);
+        *abort_flag = 1;
+        break;
       }
-      for (int it = 0; it < n_iter && !*abort_flag; ++it) {
-        if (it >= kPfStages && !mbar_wait_bounded(&sm->empty[s], ph ^ 1u)) {
-          record_dev_error(kErrEmptyWait);
-          *abort_flag = 1;
-          break;
-        }
-        if (t == 0) {  // the stage is free: its activation tile, rows m0.. x columns 64*it.., as one copy
-          mbar_arrive_expect_tx(&sm->xfull[s], (uint32_t)kXBytes);
-          tma_load_2d(base_u32 + s * kStageBytes + kWBytes, &xmap, it * kStageK, m0, &sm->xfull[s]);
-          x_issued = it + 1;
-        }
-        uint8_t* dst = base + s * kStageBytes + r * 128;
-        if constexpr (kTf32) {
-          static_assert(!kTf32 || kPfDequantWarps == 8, "the tf32 form splits a row's 32 elements between two threads");
-          uint4 out[4];
-          if (live) {
-            Fmt::stage16(row, it, part, out);
-          } else {
-  #pragma unroll
-            for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
-          }
-  #pragma unroll
-          for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + (((4 * part + c) ^ (r & 7)) << 4)) = out[c];
-        } else if constexpr (Fmt::kSplitLoad) {
-          constexpr int kChunks = 4;  // 16-byte chunks this thread writes
-          uint4 out[4];
-          if (live) {
-            const RawT cur = r0;
-            r0 = r1;
-            r1 = r2;
-            if (it + 3 < n_iter) load_raw(it + 3, r2);
-            Fmt::template convert_half<kF16>(cur, it, part, out);
-          } else {
-  #pragma unroll
-            for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
-          }
-  #pragma unroll
-          for (int c = 0; c < kChunks; ++c) *reinterpret_cast<uint4*>(dst + (((kChunks * part + c) ^ (r & 7)) << 4)) = out[c];
-        } else {  // the other formats: each of the row's two threads dequantizes half of the stage
-          uint4 out[4];
-          if (live) {
-            Fmt::template stage_half<kF16>(row, it, part, out);
-          } else {
-  #pragma unroll
-            for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
-          }
-  #pragma unroll
-          for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + ((Fmt::chunk_id(part, c) ^ (r & 7)) << 4)) = out[c];
-        }
-        fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
-        mbar_arrive(&sm->full[s]);
-        if (++s == kPfStages) s = 0, ph ^= 1u;
+      if (t == 0) {  // the stage is free: its activation tile, rows m0.. x columns 64*it.., as one copy
+        mbar_arrive_expect_tx(&sm->xfull[s], (uint32_t)kXBytes);
+        tma_load_2d(base_u32 + s * kStageBytes + kWBytes, &xmap, it * kStageK, m0, &sm->xfull[s]);
+        x_issued = it + 1;
       }
-      if (t == 0 && *abort_flag) {  // leaving early: let the copies already issued land first
-        for (int it = (x_issued > kPfStages ? x_issued - kPfStages : 0); it < x_issued; ++it)
-          if (!mbar_wait_bounded(&sm->xfull[it % kPfStages], (it / kPfStages) & 1)) record_dev_error(kErrDrainWait);
+      uint8_t* dst = base + s * kStageBytes + r * 128;
+      if constexpr (kTf32) {
+        static_assert(!kTf32 || kPfDequantWarps == 8, "the tf32 form splits a row's 32 elements between two threads");
+        uint4 out[4];
+        if (live) {
+          Fmt::stage16(row, it, part, out);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + (((4 * part + c) ^ (r & 7)) << 4)) = out[c];
+      } else if constexpr (Fmt::kSplitLoad) {
+        constexpr int kChunks = 4;  // 16-byte chunks this thread writes
+        uint4 out[4];
+        if (live) {
+          const RawT cur = r0;
+          r0 = r1;
+          r1 = r2;
+          if (it + 3 < n_iter) load_raw(it + 3, r2);
+          Fmt::template convert_half<kF16>(cur, it, part, out);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) *reinterpret_cast<uint4*>(dst + (((kChunks * part + c) ^ (r & 7)) << 4)) = out[c];
+      } else {  // the other formats: each of the row's two threads dequantizes half of the stage
+        uint4 out[4];
+        if (live) {
+          Fmt::template stage_half<kF16>(row, it, part, out);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + ((Fmt::chunk_id(part, c) ^ (r & 7)) << 4)) = out[c];
       }
+      fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+      mbar_arrive(&sm->full[s]);
+      if (++s == kPfStages) s = 0, ph ^= 1u;
+    }
+    if (t == 0 && *abort_flag) {  // leaving early: let the copies already issued land first
+      for (int it = (x_issued > kPfStages ? x_issued - kPfStages : 0); it < x_issued; ++it)
+        if (!mbar_wait_bounded(&sm->xfull[it % kPfStages], (it / kPfStages) & 1)) record_dev_error(kErrDrainWait);
     }
   } else if (lane == 0) {
     // ---------------- MMA issue: one thread
@@ -577,7 +538,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const Prefi
     uint32_t ph = 0;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
-      if (*abort_flag || (!Fmt::kTmaWeights && !mbar_wait_bounded(&sm->full[s], ph)) || !mbar_wait_bounded(&sm->xfull[s], ph)) {
+      if (*abort_flag || !mbar_wait_bounded(&sm->full[s], ph) || !mbar_wait_bounded(&sm->xfull[s], ph)) {
         if (!*abort_flag) record_dev_error(kErrFullWait);
         *abort_flag = 1;
         ok = false;
