@@ -13,8 +13,9 @@ Metric: achieved HBM GB/s = algorithmic bytes (W blocks + 4*M*k + 4*M*n per mat-
 N > 1 (torchrun): the SAME 32 matrices, each split by output rows over the N GPUs (strong scaling): a rank
 streams its rows, its kernel stores its slice of y into every GPU's copy over NVLink, and a consumer kernel on every
 GPU waits for the whole vector (takes its argmax) before the next mat-vec — the exchange is inside the kernels, no
-library collective. Beside the headline the N-GPU line carries the 7B-architecture decode (tensor-parallel), the
-column-sharded prefill GEMM and the expert-parallel MoE block at the same N.
+library collective. Beside the headline the line carries the 7B-architecture decode (tensor-parallel at N > 1), the
+prefill GEMM of configuration 3 (`prefill`; column-sharded `prefill_sharded` at N > 1) and the MoE block of configuration 5
+(`moe_block`; expert-parallel `moe_ep` at N > 1).
 --impl reference: the reference's CPU path (its arithmetic restated under oracle/, AVX2 order,
 all host threads) on the same step.
 """
@@ -218,19 +219,26 @@ def _time_graph(torch, stream, fn, reps):
 
 
 def run_side_workload(args):
-    """benchmark configurations 2 (batch sweep), 3 (prefill GEMM) and 5 (MoE block) on one GPU: seeded synthetic tensors of the
-    stated shapes, distinct weight copies cycling through more than L2, CUDA-graph replay, one JSON line per case."""
-    import torch
-
-    from fuel_b200 import GgmlDType as T, _lib, ops
-    from fuel_b200.moe import QMoeBlock
-    L = _lib.lib
+    """benchmark configurations 2 (batch sweep), 3 (prefill GEMM) and 5 (MoE block): one JSON line per case. Several GPUs: the
+    column-sharded prefill GEMM or the expert-parallel MoE block."""
     rank, local_rank, world = _dist_env()
     if world > 1:
         assert args.workload in ("moe", "prefill"), "multi-GPU forms: the MoE block (expert-parallel), the prefill GEMM (column-sharded)"
         if args.workload == "prefill":
             return run_prefill_sharded(args, rank, local_rank, world)
         return run_moe_expert_parallel(args, rank, local_rank, world)
+    for line in side_lines(args, args.workload):
+        print(json.dumps(line), flush=True)
+
+
+def side_lines(args, workload):
+    """The cases of one side workload on one GPU, as a generator of result dicts: seeded synthetic tensors of the stated
+    shapes, distinct weight copies cycling through more than L2, CUDA-graph replay."""
+    import torch
+
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    from fuel_b200.moe import QMoeBlock
+    L = _lib.lib
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     L.fuelq_set_option(_lib.OPT_PDL, 1 if args.pdl else 0)
@@ -276,18 +284,18 @@ def run_side_workload(args):
                               "frobenius_vs_cpu_path": float(np.linalg.norm(got - ref) / np.linalg.norm(ref))}
         return line
 
-    if args.workload == "sweep":
+    if workload == "sweep":
         for t, name in ((T.Q4K, "Q4_K"), (T.Q6K, "Q6_K"), (T.Q8_0, "Q8_0")):
             for n, k in ((11008, 4096), (4096, 11008)):
                 for m in (1, 2, 4, 8, 16, 32, 64, 128):
                     if args.only and args.only not in f"{name}_k{k}_n{n}_m{m}":
                         continue
-                    print(json.dumps(matmul_case(t, name, n, k, m, 12, 20)), flush=True)
-    elif args.workload == "q5k":
+                    yield matmul_case(t, name, n, k, m, 12, 20)
+    elif workload == "q5k":
         for n, k in ((11008, 4096), (4096, 11008)):
             for m in (1, 2, 4, 8, 16):
-                print(json.dumps(matmul_case(T.Q5K, "Q5_K", n, k, m, 12, 20)), flush=True)
-    elif args.workload == "formats":
+                yield matmul_case(T.Q5K, "Q5_K", n, k, m, 12, 20)
+    elif workload == "formats":
         # the formats served by the generic exact-integer decode kernel up to 16 rows, and above that by the tensor-core
         # kernel on slabs of rows dequantized into its operand type (512 rows here, with the observed error)
         for t, name in ((T.Q4_0, "Q4_0"), (T.Q4_1, "Q4_1"), (T.Q5_0, "Q5_0"), (T.Q5_1, "Q5_1"), (T.Q2K, "Q2_K"), (T.Q3K, "Q3_K"),
@@ -296,11 +304,11 @@ def run_side_workload(args):
                 if args.only and args.only not in f"{name}_k4096_n11008_m{m}":
                     continue
                 parity = 8 if m == 512 and not args.no_cpu_baseline else 0
-                print(json.dumps(matmul_case(t, name, 11008, 4096, m, 12 if m < 512 else 4, 20, parity_rows=parity)), flush=True)
-    elif args.workload == "prefill":
+                yield matmul_case(t, name, 11008, 4096, m, 12 if m < 512 else 4, 20, parity_rows=parity)
+    elif workload == "prefill":
         line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10, parity_rows=0 if args.no_cpu_baseline else 32)
         line["operands"] = "tf32" if args.tf32 else "bf16" if args.bf16 else "f16"
-        print(json.dumps(line), flush=True)
+        yield line
     else:
         E, H, F, K, N, copies = 128, 2048, 768, 8, 256, 4
         blocks = []
@@ -317,9 +325,9 @@ def run_side_workload(args):
                 b.forward(x, logits, o)
         us = _time_graph(torch, st, p, 20) / copies
         wbytes = E * 3 * F * H // 256 * 144
-        print(json.dumps({"workload": f"moe_block_e{E}_h{H}_f{F}_top{K}_tokens{N}_q4k", "us": us, "GB/s": wbytes / us / 1e3,
-                          "tokens_per_s": N / us * 1e6, "hbm_frac": wbytes / us / 1e3 / peak, "peak_kind": f"of {peak_kind}",
-                          "weight_bytes": wbytes, "weight_copies": copies, "launches_per_block": 9}), flush=True)
+        yield {"workload": f"moe_block_e{E}_h{H}_f{F}_top{K}_tokens{N}_q4k", "us": us, "GB/s": wbytes / us / 1e3,
+               "tokens_per_s": N / us * 1e6, "hbm_frac": wbytes / us / 1e3 / peak, "peak_kind": f"of {peak_kind}",
+               "weight_bytes": wbytes, "weight_copies": copies, "launches_per_block": 9}
     assert ops.device_error() == 0, "a kernel recorded an expired bounded wait"
 
 
@@ -784,8 +792,14 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         config0 = run_config0(torch, device, args.pdl)
         torch.cuda.empty_cache()
+    prefill, moe_block = None, None
     if not args.no_model:
         decode_7b = run_decode_7b(torch, dist, device, rank, world)
+        if world == 1:  # configurations 3 (prefill GEMM) and 5 (MoE block) on this GPU
+            torch.cuda.empty_cache()
+            prefill = list(side_lines(args, "prefill"))[0]
+            torch.cuda.empty_cache()
+            moe_block = list(side_lines(args, "moe"))[0]
         if world > 1:  # the other two multi-GPU forms at the same GPU count
             torch.cuda.empty_cache()
             prefill_sharded = run_prefill_sharded(args, rank, local_rank, world, own_group=False)
@@ -855,6 +869,9 @@ def main():
     }
     if config0 is not None:
         line["config0"] = config0
+    if prefill is not None:
+        line["prefill"] = prefill
+        line["moe_block"] = moe_block
     if world > 1:
         line["exchange"] = ("per mat-vec: each rank's kernel stores its rows of y as stamped 8-byte pairs into every GPU's copy over "
                             "NVLink; a consumer kernel on every GPU polls its copy until complete (no collective, no multicast)")
