@@ -1013,7 +1013,7 @@ int32_t prefill_gemm(int type, int64_t m, int64_t n, int64_t k, const void* w, f
 
 // y_dst / n_dst / ldy / n_off: see PrefillParams; the plain call passes one destination of width n
 int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, const float* x, float* const* y_dst, int n_dst,
-                     int64_t ldy, int64_t n_off, void* workspace, cudaStream_t stream) {
+                     int64_t ldy, int64_t n_off, void* workspace, cudaStream_t stream, bool one_kernel = false) {
   const bool tf32 = g_opt.prefill_tf32 != 0, f16 = !tf32 && !g_opt.prefill_bf16;
   void* xb = workspace;  // the activations in the tensor cores' operand type: f16 (rows scaled), bf16, or f32 rounded to tf32
   float* unscale = (float*)((uint8_t*)workspace + align_up((size_t)m * k * (tf32 ? 4 : 2), 256));
@@ -1025,7 +1025,7 @@ int32_t prefill_impl(int type, int64_t m, int64_t n, int64_t k, const void* w, c
   else
     f32_to_bf16_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(x, n4, (__nv_bfloat16*)xb);
   if (cudaGetLastError() != cudaSuccess) return kLaunchFailure;
-  if (!prefill_uses_slab(type, m)) return prefill_gemm(type, m, n, k, w, y_dst, n_dst, ldy, n_off, workspace, stream);
+  if (one_kernel || !prefill_uses_slab(type, m)) return prefill_gemm(type, m, n, k, w, y_dst, n_dst, ldy, n_off, workspace, stream);
   // Dequantize a slab of rows into the operand type (the reference's to_float values in f32, then one rounding), multiply
   // it, take the next slab. Kernels on one stream, so the slab is reused.
   uint8_t* slab = (uint8_t*)workspace + prefill_x_bytes(m, k);
@@ -1198,6 +1198,9 @@ int32_t fuelq_qmatmul_packed(int32_t ggml_type, int64_t m_total, int64_t n, int6
   return decode_chunked(ggml_type, m_total, n, k, w, const_cast<void*>(packed_act), y, (cudaStream_t)stream);
 }
 
+static int32_t qmatmul_integer(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
+                               float* y, void* workspace, void* stream);
+
 int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
                       float* y, void* workspace, size_t workspace_bytes, void* stream) {
   int32_t st = check_problem(ggml_type, m_total, n, k);
@@ -1213,6 +1216,13 @@ int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, 
     float* const one[1] = {y};
     return prefill_impl(ggml_type, m_total, n, k, w, x, one, 1, n, 0, workspace, (cudaStream_t)stream);
   }
+  return qmatmul_integer(ggml_type, m_total, n, k, w, x, y, workspace, stream);
+}
+
+// The integer kernels (the reference's arithmetic): activation blocks into the workspace, then the mat-vec kernels.
+static int32_t qmatmul_integer(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
+                               float* y, void* workspace, void* stream) {
+  int32_t st;
   if (g_opt.l2_prefetch) {
     st = prefetch_impl(w, n * (k / block_elems(ggml_type)) * block_bytes(ggml_type), (cudaStream_t)stream);
     if (st != kOk) return st;
@@ -1330,8 +1340,19 @@ int32_t fuelq_qmatmul_static_scratch(int32_t ggml_type, int64_t m_total, int64_t
   const int32_t st = check_problem(ggml_type, m_total, n, k);
   if (st != kOk) return st;
   if (m_total == 0 || n == 0) return kOk;
-  // sizes beyond the built-in scratch are refused, never truncated
-  if (fuelq_qmatmul_workspace_bytes(ggml_type, m_total, n, k) > kStaticScratchBytes) return kWorkspace;
+  // Sizes beyond the built-in scratch are refused, never truncated. A tensor-core problem whose activations fit but
+  // whose slab of dequantized rows does not runs without a slab: Q4_K / Q6_K / Q8_0 dequantized inside the GEMM kernel
+  // (the same arithmetic class), the other formats on the integer kernels if their activation blocks fit.
+  int fallback = 0;
+  if (fuelq_qmatmul_workspace_bytes(ggml_type, m_total, n, k) > kStaticScratchBytes) {
+    if (!prefill_available(ggml_type, m_total, n, k)) return kWorkspace;
+    if (prefill_native_type(ggml_type) && prefill_x_bytes(m_total, k) <= kStaticScratchBytes && m_total <= (1 << 30) && n <= (1 << 30))
+      fallback = 1;
+    else if (act_packed_bytes(ggml_type, m_total, k) <= kStaticScratchBytes)
+      fallback = 2;
+    else
+      return kWorkspace;
+  }
   // In host code the array's name is only a handle; the device address has to be asked for, once
   // per device, with that device current.
   static void* scratch_addr[64] = {};
@@ -1344,6 +1365,13 @@ int32_t fuelq_qmatmul_static_scratch(int32_t ggml_type, int64_t m_total, int64_t
   }
   // every plane of the scratch is written by the activation-quantization kernel before the
   // mat-vec reads it, so nothing in it needs clearing between calls
+  if (fallback) {
+    if (!w || !x || !y) return kInvalidProblem;
+    if (!aligned(w, 16) || !aligned(x, 16) || !aligned(y, 4)) return kMisaligned;
+    if (fallback == 2) return qmatmul_integer(ggml_type, m_total, n, k, w, x, y, scratch_addr[dev], stream);
+    float* const one[1] = {y};
+    return prefill_impl(ggml_type, m_total, n, k, w, x, one, 1, n, 0, scratch_addr[dev], (cudaStream_t)stream, true);
+  }
   return fuelq_qmatmul(ggml_type, m_total, n, k, w, x, y, scratch_addr[dev], kStaticScratchBytes, stream);
 }
 

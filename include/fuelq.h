@@ -181,7 +181,10 @@ int32_t fuelq_qmatmul_host(int32_t ggml_type, int64_t m_total, int64_t n, int64_
  *  - all calls share the one array: two calls whose kernels may run at the same time on the GPU
  *    (different streams, or different host threads) would overwrite each other's activations. Keep
  *    them on one stream. Nothing in the array has to be cleared between calls.
- * Results are bit-identical to fuelq_qmatmul. Calls no allocation routine of any kind. */
+ * Results are bit-identical to fuelq_qmatmul, except for tensor-core problems (fuelq_qmatmul_numerics != 0) whose
+ * activations fit the array but whose slab of dequantized weight rows does not: those run without a slab - Q4_K,
+ * Q6_K and Q8_0 as under FUELQ_OPT_PREFILL_ONE_KERNEL (same arithmetic class), the other formats on the integer
+ * kernels (the reference's arithmetic). Calls no allocation routine of any kind. */
 size_t fuelq_static_scratch_bytes(void);
 int32_t fuelq_qmatmul_static_scratch(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w,
                                      const float* x, float* y, void* stream);

@@ -45,3 +45,37 @@ def test_static_scratch_matches_workspace_entry_point_twice():
     torch.cuda.synchronize()
     assert bool((y == 7.0).all())
     assert ops.device_error() == 0
+
+
+def test_static_scratch_runs_tensor_core_problems_without_a_slab():
+    """Above the crossover the ordinary entry point wants a slab of dequantized weight rows in its workspace; the built-in
+    array has no room for one. Q4_K / Q6_K / Q8_0 then run the one-kernel form (bit-identical to the ordinary entry under
+    FUELQ_OPT_PREFILL_ONE_KERNEL), the other formats the integer kernels (bit-identical to the ordinary entry with the
+    crossover raised)."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuel_b200 import GgmlDType as T, _lib, ops
+    L = _lib.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    limit = L.fuelq_static_scratch_bytes()
+    g = torch.Generator(device="cuda")
+    for dtype, m, n, k, opt, val in ((T.Q4K, 100, 4096, 1024, _lib.OPT_PREFILL_ONE_KERNEL, 1),
+                                     (T.Q6K, 80, 2048, 512, _lib.OPT_PREFILL_ONE_KERNEL, 1),
+                                     (T.Q5K, 20, 2048, 1024, _lib.OPT_DECODE_MAX_M, 1 << 20),
+                                     (T.Q4_0, 33, 1024, 2048, _lib.OPT_DECODE_MAX_M, 1 << 20)):
+        g.manual_seed(int(dtype) + m)
+        w = ops.quantize_weights(dtype, torch.randn(n, k, generator=g, device="cuda") * 0.02)
+        x = torch.randn(m, k, generator=g, device="cuda")
+        assert L.fuelq_qmatmul_numerics(int(dtype), m, n, k) == _lib.NUMERICS_F16
+        assert L.fuelq_qmatmul_workspace_bytes(int(dtype), m, n, k) > limit
+        got = torch.full((m, n), float("nan"), device="cuda")
+        _lib.check(L.fuelq_qmatmul_static_scratch(int(dtype), m, n, k, w.data_ptr(), x.data_ptr(), got.data_ptr(), stream),
+                   "fuelq_qmatmul_static_scratch")
+        try:
+            _lib.check(L.fuelq_set_option(opt, val), "set_option")
+            want = ops.qmatmul(dtype, w, n, x)
+        finally:
+            L.fuelq_set_option(opt, 0)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), (dtype, m)
+    assert ops.device_error() == 0
