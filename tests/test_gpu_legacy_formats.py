@@ -18,8 +18,12 @@ NAMES = ("q4_1", "q5_0", "q5_1")
 def ops():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
-    from fuel_b200 import ops as _ops
+    from fuel_b200 import _lib, ops as _ops
+    # these tests are about the integer kernels (the reference's arithmetic) at every batch size: keep batches above 16 rows
+    # off the tensor-core path, which has its own tests
+    _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 1 << 20), "set_option")
     yield _ops
+    _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 0)
     assert _ops.device_error() == 0, "a kernel recorded an expired bounded wait"
 
 

@@ -1,6 +1,7 @@
 """Q5_K through the decode path (fuel-quantized/src/k_quants.rs:1626-1925): dequantization bit-identical, mat-vec
-within the 1e-3 bar of the CPU restatement for every batch size (all batches run the exact-integer kernels; there is
-no tensor-core form for this format), and a model with Q5_K linears loaded from a GGUF file."""
+within the 1e-3 bar of the CPU restatement for every batch size on the exact-integer kernels (batches above 16 rows are
+kept there by FUELQ_OPT_DECODE_MAX_M; the tensor-core form they take by default has its own tests), and a model with
+Q5_K linears loaded from a GGUF file."""
 import os
 
 import numpy as np
@@ -30,8 +31,16 @@ def test_dequantize_bit_identical(ops, oracle):
                           oracle.dequantize(oracle.Q5K, rb).view(np.uint32))
 
 
+@pytest.fixture
+def integer_path():
+    from fuel_b200 import _lib
+    _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 1 << 20), "set_option")
+    yield
+    _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 0)
+
+
 @pytest.mark.parametrize("m", [1, 2, 3, 5, 16, 21])
-def test_matvec_matches_reference(ops, oracle, m):
+def test_matvec_matches_reference(ops, oracle, integer_path, m):
     from fuel_b200 import GgmlDType as T
     for n, k in [(1, 256), (7, 256), (33, 512), (64, 4096), (300, 1024), (5, 11008)]:
         wb = oracle.quantize(oracle.Q5K, _weights(n, k, seed=n))
