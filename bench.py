@@ -63,6 +63,23 @@ def _peaks():
         return 6650.0, "fallback"
 
 
+def _tensor_peaks():
+    """Measured dense bf16 rates of this pool's GPUs: (burst, sustained under the power cap, which)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            j = json.load(f)
+        return float(j["bf16_tflops"]), float(j.get("bf16_tflops_sustained") or j["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+def tensor_roofline(tflops: float) -> dict:
+    burst, sustained, kind = _tensor_peaks()
+    return {"bound": "tensor", "achieved": tflops, "peak": burst, "unit": "TFLOP/s", "frac": tflops / burst,
+            "peak_sustained": sustained, "frac_of_sustained": tflops / sustained, "peak_kind": f"of {kind}",
+            "flops": "2*M*N*K over the whole step (activation pre-pass, weight dequantization, GEMM)"}
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons through nvidia-smi while the timed region runs."""
 
@@ -308,6 +325,7 @@ def side_lines(args, workload):
     elif workload == "prefill":
         line = matmul_case(T.Q4K, "Q4_K", 14336, 4096, 2048, 6, 10, parity_rows=0 if args.no_cpu_baseline else 32)
         line["operands"] = "tf32" if args.tf32 else "bf16" if args.bf16 else "f16"
+        line["roofline"] = tensor_roofline(line["TFLOP/s"])
         yield line
     else:
         E, H, F, K, N, copies = 128, 2048, 768, 8, 256, 4
