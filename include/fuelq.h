@@ -145,9 +145,10 @@ int32_t fuelq_qmatmul_can_implement(int32_t ggml_type, int64_t m_total, int64_t 
  * DynQuantizedStorage::fwd (fuel-backend-contract/src/quantized.rs:72-80), i.e.
  * fuel_quantized::matmul (k_quants.rs:2284-2331) and the CUDA entry it replaces,
  * baracuda_kernels_mmvq_<fmt>_batched_run (fuel-cuda-backend/src/quantized.rs:138-231).
- * Quantizes x, then runs the decode mat-vec (m_total <= DECODE_MAX_M) or the
- * tensor-core path. Weight formats: Q4_K, Q6_K, Q8_0 (both paths); Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K and Q5_K (decode
- * kernels at any m_total).
+ * Up to the crossover (FUELQ_OPT_DECODE_MAX_M) it quantizes x and runs the integer decode kernels; above it the
+ * tensor-core path (activations converted to the operand type, weights dequantized into a slab of the workspace, one
+ * GEMM per slab). Weight formats: Q4_K, Q6_K, Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, Q2_K, Q3_K and Q5_K on both paths; the
+ * tensor-core path needs k to be a multiple of 64 (other k stay on the integer kernels at any m_total).
  * w must be 16-byte aligned, x and y 16-byte aligned. */
 int32_t fuelq_qmatmul(int32_t ggml_type, int64_t m_total, int64_t n, int64_t k, const void* w, const float* x,
                       float* y, void* workspace, size_t workspace_bytes, void* stream);
