@@ -615,7 +615,7 @@ int32_t moe_mma_impl(int n_groups, int64_t n, int64_t k, const void* w, const Ac
   return e == cudaSuccess ? kOk : kLaunchFailure;
 }
 
-// ---- small batches on the integer tensor cores (mma_batch.cuh): Q4_K, Q6_K, Q8_0; k a multiple of 256
+// ---- small batches on the integer tensor cores (mma_batch.cuh): Q4_K, Q5_K, Q6_K, Q8_0; k a multiple of 256
 template <class F, int MT>
 cudaError_t launch_mma_batch(const MmaBatchParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
   static bool attr_set[64] = {};
@@ -708,6 +708,7 @@ int32_t mma_batch_impl(int type, int n_groups, int64_t n, int64_t k, const void*
   if (k % 256 || k > (1 << 20) || n > (1 << 24) || n_groups > 65535) return kNotSupported;
   switch (type) {
     case kQ4K: return mma_batch_fmt<MbQ4K>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
+    case kQ5K: return mma_batch_fmt<MbQ5K>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
     case kQ6K: return mma_batch_fmt<MbQ6K>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
     case kQ8_0: return mma_batch_fmt<MbQ8_0>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
     default: return kNotSupported;

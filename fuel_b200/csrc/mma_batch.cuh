@@ -1,5 +1,5 @@
 // Small-batch quantized matmul on the integer tensor cores: a handful of activation rows (a dense batch of
-// 2..16 rows, or the rows routed to one expert) against Q4_K, Q6_K or Q8_0 weights, the weights streamed
+// 2..16 rows, or the rows routed to one expert) against Q4_K, Q5_K, Q6_K or Q8_0 weights, the weights streamed
 // from HBM exactly once per 16 activation rows.
 //
 // Arithmetic: the reference's vec_dot per (weight row, activation row) — exact integer dot products of the
@@ -253,6 +253,89 @@ struct MbQ4K {
       facc[mt][1] += (d0 * yb) * (float)(Slo[mt][1] + (Shi[mt][1] >> 4)) - (dm0 * yb) * (float)T1;
       facc[mt][2] += (d1 * ya) * (float)(Slo[mt][2] + (Shi[mt][2] >> 4)) - (dm1 * ya) * (float)T2;
       facc[mt][3] += (d1 * yb) * (float)(Slo[mt][3] + (Shi[mt][3] >> 4)) - (dm1 * yb) * (float)T3;
+    }
+  }
+};
+
+// ------------------------------------------------------------------------------------------------ Q5_K
+// Q4_K's block with a fifth bit per element (fuel-quantized/src/k_quants.rs:1626-1760): the same 16-byte header (d, dmin,
+// packed 6-bit scales and mins), then 32 bytes of qh, then the 128 bytes of nibbles. Byte t of qh carries, in bits 2g and
+// 2g + 1, the fifth bits of the low- and high-nibble elements of byte t of nibble group g - so one ldmatrix of the qh
+// bytes per block lands in exactly the fragment positions of every group's nibble bytes. The 5-bit values are built as
+// unsigned bytes (a value times 16 no longer fits one), one MMA per 32-element sub-block as for Q4_K.
+struct MbQ5K : MbQ4K {
+  static constexpr int kType = kQ5K;
+  static constexpr int kBytes256 = 176;
+  template <int MT>
+  __device__ __forceinline__ static void block_step(const MbCtx& cx, int b, uint32_t, uint32_t, float (&facc)[MT][4]) {
+    const uint32_t blk = (uint32_t)b * 176u;
+    const uint4 h0 = lds128(cx.tile_s + cx.row_off(cx.gid) + blk);
+    const uint4 h1 = lds128(cx.tile_s + cx.row_off(cx.gid + 8) + blk);
+    const uint32_t sc0[2] = {h0.y & 0x3f3f3f3fu, (h0.w & 0x0f0f0f0fu) | (((h0.y >> 6) & 0x03030303u) << 4)};
+    const uint32_t mn0[2] = {h0.z & 0x3f3f3f3fu, ((h0.w >> 4) & 0x0f0f0f0fu) | (((h0.z >> 6) & 0x03030303u) << 4)};
+    const uint32_t sc1[2] = {h1.y & 0x3f3f3f3fu, (h1.w & 0x0f0f0f0fu) | (((h1.y >> 6) & 0x03030303u) << 4)};
+    const uint32_t mn1[2] = {h1.z & 0x3f3f3f3fu, ((h1.w >> 4) & 0x0f0f0f0fu) | (((h1.z >> 6) & 0x03030303u) << 4)};
+    // ldmatrix addresses as for Q4_K: rows (lane & 7) + 8 * bit 3, byte column 16 * bit 4 of a 32-byte run - the qh bytes
+    // at offset 16 of the block, the nibble groups from offset 48
+    const uint32_t wrow = cx.tile_s + cx.row_off((cx.lane & 7) + 8 * ((cx.lane >> 3) & 1)) + blk + 16u * (cx.lane >> 4);
+    const uint32_t wq = wrow + 48u;
+    const uint32_t aq = cx.act_s + (uint32_t)(cx.lane & 7) * cx.L.astride + (uint32_t)b * 256u + 16u * (cx.lane >> 3);
+    int Slo[MT][4], Shi[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) Slo[mt][i] = 0, Shi[mt][i] = 0;
+    uint32_t hq[4], r[2][4], q[2][MT][4];
+    ldmatrix_x4(hq, wrow + 16u);
+    ldmatrix_x4(r[0], wq);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(q[0][mt], aq + (uint32_t)(8 * mt) * cx.L.astride);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int cur = g & 1, nxt = cur ^ 1;
+      if (g < 3) {
+        ldmatrix_x4(r[nxt], wq + 32u * (g + 1));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(q[nxt][mt], aq + (uint32_t)(8 * mt) * cx.L.astride + 64u * (g + 1));
+      }
+      uint32_t alo[4], ahi[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        alo[i] = (r[cur][i] & 0x0f0f0f0fu) | (((hq[i] >> (2 * g)) & 0x01010101u) << 4);
+        ahi[i] = ((r[cur][i] >> 4) & 0x0f0f0f0fu) | (((hq[i] >> (2 * g + 1)) & 0x01010101u) << 4);
+      }
+      int cl[MT][4], ch[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma_u8s8_k32(cl[mt], alo, q[cur][mt][0], q[cur][mt][1]);
+        mma_u8s8_k32(ch[mt], ahi, q[cur][mt][2], q[cur][mt][3]);
+      }
+      const int sh = 16 * (g & 1);
+      const int s0l = (int)((sc0[g >> 1] >> sh) & 0xff), s0h = (int)((sc0[g >> 1] >> (sh + 8)) & 0xff);
+      const int s1l = (int)((sc1[g >> 1] >> sh) & 0xff), s1h = (int)((sc1[g >> 1] >> (sh + 8)) & 0xff);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        Slo[mt][0] += cl[mt][0] * s0l, Slo[mt][1] += cl[mt][1] * s0l, Slo[mt][2] += cl[mt][2] * s1l, Slo[mt][3] += cl[mt][3] * s1l;
+        Shi[mt][0] += ch[mt][0] * s0h, Shi[mt][1] += ch[mt][1] * s0h, Shi[mt][2] += ch[mt][2] * s1h, Shi[mt][3] += ch[mt][3] * s1h;
+      }
+    }
+    const float d0 = h2f_bits(h0.x & 0xffffu), dm0 = h2f_bits(h0.x >> 16);
+    const float d1 = h2f_bits(h1.x & 0xffffu), dm1 = h2f_bits(h1.x >> 16);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int m0 = 8 * mt + 2 * cx.tig;
+      const uint4 ba = lds128(cx.act_s + cx.L.off_aux + (uint32_t)m0 * cx.L.aux_stride + (uint32_t)b * 16u);
+      const uint4 bb = lds128(cx.act_s + cx.L.off_aux + (uint32_t)(m0 + 1) * cx.L.aux_stride + (uint32_t)b * 16u);
+      auto mins = [](const uint4& bs, const uint32_t (&mn)[2]) {
+        return __dp2a_hi((int)bs.w, (int)mn[1], __dp2a_lo((int)bs.z, (int)mn[1], __dp2a_hi((int)bs.y, (int)mn[0], __dp2a_lo((int)bs.x, (int)mn[0], 0))));
+      };
+      const int T0 = mins(ba, mn0), T1 = mins(bb, mn0), T2 = mins(ba, mn1), T3 = mins(bb, mn1);
+      const uint2 ydw = lds64(cx.act_s + cx.L.off_d + (uint32_t)(b * 16 + m0) * 4u);
+      const float ya = __uint_as_float(ydw.x), yb = __uint_as_float(ydw.y);
+      facc[mt][0] += (d0 * ya) * (float)(Slo[mt][0] + Shi[mt][0]) - (dm0 * ya) * (float)T0;
+      facc[mt][1] += (d0 * yb) * (float)(Slo[mt][1] + Shi[mt][1]) - (dm0 * yb) * (float)T1;
+      facc[mt][2] += (d1 * ya) * (float)(Slo[mt][2] + Shi[mt][2]) - (dm1 * ya) * (float)T2;
+      facc[mt][3] += (d1 * yb) * (float)(Slo[mt][3] + Shi[mt][3]) - (dm1 * yb) * (float)T3;
     }
   }
 };
