@@ -834,7 +834,7 @@ bool prefill_available(int type, int64_t m, int64_t n, int64_t k) {
     // The library's choice: 16 rows; 64 where the integer tensor-core kernel applies (16 rows per pass over the weights,
     // the later passes from L2) - still faster there than the bf16 GEMM, and the reference's own arithmetic.
     max_m = 16;
-    if (prefill_native_type(type) && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0 && k % 256 == 0) max_m = 64;
+    if ((prefill_native_type(type) || type == kQ5K) && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0 && k % 256 == 0) max_m = 64;
   }
   return (prefill_native_type(type) || prefill_slab_type(type)) && m > max_m && k % kPfTileK == 0 && k <= (1 << 20);
 }

@@ -60,7 +60,7 @@ int32_t fuelq_block_bytes(int32_t ggml_type);
                                     prefetch overlaps its predecessor's tail (default 0) */
 #define FUELQ_OPT_DECODE_MAX_M 2 /* largest m_total routed to the integer kernels; above it the tensor-core GEMM runs
                                     (every block format, k a multiple of 64). 0 (default) = the library's choice: 16,
-                                    and 64 for Q4_K / Q6_K / Q8_0 with k a multiple of 256 (the integer tensor-core
+                                    and 64 for Q4_K / Q5_K / Q6_K / Q8_0 with k a multiple of 256 (the integer tensor-core
                                     kernel, 16 rows per pass over the weights, is still the faster of the two there).
                                     Any positive value is taken as given */
 #define FUELQ_OPT_DECODE_GRID 3  /* CTAs for the decode kernel; 0 = two per SM (default) */

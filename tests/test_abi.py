@@ -102,7 +102,9 @@ def test_argument_validation_needs_no_device(L):
     assert f.fuelq_qmatmul_numerics(2, 17, 4096, 4096) == L.NUMERICS_F16
     assert f.fuelq_qmatmul_numerics(13, 2048, 4096, 4096) == L.NUMERICS_F16
     assert f.fuelq_qmatmul_workspace_bytes(13, 2048, 4096, 4096) == 2048 * 4096 * 2 + 2048 * 4 + 4096 * 4096 * 2
-    assert f.fuelq_qmatmul_workspace_bytes(13, 32, 1 << 20, 4096) == 32 * 4096 * 2 + 256 + (128 << 20)   # slab capped at 128 MiB
+    assert f.fuelq_qmatmul_workspace_bytes(2, 32, 1 << 20, 4096) == 32 * 4096 * 2 + 256 + (128 << 20)   # slab capped at 128 MiB
+    assert f.fuelq_qmatmul_numerics(13, 64, 4096, 4096) == L.NUMERICS_INTEGER    # Q5_K: the integer tensor-core kernel up to 64 rows
+    assert f.fuelq_qmatmul_numerics(13, 65, 4096, 4096) == L.NUMERICS_F16
     assert f.fuelq_qmatmul_numerics(2, 2048, 4096, 4096 + 32) == L.NUMERICS_INTEGER   # k not a multiple of 64: integer path
     assert f.fuelq_qmatmul_numerics(Q4K, 1, 4096, 100) == -L.INVALID_PROBLEM
 

@@ -18,8 +18,12 @@ NAMES = ["q4_0", "q4_1", "q5_0", "q5_1", "q2k", "q3k", "q5k"]
 def ops():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
-    from fuel_b200 import ops as _ops
+    from fuel_b200 import _lib, ops as _ops
+    # these tests are about the tensor-core path: put the crossover at 16 rows for every format (the library's own choice
+    # keeps Q5_K batches of up to 64 rows on the integer tensor-core kernel)
+    _lib.check(_lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 16), "set_option")
     yield _ops
+    _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 0)
     assert _ops.device_error() == 0, "a kernel recorded an expired bounded wait"
 
 
@@ -123,5 +127,5 @@ def test_crossover_option_keeps_the_integer_path(ops, oracle):
         assert _lib.lib.fuelq_qmatmul_numerics(int(t), m, n, k) == _lib.NUMERICS_INTEGER
         got = ops.qmatmul(t, torch.from_numpy(wb).cuda(), n, torch.from_numpy(x).cuda()).cpu().numpy()
     finally:
-        _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 0)
+        _lib.lib.fuelq_set_option(_lib.OPT_DECODE_MAX_M, 16)
     assert np.abs(got - want_int).max() / np.abs(want_int).max() <= 2e-6

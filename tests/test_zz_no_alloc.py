@@ -61,7 +61,7 @@ def test_static_scratch_runs_tensor_core_problems_without_a_slab():
     g = torch.Generator(device="cuda")
     for dtype, m, n, k, opt, val in ((T.Q4K, 100, 4096, 1024, _lib.OPT_PREFILL_ONE_KERNEL, 1),
                                      (T.Q6K, 80, 2048, 512, _lib.OPT_PREFILL_ONE_KERNEL, 1),
-                                     (T.Q5K, 20, 2048, 1024, _lib.OPT_DECODE_MAX_M, 1 << 20),
+                                     (T.Q5K, 70, 2048, 1024, _lib.OPT_DECODE_MAX_M, 1 << 20),
                                      (T.Q4_0, 33, 1024, 2048, _lib.OPT_DECODE_MAX_M, 1 << 20)):
         g.manual_seed(int(dtype) + m)
         w = ops.quantize_weights(dtype, torch.randn(n, k, generator=g, device="cuda") * 0.02)
