@@ -711,6 +711,8 @@ int32_t mma_batch_impl(int type, int n_groups, int64_t n, int64_t k, const void*
     case kQ5K: return mma_batch_fmt<MbQ5K>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
     case kQ6K: return mma_batch_fmt<MbQ6K>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
     case kQ8_0: return mma_batch_fmt<MbQ8_0>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
+    case kQ4_0: return mma_batch_fmt<MbQ4_0>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
+    case kQ5_0: return mma_batch_fmt<MbQ5_0>(n_groups, n, k, w, act, offsets, fixed_rows, out_rows, y, wide, stream);
     default: return kNotSupported;
   }
 }

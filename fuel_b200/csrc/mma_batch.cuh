@@ -395,6 +395,64 @@ struct MbQ8_0 {
   }
 };
 
+// ------------------------------------------------------------------------------------------------ Q4_0, Q5_0
+// 32-element blocks without a minimum (fuel-quantized/src/k_quants.rs:177-269, 463-559): f16 scale, for Q5_0 32 fifth bits,
+// 16 bytes of nibbles - byte t holds element t (low nibble) and element 16 + t (high nibble). The values minus their
+// offset (8, or 16 with the fifth bit) are signed bytes, so one s8 x s8 instruction per block against the Q8_0 activation
+// block gives the reference's integer sum directly; activation scales as for Q8_0.
+template <int kBlk, bool kFive>
+struct MbLegacy0 : MbQ8_0 {
+  static constexpr int kType = kFive ? kQ5_0 : kQ4_0;
+  static constexpr int kBytes256 = 8 * kBlk;  // 144 or 176: rows and chunks start on 16-byte boundaries
+  __device__ __forceinline__ static uint32_t spread4(uint32_t bits) {  // bit i of a nibble -> bit 4 of byte i
+    return (((bits & 0xFu) * 0x00204081u) & 0x01010101u) << 4;
+  }
+  template <int MT>
+  __device__ __forceinline__ static void block_step(const MbCtx& cx, int b, uint32_t, uint32_t, float (&facc)[MT][4]) {
+    const uint32_t r0 = cx.tile_s + cx.row_off(cx.gid) + (uint32_t)b * (uint32_t)kBytes256;
+    const uint32_t r1 = cx.tile_s + cx.row_off(cx.gid + 8) + (uint32_t)b * (uint32_t)kBytes256;
+    const uint32_t aq = cx.act_s + (uint32_t)((cx.lane & 7) + (MT == 2 ? 8 * (cx.lane >> 4) : 0)) * cx.L.astride + (uint32_t)b * 256u +
+                        16u * ((cx.lane >> 3) & 1);
+    constexpr uint32_t kOffQs = (uint32_t)kBlk - 16u;
+    constexpr uint32_t kBias = kFive ? 0x10101010u : 0x08080808u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t o = (uint32_t)kBlk * j;
+      const float dw0 = h2f_bits(lds_u16_addr(r0 + o)), dw1 = h2f_bits(lds_u16_addr(r1 + o));
+      const uint32_t w0 = lds_u32_2b_addr(r0 + o + kOffQs + 4u * cx.tig), w1 = lds_u32_2b_addr(r1 + o + kOffQs + 4u * cx.tig);
+      uint32_t lo0 = w0 & 0x0f0f0f0fu, hi0 = (w0 >> 4) & 0x0f0f0f0fu, lo1 = w1 & 0x0f0f0f0fu, hi1 = (w1 >> 4) & 0x0f0f0f0fu;
+      if (kFive) {  // bit t of qh belongs to element t, bit 16 + t to element 16 + t
+        const uint32_t h0 = lds_u32_2b_addr(r0 + o + 2u), h1 = lds_u32_2b_addr(r1 + o + 2u);
+        lo0 |= spread4(h0 >> (4 * cx.tig)), hi0 |= spread4(h0 >> (16 + 4 * cx.tig));
+        lo1 |= spread4(h1 >> (4 * cx.tig)), hi1 |= spread4(h1 >> (16 + 4 * cx.tig));
+      }
+      uint32_t a[4];
+      a[0] = __vsub4(lo0, kBias), a[1] = __vsub4(lo1, kBias), a[2] = __vsub4(hi0, kBias), a[3] = __vsub4(hi1, kBias);
+      uint32_t q[4];
+      if (MT == 2) {
+        ldmatrix_x4(q, aq + 32u * j);
+      } else {
+        uint32_t q2[2];
+        ldmatrix_x2(q2, aq + 32u * j);
+        q[0] = q2[0], q[1] = q2[1], q[2] = 0, q[3] = 0;
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        int c[4];
+        mma_s8s8_k32(c, a, q[2 * mt], q[2 * mt + 1]);
+        const uint2 ydw = lds64(cx.act_s + cx.L.off_d + (uint32_t)((b * 8 + j) * 16 + 8 * mt + 2 * cx.tig) * 4u);
+        const float ya = __uint_as_float(ydw.x), yb = __uint_as_float(ydw.y);
+        facc[mt][0] += (dw0 * ya) * (float)c[0];
+        facc[mt][1] += (dw0 * yb) * (float)c[1];
+        facc[mt][2] += (dw1 * ya) * (float)c[2];
+        facc[mt][3] += (dw1 * yb) * (float)c[3];
+      }
+    }
+  }
+};
+using MbQ4_0 = MbLegacy0<18, false>;
+using MbQ5_0 = MbLegacy0<22, true>;
+
 // ------------------------------------------------------------------------------------------------ Q6_K
 struct MbQ6K {
   static constexpr int kType = kQ6K;
