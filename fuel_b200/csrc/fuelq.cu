@@ -722,7 +722,9 @@ int32_t mma_batch_impl(int type, int n_groups, int64_t n, int64_t k, const void*
 int32_t decode_chunked(int type, int64_t m_total, int64_t n, int64_t k, const void* w, void* packed_act, float* y,
                        cudaStream_t stream) {
   const ActPlanes all = act_planes(packed_act, type, m_total, k);
-  if (m_total >= g_opt.dbg_mb_min_m && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0) {
+  // (Q4_0 / Q5_0 have no register-resident one-row kernel: their single rows take this path too, measured 11.9 against
+  // 14.3 us on the generic kernel for 4096 -> 11008)
+  if ((m_total >= g_opt.dbg_mb_min_m || type == kQ4_0 || type == kQ5_0) && g_opt.decode_kernel == 0 && g_opt.moe_kernel == 0) {
     // a few rows: one pass over the weights on the integer tensor cores (up to 16 rows per pass)
     const int32_t st = mma_batch_impl(type, 1, n, k, w, all, nullptr, (int)m_total, nullptr, y, m_total > 8, stream);
     if (st != kNotSupported) return st;
